@@ -1,0 +1,82 @@
+"""In-tree build of libcavs_b200.so (host C++ + sm_100a CUDA kernels behind the C ABI).
+
+    python -m cavs_b200.build [--force] [--verbose]
+
+Every .cc/.cu under cavs_b200/csrc is compiled with nvcc for sm_100a only
+(-gencode arch=compute_100a,code=sm_100a) and linked into one shared library next
+to this file.  Objects are cached under cavs_b200/build/ and rebuilt when the
+source or any header is newer.
+"""
+from __future__ import annotations
+
+import concurrent.futures
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+ROOT = PKG.parent
+CSRC = PKG / "csrc"
+OBJ = PKG / "build"
+LIB = PKG / "libcavs_b200.so"
+
+NVCC = os.environ.get("CAVS_NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON = ["-std=c++17", "-O3", "-lineinfo", f"-I{ROOT / 'include'}", f"-I{CSRC}", "-Xcompiler", "-fPIC,-Wall,-fvisibility=hidden"]
+CUFLAGS = ["--expt-relaxed-constexpr", "-Xptxas", "-v" if os.environ.get("CAVS_PTXAS_V") else "-O3"]
+
+
+def _sources():
+    return sorted(list(CSRC.rglob("*.cc")) + list(CSRC.rglob("*.cu")))
+
+
+def _headers_mtime() -> float:
+    hs = list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list((ROOT / "include").glob("*.h"))
+    return max((h.stat().st_mtime for h in hs), default=0.0)
+
+
+def _compile(src: Path, obj: Path, verbose: bool) -> str:
+    cmd = [NVCC, *ARCH, *COMMON]
+    if src.suffix == ".cu":
+        cmd += CUFLAGS
+    else:
+        cmd += ["-x", "cu"] if False else []
+    cmd += ["-c", str(src), "-o", str(obj)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    out = (r.stdout + r.stderr).strip()
+    if verbose and out:
+        return f"--- {src.name}\n{out}"
+    return ""
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    hdr_m = _headers_mtime()
+    jobs, objs = [], []
+    for src in _sources():
+        obj = OBJ / (str(src.relative_to(CSRC)).replace("/", "__") + ".o")
+        objs.append(obj)
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_m):
+            jobs.append((src, obj))
+    if jobs:
+        with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
+            for msg in ex.map(lambda j: _compile(j[0], j[1], verbose), jobs):
+                if msg:
+                    print(msg)
+    stale = [o for o in OBJ.glob("*.o") if o not in objs]
+    for o in stale:
+        o.unlink()
+    if jobs or force or not LIB.exists():
+        cmd = [NVCC, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(p)

@@ -1,0 +1,52 @@
+"""PyTorch-CPU restatement of the child-sum Tree-LSTM vertex function with autograd,
+used only to cross-check the C oracle (secondary oracle; float64 capable)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+def treelstm_autograd(tb, tok, label, params, H, E, V, C, K=2, dtype=torch.float64, loss_rows=0):
+    """Aligned tables only.  Returns dict with state, loss and gradients as numpy arrays."""
+    n = int(tb["n"])
+    P = {k: torch.tensor(np.asarray(v), dtype=dtype, requires_grad=True) for k, v in params.items()}
+    Emb, W, U, B, Wc, bc = (P[k] for k in ("Emb", "W", "U", "B", "Wc", "bc"))
+    U_iou = U[: 3 * H * H].reshape(H, 3 * H)
+    U_f = U[3 * H * H:].reshape(H, H)
+    b_i, b_f, b_u, b_o = B[:H], B[H:2 * H], B[2 * H:3 * H], B[3 * H:]
+    tok_t = torch.tensor(np.asarray(tok), dtype=torch.long)
+    x = Emb[tok_t]
+    a = x @ W.reshape(E, 4 * H)
+    hs = [None] * n
+    cs = [None] * n
+    zero = torch.zeros(H, dtype=dtype)
+    lo = tb["level_off"]
+    fg = tb["fg"]
+    for l in range(int(tb["n_levels"])):
+        for t in range(int(lo[l]), int(lo[l + 1])):
+            hk = [hs[int(fg[c][t])] if fg[c][t] >= 0 else zero for c in range(K)]
+            ck = [cs[int(fg[c][t])] if fg[c][t] >= 0 else zero for c in range(K)]
+            s = sum(hk[1:], hk[0])
+            p = s @ U_iou
+            i = torch.sigmoid(a[t, :H] + p[:H] + b_i)
+            o = torch.sigmoid(a[t, H:2 * H] + p[H:2 * H] + b_o)
+            u = torch.tanh(a[t, 2 * H:3 * H] + p[2 * H:] + b_u)
+            c_new = i * u
+            for c in range(K):
+                f = torch.sigmoid(a[t, 3 * H:] + hk[c] @ U_f + b_f)
+                c_new = c_new + f * ck[c]
+            hs[t] = o * torch.tanh(c_new)
+            cs[t] = c_new
+    Hout = torch.stack(hs)
+    z = Hout @ Wc.t() + bc
+    lab = torch.tensor(np.asarray(label), dtype=torch.long)
+    mask = lab >= 0
+    logp = torch.log_softmax(z, dim=1)
+    loss_rows_v = -logp[torch.arange(n), lab.clamp(min=0)] * mask
+    rows = loss_rows if loss_rows > 0 else n
+    (loss_rows_v.sum() / rows).backward()
+    out = dict(state=torch.cat([Hout, torch.stack(cs)], dim=1).detach().numpy(), loss=loss_rows_v.detach().numpy())
+    for k in ("Emb", "W", "U", "B", "Wc", "bc"):
+        g = P[k].grad
+        out["d" + k] = (g if g is not None else torch.zeros_like(P[k])).numpy()
+    return out
