@@ -10,6 +10,8 @@
 namespace cavs_b200 {
 // Records msg as the calling thread's last error and returns code.
 int Fail(int code, const std::string& msg);
+// Process-wide count of kernels this library has launched (see cavs_launch_count).
+void CountLaunch();
 }  // namespace cavs_b200
 
 #define CAVS_REQUIRE(cond, code, msg) \
@@ -28,6 +30,7 @@ int Fail(int code, const std::string& msg);
     cudaError_t _e = cudaGetLastError();                                                                 \
     if (_e != cudaSuccess)                                                                               \
       return ::cavs_b200::Fail(CAVS_ERR_CUDA, std::string(name) + " launch: " + cudaGetErrorString(_e)); \
+    ::cavs_b200::CountLaunch();                                                                          \
   } while (0)
 #endif
 

@@ -1,0 +1,492 @@
+// Level-batched execution of the child-sum Tree-LSTM vertex function, forward and
+// backward: the host-side level loop.
+//
+// Replaces GraphStatement::Run / GraphGradStatement::Run (cavs/midend/statement.cc:43-123)
+// and the per-op prologue ExprStatement::Run (statement.cc:8-41).  Differences that matter:
+//   * the input projection x.W does not depend on children, so it is one GEMM over all
+//     vertices before the loop instead of one per level (tree-lstm-cavs.cc:146);
+//   * level 0 holds only leaves, whose recurrent GEMMs multiply zero rows in the reference
+//     (op_impl_graphop.cu:77-86); they are skipped, which is exact;
+//   * per level the forward pass is 4 launches (gather, 2 GEMMs, fused cell) and the
+//     backward pass 4 (fused cell-grad, 2 GEMMs, scatter) instead of ~46 / ~90;
+//   * weight, bias and embedding gradients are deferred to one pass over all vertices after
+//     the loop, as BatchingWeightUpdater does (cavs/midend/batch_weight_updater.h:10-85);
+//   * all index tables of the batch arrive in one pinned upload; no per-op host-to-device
+//     copy and no device synchronisation inside a step.
+// Per-vertex tensors live in tensor-id (execution) order, so a level is a contiguous row
+// range [level_off[l], level_off[l+1]) of every arena (cf. graph_session.cc:27-43).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "abi_common.h"
+#include "host/sched_handle.h"
+#include "kernels/cell.h"
+#include "kernels/gemm.h"
+
+using namespace cavs_b200;
+
+struct cavs_treelstm {
+  cavs_treelstm_config cfg{};
+  bool bf16 = false;
+  size_t elt = 4;               // bytes per GEMM-operand element
+  // ---- device workspace views ----
+  int32_t* d_idx = nullptr;     // index blob, mirrored by h_idx (pinned)
+  int32_t* h_idx = nullptr;
+  size_t idx_ints = 0;
+  uint8_t *X = nullptr, *S = nullptr, *HK = nullptr, *dA = nullptr, *ZF = nullptr;   // GEMM operands (fp32 or bf16)
+  float *A = nullptr, *P = nullptr, *Q = nullptr, *gates = nullptr, *state = nullptr, *mailbox = nullptr;
+  float *dOut = nullptr, *ds = nullptr, *dq = nullptr, *dX = nullptr, *loss = nullptr, *dB_tmp = nullptr;
+  float* tail = nullptr;        // [0] loss sum, [1] status word (int)
+  float *loss_scratch = nullptr, *col_scratch = nullptr, *emb_scratch = nullptr, *splitk_scratch = nullptr;
+  size_t splitk_bytes = 0;
+  uint8_t *W_bf = nullptr, *U_bf = nullptr;
+  float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
+  // ---- current batch ----
+  int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
+  std::vector<int32_t> level_off;
+  int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
+          *seg_first_chunk = nullptr, *seg_tok = nullptr;
+  std::vector<int32_t> bucket;
+  // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
+  bool prof_on = false;
+  std::vector<cudaEvent_t> ev_pool;
+  size_t ev_used = 0;
+  struct Rec { int cls; cudaEvent_t a, b; double work; };
+  std::vector<Rec> recs;
+  cudaEvent_t NextEvent() {
+    if (ev_used == ev_pool.size()) { cudaEvent_t ev; cudaEventCreate(&ev); ev_pool.push_back(ev); }
+    return ev_pool[ev_used++];
+  }
+
+  size_t OffW() const { return static_cast<size_t>(cfg.vocab) * cfg.embed; }
+  size_t OffU() const { return OffW() + static_cast<size_t>(cfg.embed) * 4 * cfg.hidden; }
+  size_t OffB() const { return OffU() + static_cast<size_t>(4) * cfg.hidden * cfg.hidden; }
+  size_t OffWc() const { return OffB() + static_cast<size_t>(4) * cfg.hidden; }
+  size_t Offbc() const { return OffWc() + static_cast<size_t>(cfg.classes) * cfg.hidden; }
+  size_t ParamCount() const { return Offbc() + cfg.classes; }
+  int* Status() const { return reinterpret_cast<int*>(tail + 1); }
+};
+
+namespace {
+
+size_t Align(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+struct Carver {
+  uint8_t* base;
+  size_t used = 0;
+  explicit Carver(void* b) : base(static_cast<uint8_t*>(b)) {}
+  template <typename T> T* Take(size_t count) {
+    T* p = base ? reinterpret_cast<T*>(base + used) : nullptr;
+    used += Align(count * sizeof(T));
+    return p;
+  }
+};
+
+// Kernel classes reported by cavs_treelstm_profile_read.  "work" is algorithmic flops for the
+// GEMM class and algorithmic bytes (the kernel interface's inputs + outputs) for the others.
+enum ProfClass { kProfGemm = 0, kProfCellFwd, kProfCellBwd, kProfGatherH, kProfScatterGrad, kProfLossHead, kProfEmbedFwd,
+                 kProfEmbedBwd, kProfColumnSum, kProfCount };
+
+// Runs `call` (an int-returning launch) bracketed by events when profiling is on.
+#define PROF(e, cls, work_expr, st, call)                                   \
+  do {                                                                      \
+    int _rc;                                                                \
+    if ((e)->prof_on) {                                                     \
+      cudaEvent_t _a = (e)->NextEvent(), _b = (e)->NextEvent();             \
+      cudaEventRecord(_a, st);                                              \
+      _rc = (call);                                                         \
+      cudaEventRecord(_b, st);                                              \
+      (e)->recs.push_back({cls, _a, _b, static_cast<double>(work_expr)});   \
+    } else {                                                                \
+      _rc = (call);                                                         \
+    }                                                                       \
+    if (_rc) return _rc;                                                    \
+  } while (0)
+
+int CheckConfig(const cavs_treelstm_config* c) {
+  CAVS_REQUIRE(c, CAVS_ERR_BAD_ARG, "treelstm: null config");
+  CAVS_REQUIRE(c->hidden > 0 && c->embed > 0 && c->vocab > 0 && c->classes > 0, CAVS_ERR_BAD_ARG, "treelstm: sizes must be positive");
+  CAVS_REQUIRE(c->n_slots >= 1 && c->n_slots <= kMaxSlots, CAVS_ERR_BAD_ARG, "treelstm: child slots must be 1..4");
+  CAVS_REQUIRE(c->max_vertices > 0 && c->max_level_rows > 0 && c->max_level_rows <= c->max_vertices, CAVS_ERR_BAD_ARG,
+               "treelstm: capacities must be positive and max_level_rows <= max_vertices");
+  CAVS_REQUIRE(c->classes <= 8, CAVS_ERR_UNSUPPORTED, "treelstm: the fused loss head supports at most 8 classes");
+  if (c->gemm_bf16)
+    CAVS_REQUIRE(c->hidden % 8 == 0 && c->embed % 8 == 0, CAVS_ERR_BAD_ARG,
+                 "treelstm: the tensor-core path needs hidden and embed to be multiples of 8 (16-byte TMA rows)");
+  return CAVS_OK;
+}
+
+size_t MaxSegments(const cavs_treelstm_config& c) { return std::min<size_t>(c.max_vertices, c.vocab); }
+size_t MaxChunks(const cavs_treelstm_config& c) { return MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
+size_t IdxInts(const cavs_treelstm_config& c) {
+  const size_t n = c.max_vertices;
+  return (c.n_slots + 4) * n + (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
+}
+
+// Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
+size_t SplitKBytes(const cavs_treelstm_config& c) {
+  if (!c.gemm_bf16) return 0;
+  const int N = c.max_vertices, H = c.hidden, E = c.embed, K = c.n_slots;
+  size_t b = GemmBf16ScratchBytes(E, 4 * H, 32);
+  b = std::max(b, GemmBf16ScratchBytes(H, 3 * H, 32));
+  b = std::max(b, GemmBf16ScratchBytes(H, H, 32));
+  (void)N; (void)K;
+  return b;
+}
+
+// Carves every device array out of the workspace; with base == nullptr it only sizes it.
+size_t Carve(cavs_treelstm* e, void* base) {
+  const cavs_treelstm_config& c = e->cfg;
+  const size_t N = c.max_vertices, L = c.max_level_rows, H = c.hidden, E = c.embed, K = c.n_slots;
+  const size_t elt = c.gemm_bf16 ? 2 : 4;
+  Carver w(base);
+  e->d_idx = w.Take<int32_t>(IdxInts(c));
+  e->X = w.Take<uint8_t>(N * E * elt);
+  e->S = w.Take<uint8_t>(N * H * elt);
+  e->HK = w.Take<uint8_t>(N * K * H * elt);
+  e->dA = w.Take<uint8_t>(N * 4 * H * elt);
+  e->ZF = w.Take<uint8_t>(N * K * H * elt);
+  e->A = w.Take<float>(N * 4 * H);
+  e->P = w.Take<float>(L * 3 * H);
+  e->Q = w.Take<float>(L * K * H);
+  e->gates = w.Take<float>(N * (3 + K) * H);
+  e->state = w.Take<float>(N * 2 * H);
+  e->mailbox = w.Take<float>(N * 2 * H);
+  e->dOut = w.Take<float>(N * H);
+  e->ds = w.Take<float>(L * H);
+  e->dq = w.Take<float>(L * K * H);
+  e->dX = w.Take<float>(N * E);
+  e->loss = w.Take<float>(N);
+  e->dB_tmp = w.Take<float>(4 * H);
+  e->tail = w.Take<float>(4);
+  e->loss_scratch = w.Take<float>(LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
+  e->col_scratch = w.Take<float>(ColumnSumScratchBytes(4 * c.hidden) / sizeof(float));
+  e->emb_scratch = w.Take<float>(MaxChunks(c) * E);
+  e->splitk_bytes = SplitKBytes(c);
+  e->splitk_scratch = w.Take<float>(e->splitk_bytes / sizeof(float));
+  e->W_bf = w.Take<uint8_t>(c.gemm_bf16 ? static_cast<size_t>(E) * 4 * H * 2 : 0);
+  e->U_bf = w.Take<uint8_t>(c.gemm_bf16 ? static_cast<size_t>(4) * H * H * 2 : 0);
+  return w.used;
+}
+
+// One GEMM of the step in either precision.  `a_t` / `b_t`: operand is used transposed
+// relative to its row-major storage (a_t: A stored [k,m]; b_t: B stored [n,k]).
+int Gemm(cavs_treelstm* e, float* c, long long ldc, int accumulate, const void* a, long long lda, bool a_t, const void* b,
+         long long ldb, bool b_t, int m, int n, int k, bool split_ok, cudaStream_t st) {
+  if (m == 0 || n == 0 || k == 0) return CAVS_OK;
+  if (e->bf16) {
+    GemmBf16Args g;
+    g.c = c; g.ldc = ldc; g.out_mode = accumulate ? 1 : 0;
+    g.a = a; g.lda = lda; g.a_major = a_t ? 1 : 0;   // stored [k,m] = MN-major
+    g.b = b; g.ldb = ldb; g.b_major = b_t ? 0 : 1;   // stored [n,k] = K-major, [k,n] = MN-major
+    g.m = m; g.n = n; g.k = k;
+    g.status = e->Status();
+    if (split_ok) {
+      g.splits = GemmBf16SplitsFor(m, n, k);
+      g.scratch = e->splitk_scratch; g.scratch_bytes = e->splitk_bytes;
+    }
+    PROF(e, kProfGemm, 2.0 * m * n * k, st, GemmBf16(g, st));
+    return CAVS_OK;
+  }
+  GemmF32Args g;
+  g.c = c; g.ldc = ldc; g.accumulate = accumulate;
+  g.a = static_cast<const float*>(a); g.a_rs = a_t ? 1 : lda; g.a_cs = a_t ? lda : 1;
+  g.b = static_cast<const float*>(b); g.b_rs = b_t ? 1 : ldb; g.b_cs = b_t ? ldb : 1;
+  g.m = m; g.n = n; g.k = k;
+  PROF(e, kProfGemm, 2.0 * m * n * k, st, GemmF32(g, st));
+  return CAVS_OK;
+}
+
+}  // namespace
+
+extern "C" size_t cavs_treelstm_param_count(const cavs_treelstm_config* cfg) {
+  if (CheckConfig(cfg) != CAVS_OK) return 0;
+  cavs_treelstm tmp; tmp.cfg = *cfg;
+  return tmp.ParamCount();
+}
+
+extern "C" size_t cavs_treelstm_workspace_bytes(const cavs_treelstm_config* cfg) {
+  if (CheckConfig(cfg) != CAVS_OK) return 0;
+  cavs_treelstm tmp; tmp.cfg = *cfg;
+  return Carve(&tmp, nullptr);
+}
+
+extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* workspace, size_t workspace_bytes,
+                                    cavs_treelstm** out) {
+  if (int rc = CheckConfig(cfg)) return rc;
+  CAVS_REQUIRE(out && workspace, CAVS_ERR_BAD_ARG, "treelstm_create: null pointer");
+  CAVS_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, CAVS_ERR_BAD_ARG, "treelstm_create: workspace must be 256-byte aligned");
+  auto* e = new cavs_treelstm();
+  e->cfg = *cfg;
+  e->bf16 = cfg->gemm_bf16 != 0;
+  e->elt = e->bf16 ? 2 : 4;
+  const size_t need = Carve(e, workspace);
+  if (need > workspace_bytes) {
+    delete e;
+    return Fail(CAVS_ERR_CAPACITY, "treelstm_create: workspace needs " + std::to_string(need) + " bytes");
+  }
+  e->idx_ints = IdxInts(*cfg);
+  cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
+  if (err != cudaSuccess) {
+    delete e;
+    return Fail(CAVS_ERR_CUDA, std::string("treelstm_create: pinned staging: ") + cudaGetErrorString(err));
+  }
+  err = cudaMemset(e->tail, 0, 4 * sizeof(float));
+  if (err != cudaSuccess) {
+    cudaFreeHost(e->h_idx);
+    delete e;
+    return Fail(CAVS_ERR_CUDA, std::string("treelstm_create: ") + cudaGetErrorString(err));
+  }
+  *out = e;
+  return CAVS_OK;
+}
+
+extern "C" void cavs_treelstm_destroy(cavs_treelstm* e) {
+  if (!e) return;
+  if (e->h_idx) cudaFreeHost(e->h_idx);
+  for (cudaEvent_t ev : e->ev_pool) cudaEventDestroy(ev);
+  delete e;
+}
+
+extern "C" int cavs_treelstm_bind(cavs_treelstm* e, float* params, float* grads) {
+  CAVS_REQUIRE(e && params && grads, CAVS_ERR_BAD_ARG, "treelstm_bind: null pointer");
+  CAVS_REQUIRE(((reinterpret_cast<uintptr_t>(params) | reinterpret_cast<uintptr_t>(grads)) & 15u) == 0, CAVS_ERR_BAD_ARG,
+               "treelstm_bind: buffers must be 16-byte aligned");
+  e->params = params;
+  e->grads = grads;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_refresh_weights: parameters not bound");
+  if (!e->bf16) return CAVS_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t H = e->cfg.hidden, E = e->cfg.embed;
+  // W and U are adjacent in the flat buffer, and so are their bf16 shadows only logically;
+  // cast them separately into their own 16-byte aligned arrays.
+  if (int rc = LaunchCastBf16(e->W_bf, e->params + e->OffW(), E * 4 * H, st)) return rc;
+  return LaunchCastBf16(e->U_bf, e->params + e->OffU(), 4 * H * H, st);
+}
+
+extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job,
+                                        const int32_t* label_job, int loss_rows, void* stream) {
+  CAVS_REQUIRE(e && s && s->loaded && tok_job && label_job, CAVS_ERR_BAD_ARG, "treelstm_load_batch: null pointer or empty schedule");
+  const LevelSchedule& sch = s->impl;
+  const int n = sch.n_scheduled(), nt = sch.n_total(), K = e->cfg.n_slots;
+  CAVS_REQUIRE(sch.n_slots() == K, CAVS_ERR_BAD_ARG, "treelstm_load_batch: schedule was built with a different slot count");
+  CAVS_REQUIRE(nt <= e->cfg.max_vertices, CAVS_ERR_CAPACITY,
+               "treelstm_load_batch: batch has " + std::to_string(nt) + " vertices, capacity " + std::to_string(e->cfg.max_vertices));
+  CAVS_REQUIRE(sch.max_level_rows() <= e->cfg.max_level_rows, CAVS_ERR_CAPACITY,
+               "treelstm_load_batch: widest level has " + std::to_string(sch.max_level_rows()) + " rows, capacity " +
+                   std::to_string(e->cfg.max_level_rows));
+  e->n = n; e->n_total = nt; e->n_levels = sch.n_levels();
+  e->loss_rows = loss_rows > 0 ? loss_rows : std::max(n, 1);
+  e->level_off = sch.level_off();
+
+  // Pack the blob: child | parent | tok | label | order | chunk_off | seg_first_chunk | seg_tok.
+  int32_t* h = e->h_idx;
+  size_t o = 0;
+  auto view = [&](size_t count, int32_t** dev) { int32_t* p = h + o; *dev = e->d_idx + o; o += count; return p; };
+  int32_t* h_child = view(static_cast<size_t>(K) * nt, &e->child);
+  int32_t* h_parent = view(nt, &e->parent);
+  int32_t* h_tok = view(nt, &e->tok);
+  int32_t* h_label = view(nt, &e->label);
+  int32_t* h_order = view(nt, &e->order);
+  std::memcpy(h_child, sch.child_t().data(), sizeof(int32_t) * K * nt);
+  std::memcpy(h_parent, sch.parent_t().data(), sizeof(int32_t) * nt);
+  const int32_t* t2j = sch.t2j().data();
+  const int V = e->cfg.vocab;
+  // Pull (op_impl_graphop.cu:214-254) and the label permutation FunctionPopRet implies
+  // (:275-327) are folded into this host-side reorder to tensor-id order.
+  for (int t = 0; t < n; ++t) {
+    int id = tok_job[t2j[t]];
+    h_tok[t] = (id < 0 || id >= V) ? 0 : id;
+    h_label[t] = label_job[t2j[t]];
+  }
+  // Stable counting sort of rows by token -> segments and chunks for the embedding gradient.
+  e->bucket.assign(static_cast<size_t>(V) + 1, 0);
+  for (int t = 0; t < n; ++t) ++e->bucket[h_tok[t] + 1];
+  int n_seg = 0;
+  for (int v = 0; v < V; ++v) { if (e->bucket[v + 1]) ++n_seg; e->bucket[v + 1] += e->bucket[v]; }
+  int n_chunks = 0;
+  for (int v = 0; v < V; ++v) n_chunks += (e->bucket[v + 1] - e->bucket[v] + kEmbedChunk - 1) / kEmbedChunk;
+  int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &e->chunk_off);
+  int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &e->seg_first_chunk);
+  int32_t* h_seg_tok = view(n_seg, &e->seg_tok);
+  CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
+  int si = 0, ci = 0;
+  for (int v = 0; v < V; ++v) {
+    const int b0 = e->bucket[v], b1 = e->bucket[v + 1];
+    if (b0 == b1) continue;
+    h_seg_tok[si] = v;
+    h_seg_first[si++] = ci;
+    for (int b = b0; b < b1; b += kEmbedChunk) h_chunk_off[ci++] = b;
+  }
+  h_seg_first[si] = ci;
+  h_chunk_off[ci] = n;
+  for (int t = 0; t < n; ++t) h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
+  e->n_seg = n_seg; e->n_chunks = n_chunks;
+  CAVS_CUDA(cudaMemcpyAsync(e->d_idx, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_forward: parameters not bound");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n = e->n, nt = e->n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots;
+  if (n == 0) return CAVS_OK;
+  const float* Emb = e->params;
+  const void* W = e->bf16 ? static_cast<const void*>(e->W_bf) : e->params + e->OffW();
+  const uint8_t* U = e->bf16 ? e->U_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffU());
+  const void* U_iou = U;
+  const void* U_f = U + static_cast<size_t>(3) * H * H * e->elt;
+  const float* B = e->params + e->OffB();
+  int rc;
+  const double elt = static_cast<double>(e->elt);
+  PROF(e, kProfEmbedFwd, static_cast<double>(n) * (4 + 4.0 * E + elt * E), st,
+       LaunchEmbedFwd(e->X, e->bf16, Emb, e->tok, n, E, e->cfg.vocab, st));
+  if ((rc = Gemm(e, e->A, 4 * H, 0, e->X, E, false, W, 4 * H, false, n, 4 * H, E, false, st))) return rc;
+  for (int l = 0; l < e->n_levels; ++l) {
+    const int off = e->level_off[l], rows = e->level_off[l + 1] - off;
+    if (l == 0) {
+      // leaf rows: read A (4H), write gates ((3+K)H) and h|c (2H)
+      PROF(e, kProfCellFwd, 4.0 * rows * H * (4 + 3 + K + 2), st,
+           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, B, e->child, nt, off, rows, H, K, true, st));
+      continue;
+    }
+    // read K child h rows (fp32) + K indices, write S and HK
+    PROF(e, kProfGatherH, static_cast<double>(rows) * (4.0 * K * H + 4.0 * K + elt * (1 + K) * H), st,
+         LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, e->child, nt, off, rows, H, K, st));
+    const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
+    const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
+    if ((rc = Gemm(e, e->P, 3 * H, 0, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st))) return rc;
+    if ((rc = Gemm(e, e->Q, H, 0, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st))) return rc;
+    // read A (4H), P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
+    PROF(e, kProfCellFwd, 4.0 * rows * H * (4 + 3 + K + K + 3 + K + 2), st,
+         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, B, e->child, nt, off, rows, H, K, false, st));
+  }
+  (void)rc;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e && e->params && e->grads, CAVS_ERR_BAD_ARG, "treelstm_backward: parameters / gradients not bound");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int n = e->n, nt = e->n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots, C = e->cfg.classes;
+  float* g = e->grads;
+  if (n == 0) {
+    CAVS_CUDA(cudaMemsetAsync(g, 0, e->ParamCount() * sizeof(float), st));
+    return CAVS_OK;
+  }
+  const void* W = e->bf16 ? static_cast<const void*>(e->W_bf) : e->params + e->OffW();
+  const uint8_t* U = e->bf16 ? e->U_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffU());
+  const void* U_iou = U;
+  const void* U_f = U + static_cast<size_t>(3) * H * H * e->elt;
+  int rc;
+  const double elt = static_cast<double>(e->elt);
+  // Loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
+  // write loss and d(h) (H).
+  PROF(e, kProfLossHead, static_cast<double>(n) * (8.0 * H + 8), st,
+       LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, e->label,
+                      e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(e->loss_rows),
+                      e->loss_scratch, st));
+  for (int l = e->n_levels - 1; l >= 0; --l) {
+    const int off = e->level_off[l], rows = e->level_off[l + 1] - off;
+    // read dOut (H), mailbox (2H), gates ((3+K)H), own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
+    const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 3 + K + 1) + elt * 4)
+                                     : rows * H * (4.0 * (1 + 2 + 3 + K + 1 + K + K) + elt * (4 + K));
+    PROF(e, kProfCellBwd, cell_bytes, st,
+         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, e->dOut, e->gates, e->state, e->child, e->parent, nt, off, rows, H,
+                       K, l == 0, st));
+    if (l == 0) break;
+    const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
+    const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
+    // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
+    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st))) return rc;
+    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st))) return rc;
+    PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
+         LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, e->child, nt, off, rows, H, K, st));
+  }
+  // Deferred gradients over all rows at once.
+  const int off1 = e->n_levels > 1 ? e->level_off[1] : n;   // first internal row
+  const int n_int = n - off1;
+  if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dA, 4 * H, false, E, 4 * H, n, true, st))) return rc;
+  float* dU = g + e->OffU();
+  if (n_int > 0) {
+    const uint8_t* S1 = e->S + static_cast<size_t>(off1) * H * e->elt;
+    const uint8_t* dA1 = e->dA + static_cast<size_t>(off1) * 4 * H * e->elt;
+    const uint8_t* HK1 = e->HK + static_cast<size_t>(off1) * K * H * e->elt;
+    const uint8_t* ZF1 = e->ZF + static_cast<size_t>(off1) * K * H * e->elt;
+    if ((rc = Gemm(e, dU, 3 * H, 0, S1, H, true, dA1, 4 * H, false, H, 3 * H, n_int, true, st))) return rc;
+    if ((rc = Gemm(e, dU + static_cast<size_t>(3) * H * H, H, 0, HK1, H, true, ZF1, H, false, H, H, n_int * K, true, st))) return rc;
+  } else {
+    CAVS_CUDA(cudaMemsetAsync(dU, 0, static_cast<size_t>(4) * H * H * sizeof(float), st));
+  }
+  // Bias gradient: column sums of dA, gate order i,o,u,f -> bias order i,f,u,o.
+  PROF(e, kProfColumnSum, static_cast<double>(n) * 4 * H * elt, st,
+       LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
+  // dX = dA W^T, then the segmented embedding gradient.
+  if ((rc = Gemm(e, e->dX, E, 0, e->dA, 4 * H, false, W, 4 * H, true, n, E, 4 * H, false, st))) return rc;
+  CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
+  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * E) + 4.0 * E * e->n_seg, st,
+       LaunchEmbedBwd(g, e->dX, e->order, nullptr, e->chunk_off, e->n_chunks, e->seg_first_chunk, e->seg_tok, e->n_seg,
+                      e->emb_scratch, E, st));
+  (void)rc;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_profile(cavs_treelstm* e, int enable) {
+  CAVS_REQUIRE(e, CAVS_ERR_BAD_ARG, "treelstm_profile: null handle");
+  e->prof_on = enable != 0;
+  e->recs.clear();
+  e->ev_used = 0;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes) {
+  CAVS_REQUIRE(e && ms && work && launches && n_classes >= kProfCount, CAVS_ERR_BAD_ARG,
+               "treelstm_profile_read: need arrays of at least 9 entries");
+  for (int i = 0; i < n_classes; ++i) { ms[i] = 0; work[i] = 0; launches[i] = 0; }
+  for (const auto& r : e->recs) {
+    CAVS_CUDA(cudaEventSynchronize(r.b));
+    float t = 0;
+    CAVS_CUDA(cudaEventElapsedTime(&t, r.a, r.b));
+    ms[r.cls] += t; work[r.cls] += r.work; launches[r.cls] += 1;
+  }
+  e->recs.clear();
+  e->ev_used = 0;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int* status_host, void* stream) {
+  CAVS_REQUIRE(e && loss_sum_host, CAVS_ERR_BAD_ARG, "treelstm_read_loss: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float host[2];
+  CAVS_CUDA(cudaMemcpyAsync(host, e->tail, sizeof(host), cudaMemcpyDeviceToHost, st));
+  CAVS_CUDA(cudaStreamSynchronize(st));
+  *loss_sum_host = host[0];
+  int status;
+  std::memcpy(&status, &host[1], sizeof(int));
+  if (status_host) *status_host = status;
+  CAVS_REQUIRE(status == 0, CAVS_ERR_TIMEOUT, "treelstm: a bounded device-side wait expired during the step");
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes) {
+  CAVS_REQUIRE(e && dev_ptr && bytes, CAVS_ERR_BAD_ARG, "treelstm_peek: null pointer");
+  const size_t n = e->n, H = e->cfg.hidden;
+  switch (what) {
+    case 0: *dev_ptr = e->state; *bytes = n * 2 * H * sizeof(float); break;      // h|c per vertex, tensor-id order
+    case 1: *dev_ptr = e->loss; *bytes = n * sizeof(float); break;               // per-vertex loss
+    case 2: *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;           // d(loss)/d(pushed h)
+    case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
+    case 4: *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * sizeof(float); break;
+    default: return Fail(CAVS_ERR_BAD_ARG, "treelstm_peek: unknown array id");
+  }
+  return CAVS_OK;
+}

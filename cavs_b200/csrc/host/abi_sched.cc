@@ -1,25 +1,24 @@
 // C ABI of the host-side level scheduler, plus status / error plumbing.
+#include <atomic>
 #include <cstring>
 #include <string>
 #include <vector>
 
 #include "abi_common.h"
-#include "host/schedule.h"
+#include "host/sched_handle.h"
 
 namespace cavs_b200 {
 namespace {
 thread_local std::string g_last_error;
+std::atomic<unsigned long long> g_launches{0};
 }
+void CountLaunch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 int Fail(int code, const std::string& msg) {
   g_last_error = msg;
   return code;
 }
 }  // namespace cavs_b200
 
-struct cavs_sched {
-  cavs_b200::LevelSchedule impl;
-  bool loaded = false;
-};
 
 using cavs_b200::Fail;
 
@@ -36,6 +35,7 @@ extern "C" const char* cavs_status_string(int status) {
   }
 }
 extern "C" const char* cavs_last_error(void) { return cavs_b200::g_last_error.c_str(); }
+extern "C" unsigned long long cavs_launch_count(void) { return cavs_b200::g_launches.load(); }
 extern "C" const char* cavs_build_info(void) { return "cavs_b200 0.1 (sm_100a)"; }
 
 extern "C" int cavs_sched_create(cavs_sched** out) {

@@ -1,0 +1,317 @@
+// Fused child-sum Tree-LSTM cell, forward and gate-gradient backward, plus the two
+// index kernels that feed / drain the per-level gate GEMMs.
+//
+// Replaces the ~40 per-level launches the reference's vertex function expands to --
+// Slice / Add / Sigmoid / Tanh / Mul / Concat / Mirror / Accumulate statements or their
+// NVRTC-fused groups (apps/paper/tree-lstm-cavs.cc:129-172,
+// cavs/midend/runtime_compiler/code_generator.cc:20-185,
+// cavs/backend/op_impl_fused_kernel.cu:62-64) -- by one kernel per direction per level.
+// The forward Scatter (op_impl_graphop.cu:108-161) is fused away: the cell writes h|c
+// straight into the tensor-id-ordered state array the next level gathers from.  The
+// backward Scatter(Child=c) of d(c_child) is fused into the backward cell; d(h_child)
+// needs the dgrad GEMM first and is written by ScatterChildGrad.
+//
+// All kernels are HBM-bound streaming kernels: each thread owns kVec consecutive hidden
+// units of one vertex, grids are capped at SMs x resident CTAs and stride over the level.
+//
+// Gate order in memory: pre-activations from the input projection A are i,o,u,f
+// (W's column blocks, tree-lstm-cavs.cc:143-148); the bias is i,f,u,o (:120-123);
+// saved gates are i,o,u,f_0..f_{K-1}.
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "abi_common.h"
+#include "kernels/cell.h"
+#include "kernels/launch.h"
+
+namespace cavs_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int V> struct Vec { float v[V]; };
+
+template <int V>
+__device__ __forceinline__ Vec<V> LoadF(const float* p) {
+  Vec<V> r;
+  if constexpr (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; }
+  else if constexpr (V == 2) { const float2 t = *reinterpret_cast<const float2*>(p); r.v[0] = t.x; r.v[1] = t.y; }
+  else { r.v[0] = *p; }
+  return r;
+}
+template <int V>
+__device__ __forceinline__ Vec<V> Zero() { Vec<V> r; for (int i = 0; i < V; ++i) r.v[i] = 0.0f; return r; }
+
+template <int V>
+__device__ __forceinline__ void Store(float* p, const Vec<V>& r) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  else if constexpr (V == 2) *reinterpret_cast<float2*>(p) = make_float2(r.v[0], r.v[1]);
+  else *p = r.v[0];
+}
+template <int V>
+__device__ __forceinline__ void Store(__nv_bfloat16* p, const Vec<V>& r) {
+  if constexpr (V == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(r.v[0], r.v[1]), b = __floats2bfloat162_rn(r.v[2], r.v[3]);
+    uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else if constexpr (V == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(r.v[0], r.v[1]);
+  } else {
+    *p = __float2bfloat16_rn(r.v[0]);
+  }
+}
+
+__device__ __forceinline__ float Sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// S[t] = sum_c h(child_c(t)), HK[t,c] = h(child_c(t)); missing children contribute zeros.
+// Gather(Child=c) + Slice + Add of the reference (tree-lstm-cavs.cc:131-136).
+template <typename T, int K, int V>
+__global__ void __launch_bounds__(kThreads)
+GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ state, const int32_t* __restrict__ child,
+             int n_total, int off, int rows, int H) {
+  const int hv = H / V;
+  const long long total = static_cast<long long>(rows) * hv;
+  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+    const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
+    const int t = off + b;
+    Vec<V> s = Zero<V>();
+#pragma unroll
+    for (int c = 0; c < K; ++c) {
+      const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+      const Vec<V> h = ch >= 0 ? LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + j) : Zero<V>();
+#pragma unroll
+      for (int e = 0; e < V; ++e) s.v[e] = (c == 0) ? h.v[e] : s.v[e] + h.v[e];
+      Store<V>(HK + (static_cast<size_t>(t) * K + c) * H + j, h);
+    }
+    Store<V>(S + static_cast<size_t>(t) * H + j, s);
+  }
+}
+
+template <int K, int V, bool kLeaf>
+__global__ void __launch_bounds__(kThreads)
+CellFwd(float* __restrict__ state, float* __restrict__ gates, const float* __restrict__ A, const float* __restrict__ P,
+        const float* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child, int n_total,
+        int off, int rows, int H) {
+  const int hv = H / V;
+  const int G = (3 + K) * H;
+  const long long total = static_cast<long long>(rows) * hv;
+  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+    const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
+    const size_t t = static_cast<size_t>(off) + b;
+    const float* a = A + t * 4 * H + j;
+    const Vec<V> ai = LoadF<V>(a), ao = LoadF<V>(a + H), au = LoadF<V>(a + 2 * H), af = LoadF<V>(a + 3 * H);
+    const Vec<V> bi = LoadF<V>(bias + j), bf = LoadF<V>(bias + H + j), bu = LoadF<V>(bias + 2 * H + j), bo = LoadF<V>(bias + 3 * H + j);
+    Vec<V> pi = Zero<V>(), po = Zero<V>(), pu = Zero<V>();
+    if (!kLeaf) {
+      const float* p = P + static_cast<size_t>(b) * 3 * H + j;
+      pi = LoadF<V>(p); po = LoadF<V>(p + H); pu = LoadF<V>(p + 2 * H);
+    }
+    Vec<V> gi, go, gu, cc, hh;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      gi.v[e] = Sigmoid((ai.v[e] + pi.v[e]) + bi.v[e]);
+      go.v[e] = Sigmoid((ao.v[e] + po.v[e]) + bo.v[e]);
+      gu.v[e] = tanhf((au.v[e] + pu.v[e]) + bu.v[e]);
+      cc.v[e] = gi.v[e] * gu.v[e];
+    }
+    float* g = gates + t * G + j;
+#pragma unroll
+    for (int c = 0; c < K; ++c) {
+      Vec<V> q = Zero<V>(), cch = Zero<V>();
+      if (!kLeaf) {
+        q = LoadF<V>(Q + (static_cast<size_t>(b) * K + c) * H + j);
+        const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+        if (ch >= 0) cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
+      }
+      Vec<V> gf;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        gf.v[e] = Sigmoid((af.v[e] + q.v[e]) + bf.v[e]);
+        cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
+      }
+      Store<V>(g + (3 + c) * H, gf);
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * tanhf(cc.v[e]);
+    Store<V>(g, gi); Store<V>(g + H, go); Store<V>(g + 2 * H, gu);
+    Store<V>(state + t * 2 * H + j, hh);
+    Store<V>(state + t * 2 * H + H + j, cc);
+  }
+}
+
+template <typename T, int K, int V, bool kLeaf>
+__global__ void __launch_bounds__(kThreads)
+CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, const float* __restrict__ dOut,
+        const float* __restrict__ gates, const float* __restrict__ state, const int32_t* __restrict__ child,
+        const int32_t* __restrict__ parent, int n_total, int off, int rows, int H) {
+  const int hv = H / V;
+  const int G = (3 + K) * H;
+  const long long total = static_cast<long long>(rows) * hv;
+  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+    const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
+    const size_t t = static_cast<size_t>(off) + b;
+    const bool has_parent = __ldg(parent + t) >= 0;
+    // Gather of d(h|c) left by the parent; roots see zeros (op_impl_graphop.cu:77-86).
+    const Vec<V> mh = has_parent ? LoadF<V>(mailbox + t * 2 * H + j) : Zero<V>();
+    const Vec<V> mc = has_parent ? LoadF<V>(mailbox + t * 2 * H + H + j) : Zero<V>();
+    const Vec<V> dOutv = LoadF<V>(dOut + t * H + j);
+    const float* g = gates + t * G + j;
+    const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
+    const Vec<V> cown = LoadF<V>(state + t * 2 * H + H + j);
+    Vec<V> zi, zo, zu, dc, zfs = Zero<V>();
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float dh = dOutv.v[e] + mh.v[e];
+      const float th = tanhf(cown.v[e]);
+      const float d_o = dh * th;
+      dc.v[e] = mc.v[e] + (dh * go.v[e]) * (1.0f - th * th);
+      zi.v[e] = (dc.v[e] * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
+      zo.v[e] = d_o * go.v[e] * (1.0f - go.v[e]);
+      zu.v[e] = (dc.v[e] * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
+    }
+    if (!kLeaf) {
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+        const Vec<V> gf = LoadF<V>(g + (3 + c) * H);
+        Vec<V> z = Zero<V>();
+        if (ch >= 0) {
+          // c of the child is read before the same thread overwrites that slot of the
+          // mailbox (a different array), then d(c_child) = dc * f_c goes to the child's row.
+          const Vec<V> cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
+          Vec<V> dcc;
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            z.v[e] = (dc.v[e] * cch.v[e]) * gf.v[e] * (1.0f - gf.v[e]);
+            dcc.v[e] = dc.v[e] * gf.v[e];
+            zfs.v[e] += z.v[e];
+          }
+          Store<V>(mailbox + static_cast<size_t>(ch) * 2 * H + H + j, dcc);
+        }
+        Store<V>(ZF + (t * K + c) * H + j, z);
+      }
+    }
+    T* d = dA + t * 4 * H + j;
+    Store<V>(d, zi); Store<V>(d + H, zo); Store<V>(d + 2 * H, zu); Store<V>(d + 3 * H, zfs);
+  }
+}
+
+// mailbox[child_c(t)].h = ds[b] + dq[b,c]: Scatter(Child=c) of the child-state gradient
+// (cavs/backend/op_decl_graphop.cc:25-41).
+template <int K, int V>
+__global__ void __launch_bounds__(kThreads)
+ScatterChildGrad(float* __restrict__ mailbox, const float* __restrict__ ds, const float* __restrict__ dq,
+                 const int32_t* __restrict__ child, int n_total, int off, int rows, int H) {
+  const int hv = H / V;
+  const long long total = static_cast<long long>(rows) * hv;
+  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+    const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
+    const int t = off + b;
+    const Vec<V> s = LoadF<V>(ds + static_cast<size_t>(b) * H + j);
+#pragma unroll
+    for (int c = 0; c < K; ++c) {
+      const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+      if (ch < 0) continue;
+      const Vec<V> q = LoadF<V>(dq + (static_cast<size_t>(b) * K + c) * H + j);
+      Vec<V> r;
+#pragma unroll
+      for (int e = 0; e < V; ++e) r.v[e] = s.v[e] + q.v[e];
+      Store<V>(mailbox + static_cast<size_t>(ch) * 2 * H + j, r);
+    }
+  }
+}
+
+int VecWidth(int H) { return H % 4 == 0 ? 4 : (H % 2 == 0 ? 2 : 1); }
+
+#define DISPATCH_KV(K_, V_, ...)                                             \
+  do {                                                                        \
+    const int _k = (K_), _v = (V_);                                           \
+    if (_k == 1 && _v == 4) { constexpr int K = 1, V = 4; __VA_ARGS__; }             \
+    else if (_k == 1 && _v == 2) { constexpr int K = 1, V = 2; __VA_ARGS__; }        \
+    else if (_k == 1 && _v == 1) { constexpr int K = 1, V = 1; __VA_ARGS__; }        \
+    else if (_k == 2 && _v == 4) { constexpr int K = 2, V = 4; __VA_ARGS__; }        \
+    else if (_k == 2 && _v == 2) { constexpr int K = 2, V = 2; __VA_ARGS__; }        \
+    else if (_k == 2 && _v == 1) { constexpr int K = 2, V = 1; __VA_ARGS__; }        \
+    else if (_k == 3 && _v == 4) { constexpr int K = 3, V = 4; __VA_ARGS__; }        \
+    else if (_k == 3 && _v == 2) { constexpr int K = 3, V = 2; __VA_ARGS__; }        \
+    else if (_k == 3 && _v == 1) { constexpr int K = 3, V = 1; __VA_ARGS__; }        \
+    else if (_k == 4 && _v == 4) { constexpr int K = 4, V = 4; __VA_ARGS__; }        \
+    else if (_k == 4 && _v == 2) { constexpr int K = 4, V = 2; __VA_ARGS__; }        \
+    else { constexpr int K = 4, V = 1; __VA_ARGS__; }                                \
+  } while (0)
+
+int CheckCommon(const char* name, int rows, int H, int K) {
+  CAVS_REQUIRE(rows >= 0 && H > 0, CAVS_ERR_BAD_ARG, std::string(name) + ": bad shape");
+  CAVS_REQUIRE(K >= 1 && K <= 4, CAVS_ERR_BAD_ARG, std::string(name) + ": child slots must be 1..4");
+  return CAVS_OK;
+}
+
+}  // namespace
+
+int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const int32_t* child, int n_total, int off,
+                       int rows, int H, int K, cudaStream_t st) {
+  if (int rc = CheckCommon("gather_child_h", rows, H, K)) return rc;
+  if (rows == 0) return CAVS_OK;
+  const int v = VecWidth(H);
+  const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
+  DISPATCH_KV(K, v, {
+    if (bf16) GatherChildH<__nv_bfloat16, K, V><<<grid, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(S), static_cast<__nv_bfloat16*>(HK), state, child, n_total, off, rows, H);
+    else GatherChildH<float, K, V><<<grid, kThreads, 0, st>>>(static_cast<float*>(S), static_cast<float*>(HK), state, child, n_total, off, rows, H);
+  });
+  CAVS_LAUNCH_CHECK("gather_child_h");
+  return CAVS_OK;
+}
+
+int LaunchCellFwd(float* state, float* gates, const float* A, const float* P, const float* Q, const float* bias,
+                  const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st) {
+  if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
+  if (rows == 0) return CAVS_OK;
+  const int v = VecWidth(H);
+  const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
+  DISPATCH_KV(K, v, {
+    if (leaf) CellFwd<K, V, true><<<grid, kThreads, 0, st>>>(state, gates, A, P, Q, bias, child, n_total, off, rows, H);
+    else CellFwd<K, V, false><<<grid, kThreads, 0, st>>>(state, gates, A, P, Q, bias, child, n_total, off, rows, H);
+  });
+  CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
+  return CAVS_OK;
+}
+
+int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, const float* dOut, const float* gates,
+                  const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
+                  int K, bool leaf, cudaStream_t st) {
+  if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
+  if (rows == 0) return CAVS_OK;
+  const int v = VecWidth(H);
+  const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
+  DISPATCH_KV(K, v, {
+    if (bf16) {
+      auto* d = static_cast<__nv_bfloat16*>(dA); auto* z = static_cast<__nv_bfloat16*>(ZF);
+      if (leaf) CellBwd<__nv_bfloat16, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
+      else CellBwd<__nv_bfloat16, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
+    } else {
+      auto* d = static_cast<float*>(dA); auto* z = static_cast<float*>(ZF);
+      if (leaf) CellBwd<float, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
+      else CellBwd<float, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
+    }
+  });
+  CAVS_LAUNCH_CHECK("treelstm_cell_bwd");
+  return CAVS_OK;
+}
+
+int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,
+                           int rows, int H, int K, cudaStream_t st) {
+  if (int rc = CheckCommon("scatter_child_grad", rows, H, K)) return rc;
+  if (rows == 0) return CAVS_OK;
+  const int v = VecWidth(H);
+  const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
+  DISPATCH_KV(K, v, { ScatterChildGrad<K, V><<<grid, kThreads, 0, st>>>(mailbox, ds, dq, child, n_total, off, rows, H); });
+  CAVS_LAUNCH_CHECK("scatter_child_grad");
+  return CAVS_OK;
+}
+
+}  // namespace cavs_b200

@@ -1,0 +1,58 @@
+// Internal launchers of the fused Tree-LSTM cell kernels (kernels/cell.cu) and of the
+// other per-step kernels (embedding, loss head, reductions, optimizers).
+#ifndef CAVS_B200_KERNELS_CELL_H_
+#define CAVS_B200_KERNELS_CELL_H_
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace cavs_b200 {
+
+// child: [K, n_total] tensor-id of each child slot or -1; parent: [n_total] or -1.
+// Level rows are [off, off + rows).  S is [n_total, H], HK / ZF are [n_total, K, H],
+// P is [rows, 3H] and Q / dq are [rows, K, H] (level-local), A / dA are [n_total, 4H].
+int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const int32_t* child, int n_total, int off,
+                       int rows, int H, int K, cudaStream_t st);
+int LaunchCellFwd(float* state, float* gates, const float* A, const float* P, const float* Q, const float* bias,
+                  const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st);
+int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, const float* dOut, const float* gates,
+                  const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
+                  int K, bool leaf, cudaStream_t st);
+int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,
+                           int rows, int H, int K, cudaStream_t st);
+
+// Embedding lookup out[t,:] = table[tok[t],:] (fp32 table; fp32 or bf16 output).
+int LaunchEmbedFwd(void* out, bool bf16, const float* table, const int32_t* tok, int rows, int E, int vocab, cudaStream_t st);
+// Deterministic segmented embedding gradient.  order: row indices sorted by token (stable);
+// seg_off: [n_seg+1] offsets into order; seg_tok: [n_seg] token of each segment.  Long
+// segments are split into chunks of kEmbedChunk rows whose partial sums go to scratch
+// ([n_chunks, E] fp32) before a fixed-order second pass.
+constexpr int kEmbedChunk = 256;
+int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const int32_t* chunk_seg, const int32_t* chunk_off,
+                   int n_chunks, const int32_t* seg_first_chunk, const int32_t* seg_tok, int n_seg, float* scratch, int E,
+                   cudaStream_t st);
+
+// Fused classifier + softmax cross-entropy for small class counts (C <= 32), forward and backward
+// in one pass over the pushed hidden rows.  h rows are read with pitch h_pitch (state is [n,2H]).
+// Writes loss[t], dOut[t,:] = dz Wc; per-CTA partials of dWc / dbc / loss sum go to scratch and are
+// reduced in fixed order.  inv_rows scales dz (the reference divides by the logits' row count).
+size_t LossHeadScratchBytes(int H, int C);
+int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
+                   const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
+                   float* scratch, cudaStream_t st);
+
+// Column sums of a [rows, cols] matrix (fp32 or bf16) into out[perm(col)], deterministic two-stage.
+size_t ColumnSumScratchBytes(int cols);
+// block > 0 (cols == 4*block): source column block b is written to destination block m_b.
+int LaunchColumnSum(float* out, const void* x, bool bf16, long long pitch, int rows, int cols, float* scratch, cudaStream_t st,
+                    int block = 0, int m0 = 0, int m1 = 1, int m2 = 2, int m3 = 3);
+
+int LaunchSgd(float* w, const float* g, size_t n, float lr, cudaStream_t st);
+int LaunchAdagrad(float* w, float* acc, const float* g, size_t n, float lr, float eps, cudaStream_t st);
+// dst_bf16[i] = bf16(src[i])
+int LaunchCastBf16(void* dst, const float* src, size_t n, cudaStream_t st);
+
+}  // namespace cavs_b200
+#endif

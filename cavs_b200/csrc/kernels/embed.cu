@@ -1,0 +1,103 @@
+// Embedding lookup and its deterministic segmented gradient.
+//
+// Forward replaces BatchedCopy (cavs/backend/op_impl_embedding_lookup.cu:23-35,64-72);
+// token ids are int32 here (the reference carries them as floats and casts on device).
+// Backward replaces BatchedSparseUpdate's atomicAdd accumulation (:91-103), whose result
+// depends on the order in which duplicate tokens arrive.  Here rows are grouped by token
+// on the host once per batch (stable counting sort), every group is cut into chunks of at
+// most kEmbedChunk rows, each chunk is summed in row order by one CTA, and the chunks of a
+// group are summed in chunk order: the same bits on every run.
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "abi_common.h"
+#include "kernels/cell.h"
+#include "kernels/launch.h"
+
+namespace cavs_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+EmbedFwd(T* __restrict__ out, const float* __restrict__ table, const int32_t* __restrict__ tok, int rows, int E, int vocab) {
+  const int lane = threadIdx.x & 31;
+  const int warp0 = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int n_warps = gridDim.x * (kThreads / 32);
+  for (int t = warp0; t < rows; t += n_warps) {
+    int id = __ldg(tok + t);
+    if (id < 0 || id >= vocab) id = 0;
+    const float* src = table + static_cast<size_t>(id) * E;
+    T* dst = out + static_cast<size_t>(t) * E;
+    if ((E & 3) == 0) {
+      for (int e = lane * 4; e < E; e += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(src + e);
+        if constexpr (sizeof(T) == 4) {
+          *reinterpret_cast<float4*>(dst + e) = v;
+        } else {
+          __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+          uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+          *reinterpret_cast<uint2*>(dst + e) = u;
+        }
+      }
+    } else {
+      for (int e = lane; e < E; e += 32) dst[e] = static_cast<T>(src[e]);
+    }
+  }
+}
+
+// One CTA per chunk: partial[chunk,:] = sum over the chunk's rows, in order.
+__global__ void __launch_bounds__(kThreads)
+EmbedBwdChunks(float* __restrict__ partial, const float* __restrict__ dX, const int32_t* __restrict__ order,
+               const int32_t* __restrict__ chunk_off, int E) {
+  const int chunk = blockIdx.x;
+  const int begin = chunk_off[chunk], end = chunk_off[chunk + 1];
+  for (int e = threadIdx.x; e < E; e += kThreads) {
+    float acc = 0.0f;
+    for (int r = begin; r < end; ++r) acc += dX[static_cast<size_t>(order[r]) * E + e];
+    partial[static_cast<size_t>(chunk) * E + e] = acc;
+  }
+}
+// One CTA per segment: dtable[tok,:] = sum of its chunks' partials, in chunk order.
+__global__ void __launch_bounds__(kThreads)
+EmbedBwdSegments(float* __restrict__ dtable, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk,
+                 const int32_t* __restrict__ seg_tok, int E) {
+  const int seg = blockIdx.x;
+  const int c0 = seg_first_chunk[seg], c1 = seg_first_chunk[seg + 1];
+  float* dst = dtable + static_cast<size_t>(seg_tok[seg]) * E;
+  for (int e = threadIdx.x; e < E; e += kThreads) {
+    float acc = 0.0f;
+    for (int c = c0; c < c1; ++c) acc += partial[static_cast<size_t>(c) * E + e];
+    dst[e] = acc;
+  }
+}
+
+}  // namespace
+
+int LaunchEmbedFwd(void* out, bool bf16, const float* table, const int32_t* tok, int rows, int E, int vocab, cudaStream_t st) {
+  CAVS_REQUIRE(rows >= 0 && E > 0 && vocab > 0, CAVS_ERR_BAD_ARG, "embed_fwd: bad shape");
+  if (rows == 0) return CAVS_OK;
+  CAVS_REQUIRE(out && table && tok, CAVS_ERR_BAD_ARG, "embed_fwd: null pointer");
+  const int grid = GridForWarps(rows, kThreads / 32);
+  if (bf16) EmbedFwd<__nv_bfloat16><<<grid, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(out), table, tok, rows, E, vocab);
+  else EmbedFwd<float><<<grid, kThreads, 0, st>>>(static_cast<float*>(out), table, tok, rows, E, vocab);
+  CAVS_LAUNCH_CHECK("embed_fwd");
+  return CAVS_OK;
+}
+
+int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const int32_t* /*chunk_seg*/, const int32_t* chunk_off,
+                   int n_chunks, const int32_t* seg_first_chunk, const int32_t* seg_tok, int n_seg, float* scratch, int E,
+                   cudaStream_t st) {
+  CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && E > 0, CAVS_ERR_BAD_ARG, "embed_bwd: bad shape");
+  if (n_chunks == 0 || n_seg == 0) return CAVS_OK;
+  CAVS_REQUIRE(dtable && dX && order && chunk_off && seg_first_chunk && seg_tok && scratch, CAVS_ERR_BAD_ARG, "embed_bwd: null pointer");
+  EmbedBwdChunks<<<n_chunks, kThreads, 0, st>>>(scratch, dX, order, chunk_off, E);
+  CAVS_LAUNCH_CHECK("embed_bwd chunks");
+  EmbedBwdSegments<<<n_seg, kThreads, 0, st>>>(dtable, scratch, seg_first_chunk, seg_tok, E);
+  CAVS_LAUNCH_CHECK("embed_bwd segments");
+  return CAVS_OK;
+}
+
+}  // namespace cavs_b200

@@ -1,0 +1,48 @@
+// Internal C++ interface of the two GEMM paths (shared by the C ABI and the engine).
+#ifndef CAVS_B200_KERNELS_GEMM_H_
+#define CAVS_B200_KERNELS_GEMM_H_
+
+#include <cuda_runtime.h>
+
+#include <cstddef>
+
+namespace cavs_b200 {
+
+// bf16 x bf16 -> fp32 on tcgen05.  Operand majors: 0 = K-major (A is [m,k] / B is [n,k],
+// row-major), 1 = MN-major (A is [k,m] / B is [k,n], row-major).
+struct GemmBf16Args {
+  void* c = nullptr;          // [m,n] row-major, fp32 (out_mode 0 store, 1 accumulate) or bf16 (2)
+  long long ldc = 0;
+  int out_mode = 0;
+  const void* a = nullptr;
+  long long lda = 0;
+  int a_major = 0;
+  const void* b = nullptr;
+  long long ldb = 0;
+  int b_major = 0;
+  int m = 0, n = 0, k = 0;
+  int splits = 1;             // >1: K split across CTAs, partials in scratch, fixed-order reduce
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int* status = nullptr;      // device word raised when a bounded wait expires
+};
+int GemmBf16(const GemmBf16Args& args, cudaStream_t stream);
+size_t GemmBf16ScratchBytes(int m, int n, int splits);
+int GemmBf16SplitsFor(int m, int n, int k);
+
+// fp32 GEMM on the CUDA cores with arbitrary element strides:
+// C[i,j] (+)= sum_p A[i*a_rs + p*a_cs] * B[p*b_rs + j*b_cs].
+struct GemmF32Args {
+  float* c = nullptr;
+  long long ldc = 0;
+  int accumulate = 0;
+  const float* a = nullptr;
+  long long a_rs = 0, a_cs = 0;
+  const float* b = nullptr;
+  long long b_rs = 0, b_cs = 0;
+  int m = 0, n = 0, k = 0;
+};
+int GemmF32(const GemmF32Args& args, cudaStream_t stream);
+
+}  // namespace cavs_b200
+#endif

@@ -1,0 +1,293 @@
+// bf16 x bf16 -> fp32 GEMM on the Blackwell tensor cores (tcgen05.mma, accumulator in
+// TMEM), operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle), written directly in PTX.
+//
+// This is the only dense contraction of the vertex-function path: the per-level gate
+// products, their data gradients, and the once-per-step weight gradients.  The
+// reference issues these as cublasSgemm calls (cavs/backend/cublas_wrapper.cc:13-28,
+// cavs/backend/op_impl_blas3_cublas.cc:35-70).
+//
+// One CTA computes one BM x BN tile of C (optionally one K-split of it):
+//   warp 0      TMA producer: one elected lane walks the K blocks, filling a ring of stages
+//   warp 1      allocates TMEM, one elected lane issues tcgen05.mma and commits to mbarriers
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one 32-lane quarter each) and store
+// Operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the
+// latter is what the weight gradient dW = X^T dY needs, so no transpose pass exists.
+// Every mbarrier wait is bounded; on expiry the CTA raises *status and unwinds.
+#ifndef CAVS_B200_KERNELS_GEMM_TC_CUH_
+#define CAVS_B200_KERNELS_GEMM_TC_CUH_
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace cavs_b200 {
+namespace tc {
+
+constexpr int kBM = 128;        // rows of C per CTA (UMMA M)
+constexpr int kBK = 64;         // K elements per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;      // K per tcgen05.mma for 16-bit inputs
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 21;
+
+enum Major : int { kMajorK = 0, kMajorMN = 1 };
+enum OutMode : int { kStoreF32 = 0, kAccumF32 = 1, kStoreBf16 = 2 };
+
+struct Params {
+  void* c;            // output, row-major
+  long long ldc;      // elements
+  long long split_stride;  // elements between K-split partial outputs (0 when splits == 1)
+  int m, n, k;
+  int kb_per_split;   // K blocks handled by one CTA along gridDim.z
+  int out_mode;
+  int a_row_off, b_row_off;  // added to the row coordinate of every A / B tile (views into arenas)
+  int a_k_off, b_k_off;      // added to the K coordinate
+  int* status;        // device word, set non-zero when a bounded wait expires
+};
+
+template <int kBN>
+struct Smem {
+  static constexpr int kATile = kBM * kBK * 2;
+  static constexpr int kBTile = kBN * kBK * 2;
+  static constexpr int kStage = kATile + kBTile;
+  static constexpr int kStages = (kBN == 256) ? 4 : 6;
+  static constexpr int kBarOff = kStages * kStage;
+  static constexpr int kBytes = kBarOff + 256 + 1024;  // barriers + slack for 1024-byte alignment
+};
+
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait on a phase parity: non-blocking polls with a short sleep once the wait
+// is clearly not a pipeline hiccup.  Returns false if the limit expired (~0.3 s).
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (it > 4096) __nanosleep(128);
+  }
+  return false;
+}
+__device__ __forceinline__ void TmaLoad2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ bool ElectOne() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile whose base is
+// 1024-byte aligned.  K-major: rows of 128 bytes, 8-row groups 1024 bytes apart (SBO).
+// MN-major: 64-element (128-byte) runs along MN per K index, 8 K-indices per 1024-byte
+// group (SBO), next 64-element block along MN one whole 64x64 box (8192 bytes) further (LBO).
+__device__ __forceinline__ uint64_t SmemDesc(uint32_t addr, int major) {
+  const uint64_t start = (addr & 0x3FFFFu) >> 4;
+  const uint64_t lbo = (major == kMajorMN) ? (8192u >> 4) : 1u;
+  const uint64_t sbo = 1024u >> 4;
+  return start | (lbo << 16) | (sbo << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulate, bf16 A and B, given majors, N and M.
+__host__ __device__ constexpr uint32_t InstrDesc(int a_major, int b_major, int n, int m) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_major) << 15) |
+         (static_cast<uint32_t>(b_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+__device__ __forceinline__ void UmmaBf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void UmmaCommit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int kBN, int kAMajor, int kBMajor>
+__global__ void __launch_bounds__(kThreads, 1)
+GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+  using S = Smem<kBN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle needs 1024-byte aligned tiles.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + S::kStages;
+  uint64_t* accum_bar = bars + 2 * S::kStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::kStages + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kBM;
+  const int n0 = blockIdx.x * kBN;
+  const int nkb_total = (p.k + kBK - 1) / kBK;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      MbarInit(SmemAddr(full_bar + s), 1);
+      MbarInit(SmemAddr(empty_bar + s), 1);
+    }
+    MbarInit(SmemAddr(accum_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)), "r"(kBN));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (ElectOne()) {
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % S::kStages;
+        const uint32_t phase = (i / S::kStages) & 1;
+        ok = MbarWait(SmemAddr(empty_bar + s), phase ^ 1);
+        if (!ok) break;
+        const uint32_t bar = SmemAddr(full_bar + s);
+        MbarExpectTx(bar, S::kStage);
+        const uint32_t a_dst = SmemAddr(smem + s * S::kStage);
+        const uint32_t b_dst = a_dst + S::kATile;
+        const int k0 = (kb_begin + i) * kBK;
+        if (kAMajor == kMajorK) {
+          TmaLoad2d(a_dst, &map_a, bar, k0 + p.a_k_off, m0 + p.a_row_off);                       // box {64 k, 128 rows}
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j + p.a_row_off, k0 + p.a_k_off);  // box {64 mn, 64 k}
+        }
+        if (kBMajor == kMajorK) {
+          TmaLoad2d(b_dst, &map_b, bar, k0 + p.b_k_off, n0 + p.b_row_off);                       // box {64 k, kBN rows}
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBN / 64; ++j) TmaLoad2d(b_dst + j * 8192, &map_b, bar, n0 + 64 * j + p.b_row_off, k0 + p.b_k_off);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (ElectOne()) {
+      constexpr uint32_t idesc = InstrDesc(kAMajor, kBMajor, kBN, kBM);
+      constexpr uint32_t a_step = (kAMajor == kMajorK) ? (kUmmaK * 2 >> 4) : (kUmmaK * 128 >> 4);
+      constexpr uint32_t b_step = (kBMajor == kMajorK) ? (kUmmaK * 2 >> 4) : (kUmmaK * 128 >> 4);
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % S::kStages;
+        const uint32_t phase = (i / S::kStages) & 1;
+        ok = MbarWait(SmemAddr(full_bar + s), phase);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = SmemAddr(smem + s * S::kStage);
+        const uint64_t a_desc = SmemDesc(a_addr, kAMajor);
+        const uint64_t b_desc = SmemDesc(a_addr + S::kATile, kBMajor);
+#pragma unroll
+        for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+          UmmaBf16(tmem_base, a_desc + kk * a_step, b_desc + kk * b_step, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        UmmaCommit(SmemAddr(empty_bar + s));   // frees the stage once these MMAs have read it
+      }
+      UmmaCommit(SmemAddr(accum_bar));         // accumulator complete
+    }
+    __syncwarp();
+  } else {
+    // Epilogue warps 2..5 own TMEM lane quarters (warp % 4).
+    ok = MbarWait(SmemAddr(accum_bar), 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && kb_count > 0) {
+      const int quarter = warp & 3;
+      const int row = m0 + quarter * 32 + lane;
+      const long long zoff = static_cast<long long>(blockIdx.z) * p.split_stride;
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBN; c0 += 32) {
+        if (n0 + c0 >= p.n) break;   // warp-uniform
+        uint32_t r[32];
+        TmemLoad32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, r);
+        if (row < p.m) {
+          const int col0 = n0 + c0;
+          if (p.out_mode == kStoreBf16) {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
+            if (col0 + 32 <= p.n && (p.ldc & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                v.x = *reinterpret_cast<uint32_t*>(&t0); v.y = *reinterpret_cast<uint32_t*>(&t1);
+                v.z = *reinterpret_cast<uint32_t*>(&t2); v.w = *reinterpret_cast<uint32_t*>(&t3);
+                *reinterpret_cast<uint4*>(dst + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          } else {
+            float* dst = static_cast<float*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
+            const bool acc = p.out_mode == kAccumF32;
+            if (col0 + 32 <= p.n && (p.ldc & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                       __uint_as_float(r[j + 3]));
+                if (acc) {
+                  const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = (acc ? dst[j] : 0.0f) + __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (!ok && p.status != nullptr) atomicExch(p.status, 1);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBN));
+  }
+}
+
+}  // namespace tc
+}  // namespace cavs_b200
+#endif

@@ -1,0 +1,193 @@
+// Loss head: classifier + softmax cross-entropy, forward and backward in one pass over
+// the pushed hidden rows, for small class counts.
+//
+// Replaces FullyConnected (two cublasSgemm, cavs/backend/op_impl_fullyconnected_cublas.cc:33-85),
+// cudnnSoftmaxForward + SoftmaxEntropyLossForwardKernel
+// (cavs/backend/op_impl_softmax_entropy_logits_loss.cu:106-140), their gradients
+// (:213-250 and op_impl_fullyconnected_cublas.cc:104-176: three more cublasSgemm) and the
+// two device-wide synchronisations in between.  HBM-bound: reads each hidden row once
+// from DRAM (the second use hits L2), writes d(hidden) once.
+//
+// Determinism: dWc / dbc / the loss sum are accumulated per CTA in a fixed row order,
+// written to scratch, and reduced across CTAs in index order by a second kernel.
+#include <cstdint>
+
+#include "abi_common.h"
+#include "kernels/cell.h"
+#include "kernels/launch.h"
+
+namespace cavs_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kRowsPerBlock = 32;     // rows per CTA iteration (4 per warp)
+constexpr int kMaxC = 8;
+constexpr int kMaxColsPerThread = 8;  // H <= kThreads * kMaxColsPerThread
+
+__device__ __forceinline__ float WarpSum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int C>
+__global__ void __launch_bounds__(kThreads)
+LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ partial,
+               const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
+               const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows) {
+  extern __shared__ float sm[];
+  float* sW = sm;                        // [C][H]
+  float* sdz = sm + C * H;               // [kRowsPerBlock][C]
+  float* sloss = sdz + kRowsPerBlock * C;  // [kWarps]
+  for (int i = threadIdx.x; i < C * H; i += kThreads) sW[i] = Wc[i];
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float accW[kMaxColsPerThread][C];
+#pragma unroll
+  for (int q = 0; q < kMaxColsPerThread; ++q)
+#pragma unroll
+    for (int c = 0; c < C; ++c) accW[q][c] = 0.0f;
+  float accb = 0.0f;        // thread c < C owns class c of the bias gradient
+  float loss_acc = 0.0f;   // per warp (lane 0)
+
+  const int n_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  for (int blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
+    const int r0 = blk * kRowsPerBlock;
+    // Phase 1: each warp handles rows r0 + warp, r0 + warp + kWarps, ...
+    for (int rr = warp; rr < kRowsPerBlock; rr += kWarps) {
+      const int t = r0 + rr;
+      float dz[C];
+      if (t < rows) {
+        const float* hr = h + static_cast<long long>(t) * h_pitch;
+        float z[C];
+#pragma unroll
+        for (int c = 0; c < C; ++c) z[c] = 0.0f;
+        for (int j = lane; j < H; j += 32) {
+          const float hv = hr[j];
+#pragma unroll
+          for (int c = 0; c < C; ++c) z[c] = fmaf(hv, sW[c * H + j], z[c]);
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < C; ++c) { z[c] = WarpSum(z[c]) + bc[c]; mx = fmaxf(mx, z[c]); }
+        float den = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) { z[c] = expf(z[c] - mx); den += z[c]; }
+        const int y = label[t];
+        float lrow = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const float pc = z[c] / den;
+          dz[c] = (y >= 0) ? (pc - (c == y ? 1.0f : 0.0f)) * inv_rows : 0.0f;
+          if (c == y) lrow = -logf(pc);
+        }
+        if (lane == 0) { loss[t] = lrow; loss_acc += lrow; }
+        float* dr = dOut + static_cast<long long>(t) * H;
+        for (int j = lane; j < H; j += 32) {
+          float a = 0.0f;
+#pragma unroll
+          for (int c = 0; c < C; ++c) a = fmaf(dz[c], sW[c * H + j], a);
+          dr[j] = a;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < C; ++c) dz[c] = 0.0f;
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) sdz[rr * C + c] = dz[c];
+      }
+    }
+    __syncthreads();
+    // Phase 2: thread owns columns j = threadIdx.x + q * kThreads; rows in ascending order.
+    const int r_end = min(kRowsPerBlock, rows - r0);
+    for (int rr = 0; rr < r_end; ++rr) {
+      const float* hr = h + static_cast<long long>(r0 + rr) * h_pitch;
+#pragma unroll
+      for (int q = 0; q < kMaxColsPerThread; ++q) {
+        const int j = threadIdx.x + q * kThreads;
+        if (j < H) {
+          const float hv = hr[j];
+#pragma unroll
+          for (int c = 0; c < C; ++c) accW[q][c] = fmaf(sdz[rr * C + c], hv, accW[q][c]);
+        }
+      }
+      if (threadIdx.x < C) accb += sdz[rr * C + threadIdx.x];
+    }
+    __syncthreads();
+  }
+  // Per-CTA partial: [C*H] dWc, [C] dbc, [1] loss sum.
+  float* mine = partial + static_cast<size_t>(blockIdx.x) * (C * H + C + 1);
+#pragma unroll
+  for (int q = 0; q < kMaxColsPerThread; ++q) {
+    const int j = threadIdx.x + q * kThreads;
+    if (j < H) {
+#pragma unroll
+      for (int c = 0; c < C; ++c) mine[c * H + j] = accW[q][c];
+    }
+  }
+  if (threadIdx.x < C) mine[C * H + threadIdx.x] = accb;
+  if (lane == 0) sloss[warp] = loss_acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.0f;
+    for (int w = 0; w < kWarps; ++w) s += sloss[w];
+    mine[C * H + C] = s;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+LossHeadReduce(float* __restrict__ dWc, float* __restrict__ dbc, float* __restrict__ loss_sum,
+               const float* __restrict__ partial, int n_parts, int CH, int C) {
+  const int width = CH + C + 1;
+  for (int i = blockIdx.x * kThreads + threadIdx.x; i < width; i += gridDim.x * kThreads) {
+    float s = 0.0f;
+    for (int p = 0; p < n_parts; ++p) s += partial[static_cast<size_t>(p) * width + i];
+    if (i < CH) dWc[i] = s;
+    else if (i < CH + C) dbc[i - CH] = s;
+    else if (loss_sum) *loss_sum = s;
+  }
+}
+
+int LossGrid(int rows) {
+  const int n_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  return std::max(1, std::min(n_blocks, SmCount() * 2));
+}
+
+}  // namespace
+
+size_t LossHeadScratchBytes(int H, int C) {
+  return static_cast<size_t>(SmCount()) * 2 * (static_cast<size_t>(C) * H + C + 1) * sizeof(float);
+}
+
+int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
+                   const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
+                   float* scratch, cudaStream_t st) {
+  CAVS_REQUIRE(rows >= 0 && H > 0 && C > 0, CAVS_ERR_BAD_ARG, "loss_head: bad shape");
+  CAVS_REQUIRE(C <= kMaxC, CAVS_ERR_UNSUPPORTED, "loss_head: fused path supports at most 8 classes");
+  CAVS_REQUIRE(H <= kThreads * kMaxColsPerThread, CAVS_ERR_UNSUPPORTED, "loss_head: hidden size above 2048");
+  CAVS_REQUIRE(loss && dOut && dWc && dbc && h && label && Wc && bc && scratch, CAVS_ERR_BAD_ARG, "loss_head: null pointer");
+  const int grid = rows > 0 ? LossGrid(rows) : 1;
+  const size_t smem = (static_cast<size_t>(C) * H + kRowsPerBlock * C + kWarps) * sizeof(float);
+  CAVS_REQUIRE(smem <= 200 * 1024, CAVS_ERR_UNSUPPORTED, "loss_head: classifier does not fit in shared memory");
+#define LOSS_CASE(CC)                                                                                              \
+  case CC: {                                                                                                       \
+    if (smem > 48 * 1024)                                                                                          \
+      CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    LossHeadKernel<CC><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
+    break;                                                                                                         \
+  }
+  switch (C) {
+    LOSS_CASE(1) LOSS_CASE(2) LOSS_CASE(3) LOSS_CASE(4) LOSS_CASE(5) LOSS_CASE(6) LOSS_CASE(7) LOSS_CASE(8)
+    default: return Fail(CAVS_ERR_UNSUPPORTED, "loss_head: class count");
+  }
+#undef LOSS_CASE
+  CAVS_LAUNCH_CHECK("loss_head");
+  const int width = C * H + C + 1;
+  LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C);
+  CAVS_LAUNCH_CHECK("loss_head reduce");
+  return CAVS_OK;
+}
+
+}  // namespace cavs_b200

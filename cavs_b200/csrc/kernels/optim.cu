@@ -1,0 +1,136 @@
+// Parameter update, bf16 shadow copies and column reductions.
+//
+// SGD replaces SGDKernel (cavs/backend/op_impl_sgd.cu:15-47): w <- w - lr * g.
+// Adagrad has no counterpart in the reference (it registers only SGD); it is defined as
+// acc += g^2; w <- w - lr * g / (sqrt(acc) + eps).
+// ColumnSum replaces the serial-per-thread column reduction the reference uses for bias
+// gradients (cavs/backend/op_impl_elementwise.cuh:31-37) with a two-stage, fixed-order
+// reduction.
+#include <cuda_bf16.h>
+
+#include <cstdint>
+
+#include "abi_common.h"
+#include "kernels/cell.h"
+#include "kernels/launch.h"
+
+namespace cavs_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kColChunks = 64;   // row chunks of the first column-sum stage
+
+__global__ void __launch_bounds__(kThreads) SgdKernel(float* __restrict__ w, const float* __restrict__ g, size_t n, float lr) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  const size_t n4 = n / 4;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n4; i += stride) {
+    float4 wv = reinterpret_cast<float4*>(w)[i];
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    wv.x -= lr * gv.x; wv.y -= lr * gv.y; wv.z -= lr * gv.z; wv.w -= lr * gv.w;
+    reinterpret_cast<float4*>(w)[i] = wv;
+  }
+  for (size_t i = n4 * 4 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) w[i] -= lr * g[i];
+}
+
+__global__ void __launch_bounds__(kThreads)
+AdagradKernel(float* __restrict__ w, float* __restrict__ acc, const float* __restrict__ g, size_t n, float lr, float eps) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  const size_t n4 = n / 4;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n4; i += stride) {
+    float4 wv = reinterpret_cast<float4*>(w)[i];
+    float4 av = reinterpret_cast<float4*>(acc)[i];
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    av.x += gv.x * gv.x; av.y += gv.y * gv.y; av.z += gv.z * gv.z; av.w += gv.w * gv.w;
+    wv.x -= lr * gv.x / (sqrtf(av.x) + eps); wv.y -= lr * gv.y / (sqrtf(av.y) + eps);
+    wv.z -= lr * gv.z / (sqrtf(av.z) + eps); wv.w -= lr * gv.w / (sqrtf(av.w) + eps);
+    reinterpret_cast<float4*>(acc)[i] = av;
+    reinterpret_cast<float4*>(w)[i] = wv;
+  }
+  for (size_t i = n4 * 4 + static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    const float a = acc[i] + g[i] * g[i];
+    acc[i] = a;
+    w[i] -= lr * g[i] / (sqrtf(a) + eps);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) CastBf16Kernel(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, size_t n) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+// Stage 1: CTA (x = column tile of kThreads, y = row chunk) sums its rows in order.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+ColumnSumStage1(float* __restrict__ partial, const T* __restrict__ x, long long pitch, int rows, int cols, int rows_per_chunk) {
+  const int col = blockIdx.x * kThreads + threadIdx.x;
+  if (col >= cols) return;
+  const int r0 = blockIdx.y * rows_per_chunk, r1 = min(rows, r0 + rows_per_chunk);
+  float acc = 0.0f;
+  for (int r = r0; r < r1; ++r) acc += static_cast<float>(x[static_cast<long long>(r) * pitch + col]);
+  partial[static_cast<size_t>(blockIdx.y) * cols + col] = acc;
+}
+// Stage 2 optionally permutes column blocks of width `block`: source block b lands in
+// destination block map[b] (used to turn gate order i,o,u,f into bias order i,f,u,o).
+__global__ void __launch_bounds__(kThreads)
+ColumnSumStage2(float* __restrict__ out, const float* __restrict__ partial, int cols, int chunks, int block, int4 map) {
+  const int col = blockIdx.x * kThreads + threadIdx.x;
+  if (col >= cols) return;
+  float acc = 0.0f;
+  for (int c = 0; c < chunks; ++c) acc += partial[static_cast<size_t>(c) * cols + col];
+  int dst = col;
+  if (block > 0) {
+    const int b = col / block;
+    const int nb = b == 0 ? map.x : b == 1 ? map.y : b == 2 ? map.z : map.w;
+    dst = nb * block + col % block;
+  }
+  out[dst] = acc;
+}
+
+}  // namespace
+
+int LaunchSgd(float* w, const float* g, size_t n, float lr, cudaStream_t st) {
+  if (n == 0) return CAVS_OK;
+  CAVS_REQUIRE(w && g, CAVS_ERR_BAD_ARG, "sgd: null pointer");
+  CAVS_REQUIRE(((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g)) & 15u) == 0, CAVS_ERR_BAD_ARG, "sgd: buffers must be 16-byte aligned");
+  SgdKernel<<<GridForElems(n / 4 + 1, kThreads), kThreads, 0, st>>>(w, g, n, lr);
+  CAVS_LAUNCH_CHECK("sgd");
+  return CAVS_OK;
+}
+
+int LaunchAdagrad(float* w, float* acc, const float* g, size_t n, float lr, float eps, cudaStream_t st) {
+  if (n == 0) return CAVS_OK;
+  CAVS_REQUIRE(w && acc && g, CAVS_ERR_BAD_ARG, "adagrad: null pointer");
+  CAVS_REQUIRE(((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(acc)) & 15u) == 0,
+               CAVS_ERR_BAD_ARG, "adagrad: buffers must be 16-byte aligned");
+  AdagradKernel<<<GridForElems(n / 4 + 1, kThreads), kThreads, 0, st>>>(w, acc, g, n, lr, eps);
+  CAVS_LAUNCH_CHECK("adagrad");
+  return CAVS_OK;
+}
+
+int LaunchCastBf16(void* dst, const float* src, size_t n, cudaStream_t st) {
+  if (n == 0) return CAVS_OK;
+  CAVS_REQUIRE(dst && src, CAVS_ERR_BAD_ARG, "cast_bf16: null pointer");
+  CastBf16Kernel<<<GridForElems(n, kThreads), kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(dst), src, n);
+  CAVS_LAUNCH_CHECK("cast_bf16");
+  return CAVS_OK;
+}
+
+size_t ColumnSumScratchBytes(int cols) { return static_cast<size_t>(kColChunks) * cols * sizeof(float); }
+
+int LaunchColumnSum(float* out, const void* x, bool bf16, long long pitch, int rows, int cols, float* scratch, cudaStream_t st,
+                    int block, int m0, int m1, int m2, int m3) {
+  CAVS_REQUIRE(rows >= 0 && cols > 0, CAVS_ERR_BAD_ARG, "column_sum: bad shape");
+  CAVS_REQUIRE(out && scratch && (x || rows == 0), CAVS_ERR_BAD_ARG, "column_sum: null pointer");
+  const int rows_per_chunk = std::max(1, (rows + kColChunks - 1) / kColChunks);
+  const int chunks = std::max(1, (rows + rows_per_chunk - 1) / rows_per_chunk);
+  dim3 grid((cols + kThreads - 1) / kThreads, chunks);
+  if (bf16) ColumnSumStage1<__nv_bfloat16><<<grid, kThreads, 0, st>>>(scratch, static_cast<const __nv_bfloat16*>(x), pitch, rows, cols, rows_per_chunk);
+  else ColumnSumStage1<float><<<grid, kThreads, 0, st>>>(scratch, static_cast<const float*>(x), pitch, rows, cols, rows_per_chunk);
+  CAVS_LAUNCH_CHECK("column_sum stage 1");
+  CAVS_REQUIRE(block == 0 || cols == 4 * block, CAVS_ERR_BAD_ARG, "column_sum: block permutation needs cols == 4 * block");
+  ColumnSumStage2<<<(cols + kThreads - 1) / kThreads, kThreads, 0, st>>>(out, scratch, cols, chunks, block, make_int4(m0, m1, m2, m3));
+  CAVS_LAUNCH_CHECK("column_sum stage 2");
+  return CAVS_OK;
+}
+
+}  // namespace cavs_b200

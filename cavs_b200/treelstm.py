@@ -1,0 +1,123 @@
+"""Tree-LSTM engine binding: device memory comes from torch, every computation goes
+through the C ABI (cavs_treelstm_*).  Used by the tests and the benchmark."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from ._abi import check, lib, ptr
+from .schedule import Schedule
+
+
+class Config(ctypes.Structure):
+    _fields_ = [(k, ctypes.c_int) for k in
+                ("hidden", "embed", "vocab", "classes", "n_slots", "gemm_bf16", "max_vertices", "max_level_rows")]
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class TreeLSTM:
+    """Level-batched child-sum Tree-LSTM training step on one GPU."""
+
+    PARAM_NAMES = ("Emb", "W", "U", "B", "Wc", "bc")
+
+    def __init__(self, hidden, embed, vocab, classes, n_slots=2, gemm_bf16=False, max_vertices=1 << 16, max_level_rows=None,
+                 device="cuda"):
+        L = lib()
+        L.cavs_treelstm_param_count.restype = ctypes.c_size_t
+        L.cavs_treelstm_workspace_bytes.restype = ctypes.c_size_t
+        self.cfg = Config(hidden, embed, vocab, classes, n_slots, int(gemm_bf16), max_vertices, max_level_rows or max_vertices)
+        self.device = torch.device(device)
+        n_params = L.cavs_treelstm_param_count(ctypes.byref(self.cfg))
+        ws = L.cavs_treelstm_workspace_bytes(ctypes.byref(self.cfg))
+        if n_params == 0 or ws == 0:
+            check(1 if not L.cavs_last_error() else 1)
+        self.params = torch.zeros(n_params, dtype=torch.float32, device=self.device)
+        self.grads = torch.zeros(n_params, dtype=torch.float32, device=self.device)
+        self.workspace = torch.empty(ws + 256, dtype=torch.uint8, device=self.device)
+        base = (self.workspace.data_ptr() + 255) // 256 * 256
+        self._h = ctypes.c_void_p()
+        check(L.cavs_treelstm_create(ctypes.byref(self.cfg), ctypes.c_void_p(base), ctypes.c_size_t(ws), ctypes.byref(self._h)))
+        check(L.cavs_treelstm_bind(self._h, ctypes.c_void_p(self.params.data_ptr()), ctypes.c_void_p(self.grads.data_ptr())))
+        H, E, V, C = hidden, embed, vocab, classes
+        sizes = [V * E, E * 4 * H, 4 * H * H, 4 * H, C * H, C]
+        self.offsets = dict(zip(self.PARAM_NAMES, np.concatenate([[0], np.cumsum(sizes)[:-1]]).tolist()))
+        self.sizes = dict(zip(self.PARAM_NAMES, sizes))
+        self.n = 0
+
+    def close(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib().cavs_treelstm_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        o, s = self.offsets[name], self.sizes[name]
+        return flat[o:o + s]
+
+    def set_params(self, params: dict) -> None:
+        for k in self.PARAM_NAMES:
+            self.view(self.params, k).copy_(torch.from_numpy(np.ascontiguousarray(params[k], np.float32).ravel()))
+        self.refresh_weights()
+
+    def refresh_weights(self) -> None:
+        check(lib().cavs_treelstm_refresh_weights(self._h, _stream()))
+
+    def load_batch(self, sched: Schedule, tok_job: np.ndarray, label_job: np.ndarray, loss_rows: int = 0) -> None:
+        tok_job = np.ascontiguousarray(tok_job, np.int32)
+        label_job = np.ascontiguousarray(label_job, np.int32)
+        assert tok_job.size >= sched.n_total and label_job.size >= sched.n_total
+        check(lib().cavs_treelstm_load_batch(self._h, sched._h, ptr(tok_job), ptr(label_job), loss_rows, _stream()))
+        self.n = sched.n_scheduled
+
+    def forward(self) -> None:
+        check(lib().cavs_treelstm_forward(self._h, _stream()))
+
+    def backward(self) -> None:
+        check(lib().cavs_treelstm_backward(self._h, _stream()))
+
+    def read_loss(self) -> float:
+        out = ctypes.c_float()
+        status = ctypes.c_int()
+        check(lib().cavs_treelstm_read_loss(self._h, ctypes.byref(out), ctypes.byref(status), _stream()))
+        return out.value
+
+    def sgd(self, lr: float) -> None:
+        check(lib().cavs_sgd(ctypes.c_void_p(self.params.data_ptr()), ctypes.c_void_p(self.grads.data_ptr()),
+                             ctypes.c_size_t(self.params.numel()), ctypes.c_float(lr), _stream()))
+        self.refresh_weights()
+
+    def adagrad(self, acc: torch.Tensor, lr: float, eps: float = 1e-10) -> None:
+        check(lib().cavs_adagrad(ctypes.c_void_p(self.params.data_ptr()), ctypes.c_void_p(acc.data_ptr()),
+                                 ctypes.c_void_p(self.grads.data_ptr()), ctypes.c_size_t(self.params.numel()),
+                                 ctypes.c_float(lr), ctypes.c_float(eps), _stream()))
+        self.refresh_weights()
+
+    def peek(self, what: int, shape) -> np.ndarray:
+        p = ctypes.c_void_p()
+        nbytes = ctypes.c_size_t()
+        check(lib().cavs_treelstm_peek(self._h, what, ctypes.byref(p), ctypes.byref(nbytes)))
+        off = p.value - self.workspace.data_ptr()
+        t = self.workspace[off:off + nbytes.value].view(torch.float32)
+        torch.cuda.synchronize()
+        return t.cpu().numpy().reshape(shape)
+
+    def state(self) -> np.ndarray:
+        return self.peek(0, (self.n, 2 * self.cfg.hidden))
+
+    def loss_rows(self) -> np.ndarray:
+        return self.peek(1, (self.n,))
+
+    def grad_dict(self) -> dict:
+        torch.cuda.synchronize()
+        g = self.grads.cpu().numpy()
+        return {"d" + k: g[self.offsets[k]:self.offsets[k] + self.sizes[k]].copy() for k in self.PARAM_NAMES}

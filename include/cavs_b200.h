@@ -38,6 +38,8 @@ CAVS_API const char* cavs_status_string(int status);
 CAVS_API const char* cavs_last_error(void);
 /* Library version and the GPU architecture the kernels were compiled for ("sm_100a"). */
 CAVS_API const char* cavs_build_info(void);
+/* Kernels this library has launched in this process so far (every launch is counted). */
+CAVS_API unsigned long long cavs_launch_count(void);
 
 /* ------------------------------------------------------------------------ */
 /* Level scheduler (host only; no CUDA call)                                 */
@@ -76,6 +78,162 @@ CAVS_API int cavs_sched_ref_scatter(const cavs_sched* s, int level, int32_t* ids
 /* Whole forward + backward schedule serialised as one int32 stream (layout documented in
  * oracle/refsched_driver.cc); *n receives the length, CAVS_ERR_CAPACITY if it does not fit. */
 CAVS_API int cavs_sched_ref_stream(const cavs_sched* s, int32_t* out, int capacity, int* n);
+
+/* ------------------------------------------------------------------------ */
+/* Row movement behind the graph ops (device).  HBM-bound, 128-bit accesses. */
+/* ------------------------------------------------------------------------ */
+/* out[b,:] = inp[ids[b],:] for b < n_ids.  Replaces BatchedDynamicSelectedInputSliceCopyKernel
+ * as launched by GraphGatherOp / GraphPullOp (functor_batched_memcpy.cuh:34-47,
+ * op_impl_graphop.cu:62-76,243-249).  ids is a DEVICE array (the reference re-uploads a host
+ * vector before every launch).  Extension: ids[b] < 0 writes a zero row.  row_bytes must be a
+ * multiple of 4; rows that are multiples of 16 bytes in 16-byte aligned buffers take the
+ * 128-bit path. */
+CAVS_API int cavs_gather_rows(void* out, const void* inp, const int32_t* ids, int n_ids, size_t row_bytes, void* stream);
+/* out[ids[b],:] = inp[b,:] for b < n_ids.  Replaces BatchedDynamicSelectedOutputSliceCopyKernel
+ * as launched by GraphScatterOp / FunctionPopRetOp (functor_batched_memcpy.cuh:49-62,
+ * op_impl_graphop.cu:144-157,304-318).  Extension: ids[b] < 0 skips the row.  Target rows must
+ * be distinct (they are: one mailbox row per vertex). */
+CAVS_API int cavs_scatter_rows(void* out, const int32_t* ids, const void* inp, int n_ids, size_t row_bytes, void* stream);
+/* out[b,:] = 0 for b < n_rows.  Replaces BatchedDynamicSelectedAssignZeroKernel, which ignores
+ * the id values it is given and clears the first n rows (functor_batched_memcpy.cuh:64-75,
+ * op_impl_graphop.cu:77-86). */
+CAVS_API int cavs_zero_rows(void* out, int n_rows, size_t row_bytes, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Dense contractions (device).                                              */
+/* ------------------------------------------------------------------------ */
+/* bf16 x bf16 -> fp32-accumulate GEMM on the tcgen05 tensor cores (TMA-fed, TMEM accumulator).
+ * Replaces the cublasSgemm calls behind MatMul (cavs/backend/cublas_wrapper.cc:13-28,
+ * cavs/backend/op_impl_blas3_cublas.cc:35-70) for the bf16 configurations.
+ *   a_major 0: A is [m,k] row-major (pitch lda);  1: A is [k,m] row-major (used transposed)
+ *   b_major 0: B is [n,k] row-major (pitch ldb);  1: B is [k,n] row-major
+ *   out_mode 0: C (fp32) = A.B   1: C (fp32) += A.B   2: C (bf16) = A.B;  C is [m,n], pitch ldc.
+ * a and b need 16-byte aligned bases and pitches that are multiples of 8 elements.
+ * splits > 1 cuts K across CTAs: partials go to `scratch` (cavs_gemm_bf16_scratch_bytes) and are
+ * reduced in a fixed order.  status: optional device int raised if a bounded wait inside the
+ * kernel expires. */
+CAVS_API int cavs_gemm_bf16(void* c, long long ldc, int out_mode, const void* a, long long lda, int a_major,
+                            const void* b, long long ldb, int b_major, int m, int n, int k, int splits, void* scratch,
+                            size_t scratch_bytes, int* status, void* stream);
+CAVS_API size_t cavs_gemm_bf16_scratch_bytes(int m, int n, int splits);
+/* fp32 GEMM on the CUDA cores with element strides (any transpose without a copy):
+ * C[i,j] (+)= sum_p A[i*a_row_stride + p*a_col_stride] * B[p*b_row_stride + j*b_col_stride].
+ * The fp32 configurations use it to stay within 1e-5 of the reference's cublasSgemm. */
+CAVS_API int cavs_gemm_f32(float* c, long long ldc, int accumulate, const float* a, long long a_row_stride,
+                           long long a_col_stride, const float* b, long long b_row_stride, long long b_col_stride, int m,
+                           int n, int k, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Fused vertex-function kernels (device).  Level rows are [off, off+rows) of */
+/* arenas in tensor-id order; child is [n_slots, n_total], parent [n_total].  */
+/* ------------------------------------------------------------------------ */
+/* S[t] = sum_c h(child_c(t)), HK[t,c] = h(child_c(t)) for the level's rows, fp32 or bf16 output:
+ * Gather(Child=c) + Slice + Add of the vertex function (apps/paper/tree-lstm-cavs.cc:131-136,
+ * cavs/backend/op_impl_graphop.cu:32-90).  state is [n_total, 2*hidden] (h|c). */
+CAVS_API int cavs_gather_child_h(void* S, void* HK, int bf16, const float* state, const int32_t* child, int n_total,
+                                 int off, int rows, int hidden, int n_slots, void* stream);
+/* Fused child-sum Tree-LSTM cell forward (apps/paper/tree-lstm-cavs.cc:159-171; stands in for the
+ * NVRTC-fused elementwise groups, cavs/backend/op_impl_fused_kernel.cu:62-64, plus the forward
+ * Scatter and Push, cavs/backend/op_impl_graphop.cu:108-202).  A [n_total,4H] = x.W (i,o,u,f),
+ * P [rows,3H] = (sum h).U_iou, Q [rows,n_slots,H] = h_c.U_f, bias [4H] (i,f,u,o).  Writes
+ * gates [n_total,(3+n_slots)H] and state [n_total,2H].  leaf != 0: no children (P, Q unused). */
+CAVS_API int cavs_treelstm_cell_fwd(float* state, float* gates, const float* A, const float* P, const float* Q,
+                                    const float* bias, const int32_t* child, int n_total, int off, int rows, int hidden,
+                                    int n_slots, int leaf, void* stream);
+/* Fused gate-gradient backward of the cell: reads d(pushed h) dOut [n_total,H], the parent's
+ * d(h|c) from mailbox [n_total,2H] (zeros for roots), saved gates and states; writes
+ * dA [n_total,4H] (zi|zo|zu|sum zf), ZF [n_total,n_slots,H] (fp32 or bf16) and d(c_child) into the
+ * children's mailbox rows (Scatter(Child=c), cavs/backend/op_decl_graphop.cc:25-41). */
+CAVS_API int cavs_treelstm_cell_bwd(void* dA, void* ZF, int bf16, float* mailbox, const float* dOut, const float* gates,
+                                    const float* state, const int32_t* child, const int32_t* parent, int n_total, int off,
+                                    int rows, int hidden, int n_slots, int leaf, void* stream);
+/* mailbox[child_c(t)].h = ds[b] + dq[b,c]: the child-state gradient scatter. */
+CAVS_API int cavs_scatter_child_grad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total,
+                                     int off, int rows, int hidden, int n_slots, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Around the vertex function (device).                                      */
+/* ------------------------------------------------------------------------ */
+/* out[t,:] = table[tok[t],:], fp32 or bf16 output.  Replaces BatchedCopy
+ * (cavs/backend/op_impl_embedding_lookup.cu:23-35); ids are int32, out-of-range ids read row 0. */
+CAVS_API int cavs_embed_fwd(void* out, int bf16, const float* table, const int32_t* tok, int rows, int embed, int vocab,
+                            void* stream);
+/* Deterministic segmented embedding gradient; replaces BatchedSparseUpdate's atomicAdd
+ * (cavs/backend/op_impl_embedding_lookup.cu:91-103).  order: row indices grouped by token;
+ * chunk_off [n_chunks+1]: ranges of `order`, at most 256 rows each, never spanning two tokens;
+ * seg_first_chunk [n_seg+1]: first chunk of each token group; seg_tok [n_seg]: its token;
+ * scratch: [n_chunks, embed] fp32.  Rows of dtable for absent tokens are left untouched. */
+CAVS_API int cavs_embed_bwd_segmented(float* dtable, const float* dX, const int32_t* order, const int32_t* chunk_off,
+                                      int n_chunks, const int32_t* seg_first_chunk, const int32_t* seg_tok, int n_seg,
+                                      float* scratch, int embed, void* stream);
+/* Classifier + softmax cross-entropy, forward and backward in one pass (classes <= 8).  Replaces
+ * FullyConnected + SoftmaxEntropyLoss and their gradients
+ * (cavs/backend/op_impl_fullyconnected_cublas.cc:33-85,104-176,
+ * cavs/backend/op_impl_softmax_entropy_logits_loss.cu:106-140,213-250): loss[t] = -log softmax(h Wc^T + bc)[label],
+ * dz = (softmax - onehot) * inv_rows (the reference divides by the row count and ignores the
+ * upstream gradient), dH = dz Wc, dWc = dz^T h, dbc = sum dz, *loss_sum = sum loss.  label < 0 marks a
+ * row without a loss term.  h has row pitch h_pitch.  Scratch holds per-CTA partials reduced in order. */
+CAVS_API size_t cavs_fc_softmax_xent_scratch_bytes(int hidden, int classes);
+CAVS_API int cavs_fc_softmax_xent(float* loss, float* loss_sum, float* dH, float* dWc, float* dbc, const float* h,
+                                  long long h_pitch, const int32_t* label, const float* Wc, const float* bc, int rows,
+                                  int hidden, int classes, float inv_rows, float* scratch, void* stream);
+/* out[j] = sum_r x[r,j] (fp32 or bf16 input), two-stage fixed-order reduction.  Replaces the
+ * per-thread serial column loop used for bias gradients (cavs/backend/op_impl_elementwise.cuh:31-37). */
+CAVS_API size_t cavs_column_sum_scratch_bytes(int cols);
+CAVS_API int cavs_column_sum(float* out, const void* x, int bf16, long long pitch, int rows, int cols, float* scratch,
+                             void* stream);
+/* w <- w - lr*g.  Replaces SGDKernel (cavs/backend/op_impl_sgd.cu:15-47). */
+CAVS_API int cavs_sgd(float* w, const float* g, size_t count, float lr, void* stream);
+/* acc += g^2; w <- w - lr*g/(sqrt(acc)+eps).  No counterpart in the reference (it registers only SGD). */
+CAVS_API int cavs_adagrad(float* w, float* acc, const float* g, size_t count, float lr, float eps, void* stream);
+/* dst (bf16) = src (fp32): shadow copies of the GEMM weights after an update. */
+CAVS_API int cavs_cast_bf16(void* dst, const float* src, size_t count, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Tree-LSTM engine: the level loop, forward and backward.                   */
+/* Replaces GraphStatement::Run / GraphGradStatement::Run                    */
+/* (cavs/midend/statement.cc:43-123) for the child-sum Tree-LSTM vertex       */
+/* function (apps/paper/tree-lstm-cavs.cc:107-172; n_slots = 1 with permuted  */
+/* parameter blocks is the chain LSTM of apps/paper/seq-lstm-cavs.cc:45-86).  */
+/* ------------------------------------------------------------------------ */
+typedef struct cavs_treelstm cavs_treelstm;
+typedef struct cavs_treelstm_config {
+  int hidden, embed, vocab, classes, n_slots;
+  int gemm_bf16;       /* 1: gate GEMMs on tcgen05 with bf16 operands; 0: fp32 GEMMs on the CUDA cores */
+  int max_vertices;    /* capacity: vertices per batch */
+  int max_level_rows;  /* capacity: rows of the widest level */
+} cavs_treelstm_config;
+/* Parameters and gradients are ONE flat fp32 device buffer each, laid out
+ * Emb [vocab,embed] | W [embed,4H] (i,o,u,f) | U = U_iou [H,3H] then U_f [H,H] | B [4H] (i,f,u,o) | Wc [classes,H] | bc [classes]. */
+CAVS_API size_t cavs_treelstm_param_count(const cavs_treelstm_config* cfg);
+CAVS_API size_t cavs_treelstm_workspace_bytes(const cavs_treelstm_config* cfg);
+/* workspace: caller-owned device memory, 256-byte aligned.  Allocates only a pinned host staging
+ * buffer for the per-batch index upload. */
+CAVS_API int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* workspace, size_t workspace_bytes, cavs_treelstm** out);
+CAVS_API void cavs_treelstm_destroy(cavs_treelstm* e);
+CAVS_API int cavs_treelstm_bind(cavs_treelstm* e, float* params, float* grads);
+/* Refreshes the bf16 shadow copies of W and U (call after every parameter update; no-op in fp32 mode). */
+CAVS_API int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream);
+/* tok_job / label_job: host int32 per vertex in job order (compact, sample-major).  Reorders them to
+ * tensor-id order (the Pull and FunctionPopRet permutations, cavs/backend/op_impl_graphop.cu:214-254,275-327),
+ * builds the embedding-gradient segments and uploads all tables with one async copy.
+ * loss_rows: divisor of the loss gradient (0 = this batch's vertex count). */
+CAVS_API int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job, const int32_t* label_job,
+                                      int loss_rows, void* stream);
+CAVS_API int cavs_treelstm_forward(cavs_treelstm* e, void* stream);
+/* Loss head, level loop in reverse, deferred weight / bias / embedding gradients (overwrites grads). */
+CAVS_API int cavs_treelstm_backward(cavs_treelstm* e, void* stream);
+/* Copies the loss sum and the device status word to the host; synchronises `stream`. */
+CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int* status_host, void* stream);
+/* Per-kernel-class timing with CUDA events on the launching stream.  While enabled, every launch
+ * of forward / backward is bracketed by two events.  profile_read sums, per class, the elapsed
+ * milliseconds, the algorithmic work (flops for class 0, bytes otherwise) and the launch count
+ * since the last read.  Classes: 0 gate GEMMs, 1 cell forward, 2 cell backward, 3 child-h gather,
+ * 4 child-gradient scatter, 5 loss head, 6 embedding forward, 7 embedding backward, 8 column sum. */
+CAVS_API int cavs_treelstm_profile(cavs_treelstm* e, int enable);
+CAVS_API int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes);
+/* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H], 3 mailbox [n,2H], 4 gates. */
+CAVS_API int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes);
 
 /* ------------------------------------------------------------------------ */
 /* Synthetic workloads (host only).  One SplitMix64 stream per (seed, stream).*/

@@ -1,0 +1,120 @@
+"""The CUDA Tree-LSTM step (forward, loss, backward, update) through the C ABI vs the CPU oracle
+on identical seeded inputs.  fp32 configurations: 1e-5 relative; bf16-GEMM configurations: 2e-2
+relative (and tighter against the oracle run with bf16-rounded GEMM operands)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from cavs_b200 import schedule as S
+from cavs_b200.treelstm import TreeLSTM
+from helpers import make_params, make_tree_batch, rel_err, tables_from_schedule
+
+pytestmark = pytest.mark.gpu
+KEYS = ("state", "loss", "dEmb", "dW", "dU", "dB", "dWc", "dbc")
+GOLD = Path(__file__).parent / "golden" / "treelstm_small.npz"
+
+
+def _run(cuda, parents, tok_job, label_job, params, H, E, V, C, K=2, bf16=False):
+    s = S.Schedule().load(parents, n_slots=K)
+    eng = TreeLSTM(H, E, V, C, n_slots=K, gemm_bf16=bf16, max_vertices=max(s.n_total, 1), max_level_rows=max(s.max_level_rows, 1))
+    eng.set_params(params)
+    eng.load_batch(s, tok_job, label_job)
+    eng.forward()
+    eng.backward()
+    loss_sum = eng.read_loss()
+    out = dict(state=eng.state(), loss=eng.loss_rows(), **eng.grad_dict())
+    return s, eng, out, loss_sum
+
+
+def _oracle(s, tok_job, label_job, params, H, E, V, C, K=2, bf16=False):
+    tb = tables_from_schedule(s)
+    return oracle.treelstm_fwd_bwd(tb, tok_job[tb["t2j"]], label_job[tb["t2j"]], params, H, E, V, C, K=K, gemm_bf16=bf16)
+
+
+def test_golden_fp32(cuda):
+    g = np.load(GOLD)
+    H, E, V, C = (int(x) for x in g["dims"])
+    params = {k: g["p_" + k] for k in ("Emb", "W", "U", "B", "Wc", "bc")}
+    s, eng, out, loss_sum = _run(cuda, g["parents"], g["tok_job"], g["label_job"], params, H, E, V, C)
+    for k in KEYS:
+        assert rel_err(out[k], g["r_" + k]) < 1e-5, k
+    assert abs(loss_sum - g["r_loss"].sum()) < 1e-5 * abs(g["r_loss"].sum())
+
+
+@pytest.mark.parametrize("batch,leaf_hi,H,E,V,C", [
+    (64, 50, 150, 300, 21701, 5),   # the binary Tree-LSTM configuration (fp32)
+    (7, 9, 32, 20, 100, 3),
+    (1, 2, 8, 8, 10, 2),            # one tree of two leaves
+])
+def test_fp32_parity_with_oracle(cuda, batch, leaf_hi, H, E, V, C):
+    parents, tok_job, label_job = make_tree_batch(100 + batch, batch, 2, leaf_hi, V, C)
+    params = make_params(batch, H, E, V, C, scale=0.05, bias_scale=0.02)
+    s, eng, out, loss_sum = _run(cuda, parents, tok_job, label_job, params, H, E, V, C)
+    ref = _oracle(s, tok_job, label_job, params, H, E, V, C)
+    for k in KEYS:
+        assert rel_err(out[k], ref[k]) < 1e-5, k
+    # determinism: a second run is bit-identical
+    eng.forward(); eng.backward(); eng.read_loss()
+    again = dict(state=eng.state(), loss=eng.loss_rows(), **eng.grad_dict())
+    for k in KEYS:
+        assert np.array_equal(out[k], again[k]), k
+
+
+def test_bf16_parity_with_oracle(cuda):
+    H, E, V, C = 256, 128, 5000, 5
+    parents, tok_job, label_job = make_tree_batch(321, 48, 2, 40, V, C)
+    params = make_params(9, H, E, V, C, scale=0.05, bias_scale=0.02)
+    s, eng, out, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, bf16=True)
+    ref32 = _oracle(s, tok_job, label_job, params, H, E, V, C)
+    refbf = _oracle(s, tok_job, label_job, params, H, E, V, C, bf16=True)
+    for k in KEYS:
+        assert rel_err(out[k], ref32[k]) < 2e-2, k      # the bf16-GEMM contract
+        assert rel_err(out[k], refbf[k]) < 5e-3, k      # same rounding points as the oracle's bf16 mode
+
+
+@pytest.mark.parametrize("K,arity", [(1, None), (4, 4)])
+def test_other_slot_counts_fp32(cuda, K, arity):
+    H, E, V, C = 24, 16, 50, 4
+    if K == 1:
+        parents = S.synth_chains(5, 9, 2, 12)
+        lens = (parents == -1).argmax(1) + 1
+        tok_job = S.synth_zipf(6, 1.1, V, int(lens.sum()))
+        label_job = S.synth_uniform_int(7, C, int(lens.sum()))
+    else:
+        parents, tok_job, label_job = make_tree_batch(5, 9, 2, 12, V, C, max_arity=arity)
+    params = make_params(4, H, E, V, C, scale=0.3, bias_scale=0.1)
+    s, eng, out, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, K=K)
+    ref = _oracle(s, tok_job, label_job, params, H, E, V, C, K=K)
+    for k in KEYS:
+        assert rel_err(out[k], ref[k]) < 1e-5, k
+
+
+def test_updates_match_oracle(cuda):
+    H, E, V, C = 16, 16, 40, 3
+    parents, tok_job, label_job = make_tree_batch(55, 5, 2, 6, V, C)
+    params = make_params(2, H, E, V, C, scale=0.3)
+    s, eng, out, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C)
+    flat_w = eng.params.cpu().numpy().copy()
+    flat_g = eng.grads.cpu().numpy().copy()
+    eng.sgd(0.5)
+    w = flat_w.copy(); oracle.sgd(w, flat_g, 0.5)
+    assert rel_err(eng.params.cpu().numpy(), w) < 1e-6
+    acc = torch.zeros_like(eng.params)
+    acc_h = np.zeros_like(flat_w)
+    w2 = eng.params.cpu().numpy().copy()
+    eng.adagrad(acc, 0.05)
+    oracle.adagrad(w2, acc_h, flat_g, 0.05, 1e-10)
+    assert rel_err(eng.params.cpu().numpy(), w2) < 1e-6 and rel_err(acc.cpu().numpy(), acc_h) < 1e-6
+
+
+def test_capacity_errors(cuda):
+    from cavs_b200 import CavsError
+    parents, tok_job, label_job = make_tree_batch(1, 4, 2, 6, 20, 2)
+    s = S.Schedule().load(parents)
+    eng = TreeLSTM(8, 8, 20, 2, max_vertices=4, max_level_rows=4)
+    with pytest.raises(CavsError) as e:
+        eng.load_batch(s, tok_job, label_job)
+    assert e.value.status == 3
