@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the level-batched Tree-LSTM training step (forward + backward + update).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload (default "dp_treelstm"): global batch of 4096 random binary trees, leaves uniform in
+[2,128], hidden 1024, embedding 1024, vocabulary 50000 with Zipf(1.1) leaf tokens, 5-class loss on
+every vertex, bf16 gate GEMMs with fp32 accumulation and fp32 cell maths, Adagrad(lr=0.05).  The
+global batch is split evenly by tree across the ranks (strong scaling); gradients are summed with
+one NCCL all-reduce per step.  Inputs are seeded synthetic stand-ins for the SST / PTB files the
+reference's apps read (those are not distributed with it).
+
+Prints ONE JSON line on rank 0.  `value` times steps whose index tables are already resident in
+HBM; `e2e` times the whole public-API step from host arrays: host level scheduling, one pinned
+host-to-device upload, forward, backward, all-reduce, update and the device-to-host read of the
+loss.  `--impl reference` times the CPU oracle (the reference has no CPU implementation of this
+path and its CUDA-8 sources do not build here) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (global_batch, leaf_lo, leaf_hi, hidden, embed, vocab, classes, bf16)
+    "dp_treelstm": dict(batch=4096, leaf_lo=2, leaf_hi=128, hidden=1024, embed=1024, vocab=50000, classes=5, bf16=True,
+                        init_scale=0.05, lr=0.05),
+    "sst_treelstm": dict(batch=64, leaf_lo=2, leaf_hi=50, hidden=150, embed=300, vocab=21701, classes=5, bf16=False,
+                         init_scale=0.05, lr=0.05),
+}
+POOL = 16            # distinct pre-generated batches cycled through by the end-to-end loop
+SEED = 0xC0FFEE00
+
+
+def make_batch(wl, idx, rank, world):
+    """Global batch `idx`, then this rank's shard of it.  Returns (parents, tok_job, label_job, global_vertices)."""
+    from cavs_b200 import schedule as S
+    b = wl["batch"]
+    parents, is_leaf = S.synth_trees(SEED + 16 * 5 + 1000 * idx, b, wl["leaf_lo"], wl["leaf_hi"])
+    lens = (parents == -1).argmax(1) + 1
+    tok_pad = S.synth_zipf(SEED + 16 * 5 + 1000 * idx + 1, 1.1, wl["vocab"], parents.size).reshape(parents.shape) * is_leaf
+    lab_pad = S.synth_uniform_int(SEED + 16 * 5 + 1000 * idx + 2, wl["classes"], parents.size).reshape(parents.shape)
+    per = b // world
+    lo, hi = rank * per, (rank + 1) * per
+    mask = np.arange(parents.shape[1])[None, :] < lens[lo:hi, None]
+    tok_job = np.ascontiguousarray(tok_pad[lo:hi][mask], np.int32)
+    label_job = np.ascontiguousarray(lab_pad[lo:hi][mask], np.int32)
+    return np.ascontiguousarray(parents[lo:hi]), tok_job, label_job, int(lens.sum())
+
+
+def make_params(wl):
+    from cavs_b200 import schedule as S
+    H, E, V, C, sc = wl["hidden"], wl["embed"], wl["vocab"], wl["classes"], wl["init_scale"]
+    base = SEED + 16 * 5 + 3
+    return dict(Emb=S.synth_uniform_float(base, sc, (V, E)), W=S.synth_uniform_float(base + 100, sc, (E * 4 * H,)),
+                U=S.synth_uniform_float(base + 200, sc, (4 * H * H,)), B=np.zeros(4 * H, np.float32),
+                Wc=S.synth_uniform_float(base + 300, sc, (C, H)), bc=np.zeros(C, np.float32))
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.path = gpu_index, None, f"/tmp/cavs_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for line in Path(self.path).read_text().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return out
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], tflops=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
+
+
+def cpu_baseline_sample(wl, n_trees, repeats=1):
+    """Times the CPU oracle (fwd + bwd + Adagrad) on the first n_trees trees of batch 0.  Returns (trees/s, seconds)."""
+    import oracle
+    from cavs_b200 import schedule as S
+    H, E, V, C = wl["hidden"], wl["embed"], wl["vocab"], wl["classes"]
+    parents, tok_job, label_job, _ = make_batch(dict(wl, batch=n_trees), 0, 0, 1)
+    params = make_params(wl)
+    flat = {k: v.copy() for k, v in params.items()}
+    acc = {k: np.zeros_like(v) for k, v in params.items()}
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        s = S.Schedule().load(parents)
+        fg, fs, bg, bs = s.tables(0)
+        t2j, _ = s.maps()
+        tb = dict(n=s.n_total, n_levels=s.n_levels, level_off=s.level_off, fg=fg, fs=fs, bg=bg, bs=bs)
+        out = oracle.treelstm_fwd_bwd(tb, tok_job[t2j], label_job[t2j], flat, H, E, V, C, gemm_bf16=wl["bf16"])
+        for k in flat:
+            oracle.adagrad(flat[k].reshape(-1), acc[k].reshape(-1), out["d" + k].reshape(-1), wl["lr"])
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return n_trees / best, best
+
+
+def run_reference(args, wl, rank, world):
+    """The reference arm: the oracle port on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    import oracle
+    oracle.oracle_lib()
+    n_trees = args.sample_trees
+    for _ in range(max(args.warmup, 0) and 1):
+        cpu_baseline_sample(wl, max(2, n_trees // 4))
+    t0 = time.perf_counter()
+    rates = [cpu_baseline_sample(wl, n_trees)[0] for _ in range(args.steps)]
+    total = time.perf_counter() - t0
+    value = n_trees * args.steps / total
+    line = dict(metric="treelstm_train_trees_per_sec", value=value, unit="trees/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=1e3 * total / args.steps, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="bf16" if wl["bf16"] else "f32", data="synthetic", impl="reference",
+                config=dict(workload=args.workload, global_batch=wl["batch"], hidden=wl["hidden"], embed=wl["embed"],
+                            vocab=wl["vocab"], classes=wl["classes"], leaves=[wl["leaf_lo"], wl["leaf_hi"]]),
+                cpu_baseline=dict(value=value, unit="trees/s", cores=oracle.num_threads(), kind="port",
+                                  sample=f"{n_trees} trees of batch 0 per step, fwd+bwd+Adagrad, OpenMP over rows"),
+                e2e=dict(value=value, unit="trees/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                note="the reference has no CPU implementation of this path and its CUDA 8 sources do not build here; "
+                     "this arm times the CPU oracle port (oracle/cavs_oracle.c)")
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dp_treelstm", choices=sorted(WORKLOADS))
+    ap.add_argument("--sample-trees", type=int, default=24, help="trees per CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+    from cavs_b200 import lib, schedule as S
+    from cavs_b200.treelstm import TreeLSTM
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    assert wl["batch"] % world == 0
+
+    L = lib()
+    L.cavs_launch_count.restype = ctypes.c_ulonglong
+    pool = [make_batch(wl, i, rank, world) for i in range(POOL)]
+    scheds = [S.Schedule().load(p[0]) for p in pool]
+    max_n = max(s.n_total for s in scheds)
+    max_rows = max(s.max_level_rows for s in scheds)
+    eng = TreeLSTM(wl["hidden"], wl["embed"], wl["vocab"], wl["classes"], gemm_bf16=wl["bf16"], max_vertices=max_n,
+                   max_level_rows=max_rows, device=dev)
+    eng.set_params(make_params(wl))
+    acc = torch.zeros_like(eng.params)
+    pinned = [tuple(torch.from_numpy(a).pin_memory() for a in p[:3]) for p in pool]
+    host_sched = S.Schedule()
+
+    def device_step():
+        eng.forward()
+        eng.backward()
+        if world > 1:
+            dist.all_reduce(eng.grads)
+        eng.adagrad(acc, wl["lr"])
+
+    def stage(i):
+        """Host scheduling of batch i and the pinned upload of its tables (staged; forward() promotes it)."""
+        par, tok, lab = (t.numpy() for t in pinned[i % POOL])
+        host_sched.load(par)
+        eng.load_batch(host_sched, tok, lab, loss_rows=pool[i % POOL][3])
+
+    def e2e_loop(steps):
+        # Software-pipelined like a data loader: while the GPU runs step i the host schedules batch
+        # i+1 and enqueues its upload; every step's tables still cross PCIe inside the timed region.
+        losses = []
+        stage(0)
+        for i in range(steps):
+            device_step()
+            if i + 1 < steps:
+                stage(i + 1)
+            losses.append(eng.read_loss())
+        return losses
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        l0 = L.cavs_launch_count()
+        e0.record()
+        fn(steps)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = L.cavs_launch_count() - l0
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    # ---- device-resident arm: tables of batch 0 already in HBM ----
+    eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3])
+    for _ in range(args.warmup):
+        device_step()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_dev, launches = timed(lambda k: [device_step() for _ in range(k)], args.steps)
+    loss_dev = eng.read_loss()
+    # ---- end-to-end arm: host arrays in, loss out, every step ----
+    e2e_loop(args.warmup)
+    ms_e2e, _ = timed(e2e_loop, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+
+    # ---- per-kernel-class timing for the roofline (separate instrumented steps) ----
+    L.cavs_treelstm_profile(eng._h, 1)
+    prof_steps = 3
+    eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3])
+    for _ in range(prof_steps):
+        eng.forward(); eng.backward()
+    torch.cuda.synchronize()
+    n_cls = 9
+    ms_c = (ctypes.c_double * n_cls)(); work_c = (ctypes.c_double * n_cls)(); cnt_c = (ctypes.c_int * n_cls)()
+    L.cavs_treelstm_profile_read(eng._h, ms_c, work_c, cnt_c, n_cls)
+    L.cavs_treelstm_profile(eng._h, 0)
+    names = ["gate_gemm", "cell_fwd", "cell_bwd", "gather_child_h", "scatter_child_grad", "loss_head", "embed_fwd", "embed_bwd",
+             "column_sum"]
+    peaks = measured_peaks()
+    classes = {}
+    for i, nm in enumerate(names):
+        if cnt_c[i] == 0:
+            continue
+        rate = work_c[i] / (ms_c[i] * 1e-3) if ms_c[i] > 0 else 0.0
+        if i == 0:
+            classes[nm] = dict(ms_per_step=ms_c[i] / prof_steps, launches_per_step=cnt_c[i] // prof_steps, tflops=rate / 1e12,
+                               frac=rate / 1e12 / peaks["tflops"])
+        else:
+            classes[nm] = dict(ms_per_step=ms_c[i] / prof_steps, launches_per_step=cnt_c[i] // prof_steps, gbs=rate / 1e9,
+                               frac=rate / 1e9 / peaks["hbm_gbs"])
+    dominant = max(classes, key=lambda k: classes[k]["ms_per_step"])
+    d = classes[dominant]
+    if dominant == "gate_gemm":
+        roofline = dict(bound="tensor", kernel="GemmBf16Kernel (all gate / gradient GEMMs of a step)", achieved=d["tflops"],
+                        peak=peaks["tflops"], unit="TFLOP/s", frac=d["frac"], traffic=None, peak_source=peaks["source"])
+    else:
+        roofline = dict(bound="hbm", kernel=dominant, achieved=d["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=d["frac"],
+                        traffic=None, peak_source=peaks["source"])
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    trees = wl["batch"]
+    value = trees * args.steps / (ms_dev * 1e-3)
+    e2e_value = trees * args.steps / (ms_e2e * 1e-3)
+    h2d = int((2 + 5) * max_n * 4)      # child x2, parent, tok, label, order (+ small segment tables)
+    line = dict(metric="treelstm_train_trees_per_sec", value=value, unit="trees/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                ms_per_step=ms_dev / args.steps, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="bf16" if wl["bf16"] else "f32", data="synthetic",
+                config=dict(workload=args.workload, global_batch=trees, trees_per_gpu=trees // world, hidden=wl["hidden"],
+                            embed=wl["embed"], vocab=wl["vocab"], classes=wl["classes"], leaves=[wl["leaf_lo"], wl["leaf_hi"]],
+                            vertices_per_gpu=int(scheds[0].n_total), levels=int(scheds[0].n_levels), optimizer="adagrad",
+                            parallelism=f"dp{world}", l2="working set per step (tens of GB) exceeds L2; no flush needed"),
+                e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8),
+                gpu_launches=int(launches), loss_sum=loss_dev, clocks=clocks, roofline=roofline, kernel_classes=classes)
+    if not args.no_cpu_baseline:
+        rate, secs = cpu_baseline_sample(wl, args.sample_trees)
+        import oracle
+        line["cpu_baseline"] = dict(value=rate, unit="trees/s", cores=oracle.num_threads(), kind="port",
+                                    sample=f"{args.sample_trees} trees of batch 0, one fwd+bwd+Adagrad step ({secs:.1f} s)")
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

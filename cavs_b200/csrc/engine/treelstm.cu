@@ -35,7 +35,7 @@ struct cavs_treelstm {
   bool bf16 = false;
   size_t elt = 4;               // bytes per GEMM-operand element
   // ---- device workspace views ----
-  int32_t* d_idx = nullptr;     // index blob, mirrored by h_idx (pinned)
+  int32_t* d_idx = nullptr;     // two index blobs of idx_ints each, mirrored by h_idx (pinned)
   int32_t* h_idx = nullptr;
   size_t idx_ints = 0;
   uint8_t *X = nullptr, *S = nullptr, *HK = nullptr, *dA = nullptr, *ZF = nullptr;   // GEMM operands (fp32 or bf16)
@@ -46,11 +46,16 @@ struct cavs_treelstm {
   size_t splitk_bytes = 0;
   uint8_t *W_bf = nullptr, *U_bf = nullptr;
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
-  // ---- current batch ----
-  int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
-  std::vector<int32_t> level_off;
-  int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
-          *seg_first_chunk = nullptr, *seg_tok = nullptr;
+  // ---- batches: two slots so the tables of the next batch can be packed and uploaded while the
+  // current one executes; forward() promotes the staged slot ----
+  struct Batch {
+    int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
+    std::vector<int32_t> level_off;
+    int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
+            *seg_first_chunk = nullptr, *seg_tok = nullptr;
+  };
+  Batch slot[2];
+  int active = -1, staged = -1;
   std::vector<int32_t> bucket;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
   bool prof_on = false;
@@ -145,7 +150,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   const size_t N = c.max_vertices, L = c.max_level_rows, H = c.hidden, E = c.embed, K = c.n_slots;
   const size_t elt = c.gemm_bf16 ? 2 : 4;
   Carver w(base);
-  e->d_idx = w.Take<int32_t>(IdxInts(c));
+  e->d_idx = w.Take<int32_t>(2 * IdxInts(c));
   e->X = w.Take<uint8_t>(N * E * elt);
   e->S = w.Take<uint8_t>(N * H * elt);
   e->HK = w.Take<uint8_t>(N * K * H * elt);
@@ -231,7 +236,7 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     return Fail(CAVS_ERR_CAPACITY, "treelstm_create: workspace needs " + std::to_string(need) + " bytes");
   }
   e->idx_ints = IdxInts(*cfg);
-  cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
+  cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), 2 * e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
   if (err != cudaSuccess) {
     delete e;
     return Fail(CAVS_ERR_CUDA, std::string("treelstm_create: pinned staging: ") + cudaGetErrorString(err));
@@ -284,19 +289,22 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   CAVS_REQUIRE(sch.max_level_rows() <= e->cfg.max_level_rows, CAVS_ERR_CAPACITY,
                "treelstm_load_batch: widest level has " + std::to_string(sch.max_level_rows()) + " rows, capacity " +
                    std::to_string(e->cfg.max_level_rows));
-  e->n = n; e->n_total = nt; e->n_levels = sch.n_levels();
-  e->loss_rows = loss_rows > 0 ? loss_rows : std::max(n, 1);
-  e->level_off = sch.level_off();
+  const int which = e->active < 0 ? 0 : 1 - e->active;
+  cavs_treelstm::Batch& bt = e->slot[which];
+  bt.n = n; bt.n_total = nt; bt.n_levels = sch.n_levels();
+  bt.loss_rows = loss_rows > 0 ? loss_rows : std::max(n, 1);
+  bt.level_off = sch.level_off();
 
   // Pack the blob: child | parent | tok | label | order | chunk_off | seg_first_chunk | seg_tok.
-  int32_t* h = e->h_idx;
+  int32_t* h = e->h_idx + static_cast<size_t>(which) * e->idx_ints;
+  int32_t* d = e->d_idx + static_cast<size_t>(which) * e->idx_ints;
   size_t o = 0;
-  auto view = [&](size_t count, int32_t** dev) { int32_t* p = h + o; *dev = e->d_idx + o; o += count; return p; };
-  int32_t* h_child = view(static_cast<size_t>(K) * nt, &e->child);
-  int32_t* h_parent = view(nt, &e->parent);
-  int32_t* h_tok = view(nt, &e->tok);
-  int32_t* h_label = view(nt, &e->label);
-  int32_t* h_order = view(nt, &e->order);
+  auto view = [&](size_t count, int32_t** dev) { int32_t* p = h + o; *dev = d + o; o += count; return p; };
+  int32_t* h_child = view(static_cast<size_t>(K) * nt, &bt.child);
+  int32_t* h_parent = view(nt, &bt.parent);
+  int32_t* h_tok = view(nt, &bt.tok);
+  int32_t* h_label = view(nt, &bt.label);
+  int32_t* h_order = view(nt, &bt.order);
   std::memcpy(h_child, sch.child_t().data(), sizeof(int32_t) * K * nt);
   std::memcpy(h_parent, sch.parent_t().data(), sizeof(int32_t) * nt);
   const int32_t* t2j = sch.t2j().data();
@@ -315,9 +323,9 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   for (int v = 0; v < V; ++v) { if (e->bucket[v + 1]) ++n_seg; e->bucket[v + 1] += e->bucket[v]; }
   int n_chunks = 0;
   for (int v = 0; v < V; ++v) n_chunks += (e->bucket[v + 1] - e->bucket[v] + kEmbedChunk - 1) / kEmbedChunk;
-  int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &e->chunk_off);
-  int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &e->seg_first_chunk);
-  int32_t* h_seg_tok = view(n_seg, &e->seg_tok);
+  int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_off);
+  int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.seg_first_chunk);
+  int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
   CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
   int si = 0, ci = 0;
   for (int v = 0; v < V; ++v) {
@@ -330,15 +338,19 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   h_seg_first[si] = ci;
   h_chunk_off[ci] = n;
   for (int t = 0; t < n; ++t) h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
-  e->n_seg = n_seg; e->n_chunks = n_chunks;
-  CAVS_CUDA(cudaMemcpyAsync(e->d_idx, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  bt.n_seg = n_seg; bt.n_chunks = n_chunks;
+  CAVS_CUDA(cudaMemcpyAsync(d, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  e->staged = which;
   return CAVS_OK;
 }
 
 extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_forward: parameters not bound");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int n = e->n, nt = e->n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots;
+  if (e->staged >= 0) { e->active = e->staged; e->staged = -1; }
+  CAVS_REQUIRE(e->active >= 0, CAVS_ERR_BAD_ARG, "treelstm_forward: no batch loaded");
+  const cavs_treelstm::Batch& bt = e->slot[e->active];
+  const int n = bt.n, nt = bt.n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots;
   if (n == 0) return CAVS_OK;
   const float* Emb = e->params;
   const void* W = e->bf16 ? static_cast<const void*>(e->W_bf) : e->params + e->OffW();
@@ -349,26 +361,26 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   int rc;
   const double elt = static_cast<double>(e->elt);
   PROF(e, kProfEmbedFwd, static_cast<double>(n) * (4 + 4.0 * E + elt * E), st,
-       LaunchEmbedFwd(e->X, e->bf16, Emb, e->tok, n, E, e->cfg.vocab, st));
+       LaunchEmbedFwd(e->X, e->bf16, Emb, bt.tok, n, E, e->cfg.vocab, st));
   if ((rc = Gemm(e, e->A, 4 * H, 0, e->X, E, false, W, 4 * H, false, n, 4 * H, E, false, st))) return rc;
-  for (int l = 0; l < e->n_levels; ++l) {
-    const int off = e->level_off[l], rows = e->level_off[l + 1] - off;
+  for (int l = 0; l < bt.n_levels; ++l) {
+    const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     if (l == 0) {
       // leaf rows: read A (4H), write gates ((3+K)H) and h|c (2H)
       PROF(e, kProfCellFwd, 4.0 * rows * H * (4 + 3 + K + 2), st,
-           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, B, e->child, nt, off, rows, H, K, true, st));
+           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, B, bt.child, nt, off, rows, H, K, true, st));
       continue;
     }
     // read K child h rows (fp32) + K indices, write S and HK
     PROF(e, kProfGatherH, static_cast<double>(rows) * (4.0 * K * H + 4.0 * K + elt * (1 + K) * H), st,
-         LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, e->child, nt, off, rows, H, K, st));
+         LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, bt.child, nt, off, rows, H, K, st));
     const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
     if ((rc = Gemm(e, e->P, 3 * H, 0, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st))) return rc;
     if ((rc = Gemm(e, e->Q, H, 0, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st))) return rc;
     // read A (4H), P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
     PROF(e, kProfCellFwd, 4.0 * rows * H * (4 + 3 + K + K + 3 + K + 2), st,
-         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, B, e->child, nt, off, rows, H, K, false, st));
+         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, B, bt.child, nt, off, rows, H, K, false, st));
   }
   (void)rc;
   return CAVS_OK;
@@ -377,7 +389,9 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
 extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   CAVS_REQUIRE(e && e->params && e->grads, CAVS_ERR_BAD_ARG, "treelstm_backward: parameters / gradients not bound");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int n = e->n, nt = e->n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots, C = e->cfg.classes;
+  CAVS_REQUIRE(e->active >= 0, CAVS_ERR_BAD_ARG, "treelstm_backward: no batch loaded");
+  const cavs_treelstm::Batch& bt = e->slot[e->active];
+  const int n = bt.n, nt = bt.n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots, C = e->cfg.classes;
   float* g = e->grads;
   if (n == 0) {
     CAVS_CUDA(cudaMemsetAsync(g, 0, e->ParamCount() * sizeof(float), st));
@@ -392,16 +406,16 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   // Loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
   // write loss and d(h) (H).
   PROF(e, kProfLossHead, static_cast<double>(n) * (8.0 * H + 8), st,
-       LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, e->label,
-                      e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(e->loss_rows),
+       LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
+                      e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
                       e->loss_scratch, st));
-  for (int l = e->n_levels - 1; l >= 0; --l) {
-    const int off = e->level_off[l], rows = e->level_off[l + 1] - off;
+  for (int l = bt.n_levels - 1; l >= 0; --l) {
+    const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     // read dOut (H), mailbox (2H), gates ((3+K)H), own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
     const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 3 + K + 1) + elt * 4)
                                      : rows * H * (4.0 * (1 + 2 + 3 + K + 1 + K + K) + elt * (4 + K));
     PROF(e, kProfCellBwd, cell_bytes, st,
-         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, e->dOut, e->gates, e->state, e->child, e->parent, nt, off, rows, H,
+         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, e->dOut, e->gates, e->state, bt.child, bt.parent, nt, off, rows, H,
                        K, l == 0, st));
     if (l == 0) break;
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
@@ -410,10 +424,10 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st))) return rc;
     if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st))) return rc;
     PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
-         LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, e->child, nt, off, rows, H, K, st));
+         LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
   }
   // Deferred gradients over all rows at once.
-  const int off1 = e->n_levels > 1 ? e->level_off[1] : n;   // first internal row
+  const int off1 = bt.n_levels > 1 ? bt.level_off[1] : n;   // first internal row
   const int n_int = n - off1;
   if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dA, 4 * H, false, E, 4 * H, n, true, st))) return rc;
   float* dU = g + e->OffU();
@@ -433,8 +447,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   // dX = dA W^T, then the segmented embedding gradient.
   if ((rc = Gemm(e, e->dX, E, 0, e->dA, 4 * H, false, W, 4 * H, true, n, E, 4 * H, false, st))) return rc;
   CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
-  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * E) + 4.0 * E * e->n_seg, st,
-       LaunchEmbedBwd(g, e->dX, e->order, nullptr, e->chunk_off, e->n_chunks, e->seg_first_chunk, e->seg_tok, e->n_seg,
+  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * E) + 4.0 * E * bt.n_seg, st,
+       LaunchEmbedBwd(g, e->dX, bt.order, nullptr, bt.chunk_off, bt.n_chunks, bt.seg_first_chunk, bt.seg_tok, bt.n_seg,
                       e->emb_scratch, E, st));
   (void)rc;
   return CAVS_OK;
@@ -479,7 +493,7 @@ extern "C" int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, i
 
 extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes) {
   CAVS_REQUIRE(e && dev_ptr && bytes, CAVS_ERR_BAD_ARG, "treelstm_peek: null pointer");
-  const size_t n = e->n, H = e->cfg.hidden;
+  const size_t n = e->active >= 0 ? e->slot[e->active].n : 0, H = e->cfg.hidden;
   switch (what) {
     case 0: *dev_ptr = e->state; *bytes = n * 2 * H * sizeof(float); break;      // h|c per vertex, tensor-id order
     case 1: *dev_ptr = e->loss; *bytes = n * sizeof(float); break;               // per-vertex loss

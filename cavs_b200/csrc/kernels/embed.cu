@@ -48,16 +48,48 @@ EmbedFwd(T* __restrict__ out, const float* __restrict__ table, const int32_t* __
   }
 }
 
-// One CTA per chunk: partial[chunk,:] = sum over the chunk's rows, in order.
+// One CTA per chunk: partial[chunk,:] = sum over the chunk's rows.  Four interleaved running sums
+// per column (rows r, r+1, r+2, r+3 mod 4) combined as ((s0+s1)+(s2+s3)): a fixed order.
+template <int kVec>
 __global__ void __launch_bounds__(kThreads)
 EmbedBwdChunks(float* __restrict__ partial, const float* __restrict__ dX, const int32_t* __restrict__ order,
                const int32_t* __restrict__ chunk_off, int E) {
+  __shared__ int32_t rows_sm[kEmbedChunk];
   const int chunk = blockIdx.x;
-  const int begin = chunk_off[chunk], end = chunk_off[chunk + 1];
-  for (int e = threadIdx.x; e < E; e += kThreads) {
-    float acc = 0.0f;
-    for (int r = begin; r < end; ++r) acc += dX[static_cast<size_t>(order[r]) * E + e];
-    partial[static_cast<size_t>(chunk) * E + e] = acc;
+  const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
+  for (int r = threadIdx.x; r < cnt; r += kThreads) rows_sm[r] = order[begin + r];
+  __syncthreads();
+  for (int e = threadIdx.x * kVec; e < E; e += kThreads * kVec) {
+    float acc[4][kVec];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int v = 0; v < kVec; ++v) acc[u][v] = 0.0f;
+    int r = 0;
+    for (; r + 4 <= cnt; r += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float* src = dX + static_cast<size_t>(rows_sm[r + u]) * E + e;
+        if (kVec == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(src);
+          acc[u][0] += t.x; acc[u][1 % kVec] += t.y; acc[u][2 % kVec] += t.z; acc[u][3 % kVec] += t.w;
+        } else {
+          acc[u][0] += *src;
+        }
+      }
+    }
+    for (int u = 0; r < cnt; ++r, ++u) {
+      const float* src = dX + static_cast<size_t>(rows_sm[r]) * E + e;
+      if (kVec == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(src);
+        acc[u][0] += t.x; acc[u][1 % kVec] += t.y; acc[u][2 % kVec] += t.z; acc[u][3 % kVec] += t.w;
+      } else {
+        acc[u][0] += *src;
+      }
+    }
+    float* dst = partial + static_cast<size_t>(chunk) * E + e;
+#pragma unroll
+    for (int v = 0; v < kVec; ++v) dst[v] = (acc[0][v] + acc[1][v]) + (acc[2][v] + acc[3][v]);
   }
 }
 // One CTA per segment: dtable[tok,:] = sum of its chunks' partials, in chunk order.
@@ -93,7 +125,10 @@ int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const i
   CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && E > 0, CAVS_ERR_BAD_ARG, "embed_bwd: bad shape");
   if (n_chunks == 0 || n_seg == 0) return CAVS_OK;
   CAVS_REQUIRE(dtable && dX && order && chunk_off && seg_first_chunk && seg_tok && scratch, CAVS_ERR_BAD_ARG, "embed_bwd: null pointer");
-  EmbedBwdChunks<<<n_chunks, kThreads, 0, st>>>(scratch, dX, order, chunk_off, E);
+  if (E % 4 == 0 && ((reinterpret_cast<uintptr_t>(dX) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0)
+    EmbedBwdChunks<4><<<n_chunks, kThreads, 0, st>>>(scratch, dX, order, chunk_off, E);
+  else
+    EmbedBwdChunks<1><<<n_chunks, kThreads, 0, st>>>(scratch, dX, order, chunk_off, E);
   CAVS_LAUNCH_CHECK("embed_bwd chunks");
   EmbedBwdSegments<<<n_seg, kThreads, 0, st>>>(dtable, scratch, seg_first_chunk, seg_tok, E);
   CAVS_LAUNCH_CHECK("embed_bwd segments");

@@ -96,13 +96,21 @@ size_t GemmBf16ScratchBytes(int m, int n, int splits) {
 }
 
 int GemmBf16SplitsFor(int m, int n, int k) {
-  // Split K only when the tile grid leaves most SMs idle and K is deep.
-  const long long tiles = static_cast<long long>((m + tc::kBM - 1) / tc::kBM) * ((n + 255) / 256);
+  // The kernel is persistent over (tile, split) work items; pick the smallest split count whose
+  // work-item count fills whole waves of SMs noticeably better, keeping each split >= 32 K blocks.
+  const int bn = n > 128 ? 256 : 128;
+  const long long tiles = static_cast<long long>((m + tc::kBM - 1) / tc::kBM) * ((n + bn - 1) / bn);
   const int nkb = (k + tc::kBK - 1) / tc::kBK;
-  if (tiles * 2 > SmCount() || nkb < 16) return 1;
-  int splits = static_cast<int>(SmCount() / tiles);
-  splits = std::min(splits, nkb / 8);
-  return std::max(1, std::min(splits, 32));
+  const int sms = SmCount();
+  auto fill = [&](long long items) { return static_cast<double>(items) / (((items + sms - 1) / sms) * sms); };
+  int best = 1;
+  double best_fill = fill(tiles);
+  for (int s = 2; s <= 32 && nkb / s >= 32; ++s) {
+    const double f = fill(tiles * s);
+    if (f > best_fill + 0.04) { best = s; best_fill = f; }
+    if (best_fill > 0.95) break;
+  }
+  return best;
 }
 
 int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
@@ -145,7 +153,9 @@ int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
   } else {
     p.c = g.c; p.ldc = g.ldc; p.split_stride = 0; p.out_mode = g.out_mode;
   }
-  dim3 grid((g.n + bn - 1) / bn, (g.m + tc::kBM - 1) / tc::kBM, eff_splits);
+  p.n_splits = eff_splits;
+  const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tc::kBM - 1) / tc::kBM) * eff_splits;
+  dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
   rc = wide ? Dispatch<256>(g.a_major, g.b_major, ma, mb, p, grid, stream)
             : Dispatch<128>(g.a_major, g.b_major, ma, mb, p, grid, stream);
   if (rc) return rc;

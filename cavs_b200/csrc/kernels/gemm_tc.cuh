@@ -7,10 +7,11 @@
 // reference issues these as cublasSgemm calls (cavs/backend/cublas_wrapper.cc:13-28,
 // cavs/backend/op_impl_blas3_cublas.cc:35-70).
 //
-// One CTA computes one BM x BN tile of C (optionally one K-split of it):
+// Persistent CTAs (one per SM) walk BM x BN output tiles (optionally K-splits of them):
 //   warp 0      TMA producer: one elected lane walks the K blocks, filling a ring of stages
 //   warp 1      allocates TMEM, one elected lane issues tcgen05.mma and commits to mbarriers
 //   warps 2..5  epilogue: tcgen05.ld the accumulator (one 32-lane quarter each) and store
+// Two TMEM accumulators alternate so the epilogue of one tile overlaps the next tile's MMAs.
 // Operands may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the
 // latter is what the weight gradient dW = X^T dY needs, so no transpose pass exists.
 // Every mbarrier wait is bounded; on expiry the CTA raises *status and unwinds.
@@ -40,10 +41,9 @@ struct Params {
   long long ldc;      // elements
   long long split_stride;  // elements between K-split partial outputs (0 when splits == 1)
   int m, n, k;
-  int kb_per_split;   // K blocks handled by one CTA along gridDim.z
+  int kb_per_split;   // K blocks per work item
   int out_mode;
-  int a_row_off, b_row_off;  // added to the row coordinate of every A / B tile (views into arenas)
-  int a_k_off, b_k_off;      // added to the K coordinate
+  int n_splits;       // K splits per tile (work items = tiles x splits)
   int* status;        // device word, set non-zero when a bounded wait expires
 };
 
@@ -54,7 +54,7 @@ struct Smem {
   static constexpr int kStage = kATile + kBTile;
   static constexpr int kStages = (kBN == 256) ? 4 : 6;
   static constexpr int kBarOff = kStages * kStage;
-  static constexpr int kBytes = kBarOff + 256 + 1024;  // barriers + slack for 1024-byte alignment
+  static constexpr int kBytes = kBarOff + 256 + 1024;  // barriers (<= 17 x 8 bytes + TMEM slot) + slack for 1024-byte alignment
 };
 
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -138,6 +138,79 @@ __device__ __forceinline__ void TmemLoad32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void MbarArrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Two 32-column accumulator chunks per round trip: both loads are issued before the wait.
+__device__ __forceinline__ void TmemLoad64(uint32_t taddr, uint32_t (&r)[64]) {
+#define CAVS_TMEM_LD32(BASE, ADDR)                                                                                        \
+  asm volatile(                                                                                                           \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                           \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                          \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                          \
+      : "=r"(r[BASE + 0]), "=r"(r[BASE + 1]), "=r"(r[BASE + 2]), "=r"(r[BASE + 3]), "=r"(r[BASE + 4]), "=r"(r[BASE + 5]), \
+        "=r"(r[BASE + 6]), "=r"(r[BASE + 7]), "=r"(r[BASE + 8]), "=r"(r[BASE + 9]), "=r"(r[BASE + 10]),                  \
+        "=r"(r[BASE + 11]), "=r"(r[BASE + 12]), "=r"(r[BASE + 13]), "=r"(r[BASE + 14]), "=r"(r[BASE + 15]),              \
+        "=r"(r[BASE + 16]), "=r"(r[BASE + 17]), "=r"(r[BASE + 18]), "=r"(r[BASE + 19]), "=r"(r[BASE + 20]),              \
+        "=r"(r[BASE + 21]), "=r"(r[BASE + 22]), "=r"(r[BASE + 23]), "=r"(r[BASE + 24]), "=r"(r[BASE + 25]),              \
+        "=r"(r[BASE + 26]), "=r"(r[BASE + 27]), "=r"(r[BASE + 28]), "=r"(r[BASE + 29]), "=r"(r[BASE + 30]),              \
+        "=r"(r[BASE + 31])                                                                                                \
+      : "r"(ADDR))
+  CAVS_TMEM_LD32(0, taddr);
+  CAVS_TMEM_LD32(32, taddr + 32);
+#undef CAVS_TMEM_LD32
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Stores 32 consecutive accumulator columns of one row (registers r[base..base+32)).
+template <int kBase>
+__device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[64], int row, int col0, long long zoff) {
+  if (row >= p.m || col0 >= p.n) return;
+  if (p.out_mode == kStoreBf16) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
+    if (col0 + 32 <= p.n && (p.ldc & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 v;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[kBase + j]), __uint_as_float(r[kBase + j + 1]));
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[kBase + j + 2]), __uint_as_float(r[kBase + j + 3]));
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[kBase + j + 4]), __uint_as_float(r[kBase + j + 5]));
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[kBase + j + 6]), __uint_as_float(r[kBase + j + 7]));
+        v.x = *reinterpret_cast<uint32_t*>(&t0); v.y = *reinterpret_cast<uint32_t*>(&t1);
+        v.z = *reinterpret_cast<uint32_t*>(&t2); v.w = *reinterpret_cast<uint32_t*>(&t3);
+        *reinterpret_cast<uint4*>(dst + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) dst[j] = __float2bfloat16_rn(__uint_as_float(r[kBase + j]));
+    }
+  } else {
+    float* dst = static_cast<float*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
+    const bool acc = p.out_mode == kAccumF32;
+    if (col0 + 32 <= p.n && (p.ldc & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 v = make_float4(__uint_as_float(r[kBase + j]), __uint_as_float(r[kBase + j + 1]),
+                               __uint_as_float(r[kBase + j + 2]), __uint_as_float(r[kBase + j + 3]));
+        if (acc) {
+          const float4 o = *reinterpret_cast<const float4*>(dst + j);
+          v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+        }
+        *reinterpret_cast<float4*>(dst + j) = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.n) dst[j] = (acc ? dst[j] : 0.0f) + __uint_as_float(r[kBase + j]);
+    }
+  }
+}
+
+// Persistent kernel: each CTA walks work items w = blockIdx.x, blockIdx.x + gridDim.x, ...;
+// work item -> (tile, K-split) with the N tile index fastest, so the CTAs of one wave share A
+// row blocks through L2.  Two TMEM accumulators alternate between tiles: while the epilogue
+// warps drain one, the MMA warp already fills the other, and the TMA ring never drains.
 template <int kBN, int kAMajor, int kBMajor>
 __global__ void __launch_bounds__(kThreads, 1)
 GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -146,29 +219,32 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // 128-byte swizzle needs 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBarOff);
-  uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + S::kStages;
-  uint64_t* accum_bar = bars + 2 * S::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::kStages + 1);
+  uint64_t* full_bar = bars;                          // [kStages] TMA -> MMA
+  uint64_t* empty_bar = bars + S::kStages;            // [kStages] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * S::kStages;         // [2] MMA -> epilogue
+  uint64_t* acc_empty = bars + 2 * S::kStages + 2;    // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S::kStages + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM;
-  const int n0 = blockIdx.x * kBN;
+  const int n_tiles_n = (p.n + kBN - 1) / kBN;
+  const int n_tiles_m = (p.m + kBM - 1) / kBM;
   const int nkb_total = (p.k + kBK - 1) / kBK;
-  const int kb_begin = blockIdx.z * p.kb_per_split;
-  const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
+  const int n_work = n_tiles_m * n_tiles_n * p.n_splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
       MbarInit(SmemAddr(full_bar + s), 1);
       MbarInit(SmemAddr(empty_bar + s), 1);
     }
-    MbarInit(SmemAddr(accum_bar), 1);
+    for (int a = 0; a < 2; ++a) {
+      MbarInit(SmemAddr(acc_full + a), 1);
+      MbarInit(SmemAddr(acc_empty + a), 4);   // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)), "r"(kBN));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(tmem_slot)), "r"(2 * kBN));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -179,27 +255,34 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (ElectOne()) {
-      for (int i = 0; i < kb_count && ok; ++i) {
-        const int s = i % S::kStages;
-        const uint32_t phase = (i / S::kStages) & 1;
-        ok = MbarWait(SmemAddr(empty_bar + s), phase ^ 1);
-        if (!ok) break;
-        const uint32_t bar = SmemAddr(full_bar + s);
-        MbarExpectTx(bar, S::kStage);
-        const uint32_t a_dst = SmemAddr(smem + s * S::kStage);
-        const uint32_t b_dst = a_dst + S::kATile;
-        const int k0 = (kb_begin + i) * kBK;
-        if (kAMajor == kMajorK) {
-          TmaLoad2d(a_dst, &map_a, bar, k0 + p.a_k_off, m0 + p.a_row_off);                       // box {64 k, 128 rows}
-        } else {
+      uint32_t it = 0;   // ring position, continuous across work items
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const int z = w % p.n_splits, tile = w / p.n_splits;
+        const int m0 = (tile / n_tiles_n) * kBM, n0 = (tile % n_tiles_n) * kBN;
+        const int kb_begin = z * p.kb_per_split;
+        const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
+        for (int i = 0; i < kb_count; ++i, ++it) {
+          const int s = it % S::kStages;
+          const uint32_t phase = (it / S::kStages) & 1;
+          ok = MbarWait(SmemAddr(empty_bar + s), phase ^ 1);
+          if (!ok) break;
+          const uint32_t bar = SmemAddr(full_bar + s);
+          MbarExpectTx(bar, S::kStage);
+          const uint32_t a_dst = SmemAddr(smem + s * S::kStage);
+          const uint32_t b_dst = a_dst + S::kATile;
+          const int k0 = (kb_begin + i) * kBK;
+          if (kAMajor == kMajorK) {
+            TmaLoad2d(a_dst, &map_a, bar, k0, m0);                                    // box {64 k, 128 rows}
+          } else {
 #pragma unroll
-          for (int j = 0; j < kBM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j + p.a_row_off, k0 + p.a_k_off);  // box {64 mn, 64 k}
-        }
-        if (kBMajor == kMajorK) {
-          TmaLoad2d(b_dst, &map_b, bar, k0 + p.b_k_off, n0 + p.b_row_off);                       // box {64 k, kBN rows}
-        } else {
+            for (int j = 0; j < kBM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j, k0);  // box {64 mn, 64 k}
+          }
+          if (kBMajor == kMajorK) {
+            TmaLoad2d(b_dst, &map_b, bar, k0, n0);                                    // box {64 k, kBN rows}
+          } else {
 #pragma unroll
-          for (int j = 0; j < kBN / 64; ++j) TmaLoad2d(b_dst + j * 8192, &map_b, bar, n0 + 64 * j + p.b_row_off, k0 + p.b_k_off);
+            for (int j = 0; j < kBN / 64; ++j) TmaLoad2d(b_dst + j * 8192, &map_b, bar, n0 + 64 * j, k0);
+          }
         }
       }
     }
@@ -209,82 +292,67 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t idesc = InstrDesc(kAMajor, kBMajor, kBN, kBM);
       constexpr uint32_t a_step = (kAMajor == kMajorK) ? (kUmmaK * 2 >> 4) : (kUmmaK * 128 >> 4);
       constexpr uint32_t b_step = (kBMajor == kMajorK) ? (kUmmaK * 2 >> 4) : (kUmmaK * 128 >> 4);
-      for (int i = 0; i < kb_count && ok; ++i) {
-        const int s = i % S::kStages;
-        const uint32_t phase = (i / S::kStages) & 1;
-        ok = MbarWait(SmemAddr(full_bar + s), phase);
+      uint32_t it = 0, t_local = 0;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++t_local) {
+        const int z = w % p.n_splits;
+        const int kb_begin = z * p.kb_per_split;
+        const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
+        const uint32_t acc = t_local & 1, acc_phase = (t_local >> 1) & 1;
+        ok = MbarWait(SmemAddr(acc_empty + acc), acc_phase ^ 1);   // epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = SmemAddr(smem + s * S::kStage);
-        const uint64_t a_desc = SmemDesc(a_addr, kAMajor);
-        const uint64_t b_desc = SmemDesc(a_addr + S::kATile, kBMajor);
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int i = 0; i < kb_count; ++i, ++it) {
+          const int s = it % S::kStages;
+          const uint32_t phase = (it / S::kStages) & 1;
+          ok = MbarWait(SmemAddr(full_bar + s), phase);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = SmemAddr(smem + s * S::kStage);
+          const uint64_t a_desc = SmemDesc(a_addr, kAMajor);
+          const uint64_t b_desc = SmemDesc(a_addr + S::kATile, kBMajor);
 #pragma unroll
-        for (int kk = 0; kk < kBK / kUmmaK; ++kk)
-          UmmaBf16(tmem_base, a_desc + kk * a_step, b_desc + kk * b_step, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-        UmmaCommit(SmemAddr(empty_bar + s));   // frees the stage once these MMAs have read it
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+            UmmaBf16(d_tmem, a_desc + kk * a_step, b_desc + kk * b_step, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          UmmaCommit(SmemAddr(empty_bar + s));   // frees the stage once these MMAs have read it
+        }
+        if (ok) UmmaCommit(SmemAddr(acc_full + acc));   // accumulator complete
       }
-      UmmaCommit(SmemAddr(accum_bar));         // accumulator complete
     }
     __syncwarp();
   } else {
     // Epilogue warps 2..5 own TMEM lane quarters (warp % 4).
-    ok = MbarWait(SmemAddr(accum_bar), 0);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok && kb_count > 0) {
-      const int quarter = warp & 3;
+    const int quarter = warp & 3;
+    uint32_t t_local = 0;
+    for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++t_local) {
+      const int z = w % p.n_splits, tile = w / p.n_splits;
+      const int m0 = (tile / n_tiles_n) * kBM, n0 = (tile % n_tiles_n) * kBN;
+      const uint32_t acc = t_local & 1, acc_phase = (t_local >> 1) & 1;
+      ok = MbarWait(SmemAddr(acc_full + acc), acc_phase);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = m0 + quarter * 32 + lane;
-      const long long zoff = static_cast<long long>(blockIdx.z) * p.split_stride;
+      const long long zoff = static_cast<long long>(z) * p.split_stride;
+      const uint32_t t_addr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBN; c0 += 32) {
+      for (int c0 = 0; c0 < kBN; c0 += 64) {
         if (n0 + c0 >= p.n) break;   // warp-uniform
-        uint32_t r[32];
-        TmemLoad32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, r);
-        if (row < p.m) {
-          const int col0 = n0 + c0;
-          if (p.out_mode == kStoreBf16) {
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
-            if (col0 + 32 <= p.n && (p.ldc & 7) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                v.x = *reinterpret_cast<uint32_t*>(&t0); v.y = *reinterpret_cast<uint32_t*>(&t1);
-                v.z = *reinterpret_cast<uint32_t*>(&t2); v.w = *reinterpret_cast<uint32_t*>(&t3);
-                *reinterpret_cast<uint4*>(dst + j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-            }
-          } else {
-            float* dst = static_cast<float*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
-            const bool acc = p.out_mode == kAccumF32;
-            if (col0 + 32 <= p.n && (p.ldc & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                       __uint_as_float(r[j + 3]));
-                if (acc) {
-                  const float4 o = *reinterpret_cast<const float4*>(dst + j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4*>(dst + j) = v;
-              }
-            } else {
-              for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = (acc ? dst[j] : 0.0f) + __uint_as_float(r[j]);
-            }
-          }
-        }
+        uint32_t r[64];
+        TmemLoad64(t_addr + c0, r);
+        StoreChunk<0>(p, r, row, n0 + c0, zoff);
+        StoreChunk<32>(p, r, row, n0 + c0 + 32, zoff);
       }
+      // All of this warp's TMEM reads are complete (wait::ld above): hand the accumulator back.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) MbarArrive(SmemAddr(acc_empty + acc));
     }
   }
   if (!ok && p.status != nullptr) atomicExch(p.status, 1);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBN));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kBN));
   }
 }
 

@@ -23,6 +23,10 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kRowsPerBlock = 32;     // rows per CTA iteration (4 per warp)
 constexpr int kMaxC = 8;
+constexpr int kCtasPerSm = 4;
+// Floats per per-CTA partial record ([C*H] dWc, [C] dbc, [1] loss sum), padded to 16 bytes so the
+// 128-bit stores of every CTA's record stay aligned.
+__host__ __device__ constexpr int PartialStride(int C, int H) { return (C * H + C + 1 + 3) & ~3; }
 constexpr int kMaxColsPerThread = 8;  // H <= kThreads * kMaxColsPerThread
 
 __device__ __forceinline__ float WarpSum(float v) {
@@ -31,25 +35,27 @@ __device__ __forceinline__ float WarpSum(float v) {
   return v;
 }
 
-template <int C>
+// kVec = 4 when H is a multiple of 4 (128-bit accesses), else 1.
+template <int C, int kVec>
 __global__ void __launch_bounds__(kThreads)
 LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ partial,
                const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
                const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows) {
   extern __shared__ float sm[];
-  float* sW = sm;                        // [C][H]
-  float* sdz = sm + C * H;               // [kRowsPerBlock][C]
+  float* sW = sm;                          // [C][H]
+  float* sdz = sm + C * H;                 // [kRowsPerBlock][C]
   float* sloss = sdz + kRowsPerBlock * C;  // [kWarps]
   for (int i = threadIdx.x; i < C * H; i += kThreads) sW[i] = Wc[i];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float accW[kMaxColsPerThread][C];
+  float accW[kMaxColsPerThread][C];        // columns (threadIdx.x + q * kThreads) * kVec + e, q-major
 #pragma unroll
   for (int q = 0; q < kMaxColsPerThread; ++q)
 #pragma unroll
     for (int c = 0; c < C; ++c) accW[q][c] = 0.0f;
   float accb = 0.0f;        // thread c < C owns class c of the bias gradient
-  float loss_acc = 0.0f;   // per warp (lane 0)
+  float loss_acc = 0.0f;    // per warp (lane 0)
+  constexpr int kQ = kMaxColsPerThread / kVec;   // vector slots per thread
 
   const int n_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
   for (int blk = blockIdx.x; blk < n_blocks; blk += gridDim.x) {
@@ -63,10 +69,21 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
         float z[C];
 #pragma unroll
         for (int c = 0; c < C; ++c) z[c] = 0.0f;
-        for (int j = lane; j < H; j += 32) {
-          const float hv = hr[j];
+        if (kVec == 4) {
+          for (int j = lane * 4; j < H; j += 128) {
+            const float4 hv = *reinterpret_cast<const float4*>(hr + j);
 #pragma unroll
-          for (int c = 0; c < C; ++c) z[c] = fmaf(hv, sW[c * H + j], z[c]);
+            for (int c = 0; c < C; ++c) {
+              const float4 w = *reinterpret_cast<const float4*>(sW + c * H + j);
+              z[c] = fmaf(hv.x, w.x, fmaf(hv.y, w.y, fmaf(hv.z, w.z, fmaf(hv.w, w.w, z[c]))));
+            }
+          }
+        } else {
+          for (int j = lane; j < H; j += 32) {
+            const float hv = hr[j];
+#pragma unroll
+            for (int c = 0; c < C; ++c) z[c] = fmaf(hv, sW[c * H + j], z[c]);
+          }
         }
         float mx = -INFINITY;
 #pragma unroll
@@ -84,11 +101,23 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
         }
         if (lane == 0) { loss[t] = lrow; loss_acc += lrow; }
         float* dr = dOut + static_cast<long long>(t) * H;
-        for (int j = lane; j < H; j += 32) {
-          float a = 0.0f;
+        if (kVec == 4) {
+          for (int j = lane * 4; j < H; j += 128) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int c = 0; c < C; ++c) a = fmaf(dz[c], sW[c * H + j], a);
-          dr[j] = a;
+            for (int c = 0; c < C; ++c) {
+              const float4 w = *reinterpret_cast<const float4*>(sW + c * H + j);
+              a.x = fmaf(dz[c], w.x, a.x); a.y = fmaf(dz[c], w.y, a.y); a.z = fmaf(dz[c], w.z, a.z); a.w = fmaf(dz[c], w.w, a.w);
+            }
+            *reinterpret_cast<float4*>(dr + j) = a;
+          }
+        } else {
+          for (int j = lane; j < H; j += 32) {
+            float a = 0.0f;
+#pragma unroll
+            for (int c = 0; c < C; ++c) a = fmaf(dz[c], sW[c * H + j], a);
+            dr[j] = a;
+          }
         }
       } else {
 #pragma unroll
@@ -100,17 +129,35 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
       }
     }
     __syncthreads();
-    // Phase 2: thread owns columns j = threadIdx.x + q * kThreads; rows in ascending order.
+    // Phase 2: dWc += dz^T h with each thread owning fixed columns; rows in ascending order.
     const int r_end = min(kRowsPerBlock, rows - r0);
     for (int rr = 0; rr < r_end; ++rr) {
       const float* hr = h + static_cast<long long>(r0 + rr) * h_pitch;
+      if (kVec == 4) {
 #pragma unroll
-      for (int q = 0; q < kMaxColsPerThread; ++q) {
-        const int j = threadIdx.x + q * kThreads;
-        if (j < H) {
-          const float hv = hr[j];
+        for (int q = 0; q < kQ; ++q) {
+          const int j = (threadIdx.x + q * kThreads) * 4;
+          if (j < H) {
+            const float4 hv = *reinterpret_cast<const float4*>(hr + j);
 #pragma unroll
-          for (int c = 0; c < C; ++c) accW[q][c] = fmaf(sdz[rr * C + c], hv, accW[q][c]);
+            for (int c = 0; c < C; ++c) {
+              const float d = sdz[rr * C + c];
+              accW[q * 4 + 0][c] = fmaf(d, hv.x, accW[q * 4 + 0][c]);
+              accW[q * 4 + 1][c] = fmaf(d, hv.y, accW[q * 4 + 1][c]);
+              accW[q * 4 + 2][c] = fmaf(d, hv.z, accW[q * 4 + 2][c]);
+              accW[q * 4 + 3][c] = fmaf(d, hv.w, accW[q * 4 + 3][c]);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < kMaxColsPerThread; ++q) {
+          const int j = threadIdx.x + q * kThreads;
+          if (j < H) {
+            const float hv = hr[j];
+#pragma unroll
+            for (int c = 0; c < C; ++c) accW[q][c] = fmaf(sdz[rr * C + c], hv, accW[q][c]);
+          }
         }
       }
       if (threadIdx.x < C) accb += sdz[rr * C + threadIdx.x];
@@ -118,13 +165,26 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
     __syncthreads();
   }
   // Per-CTA partial: [C*H] dWc, [C] dbc, [1] loss sum.
-  float* mine = partial + static_cast<size_t>(blockIdx.x) * (C * H + C + 1);
+  float* mine = partial + static_cast<size_t>(blockIdx.x) * PartialStride(C, H);
+  if (kVec == 4) {
 #pragma unroll
-  for (int q = 0; q < kMaxColsPerThread; ++q) {
-    const int j = threadIdx.x + q * kThreads;
-    if (j < H) {
+    for (int q = 0; q < kQ; ++q) {
+      const int j = (threadIdx.x + q * kThreads) * 4;
+      if (j < H) {
 #pragma unroll
-      for (int c = 0; c < C; ++c) mine[c * H + j] = accW[q][c];
+        for (int c = 0; c < C; ++c)
+          *reinterpret_cast<float4*>(mine + c * H + j) =
+              make_float4(accW[q * 4 + 0][c], accW[q * 4 + 1][c], accW[q * 4 + 2][c], accW[q * 4 + 3][c]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < kMaxColsPerThread; ++q) {
+      const int j = threadIdx.x + q * kThreads;
+      if (j < H) {
+#pragma unroll
+        for (int c = 0; c < C; ++c) mine[c * H + j] = accW[q][c];
+      }
     }
   }
   if (threadIdx.x < C) mine[C * H + threadIdx.x] = accb;
@@ -139,11 +199,11 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
 
 __global__ void __launch_bounds__(kThreads)
 LossHeadReduce(float* __restrict__ dWc, float* __restrict__ dbc, float* __restrict__ loss_sum,
-               const float* __restrict__ partial, int n_parts, int CH, int C) {
+               const float* __restrict__ partial, int n_parts, int CH, int C, int stride) {
   const int width = CH + C + 1;
   for (int i = blockIdx.x * kThreads + threadIdx.x; i < width; i += gridDim.x * kThreads) {
     float s = 0.0f;
-    for (int p = 0; p < n_parts; ++p) s += partial[static_cast<size_t>(p) * width + i];
+    for (int p = 0; p < n_parts; ++p) s += partial[static_cast<size_t>(p) * stride + i];
     if (i < CH) dWc[i] = s;
     else if (i < CH + C) dbc[i - CH] = s;
     else if (loss_sum) *loss_sum = s;
@@ -152,13 +212,13 @@ LossHeadReduce(float* __restrict__ dWc, float* __restrict__ dbc, float* __restri
 
 int LossGrid(int rows) {
   const int n_blocks = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
-  return std::max(1, std::min(n_blocks, SmCount() * 2));
+  return std::max(1, std::min(n_blocks, SmCount() * kCtasPerSm));
 }
 
 }  // namespace
 
 size_t LossHeadScratchBytes(int H, int C) {
-  return static_cast<size_t>(SmCount()) * 2 * (static_cast<size_t>(C) * H + C + 1) * sizeof(float);
+  return static_cast<size_t>(SmCount()) * kCtasPerSm * PartialStride(C, H) * sizeof(float);
 }
 
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
@@ -170,12 +230,19 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   CAVS_REQUIRE(loss && dOut && dWc && dbc && h && label && Wc && bc && scratch, CAVS_ERR_BAD_ARG, "loss_head: null pointer");
   const int grid = rows > 0 ? LossGrid(rows) : 1;
   const size_t smem = (static_cast<size_t>(C) * H + kRowsPerBlock * C + kWarps) * sizeof(float);
+  const bool vec4 = H % 4 == 0 && h_pitch % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dOut) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0;
   CAVS_REQUIRE(smem <= 200 * 1024, CAVS_ERR_UNSUPPORTED, "loss_head: classifier does not fit in shared memory");
 #define LOSS_CASE(CC)                                                                                              \
   case CC: {                                                                                                       \
-    if (smem > 48 * 1024)                                                                                          \
-      CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    LossHeadKernel<CC><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
+    if (vec4) {                                                                                                    \
+      if (smem > 48 * 1024)                                                                                        \
+        CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      LossHeadKernel<CC, 4><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
+    } else {                                                                                                       \
+      if (smem > 48 * 1024)                                                                                        \
+        CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      LossHeadKernel<CC, 1><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
+    }                                                                                                              \
     break;                                                                                                         \
   }
   switch (C) {
@@ -185,7 +252,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
 #undef LOSS_CASE
   CAVS_LAUNCH_CHECK("loss_head");
   const int width = C * H + C + 1;
-  LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C);
+  LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C, PartialStride(C, H));
   CAVS_LAUNCH_CHECK("loss_head reduce");
   return CAVS_OK;
 }
