@@ -77,6 +77,51 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+HOST_LIB = PKG / "libcavs_host.so"
+HOST_SRC = PKG / "cavs"
+CPP_TESTS = ROOT / "tests" / "cpp"
+CXX = os.environ.get("CAVS_CXX", "g++")
+CUDA_HOME = Path(NVCC).resolve().parent.parent
+
+
+def build_host(force: bool = False) -> Path:
+    """libcavs_host.so: the C++ mirror of the reference's operator interface (cavs/backend, cavs/midend)
+    on top of the C ABI.  Plain g++; links libcavs_b200.so and the CUDA runtime."""
+    srcs = sorted(HOST_SRC.rglob("*.cc"))
+    hdrs = list(HOST_SRC.rglob("*.h")) + list((ROOT / "include").glob("*.h"))
+    newest = max(p.stat().st_mtime for p in srcs + hdrs + [LIB])
+    if force or not HOST_LIB.exists() or HOST_LIB.stat().st_mtime < newest:
+        cmd = [CXX, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", f"-I{ROOT / 'include'}", f"-I{PKG}", f"-I{CUDA_HOME / 'include'}",
+               *map(str, srcs), "-o", str(HOST_LIB), f"-L{PKG}", "-lcavs_b200", f"-L{CUDA_HOME / 'lib64'}", "-lcudart",
+               "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{CUDA_HOME / 'lib64'}"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"host library failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return HOST_LIB
+
+
+def build_cpp_tests(force: bool = False) -> list[Path]:
+    """tests/cpp/*.cc -> tests/cpp/bin/<name>; they link the host library and the test oracle."""
+    out_dir = CPP_TESTS / "bin"
+    out_dir.mkdir(exist_ok=True)
+    oracle_dir = ROOT / "oracle"
+    built = []
+    for src in sorted(CPP_TESTS.glob("*.cc")):
+        exe = out_dir / src.stem
+        built.append(exe)
+        deps = [src, HOST_LIB, oracle_dir / "libcavs_oracle.so"]
+        if not force and exe.exists() and all(exe.stat().st_mtime >= d.stat().st_mtime for d in deps if d.exists()):
+            continue
+        cmd = [CXX, "-std=c++17", "-O1", "-Wall", f"-I{ROOT / 'include'}", f"-I{PKG}", f"-I{CUDA_HOME / 'include'}", str(src), "-o", str(exe),
+               f"-L{PKG}", "-lcavs_host", "-lcavs_b200", f"-L{oracle_dir}", "-lcavs_oracle", f"-L{CUDA_HOME / 'lib64'}", "-lcudart",
+               f"-Wl,-rpath,{PKG}", f"-Wl,-rpath,{oracle_dir}", f"-Wl,-rpath,{CUDA_HOME / 'lib64'}"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"C++ test failed to build: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    return built
+
+
 if __name__ == "__main__":
     p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(p)
+    print(build_host(force="--force" in sys.argv))

@@ -39,12 +39,16 @@ struct cavs_treelstm {
   int32_t* h_idx = nullptr;
   size_t idx_ints = 0;
   uint8_t *X = nullptr, *S = nullptr, *HK = nullptr, *dA = nullptr, *ZF = nullptr;   // GEMM operands (fp32 or bf16)
-  float *A = nullptr, *P = nullptr, *Q = nullptr, *gates = nullptr, *state = nullptr, *mailbox = nullptr;
+  uint8_t *A = nullptr, *P = nullptr, *Q = nullptr;   // gate pre-activations: fp32, or bf16 in bf16 mode
+  float *gates = nullptr, *state = nullptr, *mailbox = nullptr;
   float *dOut = nullptr, *ds = nullptr, *dq = nullptr, *dX = nullptr, *loss = nullptr, *dB_tmp = nullptr;
   float* tail = nullptr;        // [0] loss sum, [1] status word (int)
   float *loss_scratch = nullptr, *col_scratch = nullptr, *emb_scratch = nullptr, *splitk_scratch = nullptr;
   size_t splitk_bytes = 0;
   uint8_t *W_bf = nullptr, *U_bf = nullptr;
+  // TMA maps of the per-level GEMM operands, encoded once over whole arenas (bf16 mode).
+  TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
+  TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
   // ---- batches: two slots so the tables of the next batch can be packed and uploaded while the
   // current one executes; forward() promotes the staged slot ----
@@ -156,9 +160,9 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->HK = w.Take<uint8_t>(N * K * H * elt);
   e->dA = w.Take<uint8_t>(N * 4 * H * elt);
   e->ZF = w.Take<uint8_t>(N * K * H * elt);
-  e->A = w.Take<float>(N * 4 * H);
-  e->P = w.Take<float>(L * 3 * H);
-  e->Q = w.Take<float>(L * K * H);
+  e->A = w.Take<uint8_t>(N * 4 * H * elt);
+  e->P = w.Take<uint8_t>(L * 3 * H * elt);
+  e->Q = w.Take<uint8_t>(L * K * H * elt);
   e->gates = w.Take<float>(N * (3 + K) * H);
   e->state = w.Take<float>(N * 2 * H);
   e->mailbox = w.Take<float>(N * 2 * H);
@@ -167,7 +171,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->dq = w.Take<float>(L * K * H);
   e->dX = w.Take<float>(N * E);
   e->loss = w.Take<float>(N);
-  e->dB_tmp = w.Take<float>(4 * H);
+  e->dB_tmp = w.Take<float>(CellBwdFusesBias(c.hidden) ? static_cast<size_t>(CellBwdMaxGrid()) * 4 * H : 4 * H);
   e->tail = w.Take<float>(4);
   e->loss_scratch = w.Take<float>(LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
   e->col_scratch = w.Take<float>(ColumnSumScratchBytes(4 * c.hidden) / sizeof(float));
@@ -181,12 +185,24 @@ size_t Carve(cavs_treelstm* e, void* base) {
 
 // One GEMM of the step in either precision.  `a_t` / `b_t`: operand is used transposed
 // relative to its row-major storage (a_t: A stored [k,m]; b_t: B stored [n,k]).
-int Gemm(cavs_treelstm* e, float* c, long long ldc, int accumulate, const void* a, long long lda, bool a_t, const void* b,
-         long long ldb, bool b_t, int m, int n, int k, bool split_ok, cudaStream_t st) {
+// `accumulate`: 0 store, 1 add into C, 2 store C as bf16 (bf16 mode only; the fp32 path always writes fp32).
+int Gemm(cavs_treelstm* e, void* c, long long ldc, int accumulate, const void* a, long long lda, bool a_t, const void* b,
+         long long ldb, bool b_t, int m, int n, int k, bool split_ok, cudaStream_t st, const TcOperandMap* amap = nullptr,
+         int a_row_off = 0, const TcOperandMap* bmap = nullptr) {
   if (m == 0 || n == 0 || k == 0) return CAVS_OK;
+  if (e->bf16 && amap && bmap) {
+    // Per-level GEMM through pre-encoded arena maps: `a` is not used, the level is a row offset.
+    GemmBf16MappedArgs g;
+    g.c = c; g.ldc = ldc; g.out_mode = accumulate;
+    g.a = amap; g.a_row_off = a_row_off; g.b = bmap;
+    g.m = m; g.n = n; g.k = k;
+    g.status = e->Status();
+    PROF(e, kProfGemm, 2.0 * m * n * k, st, GemmBf16Mapped(g, st));
+    return CAVS_OK;
+  }
   if (e->bf16) {
     GemmBf16Args g;
-    g.c = c; g.ldc = ldc; g.out_mode = accumulate ? 1 : 0;
+    g.c = c; g.ldc = ldc; g.out_mode = accumulate;
     g.a = a; g.lda = lda; g.a_major = a_t ? 1 : 0;   // stored [k,m] = MN-major
     g.b = b; g.ldb = ldb; g.b_major = b_t ? 0 : 1;   // stored [n,k] = K-major, [k,n] = MN-major
     g.m = m; g.n = n; g.k = k;
@@ -199,7 +215,7 @@ int Gemm(cavs_treelstm* e, float* c, long long ldc, int accumulate, const void* 
     return CAVS_OK;
   }
   GemmF32Args g;
-  g.c = c; g.ldc = ldc; g.accumulate = accumulate;
+  g.c = static_cast<float*>(c); g.ldc = ldc; g.accumulate = accumulate == 1;
   g.a = static_cast<const float*>(a); g.a_rs = a_t ? 1 : lda; g.a_cs = a_t ? lda : 1;
   g.b = static_cast<const float*>(b); g.b_rs = b_t ? 1 : ldb; g.b_cs = b_t ? ldb : 1;
   g.m = m; g.n = n; g.k = k;
@@ -236,6 +252,19 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     return Fail(CAVS_ERR_CAPACITY, "treelstm_create: workspace needs " + std::to_string(need) + " bytes");
   }
   e->idx_ints = IdxInts(*cfg);
+  if (e->bf16) {
+    const long long N = cfg->max_vertices, H = cfg->hidden, K = cfg->n_slots;
+    const uint8_t* Uf = e->U_bf + static_cast<size_t>(3) * H * H * 2;
+    int rc = EncodeTcOperand(&e->map_S, e->S, N, H, H, 0, 128);
+    if (!rc) rc = EncodeTcOperand(&e->map_HK, e->HK, N * K, H, H, 0, 128);
+    if (!rc) rc = EncodeTcOperand(&e->map_dA3, e->dA, N, 3 * H, 4 * H, 0, 128);
+    if (!rc) rc = EncodeTcOperand(&e->map_ZF, e->ZF, N * K, H, H, 0, 128);
+    if (!rc) rc = EncodeTcOperand(&e->map_Uiou_mn, e->U_bf, 3 * H, H, 3 * H, 1, 0);                        // [k=H, n=3H]
+    if (!rc) rc = EncodeTcOperand(&e->map_Uf_mn, Uf, H, H, H, 1, 0);                                       // [k=H, n=H]
+    if (!rc) rc = EncodeTcOperand(&e->map_Uiou_k, e->U_bf, H, 3 * H, 3 * H, 0, GemmBf16TileN(static_cast<int>(H)));  // [n=H, k=3H]
+    if (!rc) rc = EncodeTcOperand(&e->map_Uf_k, Uf, H, H, H, 0, GemmBf16TileN(static_cast<int>(H)));       // [n=H, k=H]
+    if (rc) { delete e; return rc; }
+  }
   cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), 2 * e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
   if (err != cudaSuccess) {
     delete e;
@@ -362,13 +391,14 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   const double elt = static_cast<double>(e->elt);
   PROF(e, kProfEmbedFwd, static_cast<double>(n) * (4 + 4.0 * E + elt * E), st,
        LaunchEmbedFwd(e->X, e->bf16, Emb, bt.tok, n, E, e->cfg.vocab, st));
-  if ((rc = Gemm(e, e->A, 4 * H, 0, e->X, E, false, W, 4 * H, false, n, 4 * H, E, false, st))) return rc;
+  const int pre = e->bf16 ? 2 : 0;   // pre-activations are stored in the GEMM operand precision
+  if ((rc = Gemm(e, e->A, 4 * H, pre, e->X, E, false, W, 4 * H, false, n, 4 * H, E, false, st))) return rc;
   for (int l = 0; l < bt.n_levels; ++l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     if (l == 0) {
-      // leaf rows: read A (4H), write gates ((3+K)H) and h|c (2H)
-      PROF(e, kProfCellFwd, 4.0 * rows * H * (4 + 3 + K + 2), st,
-           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, B, bt.child, nt, off, rows, H, K, true, st));
+      // leaf rows: read A's i,o,u blocks (3H), write gates i,o,u (3H) and h|c (2H)
+      PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * 3 + 4.0 * (3 + 2)), st,
+           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, nt, off, rows, H, K, true, st));
       continue;
     }
     // read K child h rows (fp32) + K indices, write S and HK
@@ -376,11 +406,11 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
          LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, bt.child, nt, off, rows, H, K, st));
     const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
-    if ((rc = Gemm(e, e->P, 3 * H, 0, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st))) return rc;
-    if ((rc = Gemm(e, e->Q, H, 0, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st))) return rc;
+    if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn))) return rc;
+    if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn))) return rc;
     // read A (4H), P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
-    PROF(e, kProfCellFwd, 4.0 * rows * H * (4 + 3 + K + K + 3 + K + 2), st,
-         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, B, bt.child, nt, off, rows, H, K, false, st));
+    PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (4 + 3 + K) + 4.0 * (K + 3 + K + 2)), st,
+         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, nt, off, rows, H, K, false, st));
   }
   (void)rc;
   return CAVS_OK;
@@ -409,20 +439,23 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
        LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
                       e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
                       e->loss_scratch, st));
+  const bool fuse_bias = CellBwdFusesBias(H);
+  const size_t dB_rows = static_cast<size_t>(CellBwdMaxGrid());
+  if (fuse_bias) CAVS_CUDA(cudaMemsetAsync(e->dB_tmp, 0, dB_rows * 4 * H * sizeof(float), st));
   for (int l = bt.n_levels - 1; l >= 0; --l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     // read dOut (H), mailbox (2H), gates ((3+K)H), own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
     const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 3 + K + 1) + elt * 4)
                                      : rows * H * (4.0 * (1 + 2 + 3 + K + 1 + K + K) + elt * (4 + K));
     PROF(e, kProfCellBwd, cell_bytes, st,
-         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, e->dOut, e->gates, e->state, bt.child, bt.parent, nt, off, rows, H,
+         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->dOut, e->gates, e->state, bt.child, bt.parent, nt, off, rows, H,
                        K, l == 0, st));
     if (l == 0) break;
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
-    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st))) return rc;
-    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st))) return rc;
+    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k))) return rc;
+    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k))) return rc;
     PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
          LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
   }
@@ -442,8 +475,13 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     CAVS_CUDA(cudaMemsetAsync(dU, 0, static_cast<size_t>(4) * H * H * sizeof(float), st));
   }
   // Bias gradient: column sums of dA, gate order i,o,u,f -> bias order i,f,u,o.
-  PROF(e, kProfColumnSum, static_cast<double>(n) * 4 * H * elt, st,
-       LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
+  if (fuse_bias) {
+    PROF(e, kProfColumnSum, static_cast<double>(dB_rows) * 4 * H * 4, st,
+         LaunchColumnSum(g + e->OffB(), e->dB_tmp, false, 4 * H, static_cast<int>(dB_rows), 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
+  } else {
+    PROF(e, kProfColumnSum, static_cast<double>(n) * 4 * H * elt, st,
+         LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
+  }
   // dX = dA W^T, then the segmented embedding gradient.
   if ((rc = Gemm(e, e->dX, E, 0, e->dA, 4 * H, false, W, 4 * H, true, n, E, 4 * H, false, st))) return rc;
   CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));

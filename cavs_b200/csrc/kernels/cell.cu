@@ -41,6 +41,22 @@ __device__ __forceinline__ Vec<V> LoadF(const float* p) {
   return r;
 }
 template <int V>
+__device__ __forceinline__ Vec<V> LoadF(const __nv_bfloat16* p) {
+  Vec<V> r;
+  if constexpr (V == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y;
+  } else if constexpr (V == 2) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    r.v[0] = a.x; r.v[1] = a.y;
+  } else {
+    r.v[0] = __bfloat162float(*p);
+  }
+  return r;
+}
+template <int V>
 __device__ __forceinline__ Vec<V> Zero() { Vec<V> r; for (int i = 0; i < V; ++i) r.v[i] = 0.0f; return r; }
 
 template <int V>
@@ -89,10 +105,11 @@ GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ st
   }
 }
 
-template <int K, int V, bool kLeaf>
+// TP: storage type of the gate pre-activations A, P, Q (fp32, or bf16 written by the GEMM epilogue).
+template <typename TP, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
-CellFwd(float* __restrict__ state, float* __restrict__ gates, const float* __restrict__ A, const float* __restrict__ P,
-        const float* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child, int n_total,
+CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
+        const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child, int n_total,
         int off, int rows, int H) {
   const int hv = H / V;
   const int G = (3 + K) * H;
@@ -101,12 +118,12 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const float* __res
   for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
     const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
     const size_t t = static_cast<size_t>(off) + b;
-    const float* a = A + t * 4 * H + j;
-    const Vec<V> ai = LoadF<V>(a), ao = LoadF<V>(a + H), au = LoadF<V>(a + 2 * H), af = LoadF<V>(a + 3 * H);
+    const TP* a = A + t * 4 * H + j;
+    const Vec<V> ai = LoadF<V>(a), ao = LoadF<V>(a + H), au = LoadF<V>(a + 2 * H), af = kLeaf ? Zero<V>() : LoadF<V>(a + 3 * H);
     const Vec<V> bi = LoadF<V>(bias + j), bf = LoadF<V>(bias + H + j), bu = LoadF<V>(bias + 2 * H + j), bo = LoadF<V>(bias + 3 * H + j);
     Vec<V> pi = Zero<V>(), po = Zero<V>(), pu = Zero<V>();
     if (!kLeaf) {
-      const float* p = P + static_cast<size_t>(b) * 3 * H + j;
+      const TP* p = P + static_cast<size_t>(b) * 3 * H + j;
       pi = LoadF<V>(p); po = LoadF<V>(p + H); pu = LoadF<V>(p + 2 * H);
     }
     Vec<V> gi, go, gu, cc, hh;
@@ -118,21 +135,22 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const float* __res
       cc.v[e] = gi.v[e] * gu.v[e];
     }
     float* g = gates + t * G + j;
+    // Leaves have no child cell state: their forget gates multiply zeros in the forward pass and
+    // receive a zero gradient in the backward pass, so they are neither computed nor stored.
+    if (!kLeaf) {
 #pragma unroll
-    for (int c = 0; c < K; ++c) {
-      Vec<V> q = Zero<V>(), cch = Zero<V>();
-      if (!kLeaf) {
-        q = LoadF<V>(Q + (static_cast<size_t>(b) * K + c) * H + j);
+      for (int c = 0; c < K; ++c) {
+        const Vec<V> q = LoadF<V>(Q + (static_cast<size_t>(b) * K + c) * H + j);
         const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
-        if (ch >= 0) cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
-      }
-      Vec<V> gf;
+        const Vec<V> cch = ch >= 0 ? LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j) : Zero<V>();
+        Vec<V> gf;
 #pragma unroll
-      for (int e = 0; e < V; ++e) {
-        gf.v[e] = Sigmoid((af.v[e] + q.v[e]) + bf.v[e]);
-        cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
+        for (int e = 0; e < V; ++e) {
+          gf.v[e] = Sigmoid((af.v[e] + q.v[e]) + bf.v[e]);
+          cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
+        }
+        Store<V>(g + (3 + c) * H, gf);
       }
-      Store<V>(g + (3 + c) * H, gf);
     }
 #pragma unroll
     for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * tanhf(cc.v[e]);
@@ -142,61 +160,97 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const float* __res
   }
 }
 
+// Thread mapping: tpr = H / V threads cover one row, a CTA covers kThreads / tpr rows per iteration
+// and strides over the level, so a thread keeps the same hidden units for its whole life.  That lets
+// it accumulate the bias gradient (column sums of zi, zo, zu, sum zf) in registers; at the end the
+// CTA folds its rows in a fixed order and adds the result to its own row of dB_part
+// ([gridDim.x, 4H], zeroed by the caller before the first level), which a final column sum
+// reduces in CTA order.  dB_part == nullptr skips this (H / V > kThreads).
 template <typename T, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
-CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, const float* __restrict__ dOut,
-        const float* __restrict__ gates, const float* __restrict__ state, const int32_t* __restrict__ child,
-        const int32_t* __restrict__ parent, int n_total, int off, int rows, int H) {
-  const int hv = H / V;
+CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, float* __restrict__ dB_part,
+        const float* __restrict__ dOut, const float* __restrict__ gates, const float* __restrict__ state,
+        const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H) {
+  __shared__ float fold[kThreads * 4 * V];
+  const int tpr = H / V;
   const int G = (3 + K) * H;
-  const long long total = static_cast<long long>(rows) * hv;
-  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
-  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
-    const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
-    const size_t t = static_cast<size_t>(off) + b;
-    const bool has_parent = __ldg(parent + t) >= 0;
-    // Gather of d(h|c) left by the parent; roots see zeros (op_impl_graphop.cu:77-86).
-    const Vec<V> mh = has_parent ? LoadF<V>(mailbox + t * 2 * H + j) : Zero<V>();
-    const Vec<V> mc = has_parent ? LoadF<V>(mailbox + t * 2 * H + H + j) : Zero<V>();
-    const Vec<V> dOutv = LoadF<V>(dOut + t * H + j);
-    const float* g = gates + t * G + j;
-    const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
-    const Vec<V> cown = LoadF<V>(state + t * 2 * H + H + j);
-    Vec<V> zi, zo, zu, dc, zfs = Zero<V>();
+  const int rows_per_iter = tpr <= kThreads ? kThreads / tpr : 1;
+  const int r_in = tpr <= kThreads ? threadIdx.x / tpr : 0;
+  const bool active = r_in < rows_per_iter;
+  float sb[4][V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      const float dh = dOutv.v[e] + mh.v[e];
-      const float th = tanhf(cown.v[e]);
-      const float d_o = dh * th;
-      dc.v[e] = mc.v[e] + (dh * go.v[e]) * (1.0f - th * th);
-      zi.v[e] = (dc.v[e] * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
-      zo.v[e] = d_o * go.v[e] * (1.0f - go.v[e]);
-      zu.v[e] = (dc.v[e] * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
-    }
-    if (!kLeaf) {
+  for (int g4 = 0; g4 < 4; ++g4)
 #pragma unroll
-      for (int c = 0; c < K; ++c) {
-        const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
-        const Vec<V> gf = LoadF<V>(g + (3 + c) * H);
-        Vec<V> z = Zero<V>();
-        if (ch >= 0) {
-          // c of the child is read before the same thread overwrites that slot of the
-          // mailbox (a different array), then d(c_child) = dc * f_c goes to the child's row.
-          const Vec<V> cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
-          Vec<V> dcc;
+    for (int e = 0; e < V; ++e) sb[g4][e] = 0.0f;
+  for (int cg0 = (tpr <= kThreads ? threadIdx.x % tpr : threadIdx.x); cg0 < tpr; cg0 += kThreads) {
+    const int j = cg0 * V;
+    for (long long b = static_cast<long long>(blockIdx.x) * rows_per_iter + r_in; active && b < rows;
+         b += static_cast<long long>(gridDim.x) * rows_per_iter) {
+      const size_t t = static_cast<size_t>(off) + b;
+      const bool has_parent = __ldg(parent + t) >= 0;
+      // Gather of d(h|c) left by the parent; roots see zeros (op_impl_graphop.cu:77-86).
+      const Vec<V> mh = has_parent ? LoadF<V>(mailbox + t * 2 * H + j) : Zero<V>();
+      const Vec<V> mc = has_parent ? LoadF<V>(mailbox + t * 2 * H + H + j) : Zero<V>();
+      const Vec<V> dOutv = LoadF<V>(dOut + t * H + j);
+      const float* g = gates + t * G + j;
+      const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
+      const Vec<V> cown = LoadF<V>(state + t * 2 * H + H + j);
+      Vec<V> zi, zo, zu, dc, zfs = Zero<V>();
 #pragma unroll
-          for (int e = 0; e < V; ++e) {
-            z.v[e] = (dc.v[e] * cch.v[e]) * gf.v[e] * (1.0f - gf.v[e]);
-            dcc.v[e] = dc.v[e] * gf.v[e];
-            zfs.v[e] += z.v[e];
-          }
-          Store<V>(mailbox + static_cast<size_t>(ch) * 2 * H + H + j, dcc);
-        }
-        Store<V>(ZF + (t * K + c) * H + j, z);
+      for (int e = 0; e < V; ++e) {
+        const float dh = dOutv.v[e] + mh.v[e];
+        const float th = tanhf(cown.v[e]);
+        const float d_o = dh * th;
+        dc.v[e] = mc.v[e] + (dh * go.v[e]) * (1.0f - th * th);
+        zi.v[e] = (dc.v[e] * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
+        zo.v[e] = d_o * go.v[e] * (1.0f - go.v[e]);
+        zu.v[e] = (dc.v[e] * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
       }
+      if (!kLeaf) {
+#pragma unroll
+        for (int c = 0; c < K; ++c) {
+          const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+          const Vec<V> gf = LoadF<V>(g + (3 + c) * H);
+          Vec<V> z = Zero<V>();
+          if (ch >= 0) {
+            // c of the child is read from the state array, then d(c_child) = dc * f_c goes to the
+            // child's mailbox row (a different array; the child's level runs in a later launch).
+            const Vec<V> cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
+            Vec<V> dcc;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              z.v[e] = (dc.v[e] * cch.v[e]) * gf.v[e] * (1.0f - gf.v[e]);
+              dcc.v[e] = dc.v[e] * gf.v[e];
+              zfs.v[e] += z.v[e];
+            }
+            Store<V>(mailbox + static_cast<size_t>(ch) * 2 * H + H + j, dcc);
+          }
+          Store<V>(ZF + (t * K + c) * H + j, z);
+        }
+      }
+      T* d = dA + t * 4 * H + j;
+      Store<V>(d, zi); Store<V>(d + H, zo); Store<V>(d + 2 * H, zu); Store<V>(d + 3 * H, zfs);
+#pragma unroll
+      for (int e = 0; e < V; ++e) { sb[0][e] += zi.v[e]; sb[1][e] += zo.v[e]; sb[2][e] += zu.v[e]; sb[3][e] += zfs.v[e]; }
     }
-    T* d = dA + t * 4 * H + j;
-    Store<V>(d, zi); Store<V>(d + H, zo); Store<V>(d + 2 * H, zu); Store<V>(d + 3 * H, zfs);
+  }
+  if (dB_part == nullptr) return;   // uniform across the grid
+  // Fold the CTA's row groups in order, then add into this CTA's partial row.
+#pragma unroll
+  for (int g4 = 0; g4 < 4; ++g4)
+#pragma unroll
+    for (int e = 0; e < V; ++e) fold[(threadIdx.x * 4 + g4) * V + e] = sb[g4][e];
+  __syncthreads();
+  if (r_in == 0 && threadIdx.x < tpr) {
+    float* mine = dB_part + static_cast<size_t>(blockIdx.x) * 4 * H;
+#pragma unroll
+    for (int g4 = 0; g4 < 4; ++g4)
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        float acc = 0.0f;
+        for (int r = 0; r < rows_per_iter; ++r) acc += fold[((r * tpr + threadIdx.x) * 4 + g4) * V + e];
+        mine[g4 * H + threadIdx.x * V + e] += acc;
+      }
   }
 }
 
@@ -228,6 +282,7 @@ ScatterChildGrad(float* __restrict__ mailbox, const float* __restrict__ ds, cons
 
 int VecWidth(int H) { return H % 4 == 0 ? 4 : (H % 2 == 0 ? 2 : 1); }
 
+
 #define DISPATCH_KV(K_, V_, ...)                                             \
   do {                                                                        \
     const int _k = (K_), _v = (V_);                                           \
@@ -253,6 +308,9 @@ int CheckCommon(const char* name, int rows, int H, int K) {
 
 }  // namespace
 
+int CellBwdMaxGrid() { return SmCount() * ResidentCtas(kThreads); }
+bool CellBwdFusesBias(int H) { return H / VecWidth(H) <= kThreads; }
+
 int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const int32_t* child, int n_total, int off,
                        int rows, int H, int K, cudaStream_t st) {
   if (int rc = CheckCommon("gather_child_h", rows, H, K)) return rc;
@@ -267,36 +325,53 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
   return CAVS_OK;
 }
 
-int LaunchCellFwd(float* state, float* gates, const float* A, const float* P, const float* Q, const float* bias,
+int LaunchCellFwd(float* state, float* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st) {
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
   const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
   DISPATCH_KV(K, v, {
-    if (leaf) CellFwd<K, V, true><<<grid, kThreads, 0, st>>>(state, gates, A, P, Q, bias, child, n_total, off, rows, H);
-    else CellFwd<K, V, false><<<grid, kThreads, 0, st>>>(state, gates, A, P, Q, bias, child, n_total, off, rows, H);
+    if (preact_bf16) {
+      using TP = __nv_bfloat16;
+      auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
+      if (leaf) CellFwd<TP, K, V, true><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
+      else CellFwd<TP, K, V, false><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
+    } else {
+      auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
+      if (leaf) CellFwd<float, K, V, true><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
+      else CellFwd<float, K, V, false><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
+    }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
   return CAVS_OK;
 }
 
-int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, const float* dOut, const float* gates,
+int CellBwdGrid(int rows, int H) {
+  const int v = VecWidth(H), tpr = H / v;
+  const int rows_per_iter = tpr <= kThreads ? kThreads / tpr : 1;
+  const long long want = (static_cast<long long>(rows) + rows_per_iter - 1) / rows_per_iter;
+  return static_cast<int>(std::max(1LL, std::min<long long>(want, CellBwdMaxGrid())));
+}
+
+int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const float* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
-  const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
+  CAVS_REQUIRE(dB_part == nullptr || H / v <= kThreads, CAVS_ERR_UNSUPPORTED,
+               "treelstm_cell_bwd: the fused bias gradient needs hidden / vector width <= 256");
+  const int grid = CellBwdGrid(rows, H);
   DISPATCH_KV(K, v, {
     if (bf16) {
       auto* d = static_cast<__nv_bfloat16*>(dA); auto* z = static_cast<__nv_bfloat16*>(ZF);
-      if (leaf) CellBwd<__nv_bfloat16, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
-      else CellBwd<__nv_bfloat16, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
+      if (leaf) CellBwd<__nv_bfloat16, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
+      else CellBwd<__nv_bfloat16, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
     } else {
       auto* d = static_cast<float*>(dA); auto* z = static_cast<float*>(ZF);
-      if (leaf) CellBwd<float, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
-      else CellBwd<float, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dOut, gates, state, child, parent, n_total, off, rows, H);
+      if (leaf) CellBwd<float, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
+      else CellBwd<float, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_bwd");

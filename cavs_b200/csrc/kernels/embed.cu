@@ -92,17 +92,42 @@ EmbedBwdChunks(float* __restrict__ partial, const float* __restrict__ dX, const 
     for (int v = 0; v < kVec; ++v) dst[v] = (acc[0][v] + acc[1][v]) + (acc[2][v] + acc[3][v]);
   }
 }
-// One CTA per segment: dtable[tok,:] = sum of its chunks' partials, in chunk order.
+// One CTA per segment: dtable[tok,:] = sum of its chunks' partials.  The loads of eight chunks
+// are issued together; the adds keep chunk order, so the result is the plain left-to-right sum.
+template <int kVec>
 __global__ void __launch_bounds__(kThreads)
 EmbedBwdSegments(float* __restrict__ dtable, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk,
                  const int32_t* __restrict__ seg_tok, int E) {
   const int seg = blockIdx.x;
   const int c0 = seg_first_chunk[seg], c1 = seg_first_chunk[seg + 1];
   float* dst = dtable + static_cast<size_t>(seg_tok[seg]) * E;
-  for (int e = threadIdx.x; e < E; e += kThreads) {
-    float acc = 0.0f;
-    for (int c = c0; c < c1; ++c) acc += partial[static_cast<size_t>(c) * E + e];
-    dst[e] = acc;
+  for (int e = threadIdx.x * kVec; e < E; e += kThreads * kVec) {
+    float acc[kVec];
+#pragma unroll
+    for (int v = 0; v < kVec; ++v) acc[v] = 0.0f;
+    int c = c0;
+    for (; c + 8 <= c1; c += 8) {
+      float t[8][kVec];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float* src = partial + static_cast<size_t>(c + u) * E + e;
+        if (kVec == 4) {
+          const float4 q = *reinterpret_cast<const float4*>(src);
+          t[u][0] = q.x; t[u][1 % kVec] = q.y; t[u][2 % kVec] = q.z; t[u][3 % kVec] = q.w;
+        } else {
+          t[u][0] = *src;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int v = 0; v < kVec; ++v) acc[v] += t[u][v];
+    }
+    for (; c < c1; ++c)
+#pragma unroll
+      for (int v = 0; v < kVec; ++v) acc[v] += partial[static_cast<size_t>(c) * E + e + v];
+#pragma unroll
+    for (int v = 0; v < kVec; ++v) dst[e + v] = acc[v];
   }
 }
 
@@ -130,7 +155,10 @@ int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const i
   else
     EmbedBwdChunks<1><<<n_chunks, kThreads, 0, st>>>(scratch, dX, order, chunk_off, E);
   CAVS_LAUNCH_CHECK("embed_bwd chunks");
-  EmbedBwdSegments<<<n_seg, kThreads, 0, st>>>(dtable, scratch, seg_first_chunk, seg_tok, E);
+  if (E % 4 == 0 && ((reinterpret_cast<uintptr_t>(dtable) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0)
+    EmbedBwdSegments<4><<<n_seg, kThreads, 0, st>>>(dtable, scratch, seg_first_chunk, seg_tok, E);
+  else
+    EmbedBwdSegments<1><<<n_seg, kThreads, 0, st>>>(dtable, scratch, seg_first_chunk, seg_tok, E);
   CAVS_LAUNCH_CHECK("embed_bwd segments");
   return CAVS_OK;
 }

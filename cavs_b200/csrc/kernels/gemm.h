@@ -27,6 +27,37 @@ struct GemmBf16Args {
   int* status = nullptr;      // device word raised when a bounded wait expires
 };
 int GemmBf16(const GemmBf16Args& args, cudaStream_t stream);
+
+// A TMA tensor map of one operand, encoded once and reused across launches: building one costs
+// microseconds of host time, which dominates the small GEMMs of deep, narrow levels.
+struct TcOperandMap {
+  alignas(64) unsigned char bytes[128];   // CUtensorMap
+  int major = 0;                          // 0 K-major, 1 MN-major
+  int tile_rows = 0;                      // K-major: rows per box (128 for A, the N tile for B)
+};
+// base: row-major matrix with pitch ld.  K-major: [rows, k] -> extents (k, rows); MN-major: [k, rows].
+// tile_rows: 128 for an A operand; for a K-major B operand the N tile the GEMM will use (GemmBf16TileN).
+int EncodeTcOperand(TcOperandMap* out, const void* base, long long rows, long long k, long long ld, int major, int tile_rows);
+inline int GemmBf16TileN(int n) { return n > 128 ? 256 : 128; }
+struct GemmBf16MappedArgs {
+  void* c = nullptr;
+  long long ldc = 0;
+  int out_mode = 0;
+  const TcOperandMap* a = nullptr;
+  int a_row_off = 0;          // first row of this GEMM's A view inside the mapped arena (K-major A only)
+  const TcOperandMap* b = nullptr;
+  // Optional pre-encoded map of the output (EncodeTcOutput over [>= m rows, n] at c); when null and
+  // the TMA-store epilogue applies, one is encoded per call.  The map's row extent clips the M tail,
+  // so it must cover exactly the rows this GEMM may write.
+  const TcOperandMap* c_map = nullptr;
+  int m = 0, n = 0, k = 0;
+  int splits = 1;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int* status = nullptr;
+};
+int EncodeTcOutput(TcOperandMap* out, void* base, long long m, long long n, long long ldc, bool bf16);
+int GemmBf16Mapped(const GemmBf16MappedArgs& args, cudaStream_t stream);
 size_t GemmBf16ScratchBytes(int m, int n, int splits);
 int GemmBf16SplitsFor(int m, int n, int k);
 

@@ -52,6 +52,23 @@ int EncodeBf16(CUtensorMap* map, const void* base, long long inner, long long ou
   return CAVS_OK;
 }
 
+// Tensor map of the output for the TMA-store epilogue: boxes of 32 rows x 128 bytes, 128-byte swizzle.
+int EncodeC(CUtensorMap* map, void* base, long long n, long long m, long long ldc, bool bf16) {
+  std::string err;
+  EncodeFn fn = GetEncodeFn(&err);
+  if (!fn) return Fail(CAVS_ERR_CUDA, err);
+  const size_t elt = bf16 ? 2 : 4;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldc) * elt};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elt), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return Fail(CAVS_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult " + std::to_string(r));
+  return CAVS_OK;
+}
+
 __global__ void __launch_bounds__(256) SplitKReduce(float* __restrict__ c, long long ldc, const float* __restrict__ part,
                                                     int m, int n, int splits, int accumulate) {
   const long long total = static_cast<long long>(m) * n;
@@ -65,7 +82,7 @@ __global__ void __launch_bounds__(256) SplitKReduce(float* __restrict__ c, long 
 }
 
 template <int kBN, int kAMajor, int kBMajor>
-int Launch(const CUtensorMap& ma, const CUtensorMap& mb, const tc::Params& p, dim3 grid, cudaStream_t stream) {
+int Launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const tc::Params& p, dim3 grid, cudaStream_t stream) {
   using S = tc::Smem<kBN>;
   auto kern = tc::GemmBf16Kernel<kBN, kAMajor, kBMajor>;
   static bool configured = false;   // per instantiation
@@ -73,18 +90,18 @@ int Launch(const CUtensorMap& ma, const CUtensorMap& mb, const tc::Params& p, di
     CAVS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
     configured = true;
   }
-  kern<<<grid, tc::kThreads, S::kBytes, stream>>>(ma, mb, p);
+  kern<<<grid, tc::kThreads, S::kBytes, stream>>>(ma, mb, mc, p);
   CAVS_LAUNCH_CHECK("gemm_bf16");
   return CAVS_OK;
 }
 
 template <int kBN>
-int Dispatch(int a_major, int b_major, const CUtensorMap& ma, const CUtensorMap& mb, const tc::Params& p, dim3 grid,
-             cudaStream_t stream) {
-  if (a_major == tc::kMajorK && b_major == tc::kMajorK) return Launch<kBN, 0, 0>(ma, mb, p, grid, stream);
-  if (a_major == tc::kMajorK && b_major == tc::kMajorMN) return Launch<kBN, 0, 1>(ma, mb, p, grid, stream);
-  if (a_major == tc::kMajorMN && b_major == tc::kMajorK) return Launch<kBN, 1, 0>(ma, mb, p, grid, stream);
-  return Launch<kBN, 1, 1>(ma, mb, p, grid, stream);
+int Dispatch(int a_major, int b_major, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const tc::Params& p,
+             dim3 grid, cudaStream_t stream) {
+  if (a_major == tc::kMajorK && b_major == tc::kMajorK) return Launch<kBN, 0, 0>(ma, mb, mc, p, grid, stream);
+  if (a_major == tc::kMajorK && b_major == tc::kMajorMN) return Launch<kBN, 0, 1>(ma, mb, mc, p, grid, stream);
+  if (a_major == tc::kMajorMN && b_major == tc::kMajorK) return Launch<kBN, 1, 0>(ma, mb, mc, p, grid, stream);
+  return Launch<kBN, 1, 1>(ma, mb, mc, p, grid, stream);
 }
 
 bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -113,33 +130,45 @@ int GemmBf16SplitsFor(int m, int n, int k) {
   return best;
 }
 
-int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
+int EncodeTcOperand(TcOperandMap* out, const void* base, long long rows, long long k, long long ld, int major, int tile_rows) {
+  CAVS_REQUIRE(out && base && rows > 0 && k > 0, CAVS_ERR_BAD_ARG, "gemm_bf16: bad operand");
+  CAVS_REQUIRE(major == 0 || major == 1, CAVS_ERR_BAD_ARG, "gemm_bf16: operand major must be 0 (K) or 1 (MN)");
+  // TMA: 16-byte aligned base and row pitch (8 bf16 elements).
+  CAVS_REQUIRE(Aligned16(base) && ld % 8 == 0, CAVS_ERR_BAD_ARG,
+               "gemm_bf16: operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
+  static_assert(sizeof(CUtensorMap) <= sizeof(out->bytes), "tensor map storage");
+  out->major = major;
+  out->tile_rows = tile_rows;
+  CUtensorMap* map = reinterpret_cast<CUtensorMap*>(out->bytes);
+  if (major == tc::kMajorK) return EncodeBf16(map, base, k, rows, ld, tc::kBK, tile_rows);   // [rows, k]
+  return EncodeBf16(map, base, rows, k, ld, 64, tc::kBK);                                     // [k, rows]
+}
+
+int EncodeTcOutput(TcOperandMap* out, void* base, long long m, long long n, long long ldc, bool bf16) {
+  CAVS_REQUIRE(out && base && m > 0 && n > 0 && ldc >= n, CAVS_ERR_BAD_ARG, "gemm_bf16: bad output");
+  CAVS_REQUIRE(Aligned16(base) && (ldc * (bf16 ? 2 : 4)) % 16 == 0, CAVS_ERR_BAD_ARG, "gemm_bf16: output map needs 16-byte aligned rows");
+  out->major = -1;
+  out->tile_rows = bf16 ? 2 : 4;
+  return EncodeC(reinterpret_cast<CUtensorMap*>(out->bytes), base, n, m, ldc, bf16);
+}
+
+int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   CAVS_REQUIRE(g.m >= 0 && g.n >= 0 && g.k >= 0, CAVS_ERR_BAD_ARG, "gemm_bf16: negative dimension");
   if (g.m == 0 || g.n == 0) return CAVS_OK;
   CAVS_REQUIRE(g.k > 0, CAVS_ERR_BAD_ARG, "gemm_bf16: k must be positive");
   CAVS_REQUIRE(g.a && g.b && g.c, CAVS_ERR_BAD_ARG, "gemm_bf16: null pointer");
-  CAVS_REQUIRE(g.a_major == 0 || g.a_major == 1, CAVS_ERR_BAD_ARG, "gemm_bf16: a_major must be 0 (K) or 1 (MN)");
-  CAVS_REQUIRE(g.b_major == 0 || g.b_major == 1, CAVS_ERR_BAD_ARG, "gemm_bf16: b_major must be 0 (K) or 1 (MN)");
   CAVS_REQUIRE(g.out_mode >= 0 && g.out_mode <= 2, CAVS_ERR_BAD_ARG, "gemm_bf16: bad out_mode");
-  // TMA: 16-byte aligned bases and row pitches (8 bf16 elements).
-  CAVS_REQUIRE(Aligned16(g.a) && Aligned16(g.b) && g.lda % 8 == 0 && g.ldb % 8 == 0, CAVS_ERR_BAD_ARG,
-               "gemm_bf16: operands need 16-byte aligned bases and row pitches that are multiples of 8 elements");
   CAVS_REQUIRE(g.ldc >= g.n, CAVS_ERR_BAD_ARG, "gemm_bf16: ldc < n");
+  CAVS_REQUIRE(g.a_row_off == 0 || g.a->major == tc::kMajorK, CAVS_ERR_BAD_ARG, "gemm_bf16: row offsets need a K-major A");
+  const int bn = GemmBf16TileN(g.n);
+  CAVS_REQUIRE(g.a->major != tc::kMajorK || g.a->tile_rows == tc::kBM, CAVS_ERR_BAD_ARG, "gemm_bf16: A map was not encoded for 128-row tiles");
+  CAVS_REQUIRE(g.b->major != tc::kMajorK || g.b->tile_rows == bn, CAVS_ERR_BAD_ARG, "gemm_bf16: B map was encoded for a different N tile");
   const int splits = std::max(1, g.splits);
   CAVS_REQUIRE(splits == 1 || g.out_mode != tc::kStoreBf16, CAVS_ERR_BAD_ARG, "gemm_bf16: split-K needs an fp32 output");
   CAVS_REQUIRE(splits == 1 || (g.scratch && g.scratch_bytes >= GemmBf16ScratchBytes(g.m, g.n, splits)), CAVS_ERR_CAPACITY,
                "gemm_bf16: split-K scratch too small");
-
-  const bool wide = g.n > 128;
-  const int bn = wide ? 256 : 128;
-  CUtensorMap ma, mb;
-  int rc;
-  if (g.a_major == tc::kMajorK) rc = EncodeBf16(&ma, g.a, g.k, g.m, g.lda, tc::kBK, tc::kBM);   // [m, k]
-  else                          rc = EncodeBf16(&ma, g.a, g.m, g.k, g.lda, 64, tc::kBK);         // [k, m]
-  if (rc) return rc;
-  if (g.b_major == tc::kMajorK) rc = EncodeBf16(&mb, g.b, g.k, g.n, g.ldb, tc::kBK, bn);         // [n, k]
-  else                          rc = EncodeBf16(&mb, g.b, g.n, g.k, g.ldb, 64, tc::kBK);         // [k, n]
-  if (rc) return rc;
+  const CUtensorMap& ma = *reinterpret_cast<const CUtensorMap*>(g.a->bytes);
+  const CUtensorMap& mb = *reinterpret_cast<const CUtensorMap*>(g.b->bytes);
 
   const int nkb = (g.k + tc::kBK - 1) / tc::kBK;
   const int kb_per = (nkb + splits - 1) / splits;
@@ -147,17 +176,32 @@ int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
   tc::Params p{};
   p.m = g.m; p.n = g.n; p.k = g.k;
   p.kb_per_split = kb_per;
+  p.n_splits = eff_splits;
+  p.a_row_off = g.a_row_off;
   p.status = g.status;
   if (eff_splits > 1) {
     p.c = g.scratch; p.ldc = g.n; p.split_stride = static_cast<long long>(g.m) * g.n; p.out_mode = tc::kStoreF32;
   } else {
     p.c = g.c; p.ldc = g.ldc; p.split_stride = 0; p.out_mode = g.out_mode;
   }
-  p.n_splits = eff_splits;
+  // TMA-store epilogue: plain stores (no accumulate, no K split) into a 16-byte aligned output.
+  CUtensorMap mc_local;
+  const CUtensorMap* mc = &ma;   // placeholder when unused
+  const size_t c_elt = g.out_mode == tc::kStoreBf16 ? 2 : 4;
+  p.tma_store = 0;
+  if (eff_splits == 1 && g.out_mode != tc::kAccumF32 && Aligned16(g.c) && (g.ldc * c_elt) % 16 == 0) {
+    if (g.c_map) {
+      mc = reinterpret_cast<const CUtensorMap*>(g.c_map->bytes);
+    } else {
+      if (int erc = EncodeC(&mc_local, g.c, g.n, g.m, g.ldc, g.out_mode == tc::kStoreBf16)) return erc;
+      mc = &mc_local;
+    }
+    p.tma_store = 1;
+  }
   const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tc::kBM - 1) / tc::kBM) * eff_splits;
   dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
-  rc = wide ? Dispatch<256>(g.a_major, g.b_major, ma, mb, p, grid, stream)
-            : Dispatch<128>(g.a_major, g.b_major, ma, mb, p, grid, stream);
+  int rc = bn == 256 ? Dispatch<256>(g.a->major, g.b->major, ma, mb, *mc, p, grid, stream)
+                     : Dispatch<128>(g.a->major, g.b->major, ma, mb, *mc, p, grid, stream);
   if (rc) return rc;
   if (eff_splits > 1) {
     const size_t total = static_cast<size_t>(g.m) * g.n;
@@ -167,6 +211,22 @@ int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
     CAVS_LAUNCH_CHECK("gemm_bf16 split-K reduce");
   }
   return CAVS_OK;
+}
+
+int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
+  CAVS_REQUIRE(g.m >= 0 && g.n >= 0 && g.k >= 0, CAVS_ERR_BAD_ARG, "gemm_bf16: negative dimension");
+  if (g.m == 0 || g.n == 0) return CAVS_OK;
+  CAVS_REQUIRE(g.k > 0, CAVS_ERR_BAD_ARG, "gemm_bf16: k must be positive");
+  CAVS_REQUIRE(g.a && g.b && g.c, CAVS_ERR_BAD_ARG, "gemm_bf16: null pointer");
+  TcOperandMap ma, mb;
+  if (int rc = EncodeTcOperand(&ma, g.a, g.m, g.k, g.lda, g.a_major, tc::kBM)) return rc;
+  if (int rc = EncodeTcOperand(&mb, g.b, g.n, g.k, g.ldb, g.b_major, GemmBf16TileN(g.n))) return rc;
+  GemmBf16MappedArgs a;
+  a.c = g.c; a.ldc = g.ldc; a.out_mode = g.out_mode;
+  a.a = &ma; a.b = &mb;
+  a.m = g.m; a.n = g.n; a.k = g.k;
+  a.splits = g.splits; a.scratch = g.scratch; a.scratch_bytes = g.scratch_bytes; a.status = g.status;
+  return GemmBf16Mapped(a, stream);
 }
 
 }  // namespace cavs_b200

@@ -44,6 +44,8 @@ struct Params {
   int kb_per_split;   // K blocks per work item
   int out_mode;
   int n_splits;       // K splits per tile (work items = tiles x splits)
+  int a_row_off;      // added to the row coordinate of K-major A tiles (a level's view into an arena map)
+  int tma_store;      // 1: the epilogue stages C in shared memory and writes it with TMA (map_c valid)
   int* status;        // device word, set non-zero when a bounded wait expires
 };
 
@@ -53,7 +55,10 @@ struct Smem {
   static constexpr int kBTile = kBN * kBK * 2;
   static constexpr int kStage = kATile + kBTile;
   static constexpr int kStages = (kBN == 256) ? 4 : 6;
-  static constexpr int kBarOff = kStages * kStage;
+  // Epilogue staging: 4 warps x 2 slots x (32 rows x 128 bytes), 128-byte swizzled for the TMA store.
+  static constexpr int kCSlot = 32 * 128;
+  static constexpr int kCOff = kStages * kStage;
+  static constexpr int kBarOff = kCOff + 4 * 2 * kCSlot;
   static constexpr int kBytes = kBarOff + 256 + 1024;  // barriers (<= 17 x 8 bytes + TMEM slot) + slack for 1024-byte alignment
 };
 
@@ -162,6 +167,33 @@ __device__ __forceinline__ void TmemLoad64(uint32_t taddr, uint32_t (&r)[64]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void TmaStore2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+// Writes this lane's 128-byte row of a staging slot: eight 16-byte words at 128-byte-swizzled positions.
+template <int kBase, bool kBf16>
+__device__ __forceinline__ void StageRow(uint32_t slot, int lane, const uint32_t (&r)[64]) {
+  const uint32_t row = slot + lane * 128;
+  const uint32_t sw = lane & 7;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    uint32_t v0, v1, v2, v3;
+    if (kBf16) {   // 8 columns -> 16 bytes
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 0]), __uint_as_float(r[kBase + 8 * w + 1]));
+      __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 2]), __uint_as_float(r[kBase + 8 * w + 3]));
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 4]), __uint_as_float(r[kBase + 8 * w + 5]));
+      __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 6]), __uint_as_float(r[kBase + 8 * w + 7]));
+      v0 = *reinterpret_cast<uint32_t*>(&t0); v1 = *reinterpret_cast<uint32_t*>(&t1);
+      v2 = *reinterpret_cast<uint32_t*>(&t2); v3 = *reinterpret_cast<uint32_t*>(&t3);
+    } else {       // 4 columns -> 16 bytes
+      v0 = r[kBase + 4 * w + 0]; v1 = r[kBase + 4 * w + 1]; v2 = r[kBase + 4 * w + 2]; v3 = r[kBase + 4 * w + 3];
+    }
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((w ^ sw) << 4)), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
+  }
+}
+
 // Stores 32 consecutive accumulator columns of one row (registers r[base..base+32)).
 template <int kBase>
 __device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[64], int row, int col0, long long zoff) {
@@ -213,7 +245,8 @@ __device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[
 // warps drain one, the MMA warp already fills the other, and the TMA ring never drains.
 template <int kBN, int kAMajor, int kBMajor>
 __global__ void __launch_bounds__(kThreads, 1)
-GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const Params p) {
   using S = Smem<kBN>;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles.
@@ -272,7 +305,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t b_dst = a_dst + S::kATile;
           const int k0 = (kb_begin + i) * kBK;
           if (kAMajor == kMajorK) {
-            TmaLoad2d(a_dst, &map_a, bar, k0, m0);                                    // box {64 k, 128 rows}
+            TmaLoad2d(a_dst, &map_a, bar, k0, m0 + p.a_row_off);                      // box {64 k, 128 rows}
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j, k0);  // box {64 mn, 64 k}
@@ -324,6 +357,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Epilogue warps 2..5 own TMEM lane quarters (warp % 4).
     const int quarter = warp & 3;
     uint32_t t_local = 0;
+    uint32_t n_stores = 0;   // bulk stores issued by this warp; picks the staging slot (alternating)
     for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++t_local) {
       const int z = w % p.n_splits, tile = w / p.n_splits;
       const int m0 = (tile / n_tiles_n) * kBM, n0 = (tile % n_tiles_n) * kBN;
@@ -334,13 +368,69 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int row = m0 + quarter * 32 + lane;
       const long long zoff = static_cast<long long>(z) * p.split_stride;
       const uint32_t t_addr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (p.tma_store) {
+        // Registers -> swizzled shared staging -> TMA store: every global write is a full 128-byte
+        // row segment, and the tensor map clips the M / N tails.  Two slots per warp alternate on
+        // every store; before a slot is rewritten, all but the most recent bulk group (which reads
+        // the other slot) must have finished reading shared memory.
+        const uint32_t slots = SmemAddr(smem + S::kCOff) + (warp - 2) * 2 * S::kCSlot;
+        const int row0 = m0 + quarter * 32;
+        const bool bf16_out = p.out_mode == kStoreBf16;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBN; c0 += 64) {
-        if (n0 + c0 >= p.n) break;   // warp-uniform
-        uint32_t r[64];
-        TmemLoad64(t_addr + c0, r);
-        StoreChunk<0>(p, r, row, n0 + c0, zoff);
-        StoreChunk<32>(p, r, row, n0 + c0 + 32, zoff);
+        for (int c0 = 0; c0 < kBN; c0 += 64) {
+          if (n0 + c0 >= p.n) break;   // warp-uniform
+          uint32_t r[64];
+          TmemLoad64(t_addr + c0, r);
+          if (row0 < p.m) {
+            if (bf16_out) {
+              // 64 columns of bf16 = one 128-byte row: one slot, one store
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              __syncwarp();
+              const uint32_t slot = slots + (n_stores++ & 1) * S::kCSlot;
+              StageRow<0, true>(slot, lane, r);
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                TmaStore2d(&map_c, slot, n0 + c0, row0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              }
+            } else {
+              // two 32-column fp32 halves, one slot and one bulk group each; a slot is rewritten
+              // once the group issued two stores ago has finished reading it
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              __syncwarp();
+              const uint32_t slot_a = slots + (n_stores++ & 1) * S::kCSlot;
+              StageRow<0, false>(slot_a, lane, r);
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                TmaStore2d(&map_c, slot_a, n0 + c0, row0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              }
+              if (n0 + c0 + 32 < p.n) {
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
+                const uint32_t slot_b = slots + (n_stores++ & 1) * S::kCSlot;
+                StageRow<32, false>(slot_b, lane, r);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                  TmaStore2d(&map_c, slot_b, n0 + c0 + 32, row0);
+                  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 64) {
+          if (n0 + c0 >= p.n) break;   // warp-uniform
+          uint32_t r[64];
+          TmemLoad64(t_addr + c0, r);
+          StoreChunk<0>(p, r, row, n0 + c0, zoff);
+          StoreChunk<32>(p, r, row, n0 + c0 + 32, zoff);
+        }
       }
       // All of this warp's TMEM reads are complete (wait::ld above): hand the accumulator back.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -348,6 +438,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0) MbarArrive(SmemAddr(acc_empty + acc));
     }
   }
+  if (warp >= 2 && lane == 0 && p.tma_store) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   if (!ok && p.status != nullptr) atomicExch(p.status, 1);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();

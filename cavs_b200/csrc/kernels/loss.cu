@@ -23,7 +23,7 @@ constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kRowsPerBlock = 32;     // rows per CTA iteration (4 per warp)
 constexpr int kMaxC = 8;
-constexpr int kCtasPerSm = 4;
+constexpr int kCtasPerSm = 2;
 // Floats per per-CTA partial record ([C*H] dWc, [C] dbc, [1] loss sum), padded to 16 bytes so the
 // 128-bit stores of every CTA's record stay aligned.
 __host__ __device__ constexpr int PartialStride(int C, int H) { return (C * H + C + 1 + 3) & ~3; }
@@ -36,8 +36,10 @@ __device__ __forceinline__ float WarpSum(float v) {
 }
 
 // kVec = 4 when H is a multiple of 4 (128-bit accesses), else 1.
-template <int C, int kVec>
-__global__ void __launch_bounds__(kThreads)
+// kIters > 0: H == 128 * kIters, so a lane's whole share of a row (kIters 128-bit words) is loaded
+// up front and every loop unrolls; kIters == 0: generic loops.
+template <int C, int kVec, int kIters>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ partial,
                const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
                const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows) {
@@ -69,7 +71,19 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
         float z[C];
 #pragma unroll
         for (int c = 0; c < C; ++c) z[c] = 0.0f;
-        if (kVec == 4) {
+        if (kIters > 0) {
+          float4 hv[kIters > 0 ? kIters : 1];
+#pragma unroll
+          for (int it = 0; it < kIters; ++it) hv[it] = __ldcs(reinterpret_cast<const float4*>(hr + lane * 4 + it * 128));
+#pragma unroll
+          for (int it = 0; it < kIters; ++it) {
+#pragma unroll
+            for (int c = 0; c < C; ++c) {
+              const float4 w = *reinterpret_cast<const float4*>(sW + c * H + lane * 4 + it * 128);
+              z[c] = fmaf(hv[it].x, w.x, fmaf(hv[it].y, w.y, fmaf(hv[it].z, w.z, fmaf(hv[it].w, w.w, z[c]))));
+            }
+          }
+        } else if (kVec == 4) {
           for (int j = lane * 4; j < H; j += 128) {
             const float4 hv = *reinterpret_cast<const float4*>(hr + j);
 #pragma unroll
@@ -102,6 +116,7 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
         if (lane == 0) { loss[t] = lrow; loss_acc += lrow; }
         float* dr = dOut + static_cast<long long>(t) * H;
         if (kVec == 4) {
+#pragma unroll 4
           for (int j = lane * 4; j < H; j += 128) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -109,7 +124,7 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
               const float4 w = *reinterpret_cast<const float4*>(sW + c * H + j);
               a.x = fmaf(dz[c], w.x, a.x); a.y = fmaf(dz[c], w.y, a.y); a.z = fmaf(dz[c], w.z, a.z); a.w = fmaf(dz[c], w.w, a.w);
             }
-            *reinterpret_cast<float4*>(dr + j) = a;
+            __stcs(reinterpret_cast<float4*>(dr + j), a);
           }
         } else {
           for (int j = lane; j < H; j += 32) {
@@ -131,6 +146,7 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
     __syncthreads();
     // Phase 2: dWc += dz^T h with each thread owning fixed columns; rows in ascending order.
     const int r_end = min(kRowsPerBlock, rows - r0);
+#pragma unroll 8
     for (int rr = 0; rr < r_end; ++rr) {
       const float* hr = h + static_cast<long long>(r0 + rr) * h_pitch;
       if (kVec == 4) {
@@ -232,23 +248,26 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   const size_t smem = (static_cast<size_t>(C) * H + kRowsPerBlock * C + kWarps) * sizeof(float);
   const bool vec4 = H % 4 == 0 && h_pitch % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dOut) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0;
   CAVS_REQUIRE(smem <= 200 * 1024, CAVS_ERR_UNSUPPORTED, "loss_head: classifier does not fit in shared memory");
-#define LOSS_CASE(CC)                                                                                              \
-  case CC: {                                                                                                       \
-    if (vec4) {                                                                                                    \
-      if (smem > 48 * 1024)                                                                                        \
-        CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-      LossHeadKernel<CC, 4><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
-    } else {                                                                                                       \
-      if (smem > 48 * 1024)                                                                                        \
-        CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-      LossHeadKernel<CC, 1><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
-    }                                                                                                              \
-    break;                                                                                                         \
+#define LOSS_LAUNCH(CC, VV, II)                                                                                      \
+  do {                                                                                                               \
+    if (smem > 48 * 1024)                                                                                            \
+      CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC, VV, II>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+    LossHeadKernel<CC, VV, II><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
+  } while (0)
+#define LOSS_CASE(CC)                                                        \
+  case CC: {                                                                 \
+    if (vec4 && H == 1024) LOSS_LAUNCH(CC, 4, 8);                            \
+    else if (vec4 && H == 512) LOSS_LAUNCH(CC, 4, 4);                        \
+    else if (vec4 && H == 256) LOSS_LAUNCH(CC, 4, 2);                        \
+    else if (vec4) LOSS_LAUNCH(CC, 4, 0);                                    \
+    else LOSS_LAUNCH(CC, 1, 0);                                              \
+    break;                                                                   \
   }
   switch (C) {
     LOSS_CASE(1) LOSS_CASE(2) LOSS_CASE(3) LOSS_CASE(4) LOSS_CASE(5) LOSS_CASE(6) LOSS_CASE(7) LOSS_CASE(8)
     default: return Fail(CAVS_ERR_UNSUPPORTED, "loss_head: class count");
   }
+#undef LOSS_LAUNCH
 #undef LOSS_CASE
   CAVS_LAUNCH_CHECK("loss_head");
   const int width = C * H + C + 1;

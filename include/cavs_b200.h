@@ -136,8 +136,10 @@ CAVS_API int cavs_gather_child_h(void* S, void* HK, int bf16, const float* state
  * NVRTC-fused elementwise groups, cavs/backend/op_impl_fused_kernel.cu:62-64, plus the forward
  * Scatter and Push, cavs/backend/op_impl_graphop.cu:108-202).  A [n_total,4H] = x.W (i,o,u,f),
  * P [rows,3H] = (sum h).U_iou, Q [rows,n_slots,H] = h_c.U_f, bias [4H] (i,f,u,o).  Writes
- * gates [n_total,(3+n_slots)H] and state [n_total,2H].  leaf != 0: no children (P, Q unused). */
-CAVS_API int cavs_treelstm_cell_fwd(float* state, float* gates, const float* A, const float* P, const float* Q,
+ * gates [n_total,(3+n_slots)H] and state [n_total,2H].  leaf != 0: no children (P, Q unused, the
+ * forget gates are neither computed nor stored).  preact_bf16 != 0: A, P, Q hold bf16 (the GEMM
+ * epilogue's rounded output), else fp32. */
+CAVS_API int cavs_treelstm_cell_fwd(float* state, float* gates, const void* A, const void* P, const void* Q, int preact_bf16,
                                     const float* bias, const int32_t* child, int n_total, int off, int rows, int hidden,
                                     int n_slots, int leaf, void* stream);
 /* Fused gate-gradient backward of the cell: reads d(pushed h) dOut [n_total,H], the parent's

@@ -92,14 +92,15 @@ def tables(parents: np.ndarray, n_slots: int = 2, mode: int = 0):
 
 class Cfg(ctypes.Structure):
     _fields_ = [(k, ctypes.c_int) for k in
-                ("n", "n_levels", "hidden", "embed", "vocab", "classes", "n_slots", "gemm_bf16", "loss_rows")]
+                ("n", "n_levels", "hidden", "embed", "vocab", "classes", "n_slots", "gemm_bf16", "loss_rows", "preact_bf16")]
 
 
-def treelstm_fwd_bwd(tb: dict, tok, label, params: dict, H, E, V, C, K=2, gemm_bf16=False, loss_rows=0, want_dstate=False):
+def treelstm_fwd_bwd(tb: dict, tok, label, params: dict, H, E, V, C, K=2, gemm_bf16=False, loss_rows=0, want_dstate=False,
+                     preact_bf16=False):
     """Runs the oracle's Tree-LSTM forward + loss + backward on index tables `tb`
     (from tables() or from the product scheduler).  Returns a dict of numpy arrays."""
     n = int(tb["n"])
-    cfg = Cfg(n, int(tb["n_levels"]), H, E, V, C, K, int(gemm_bf16), int(loss_rows))
+    cfg = Cfg(n, int(tb["n_levels"]), H, E, V, C, K, int(gemm_bf16), int(loss_rows), int(preact_bf16))
     f32 = lambda a: np.ascontiguousarray(a, np.float32)
     i32 = lambda a: np.ascontiguousarray(a, np.int32)
     Emb, W, U, B, Wc, bc = (f32(params[k]) for k in ("Emb", "W", "U", "B", "Wc", "bc"))

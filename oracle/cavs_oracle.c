@@ -367,6 +367,7 @@ typedef struct {
   int n_slots;    /* K */
   int gemm_bf16;  /* round every GEMM operand to bf16 first (extension)  */
   int loss_rows;  /* divisor of the loss gradient; the reference uses the row count of the logits */
+  int preact_bf16; /* also round the forward GEMM outputs (gate pre-activations) to bf16 (extension) */
 } cavs_oracle_cfg;
 
 typedef struct {
@@ -419,6 +420,7 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
     for (int e = 0; e < E; e++) x[(size_t)t * E + e] = bf ? bf16_round(Emb[(size_t)id * E + e]) : Emb[(size_t)id * E + e];
   }
   gemm_nn(a, x, Wr, n, 4 * H, E, 0);
+  if (cfg->preact_bf16) for (size_t i = 0; i < (size_t)n * 4 * H; i++) a[i] = bf16_round(a[i]);
 
   for (int l = 0; l < cfg->n_levels; l++) {
     const int off = level_off[l], cnt = level_off[l + 1] - off;
@@ -444,6 +446,11 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
     gemm_nn(p + (size_t)off * 3 * H, s + (size_t)off * H, Ur_iou, cnt, 3 * H, H, 0);
     for (int c = 0; c < K; c++)
       gemm_nn(q + ((size_t)c * n + off) * H, hk + ((size_t)c * n + off) * H, Ur_f, cnt, H, H, 0);
+    if (cfg->preact_bf16) {
+      for (size_t i = (size_t)off * 3 * H; i < (size_t)(off + cnt) * 3 * H; i++) p[i] = bf16_round(p[i]);
+      for (int c = 0; c < K; c++)
+        for (size_t i = ((size_t)c * n + off) * H; i < ((size_t)c * n + off + cnt) * H; i++) q[i] = bf16_round(q[i]);
+    }
     /* Gates and cell (tree-lstm-cavs.cc:159-168), add order (xW + hU) + b. */
 #pragma omp parallel for schedule(static)
     for (int t = off; t < off + cnt; t++) {

@@ -1,0 +1,259 @@
+// Graph-op tests written against the reference's operator interface (OpDef -> CreateOp ->
+// OpImpl::Compute(OpContext*)), in the style of the reference's own *_test.cc executables.
+//
+//   graph_ops_test cpu   registry, gradient pairing and the scheduler facade (no CUDA call)
+//   graph_ops_test gpu   Gather / Scatter / Pull / Push / FunctionPopRet on a device, compared
+//                        bit-for-bit with the CPU oracle's row ops driven by the same lists
+//
+// Links the product host library and the test oracle (oracle/libcavs_oracle.so).
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "cavs/backend/op_decl.h"
+#include "cavs/backend/op_impl.h"
+#include "cavs/midend/graph_scheduler.h"
+#include "cavs/util/op_def_builder.h"
+
+extern "C" {
+int cavs_oracle_schedule_stream(const int* parents, int batch, int max_len, int* out, int capacity);
+void cavs_oracle_gather_rows(float* out, const float* inp, const int* ids, int n_ids, int row);
+void cavs_oracle_scatter_rows(float* out, const int* ids, const float* inp, int n_ids, int row);
+void cavs_oracle_zero_rows(float* out, int n_ids, int row);
+}
+
+using backend::CreateOp;
+using backend::OpImpl;
+using midend::BatchGraphScheduler;
+using midend::OpContext;
+using midend::Tensor;
+using midend::TensorShape;
+
+static int g_failures = 0;
+#define EXPECT(cond)                                                          \
+  do {                                                                        \
+    if (!(cond)) { std::printf("FAILED %s:%d  %s\n", __FILE__, __LINE__, #cond); ++g_failures; } \
+  } while (0)
+
+// Tree A (2 leaves) and tree B (3 leaves): level 1 mixes A's root with B's inner vertex, the case
+// where the reference's compact lists shift rows.
+static const int kSkew[2][5] = {{2, 2, -1, -1, -1}, {3, 3, 4, 4, -1}};
+static const int kBatch = 2, kMaxLen = 5;
+
+static OpDef GraphOp(const char* name, int child, const std::vector<int>& shape, bool source) {
+  OpDefBuilder b(name);
+  if (source) b.Output(std::string(name) + "_out").Shape(shape);
+  else b.Input(std::string(name) + "_in").Output(std::string(name) + "_out").Shape(shape);
+  if (child >= 0) b.AttrSingle("Child", child);
+  return b.Device("GPU").Finalize();
+}
+
+static void TestRegistryAndDecls() {
+  for (const char* name : {"Gather", "Scatter", "Pull", "Push", "FunctionPushArg", "FunctionPopRet"}) {
+    OpDef def = GraphOp(name, 0, {4}, false);
+    if (std::string(name) == "Gather") def = GraphOp(name, 0, {4}, true);
+    std::unique_ptr<OpImpl> op(CreateOp(def));
+    EXPECT(op != nullptr);
+    if (op) EXPECT(op->name() == name);
+  }
+  OpDef unknown = OpDefBuilder("NoSuchOp").Device("GPU").Finalize();
+  EXPECT(CreateOp(unknown) == nullptr);
+  OpDef cpu_gather = OpDefBuilder("Gather").Output("g").Shape(std::vector<int>{4}).AttrSingle("Child", 0).Device("CPU").Finalize();
+  EXPECT(CreateOp(cpu_gather) == nullptr);   // GPU only, like the reference
+
+  // Gather(Child=1) <-> Scatter(Child=1)
+  OpDef gather = GraphOp("Gather", 1, {8}, true);
+  std::vector<OpDef> g = backend::MakeGradient(gather);
+  EXPECT(g.size() == 1 && g[0].name() == "Scatter");
+  EXPECT(g[0].input(0) == GetGradientName("Gather_out"));
+  EXPECT(GetSingleArg<int>(g[0], "Child") == 1);
+  OpDef scatter = GraphOp("Scatter", 0, {8}, false);
+  g = backend::MakeGradient(scatter);
+  EXPECT(g.size() == 1 && g[0].name() == "Gather" && g[0].output(0) == GetGradientName("Scatter_in"));
+  EXPECT(g[0].shape(0).dim(0) == 8 && GetSingleArg<int>(g[0], "Child") == 0);
+  // Pull <-> Push
+  g = backend::MakeGradient(GraphOp("Pull", -1, {1}, true));
+  EXPECT(g.size() == 1 && g[0].name() == "Push");
+  g = backend::MakeGradient(GraphOp("Push", -1, {6}, false));
+  EXPECT(g.size() == 1 && g[0].name() == "Pull" && g[0].shape(0).dim(0) == 6);
+  // GraphOutput -> GraphOutput_grad over the variables it closes over
+  OpDef go = OpDefBuilder("GraphOutput").Input("graph").Input("x").Input("W").Output("y").Shape({-1, 6}).Device("GPU").Finalize();
+  g = backend::MakeGradient(go);
+  EXPECT(g.size() == 1 && g[0].name() == "GraphOutput_grad" && g[0].input_size() == 3 && g[0].output_size() == 2);
+  EXPECT(g[0].output(1) == "W_grad");
+  std::vector<TensorShapeDef> shp = backend::ShapeInference(gather, {});
+  EXPECT(shp.size() == 1 && shp[0].dim(0) == 8);
+}
+
+// Walks the facade like GraphStatement::Run / GraphGradStatement::Run and rebuilds the oracle's
+// schedule stream from what the accessors return.
+static void TestSchedulerFacade() {
+  Tensor graph("graph", CPU, DT_INT32, TensorShape({kBatch, kMaxLen}), const_cast<int*>(&kSkew[0][0]));
+  BatchGraphScheduler gs;
+  const int total = gs.LoadGraph(graph);
+  std::vector<int> offs, body;
+  auto put = [&body](const std::vector<int>& v) { body.push_back((int)v.size()); body.insert(body.end(), v.begin(), v.end()); };
+  int levels = 0, sched = 0;
+  gs.Initialize();
+  while (!gs.Terminate()) {
+    offs.push_back(gs.GetCurrentRoundOffset());
+    sched = gs.GetCurrentRoundOffset() + (int)gs.GetJobId().size();
+    put(gs.GetJobId());
+    put(gs.CurrentRoundTensorIdsForGather(0));
+    put(gs.CurrentRoundTensorIdsForGather(1));
+    put(gs.CurrentRoundTensorIdsForScatter(0));
+    put(gs.CurrentRoundTensorIdsForGatherInitialization());
+    gs.ActivateNext();
+    ++levels;
+  }
+  offs.push_back(sched);
+  body.insert(body.end(), gs.TensorIdsToJobIds().begin(), gs.TensorIdsToJobIds().end());
+  gs.ReverseGraph();
+  gs.Initialize();
+  while (!gs.Terminate()) {
+    body.push_back(gs.GetCurrentRoundOffset());
+    put(gs.GetJobId());
+    put(gs.CurrentRoundTensorIdsForGather(0));
+    put(gs.CurrentRoundTensorIdsForScatter(0));
+    put(gs.CurrentRoundTensorIdsForScatter(1));
+    put(gs.CurrentRoundTensorIdsForGatherInitialization());
+    gs.ActivateNext();
+  }
+  std::vector<int> mine = {total, levels};
+  mine.insert(mine.end(), offs.begin(), offs.end());
+  mine.insert(mine.end(), body.begin(), body.end());
+  std::vector<int> want(4096);
+  const int n = cavs_oracle_schedule_stream(&kSkew[0][0], kBatch, kMaxLen, want.data(), (int)want.size());
+  EXPECT(n == (int)mine.size());
+  EXPECT(n > 0 && std::memcmp(want.data(), mine.data(), sizeof(int) * mine.size()) == 0);
+}
+
+static std::vector<float> ToHost(const Tensor& t, size_t elems) {
+  std::vector<float> h(elems);
+  cudaMemcpy(h.data(), t.data<float>(), elems * sizeof(float), cudaMemcpyDeviceToHost);
+  return h;
+}
+
+// One forward sweep of a toy vertex function y = g0 + 2*g1 + x (combined on the host) through the
+// real operators, against the same sweep done with the oracle's row ops on the host.
+static void TestGraphOpsOnDevice(bool aligned) {
+  const int W = 12;   // mailbox row width (floats)
+  Tensor graph("graph", CPU, DT_INT32, TensorShape({kBatch, kMaxLen}), const_cast<int*>(&kSkew[0][0]));
+  BatchGraphScheduler gs;
+  gs.SetAlignedTables(aligned);
+  const int total = gs.LoadGraph(graph);
+  const int cap = kBatch * kMaxLen;
+
+  // Arenas [cap, W]; per-vertex tensors are dynamic, the vertex input is job-ordered.
+  auto arena = [&](const char* name) { Tensor t(name, GPU, DT_FLOAT, TensorShape({cap, W})); t.SetAsDynamic(); return t; };
+  Tensor mailbox = arena("mailbox"), g0 = arena("g0"), g1 = arena("g1"), xin = arena("x"), y = arena("y"), pushed = arena("pushed");
+  Tensor func_arg("arg", GPU, DT_FLOAT, TensorShape({cap, W}));
+  Tensor graph_out("out", GPU, DT_FLOAT, TensorShape({cap, W}));
+  std::vector<float> h_arg((size_t)cap * W);
+  for (size_t i = 0; i < h_arg.size(); i++) h_arg[i] = 0.25f * (float)((i * 2654435761u) % 97) - 3.0f;
+  cudaMemcpy(func_arg.mutable_data<float>(), h_arg.data(), h_arg.size() * sizeof(float), cudaMemcpyHostToDevice);
+  gs.SetMessagePasser(mailbox);
+
+  std::unique_ptr<OpImpl> gather0(CreateOp(GraphOp("Gather", 0, {W}, true))), gather1(CreateOp(GraphOp("Gather", 1, {W}, true)));
+  std::unique_ptr<OpImpl> pull(CreateOp(GraphOp("Pull", -1, {W}, true))), scatter(CreateOp(GraphOp("Scatter", 0, {W}, false)));
+  std::unique_ptr<OpImpl> push(CreateOp(GraphOp("Push", -1, {W}, false)));
+  std::unique_ptr<OpImpl> pusharg(CreateOp(GraphOp("FunctionPushArg", -1, {W}, false))), popret(CreateOp(GraphOp("FunctionPopRet", -1, {W}, false)));
+  auto ctx = [&](std::vector<const Tensor*> in, std::vector<Tensor*> out) {
+    std::unique_ptr<OpContext> c(new OpContext());
+    for (auto* t : in) c->AppendInput(t);
+    for (auto* t : out) c->AppendOutput(t);
+    c->SetGraphScheduler(&gs);
+    return c;
+  };
+  auto c_g0 = ctx({}, {&g0}), c_g1 = ctx({}, {&g1}), c_pull = ctx({}, {&xin}), c_sc = ctx({&y}, {&mailbox}), c_push = ctx({&y}, {&pushed});
+  auto c_arg = ctx({&func_arg}, {}), c_ret = ctx({}, {&graph_out});
+
+  // Host model of the same sweep with the oracle's row ops.
+  std::vector<float> m_mail((size_t)cap * W, 0.f), m_g0((size_t)cap * W, 0.f), m_g1((size_t)cap * W, 0.f), m_x((size_t)cap * W, 0.f),
+      m_y((size_t)cap * W, 0.f), m_out((size_t)cap * W, 0.f);
+
+  pusharg->Compute(c_arg.get());
+  gs.Initialize();
+  while (!gs.Terminate()) {
+    const int off = gs.GetCurrentRoundOffset(), rows = (int)gs.GetJobId().size();
+    for (OpContext* c : {c_g0.get(), c_g1.get(), c_pull.get(), c_sc.get(), c_push.get()}) c->SetTensorOffset();
+    gather0->Compute(c_g0.get());
+    gather1->Compute(c_g1.get());
+    pull->Compute(c_pull.get());
+    // oracle side of the three source ops
+    for (int c = 0; c < 2; c++) {
+      std::vector<float>& mg = c == 0 ? m_g0 : m_g1;
+      const std::vector<int>& ids = gs.CurrentRoundTensorIdsForGather(c);
+      if (aligned) {
+        // row b pairs with its own slot-c child: rebuild the padded list from the compact one
+        // by walking the level (children exist exactly for the first |ids| jobs that own the slot).
+        std::vector<float> tmp((size_t)rows * W, 0.f);
+        // The facade's aligned device list is what the product used; model it from the schedule:
+        // a job owns slot c iff it has > c children, which for this batch is read off the parent array.
+        int k = 0;
+        for (int b = 0; b < rows; b++) {
+          const int job = gs.GetJobId()[b];
+          int n_child = 0;
+          const int sample = job < 3 ? 0 : 1, base = sample == 0 ? 0 : 3, len = sample == 0 ? 3 : 5;
+          for (int j = 0; j < len; j++) if (kSkew[sample][j] == job - base) n_child++;
+          if (c < n_child) { std::memcpy(&tmp[(size_t)b * W], &m_mail[(size_t)ids[k] * W], W * sizeof(float)); k++; }
+        }
+        std::memcpy(&mg[(size_t)off * W], tmp.data(), tmp.size() * sizeof(float));
+      } else if (!ids.empty()) {
+        cavs_oracle_gather_rows(&mg[(size_t)off * W], m_mail.data(), ids.data(), (int)ids.size(), W);
+      } else {
+        cavs_oracle_zero_rows(&mg[(size_t)off * W], (int)gs.CurrentRoundTensorIdsForGatherInitialization().size(), W);
+      }
+    }
+    cavs_oracle_gather_rows(&m_x[(size_t)off * W], h_arg.data(), gs.GetJobId().data(), rows, W);
+    // toy vertex function on the host, from the DEVICE results of the source ops
+    std::vector<float> d_g0 = ToHost(g0, (size_t)rows * W), d_g1 = ToHost(g1, (size_t)rows * W), d_x = ToHost(xin, (size_t)rows * W);
+    EXPECT(std::memcmp(d_g0.data(), &m_g0[(size_t)off * W], d_g0.size() * sizeof(float)) == 0);
+    EXPECT(std::memcmp(d_g1.data(), &m_g1[(size_t)off * W], d_g1.size() * sizeof(float)) == 0);
+    EXPECT(std::memcmp(d_x.data(), &m_x[(size_t)off * W], d_x.size() * sizeof(float)) == 0);
+    std::vector<float> hy((size_t)rows * W);
+    for (size_t i = 0; i < hy.size(); i++) hy[i] = d_g0[i] + 2.0f * d_g1[i] + d_x[i];
+    std::memcpy(&m_y[(size_t)off * W], hy.data(), hy.size() * sizeof(float));
+    y.ScaleDynamicDimension(rows);
+    cudaMemcpy(y.mutable_data<float>(), hy.data(), hy.size() * sizeof(float), cudaMemcpyHostToDevice);
+    scatter->Compute(c_sc.get());
+    push->Compute(c_push.get());
+    // oracle side of Scatter
+    const std::vector<int>& sids = gs.CurrentRoundTensorIdsForScatter(0);
+    if (aligned) {
+      int k = 0;
+      for (int b = 0; b < rows; b++) {
+        const int job = gs.GetJobId()[b];
+        const bool root = (job == 2 || job == 7);
+        if (!root) { std::memcpy(&m_mail[(size_t)sids[k] * W], &hy[(size_t)b * W], W * sizeof(float)); k++; }
+      }
+    } else if (!sids.empty()) {
+      cavs_oracle_scatter_rows(m_mail.data(), sids.data(), hy.data(), (int)sids.size(), W);
+    }
+    gs.ActivateNext();
+  }
+  for (OpContext* c : {c_g0.get(), c_g1.get(), c_pull.get(), c_sc.get(), c_push.get()}) c->ResetTensorOffset();
+  popret->Compute(c_ret.get());
+  cavs_oracle_scatter_rows(m_out.data(), gs.TensorIdsToJobIds().data(), m_y.data(), total, W);
+  cudaDeviceSynchronize();
+  mailbox.SetOffsetWithId(0);
+  std::vector<float> d_mail = ToHost(mailbox, (size_t)cap * W), d_out = ToHost(graph_out, (size_t)cap * W);
+  EXPECT(std::memcmp(d_mail.data(), m_mail.data(), d_mail.size() * sizeof(float)) == 0);
+  EXPECT(std::memcmp(d_out.data(), m_out.data(), (size_t)total * W * sizeof(float)) == 0);
+  EXPECT(cudaGetLastError() == cudaSuccess);
+}
+
+int main(int argc, char** argv) {
+  const std::string mode = argc > 1 ? argv[1] : "cpu";
+  TestRegistryAndDecls();
+  TestSchedulerFacade();
+  if (mode == "gpu") {
+    TestGraphOpsOnDevice(false);   // the reference's positional lists
+    TestGraphOpsOnDevice(true);    // aligned lists
+  }
+  if (g_failures == 0) std::printf("graph_ops_test %s: ok\n", mode.c_str());
+  return g_failures == 0 ? 0 : 1;
+}

@@ -31,7 +31,9 @@ def _run(cuda, parents, tok_job, label_job, params, H, E, V, C, K=2, bf16=False)
 
 def _oracle(s, tok_job, label_job, params, H, E, V, C, K=2, bf16=False):
     tb = tables_from_schedule(s)
-    return oracle.treelstm_fwd_bwd(tb, tok_job[tb["t2j"]], label_job[tb["t2j"]], params, H, E, V, C, K=K, gemm_bf16=bf16)
+    # in bf16 mode the product rounds the GEMM operands and the stored gate pre-activations to bf16
+    return oracle.treelstm_fwd_bwd(tb, tok_job[tb["t2j"]], label_job[tb["t2j"]], params, H, E, V, C, K=K, gemm_bf16=bf16,
+                                   preact_bf16=bf16)
 
 
 def test_golden_fp32(cuda):

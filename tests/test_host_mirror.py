@@ -1,0 +1,29 @@
+"""The C++ mirror of the reference's operator interface (OpDef -> CreateOp -> OpImpl::Compute),
+exercised by a C++ test executable in the style of the reference's own *_test.cc programs
+(tests/cpp/graph_ops_test.cc).  The executable is built by __graft_entry__.build()."""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+EXE = Path(__file__).parent / "cpp" / "bin" / "graph_ops_test"
+
+
+def _build():
+    if not EXE.exists():
+        import __graft_entry__ as g
+        g.build()
+    return EXE
+
+
+def test_registry_decls_and_scheduler_facade_cpu():
+    r = subprocess.run([str(_build()), "cpu"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ok" in r.stdout
+
+
+@pytest.mark.gpu
+def test_graph_ops_bit_exact_on_device(cuda):
+    r = subprocess.run([str(_build()), "gpu"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ok" in r.stdout
