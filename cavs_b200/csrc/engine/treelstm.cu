@@ -19,6 +19,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -49,6 +51,7 @@ struct cavs_treelstm {
   // TMA maps of the per-level GEMM operands, encoded once over whole arenas (bf16 mode).
   TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
+  TcOperandMap map_P, map_Q, map_ds, map_dq;                 // level-local outputs (rows past a level's end are scratch)
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
   // ---- batches: two slots so the tables of the next batch can be packed and uploaded while the
   // current one executes; forward() promotes the staged slot ----
@@ -188,13 +191,13 @@ size_t Carve(cavs_treelstm* e, void* base) {
 // `accumulate`: 0 store, 1 add into C, 2 store C as bf16 (bf16 mode only; the fp32 path always writes fp32).
 int Gemm(cavs_treelstm* e, void* c, long long ldc, int accumulate, const void* a, long long lda, bool a_t, const void* b,
          long long ldb, bool b_t, int m, int n, int k, bool split_ok, cudaStream_t st, const TcOperandMap* amap = nullptr,
-         int a_row_off = 0, const TcOperandMap* bmap = nullptr) {
+         int a_row_off = 0, const TcOperandMap* bmap = nullptr, const TcOperandMap* cmap = nullptr) {
   if (m == 0 || n == 0 || k == 0) return CAVS_OK;
   if (e->bf16 && amap && bmap) {
     // Per-level GEMM through pre-encoded arena maps: `a` is not used, the level is a row offset.
     GemmBf16MappedArgs g;
     g.c = c; g.ldc = ldc; g.out_mode = accumulate;
-    g.a = amap; g.a_row_off = a_row_off; g.b = bmap;
+    g.a = amap; g.a_row_off = a_row_off; g.b = bmap; g.c_map = cmap;
     g.m = m; g.n = n; g.k = k;
     g.status = e->Status();
     PROF(e, kProfGemm, 2.0 * m * n * k, st, GemmBf16Mapped(g, st));
@@ -263,6 +266,11 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     if (!rc) rc = EncodeTcOperand(&e->map_Uf_mn, Uf, H, H, H, 1, 0);                                       // [k=H, n=H]
     if (!rc) rc = EncodeTcOperand(&e->map_Uiou_k, e->U_bf, H, 3 * H, 3 * H, 0, GemmBf16TileN(static_cast<int>(H)));  // [n=H, k=3H]
     if (!rc) rc = EncodeTcOperand(&e->map_Uf_k, Uf, H, H, H, 0, GemmBf16TileN(static_cast<int>(H)));       // [n=H, k=H]
+    const long long L = cfg->max_level_rows;
+    if (!rc) rc = EncodeTcOutput(&e->map_P, e->P, L, 3 * H, 3 * H, true);
+    if (!rc) rc = EncodeTcOutput(&e->map_Q, e->Q, L * K, H, H, true);
+    if (!rc) rc = EncodeTcOutput(&e->map_ds, e->ds, L, H, H, false);
+    if (!rc) rc = EncodeTcOutput(&e->map_dq, e->dq, L * K, H, H, false);
     if (rc) { delete e; return rc; }
   }
   cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), 2 * e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
@@ -406,8 +414,8 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
          LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, bt.child, nt, off, rows, H, K, st));
     const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
-    if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn))) return rc;
-    if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn))) return rc;
+    if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn, &e->map_P))) return rc;
+    if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn, &e->map_Q))) return rc;
     // read A (4H), P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
     PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (4 + 3 + K) + 4.0 * (K + 3 + K + 2)), st,
          LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, nt, off, rows, H, K, false, st));
@@ -454,8 +462,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
-    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k))) return rc;
-    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k))) return rc;
+    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k, &e->map_ds))) return rc;
+    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq))) return rc;
     PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
          LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
   }
@@ -504,10 +512,12 @@ extern "C" int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* 
   CAVS_REQUIRE(e && ms && work && launches && n_classes >= kProfCount, CAVS_ERR_BAD_ARG,
                "treelstm_profile_read: need arrays of at least 9 entries");
   for (int i = 0; i < n_classes; ++i) { ms[i] = 0; work[i] = 0; launches[i] = 0; }
+  const bool dump = std::getenv("CAVS_PROF_DUMP") != nullptr;   // one line per launch on stderr
   for (const auto& r : e->recs) {
     CAVS_CUDA(cudaEventSynchronize(r.b));
     float t = 0;
     CAVS_CUDA(cudaEventElapsedTime(&t, r.a, r.b));
+    if (dump) std::fprintf(stderr, "prof cls=%d work=%.4g ms=%.4f\n", r.cls, r.work, t);
     ms[r.cls] += t; work[r.cls] += r.work; launches[r.cls] += 1;
   }
   e->recs.clear();

@@ -78,7 +78,18 @@ __device__ __forceinline__ void Store(__nv_bfloat16* p, const Vec<V>& r) {
   }
 }
 
-__device__ __forceinline__ float Sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+// kFast = false: libm-accurate forms (the fp32 configurations must stay within 1e-5 of the
+// reference's 1/(1+expf(-x)) and tanhf, cavs/midend/runtime_compiler/expression.h:40-72).
+// kFast = true (bf16-GEMM configurations, 2e-2 contract): exp2-unit forms, ~1e-6 absolute error,
+// a fraction of the instructions -- the cell kernels are otherwise issue-bound, not HBM-bound.
+template <bool kFast>
+__device__ __forceinline__ float SigmoidT(float x) {
+  return kFast ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
+}
+template <bool kFast>
+__device__ __forceinline__ float TanhT(float x) {
+  return kFast ? 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f) : tanhf(x);
+}
 
 // S[t] = sum_c h(child_c(t)), HK[t,c] = h(child_c(t)); missing children contribute zeros.
 // Gather(Child=c) + Slice + Add of the reference (tree-lstm-cavs.cc:131-136).
@@ -111,6 +122,7 @@ __global__ void __launch_bounds__(kThreads)
 CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
         const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child, int n_total,
         int off, int rows, int H) {
+  constexpr bool kFast = sizeof(TP) == 2;
   const int hv = H / V;
   const int G = (3 + K) * H;
   const long long total = static_cast<long long>(rows) * hv;
@@ -129,9 +141,9 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restri
     Vec<V> gi, go, gu, cc, hh;
 #pragma unroll
     for (int e = 0; e < V; ++e) {
-      gi.v[e] = Sigmoid((ai.v[e] + pi.v[e]) + bi.v[e]);
-      go.v[e] = Sigmoid((ao.v[e] + po.v[e]) + bo.v[e]);
-      gu.v[e] = tanhf((au.v[e] + pu.v[e]) + bu.v[e]);
+      gi.v[e] = SigmoidT<kFast>((ai.v[e] + pi.v[e]) + bi.v[e]);
+      go.v[e] = SigmoidT<kFast>((ao.v[e] + po.v[e]) + bo.v[e]);
+      gu.v[e] = TanhT<kFast>((au.v[e] + pu.v[e]) + bu.v[e]);
       cc.v[e] = gi.v[e] * gu.v[e];
     }
     float* g = gates + t * G + j;
@@ -146,14 +158,14 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restri
         Vec<V> gf;
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          gf.v[e] = Sigmoid((af.v[e] + q.v[e]) + bf.v[e]);
+          gf.v[e] = SigmoidT<kFast>((af.v[e] + q.v[e]) + bf.v[e]);
           cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
         }
         Store<V>(g + (3 + c) * H, gf);
       }
     }
 #pragma unroll
-    for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * tanhf(cc.v[e]);
+    for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * TanhT<kFast>(cc.v[e]);
     Store<V>(g, gi); Store<V>(g + H, go); Store<V>(g + 2 * H, gu);
     Store<V>(state + t * 2 * H + j, hh);
     Store<V>(state + t * 2 * H + H + j, cc);
@@ -199,7 +211,7 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         const float dh = dOutv.v[e] + mh.v[e];
-        const float th = tanhf(cown.v[e]);
+        const float th = TanhT<sizeof(T) == 2>(cown.v[e]);
         const float d_o = dh * th;
         dc.v[e] = mc.v[e] + (dh * go.v[e]) * (1.0f - th * th);
         zi.v[e] = (dc.v[e] * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);

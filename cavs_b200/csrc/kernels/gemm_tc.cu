@@ -113,19 +113,22 @@ size_t GemmBf16ScratchBytes(int m, int n, int splits) {
 }
 
 int GemmBf16SplitsFor(int m, int n, int k) {
-  // The kernel is persistent over (tile, split) work items; pick the smallest split count whose
-  // work-item count fills whole waves of SMs noticeably better, keeping each split >= 32 K blocks.
-  const int bn = n > 128 ? 256 : 128;
+  // The kernel is persistent over (tile, split) work items.  Splitting K costs partial traffic, a
+  // plain-store epilogue and a reduce pass, so it is used only when the tile grid leaves more than a
+  // quarter of the SMs idle; then the smallest split count that fills whole waves to >= 90 % wins,
+  // keeping each split >= 32 K blocks.
+  const int bn = GemmBf16TileN(n);
   const long long tiles = static_cast<long long>((m + tc::kBM - 1) / tc::kBM) * ((n + bn - 1) / bn);
   const int nkb = (k + tc::kBK - 1) / tc::kBK;
   const int sms = SmCount();
   auto fill = [&](long long items) { return static_cast<double>(items) / (((items + sms - 1) / sms) * sms); };
+  if (fill(tiles) >= 0.75) return 1;
   int best = 1;
   double best_fill = fill(tiles);
-  for (int s = 2; s <= 32 && nkb / s >= 32; ++s) {
+  for (int s = 2; s <= 16 && nkb / s >= 32; ++s) {
     const double f = fill(tiles * s);
     if (f > best_fill + 0.04) { best = s; best_fill = f; }
-    if (best_fill > 0.95) break;
+    if (best_fill >= 0.9) break;
   }
   return best;
 }
