@@ -11,6 +11,7 @@
 // Determinism: dWc / dbc / the loss sum are accumulated per CTA in a fixed row order,
 // written to scratch, and reduced across CTAs in index order by a second kernel.
 #include <cstdint>
+#include <mutex>
 
 #include "abi_common.h"
 #include "kernels/cell.h"
@@ -277,3 +278,70 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
 }
 
 }  // namespace cavs_b200
+
+// ---------------------------------------------------------------------------------------------
+// Loss head for callers that cannot allocate device memory.
+//
+// Some hosts of this library own the GPU's memory outright: an embedding application that hands
+// the whole device to its own pool at start-up, or a step loop that forbids cudaMalloc / cudaFree
+// once it is running because both stall the device.  Such a caller can still pass inputs and
+// outputs it already owns, but it has nowhere to get the per-CTA partial buffer the loss head
+// reduces through.  cavs_fc_softmax_xent_static therefore keeps that buffer inside the library, in
+// a fixed-size __device__ array, and calls no allocating routine at all.
+//
+// The array is per device (every GPU that loads the library holds its kStaticScratchFloats * 4
+// bytes until the process exits) and is shared by every call on that device:
+//   * calls that may overlap on the GPU (different streams, different threads) race on it;
+//     issue them on one stream or order them yourself;
+//   * nothing in it has to start at zero -- each launch first overwrites every record the
+//     reduction then reads -- so the previous call's leftovers are harmless;
+//   * shapes whose partial records do not fit are rejected with CAVS_ERR_CAPACITY.
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+// device current) and caches it; make that first call before starting any stream capture.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kStaticMaxCtas = 296;                  // 148 SMs x 2 resident CTAs on B200
+constexpr int kStaticMaxStride = 10240;              // floats per CTA record: classes*hidden + classes + 1, padded
+constexpr size_t kStaticScratchFloats = static_cast<size_t>(kStaticMaxCtas) * kStaticMaxStride;   // 12.1 MB
+
+static __device__ __align__(256) float g_loss_head_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_static_ptr[kMaxDevices] = {};
+std::mutex g_static_mu;
+
+// Device address of g_loss_head_scratch on the current device (the host-side symbol is only a
+// handle; a kernel must be given this address, never &g_loss_head_scratch).
+int StaticScratch(float** out) {
+  int dev = 0;
+  CAVS_CUDA(cudaGetDevice(&dev));
+  CAVS_REQUIRE(dev >= 0 && dev < kMaxDevices, CAVS_ERR_UNSUPPORTED, "fc_softmax_xent_static: device ordinal above 63");
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    CAVS_CUDA(cudaGetSymbolAddress(&p, g_loss_head_scratch));
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return CAVS_OK;
+}
+
+}  // namespace
+
+extern "C" int cavs_fc_softmax_xent_static(float* loss, float* loss_sum, float* dH, float* dWc, float* dbc, const float* h,
+                                           long long h_pitch, const int32_t* label, const float* Wc, const float* bc, int rows,
+                                           int hidden, int classes, float inv_rows, void* stream) {
+  using namespace cavs_b200;
+  CAVS_REQUIRE(hidden > 0 && classes > 0, CAVS_ERR_BAD_ARG, "fc_softmax_xent_static: bad shape");
+  CAVS_REQUIRE(LossHeadScratchBytes(hidden, classes) <= kStaticScratchFloats * sizeof(float) &&
+                   PartialStride(classes, hidden) <= kStaticMaxStride,
+               CAVS_ERR_CAPACITY,
+               "fc_softmax_xent_static: classes*hidden + classes + 1 = " + std::to_string(classes * hidden + classes + 1) +
+                   " floats per partial record exceeds the built-in scratch (" + std::to_string(kStaticMaxStride) +
+                   " floats x " + std::to_string(kStaticMaxCtas) + " CTAs); use cavs_fc_softmax_xent with caller scratch");
+  float* scratch = nullptr;
+  if (int rc = StaticScratch(&scratch)) return rc;
+  return LaunchLossHead(loss, loss_sum, dH, dWc, dbc, h, h_pitch, label, Wc, bc, rows, hidden, classes, inv_rows, scratch,
+                        static_cast<cudaStream_t>(stream));
+}

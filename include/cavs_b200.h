@@ -179,6 +179,22 @@ CAVS_API size_t cavs_fc_softmax_xent_scratch_bytes(int hidden, int classes);
 CAVS_API int cavs_fc_softmax_xent(float* loss, float* loss_sum, float* dH, float* dWc, float* dbc, const float* h,
                                   long long h_pitch, const int32_t* label, const float* Wc, const float* bc, int rows,
                                   int hidden, int classes, float inv_rows, float* scratch, void* stream);
+/* The same loss head for callers that cannot allocate device memory -- for example a host program
+ * that gave the whole GPU to its own memory pool at start-up, or a running step loop in which
+ * cudaMalloc / cudaFree are forbidden because they stall the device.  It takes no scratch argument:
+ * the per-CTA partial records live in a fixed array inside the library (about 12 MB per GPU, held
+ * by every GPU that loads the library until the process exits), and the call uses no allocating
+ * routine.  This entry point has no counterpart in the reference.
+ *   Limit: classes*hidden + classes + 1 <= 10240 floats per record (e.g. 5 x 1024, 8 x 1024);
+ *   larger shapes return CAVS_ERR_CAPACITY -- use cavs_fc_softmax_xent with your own scratch.
+ *   Sharing: every call on a device uses the same array.  Calls that can overlap on the GPU
+ *   (different streams or threads) race; keep them on one stream or order them yourself.  Nothing
+ *   in the array needs to start at zero: each launch rewrites every record it later reads.
+ *   First call: the first call on each device looks up the array's device address (with that device
+ *   current) and caches it; make that call before you begin any stream capture. */
+CAVS_API int cavs_fc_softmax_xent_static(float* loss, float* loss_sum, float* dH, float* dWc, float* dbc, const float* h,
+                                         long long h_pitch, const int32_t* label, const float* Wc, const float* bc, int rows,
+                                         int hidden, int classes, float inv_rows, void* stream);
 /* out[j] = sum_r x[r,j] (fp32 or bf16 input), two-stage fixed-order reduction.  Replaces the
  * per-thread serial column loop used for bias gradients (cavs/backend/op_impl_elementwise.cuh:31-37). */
 CAVS_API size_t cavs_column_sum_scratch_bytes(int cols);
