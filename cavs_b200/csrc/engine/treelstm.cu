@@ -42,7 +42,8 @@ struct cavs_treelstm {
   size_t idx_ints = 0;
   uint8_t *X = nullptr, *S = nullptr, *HK = nullptr, *dA = nullptr, *ZF = nullptr;   // GEMM operands (fp32 or bf16)
   uint8_t *A = nullptr, *P = nullptr, *Q = nullptr;   // gate pre-activations: fp32, or bf16 in bf16 mode
-  float *gates = nullptr, *state = nullptr, *mailbox = nullptr;
+  uint8_t* gates = nullptr;                           // saved gates: fp32, or fp16 in bf16 mode
+  float *state = nullptr, *mailbox = nullptr;
   float *dOut = nullptr, *ds = nullptr, *dq = nullptr, *dX = nullptr, *loss = nullptr, *dB_tmp = nullptr;
   float* tail = nullptr;        // [0] loss sum, [1] status word (int)
   float *loss_scratch = nullptr, *col_scratch = nullptr, *emb_scratch = nullptr, *splitk_scratch = nullptr;
@@ -166,7 +167,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->A = w.Take<uint8_t>(N * 4 * H * elt);
   e->P = w.Take<uint8_t>(L * 3 * H * elt);
   e->Q = w.Take<uint8_t>(L * K * H * elt);
-  e->gates = w.Take<float>(N * (3 + K) * H);
+  e->gates = w.Take<uint8_t>(N * (3 + K) * H * elt);
   e->state = w.Take<float>(N * 2 * H);
   e->mailbox = w.Take<float>(N * 2 * H);
   e->dOut = w.Take<float>(N * H);
@@ -405,7 +406,7 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     if (l == 0) {
       // leaf rows: read A's i,o,u blocks (3H), write gates i,o,u (3H) and h|c (2H)
-      PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * 3 + 4.0 * (3 + 2)), st,
+      PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (3 + 3) + 4.0 * 2), st,
            LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, nt, off, rows, H, K, true, st));
       continue;
     }
@@ -417,7 +418,7 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn, &e->map_P))) return rc;
     if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn, &e->map_Q))) return rc;
     // read A (4H), P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
-    PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (4 + 3 + K) + 4.0 * (K + 3 + K + 2)), st,
+    PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (4 + 3 + K + 3 + K) + 4.0 * (K + 2)), st,
          LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, nt, off, rows, H, K, false, st));
   }
   (void)rc;
@@ -453,8 +454,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   for (int l = bt.n_levels - 1; l >= 0; --l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     // read dOut (H), mailbox (2H), gates ((3+K)H), own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
-    const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 3 + K + 1) + elt * 4)
-                                     : rows * H * (4.0 * (1 + 2 + 3 + K + 1 + K + K) + elt * (4 + K));
+    const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 1) + elt * (3 + 4))
+                                     : rows * H * (4.0 * (1 + 2 + 1 + K + K) + elt * (3 + K + 4 + K));
     PROF(e, kProfCellBwd, cell_bytes, st,
          LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->dOut, e->gates, e->state, bt.child, bt.parent, nt, off, rows, H,
                        K, l == 0, st));
@@ -547,7 +548,7 @@ extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_p
     case 1: *dev_ptr = e->loss; *bytes = n * sizeof(float); break;               // per-vertex loss
     case 2: *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;           // d(loss)/d(pushed h)
     case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
-    case 4: *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * sizeof(float); break;
+    case 4: *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
     default: return Fail(CAVS_ERR_BAD_ARG, "treelstm_peek: unknown array id");
   }
   return CAVS_OK;

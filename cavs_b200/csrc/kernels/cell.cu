@@ -18,6 +18,7 @@
 // (W's column blocks, tree-lstm-cavs.cc:143-148); the bias is i,f,u,o (:120-123);
 // saved gates are i,o,u,f_0..f_{K-1}.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <cstdint>
 
@@ -57,6 +58,22 @@ __device__ __forceinline__ Vec<V> LoadF(const __nv_bfloat16* p) {
   return r;
 }
 template <int V>
+__device__ __forceinline__ Vec<V> LoadF(const __half* p) {
+  Vec<V> r;
+  if constexpr (V == 4) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = b.x; r.v[3] = b.y;
+  } else if constexpr (V == 2) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(p));
+    r.v[0] = a.x; r.v[1] = a.y;
+  } else {
+    r.v[0] = __half2float(*p);
+  }
+  return r;
+}
+template <int V>
 __device__ __forceinline__ Vec<V> Zero() { Vec<V> r; for (int i = 0; i < V; ++i) r.v[i] = 0.0f; return r; }
 
 template <int V>
@@ -77,6 +94,25 @@ __device__ __forceinline__ void Store(__nv_bfloat16* p, const Vec<V>& r) {
     *p = __float2bfloat16_rn(r.v[0]);
   }
 }
+
+template <int V>
+__device__ __forceinline__ void Store(__half* p, const Vec<V>& r) {
+  if constexpr (V == 4) {
+    __half2 a = __floats2half2_rn(r.v[0], r.v[1]), b = __floats2half2_rn(r.v[2], r.v[3]);
+    uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else if constexpr (V == 2) {
+    *reinterpret_cast<__half2*>(p) = __floats2half2_rn(r.v[0], r.v[1]);
+  } else {
+    *p = __float2half_rn(r.v[0]);
+  }
+}
+
+// Saved gates (values in [-1, 1]) are kept in fp16 in the bf16-GEMM configurations: 11 mantissa
+// bits cost ~5e-4 relative in the backward products and halve the largest forward-to-backward
+// tensor; the fp32 configurations keep fp32 gates.
+template <typename TP> struct GateType { using type = float; };
+template <> struct GateType<__nv_bfloat16> { using type = __half; };
 
 // kFast = false: libm-accurate forms (the fp32 configurations must stay within 1e-5 of the
 // reference's 1/(1+expf(-x)) and tanhf, cavs/midend/runtime_compiler/expression.h:40-72).
@@ -119,7 +155,7 @@ GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ st
 // TP: storage type of the gate pre-activations A, P, Q (fp32, or bf16 written by the GEMM epilogue).
 template <typename TP, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
-CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
+CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
         const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child, int n_total,
         int off, int rows, int H) {
   constexpr bool kFast = sizeof(TP) == 2;
@@ -146,7 +182,7 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restri
       gu.v[e] = TanhT<kFast>((au.v[e] + pu.v[e]) + bu.v[e]);
       cc.v[e] = gi.v[e] * gu.v[e];
     }
-    float* g = gates + t * G + j;
+    typename GateType<TP>::type* g = gates + t * G + j;
     // Leaves have no child cell state: their forget gates multiply zeros in the forward pass and
     // receive a zero gradient in the backward pass, so they are neither computed nor stored.
     if (!kLeaf) {
@@ -181,7 +217,7 @@ CellFwd(float* __restrict__ state, float* __restrict__ gates, const TP* __restri
 template <typename T, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
 CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, float* __restrict__ dB_part,
-        const float* __restrict__ dOut, const float* __restrict__ gates, const float* __restrict__ state,
+        const float* __restrict__ dOut, const typename GateType<T>::type* __restrict__ gates, const float* __restrict__ state,
         const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H) {
   __shared__ float fold[kThreads * 4 * V];
   const int tpr = H / V;
@@ -204,7 +240,7 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
       const Vec<V> mh = has_parent ? LoadF<V>(mailbox + t * 2 * H + j) : Zero<V>();
       const Vec<V> mc = has_parent ? LoadF<V>(mailbox + t * 2 * H + H + j) : Zero<V>();
       const Vec<V> dOutv = LoadF<V>(dOut + t * H + j);
-      const float* g = gates + t * G + j;
+      const typename GateType<T>::type* g = gates + t * G + j;
       const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
       const Vec<V> cown = LoadF<V>(state + t * 2 * H + H + j);
       Vec<V> zi, zo, zu, dc, zfs = Zero<V>();
@@ -337,7 +373,7 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
   return CAVS_OK;
 }
 
-int LaunchCellFwd(float* state, float* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
+int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st) {
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
@@ -347,12 +383,12 @@ int LaunchCellFwd(float* state, float* gates, const void* A, const void* P, cons
     if (preact_bf16) {
       using TP = __nv_bfloat16;
       auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
-      if (leaf) CellFwd<TP, K, V, true><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
-      else CellFwd<TP, K, V, false><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
+      if (leaf) CellFwd<TP, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, n_total, off, rows, H);
+      else CellFwd<TP, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, n_total, off, rows, H);
     } else {
       auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
-      if (leaf) CellFwd<float, K, V, true><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
-      else CellFwd<float, K, V, false><<<grid, kThreads, 0, st>>>(state, gates, a, p, q, bias, child, n_total, off, rows, H);
+      if (leaf) CellFwd<float, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, n_total, off, rows, H);
+      else CellFwd<float, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, n_total, off, rows, H);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
@@ -366,7 +402,7 @@ int CellBwdGrid(int rows, int H) {
   return static_cast<int>(std::max(1LL, std::min<long long>(want, CellBwdMaxGrid())));
 }
 
-int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const float* gates,
+int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
@@ -378,12 +414,12 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
   DISPATCH_KV(K, v, {
     if (bf16) {
       auto* d = static_cast<__nv_bfloat16*>(dA); auto* z = static_cast<__nv_bfloat16*>(ZF);
-      if (leaf) CellBwd<__nv_bfloat16, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
-      else CellBwd<__nv_bfloat16, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
+      if (leaf) CellBwd<__nv_bfloat16, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const __half*>(gates), state, child, parent, n_total, off, rows, H);
+      else CellBwd<__nv_bfloat16, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const __half*>(gates), state, child, parent, n_total, off, rows, H);
     } else {
       auto* d = static_cast<float*>(dA); auto* z = static_cast<float*>(ZF);
-      if (leaf) CellBwd<float, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
-      else CellBwd<float, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, gates, state, child, parent, n_total, off, rows, H);
+      if (leaf) CellBwd<float, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const float*>(gates), state, child, parent, n_total, off, rows, H);
+      else CellBwd<float, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const float*>(gates), state, child, parent, n_total, off, rows, H);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_bwd");

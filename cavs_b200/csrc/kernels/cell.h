@@ -16,14 +16,15 @@ namespace cavs_b200 {
 int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const int32_t* child, int n_total, int off,
                        int rows, int H, int K, cudaStream_t st);
 // A, P, Q are fp32, or bf16 when preact_bf16 is set.
-int LaunchCellFwd(float* state, float* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
+// gates: fp32, or fp16 when preact_bf16 / bf16 is set (the bf16-GEMM configurations).
+int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st);
 // dB_part (optional): [CellBwdMaxGrid(), 4H] fp32, zeroed by the caller before the first level of a
 // backward sweep; every launch adds its per-CTA column sums of (zi, zo, zu, sum zf) into it, and a
 // final column sum over its rows gives the bias gradient.  Needs CellBwdFusesBias(H).
 int CellBwdMaxGrid();
 bool CellBwdFusesBias(int H);
-int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const float* gates,
+int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st);
 int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,

@@ -75,7 +75,7 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
         if (kIters > 0) {
           float4 hv[kIters > 0 ? kIters : 1];
 #pragma unroll
-          for (int it = 0; it < kIters; ++it) hv[it] = __ldcs(reinterpret_cast<const float4*>(hr + lane * 4 + it * 128));
+          for (int it = 0; it < kIters; ++it) hv[it] = *reinterpret_cast<const float4*>(hr + lane * 4 + it * 128);
 #pragma unroll
           for (int it = 0; it < kIters; ++it) {
 #pragma unroll

@@ -138,15 +138,16 @@ CAVS_API int cavs_gather_child_h(void* S, void* HK, int bf16, const float* state
  * P [rows,3H] = (sum h).U_iou, Q [rows,n_slots,H] = h_c.U_f, bias [4H] (i,f,u,o).  Writes
  * gates [n_total,(3+n_slots)H] and state [n_total,2H].  leaf != 0: no children (P, Q unused, the
  * forget gates are neither computed nor stored).  preact_bf16 != 0: A, P, Q hold bf16 (the GEMM
- * epilogue's rounded output), else fp32. */
-CAVS_API int cavs_treelstm_cell_fwd(float* state, float* gates, const void* A, const void* P, const void* Q, int preact_bf16,
+ * epilogue's rounded output) and gates are stored as fp16; else both are fp32. */
+CAVS_API int cavs_treelstm_cell_fwd(float* state, void* gates, const void* A, const void* P, const void* Q, int preact_bf16,
                                     const float* bias, const int32_t* child, int n_total, int off, int rows, int hidden,
                                     int n_slots, int leaf, void* stream);
 /* Fused gate-gradient backward of the cell: reads d(pushed h) dOut [n_total,H], the parent's
  * d(h|c) from mailbox [n_total,2H] (zeros for roots), saved gates and states; writes
- * dA [n_total,4H] (zi|zo|zu|sum zf), ZF [n_total,n_slots,H] (fp32 or bf16) and d(c_child) into the
+ * dA [n_total,4H] (zi|zo|zu|sum zf), ZF [n_total,n_slots,H] (fp32, or bf16 with fp16 gates when bf16 != 0)
+ * and d(c_child) into the
  * children's mailbox rows (Scatter(Child=c), cavs/backend/op_decl_graphop.cc:25-41). */
-CAVS_API int cavs_treelstm_cell_bwd(void* dA, void* ZF, int bf16, float* mailbox, const float* dOut, const float* gates,
+CAVS_API int cavs_treelstm_cell_bwd(void* dA, void* ZF, int bf16, float* mailbox, const float* dOut, const void* gates,
                                     const float* state, const int32_t* child, const int32_t* parent, int n_total, int off,
                                     int rows, int hidden, int n_slots, int leaf, void* stream);
 /* mailbox[child_c(t)].h = ds[b] + dq[b,c]: the child-state gradient scatter. */
