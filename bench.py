@@ -225,11 +225,18 @@ def main():
             dist.all_reduce(eng.grads)
         eng.adagrad(acc, wl["lr"])
 
+    host_ms = [0.0, 0.0, 0]   # schedule ms, pack + upload-enqueue ms, calls
+
     def stage(i):
         """Host scheduling of batch i and the pinned upload of its tables (staged; forward() promotes it)."""
         par, tok, lab = (t.numpy() for t in pinned[i % POOL])
+        t0 = time.perf_counter()
         host_sched.load(par)
+        t1 = time.perf_counter()
         eng.load_batch(host_sched, tok, lab, loss_rows=pool[i % POOL][3])
+        host_ms[0] += (t1 - t0) * 1e3
+        host_ms[1] += (time.perf_counter() - t1) * 1e3
+        host_ms[2] += 1
 
     def e2e_loop(steps):
         # Software-pipelined like a data loader: while the GPU runs step i the host schedules batch
@@ -327,7 +334,8 @@ def main():
                             embed=wl["embed"], vocab=wl["vocab"], classes=wl["classes"], leaves=[wl["leaf_lo"], wl["leaf_hi"]],
                             vertices_per_gpu=int(scheds[0].n_total), levels=int(scheds[0].n_levels), optimizer="adagrad",
                             parallelism=f"dp{world}", l2="working set per step (tens of GB) exceeds L2; no flush needed"),
-                e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8),
+                e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8,
+                         host_schedule_ms=host_ms[0] / max(host_ms[2], 1), host_pack_ms=host_ms[1] / max(host_ms[2], 1)),
                 gpu_launches=int(launches), loss_sum=loss_dev, clocks=clocks, roofline=roofline, kernel_classes=classes)
     if not args.no_cpu_baseline:
         rate, secs = cpu_baseline_sample(wl, args.sample_trees)

@@ -3,8 +3,12 @@
 //
 // Replaces GraphStatement::Run / GraphGradStatement::Run (cavs/midend/statement.cc:43-123)
 // and the per-op prologue ExprStatement::Run (statement.cc:8-41).  Differences that matter:
-//   * the input projection x.W does not depend on children, so it is one GEMM over all
-//     vertices before the loop instead of one per level (tree-lstm-cavs.cc:146);
+//   * the input projection x.W does not depend on children and depends on a vertex only through
+//     its token (x is an embedding row), so it is one GEMM over the batch's DISTINCT tokens before
+//     the loop -- (Emb.W)[tok] instead of Emb[tok].W per vertex per level (tree-lstm-cavs.cc:139-146);
+//     the cell reads its row through a per-vertex index.  Symmetrically, d(pre-activation) rows are
+//     summed per token before the input-weight and embedding gradients, which turns the three
+//     largest GEMMs of a step into one segmented row sum plus GEMMs over distinct tokens;
 //   * level 0 holds only leaves, whose recurrent GEMMs multiply zero rows in the reference
 //     (op_impl_graphop.cu:77-86); they are skipped, which is exact;
 //   * per level the forward pass is 4 launches (gather, 2 GEMMs, fused cell) and the
@@ -41,6 +45,7 @@ struct cavs_treelstm {
   int32_t* h_idx = nullptr;
   size_t idx_ints = 0;
   uint8_t *X = nullptr, *S = nullptr, *HK = nullptr, *dA = nullptr, *ZF = nullptr;   // GEMM operands (fp32 or bf16)
+  uint8_t* dAtok = nullptr;     // [distinct tokens, 4H] per-token sums of dA (GEMM operand precision)
   uint8_t *A = nullptr, *P = nullptr, *Q = nullptr;   // gate pre-activations: fp32, or bf16 in bf16 mode
   uint8_t* gates = nullptr;                           // saved gates: fp32, or fp16 in bf16 mode
   float *state = nullptr, *mailbox = nullptr;
@@ -60,11 +65,16 @@ struct cavs_treelstm {
     int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
     std::vector<int32_t> level_off;
     int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
-            *seg_first_chunk = nullptr, *seg_tok = nullptr;
+            *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr;
   };
   Batch slot[2];
   int active = -1, staged = -1;
-  std::vector<int32_t> bucket;
+  // The table upload runs on its own stream so it overlaps the step in flight: copied[s] marks the
+  // upload into slot s, slot_done[s] the end of the last backward pass that read slot s.
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t copied[2] = {nullptr, nullptr}, slot_done[2] = {nullptr, nullptr};
+  bool slot_used[2] = {false, false};
+  std::vector<int32_t> bucket, slot_of_token;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
   bool prof_on = false;
   std::vector<cudaEvent_t> ev_pool;
@@ -138,7 +148,7 @@ size_t MaxSegments(const cavs_treelstm_config& c) { return std::min<size_t>(c.ma
 size_t MaxChunks(const cavs_treelstm_config& c) { return MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
-  return (c.n_slots + 4) * n + (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
+  return (c.n_slots + 5) * n + (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -159,12 +169,14 @@ size_t Carve(cavs_treelstm* e, void* base) {
   const size_t elt = c.gemm_bf16 ? 2 : 4;
   Carver w(base);
   e->d_idx = w.Take<int32_t>(2 * IdxInts(c));
-  e->X = w.Take<uint8_t>(N * E * elt);
+  const size_t T = MaxSegments(c);   // distinct tokens per batch
+  e->X = w.Take<uint8_t>(T * E * elt);
   e->S = w.Take<uint8_t>(N * H * elt);
   e->HK = w.Take<uint8_t>(N * K * H * elt);
   e->dA = w.Take<uint8_t>(N * 4 * H * elt);
   e->ZF = w.Take<uint8_t>(N * K * H * elt);
-  e->A = w.Take<uint8_t>(N * 4 * H * elt);
+  e->A = w.Take<uint8_t>(T * 4 * H * elt);
+  e->dAtok = w.Take<uint8_t>(T * 4 * H * elt);
   e->P = w.Take<uint8_t>(L * 3 * H * elt);
   e->Q = w.Take<uint8_t>(L * K * H * elt);
   e->gates = w.Take<uint8_t>(N * (3 + K) * H * elt);
@@ -173,13 +185,13 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->dOut = w.Take<float>(N * H);
   e->ds = w.Take<float>(L * H);
   e->dq = w.Take<float>(L * K * H);
-  e->dX = w.Take<float>(N * E);
+  e->dX = w.Take<float>(T * E);
   e->loss = w.Take<float>(N);
   e->dB_tmp = w.Take<float>(CellBwdFusesBias(c.hidden) ? static_cast<size_t>(CellBwdMaxGrid()) * 4 * H : 4 * H);
   e->tail = w.Take<float>(4);
   e->loss_scratch = w.Take<float>(LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
   e->col_scratch = w.Take<float>(ColumnSumScratchBytes(4 * c.hidden) / sizeof(float));
-  e->emb_scratch = w.Take<float>(MaxChunks(c) * E);
+  e->emb_scratch = w.Take<float>(MaxChunks(c) * 4 * H);
   e->splitk_bytes = SplitKBytes(c);
   e->splitk_scratch = w.Take<float>(e->splitk_bytes / sizeof(float));
   e->W_bf = w.Take<uint8_t>(c.gemm_bf16 ? static_cast<size_t>(E) * 4 * H * 2 : 0);
@@ -279,7 +291,12 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     delete e;
     return Fail(CAVS_ERR_CUDA, std::string("treelstm_create: pinned staging: ") + cudaGetErrorString(err));
   }
-  err = cudaMemset(e->tail, 0, 4 * sizeof(float));
+  if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking);
+  for (int i = 0; i < 2 && err == cudaSuccess; ++i) {
+    err = cudaEventCreateWithFlags(&e->copied[i], cudaEventDisableTiming);
+    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->slot_done[i], cudaEventDisableTiming);
+  }
+  if (err == cudaSuccess) err = cudaMemset(e->tail, 0, 4 * sizeof(float));
   if (err != cudaSuccess) {
     cudaFreeHost(e->h_idx);
     delete e;
@@ -293,6 +310,11 @@ extern "C" void cavs_treelstm_destroy(cavs_treelstm* e) {
   if (!e) return;
   if (e->h_idx) cudaFreeHost(e->h_idx);
   for (cudaEvent_t ev : e->ev_pool) cudaEventDestroy(ev);
+  for (int i = 0; i < 2; ++i) {
+    if (e->copied[i]) cudaEventDestroy(e->copied[i]);
+    if (e->slot_done[i]) cudaEventDestroy(e->slot_done[i]);
+  }
+  if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
   delete e;
 }
 
@@ -329,6 +351,8 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
                    std::to_string(e->cfg.max_level_rows));
   const int which = e->active < 0 ? 0 : 1 - e->active;
   cavs_treelstm::Batch& bt = e->slot[which];
+  // The pinned half of this slot is free once its previous upload has finished.
+  CAVS_CUDA(cudaEventSynchronize(e->copied[which]));
   bt.n = n; bt.n_total = nt; bt.n_levels = sch.n_levels();
   bt.loss_rows = loss_rows > 0 ? loss_rows : std::max(n, 1);
   bt.level_off = sch.level_off();
@@ -343,6 +367,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   int32_t* h_tok = view(nt, &bt.tok);
   int32_t* h_label = view(nt, &bt.label);
   int32_t* h_order = view(nt, &bt.order);
+  int32_t* h_slot = view(nt, &bt.tok_slot);
   std::memcpy(h_child, sch.child_t().data(), sizeof(int32_t) * K * nt);
   std::memcpy(h_parent, sch.parent_t().data(), sizeof(int32_t) * nt);
   const int32_t* t2j = sch.t2j().data();
@@ -366,18 +391,27 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
   CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
   int si = 0, ci = 0;
+  e->slot_of_token.resize(V);
   for (int v = 0; v < V; ++v) {
     const int b0 = e->bucket[v], b1 = e->bucket[v + 1];
     if (b0 == b1) continue;
+    e->slot_of_token[v] = si;
     h_seg_tok[si] = v;
     h_seg_first[si++] = ci;
     for (int b = b0; b < b1; b += kEmbedChunk) h_chunk_off[ci++] = b;
   }
   h_seg_first[si] = ci;
   h_chunk_off[ci] = n;
-  for (int t = 0; t < n; ++t) h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
+  for (int t = 0; t < n; ++t) {
+    h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
+    h_slot[t] = e->slot_of_token[h_tok[t]];
+  }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
-  CAVS_CUDA(cudaMemcpyAsync(d, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  // The device half is free once the last backward pass that read it has finished.
+  (void)stream;
+  if (e->slot_used[which]) CAVS_CUDA(cudaStreamWaitEvent(e->copy_stream, e->slot_done[which], 0));
+  CAVS_CUDA(cudaMemcpyAsync(d, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, e->copy_stream));
+  CAVS_CUDA(cudaEventRecord(e->copied[which], e->copy_stream));
   e->staged = which;
   return CAVS_OK;
 }
@@ -385,29 +419,35 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
 extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_forward: parameters not bound");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (e->staged >= 0) { e->active = e->staged; e->staged = -1; }
+  if (e->staged >= 0) {
+    e->active = e->staged;
+    e->staged = -1;
+    CAVS_CUDA(cudaStreamWaitEvent(st, e->copied[e->active], 0));   // tables of this batch are in place
+  }
   CAVS_REQUIRE(e->active >= 0, CAVS_ERR_BAD_ARG, "treelstm_forward: no batch loaded");
   const cavs_treelstm::Batch& bt = e->slot[e->active];
   const int n = bt.n, nt = bt.n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots;
   if (n == 0) return CAVS_OK;
   const float* Emb = e->params;
-  const void* W = e->bf16 ? static_cast<const void*>(e->W_bf) : e->params + e->OffW();
+  const uint8_t* W = e->bf16 ? e->W_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffW());
   const uint8_t* U = e->bf16 ? e->U_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffU());
   const void* U_iou = U;
   const void* U_f = U + static_cast<size_t>(3) * H * H * e->elt;
   const float* B = e->params + e->OffB();
   int rc;
   const double elt = static_cast<double>(e->elt);
-  PROF(e, kProfEmbedFwd, static_cast<double>(n) * (4 + 4.0 * E + elt * E), st,
-       LaunchEmbedFwd(e->X, e->bf16, Emb, bt.tok, n, E, e->cfg.vocab, st));
+  const int n_tok = bt.n_seg;        // distinct tokens of the batch
+  // X = Emb[distinct tokens]; A = X.W: one row per token, shared by every vertex carrying it.
+  PROF(e, kProfEmbedFwd, static_cast<double>(n_tok) * (4 + 4.0 * E + elt * E), st,
+       LaunchEmbedFwd(e->X, e->bf16, Emb, bt.seg_tok, n_tok, E, e->cfg.vocab, st));
   const int pre = e->bf16 ? 2 : 0;   // pre-activations are stored in the GEMM operand precision
-  if ((rc = Gemm(e, e->A, 4 * H, pre, e->X, E, false, W, 4 * H, false, n, 4 * H, E, false, st))) return rc;
+  if ((rc = Gemm(e, e->A, 4 * H, pre, e->X, E, false, W, 4 * H, false, n_tok, 4 * H, E, false, st))) return rc;
   for (int l = 0; l < bt.n_levels; ++l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     if (l == 0) {
-      // leaf rows: read A's i,o,u blocks (3H), write gates i,o,u (3H) and h|c (2H)
-      PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (3 + 3) + 4.0 * 2), st,
-           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, nt, off, rows, H, K, true, st));
+      // leaf rows: read the token row's i,o,u blocks (3H) + its index, write gates i,o,u (3H) and h|c (2H)
+      PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (3 + 3) + 4.0 * 2) + 4), st,
+           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, true, st));
       continue;
     }
     // read K child h rows (fp32) + K indices, write S and HK
@@ -417,9 +457,9 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
     if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn, &e->map_P))) return rc;
     if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn, &e->map_Q))) return rc;
-    // read A (4H), P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
-    PROF(e, kProfCellFwd, static_cast<double>(rows) * H * (elt * (4 + 3 + K + 3 + K) + 4.0 * (K + 2)), st,
-         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, nt, off, rows, H, K, false, st));
+    // read the token row (4H) + index, P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
+    PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (4 + 3 + K + 3 + K) + 4.0 * (K + 2)) + 4), st,
+         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, false, st));
   }
   (void)rc;
   return CAVS_OK;
@@ -436,7 +476,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     CAVS_CUDA(cudaMemsetAsync(g, 0, e->ParamCount() * sizeof(float), st));
     return CAVS_OK;
   }
-  const void* W = e->bf16 ? static_cast<const void*>(e->W_bf) : e->params + e->OffW();
+  const uint8_t* W = e->bf16 ? e->W_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffW());
   const uint8_t* U = e->bf16 ? e->U_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffU());
   const void* U_iou = U;
   const void* U_f = U + static_cast<size_t>(3) * H * H * e->elt;
@@ -453,12 +493,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   if (fuse_bias) CAVS_CUDA(cudaMemsetAsync(e->dB_tmp, 0, dB_rows * 4 * H * sizeof(float), st));
   for (int l = bt.n_levels - 1; l >= 0; --l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
-    // read dOut (H), mailbox (2H), gates ((3+K)H), own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
+    // read dOut (H), mailbox (2H), gates, own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
     const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 1) + elt * (3 + 4))
                                      : rows * H * (4.0 * (1 + 2 + 1 + K + K) + elt * (3 + K + 4 + K));
     PROF(e, kProfCellBwd, cell_bytes, st,
-         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->dOut, e->gates, e->state, bt.child, bt.parent, nt, off, rows, H,
-                       K, l == 0, st));
+         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->dOut, e->gates, e->state, bt.child,
+                       bt.parent, nt, off, rows, H, K, l == 0, st));
     if (l == 0) break;
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
@@ -468,10 +508,9 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
          LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
   }
-  // Deferred gradients over all rows at once.
+  // Deferred gradients, one pass per weight over all rows (cavs/midend/batch_weight_updater.h:10-85).
   const int off1 = bt.n_levels > 1 ? bt.level_off[1] : n;   // first internal row
   const int n_int = n - off1;
-  if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dA, 4 * H, false, E, 4 * H, n, true, st))) return rc;
   float* dU = g + e->OffU();
   if (n_int > 0) {
     const uint8_t* S1 = e->S + static_cast<size_t>(off1) * H * e->elt;
@@ -491,13 +530,19 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     PROF(e, kProfColumnSum, static_cast<double>(n) * 4 * H * elt, st,
          LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
   }
-  // dX = dA W^T, then the segmented embedding gradient.
-  if ((rc = Gemm(e, e->dX, E, 0, e->dA, 4 * H, false, W, 4 * H, true, n, E, 4 * H, false, st))) return rc;
+  // Input weights and embedding: dA rows are first summed per distinct token (fixed order), then
+  //   dW = X^T dAtok  and  dEmb[token] = dAtok W^T  run over tokens, not vertices.
+  const int n_tok = bt.n_seg;
+  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
+       LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
+                             bt.seg_first_chunk, n_tok, e->emb_scratch, st));
+  if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
+  if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
   CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
-  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * E) + 4.0 * E * bt.n_seg, st,
-       LaunchEmbedBwd(g, e->dX, bt.order, nullptr, bt.chunk_off, bt.n_chunks, bt.seg_first_chunk, bt.seg_tok, bt.n_seg,
-                      e->emb_scratch, E, st));
+  if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
   (void)rc;
+  CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
+  e->slot_used[e->active] = true;
   return CAVS_OK;
 }
 

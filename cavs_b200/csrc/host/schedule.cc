@@ -1,97 +1,186 @@
 #include "host/schedule.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
+#include <thread>
 
 #include "abi_common.h"
 
 namespace cavs_b200 {
 
+namespace {
+
+// Runs fn(begin, end) over [0, n) on up to `threads` host threads (the caller's included).
+template <typename F>
+void ParallelFor(int n, int threads, F fn) {
+  threads = std::max(1, std::min(threads, n / 64 + 1));
+  if (threads == 1) { fn(0, n); return; }
+  std::vector<std::thread> pool;
+  const int chunk = (n + threads - 1) / threads;
+  for (int t = 1; t < threads; ++t) {
+    const int b = t * chunk, e = std::min(n, b + chunk);
+    if (b < e) pool.emplace_back([=] { fn(b, e); });
+  }
+  fn(0, std::min(n, chunk));
+  for (auto& th : pool) th.join();
+}
+
+int HostThreads() {
+  static int n = [] {
+    const char* env = std::getenv("CAVS_HOST_THREADS");
+    if (env) return std::max(1, std::atoi(env));
+    const unsigned hw = std::thread::hardware_concurrency();
+    return static_cast<int>(std::max(1u, std::min(hw, 8u)));
+  }();
+  return n;
+}
+
+}  // namespace
+
+// The reference discovers levels by one global wavefront over all samples
+// (graph_scheduler.cc:169-258).  Its order has a structure that makes the work separable: level 0
+// lists vertices in ascending global id, i.e. sample by sample, and scanning a sample-major level
+// discovers the next level sample by sample too -- so EVERY level is the concatenation, over
+// samples, of that sample's own wavefront order.  Each sample (a tree of at most max_len vertices,
+// cache resident) is therefore scheduled independently and in parallel; a prefix sum over
+// per-sample level counts then places it in the global order.  Output is identical to the
+// sequential wavefront.
 int LevelSchedule::Load(const int32_t* parents, int batch, int max_len, int n_slots, std::string* err) {
   if (parents == nullptr || batch < 0 || max_len <= 0 || n_slots < 1 || n_slots > kMaxSlots) {
     *err = "schedule: bad argument (parents null, batch < 0, max_len <= 0 or slots outside 1..4)";
     return CAVS_ERR_BAD_ARG;
   }
   batch_ = batch; max_len_ = max_len; n_slots_ = n_slots;
+  const int threads = HostThreads();
   sample_off_.assign(static_cast<size_t>(batch) + 1, 0);
-  // Pass 1: sample lengths.  The root carries -1 and must be the sample's last vertex.
-  for (int i = 0; i < batch; ++i) {
-    const int32_t* row = parents + static_cast<size_t>(i) * max_len;
-    const int32_t* end = std::find(row, row + max_len, -1);
-    if (end == row + max_len) {
-      *err = "schedule: sample " + std::to_string(i) + " has no -1 terminator";
-      return CAVS_ERR_BAD_GRAPH;
+
+  // Phase A (parallel over samples): validate, run the sample's wavefront, record for every local
+  // vertex its level and its position inside the sample's list of that level.
+  // local_[i*max_len + j] = level << 16 | position  (max_len <= 65535 enforced below), -1 if unscheduled.
+  if (max_len > 65535) { *err = "schedule: max_len above 65535"; return CAVS_ERR_UNSUPPORTED; }
+  local_.assign(static_cast<size_t>(batch) * max_len, -1);
+  sample_len_.assign(batch, 0);
+  sample_levels_.assign(batch, 0);
+  // per-sample level counts, laid out [batch][max_len] lazily: only the first sample_levels_[i] entries are used
+  level_cnt_.assign(static_cast<size_t>(batch) * max_len, 0);
+  std::vector<int> first_error(batch, 0);
+  ParallelFor(batch, threads, [&](int b0, int b1) {
+    std::vector<int32_t> nchild(max_len), hits(max_len), cur(max_len), nxt(max_len);
+    for (int i = b0; i < b1; ++i) {
+      const int32_t* row = parents + static_cast<size_t>(i) * max_len;
+      const int32_t* end = std::find(row, row + max_len, -1);
+      if (end == row + max_len) { first_error[i] = 1; continue; }        // no terminator
+      const int len = static_cast<int>(end - row) + 1;
+      sample_len_[i] = len;
+      std::fill(nchild.begin(), nchild.begin() + len, 0);
+      std::fill(hits.begin(), hits.begin() + len, 0);
+      bool bad = false;
+      for (int j = 0; j + 1 < len; ++j) {
+        const int p = row[j];
+        if (p < 0 || p >= len || p == j) { first_error[i] = 2 + (j << 4); bad = true; break; }
+        if (++nchild[p] > n_slots) { first_error[i] = 3 + (p << 4); bad = true; break; }
+      }
+      if (bad) continue;
+      int32_t* loc = local_.data() + static_cast<size_t>(i) * max_len;
+      int32_t* cnt = level_cnt_.data() + static_cast<size_t>(i) * max_len;
+      int n_cur = 0, placed = 0, level = 0;
+      for (int j = 0; j + 1 < len; ++j)            // the root (j = len-1) has no parent: never on level 0
+        if (nchild[j] == 0) cur[n_cur++] = j;
+      while (n_cur > 0) {
+        cnt[level] = n_cur;
+        int n_nxt = 0;
+        for (int b = 0; b < n_cur; ++b) {
+          const int v = cur[b];
+          loc[v] = (level << 16) | b;
+          if (v + 1 < len) {                       // every vertex but the root has a parent
+            const int p = row[v];
+            if (++hits[p] == nchild[p]) nxt[n_nxt++] = p;
+          }
+        }
+        placed += n_cur;
+        cur.swap(nxt);
+        n_cur = n_nxt;
+        ++level;
+      }
+      sample_levels_[i] = level;
+      // A single-vertex sample never executes (graph_scheduler.cc:180); anything else left over is a cycle.
+      if (placed != len && !(len == 1)) first_error[i] = 4;
     }
-    sample_off_[i + 1] = sample_off_[i] + static_cast<int32_t>(end - row) + 1;
+  });
+  for (int i = 0; i < batch; ++i) {
+    if (first_error[i] == 0) continue;
+    const int code = first_error[i] & 15, where = first_error[i] >> 4;
+    if (code == 1) *err = "schedule: sample " + std::to_string(i) + " has no -1 terminator";
+    else if (code == 2) *err = "schedule: sample " + std::to_string(i) + " vertex " + std::to_string(where) + " has a parent index outside the sample";
+    else if (code == 3) *err = "schedule: sample " + std::to_string(i) + " vertex " + std::to_string(where) + " has more than " + std::to_string(n_slots) + " children";
+    else *err = "schedule: sample " + std::to_string(i) + " contains a cycle (a vertex never becomes ready)";
+    return CAVS_ERR_BAD_GRAPH;
+  }
+
+  // Phase B (serial, O(batch * depth)): global sizes and, per sample and level, the first global
+  // position of that sample's block.
+  int n_levels = 0;
+  for (int i = 0; i < batch; ++i) {
+    sample_off_[i + 1] = sample_off_[i] + sample_len_[i];
+    n_levels = std::max(n_levels, sample_levels_[i]);
   }
   const int n = n_total_ = sample_off_[batch];
   const size_t nz = static_cast<size_t>(n);
-  parent_g_.assign(nz, -1);
-  nchild_g_.assign(nz, 0);
-  child_g_.assign(nz * n_slots, -1);
-  // Pass 2: adjacency in global-id space; children land in ascending id order.
+  level_off_.assign(static_cast<size_t>(n_levels) + 1, 0);
   for (int i = 0; i < batch; ++i) {
-    const int32_t* row = parents + static_cast<size_t>(i) * max_len;
-    const int base = sample_off_[i], len = sample_off_[i + 1] - base;
-    for (int j = 0; j + 1 < len; ++j) {
-      const int p = row[j];
-      if (p < 0 || p >= len || p == j) {
-        *err = "schedule: sample " + std::to_string(i) + " vertex " + std::to_string(j) + " has parent index " +
-               std::to_string(p) + " outside the sample";
-        return CAVS_ERR_BAD_GRAPH;
-      }
-      const int pg = base + p;
-      parent_g_[base + j] = pg;
-      int& k = nchild_g_[pg];
-      if (k >= n_slots) {
-        *err = "schedule: sample " + std::to_string(i) + " vertex " + std::to_string(p) + " has more than " +
-               std::to_string(n_slots) + " children";
-        return CAVS_ERR_BAD_GRAPH;
-      }
-      child_g_[static_cast<size_t>(k) * nz + pg] = base + j;
-      ++k;
+    const int32_t* cnt = level_cnt_.data() + static_cast<size_t>(i) * max_len;
+    for (int l = 0; l < sample_levels_[i]; ++l) level_off_[l + 1] += cnt[l];
+  }
+  max_level_rows_ = 0;
+  for (int l = 0; l < n_levels; ++l) {
+    max_level_rows_ = std::max(max_level_rows_, level_off_[l + 1]);
+    level_off_[l + 1] += level_off_[l];
+  }
+  n_sched_ = level_off_[n_levels];
+  // level_cnt_[i][l] becomes the global tensor id of sample i's first vertex on level l
+  {
+    std::vector<int32_t> running(level_off_.begin(), level_off_.end() - 1);
+    for (int i = 0; i < batch; ++i) {
+      int32_t* cnt = level_cnt_.data() + static_cast<size_t>(i) * max_len;
+      for (int l = 0; l < sample_levels_[i]; ++l) { const int c = cnt[l]; cnt[l] = running[l]; running[l] += c; }
     }
   }
-  // Pass 3: wavefront.  t2j doubles as the frontier queue: level l occupies
-  // t2j[level_off[l] .. level_off[l+1]) and is scanned to discover level l+1.
+
+  // Phase C (parallel over samples): global tensor ids and tensor-id-space adjacency.
   t2j_.assign(nz, 0);
   j2t_.assign(nz, -1);
-  hits_.assign(nz, 0);
-  level_off_.clear();
-  level_off_.push_back(0);
-  int placed = 0;
-  for (int g = 0; g < n; ++g)
-    if (nchild_g_[g] == 0 && parent_g_[g] >= 0) { j2t_[g] = placed; t2j_[placed++] = g; }
-  max_level_rows_ = placed;
-  int begin = 0;
-  while (placed > begin) {
-    level_off_.push_back(placed);
-    max_level_rows_ = std::max(max_level_rows_, placed - begin);
-    const int end = placed;
-    for (int t = begin; t < end; ++t) {
-      const int p = parent_g_[t2j_[t]];
-      if (p >= 0 && ++hits_[p] == nchild_g_[p]) { j2t_[p] = placed; t2j_[placed++] = p; }
-    }
-    begin = end;
-  }
-  n_sched_ = placed;
-  if (placed != n) {
-    for (int g = 0; g < n; ++g)
-      if (j2t_[g] < 0 && !(nchild_g_[g] == 0 && parent_g_[g] < 0)) {
-        *err = "schedule: vertex " + std::to_string(g) + " is on a cycle (never becomes ready)";
-        return CAVS_ERR_BAD_GRAPH;
-      }
-  }
-  // Pass 4: adjacency in tensor-id space.
   child_t_.assign(nz * n_slots, -1);
   parent_t_.assign(nz, -1);
+  std::vector<int> roots_per_thread_sample(batch, 0);
+  ParallelFor(batch, threads, [&](int b0, int b1) {
+    std::vector<int32_t> slot_used(max_len);
+    for (int i = b0; i < b1; ++i) {
+      const int32_t* row = parents + static_cast<size_t>(i) * max_len;
+      const int32_t* loc = local_.data() + static_cast<size_t>(i) * max_len;
+      const int32_t* base_l = level_cnt_.data() + static_cast<size_t>(i) * max_len;
+      const int len = sample_len_[i], base = sample_off_[i];
+      if (sample_levels_[i] == 0) continue;       // single-vertex sample
+      auto tid_of = [&](int v) { return base_l[loc[v] >> 16] + (loc[v] & 0xffff); };
+      std::fill(slot_used.begin(), slot_used.begin() + len, 0);
+      for (int v = 0; v < len; ++v) {
+        const int t = tid_of(v);
+        t2j_[t] = base + v;
+        j2t_[base + v] = t;
+        if (v + 1 < len) {
+          const int p = row[v];
+          const int pt = tid_of(p);
+          parent_t_[t] = pt;
+          // children land in ascending id order: v ascends, so the next free slot of p is v's slot
+          child_t_[static_cast<size_t>(slot_used[p]++) * nz + pt] = t;
+        } else {
+          roots_per_thread_sample[i] = 1;
+        }
+      }
+    }
+  });
   n_roots_ = 0;
-  for (int t = 0; t < n_sched_; ++t) {
-    const int g = t2j_[t];
-    const int p = parent_g_[g];
-    if (p >= 0) parent_t_[t] = j2t_[p]; else ++n_roots_;
-    for (int c = 0; c < nchild_g_[g]; ++c) child_t_[static_cast<size_t>(c) * nz + t] = j2t_[child_g_[static_cast<size_t>(c) * nz + g]];
-  }
+  for (int i = 0; i < batch; ++i) n_roots_ += roots_per_thread_sample[i];
   return CAVS_OK;
 }
 

@@ -5,7 +5,8 @@
 // ActivateNext() call -- each call reserving four 1M-entry vectors
 // (graph_scheduler.cc:209-214) and each graph op uploading its index list from
 // pageable memory -- every level of the batch is laid out at once as flat arrays
-// in tensor-id (execution) order, ready for a single pinned upload.
+// in tensor-id (execution) order, ready for a single pinned upload.  Samples are scheduled
+// independently on several host threads (CAVS_HOST_THREADS, default min(cores, 8)).
 //
 // The job order inside each level and therefore every tensor id is identical to
 // the reference's (ascending id on level 0, graph_scheduler.cc:178-188; discovery
@@ -66,7 +67,7 @@ class LevelSchedule {
   int n_total_ = 0, n_sched_ = 0, max_level_rows_ = 0, n_roots_ = 0;
   std::vector<int32_t> sample_off_, level_off_, t2j_, j2t_, child_t_, parent_t_;
   // scratch kept between Load() calls so steady-state loads do not allocate
-  std::vector<int32_t> parent_g_, nchild_g_, child_g_, hits_, frontier_;
+  std::vector<int32_t> local_, sample_len_, sample_levels_, level_cnt_;
 };
 
 }  // namespace cavs_b200

@@ -12,11 +12,11 @@ extern "C" int cavs_gather_child_h(void* S, void* HK, int bf16, const float* sta
   return LaunchGatherChildH(S, HK, bf16 != 0, state, child, n_total, off, rows, hidden, n_slots, St(stream));
 }
 extern "C" int cavs_treelstm_cell_fwd(float* state, void* gates, const void* A, const void* P, const void* Q, int preact_bf16,
-                                      const float* bias, const int32_t* child, int n_total, int off, int rows, int hidden,
-                                      int n_slots, int leaf, void* stream) {
+                                      const float* bias, const int32_t* child, const int32_t* a_row, int n_total, int off, int rows,
+                                      int hidden, int n_slots, int leaf, void* stream) {
   CAVS_REQUIRE((state && gates && A && bias && (leaf || (P && Q && child))) || rows == 0, CAVS_ERR_BAD_ARG,
                "treelstm_cell_fwd: null pointer");
-  return LaunchCellFwd(state, gates, A, P, Q, preact_bf16 != 0, bias, child, n_total, off, rows, hidden, n_slots, leaf != 0, St(stream));
+  return LaunchCellFwd(state, gates, A, P, Q, preact_bf16 != 0, bias, child, a_row, n_total, off, rows, hidden, n_slots, leaf != 0, St(stream));
 }
 extern "C" int cavs_treelstm_cell_bwd(void* dA, void* ZF, int bf16, float* mailbox, const float* dOut, const void* gates,
                                       const float* state, const int32_t* child, const int32_t* parent, int n_total, int off,

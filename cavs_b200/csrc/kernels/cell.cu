@@ -156,8 +156,8 @@ GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ st
 template <typename TP, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
 CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
-        const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child, int n_total,
-        int off, int rows, int H) {
+        const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child,
+        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H) {
   constexpr bool kFast = sizeof(TP) == 2;
   const int hv = H / V;
   const int G = (3 + K) * H;
@@ -166,7 +166,10 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
   for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
     const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
     const size_t t = static_cast<size_t>(off) + b;
-    const TP* a = A + t * 4 * H + j;
+    // The input projection depends on the vertex only through its token: with a_row, A holds one row
+    // per distinct token and a_row[t] selects it (hot rows stay in L2); without, one row per vertex.
+    const size_t ar = a_row ? static_cast<size_t>(__ldg(a_row + t)) : t;
+    const TP* a = A + ar * 4 * H + j;
     const Vec<V> ai = LoadF<V>(a), ao = LoadF<V>(a + H), au = LoadF<V>(a + 2 * H), af = kLeaf ? Zero<V>() : LoadF<V>(a + 3 * H);
     const Vec<V> bi = LoadF<V>(bias + j), bf = LoadF<V>(bias + H + j), bu = LoadF<V>(bias + 2 * H + j), bo = LoadF<V>(bias + 3 * H + j);
     Vec<V> pi = Zero<V>(), po = Zero<V>(), pu = Zero<V>();
@@ -374,7 +377,7 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 }
 
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
-                  const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st) {
+                  const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st) {
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
@@ -383,12 +386,12 @@ int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const
     if (preact_bf16) {
       using TP = __nv_bfloat16;
       auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
-      if (leaf) CellFwd<TP, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, n_total, off, rows, H);
-      else CellFwd<TP, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, n_total, off, rows, H);
+      if (leaf) CellFwd<TP, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
+      else CellFwd<TP, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
     } else {
       auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
-      if (leaf) CellFwd<float, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, n_total, off, rows, H);
-      else CellFwd<float, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, n_total, off, rows, H);
+      if (leaf) CellFwd<float, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
+      else CellFwd<float, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");

@@ -17,8 +17,9 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
                        int rows, int H, int K, cudaStream_t st);
 // A, P, Q are fp32, or bf16 when preact_bf16 is set.
 // gates: fp32, or fp16 when preact_bf16 / bf16 is set (the bf16-GEMM configurations).
+// a_row (optional): [n_total] row of A for each vertex (A then holds one row per distinct token).
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
-                  const int32_t* child, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st);
+                  const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st);
 // dB_part (optional): [CellBwdMaxGrid(), 4H] fp32, zeroed by the caller before the first level of a
 // backward sweep; every launch adds its per-CTA column sums of (zi, zo, zu, sum zf) into it, and a
 // final column sum over its rows gives the bias gradient.  Needs CellBwdFusesBias(H).
@@ -41,6 +42,12 @@ int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const i
                    int n_chunks, const int32_t* seg_first_chunk, const int32_t* seg_tok, int n_seg, float* scratch, int E,
                    cudaStream_t st);
 
+// out[s,:] = sum over the rows of segment s of x[row,:] (rows listed in `order`, cut into chunks as for
+// LaunchEmbedBwd); fp32 accumulation in a fixed order; scratch: [n_chunks, width] fp32.
+int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16, long long pitch, int width, const int32_t* order,
+                          const int32_t* chunk_off, int n_chunks, const int32_t* seg_first_chunk, int n_seg, float* scratch,
+                          cudaStream_t st);
+
 // Fused classifier + softmax cross-entropy for small class counts (C <= 32), forward and backward
 // in one pass over the pushed hidden rows.  h rows are read with pitch h_pitch (state is [n,2H]).
 // Writes loss[t], dOut[t,:] = dz Wc; per-CTA partials of dWc / dbc / loss sum go to scratch and are
@@ -48,7 +55,7 @@ int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const i
 size_t LossHeadScratchBytes(int H, int C);
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
-                   float* scratch, cudaStream_t st);
+                   float* scratch, cudaStream_t st, bool accumulate = false);   // accumulate: add into dWc / dbc / loss_sum
 
 // Column sums of a [rows, cols] matrix (fp32 or bf16) into out[perm(col)], deterministic two-stage.
 size_t ColumnSumScratchBytes(int cols);

@@ -131,7 +131,108 @@ EmbedBwdSegments(float* __restrict__ dtable, const float* __restrict__ partial, 
   }
 }
 
+// ---- Segmented row sums (rows grouped by token), any input precision ----
+// The input projection x.W and its gradients depend on a vertex only through its token, so the
+// engine sums d(pre-activation) rows per distinct token before the weight-gradient and
+// embedding-gradient GEMMs.  Same fixed-order two-level scheme as above: chunks of at most
+// kEmbedChunk rows, then the chunks of a segment in order.
+template <typename TIn>
+__device__ __forceinline__ void Load4(const TIn* p, float (&v)[4]) {
+  if constexpr (sizeof(TIn) == 4) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  }
+}
+// One CTA per chunk; width must be a multiple of 4.  partial[chunk,:] in fp32.
+template <typename TIn>
+__global__ void __launch_bounds__(kThreads)
+SegSumChunks(float* __restrict__ partial, const TIn* __restrict__ x, long long pitch, const int32_t* __restrict__ order,
+             const int32_t* __restrict__ chunk_off, int width) {
+  __shared__ int32_t rows_sm[kEmbedChunk];
+  const int chunk = blockIdx.x;
+  const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
+  for (int r = threadIdx.x; r < cnt; r += kThreads) rows_sm[r] = order[begin + r];
+  __syncthreads();
+  for (int e = threadIdx.x * 4; e < width; e += kThreads * 4) {
+    float acc[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int v = 0; v < 4; ++v) acc[u][v] = 0.0f;
+    int r = 0;
+    for (; r + 4 <= cnt; r += 4) {
+      float t[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) Load4(x + static_cast<long long>(rows_sm[r + u]) * pitch + e, t[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[u][v] += t[u][v];
+    }
+    for (int u = 0; r < cnt; ++r, ++u) {
+      float t[4];
+      Load4(x + static_cast<long long>(rows_sm[r]) * pitch + e, t);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) acc[u][v] += t[v];
+    }
+    *reinterpret_cast<float4*>(partial + static_cast<size_t>(chunk) * width + e) =
+        make_float4((acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]), (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]),
+                    (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]), (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]));
+  }
+}
+// One CTA per segment: out[seg,:] = sum of its chunks' partials in chunk order (fp32 or bf16 output).
+template <typename TOut>
+__global__ void __launch_bounds__(kThreads)
+SegSumFinal(TOut* __restrict__ out, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk, int width) {
+  const int seg = blockIdx.x;
+  const int c0 = seg_first_chunk[seg], c1 = seg_first_chunk[seg + 1];
+  for (int e = threadIdx.x * 4; e < width; e += kThreads * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int c = c0;
+    for (; c + 8 <= c1; c += 8) {
+      float4 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) t[u] = *reinterpret_cast<const float4*>(partial + static_cast<size_t>(c + u) * width + e);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) { acc[0] += t[u].x; acc[1] += t[u].y; acc[2] += t[u].z; acc[3] += t[u].w; }
+    }
+    for (; c < c1; ++c) {
+      const float4 t = *reinterpret_cast<const float4*>(partial + static_cast<size_t>(c) * width + e);
+      acc[0] += t.x; acc[1] += t.y; acc[2] += t.z; acc[3] += t.w;
+    }
+    TOut* dst = out + static_cast<size_t>(seg) * width + e;
+    if constexpr (sizeof(TOut) == 4) {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(acc[0], acc[1]), b = __floats2bfloat162_rn(acc[2], acc[3]);
+      uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(dst) = u;
+    }
+  }
+}
+
 }  // namespace
+
+int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16, long long pitch, int width, const int32_t* order,
+                          const int32_t* chunk_off, int n_chunks, const int32_t* seg_first_chunk, int n_seg, float* scratch,
+                          cudaStream_t st) {
+  CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && width > 0 && width % 4 == 0 && pitch % 4 == 0, CAVS_ERR_BAD_ARG,
+               "segmented_row_sum: width and pitch must be positive multiples of 4");
+  if (n_chunks == 0 || n_seg == 0) return CAVS_OK;
+  CAVS_REQUIRE(out && x && order && chunk_off && seg_first_chunk && scratch, CAVS_ERR_BAD_ARG, "segmented_row_sum: null pointer");
+  if (in_bf16) SegSumChunks<__nv_bfloat16><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const __nv_bfloat16*>(x), pitch, order, chunk_off, width);
+  else SegSumChunks<float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const float*>(x), pitch, order, chunk_off, width);
+  CAVS_LAUNCH_CHECK("segmented_row_sum chunks");
+  if (out_bf16) SegSumFinal<__nv_bfloat16><<<n_seg, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(out), scratch, seg_first_chunk, width);
+  else SegSumFinal<float><<<n_seg, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, width);
+  CAVS_LAUNCH_CHECK("segmented_row_sum final");
+  return CAVS_OK;
+}
 
 int LaunchEmbedFwd(void* out, bool bf16, const float* table, const int32_t* tok, int rows, int E, int vocab, cudaStream_t st) {
   CAVS_REQUIRE(rows >= 0 && E > 0 && vocab > 0, CAVS_ERR_BAD_ARG, "embed_fwd: bad shape");

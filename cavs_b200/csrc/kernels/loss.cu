@@ -216,14 +216,13 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
 
 __global__ void __launch_bounds__(kThreads)
 LossHeadReduce(float* __restrict__ dWc, float* __restrict__ dbc, float* __restrict__ loss_sum,
-               const float* __restrict__ partial, int n_parts, int CH, int C, int stride) {
+               const float* __restrict__ partial, int n_parts, int CH, int C, int stride, int accumulate) {
   const int width = CH + C + 1;
   for (int i = blockIdx.x * kThreads + threadIdx.x; i < width; i += gridDim.x * kThreads) {
     float s = 0.0f;
     for (int p = 0; p < n_parts; ++p) s += partial[static_cast<size_t>(p) * stride + i];
-    if (i < CH) dWc[i] = s;
-    else if (i < CH + C) dbc[i - CH] = s;
-    else if (loss_sum) *loss_sum = s;
+    float* dst = i < CH ? dWc + i : (i < CH + C ? dbc + (i - CH) : loss_sum);
+    if (dst) *dst = accumulate ? *dst + s : s;
   }
 }
 
@@ -240,7 +239,7 @@ size_t LossHeadScratchBytes(int H, int C) {
 
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
-                   float* scratch, cudaStream_t st) {
+                   float* scratch, cudaStream_t st, bool accumulate) {
   CAVS_REQUIRE(rows >= 0 && H > 0 && C > 0, CAVS_ERR_BAD_ARG, "loss_head: bad shape");
   CAVS_REQUIRE(C <= kMaxC, CAVS_ERR_UNSUPPORTED, "loss_head: fused path supports at most 8 classes");
   CAVS_REQUIRE(H <= kThreads * kMaxColsPerThread, CAVS_ERR_UNSUPPORTED, "loss_head: hidden size above 2048");
@@ -272,7 +271,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
 #undef LOSS_CASE
   CAVS_LAUNCH_CHECK("loss_head");
   const int width = C * H + C + 1;
-  LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C, PartialStride(C, H));
+  LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
   CAVS_LAUNCH_CHECK("loss_head reduce");
   return CAVS_OK;
 }

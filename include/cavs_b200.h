@@ -138,10 +138,12 @@ CAVS_API int cavs_gather_child_h(void* S, void* HK, int bf16, const float* state
  * P [rows,3H] = (sum h).U_iou, Q [rows,n_slots,H] = h_c.U_f, bias [4H] (i,f,u,o).  Writes
  * gates [n_total,(3+n_slots)H] and state [n_total,2H].  leaf != 0: no children (P, Q unused, the
  * forget gates are neither computed nor stored).  preact_bf16 != 0: A, P, Q hold bf16 (the GEMM
- * epilogue's rounded output) and gates are stored as fp16; else both are fp32. */
+ * epilogue's rounded output) and gates are stored as fp16; else both are fp32.  a_row (optional,
+ * [n_total]): row of A to use for each vertex -- x.W depends on a vertex only through its token, so A may
+ * hold one row per distinct token; NULL: one row per vertex. */
 CAVS_API int cavs_treelstm_cell_fwd(float* state, void* gates, const void* A, const void* P, const void* Q, int preact_bf16,
-                                    const float* bias, const int32_t* child, int n_total, int off, int rows, int hidden,
-                                    int n_slots, int leaf, void* stream);
+                                    const float* bias, const int32_t* child, const int32_t* a_row, int n_total, int off, int rows,
+                                    int hidden, int n_slots, int leaf, void* stream);
 /* Fused gate-gradient backward of the cell: reads d(pushed h) dOut [n_total,H], the parent's
  * d(h|c) from mailbox [n_total,2H] (zeros for roots), saved gates and states; writes
  * dA [n_total,4H] (zi|zo|zu|sum zf), ZF [n_total,n_slots,H] (fp32, or bf16 with fp16 gates when bf16 != 0)
@@ -235,10 +237,13 @@ CAVS_API int cavs_treelstm_bind(cavs_treelstm* e, float* params, float* grads);
 CAVS_API int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream);
 /* tok_job / label_job: host int32 per vertex in job order (compact, sample-major).  Reorders them to
  * tensor-id order (the Pull and FunctionPopRet permutations, cavs/backend/op_impl_graphop.cu:214-254,275-327),
- * builds the embedding-gradient segments and uploads all tables with one async copy.
+ * builds the embedding-gradient segments and uploads all tables with one async copy on an internal
+ * copy stream (the `stream` argument is ignored); the next cavs_treelstm_forward waits for it.  Two
+ * table slots alternate, so the batch after the one in flight can be loaded while it executes.
  * loss_rows: divisor of the loss gradient (0 = this batch's vertex count). */
 CAVS_API int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job, const int32_t* label_job,
                                       int loss_rows, void* stream);
+/* Embedding lookup and input projection over the batch's distinct tokens, then the forward level loop. */
 CAVS_API int cavs_treelstm_forward(cavs_treelstm* e, void* stream);
 /* Loss head, level loop in reverse, deferred weight / bias / embedding gradients (overwrites grads). */
 CAVS_API int cavs_treelstm_backward(cavs_treelstm* e, void* stream);
