@@ -1,0 +1,79 @@
+"""Small, self-contained cases of the library's kernels, sized for profiler captures
+(inputs larger than L2, a few GB on the device at most, a handful of launches).
+
+    python -m cavs_b200.cases gemm    one per-level gate product: [65536,1024] x [1024,3072], bf16 in / bf16 out
+    python -m cavs_b200.cases loss    the fused loss head on 65536 rows of hidden size 1024, 5 classes
+    python -m cavs_b200.cases shard   two training steps of the Tree-LSTM engine on one rank's shard of the
+                                      benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB)
+"""
+from __future__ import annotations
+
+import ctypes
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from cavs_b200 import lib, schedule as S  # noqa: E402
+from cavs_b200.treelstm import TreeLSTM  # noqa: E402
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _st():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def gemm(iters: int = 3) -> None:
+    L, dev, ll = lib(), torch.device("cuda"), ctypes.c_longlong
+    m, n, k = 65536, 3072, 1024
+    a = torch.randn((m, k), device=dev).to(torch.bfloat16)
+    b = torch.randn((k, n), device=dev).to(torch.bfloat16)
+    c = torch.empty((m, n), device=dev, dtype=torch.bfloat16)
+    for _ in range(iters):
+        rc = L.cavs_gemm_bf16(_p(c), ll(n), 2, _p(a), ll(k), 0, _p(b), ll(n), 1, m, n, k, 1, _p(None), ctypes.c_size_t(0), _p(None), _st())
+        assert rc == 0, L.cavs_last_error()
+    torch.cuda.synchronize()
+
+
+def loss(iters: int = 3) -> None:
+    L, dev, ll = lib(), torch.device("cuda"), ctypes.c_longlong
+    L.cavs_fc_softmax_xent_scratch_bytes.restype = ctypes.c_size_t
+    rows, H, C = 65536, 1024, 5
+    state = torch.randn((rows, 2 * H), device=dev)
+    label = torch.randint(0, C, (rows,), device=dev, dtype=torch.int32)
+    Wc = torch.randn((C, H), device=dev) * 0.05
+    bc = torch.zeros(C, device=dev)
+    out = [torch.empty(rows, device=dev), torch.empty(4, device=dev), torch.empty((rows, H), device=dev),
+           torch.empty((C, H), device=dev), torch.empty(C, device=dev)]
+    scratch = torch.empty(L.cavs_fc_softmax_xent_scratch_bytes(H, C), dtype=torch.uint8, device=dev)
+    for _ in range(iters):
+        rc = L.cavs_fc_softmax_xent(*map(_p, out), _p(state), ll(2 * H), _p(label), _p(Wc), _p(bc), rows, H, C,
+                                    ctypes.c_float(1.0 / rows), _p(scratch), _st())
+        assert rc == 0, L.cavs_last_error()
+    torch.cuda.synchronize()
+
+
+def shard(steps: int = 2) -> None:
+    import bench
+    wl = bench.WORKLOADS["dp_treelstm"]
+    par, tok, lab, _ = bench.make_batch(wl, 0, 0, 8)
+    s = S.Schedule().load(par)
+    eng = TreeLSTM(wl["hidden"], wl["embed"], wl["vocab"], wl["classes"], gemm_bf16=True, max_vertices=s.n_total,
+                   max_level_rows=s.max_level_rows)
+    eng.set_params(bench.make_params(wl))
+    eng.load_batch(s, tok, lab)
+    for _ in range(steps):
+        eng.forward()
+        eng.backward()
+    print("loss", eng.read_loss(), "vertices", s.n_total, "levels", s.n_levels)
+
+
+if __name__ == "__main__":
+    {"gemm": gemm, "loss": loss, "shard": shard}[sys.argv[1]]()
+    print("ok", sys.argv[1])

@@ -53,7 +53,12 @@ struct cavs_treelstm {
   float* tail = nullptr;        // [0] loss sum, [1] status word (int)
   float *loss_scratch = nullptr, *col_scratch = nullptr, *emb_scratch = nullptr, *splitk_scratch = nullptr;
   size_t splitk_bytes = 0;
-  uint8_t *W_bf = nullptr, *U_bf = nullptr;
+  uint8_t *W_bf = nullptr, *U_bf = nullptr, *Wc_bf = nullptr;
+  // wide loss head (classes > 8): logits / dz [N, Cp] fp32, bf16 copies of dz and of the pushed h rows
+  float* logits = nullptr;
+  uint8_t *dz_bf = nullptr, *h_bf = nullptr;
+  int Cp() const { return (cfg.classes + 7) & ~7; }
+  bool WideHead() const { return cfg.classes > 8; }
   // TMA maps of the per-level GEMM operands, encoded once over whole arenas (bf16 mode).
   TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
@@ -137,7 +142,6 @@ int CheckConfig(const cavs_treelstm_config* c) {
   CAVS_REQUIRE(c->n_slots >= 1 && c->n_slots <= kMaxSlots, CAVS_ERR_BAD_ARG, "treelstm: child slots must be 1..4");
   CAVS_REQUIRE(c->max_vertices > 0 && c->max_level_rows > 0 && c->max_level_rows <= c->max_vertices, CAVS_ERR_BAD_ARG,
                "treelstm: capacities must be positive and max_level_rows <= max_vertices");
-  CAVS_REQUIRE(c->classes <= 8, CAVS_ERR_UNSUPPORTED, "treelstm: the fused loss head supports at most 8 classes");
   if (c->gemm_bf16)
     CAVS_REQUIRE(c->hidden % 8 == 0 && c->embed % 8 == 0, CAVS_ERR_BAD_ARG,
                  "treelstm: the tensor-core path needs hidden and embed to be multiples of 8 (16-byte TMA rows)");
@@ -158,6 +162,7 @@ size_t SplitKBytes(const cavs_treelstm_config& c) {
   size_t b = GemmBf16ScratchBytes(E, 4 * H, 32);
   b = std::max(b, GemmBf16ScratchBytes(H, 3 * H, 32));
   b = std::max(b, GemmBf16ScratchBytes(H, H, 32));
+  if (c.classes > 8) b = std::max(b, GemmBf16ScratchBytes(c.classes, H, 16));
   (void)N; (void)K;
   return b;
 }
@@ -189,8 +194,14 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->loss = w.Take<float>(N);
   e->dB_tmp = w.Take<float>(CellBwdFusesBias(c.hidden) ? static_cast<size_t>(CellBwdMaxGrid()) * 4 * H : 4 * H);
   e->tail = w.Take<float>(4);
-  e->loss_scratch = w.Take<float>(LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
-  e->col_scratch = w.Take<float>(ColumnSumScratchBytes(4 * c.hidden) / sizeof(float));
+  const bool wide = c.classes > 8;
+  const size_t Cp = (c.classes + 7) & ~static_cast<size_t>(7);
+  e->loss_scratch = w.Take<float>(wide ? 0 : LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
+  e->logits = w.Take<float>(wide ? N * Cp : 0);
+  e->dz_bf = w.Take<uint8_t>(wide && c.gemm_bf16 ? N * Cp * 2 : 0);
+  e->h_bf = w.Take<uint8_t>(wide && c.gemm_bf16 ? N * H * 2 : 0);
+  e->Wc_bf = w.Take<uint8_t>(wide && c.gemm_bf16 ? static_cast<size_t>(c.classes) * H * 2 : 0);
+  e->col_scratch = w.Take<float>(ColumnSumScratchBytes(std::max(4 * c.hidden, c.classes)) / sizeof(float));
   e->emb_scratch = w.Take<float>(MaxChunks(c) * 4 * H);
   e->splitk_bytes = SplitKBytes(c);
   e->splitk_scratch = w.Take<float>(e->splitk_bytes / sizeof(float));
@@ -335,6 +346,8 @@ extern "C" int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream) {
   // W and U are adjacent in the flat buffer, and so are their bf16 shadows only logically;
   // cast them separately into their own 16-byte aligned arrays.
   if (int rc = LaunchCastBf16(e->W_bf, e->params + e->OffW(), E * 4 * H, st)) return rc;
+  if (e->WideHead())
+    if (int rc = LaunchCastBf16(e->Wc_bf, e->params + e->OffWc(), static_cast<size_t>(e->cfg.classes) * H, st)) return rc;
   return LaunchCastBf16(e->U_bf, e->params + e->OffU(), 4 * H * H, st);
 }
 
@@ -482,12 +495,35 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   const void* U_f = U + static_cast<size_t>(3) * H * H * e->elt;
   int rc;
   const double elt = static_cast<double>(e->elt);
-  // Loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
-  // write loss and d(h) (H).
-  PROF(e, kProfLossHead, static_cast<double>(n) * (8.0 * H + 8), st,
-       LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
-                      e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
-                      e->loss_scratch, st));
+  if (!e->WideHead()) {
+    // Fused loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
+    // write loss and d(h) (H).
+    PROF(e, kProfLossHead, static_cast<double>(n) * (8.0 * H + 8), st,
+         LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
+                        e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
+                        e->loss_scratch, st));
+  } else {
+    // Wide head (vocabulary-sized class count): logits = h Wc^T, row softmax cross-entropy, then
+    // dH = dz Wc, dWc = dz^T h, dbc = column sums of dz -- FullyConnected + SoftmaxEntropyLoss and their
+    // gradients (op_impl_fullyconnected_cublas.cc:33-176, op_impl_softmax_entropy_logits_loss.cu:106-250).
+    const int Cp = e->Cp();
+    const void* hA = e->state;      // h rows: fp32 view of the state with pitch 2H, or a dense bf16 copy
+    long long ldh = 2 * H;
+    const void* Wc = e->params + e->OffWc();
+    if (e->bf16) {
+      if ((rc = LaunchCastRowsBf16(e->h_bf, e->state, n, H, 2 * H, st))) return rc;
+      hA = e->h_bf; ldh = H; Wc = e->Wc_bf;
+    }
+    if ((rc = Gemm(e, e->logits, Cp, 0, hA, ldh, false, Wc, H, true, n, C, H, false, st))) return rc;
+    PROF(e, kProfLossHead, static_cast<double>(n) * (8.0 * C + 8), st,
+         LaunchSoftmaxXentRows(e->loss, e->logits, e->bf16 ? e->dz_bf : nullptr, Cp, e->params + e->Offbc(), bt.label, n, C,
+                               1.0f / static_cast<float>(bt.loss_rows), st));
+    const void* dz = e->bf16 ? static_cast<const void*>(e->dz_bf) : e->logits;
+    if ((rc = Gemm(e, e->dOut, H, 0, dz, Cp, false, Wc, H, false, n, H, C, false, st))) return rc;
+    if ((rc = Gemm(e, g + e->OffWc(), H, 0, dz, Cp, true, hA, ldh, false, C, H, n, true, st))) return rc;
+    if ((rc = LaunchColumnSum(g + e->Offbc(), e->logits, false, Cp, n, C, e->col_scratch, st))) return rc;
+    if ((rc = LaunchColumnSum(e->tail, e->loss, false, 1, n, 1, e->col_scratch, st))) return rc;
+  }
   const bool fuse_bias = CellBwdFusesBias(H);
   const size_t dB_rows = static_cast<size_t>(CellBwdMaxGrid());
   if (fuse_bias) CAVS_CUDA(cudaMemsetAsync(e->dB_tmp, 0, dB_rows * 4 * H * sizeof(float), st));

@@ -57,6 +57,12 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
                    float* scratch, cudaStream_t st, bool accumulate = false);   // accumulate: add into dWc / dbc / loss_sum
 
+// Softmax cross-entropy over wide rows: z [rows, C] (pitch ldz) holds logits WITHOUT bias on entry
+// (bias, optional, is added here) and dz = (softmax - onehot) * inv_rows on exit; dz_bf16 (optional,
+// same pitch) receives a bf16 copy for the gradient GEMMs; loss[r] = -log softmax(z_r)[label_r].
+int LaunchSoftmaxXentRows(float* loss, float* z, void* dz_bf16, long long ldz, const float* bias, const int32_t* label, int rows,
+                          int C, float inv_rows, cudaStream_t st);
+
 // Column sums of a [rows, cols] matrix (fp32 or bf16) into out[perm(col)], deterministic two-stage.
 size_t ColumnSumScratchBytes(int cols);
 // block > 0 (cols == 4*block): source column block b is written to destination block m_b.
@@ -67,6 +73,8 @@ int LaunchSgd(float* w, const float* g, size_t n, float lr, cudaStream_t st);
 int LaunchAdagrad(float* w, float* acc, const float* g, size_t n, float lr, float eps, cudaStream_t st);
 // dst_bf16[i] = bf16(src[i])
 int LaunchCastBf16(void* dst, const float* src, size_t n, cudaStream_t st);
+// dst [rows, cols] (dense, bf16) = src [rows, cols] with row pitch src_pitch (fp32)
+int LaunchCastRowsBf16(void* dst, const float* src, long long rows, int cols, long long src_pitch, cudaStream_t st);
 
 }  // namespace cavs_b200
 #endif

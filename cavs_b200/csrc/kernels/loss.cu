@@ -10,6 +10,8 @@
 //
 // Determinism: dWc / dbc / the loss sum are accumulated per CTA in a fixed row order,
 // written to scratch, and reduced across CTAs in index order by a second kernel.
+#include <cuda_bf16.h>
+
 #include <cstdint>
 #include <mutex>
 
@@ -273,6 +275,75 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   const int width = C * H + C + 1;
   LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
   CAVS_LAUNCH_CHECK("loss_head reduce");
+  return CAVS_OK;
+}
+
+}  // namespace cavs_b200
+
+// ---------------------------------------------------------------------------------------------
+// Softmax cross-entropy over wide logit rows (language-model heads: classes = vocabulary).
+// One CTA per row, three passes over the row held in registers where it fits: max, sum of
+// exponentials, then dz = (softmax - onehot) * inv_rows written in place of the logits (and
+// optionally as bf16 for the gradient GEMMs).  Replaces cudnnSoftmaxForward + the two
+// elementwise kernels + cublasSscal (op_impl_softmax_entropy_logits_loss.cu:106-140,213-250).
+// The classifier products around it (logits, dH, dWc) are ordinary GEMMs.
+// ---------------------------------------------------------------------------------------------
+namespace cavs_b200 {
+namespace {
+
+__device__ __forceinline__ float BlockReduce(float v, bool is_max, float* sm) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : v + other;
+  }
+  __syncthreads();               // sm may still be read by the previous reduction
+  if (lane == 0) sm[warp] = v;
+  __syncthreads();
+  float r = sm[0];
+  for (int w = 1; w < kWarps; ++w) r = is_max ? fmaxf(r, sm[w]) : r + sm[w];   // fixed order
+  return r;
+}
+
+__global__ void __launch_bounds__(kThreads)
+SoftmaxXentRows(float* __restrict__ loss, float* __restrict__ z, __nv_bfloat16* __restrict__ dz_bf16, long long ldz,
+                const float* __restrict__ bias, const int32_t* __restrict__ label, int rows, int C, float inv_rows) {
+  __shared__ float sm[kWarps];
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    float* zr = z + static_cast<long long>(r) * ldz;
+    float mx = -INFINITY;
+    for (int c = threadIdx.x; c < C; c += kThreads) {
+      const float v = zr[c] + (bias ? bias[c] : 0.0f);
+      zr[c] = v;
+      mx = fmaxf(mx, v);
+    }
+    mx = BlockReduce(mx, true, sm);
+    float den = 0.0f;
+    for (int c = threadIdx.x; c < C; c += kThreads) den += expf(zr[c] - mx);
+    den = BlockReduce(den, false, sm);
+    const int y = label[r];
+    const float scale = (y >= 0) ? inv_rows : 0.0f;
+    if (threadIdx.x == 0) loss[r] = (y >= 0 && y < C) ? -(zr[y] - mx - logf(den)) : 0.0f;
+    __syncthreads();               // loss read zr[y] before it is overwritten below
+    for (int c = threadIdx.x; c < C; c += kThreads) {
+      const float d = (expf(zr[c] - mx) / den - (c == y ? 1.0f : 0.0f)) * scale;
+      zr[c] = d;
+      if (dz_bf16) dz_bf16[static_cast<long long>(r) * ldz + c] = __float2bfloat16_rn(d);
+    }
+  }
+}
+
+}  // namespace
+
+int LaunchSoftmaxXentRows(float* loss, float* z, void* dz_bf16, long long ldz, const float* bias, const int32_t* label, int rows,
+                          int C, float inv_rows, cudaStream_t st) {
+  CAVS_REQUIRE(rows >= 0 && C > 0 && ldz >= C, CAVS_ERR_BAD_ARG, "softmax_xent_rows: bad shape");
+  if (rows == 0) return CAVS_OK;
+  CAVS_REQUIRE(loss && z && label, CAVS_ERR_BAD_ARG, "softmax_xent_rows: null pointer");
+  const int grid = std::min(rows, SmCount() * 8);
+  SoftmaxXentRows<<<grid, kThreads, 0, st>>>(loss, z, static_cast<__nv_bfloat16*>(dz_bf16), ldz, bias, label, rows, C, inv_rows);
+  CAVS_LAUNCH_CHECK("softmax_xent_rows");
   return CAVS_OK;
 }
 

@@ -58,6 +58,14 @@ __global__ void __launch_bounds__(kThreads) CastBf16Kernel(__nv_bfloat16* __rest
   for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
 }
 
+__global__ void __launch_bounds__(kThreads)
+CastRowsBf16Kernel(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, long long rows, int cols, long long src_pitch) {
+  const long long total = rows * cols;
+  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride)
+    dst[i] = __float2bfloat16_rn(src[(i / cols) * src_pitch + (i % cols)]);
+}
+
 // Stage 1: CTA (x = column tile of kThreads, y = row chunk) sums its rows in order.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -112,6 +120,14 @@ int LaunchCastBf16(void* dst, const float* src, size_t n, cudaStream_t st) {
   CAVS_REQUIRE(dst && src, CAVS_ERR_BAD_ARG, "cast_bf16: null pointer");
   CastBf16Kernel<<<GridForElems(n, kThreads), kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(dst), src, n);
   CAVS_LAUNCH_CHECK("cast_bf16");
+  return CAVS_OK;
+}
+
+int LaunchCastRowsBf16(void* dst, const float* src, long long rows, int cols, long long src_pitch, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return CAVS_OK;
+  CAVS_REQUIRE(dst && src, CAVS_ERR_BAD_ARG, "cast_rows_bf16: null pointer");
+  CastRowsBf16Kernel<<<GridForElems(static_cast<size_t>(rows) * cols, kThreads), kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(dst), src, rows, cols, src_pitch);
+  CAVS_LAUNCH_CHECK("cast_rows_bf16");
   return CAVS_OK;
 }
 
