@@ -39,3 +39,31 @@ def rel_err(a, b):
     a = np.asarray(a, np.float64).ravel()
     b = np.asarray(b, np.float64).ravel()
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def chain_to_tree_params(Uc, Wc_rec, b, H):
+    """Chain-LSTM parameters in the reference app's layout (apps/paper/seq-lstm-cavs.cc:45-74: U [E,4H] multiplies
+    x, W [H,4H] multiplies the child's h, both with column blocks i,f,u,o; bias i,f,u,o) rearranged into the
+    child-sum Tree-LSTM layout with one child slot (W [E,4H] blocks i,o,u,f; U = U_iou [H,3H] then U_f [H,H])."""
+    Uc = np.asarray(Uc, np.float32).reshape(-1, 4 * H)
+    Wr = np.asarray(Wc_rec, np.float32).reshape(H, 4 * H)
+    blk = lambda m, k: m[:, k * H:(k + 1) * H]
+    W_tree = np.concatenate([blk(Uc, 0), blk(Uc, 3), blk(Uc, 2), blk(Uc, 1)], axis=1)
+    U_iou = np.concatenate([blk(Wr, 0), blk(Wr, 3), blk(Wr, 2)], axis=1)
+    U_tree = np.concatenate([U_iou.ravel(), blk(Wr, 1).ravel()])
+    return W_tree.ravel().copy(), U_tree.copy(), np.asarray(b, np.float32).copy()
+
+
+def make_chain_batch(seed, batch, len_lo, len_hi, vocab):
+    """Ragged chains with Zipf tokens and next-token labels (the last position predicts token 0)."""
+    parents = S.synth_chains(seed, batch, len_lo, len_hi)
+    lens = (parents == -1).argmax(1) + 1
+    n = int(lens.sum())
+    tok_job = S.synth_zipf(seed + 1, 1.1, vocab, n)
+    label_job = np.empty(n, np.int32)
+    off = 0
+    for L in lens:
+        label_job[off:off + L - 1] = tok_job[off + 1:off + L]
+        label_job[off + L - 1] = 0
+        off += L
+    return parents, tok_job, label_job
