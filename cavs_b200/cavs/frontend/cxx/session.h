@@ -1,0 +1,46 @@
+// Session::Run with the reference's signature (cavs/frontend/cxx/session.h:13-30).  Where the reference
+// compiles the recorded program into a statement list and interprets the vertex function op by op per
+// level, this Session recognises the program --
+//     GraphOutput(Node) -> FullyConnected -> SoftmaxEntropyLoss [-> Optimizer | Reduce_mean]
+// with Node() the child-sum Tree-LSTM (apps/paper/tree-lstm-cavs.cc:129-172) or the chain LSTM
+// (apps/paper/seq-lstm-cavs.cc:62-86) -- and binds it to the fused engine behind the C ABI
+// (cavs_treelstm_*).  Any other program is a fatal error: there is no generic interpreter and no
+// CPU fallback.
+#ifndef CAVS_FRONTEND_CXX_SESSION_H_
+#define CAVS_FRONTEND_CXX_SESSION_H_
+
+#include <initializer_list>
+#include <memory>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "cavs/frontend/cxx/sym.h"
+#include "cavs/proto/opt.pb.h"
+
+class Session {
+ public:
+  Session(int opt = 0, std::string name = "SimpleSession");
+  ~Session();
+  // feeds: {placeholder, host pointer} sized by the placeholder's shape.  The graph placeholder takes
+  // int parent indices [batch, max_len]; the vertex and label placeholders take floats read in compact
+  // job order, as Pull / the loss do in the reference (cavs/backend/op_impl_graphop.cu:214-254).
+  void Run(std::vector<Sym> outputs, const std::initializer_list<std::pair<Sym&, void*>>& feed = {});
+  void Run(Sym& output, const std::initializer_list<std::pair<Sym&, void*>>& feed = {}) {
+    std::vector<Sym> out = {output};
+    Run(out, feed);
+  }
+  // Not in the reference: direct access to a Variable's values in its declared layout, for parity runs
+  // (the reference fills every Uniform variable from the same default-seeded engine, functor_filler.h:93-97).
+  void SetVariable(const Sym& var, const float* host, size_t count);
+  void GetVariable(const Sym& var, float* host, size_t count);
+
+ private:
+  struct Impl;
+  std::unique_ptr<Impl> impl_;
+};
+
+// Extra optimisation bit understood by this Session only: run the gate GEMMs on the tensor cores with
+// bf16 operands (the default, like the reference, is fp32 throughout).
+enum { OPT_BF16_GEMM = 8 };
+#endif

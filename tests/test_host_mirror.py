@@ -6,14 +6,16 @@ from pathlib import Path
 
 import pytest
 
-EXE = Path(__file__).parent / "cpp" / "bin" / "graph_ops_test"
+BIN = Path(__file__).parent / "cpp" / "bin"
+EXE = BIN / "graph_ops_test"
+FRONTEND = BIN / "frontend_test"
 
 
-def _build():
-    if not EXE.exists():
+def _build(exe=EXE):
+    if not exe.exists():
         import __graft_entry__ as g
         g.build()
-    return EXE
+    return exe
 
 
 def test_registry_decls_and_scheduler_facade_cpu():
@@ -25,5 +27,19 @@ def test_registry_decls_and_scheduler_facade_cpu():
 @pytest.mark.gpu
 def test_graph_ops_bit_exact_on_device(cuda):
     r = subprocess.run([str(_build()), "gpu"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ok" in r.stdout
+
+
+def test_vertex_function_recording_cpu():
+    r = subprocess.run([str(_build(FRONTEND)), "cpu"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ok" in r.stdout
+
+
+@pytest.mark.gpu
+def test_session_run_matches_oracle_on_device(cuda):
+    """Tree-LSTM and chain LSTM declared through Sym / GraphSupport::Node(), one Session::Run training step each."""
+    r = subprocess.run([str(_build(FRONTEND)), "gpu"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "ok" in r.stdout
