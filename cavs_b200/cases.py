@@ -3,6 +3,8 @@
 
     python -m cavs_b200.cases gemm    one per-level gate product: [65536,1024] x [1024,3072], bf16 in / bf16 out
     python -m cavs_b200.cases loss    the fused loss head on 65536 rows of hidden size 1024, 5 classes
+    python -m cavs_b200.cases cell    one interior level of 16384 two-child vertices (hidden 1024, 4 slots, bf16 mode):
+                                      child-state gather, cell forward, cell backward, child-gradient scatter
     python -m cavs_b200.cases shard   two training steps of the Tree-LSTM engine on one rank's shard of the
                                       benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB)
 """
@@ -59,6 +61,44 @@ def loss(iters: int = 3) -> None:
     torch.cuda.synchronize()
 
 
+def cell(iters: int = 3) -> None:
+    L, dev = lib(), torch.device("cuda")
+    R, H, K = 16384, 1024, 4
+    n = 3 * R                                   # children occupy rows [0, 2R), the level rows [2R, 3R)
+    bf, hf = torch.bfloat16, torch.float16
+    child = torch.full((K, n), -1, dtype=torch.int32)
+    child[0, 2 * R:] = torch.arange(0, 2 * R, 2, dtype=torch.int32)
+    child[1, 2 * R:] = torch.arange(1, 2 * R, 2, dtype=torch.int32)
+    parent = torch.full((n,), -1, dtype=torch.int32)
+    parent[:2 * R] = 2 * R + torch.arange(2 * R, dtype=torch.int32) // 2
+    child, parent = child.to(dev), parent.to(dev)
+    state = torch.randn((n, 2 * H), device=dev) * 0.5
+    gates = torch.empty((n, (3 + K) * H), device=dev, dtype=hf)
+    A = (torch.randn((n, 4 * H), device=dev) * 0.5).to(bf)
+    P = (torch.randn((R, 3 * H), device=dev) * 0.5).to(bf)
+    Q = (torch.randn((R, K, H), device=dev) * 0.5).to(bf)
+    bias = torch.zeros(4 * H, device=dev)
+    S = torch.empty((R, H), device=dev, dtype=bf)
+    HK = torch.empty((R, K, H), device=dev, dtype=bf)
+    mailbox = torch.randn((n, 2 * H), device=dev) * 0.1
+    dOut = torch.randn((n, H), device=dev) * 0.1
+    dA = torch.empty((n, 4 * H), device=dev, dtype=bf)
+    ZF = torch.empty((n, K, H), device=dev, dtype=bf)
+    ds = torch.randn((R, H), device=dev) * 0.1
+    dq = torch.randn((R, K, H), device=dev) * 0.1
+    for _ in range(iters):
+        for rc in (
+            L.cavs_gather_child_h(_p(S), _p(HK), 1, _p(state), _p(child), n, 2 * R, R, H, K, _st()),
+            L.cavs_treelstm_cell_fwd(_p(state), _p(gates), _p(A), _p(P), _p(Q), 1, _p(bias), _p(child), _p(None), n, 2 * R, R,
+                                     H, K, 0, _st()),
+            L.cavs_treelstm_cell_bwd(_p(dA), _p(ZF), 1, _p(mailbox), _p(dOut), _p(gates), _p(state), _p(child), _p(parent), n,
+                                     2 * R, R, H, K, 0, _st()),
+            L.cavs_scatter_child_grad(_p(mailbox), _p(ds), _p(dq), _p(child), n, 2 * R, R, H, K, _st()),
+        ):
+            assert rc == 0, L.cavs_last_error()
+    torch.cuda.synchronize()
+
+
 def shard(steps: int = 2) -> None:
     import bench
     wl = bench.WORKLOADS["dp_treelstm"]
@@ -75,5 +115,5 @@ def shard(steps: int = 2) -> None:
 
 
 if __name__ == "__main__":
-    {"gemm": gemm, "loss": loss, "shard": shard}[sys.argv[1]]()
+    {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard}[sys.argv[1]]()
     print("ok", sys.argv[1])

@@ -131,8 +131,8 @@ __device__ __forceinline__ float TanhT(float x) {
 // Gather(Child=c) + Slice + Add of the reference (tree-lstm-cavs.cc:131-136).
 template <typename T, int K, int V>
 __global__ void __launch_bounds__(kThreads)
-GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ state, const int32_t* __restrict__ child,
-             int n_total, int off, int rows, int H) {
+GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ state, int state_pitch,
+             const int32_t* __restrict__ child, int n_total, int off, int rows, int H) {
   const int hv = H / V;
   const long long total = static_cast<long long>(rows) * hv;
   const long long stride = static_cast<long long>(gridDim.x) * kThreads;
@@ -143,7 +143,7 @@ GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ st
 #pragma unroll
     for (int c = 0; c < K; ++c) {
       const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
-      const Vec<V> h = ch >= 0 ? LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + j) : Zero<V>();
+      const Vec<V> h = ch >= 0 ? LoadF<V>(state + static_cast<size_t>(ch) * state_pitch + j) : Zero<V>();
 #pragma unroll
       for (int e = 0; e < V; ++e) s.v[e] = (c == 0) ? h.v[e] : s.v[e] + h.v[e];
       Store<V>(HK + (static_cast<size_t>(t) * K + c) * H + j, h);
@@ -363,14 +363,15 @@ int CellBwdMaxGrid() { return SmCount() * ResidentCtas(kThreads); }
 bool CellBwdFusesBias(int H) { return H / VecWidth(H) <= kThreads; }
 
 int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const int32_t* child, int n_total, int off,
-                       int rows, int H, int K, cudaStream_t st) {
+                       int rows, int H, int K, cudaStream_t st, int state_pitch) {
+  if (state_pitch <= 0) state_pitch = 2 * H;
   if (int rc = CheckCommon("gather_child_h", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
   const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
   DISPATCH_KV(K, v, {
-    if (bf16) GatherChildH<__nv_bfloat16, K, V><<<grid, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(S), static_cast<__nv_bfloat16*>(HK), state, child, n_total, off, rows, H);
-    else GatherChildH<float, K, V><<<grid, kThreads, 0, st>>>(static_cast<float*>(S), static_cast<float*>(HK), state, child, n_total, off, rows, H);
+    if (bf16) GatherChildH<__nv_bfloat16, K, V><<<grid, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(S), static_cast<__nv_bfloat16*>(HK), state, state_pitch, child, n_total, off, rows, H);
+    else GatherChildH<float, K, V><<<grid, kThreads, 0, st>>>(static_cast<float*>(S), static_cast<float*>(HK), state, state_pitch, child, n_total, off, rows, H);
   });
   CAVS_LAUNCH_CHECK("gather_child_h");
   return CAVS_OK;

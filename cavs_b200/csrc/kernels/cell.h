@@ -13,8 +13,9 @@ namespace cavs_b200 {
 // child: [K, n_total] tensor-id of each child slot or -1; parent: [n_total] or -1.
 // Level rows are [off, off + rows).  S is [n_total, H], HK / ZF are [n_total, K, H],
 // P is [rows, 3H] and Q / dq are [rows, K, H] (level-local), A / dA are [n_total, 4H].
+// state_pitch: floats per state row (h first); 0 = 2H (the Tree-LSTM's h|c rows).
 int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const int32_t* child, int n_total, int off,
-                       int rows, int H, int K, cudaStream_t st);
+                       int rows, int H, int K, cudaStream_t st, int state_pitch = 0);
 // A, P, Q are fp32, or bf16 when preact_bf16 is set.
 // gates: fp32, or fp16 when preact_bf16 / bf16 is set (the bf16-GEMM configurations).
 // a_row (optional): [n_total] row of A for each vertex (A then holds one row per distinct token).

@@ -119,6 +119,26 @@ def treelstm_fwd_bwd(tb: dict, tok, label, params: dict, H, E, V, C, K=2, gemm_b
     return out
 
 
+def treegru_fwd_bwd(tb: dict, tok, label, params: dict, H, E, V, C, K=4, gemm_bf16=False, loss_rows=0, preact_bf16=False):
+    """Child-sum Tree-GRU forward + loss + backward (an extension defined by the oracle).  params: Emb [V,E],
+    W [E*3H] (r,z,n), U [3*H*H] (U_r|U_z|U_n), B [3H], Wc [C,H], bc [C]."""
+    n = int(tb["n"])
+    cfg = Cfg(n, int(tb["n_levels"]), H, E, V, C, K, int(gemm_bf16), int(loss_rows), int(preact_bf16))
+    f32 = lambda a: np.ascontiguousarray(a, np.float32)
+    i32 = lambda a: np.ascontiguousarray(a, np.int32)
+    Emb, W, U, B, Wc, bc = (f32(params[k]) for k in ("Emb", "W", "U", "B", "Wc", "bc"))
+    out = dict(state=np.zeros((n, H), np.float32), loss=np.zeros(n, np.float32), dEmb=np.zeros_like(Emb),
+               dW=np.zeros_like(W), dU=np.zeros_like(U), dB=np.zeros_like(B), dWc=np.zeros_like(Wc), dbc=np.zeros_like(bc))
+    lo, fg, fs, bg, bs = i32(tb["level_off"]), i32(tb["fg"]), i32(tb["fs"]), i32(tb["bg"]), i32(tb["bs"])
+    tok, label = i32(tok), i32(label)
+    rc = oracle_lib().cavs_oracle_treegru_fwd_bwd(
+        ctypes.byref(cfg), _p(lo), _p(fg), _p(fs), _p(bg), _p(bs), _p(tok), _p(label), _p(Emb), _p(W), _p(U), _p(B), _p(Wc), _p(bc),
+        _p(out["state"]), _p(out["loss"]), _p(out["dEmb"]), _p(out["dW"]), _p(out["dU"]), _p(out["dB"]), _p(out["dWc"]),
+        _p(out["dbc"]))
+    assert rc == 0
+    return out
+
+
 def sgd(w, g, lr):
     oracle_lib().cavs_oracle_sgd(_p(w), _p(g), ctypes.c_size_t(w.size), ctypes.c_float(lr))
 

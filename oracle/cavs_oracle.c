@@ -620,6 +620,219 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
   return 0;
 }
 
+/* ------------------------------------------------------------------------- */
+/* Child-sum Tree-GRU with n_slots child slots (EXTENSION: the reference has   */
+/* no GRU; this definition is the contract, parity unpinned).                  */
+/*   a = x W  (W [E,3H], column blocks r,z,n);  ht = sum_k h_k                 */
+/*   r_k = sigmoid((a_r + h_k U_r) + b_r)       z = sigmoid((a_z + ht U_z) + b_z) */
+/*   m = sum_k r_k o h_k                        n = tanh((a_n + m U_n) + b_n)  */
+/*   h = (1 - z) o ht + z o n                                                  */
+/* U = U_r [H,H] | U_z [H,H] | U_n [H,H]; B [3H] blocks r,z,n; state row = h.  */
+/* Missing children contribute zero rows.  Same loss head and index tables as  */
+/* the Tree-LSTM; the mailbox row is d(h) only.                                */
+/* ------------------------------------------------------------------------- */
+int cavs_oracle_treegru_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_off, const int *fg, const int *fs,
+                                const int *bg, const int *bs, const int *tok, const int *label, const float *Emb,
+                                const float *W, const float *U, const float *B, const float *Wc, const float *bc,
+                                float *state_out, float *loss_out, float *dEmb, float *dW, float *dU, float *dB,
+                                float *dWc, float *dbc) {
+  const int n = cfg->n, H = cfg->hidden, E = cfg->embed, C = cfg->classes, K = cfg->n_slots, V = cfg->vocab;
+  const int bf = cfg->gemm_bf16;
+  const size_t nn = (size_t)(n > 0 ? n : 1);
+  const float *b_r = B, *b_z = B + H, *b_n = B + 2 * H;
+  float *Wr = (float *)malloc(sizeof(float) * (size_t)E * 3 * H);
+  float *Ur = (float *)malloc(sizeof(float) * (size_t)3 * H * H);
+  round_copy(Wr, W, (size_t)E * 3 * H, bf);
+  round_copy(Ur, U, (size_t)3 * H * H, bf);
+  const float *U_r = Ur, *U_z = Ur + (size_t)H * H, *U_n = Ur + (size_t)2 * H * H;
+
+  float *x = (float *)calloc(nn * E, sizeof(float));
+  float *a = (float *)calloc(nn * 3 * H, sizeof(float));
+  float *hk = (float *)calloc(nn * H * K, sizeof(float));      /* [K][n,H] gathered child h (fp32)     */
+  float *hk_r = (float *)calloc(nn * H * K, sizeof(float));    /* GEMM-operand copy                    */
+  float *ht = (float *)calloc(nn * H, sizeof(float));
+  float *ht_r = (float *)calloc(nn * H, sizeof(float));
+  float *pr = (float *)calloc(nn * H * K, sizeof(float));
+  float *pz = (float *)calloc(nn * H, sizeof(float));
+  float *pn = (float *)calloc(nn * H, sizeof(float));
+  float *rk = (float *)calloc(nn * H * K, sizeof(float));
+  float *m = (float *)calloc(nn * H, sizeof(float));
+  float *m_r = (float *)calloc(nn * H, sizeof(float));
+  float *zg = (float *)calloc(nn * H, sizeof(float));
+  float *ng = (float *)calloc(nn * H, sizeof(float));
+  float *state = (float *)calloc(nn * H, sizeof(float));
+  float *mailbox = (float *)calloc(nn * H, sizeof(float));
+
+  for (int t = 0; t < n; t++) {
+    int id = tok[t];
+    if (id < 0 || id >= V) id = 0;
+    for (int e = 0; e < E; e++) x[(size_t)t * E + e] = bf ? bf16_round(Emb[(size_t)id * E + e]) : Emb[(size_t)id * E + e];
+  }
+  gemm_nn(a, x, Wr, n, 3 * H, E, 0);
+  if (cfg->preact_bf16) for (size_t i = 0; i < (size_t)n * 3 * H; i++) a[i] = bf16_round(a[i]);
+
+  for (int l = 0; l < cfg->n_levels; l++) {
+    const int off = level_off[l], cnt = level_off[l + 1] - off;
+    for (int t = off; t < off + cnt; t++)
+      for (int j = 0; j < H; j++) {
+        float acc = 0.0f;
+        for (int c = 0; c < K; c++) {
+          int src = fg[(size_t)c * n + t];
+          float hv = src >= 0 ? mailbox[(size_t)src * H + j] : 0.0f;
+          hk[((size_t)c * n + t) * H + j] = hv;
+          hk_r[((size_t)c * n + t) * H + j] = bf ? bf16_round(hv) : hv;
+          acc = (c == 0) ? hv : acc + hv;
+        }
+        ht[(size_t)t * H + j] = acc;
+        ht_r[(size_t)t * H + j] = bf ? bf16_round(acc) : acc;
+      }
+    gemm_nn(pz + (size_t)off * H, ht_r + (size_t)off * H, U_z, cnt, H, H, 0);
+    for (int c = 0; c < K; c++)
+      gemm_nn(pr + ((size_t)c * n + off) * H, hk_r + ((size_t)c * n + off) * H, U_r, cnt, H, H, 0);
+    if (cfg->preact_bf16) {
+      for (size_t i = (size_t)off * H; i < (size_t)(off + cnt) * H; i++) pz[i] = bf16_round(pz[i]);
+      for (int c = 0; c < K; c++)
+        for (size_t i = ((size_t)c * n + off) * H; i < ((size_t)c * n + off + cnt) * H; i++) pr[i] = bf16_round(pr[i]);
+    }
+    for (int t = off; t < off + cnt; t++)
+      for (int j = 0; j < H; j++) {
+        float acc = 0.0f;
+        for (int c = 0; c < K; c++) {
+          float r = sigmoidf_((a[(size_t)t * 3 * H + j] + pr[((size_t)c * n + t) * H + j]) + b_r[j]);
+          rk[((size_t)c * n + t) * H + j] = r;
+          acc += r * hk[((size_t)c * n + t) * H + j];
+        }
+        m[(size_t)t * H + j] = acc;
+        m_r[(size_t)t * H + j] = bf ? bf16_round(acc) : acc;
+      }
+    gemm_nn(pn + (size_t)off * H, m_r + (size_t)off * H, U_n, cnt, H, H, 0);
+    if (cfg->preact_bf16) for (size_t i = (size_t)off * H; i < (size_t)(off + cnt) * H; i++) pn[i] = bf16_round(pn[i]);
+    for (int t = off; t < off + cnt; t++)
+      for (int j = 0; j < H; j++) {
+        float z = sigmoidf_((a[(size_t)t * 3 * H + H + j] + pz[(size_t)t * H + j]) + b_z[j]);
+        float g = tanhf((a[(size_t)t * 3 * H + 2 * H + j] + pn[(size_t)t * H + j]) + b_n[j]);
+        zg[(size_t)t * H + j] = z;
+        ng[(size_t)t * H + j] = g;
+        state[(size_t)t * H + j] = (1.0f - z) * ht[(size_t)t * H + j] + z * g;
+      }
+    for (int t = off; t < off + cnt; t++)
+      if (fs[t] >= 0) memcpy(mailbox + (size_t)fs[t] * H, state + (size_t)t * H, sizeof(float) * H);
+  }
+  if (state_out) memcpy(state_out, state, sizeof(float) * (size_t)n * H);
+
+  /* Loss head (same as the Tree-LSTM's). */
+  float *dOut = (float *)calloc(nn * H, sizeof(float));
+  float *dz = (float *)calloc(nn * C, sizeof(float));
+  const float inv_rows = 1.0f / (float)(cfg->loss_rows > 0 ? cfg->loss_rows : (n > 0 ? n : 1));
+  for (int t = 0; t < n; t++) {
+    float *zz = (float *)malloc(sizeof(float) * C);
+    const float *h = state + (size_t)t * H;
+    float mx = -INFINITY;
+    for (int c = 0; c < C; c++) {
+      float acc = 0.0f;
+      for (int j = 0; j < H; j++) acc += h[j] * Wc[(size_t)c * H + j];
+      zz[c] = acc + bc[c];
+      if (zz[c] > mx) mx = zz[c];
+    }
+    float den = 0.0f;
+    for (int c = 0; c < C; c++) { zz[c] = expf(zz[c] - mx); den += zz[c]; }
+    int y = label[t];
+    if (loss_out) loss_out[t] = (y >= 0) ? -logf(zz[y] / den) : 0.0f;
+    if (y >= 0) for (int c = 0; c < C; c++) dz[(size_t)t * C + c] = (zz[c] / den - (c == y ? 1.0f : 0.0f)) * inv_rows;
+    for (int j = 0; j < H; j++) {
+      float acc = 0.0f;
+      for (int c = 0; c < C; c++) acc += dz[(size_t)t * C + c] * Wc[(size_t)c * H + j];
+      dOut[(size_t)t * H + j] = acc;
+    }
+    free(zz);
+  }
+  for (int c = 0; c < C; c++) {
+    float accb = 0.0f;
+    for (int t = 0; t < n; t++) accb += dz[(size_t)t * C + c];
+    dbc[c] = accb;
+    for (int j = 0; j < H; j++) {
+      float acc = 0.0f;
+      for (int t = 0; t < n; t++) acc += dz[(size_t)t * C + c] * state[(size_t)t * H + j];
+      dWc[(size_t)c * H + j] = acc;
+    }
+  }
+
+  /* Backward sweep. */
+  float *dA = (float *)calloc(nn * 3 * H, sizeof(float));      /* sum_k zr_k | zz | zn */
+  float *zz_r = (float *)calloc(nn * H, sizeof(float));
+  float *zn_r = (float *)calloc(nn * H, sizeof(float));
+  float *zr_r = (float *)calloc(nn * H * K, sizeof(float));
+  float *dht = (float *)calloc(nn * H, sizeof(float));
+  float *dm = (float *)calloc(nn * H, sizeof(float));
+  float *dsz = (float *)calloc(nn * H, sizeof(float));
+  float *dqr = (float *)calloc(nn * H * K, sizeof(float));
+  for (int l = cfg->n_levels - 1; l >= 0; l--) {
+    const int off = level_off[l], cnt = level_off[l + 1] - off;
+    for (int t = off; t < off + cnt; t++) {
+      const float *mb = bg[t] >= 0 ? mailbox + (size_t)bg[t] * H : NULL;
+      for (int j = 0; j < H; j++) {
+        float dh = dOut[(size_t)t * H + j] + (mb ? mb[j] : 0.0f);
+        float z = zg[(size_t)t * H + j], g = ng[(size_t)t * H + j];
+        float zz = (dh * (g - ht[(size_t)t * H + j])) * z * (1.0f - z);
+        float zn = (dh * z) * (1.0f - g * g);
+        dht[(size_t)t * H + j] = dh * (1.0f - z);
+        dA[(size_t)t * 3 * H + H + j] = zz;
+        dA[(size_t)t * 3 * H + 2 * H + j] = zn;
+        zz_r[(size_t)t * H + j] = bf ? bf16_round(zz) : zz;
+        zn_r[(size_t)t * H + j] = bf ? bf16_round(zn) : zn;
+      }
+    }
+    gemm_nt(dm + (size_t)off * H, zn_r + (size_t)off * H, U_n, cnt, H, H, 0);
+    gemm_nt(dsz + (size_t)off * H, zz_r + (size_t)off * H, U_z, cnt, H, H, 0);
+    for (int t = off; t < off + cnt; t++)
+      for (int j = 0; j < H; j++) {
+        float acc = 0.0f;
+        for (int c = 0; c < K; c++) {
+          float r = rk[((size_t)c * n + t) * H + j];
+          float zr = (dm[(size_t)t * H + j] * hk[((size_t)c * n + t) * H + j]) * r * (1.0f - r);
+          zr_r[((size_t)c * n + t) * H + j] = bf ? bf16_round(zr) : zr;
+          acc += zr;
+        }
+        dA[(size_t)t * 3 * H + j] = acc;
+      }
+    for (int c = 0; c < K; c++)
+      gemm_nt(dqr + ((size_t)c * n + off) * H, zr_r + ((size_t)c * n + off) * H, U_r, cnt, H, H, 0);
+    for (int c = 0; c < K; c++)
+      for (int t = off; t < off + cnt; t++) {
+        int dst = bs[(size_t)c * n + t];
+        if (dst < 0) continue;
+        for (int j = 0; j < H; j++)
+          mailbox[(size_t)dst * H + j] = ((dht[(size_t)t * H + j] + dsz[(size_t)t * H + j]) +
+                                          dm[(size_t)t * H + j] * rk[((size_t)c * n + t) * H + j]) +
+                                         dqr[((size_t)c * n + t) * H + j];
+      }
+  }
+  /* Deferred weight gradients. */
+  float *dA_r = (float *)malloc(sizeof(float) * nn * 3 * H);
+  round_copy(dA_r, dA, (size_t)n * 3 * H, bf);
+  gemm_tn(dW, x, dA_r, E, 3 * H, n, 0);
+  for (int c = 0; c < K; c++) gemm_tn(dU, hk_r + (size_t)c * n * H, zr_r + (size_t)c * n * H, H, H, n, c > 0);
+  gemm_tn(dU + (size_t)H * H, ht_r, zz_r, H, H, n, 0);
+  gemm_tn(dU + (size_t)2 * H * H, m_r, zn_r, H, H, n, 0);
+  for (int j = 0; j < 3 * H; j++) {
+    float acc = 0.0f;
+    for (int t = 0; t < n; t++) acc += dA[(size_t)t * 3 * H + j];
+    dB[j] = acc;
+  }
+  float *dX = (float *)malloc(sizeof(float) * nn * E);
+  gemm_nt(dX, dA_r, Wr, n, E, 3 * H, 0);
+  memset(dEmb, 0, sizeof(float) * (size_t)V * E);
+  for (int t = 0; t < n; t++) {
+    int id = tok[t];
+    if (id < 0 || id >= V) id = 0;
+    for (int e = 0; e < E; e++) dEmb[(size_t)id * E + e] += dX[(size_t)t * E + e];
+  }
+  free(Wr); free(Ur); free(x); free(a); free(hk); free(hk_r); free(ht); free(ht_r); free(pr); free(pz); free(pn); free(rk);
+  free(m); free(m_r); free(zg); free(ng); free(state); free(mailbox); free(dOut); free(dz); free(dA); free(zz_r); free(zn_r);
+  free(zr_r); free(dht); free(dm); free(dsz); free(dqr); free(dA_r); free(dX);
+  return 0;
+}
+
 /* SGD (op_impl_sgd.cu:15-47): w <- w - lr * g. */
 void cavs_oracle_sgd(float *w, const float *g, size_t count, float lr) {
 #pragma omp parallel for schedule(static)

@@ -50,3 +50,37 @@ def treelstm_autograd(tb, tok, label, params, H, E, V, C, K=2, dtype=torch.float
         g = P[k].grad
         out["d" + k] = (g if g is not None else torch.zeros_like(P[k])).numpy()
     return out
+
+
+def treegru_autograd(tb, tok, label, params, H, E, V, C, K=4, dtype=torch.float64, loss_rows=0):
+    """Child-sum Tree-GRU (r_k per child, update gate on the child sum) with autograd; aligned tables only."""
+    n = int(tb["n"])
+    P = {k: torch.tensor(np.asarray(v), dtype=dtype, requires_grad=True) for k, v in params.items()}
+    Emb, W, U, B, Wc, bc = (P[k] for k in ("Emb", "W", "U", "B", "Wc", "bc"))
+    U_r, U_z, U_n = (U[i * H * H:(i + 1) * H * H].reshape(H, H) for i in range(3))
+    b_r, b_z, b_n = B[:H], B[H:2 * H], B[2 * H:]
+    a = Emb[torch.tensor(np.asarray(tok), dtype=torch.long)] @ W.reshape(E, 3 * H)
+    hs = [None] * n
+    zero = torch.zeros(H, dtype=dtype)
+    lo, fg = tb["level_off"], tb["fg"]
+    for l in range(int(tb["n_levels"])):
+        for t in range(int(lo[l]), int(lo[l + 1])):
+            hk = [hs[int(fg[c][t])] if fg[c][t] >= 0 else zero for c in range(K)]
+            ht = sum(hk[1:], hk[0])
+            m = sum(torch.sigmoid(a[t, :H] + h @ U_r + b_r) * h for h in hk)
+            z = torch.sigmoid(a[t, H:2 * H] + ht @ U_z + b_z)
+            g = torch.tanh(a[t, 2 * H:] + m @ U_n + b_n)
+            hs[t] = (1 - z) * ht + z * g
+    Hout = torch.stack(hs)
+    logits = Hout @ Wc.t() + bc
+    lab = torch.tensor(np.asarray(label), dtype=torch.long)
+    mask = lab >= 0
+    logp = torch.log_softmax(logits, dim=1)
+    loss_rows_v = -logp[torch.arange(n), lab.clamp(min=0)] * mask
+    rows = loss_rows if loss_rows > 0 else n
+    (loss_rows_v.sum() / rows).backward()
+    out = dict(state=Hout.detach().numpy(), loss=loss_rows_v.detach().numpy())
+    for k in ("Emb", "W", "U", "B", "Wc", "bc"):
+        g_ = P[k].grad
+        out["d" + k] = (g_ if g_ is not None else torch.zeros_like(P[k])).numpy()
+    return out
