@@ -49,7 +49,7 @@ struct cavs_treelstm {
   uint8_t *A = nullptr, *P = nullptr, *Q = nullptr;   // gate pre-activations: fp32, or bf16 in bf16 mode
   uint8_t* gates = nullptr;                           // saved gates: fp32, or fp16 in bf16 mode
   float *state = nullptr, *mailbox = nullptr;
-  float *dOut = nullptr, *ds = nullptr, *dq = nullptr, *dX = nullptr, *loss = nullptr, *dB_tmp = nullptr;
+  float *dOut = nullptr, *dz8 = nullptr, *ds = nullptr, *dq = nullptr, *dX = nullptr, *loss = nullptr, *dB_tmp = nullptr;
   float* tail = nullptr;        // [0] loss sum, [1] status word (int)
   float *loss_scratch = nullptr, *col_scratch = nullptr, *emb_scratch = nullptr, *splitk_scratch = nullptr;
   size_t splitk_bytes = 0;
@@ -59,6 +59,8 @@ struct cavs_treelstm {
   uint8_t *dz_bf = nullptr, *h_bf = nullptr;
   int Cp() const { return (cfg.classes + 7) & ~7; }
   bool WideHead() const { return cfg.classes > 8; }
+  // d(pushed h) is rebuilt inside the cell gradient from d(logits) rows when the classifier fits its shared-memory copy
+  bool FusedDh() const { return !WideHead() && static_cast<long long>(cfg.classes) * cfg.hidden <= 8192; }
   // TMA maps of the per-level GEMM operands, encoded once over whole arenas (bf16 mode).
   TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
@@ -187,7 +189,9 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->gates = w.Take<uint8_t>(N * (3 + K) * H * elt);
   e->state = w.Take<float>(N * 2 * H);
   e->mailbox = w.Take<float>(N * 2 * H);
-  e->dOut = w.Take<float>(N * H);
+  // d(pushed h): materialised only by the wide loss head; the fused head hands d(logits) rows (dz8) to the cell gradient
+  e->dOut = w.Take<float>(e->FusedDh() ? 0 : N * H);
+  e->dz8 = w.Take<float>(e->FusedDh() ? N * kHeadDzPitch : 0);
   e->ds = w.Take<float>(L * H);
   e->dq = w.Take<float>(L * K * H);
   e->dX = w.Take<float>(T * E);
@@ -497,11 +501,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   const double elt = static_cast<double>(e->elt);
   if (!e->WideHead()) {
     // Fused loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
-    // write loss and d(h) (H).
-    PROF(e, kProfLossHead, static_cast<double>(n) * (8.0 * H + 8), st,
-         LaunchLossHead(e->loss, e->tail, e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
+    // write loss and the d(logits) row; d(h) = dz Wc is rebuilt inside the cell gradient, never stored.
+    const bool fdh = e->FusedDh();
+    PROF(e, kProfLossHead, static_cast<double>(n) * (4.0 * H + 8 + (fdh ? 4.0 * kHeadDzPitch : 4.0 * H)), st,
+         LaunchLossHead(e->loss, e->tail, fdh ? nullptr : e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
                         e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
-                        e->loss_scratch, st));
+                        e->loss_scratch, st, false, fdh ? e->dz8 : nullptr, e->Status()));
   } else {
     // Wide head (vocabulary-sized class count): logits = h Wc^T, row softmax cross-entropy, then
     // dH = dz Wc, dWc = dz^T h, dbc = column sums of dz -- FullyConnected + SoftmaxEntropyLoss and their
@@ -529,12 +534,15 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   if (fuse_bias) CAVS_CUDA(cudaMemsetAsync(e->dB_tmp, 0, dB_rows * 4 * H * sizeof(float), st));
   for (int l = bt.n_levels - 1; l >= 0; --l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
-    // read dOut (H), mailbox (2H), gates, own c (H) [+ child c (KH)]; write dA (4H) [+ ZF (KH), child dc (KH)]
-    const double cell_bytes = l == 0 ? rows * H * (4.0 * (1 + 2 + 1) + elt * (3 + 4))
-                                     : rows * H * (4.0 * (1 + 2 + 1 + K + K) + elt * (3 + K + 4 + K));
+    // read d(h) (H; or the dz row with the fused head), mailbox (2H), gates, own c (H) [+ child c (KH)];
+    // write dA (4H) [+ ZF (KH), child dc (KH)]
+    const double dh_bytes = e->FusedDh() ? 4.0 * kHeadDzPitch : 4.0 * H;
+    const double cell_bytes = l == 0 ? rows * (H * (4.0 * (2 + 1) + elt * (3 + 4)) + dh_bytes)
+                                     : rows * (H * (4.0 * (2 + 1 + K + K) + elt * (3 + K + 4 + K)) + dh_bytes);
     PROF(e, kProfCellBwd, cell_bytes, st,
-         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->dOut, e->gates, e->state, bt.child,
-                       bt.parent, nt, off, rows, H, K, l == 0, st));
+         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->FusedDh() ? nullptr : e->dOut,
+                       e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
+                       e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C));
     if (l == 0) break;
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
@@ -627,7 +635,9 @@ extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_p
   switch (what) {
     case 0: *dev_ptr = e->state; *bytes = n * 2 * H * sizeof(float); break;      // h|c per vertex, tensor-id order
     case 1: *dev_ptr = e->loss; *bytes = n * sizeof(float); break;               // per-vertex loss
-    case 2: *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;           // d(loss)/d(pushed h)
+    case 2:                                                                      // d(loss)/d(pushed h), wide head only
+      if (e->FusedDh()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(h) is not materialised with the fused loss head");
+      *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;
     case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
     case 4: *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
     default: return Fail(CAVS_ERR_BAD_ARG, "treelstm_peek: unknown array id");

@@ -217,12 +217,22 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
 // CTA folds its rows in a fixed order and adds the result to its own row of dB_part
 // ([gridDim.x, 4H], zeroed by the caller before the first level), which a final column sum
 // reduces in CTA order.  dB_part == nullptr skips this (H / V > kThreads).
-template <typename T, int K, int V, bool kLeaf>
+//
+// kHead: d(pushed h) is not read from dOut but rebuilt as dz[t,:] . Wc[:, j] from the loss head's
+// d(logits) rows (dz, [n_total, 8] zero-padded) and the classifier weights (Wc [C, H], C <= 8), whose
+// copy in shared memory -- same fused-multiply-add order as the loss head itself.
+template <typename T, int K, int V, bool kLeaf, bool kHead>
 __global__ void __launch_bounds__(kThreads)
 CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, float* __restrict__ dB_part,
         const float* __restrict__ dOut, const typename GateType<T>::type* __restrict__ gates, const float* __restrict__ state,
-        const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H) {
+        const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H,
+        const float* __restrict__ dz, const float* __restrict__ Wc, int C) {
   __shared__ float fold[kThreads * 4 * V];
+  extern __shared__ __align__(16) float s_wc[];   // kHead: the classifier [C, H]
+  if (kHead) {
+    for (int i = threadIdx.x; i < C * H; i += kThreads) s_wc[i] = Wc[i];
+    __syncthreads();
+  }
   const int tpr = H / V;
   const int G = (3 + K) * H;
   const int rows_per_iter = tpr <= kThreads ? kThreads / tpr : 1;
@@ -242,7 +252,27 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
       // Gather of d(h|c) left by the parent; roots see zeros (op_impl_graphop.cu:77-86).
       const Vec<V> mh = has_parent ? LoadF<V>(mailbox + t * 2 * H + j) : Zero<V>();
       const Vec<V> mc = has_parent ? LoadF<V>(mailbox + t * 2 * H + H + j) : Zero<V>();
-      const Vec<V> dOutv = LoadF<V>(dOut + t * H + j);
+      Vec<V> dOutv;
+      if (kHead) {
+        const float4 d0 = __ldg(reinterpret_cast<const float4*>(dz + t * kHeadDzPitch));
+        const float4 d1 = __ldg(reinterpret_cast<const float4*>(dz + t * kHeadDzPitch) + 1);
+        const float dzr[kHeadDzPitch] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        dOutv = Zero<V>();
+        // The thread's classifier columns are re-read from shared memory for every row: keeping them in
+        // registers costs a third of the occupancy, and reading them through L1 loses to the streaming data.
+        const float* wcol = s_wc + j;
+        asm volatile("" : "+l"(wcol));   // opaque per row: stops the loads from being hoisted into registers
+#pragma unroll
+        for (int c = 0; c < kHeadDzPitch; ++c) {
+          if (c < C) {
+            const Vec<V> w = LoadF<V>(wcol + static_cast<size_t>(c) * H);
+#pragma unroll
+            for (int e = 0; e < V; ++e) dOutv.v[e] = fmaf(dzr[c], w.v[e], dOutv.v[e]);
+          }
+        }
+      } else {
+        dOutv = LoadF<V>(dOut + t * H + j);
+      }
       const typename GateType<T>::type* g = gates + t * G + j;
       const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
       const Vec<V> cown = LoadF<V>(state + t * 2 * H + H + j);
@@ -408,24 +438,32 @@ int CellBwdGrid(int rows, int H) {
 
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
-                  int K, bool leaf, cudaStream_t st) {
+                  int K, bool leaf, cudaStream_t st, const float* dz, const float* Wc, int C) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
+  const bool head = dz != nullptr;
+  CAVS_REQUIRE(head ? (Wc && C >= 1 && C <= kHeadDzPitch && (reinterpret_cast<uintptr_t>(dz) & 15u) == 0) : dOut != nullptr,
+               CAVS_ERR_BAD_ARG, "treelstm_cell_bwd: needs dOut, or 16-byte aligned dz rows with Wc and 1..8 classes");
   const int v = VecWidth(H);
   CAVS_REQUIRE(dB_part == nullptr || H / v <= kThreads, CAVS_ERR_UNSUPPORTED,
                "treelstm_cell_bwd: the fused bias gradient needs hidden / vector width <= 256");
   const int grid = CellBwdGrid(rows, H);
+  const size_t head_smem = head ? static_cast<size_t>(C) * H * sizeof(float) : 0;
+  CAVS_REQUIRE(head_smem <= 32 * 1024, CAVS_ERR_UNSUPPORTED, "treelstm_cell_bwd: classifier above 32 KB (classes * hidden <= 8192)");
+#define CELL_BWD(TT, GT, LEAF, HEAD)                                                                                   \
+  CellBwd<TT, K, V, LEAF, HEAD><<<grid, kThreads, head_smem, st>>>(static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
+                                                           static_cast<const GT*>(gates), state, child, parent, n_total, off,  \
+                                                           rows, H, dz, Wc, C)
   DISPATCH_KV(K, v, {
     if (bf16) {
-      auto* d = static_cast<__nv_bfloat16*>(dA); auto* z = static_cast<__nv_bfloat16*>(ZF);
-      if (leaf) CellBwd<__nv_bfloat16, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const __half*>(gates), state, child, parent, n_total, off, rows, H);
-      else CellBwd<__nv_bfloat16, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const __half*>(gates), state, child, parent, n_total, off, rows, H);
+      if (leaf) { if (head) CELL_BWD(__nv_bfloat16, __half, true, true); else CELL_BWD(__nv_bfloat16, __half, true, false); }
+      else { if (head) CELL_BWD(__nv_bfloat16, __half, false, true); else CELL_BWD(__nv_bfloat16, __half, false, false); }
     } else {
-      auto* d = static_cast<float*>(dA); auto* z = static_cast<float*>(ZF);
-      if (leaf) CellBwd<float, K, V, true><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const float*>(gates), state, child, parent, n_total, off, rows, H);
-      else CellBwd<float, K, V, false><<<grid, kThreads, 0, st>>>(d, z, mailbox, dB_part, dOut, static_cast<const float*>(gates), state, child, parent, n_total, off, rows, H);
+      if (leaf) { if (head) CELL_BWD(float, float, true, true); else CELL_BWD(float, float, true, false); }
+      else { if (head) CELL_BWD(float, float, false, true); else CELL_BWD(float, float, false, false); }
     }
   });
+#undef CELL_BWD
   CAVS_LAUNCH_CHECK("treelstm_cell_bwd");
   return CAVS_OK;
 }

@@ -24,11 +24,14 @@ int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const
 // dB_part (optional): [CellBwdMaxGrid(), 4H] fp32, zeroed by the caller before the first level of a
 // backward sweep; every launch adds its per-CTA column sums of (zi, zo, zu, sum zf) into it, and a
 // final column sum over its rows gives the bias gradient.  Needs CellBwdFusesBias(H).
+constexpr int kHeadDzPitch = 8;
 int CellBwdMaxGrid();
 bool CellBwdFusesBias(int H);
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
-                  int K, bool leaf, cudaStream_t st);
+                  int K, bool leaf, cudaStream_t st, const float* dz = nullptr, const float* Wc = nullptr, int C = 0);
+// dz / Wc / C (optional): rebuild d(pushed h) = dz[t,:] . Wc inside the kernel instead of reading dOut
+// (dz: [n_total, kHeadDzPitch] rows from LaunchLossHead's dz_out; Wc: [C, H], C <= 8); dOut may then be NULL.
 int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,
                            int rows, int H, int K, cudaStream_t st);
 
@@ -56,7 +59,12 @@ int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16,
 size_t LossHeadScratchBytes(int H, int C);
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
-                   float* scratch, cudaStream_t st, bool accumulate = false);   // accumulate: add into dWc / dbc / loss_sum
+                   float* scratch, cudaStream_t st, bool accumulate = false,    // accumulate: add into dWc / dbc / loss_sum
+                   float* dz_out = nullptr, int* status = nullptr);
+// status (optional, device): raised to 1 if a bounded wait on an asynchronous row copy expires.
+// dz_out (optional, [rows, 8]): d(logits) rows zero-padded to 8 floats.  With dz_out set, dOut may be NULL:
+// the cell-gradient kernel then rebuilds d(hidden) = dz Wc on the fly (LaunchCellBwd's head arguments)
+// instead of reading it back from memory.
 
 // Softmax cross-entropy over wide rows: z [rows, C] (pitch ldz) holds logits WITHOUT bias on entry
 // (bias, optional, is added here) and dz = (softmax - onehot) * inv_rows on exit; dz_bf16 (optional,

@@ -185,6 +185,31 @@ SegSumChunks(float* __restrict__ partial, const TIn* __restrict__ x, long long p
                     (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]), (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]));
   }
 }
+// Scalar forms of the two passes for widths or pitches that are not multiples of 4 (same summation order
+// per column: rows of a chunk in order, then chunks in order).
+template <typename TIn>
+__global__ void __launch_bounds__(kThreads)
+SegSumChunksScalar(float* __restrict__ partial, const TIn* __restrict__ x, long long pitch, const int32_t* __restrict__ order,
+                   const int32_t* __restrict__ chunk_off, int width) {
+  const int chunk = blockIdx.x;
+  const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
+  for (int e = threadIdx.x; e < width; e += kThreads) {
+    float acc = 0.0f;
+    for (int r = 0; r < cnt; ++r) acc += static_cast<float>(x[static_cast<long long>(order[begin + r]) * pitch + e]);
+    partial[static_cast<size_t>(chunk) * width + e] = acc;
+  }
+}
+template <typename TOut>
+__global__ void __launch_bounds__(kThreads)
+SegSumFinalScalar(TOut* __restrict__ out, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk, int width) {
+  const int seg = blockIdx.x;
+  const int c0 = seg_first_chunk[seg], c1 = seg_first_chunk[seg + 1];
+  for (int e = threadIdx.x; e < width; e += kThreads) {
+    float acc = 0.0f;
+    for (int c = c0; c < c1; ++c) acc += partial[static_cast<size_t>(c) * width + e];
+    out[static_cast<size_t>(seg) * width + e] = static_cast<TOut>(acc);
+  }
+}
 // One CTA per segment: out[seg,:] = sum of its chunks' partials in chunk order (fp32 or bf16 output).
 template <typename TOut>
 __global__ void __launch_bounds__(kThreads)
@@ -221,10 +246,22 @@ SegSumFinal(TOut* __restrict__ out, const float* __restrict__ partial, const int
 int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16, long long pitch, int width, const int32_t* order,
                           const int32_t* chunk_off, int n_chunks, const int32_t* seg_first_chunk, int n_seg, float* scratch,
                           cudaStream_t st) {
-  CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && width > 0 && width % 4 == 0 && pitch % 4 == 0, CAVS_ERR_BAD_ARG,
-               "segmented_row_sum: width and pitch must be positive multiples of 4");
+  CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && width > 0 && pitch >= width, CAVS_ERR_BAD_ARG,
+               "segmented_row_sum: width must be positive and pitch >= width");
   if (n_chunks == 0 || n_seg == 0) return CAVS_OK;
   CAVS_REQUIRE(out && x && order && chunk_off && seg_first_chunk && scratch, CAVS_ERR_BAD_ARG, "segmented_row_sum: null pointer");
+  using bf = __nv_bfloat16;
+  const bool vec = width % 4 == 0 && pitch % 4 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0;
+  if (!vec) {
+    if (in_bf16) SegSumChunksScalar<bf><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const bf*>(x), pitch, order, chunk_off, width);
+    else SegSumChunksScalar<float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const float*>(x), pitch, order, chunk_off, width);
+    CAVS_LAUNCH_CHECK("segmented_row_sum chunks");
+    if (out_bf16) SegSumFinalScalar<bf><<<n_seg, kThreads, 0, st>>>(static_cast<bf*>(out), scratch, seg_first_chunk, width);
+    else SegSumFinalScalar<float><<<n_seg, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, width);
+    CAVS_LAUNCH_CHECK("segmented_row_sum final");
+    return CAVS_OK;
+  }
   if (in_bf16) SegSumChunks<__nv_bfloat16><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const __nv_bfloat16*>(x), pitch, order, chunk_off, width);
   else SegSumChunks<float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const float*>(x), pitch, order, chunk_off, width);
   CAVS_LAUNCH_CHECK("segmented_row_sum chunks");

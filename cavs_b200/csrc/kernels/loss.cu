@@ -16,6 +16,7 @@
 #include <mutex>
 
 #include "abi_common.h"
+#include "kernels/bulk.cuh"
 #include "kernels/cell.h"
 #include "kernels/launch.h"
 
@@ -43,7 +44,7 @@ __device__ __forceinline__ float WarpSum(float v) {
 // up front and every loop unrolls; kIters == 0: generic loops.
 template <int C, int kVec, int kIters>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
-LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ partial,
+LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ dz_out, float* __restrict__ partial,
                const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
                const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows) {
   extern __shared__ float sm[];
@@ -117,8 +118,19 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
           if (c == y) lrow = -logf(pc);
         }
         if (lane == 0) { loss[t] = lrow; loss_acc += lrow; }
+        if (dz_out != nullptr && lane == 0) {
+          // d(logits) row, zero-padded to kMaxC floats: the consumer rebuilds d(hidden) = dz Wc itself.
+          float pad[kMaxC];
+#pragma unroll
+          for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? dz[c < C ? c : 0] : 0.0f;
+          float4* dst = reinterpret_cast<float4*>(dz_out + static_cast<long long>(t) * kMaxC);
+          dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
+          dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
+        }
         float* dr = dOut + static_cast<long long>(t) * H;
-        if (kVec == 4) {
+        if (dOut == nullptr) {
+          // d(hidden) is not materialised
+        } else if (kVec == 4) {
 #pragma unroll 4
           for (int j = lane * 4; j < H; j += 128) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -216,6 +228,192 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
   }
 }
 
+// Streaming form for H <= 1024 (H a multiple of 4): rows arrive in shared memory through bulk copies that
+// complete on an mbarrier, kStreamStages batches of kStreamRows rows in flight per CTA, so DRAM latency is
+// hidden without occupancy.  Each thread owns four columns for the CTA's whole life: its slice of the
+// classifier and its dWc accumulators live in registers, every row is read from DRAM exactly once and
+// from shared memory once.  Per batch: partial logits per thread -> transpose-reduce inside the warp
+// (lane l ends up with row l/4) -> shared memory across the 8 warps -> one thread per row finishes the
+// softmax -> every thread adds dz^T h for its columns from registers.  Same per-CTA partial record as
+// LossHeadKernel.  A bulk copy that does not land within the wait limit raises *status (if given),
+// poisons the CTA's loss sum with NaN and ends the CTA's loop.
+constexpr int kStreamRows = 8;
+constexpr int kStreamStages = 3;
+
+template <int C>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ dz_out, float* __restrict__ partial,
+               const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
+               const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows,
+               int* __restrict__ status) {
+  extern __shared__ __align__(16) float sm[];
+  float* stage = sm;                                                  // [kStreamStages][kStreamRows][H]
+  float* red = sm + kStreamStages * kStreamRows * H;                  // [kWarps][kStreamRows][C]
+  float* sdz = red + kWarps * kStreamRows * C;                        // [kStreamRows][C]
+  __shared__ __align__(8) unsigned long long bars[kStreamStages];
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int j = tid * 4;
+  const bool col_ok = j < H;
+  const uint32_t row_bytes = static_cast<uint32_t>(H) * 4u;
+  const int n_batches = (rows + kStreamRows - 1) / kStreamRows;
+  const int my_batches = blockIdx.x < n_batches ? (n_batches - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  auto issue = [&](int k) {   // thread 0: start the copies of this CTA's k-th batch
+    const int s = k % kStreamStages;
+    const int r0 = (blockIdx.x + k * gridDim.x) * kStreamRows;
+    const int cnt = min(kStreamRows, rows - r0);
+    const uint32_t bar = bulk::SmemAddr(&bars[s]);
+    bulk::MbarExpectTx(bar, row_bytes * cnt);
+    for (int r = 0; r < cnt; ++r)
+      bulk::Load(bulk::SmemAddr(stage + (s * kStreamRows + r) * H), h + static_cast<long long>(r0 + r) * h_pitch, row_bytes, bar);
+  };
+  if (tid == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStreamStages; ++s) bulk::MbarInit(bulk::SmemAddr(&bars[s]), 1);
+    bulk::FenceMbarInit();
+  }
+  __syncthreads();
+  if (tid == 0)
+    for (int k = 0; k < kStreamStages && k < my_batches; ++k) issue(k);
+
+  float wc[C][4], accW[C][4];
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const float4 w = col_ok ? *reinterpret_cast<const float4*>(Wc + c * H + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    wc[c][0] = w.x; wc[c][1] = w.y; wc[c][2] = w.z; wc[c][3] = w.w;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) accW[c][e] = 0.0f;
+  }
+  float accb = 0.0f;       // thread c < C: bias gradient of class c
+  float loss_acc = 0.0f;   // thread r < kStreamRows: loss of the rows it finished
+
+  for (int k = 0; k < my_batches; ++k) {
+    const int s = k % kStreamStages;
+    const int r0 = (blockIdx.x + k * gridDim.x) * kStreamRows;
+    const int cnt = min(kStreamRows, rows - r0);
+    if (!bulk::MbarWait(bulk::SmemAddr(&bars[s]), (k / kStreamStages) & 1)) s_abort = 1;
+    float hr[kStreamRows][4];
+#pragma unroll
+    for (int r = 0; r < kStreamRows; ++r) {
+      const float4 v = (col_ok && r < cnt) ? *reinterpret_cast<const float4*>(stage + (s * kStreamRows + r) * H + j)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+      hr[r][0] = v.x; hr[r][1] = v.y; hr[r][2] = v.z; hr[r][3] = v.w;
+    }
+    // Partial logits of the thread's columns, then the warp's transpose-reduce: 8 rows -> 4 -> 2 -> 1 value
+    // per lane while the lane distance halves, then the last two butterfly steps.
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      float v[kStreamRows];
+#pragma unroll
+      for (int r = 0; r < kStreamRows; ++r)
+        v[r] = fmaf(hr[r][0], wc[c][0], fmaf(hr[r][1], wc[c][1], fmaf(hr[r][2], wc[c][2], hr[r][3] * wc[c][3])));
+      const bool b16 = lane & 16, b8 = lane & 8, b4 = lane & 4;
+      float w4[4], w2[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float recv = __shfl_xor_sync(0xffffffffu, b16 ? v[i] : v[i + 4], 16);
+        w4[i] = (b16 ? v[i + 4] : v[i]) + recv;
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float recv = __shfl_xor_sync(0xffffffffu, b8 ? w4[i] : w4[i + 2], 8);
+        w2[i] = (b8 ? w4[i + 2] : w4[i]) + recv;
+      }
+      float y = (b4 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, b4 ? w2[0] : w2[1], 4);
+      y += __shfl_xor_sync(0xffffffffu, y, 2);
+      y += __shfl_xor_sync(0xffffffffu, y, 1);
+      // lane l now holds the warp's sum for row ((l>>2)&1) + 2*((l>>3)&1) + 4*((l>>4)&1) = l >> 2
+      if ((lane & 3) == 0) red[(warp * kStreamRows + (lane >> 2)) * C + c] = y;
+    }
+    __syncthreads();   // the stage has been read by everyone and the partial logits are visible
+    if (tid == 0 && k + kStreamStages < my_batches && !s_abort) issue(k + kStreamStages);
+    if (tid < kStreamRows) {
+      const int t = r0 + tid;
+      float dz[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) dz[c] = 0.0f;
+      if (tid < cnt) {
+        float z[C], mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          float a = 0.0f;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) a += red[(w * kStreamRows + tid) * C + c];
+          z[c] = a + bc[c];
+          mx = fmaxf(mx, z[c]);
+        }
+        float den = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) { z[c] = expf(z[c] - mx); den += z[c]; }
+        const int y = label[t];
+        float lrow = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const float pc = z[c] / den;
+          dz[c] = (y >= 0) ? (pc - (c == y ? 1.0f : 0.0f)) * inv_rows : 0.0f;
+          if (c == y) lrow = -logf(pc);
+        }
+        loss[t] = lrow;
+        loss_acc += lrow;
+        if (dz_out != nullptr) {
+          float pad[kMaxC];
+#pragma unroll
+          for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? dz[c < C ? c : 0] : 0.0f;
+          float4* dst = reinterpret_cast<float4*>(dz_out + static_cast<long long>(t) * kMaxC);
+          dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
+          dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < C; ++c) sdz[tid * C + c] = dz[c];
+    }
+    __syncthreads();
+    if (s_abort) break;   // uniform: read after the barrier that follows every write
+#pragma unroll
+    for (int r = 0; r < kStreamRows; ++r) {
+      float d[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) d[c] = sdz[r * C + c];
+#pragma unroll
+      for (int c = 0; c < C; ++c)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) accW[c][e] = fmaf(d[c], hr[r][e], accW[c][e]);
+      if (dOut != nullptr && col_ok && r < cnt) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) a[e] = fmaf(d[c], wc[c][e], a[e]);
+        __stcs(reinterpret_cast<float4*>(dOut + static_cast<long long>(r0 + r) * H + j), make_float4(a[0], a[1], a[2], a[3]));
+      }
+      if (tid < C) accb += sdz[r * C + tid];
+    }
+    // No barrier here: red is rewritten before the next batch's first barrier, by threads that have passed
+    // this batch's second one (its readers finished before it); sdz is rewritten after the next batch's
+    // first barrier, which every thread reaches only after this loop.
+  }
+  float* mine = partial + static_cast<size_t>(blockIdx.x) * PartialStride(C, H);
+  if (col_ok) {
+#pragma unroll
+    for (int c = 0; c < C; ++c)
+      *reinterpret_cast<float4*>(mine + c * H + j) = make_float4(accW[c][0], accW[c][1], accW[c][2], accW[c][3]);
+  }
+  if (tid < C) mine[C * H + tid] = accb;
+  __shared__ float sloss[kStreamRows];
+  if (tid < kStreamRows) sloss[tid] = loss_acc;
+  __syncthreads();
+  if (tid == 0) {
+    float sum = 0.0f;
+    for (int r = 0; r < kStreamRows; ++r) sum += sloss[r];
+    if (s_abort) {
+      sum = NAN;
+      if (status != nullptr) atomicExch(status, 1);
+    }
+    mine[C * H + C] = sum;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 LossHeadReduce(float* __restrict__ dWc, float* __restrict__ dbc, float* __restrict__ loss_sum,
                const float* __restrict__ partial, int n_parts, int CH, int C, int stride, int accumulate) {
@@ -241,11 +439,37 @@ size_t LossHeadScratchBytes(int H, int C) {
 
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
-                   float* scratch, cudaStream_t st, bool accumulate) {
+                   float* scratch, cudaStream_t st, bool accumulate, float* dz_out, int* status) {
   CAVS_REQUIRE(rows >= 0 && H > 0 && C > 0, CAVS_ERR_BAD_ARG, "loss_head: bad shape");
   CAVS_REQUIRE(C <= kMaxC, CAVS_ERR_UNSUPPORTED, "loss_head: fused path supports at most 8 classes");
   CAVS_REQUIRE(H <= kThreads * kMaxColsPerThread, CAVS_ERR_UNSUPPORTED, "loss_head: hidden size above 2048");
-  CAVS_REQUIRE(loss && dOut && dWc && dbc && h && label && Wc && bc && scratch, CAVS_ERR_BAD_ARG, "loss_head: null pointer");
+  CAVS_REQUIRE(loss && (dOut || dz_out) && dWc && dbc && h && label && Wc && bc && scratch, CAVS_ERR_BAD_ARG, "loss_head: null pointer");
+  CAVS_REQUIRE((reinterpret_cast<uintptr_t>(dz_out) & 15u) == 0, CAVS_ERR_BAD_ARG, "loss_head: dz rows must be 16-byte aligned");
+  // Streaming form: 16-byte aligned rows of at most 1024 floats.
+  const bool stream_ok = H % 4 == 0 && H <= kThreads * 4 && h_pitch % 4 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dOut) | reinterpret_cast<uintptr_t>(scratch) |
+                           reinterpret_cast<uintptr_t>(Wc)) & 15u) == 0;
+  if (stream_ok && rows > 0) {
+    const int n_batches = (rows + kStreamRows - 1) / kStreamRows;
+    const int sgrid = std::max(1, std::min(n_batches, SmCount() * kCtasPerSm));
+    const size_t ssmem = (static_cast<size_t>(kStreamStages) * kStreamRows * H + (kWarps + 1) * kStreamRows * C) * sizeof(float);
+#define STREAM_CASE(CC)                                                                                              \
+  case CC:                                                                                                           \
+    if (ssmem > 48 * 1024)                                                                                           \
+      CAVS_CUDA(cudaFuncSetAttribute(LossHeadStream<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssmem));  \
+    LossHeadStream<CC><<<sgrid, kThreads, ssmem, st>>>(loss, dOut, dz_out, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows, status); \
+    break;
+    switch (C) {
+      STREAM_CASE(1) STREAM_CASE(2) STREAM_CASE(3) STREAM_CASE(4) STREAM_CASE(5) STREAM_CASE(6) STREAM_CASE(7) STREAM_CASE(8)
+      default: return Fail(CAVS_ERR_UNSUPPORTED, "loss_head: class count");
+    }
+#undef STREAM_CASE
+    CAVS_LAUNCH_CHECK("loss_head stream");
+    const int swidth = C * H + C + 1;
+    LossHeadReduce<<<std::min((swidth + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, sgrid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
+    CAVS_LAUNCH_CHECK("loss_head reduce");
+    return CAVS_OK;
+  }
   const int grid = rows > 0 ? LossGrid(rows) : 1;
   const size_t smem = (static_cast<size_t>(C) * H + kRowsPerBlock * C + kWarps) * sizeof(float);
   const bool vec4 = H % 4 == 0 && h_pitch % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dOut) | reinterpret_cast<uintptr_t>(scratch)) & 15u) == 0;
@@ -254,7 +478,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   do {                                                                                                               \
     if (smem > 48 * 1024)                                                                                            \
       CAVS_CUDA(cudaFuncSetAttribute(LossHeadKernel<CC, VV, II>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-    LossHeadKernel<CC, VV, II><<<grid, kThreads, smem, st>>>(loss, dOut, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
+    LossHeadKernel<CC, VV, II><<<grid, kThreads, smem, st>>>(loss, dOut, dz_out, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows); \
   } while (0)
 #define LOSS_CASE(CC)                                                        \
   case CC: {                                                                 \

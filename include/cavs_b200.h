@@ -256,8 +256,36 @@ CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int
  * 4 child-gradient scatter, 5 loss head, 6 embedding forward, 7 embedding backward, 8 column sum. */
 CAVS_API int cavs_treelstm_profile(cavs_treelstm* e, int enable);
 CAVS_API int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes);
-/* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H], 3 mailbox [n,2H], 4 gates. */
+/* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H] (classes > 8 only: the fused
+ * loss head does not materialise it), 3 mailbox [n,2H], 4 gates. */
 CAVS_API int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes);
+
+/* ------------------------------------------------------------------------ */
+/* Child-sum Tree-GRU engine: the same level loop over a second vertex        */
+/* function.  The reference ships LSTM vertex functions only (apps/paper/     */
+/* tree-lstm-cavs.cc, apps/lstm/); this shows what a user-defined F costs on  */
+/* top of the shared tables, input projection, loss head and weight-gradient  */
+/* passes.  Per vertex with children h_k: ht = sum h_k; r_k = sigmoid(a_r +   */
+/* h_k U_r + b_r); z = sigmoid(a_z + ht U_z + b_z); n = tanh(a_n + (sum r_k o */
+/* h_k) U_n + b_n); h = (1-z) o ht + z o n, with a = Emb[tok] W.              */
+/* Flat parameters: Emb [V,E] | W [E,3H] (r,z,n) | U [3,H,H] | B [3H] |       */
+/* Wc [C,H] | bc [C].  Same config struct and call sequence as cavs_treelstm; */
+/* classes <= 8; one batch at a time, tables uploaded on the caller's stream. */
+/* ------------------------------------------------------------------------ */
+typedef struct cavs_treegru cavs_treegru;
+CAVS_API size_t cavs_treegru_param_count(const cavs_treelstm_config* cfg);
+CAVS_API size_t cavs_treegru_workspace_bytes(const cavs_treelstm_config* cfg);
+CAVS_API int cavs_treegru_create(const cavs_treelstm_config* cfg, void* workspace, size_t workspace_bytes, cavs_treegru** out);
+CAVS_API void cavs_treegru_destroy(cavs_treegru* e);
+CAVS_API int cavs_treegru_bind(cavs_treegru* e, float* params, float* grads);
+CAVS_API int cavs_treegru_refresh_weights(cavs_treegru* e, void* stream);
+CAVS_API int cavs_treegru_load_batch(cavs_treegru* e, const cavs_sched* s, const int32_t* tok_job, const int32_t* label_job,
+                                     int loss_rows, void* stream);
+CAVS_API int cavs_treegru_forward(cavs_treegru* e, void* stream);
+CAVS_API int cavs_treegru_backward(cavs_treegru* e, void* stream);
+CAVS_API int cavs_treegru_read_loss(cavs_treegru* e, float* loss_sum_host, int* status_host, void* stream);
+/* Device views: 0 state [n,H], 1 loss [n], 2 dOut [n,H], 3 mailbox [n,H]. */
+CAVS_API int cavs_treegru_peek(cavs_treegru* e, int what, const void** dev_ptr, size_t* bytes);
 
 /* ------------------------------------------------------------------------ */
 /* Synthetic workloads (host only).  One SplitMix64 stream per (seed, stream).*/

@@ -67,3 +67,21 @@ def make_chain_batch(seed, batch, len_lo, len_hi, vocab):
         label_job[off + L - 1] = 0
         off += L
     return parents, tok_job, label_job
+
+
+def make_gru_params(seed, H, E, V, C, scale=0.05, bias_scale=0.0):
+    """Tree-GRU parameters: W [E,3H] (r,z,n), U [3,H,H], B [3H]."""
+    p = dict(Emb=S.synth_uniform_float(seed + 10, scale, (V, E)), W=S.synth_uniform_float(seed + 11, scale, (E * 3 * H,)),
+             U=S.synth_uniform_float(seed + 12, scale, (3 * H * H,)), Wc=S.synth_uniform_float(seed + 13, scale, (C, H)))
+    p["B"] = S.synth_uniform_float(seed + 14, bias_scale, (3 * H,)) if bias_scale else np.zeros(3 * H, np.float32)
+    p["bc"] = S.synth_uniform_float(seed + 15, bias_scale, (C,)) if bias_scale else np.zeros(C, np.float32)
+    return p
+
+
+def root_only_labels(parents, label_job):
+    """Keeps the label of each sample's root (its last vertex) and sets every other label to -1."""
+    lens = (parents == -1).argmax(1) + 1
+    out = np.full_like(label_job, -1)
+    ends = np.cumsum(lens) - 1
+    out[ends] = label_job[ends]
+    return out

@@ -8,7 +8,7 @@ import pytest
 import oracle
 from cavs_b200 import schedule as S
 from helpers import make_params, make_tree_batch, rel_err, tables_from_schedule
-from torch_ref import treelstm_autograd
+from torch_ref import treegru_autograd, treelstm_autograd
 
 GOLD = Path(__file__).parent / "golden" / "treelstm_small.npz"
 KEYS = ("state", "loss", "dEmb", "dW", "dU", "dB", "dWc", "dbc")
@@ -113,3 +113,22 @@ def test_row_ops_and_optimizers():
     acc = np.zeros(101, np.float32); w1 = w.copy()
     oracle.adagrad(w, acc, g, 0.05, 1e-10)
     assert np.allclose(acc, g * g) and np.allclose(w, w1 - 0.05 * g / (np.abs(g) + 1e-10), rtol=1e-6)
+
+
+@pytest.mark.parametrize("K,arity,root_only", [(4, 4, True), (2, 2, False)])
+def test_treegru_against_autograd(K, arity, root_only):
+    """The Tree-GRU restatement (an extension: N-ary trees, label on the root) vs torch autograd in fp64."""
+    from helpers import make_gru_params, root_only_labels
+    H, E, V, C = 12, 10, 30, 3
+    parents, tok_job, label_job = make_tree_batch(21, 6, 2, 9, V, C, max_arity=arity)
+    if root_only:
+        label_job = root_only_labels(parents, label_job)
+    s = S.Schedule().load(parents, n_slots=K)
+    tb = tables_from_schedule(s)
+    params = make_gru_params(5, H, E, V, C, scale=0.4, bias_scale=0.1)
+    rows = parents.shape[0] if root_only else 0
+    tok, lab = tok_job[tb["t2j"]], label_job[tb["t2j"]]
+    got = oracle.treegru_fwd_bwd(tb, tok, lab, params, H, E, V, C, K=K, loss_rows=rows)
+    ref = treegru_autograd(tb, tok, lab, params, H, E, V, C, K=K, loss_rows=rows)
+    for k in KEYS:
+        assert rel_err(got[k], ref[k]) < 2e-5, k
