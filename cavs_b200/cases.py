@@ -6,7 +6,8 @@
     python -m cavs_b200.cases cell    one interior level of 16384 two-child vertices (hidden 1024, 4 slots, bf16 mode):
                                       child-state gather, cell forward, cell backward, child-gradient scatter
     python -m cavs_b200.cases shard   two training steps of the Tree-LSTM engine on one rank's shard of the
-                                      benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB)
+                                      benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB);
+                                      `shard 50` also times 50 further steps with CUDA events
 """
 from __future__ import annotations
 
@@ -112,8 +113,19 @@ def shard(steps: int = 2) -> None:
         eng.forward()
         eng.backward()
     print("loss", eng.read_loss(), "vertices", s.n_total, "levels", s.n_levels)
+    if steps > 2:   # timing run: forward + backward of the resident shard, CUDA events on the launching stream
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            eng.forward()
+            eng.backward()
+        b.record()
+        torch.cuda.synchronize()
+        print("ms_per_step", a.elapsed_time(b) / steps)
 
 
 if __name__ == "__main__":
-    {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard}[sys.argv[1]]()
+    fn = {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard}[sys.argv[1]]
+    fn(*(int(a) for a in sys.argv[2:3]))   # optional iteration / step count
     print("ok", sys.argv[1])

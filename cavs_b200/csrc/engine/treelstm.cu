@@ -33,6 +33,7 @@
 #include "host/sched_handle.h"
 #include "kernels/cell.h"
 #include "kernels/gemm.h"
+#include "kernels/launch.h"
 
 using namespace cavs_b200;
 
@@ -119,6 +120,9 @@ struct Carver {
 
 // Kernel classes reported by cavs_treelstm_profile_read.  "work" is algorithmic flops for the
 // GEMM class and algorithmic bytes (the kernel interface's inputs + outputs) for the others.
+// Levels of at most this many rows release their successors early whatever they are (chained launches).
+constexpr int kChainSmallRows = 4096;
+
 enum ProfClass { kProfGemm = 0, kProfCellFwd, kProfCellBwd, kProfGatherH, kProfScatterGrad, kProfLossHead, kProfEmbedFwd,
                  kProfEmbedBwd, kProfColumnSum, kProfCount };
 
@@ -454,6 +458,7 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   int rc;
   const double elt = static_cast<double>(e->elt);
   const int n_tok = bt.n_seg;        // distinct tokens of the batch
+  ChainHint(false);
   // X = Emb[distinct tokens]; A = X.W: one row per token, shared by every vertex carrying it.
   PROF(e, kProfEmbedFwd, static_cast<double>(n_tok) * (4 + 4.0 * E + elt * E), st,
        LaunchEmbedFwd(e->X, e->bf16, Emb, bt.seg_tok, n_tok, E, e->cfg.vocab, st));
@@ -467,17 +472,23 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
            LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, true, st));
       continue;
     }
+    // Chained launches: a kernel releases its successor early when that successor is a GEMM (one CTA per
+    // SM) or the level is small enough that placement does not matter.
+    const bool small = rows <= kChainSmallRows;
+    ChainHint(true);       // gather -> P GEMM -> Q GEMM
     // read K child h rows (fp32) + K indices, write S and HK
     PROF(e, kProfGatherH, static_cast<double>(rows) * (4.0 * K * H + 4.0 * K + elt * (1 + K) * H), st,
          LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, bt.child, nt, off, rows, H, K, st));
     const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
     if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn, &e->map_P))) return rc;
+    ChainHint(small);      // Q GEMM -> cell -> next level's gather: wide grid-stride kernels
     if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn, &e->map_Q))) return rc;
     // read the token row (4H) + index, P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
     PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (4 + 3 + K + 3 + K) + 4.0 * (K + 2)) + 4), st,
          LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, false, st));
   }
+  ChainHint(false);
   (void)rc;
   return CAVS_OK;
 }
@@ -499,6 +510,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   const void* U_f = U + static_cast<size_t>(3) * H * H * e->elt;
   int rc;
   const double elt = static_cast<double>(e->elt);
+  ChainHint(false);
   if (!e->WideHead()) {
     // Fused loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
     // write loss and the d(logits) row; d(h) = dz Wc is rebuilt inside the cell gradient, never stored.
@@ -539,6 +551,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     const double dh_bytes = e->FusedDh() ? 4.0 * kHeadDzPitch : 4.0 * H;
     const double cell_bytes = l == 0 ? rows * (H * (4.0 * (2 + 1) + elt * (3 + 4)) + dh_bytes)
                                      : rows * (H * (4.0 * (2 + 1 + K + K) + elt * (3 + K + 4 + K)) + dh_bytes);
+    ChainHint(l > 0);      // cell gradient -> ds GEMM -> dq GEMM
     PROF(e, kProfCellBwd, cell_bytes, st,
          LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->FusedDh() ? nullptr : e->dOut,
                        e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
@@ -548,10 +561,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
     if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k, &e->map_ds))) return rc;
+    ChainHint(rows <= kChainSmallRows);   // dq GEMM -> scatter -> next level's cell gradient
     if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq))) return rc;
     PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
          LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
   }
+  ChainHint(false);
   // Deferred gradients, one pass per weight over all rows (cavs/midend/batch_weight_updater.h:10-85).
   const int off1 = bt.n_levels > 1 ? bt.level_off[1] : n;   // first internal row
   const int n_int = n - off1;

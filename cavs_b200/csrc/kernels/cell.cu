@@ -132,7 +132,9 @@ __device__ __forceinline__ float TanhT(float x) {
 template <typename T, int K, int V>
 __global__ void __launch_bounds__(kThreads)
 GatherChildH(T* __restrict__ S, T* __restrict__ HK, const float* __restrict__ state, int state_pitch,
-             const int32_t* __restrict__ child, int n_total, int off, int rows, int H) {
+             const int32_t* __restrict__ child, int n_total, int off, int rows, int H, int chain_early) {
+  ChainRelease(chain_early);
+  ChainAcquire();
   const int hv = H / V;
   const long long total = static_cast<long long>(rows) * hv;
   const long long stride = static_cast<long long>(gridDim.x) * kThreads;
@@ -157,7 +159,9 @@ template <typename TP, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
 CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
         const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child,
-        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H) {
+        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H, int chain_early) {
+  ChainRelease(chain_early);
+  ChainAcquire();
   constexpr bool kFast = sizeof(TP) == 2;
   const int hv = H / V;
   const int G = (3 + K) * H;
@@ -226,7 +230,9 @@ __global__ void __launch_bounds__(kThreads)
 CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, float* __restrict__ dB_part,
         const float* __restrict__ dOut, const typename GateType<T>::type* __restrict__ gates, const float* __restrict__ state,
         const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H,
-        const float* __restrict__ dz, const float* __restrict__ Wc, int C) {
+        const float* __restrict__ dz, const float* __restrict__ Wc, int C, int chain_early) {
+  ChainRelease(chain_early);
+  ChainAcquire();
   __shared__ float fold[kThreads * 4 * V];
   extern __shared__ __align__(16) float s_wc[];   // kHead: the classifier [C, H]
   if (kHead) {
@@ -340,7 +346,9 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
 template <int K, int V>
 __global__ void __launch_bounds__(kThreads)
 ScatterChildGrad(float* __restrict__ mailbox, const float* __restrict__ ds, const float* __restrict__ dq,
-                 const int32_t* __restrict__ child, int n_total, int off, int rows, int H) {
+                 const int32_t* __restrict__ child, int n_total, int off, int rows, int H, int chain_early) {
+  ChainRelease(chain_early);
+  ChainAcquire();
   const int hv = H / V;
   const long long total = static_cast<long long>(rows) * hv;
   const long long stride = static_cast<long long>(gridDim.x) * kThreads;
@@ -400,8 +408,8 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
   const int v = VecWidth(H);
   const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
   DISPATCH_KV(K, v, {
-    if (bf16) GatherChildH<__nv_bfloat16, K, V><<<grid, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(S), static_cast<__nv_bfloat16*>(HK), state, state_pitch, child, n_total, off, rows, H);
-    else GatherChildH<float, K, V><<<grid, kThreads, 0, st>>>(static_cast<float*>(S), static_cast<float*>(HK), state, state_pitch, child, n_total, off, rows, H);
+    if (bf16) LaunchChained(GatherChildH<__nv_bfloat16, K, V>, dim3(grid), dim3(kThreads), 0, st, static_cast<__nv_bfloat16*>(S), static_cast<__nv_bfloat16*>(HK), state, state_pitch, child, n_total, off, rows, H, ChainEarly());
+    else LaunchChained(GatherChildH<float, K, V>, dim3(grid), dim3(kThreads), 0, st, static_cast<float*>(S), static_cast<float*>(HK), state, state_pitch, child, n_total, off, rows, H, ChainEarly());
   });
   CAVS_LAUNCH_CHECK("gather_child_h");
   return CAVS_OK;
@@ -417,12 +425,12 @@ int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const
     if (preact_bf16) {
       using TP = __nv_bfloat16;
       auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
-      if (leaf) CellFwd<TP, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
-      else CellFwd<TP, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
+      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
+      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
     } else {
       auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
-      if (leaf) CellFwd<float, K, V, true><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
-      else CellFwd<float, K, V, false><<<grid, kThreads, 0, st>>>(state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H);
+      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
+      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
@@ -451,9 +459,9 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
   const size_t head_smem = head ? static_cast<size_t>(C) * H * sizeof(float) : 0;
   CAVS_REQUIRE(head_smem <= 32 * 1024, CAVS_ERR_UNSUPPORTED, "treelstm_cell_bwd: classifier above 32 KB (classes * hidden <= 8192)");
 #define CELL_BWD(TT, GT, LEAF, HEAD)                                                                                   \
-  CellBwd<TT, K, V, LEAF, HEAD><<<grid, kThreads, head_smem, st>>>(static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
+  LaunchChained(CellBwd<TT, K, V, LEAF, HEAD>, dim3(grid), dim3(kThreads), head_smem, st, static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
                                                            static_cast<const GT*>(gates), state, child, parent, n_total, off,  \
-                                                           rows, H, dz, Wc, C)
+                                                           rows, H, dz, Wc, C, ChainEarly())
   DISPATCH_KV(K, v, {
     if (bf16) {
       if (leaf) { if (head) CELL_BWD(__nv_bfloat16, __half, true, true); else CELL_BWD(__nv_bfloat16, __half, true, false); }
@@ -474,7 +482,7 @@ int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, con
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
   const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
-  DISPATCH_KV(K, v, { ScatterChildGrad<K, V><<<grid, kThreads, 0, st>>>(mailbox, ds, dq, child, n_total, off, rows, H); });
+  DISPATCH_KV(K, v, { LaunchChained(ScatterChildGrad<K, V>, dim3(grid), dim3(kThreads), 0, st, mailbox, ds, dq, child, n_total, off, rows, H, ChainEarly()); });
   CAVS_LAUNCH_CHECK("scatter_child_grad");
   return CAVS_OK;
 }

@@ -90,7 +90,7 @@ int Launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, 
     CAVS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
     configured = true;
   }
-  kern<<<grid, tc::kThreads, S::kBytes, stream>>>(ma, mb, mc, p);
+  CAVS_CUDA(LaunchChained(kern, grid, dim3(tc::kThreads), S::kBytes, stream, ma, mb, mc, p));
   CAVS_LAUNCH_CHECK("gemm_bf16");
   return CAVS_OK;
 }
@@ -182,6 +182,7 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   p.n_splits = eff_splits;
   p.a_row_off = g.a_row_off;
   p.status = g.status;
+  p.chain_early = ChainEarly();
   if (eff_splits > 1) {
     p.c = g.scratch; p.ldc = g.n; p.split_stride = static_cast<long long>(g.m) * g.n; p.out_mode = tc::kStoreF32;
   } else {

@@ -24,6 +24,8 @@
 
 #include <cstdint>
 
+#include "kernels/launch.h"
+
 namespace cavs_b200 {
 namespace tc {
 
@@ -46,6 +48,7 @@ struct Params {
   int n_splits;       // K splits per tile (work items = tiles x splits)
   int a_row_off;      // added to the row coordinate of K-major A tiles (a level's view into an arena map)
   int tma_store;      // 1: the epilogue stages C in shared memory and writes it with TMA (map_c valid)
+  int chain_early;    // 1: release the following kernel at once (chained launches, kernels/launch.h)
   int* status;        // device word, set non-zero when a bounded wait expires
 };
 
@@ -248,6 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const Params p) {
   using S = Smem<kBN>;
+  ChainRelease(p.chain_early);
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -285,6 +289,9 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
+  // Everything above touched only this CTA's shared memory and TMEM; operands and outputs in global
+  // memory belong to the preceding kernel until here.
+  ChainAcquire();
 
   if (warp == 0) {
     if (ElectOne()) {
