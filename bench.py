@@ -114,6 +114,9 @@ class ClockSampler:
         return out
 
 
+GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.957e9 / 31744
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -218,11 +221,21 @@ def main():
     pinned = [tuple(torch.from_numpy(a).pin_memory() for a in p[:3]) for p in pool]
     host_sched = S.Schedule()
 
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    n_emb = wl["vocab"] * wl["embed"]
+
     def device_step():
         eng.forward()
         eng.backward()
         if world > 1:
-            dist.all_reduce(eng.grads)
+            # backward finishes the embedding gradient (the bulk of the buffer) first: its all-reduce runs on a
+            # second stream under the rest of backward; the weight gradients follow on the main stream.
+            main = torch.cuda.current_stream()
+            eng.wait_embed_grad(comm)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(eng.grads[:n_emb])
+            dist.all_reduce(eng.grads[n_emb:])
+            main.wait_stream(comm)
         eng.adagrad(acc, wl["lr"])
 
     host_ms = [0.0, 0.0, 0]   # schedule ms, pack + upload-enqueue ms, calls
@@ -313,8 +326,15 @@ def main():
     dominant = max(classes, key=lambda k: classes[k]["ms_per_step"])
     d = classes[dominant]
     if dominant == "gate_gemm":
+        # DRAM bytes per GEMM launch: captured with ncu on one rank's shard at 8 GPUs (all 81 GEMM launches of a step:
+        # 1.957 GB for 31,744 internal vertices, profiles/gemm_dram_traffic_shard_512_trees.md) and scaled by internal
+        # vertices, to which every per-level operand and output is proportional.
+        internal_rows = int(scheds[0].n_total - scheds[0].level_off[1]) if scheds[0].n_levels > 1 else 0
+        traffic = GEMM_DRAM_BYTES_PER_INTERNAL_ROW * internal_rows / max(d["launches_per_step"], 1)
         roofline = dict(bound="tensor", kernel="GemmBf16Kernel (all gate / gradient GEMMs of a step)", achieved=d["tflops"],
-                        peak=peaks["tflops"], unit="TFLOP/s", frac=d["frac"], traffic=None, peak_source=peaks["source"])
+                        peak=peaks["tflops"], unit="TFLOP/s", frac=d["frac"], traffic=traffic,
+                        traffic_unit="DRAM bytes per launch (ncu on a 512-tree shard, scaled by internal vertices)",
+                        peak_source=peaks["source"])
     else:
         roofline = dict(bound="hbm", kernel=dominant, achieved=d["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=d["frac"],
                         traffic=None, peak_source=peaks["source"])
@@ -337,7 +357,7 @@ def main():
                 e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8,
                          host_schedule_ms=host_ms[0] / max(host_ms[2], 1), host_pack_ms=host_ms[1] / max(host_ms[2], 1)),
                 gpu_launches=int(launches), loss_sum=loss_dev, clocks=clocks, roofline=roofline, kernel_classes=classes)
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:   # torchrun pins ranks to one host thread: the CPU arm runs at N=1 only
         rate, secs = cpu_baseline_sample(wl, args.sample_trees)
         import oracle
         line["cpu_baseline"] = dict(value=rate, unit="trees/s", cores=oracle.num_threads(), kind="port",

@@ -65,6 +65,7 @@ struct cavs_treelstm {
   // TMA maps of the per-level GEMM operands, encoded once over whole arenas (bf16 mode).
   TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
+  TcOperandMap map_Uiou_k64, map_Uf_k64;                     // the dgrad maps again for 64-column tiles (small levels)
   TcOperandMap map_P, map_Q, map_ds, map_dq;                 // level-local outputs (rows past a level's end are scratch)
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
   // ---- batches: two slots so the tables of the next batch can be packed and uploaded while the
@@ -81,6 +82,7 @@ struct cavs_treelstm {
   // upload into slot s, slot_done[s] the end of the last backward pass that read slot s.
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t copied[2] = {nullptr, nullptr}, slot_done[2] = {nullptr, nullptr};
+  cudaEvent_t emb_ready = nullptr;   // recorded in backward once the embedding gradient is complete
   bool slot_used[2] = {false, false};
   std::vector<int32_t> bucket, slot_of_token;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
@@ -223,13 +225,14 @@ size_t Carve(cavs_treelstm* e, void* base) {
 // `accumulate`: 0 store, 1 add into C, 2 store C as bf16 (bf16 mode only; the fp32 path always writes fp32).
 int Gemm(cavs_treelstm* e, void* c, long long ldc, int accumulate, const void* a, long long lda, bool a_t, const void* b,
          long long ldb, bool b_t, int m, int n, int k, bool split_ok, cudaStream_t st, const TcOperandMap* amap = nullptr,
-         int a_row_off = 0, const TcOperandMap* bmap = nullptr, const TcOperandMap* cmap = nullptr) {
+         int a_row_off = 0, const TcOperandMap* bmap = nullptr, const TcOperandMap* cmap = nullptr,
+         const TcOperandMap* bmap_small = nullptr) {
   if (m == 0 || n == 0 || k == 0) return CAVS_OK;
   if (e->bf16 && amap && bmap) {
     // Per-level GEMM through pre-encoded arena maps: `a` is not used, the level is a row offset.
     GemmBf16MappedArgs g;
     g.c = c; g.ldc = ldc; g.out_mode = accumulate;
-    g.a = amap; g.a_row_off = a_row_off; g.b = bmap; g.c_map = cmap;
+    g.a = amap; g.a_row_off = a_row_off; g.b = bmap; g.b_small = bmap_small; g.c_map = cmap;
     g.m = m; g.n = n; g.k = k;
     g.status = e->Status();
     PROF(e, kProfGemm, 2.0 * m * n * k, st, GemmBf16Mapped(g, st));
@@ -298,6 +301,8 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     if (!rc) rc = EncodeTcOperand(&e->map_Uf_mn, Uf, H, H, H, 1, 0);                                       // [k=H, n=H]
     if (!rc) rc = EncodeTcOperand(&e->map_Uiou_k, e->U_bf, H, 3 * H, 3 * H, 0, GemmBf16TileN(static_cast<int>(H)));  // [n=H, k=3H]
     if (!rc) rc = EncodeTcOperand(&e->map_Uf_k, Uf, H, H, H, 0, GemmBf16TileN(static_cast<int>(H)));       // [n=H, k=H]
+    if (!rc) rc = EncodeTcOperand(&e->map_Uiou_k64, e->U_bf, H, 3 * H, 3 * H, 0, 64);
+    if (!rc) rc = EncodeTcOperand(&e->map_Uf_k64, Uf, H, H, H, 0, 64);
     const long long L = cfg->max_level_rows;
     if (!rc) rc = EncodeTcOutput(&e->map_P, e->P, L, 3 * H, 3 * H, true);
     if (!rc) rc = EncodeTcOutput(&e->map_Q, e->Q, L * K, H, H, true);
@@ -315,6 +320,7 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     err = cudaEventCreateWithFlags(&e->copied[i], cudaEventDisableTiming);
     if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->slot_done[i], cudaEventDisableTiming);
   }
+  if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->emb_ready, cudaEventDisableTiming);
   if (err == cudaSuccess) err = cudaMemset(e->tail, 0, 4 * sizeof(float));
   if (err != cudaSuccess) {
     cudaFreeHost(e->h_idx);
@@ -333,6 +339,7 @@ extern "C" void cavs_treelstm_destroy(cavs_treelstm* e) {
     if (e->copied[i]) cudaEventDestroy(e->copied[i]);
     if (e->slot_done[i]) cudaEventDestroy(e->slot_done[i]);
   }
+  if (e->emb_ready) cudaEventDestroy(e->emb_ready);
   if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
   delete e;
 }
@@ -502,6 +509,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   float* g = e->grads;
   if (n == 0) {
     CAVS_CUDA(cudaMemsetAsync(g, 0, e->ParamCount() * sizeof(float), st));
+    CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
     return CAVS_OK;
   }
   const uint8_t* W = e->bf16 ? e->W_bf : reinterpret_cast<const uint8_t*>(e->params + e->OffW());
@@ -560,14 +568,28 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
-    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k, &e->map_ds))) return rc;
+    if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k, &e->map_ds, &e->map_Uiou_k64))) return rc;
     ChainHint(rows <= kChainSmallRows);   // dq GEMM -> scatter -> next level's cell gradient
-    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq))) return rc;
+    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq, &e->map_Uf_k64))) return rc;
     PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
          LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
   }
   ChainHint(false);
-  // Deferred gradients, one pass per weight over all rows (cavs/midend/batch_weight_updater.h:10-85).
+  // Deferred gradients, one pass per weight over all rows (cavs/midend/batch_weight_updater.h:10-85).  The
+  // embedding gradient -- by far the largest block of the flat gradient buffer -- comes first and is
+  // announced by an event, so a data-parallel caller can start reducing it across GPUs while the weight
+  // gradients below are still being computed (cavs_treelstm_wait_embed_grad).
+  // dA rows are first summed per distinct token (fixed order); dEmb[token] = dAtok W^T and dW = X^T dAtok
+  // then run over tokens, not vertices.
+  const int n_tok = bt.n_seg;
+  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
+       LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
+                             bt.seg_first_chunk, n_tok, e->emb_scratch, st));
+  if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
+  CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
+  if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
+  CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
+  if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
   const int off1 = bt.n_levels > 1 ? bt.level_off[1] : n;   // first internal row
   const int n_int = n - off1;
   float* dU = g + e->OffU();
@@ -589,19 +611,15 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     PROF(e, kProfColumnSum, static_cast<double>(n) * 4 * H * elt, st,
          LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
   }
-  // Input weights and embedding: dA rows are first summed per distinct token (fixed order), then
-  //   dW = X^T dAtok  and  dEmb[token] = dAtok W^T  run over tokens, not vertices.
-  const int n_tok = bt.n_seg;
-  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
-       LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
-                             bt.seg_first_chunk, n_tok, e->emb_scratch, st));
-  if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
-  if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
-  CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
-  if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
   (void)rc;
   CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
   e->slot_used[e->active] = true;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_wait_embed_grad(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e, CAVS_ERR_BAD_ARG, "treelstm_wait_embed_grad: null handle");
+  CAVS_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), e->emb_ready, 0));
   return CAVS_OK;
 }
 

@@ -112,6 +112,13 @@ size_t GemmBf16ScratchBytes(int m, int n, int splits) {
   return splits > 1 ? static_cast<size_t>(splits) * m * n * sizeof(float) : 0;
 }
 
+int GemmBf16TileNFor(int m, int n, int k) {
+  const int base = GemmBf16TileN(n);
+  const long long tiles64 = static_cast<long long>((m + tc::kBM - 1) / tc::kBM) * ((n + 63) / 64);
+  const int nkb = (k + tc::kBK - 1) / tc::kBK;
+  return (n > 64 && nkb <= 64 && tiles64 <= SmCount()) ? 64 : base;   // one wave of 64-column tiles
+}
+
 int GemmBf16SplitsFor(int m, int n, int k) {
   // The kernel is persistent over (tile, split) work items.  Splitting K costs partial traffic, a
   // plain-store epilogue and a reduce pass, so it is used only when the tile grid leaves more than a
@@ -163,15 +170,21 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   CAVS_REQUIRE(g.out_mode >= 0 && g.out_mode <= 2, CAVS_ERR_BAD_ARG, "gemm_bf16: bad out_mode");
   CAVS_REQUIRE(g.ldc >= g.n, CAVS_ERR_BAD_ARG, "gemm_bf16: ldc < n");
   CAVS_REQUIRE(g.a_row_off == 0 || g.a->major == tc::kMajorK, CAVS_ERR_BAD_ARG, "gemm_bf16: row offsets need a K-major A");
-  const int bn = GemmBf16TileN(g.n);
-  CAVS_REQUIRE(g.a->major != tc::kMajorK || g.a->tile_rows == tc::kBM, CAVS_ERR_BAD_ARG, "gemm_bf16: A map was not encoded for 128-row tiles");
-  CAVS_REQUIRE(g.b->major != tc::kMajorK || g.b->tile_rows == bn, CAVS_ERR_BAD_ARG, "gemm_bf16: B map was encoded for a different N tile");
   const int splits = std::max(1, g.splits);
+  int bn = GemmBf16TileN(g.n);
+  const TcOperandMap* bmap = g.b;
+  if (splits == 1 && GemmBf16TileNFor(g.m, g.n, g.k) == 64) {
+    if (g.b->major == tc::kMajorMN) bn = 64;
+    else if (g.b->tile_rows == 64) bn = 64;
+    else if (g.b_small != nullptr && g.b_small->major == tc::kMajorK && g.b_small->tile_rows == 64) { bn = 64; bmap = g.b_small; }
+  }
+  CAVS_REQUIRE(g.a->major != tc::kMajorK || g.a->tile_rows == tc::kBM, CAVS_ERR_BAD_ARG, "gemm_bf16: A map was not encoded for 128-row tiles");
+  CAVS_REQUIRE(bmap->major != tc::kMajorK || bmap->tile_rows == bn, CAVS_ERR_BAD_ARG, "gemm_bf16: B map was encoded for a different N tile");
   CAVS_REQUIRE(splits == 1 || g.out_mode != tc::kStoreBf16, CAVS_ERR_BAD_ARG, "gemm_bf16: split-K needs an fp32 output");
   CAVS_REQUIRE(splits == 1 || (g.scratch && g.scratch_bytes >= GemmBf16ScratchBytes(g.m, g.n, splits)), CAVS_ERR_CAPACITY,
                "gemm_bf16: split-K scratch too small");
   const CUtensorMap& ma = *reinterpret_cast<const CUtensorMap*>(g.a->bytes);
-  const CUtensorMap& mb = *reinterpret_cast<const CUtensorMap*>(g.b->bytes);
+  const CUtensorMap& mb = *reinterpret_cast<const CUtensorMap*>(bmap->bytes);
 
   const int nkb = (g.k + tc::kBK - 1) / tc::kBK;
   const int kb_per = (nkb + splits - 1) / splits;
@@ -204,8 +217,9 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   }
   const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tc::kBM - 1) / tc::kBM) * eff_splits;
   dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
-  int rc = bn == 256 ? Dispatch<256>(g.a->major, g.b->major, ma, mb, *mc, p, grid, stream)
-                     : Dispatch<128>(g.a->major, g.b->major, ma, mb, *mc, p, grid, stream);
+  int rc = bn == 256   ? Dispatch<256>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
+           : bn == 128 ? Dispatch<128>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
+                       : Dispatch<64>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream);
   if (rc) return rc;
   if (eff_splits > 1) {
     const size_t total = static_cast<size_t>(g.m) * g.n;
@@ -224,7 +238,8 @@ int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
   CAVS_REQUIRE(g.a && g.b && g.c, CAVS_ERR_BAD_ARG, "gemm_bf16: null pointer");
   TcOperandMap ma, mb;
   if (int rc = EncodeTcOperand(&ma, g.a, g.m, g.k, g.lda, g.a_major, tc::kBM)) return rc;
-  if (int rc = EncodeTcOperand(&mb, g.b, g.n, g.k, g.ldb, g.b_major, GemmBf16TileN(g.n))) return rc;
+  const int tile_n = std::max(1, g.splits) == 1 ? GemmBf16TileNFor(g.m, g.n, g.k) : GemmBf16TileN(g.n);
+  if (int rc = EncodeTcOperand(&mb, g.b, g.n, g.k, g.ldb, g.b_major, tile_n)) return rc;
   GemmBf16MappedArgs a;
   a.c = g.c; a.ldc = g.ldc; a.out_mode = g.out_mode;
   a.a = &ma; a.b = &mb;

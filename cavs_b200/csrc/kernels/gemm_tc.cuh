@@ -57,7 +57,7 @@ struct Smem {
   static constexpr int kATile = kBM * kBK * 2;
   static constexpr int kBTile = kBN * kBK * 2;
   static constexpr int kStage = kATile + kBTile;
-  static constexpr int kStages = (kBN == 256) ? 4 : 6;
+  static constexpr int kStages = (kBN == 256) ? 4 : (kBN == 128 ? 6 : 7);
   // Epilogue staging: 4 warps x 2 slots x (32 rows x 128 bytes), 128-byte swizzled for the TMA store.
   static constexpr int kCSlot = 32 * 128;
   static constexpr int kCOff = kStages * kStage;

@@ -85,6 +85,10 @@ class TreeLSTM:
     def backward(self) -> None:
         check(lib().cavs_treelstm_backward(self._h, _stream()))
 
+    def wait_embed_grad(self, stream) -> None:
+        """Makes `stream` (a torch.cuda.Stream) wait for the embedding-gradient block of the last backward()."""
+        check(lib().cavs_treelstm_wait_embed_grad(self._h, ctypes.c_void_p(stream.cuda_stream)))
+
     def read_loss(self) -> float:
         out = ctypes.c_float()
         status = ctypes.c_int()

@@ -248,6 +248,11 @@ CAVS_API int cavs_treelstm_forward(cavs_treelstm* e, void* stream);
 /* Loss head, level loop in reverse, deferred weight / bias / embedding gradients (overwrites grads). */
 CAVS_API int cavs_treelstm_backward(cavs_treelstm* e, void* stream);
 /* Copies the loss sum and the device status word to the host; synchronises `stream`. */
+/* Makes `stream` wait until the embedding-gradient block (the first vocab*embed floats of the bound gradient
+ * buffer) written by the most recent cavs_treelstm_backward is complete.  backward produces that block before
+ * the weight gradients, so a data-parallel caller can start its cross-GPU reduction on another stream
+ * while the rest of backward is still running.  Does not block the host. */
+CAVS_API int cavs_treelstm_wait_embed_grad(cavs_treelstm* e, void* stream);
 CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int* status_host, void* stream);
 /* Per-kernel-class timing with CUDA events on the launching stream.  While enabled, every launch
  * of forward / backward is bracketed by two events.  profile_read sums, per class, the elapsed

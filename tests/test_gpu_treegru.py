@@ -67,3 +67,16 @@ def test_bf16_parity(cuda):
     for k in KEYS:
         assert rel_err(out[k], ref32[k]) < 2e-2, k
         assert rel_err(out[k], refbf[k]) < 5e-3, k
+
+
+def test_nary_treegru_configuration_dims_bf16(cuda):
+    """The N-ary Tree-GRU configuration's dimensions (hidden 1024, embedding 512, vocabulary 32,000, 1-4 children,
+    8-128 leaves, 2-class loss on the root) on a batch small enough for the CPU oracle."""
+    H, E, V, C, K, batch = 1024, 512, 32000, 2, 4, 6
+    parents, tok_job, label_job = make_tree_batch(4040, batch, 8, 128, V, C, max_arity=4)
+    label_job = root_only_labels(parents, label_job)
+    params = make_gru_params(17, H, E, V, C, scale=0.03, bias_scale=0.02)
+    _, out, _, ref32, refbf = _both(parents, tok_job, label_job, params, H, E, V, C, K, bf16=True, loss_rows=batch)
+    for k in KEYS:
+        assert rel_err(out[k], ref32[k]) < 2e-2, k
+        assert rel_err(out[k], refbf[k]) < 5e-3, k

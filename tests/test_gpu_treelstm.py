@@ -120,3 +120,27 @@ def test_capacity_errors(cuda):
     with pytest.raises(CavsError) as e:
         eng.load_batch(s, tok_job, label_job)
     assert e.value.status == 3
+
+
+def test_embedding_gradient_is_announced_before_the_weight_gradients(cuda):
+    """A second stream that waits on cavs_treelstm_wait_embed_grad sees the finished embedding-gradient block
+    (the data-parallel caller starts its all-reduce there while backward continues)."""
+    H, E, V, C = 64, 32, 300, 5
+    parents, tok_job, label_job = make_tree_batch(77, 24, 2, 30, V, C)
+    params = make_params(3, H, E, V, C, scale=0.1, bias_scale=0.05)
+    s = S.Schedule().load(parents)
+    eng = TreeLSTM(H, E, V, C, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+    eng.set_params(params)
+    eng.load_batch(s, tok_job, label_job)
+    side = torch.cuda.Stream()
+    for _ in range(3):
+        eng.grads.fill_(7.0)          # stale values a too-early reader would see
+        eng.forward()
+        eng.backward()
+        eng.wait_embed_grad(side)
+        with torch.cuda.stream(side):
+            early = eng.grads[:V * E].clone()
+        torch.cuda.synchronize()
+        assert torch.equal(early, eng.grads[:V * E])
+    ref = _oracle(s, tok_job, label_job, params, H, E, V, C)
+    assert rel_err(early.cpu().numpy(), ref["dEmb"]) < 1e-5
