@@ -3,7 +3,7 @@
 
     python -m cavs_b200.cases gemm    one per-level gate product: [65536,1024] x [1024,3072], bf16 in / bf16 out
     python -m cavs_b200.cases loss    the fused loss head on 65536 rows of hidden size 1024, 5 classes
-    python -m cavs_b200.cases cell    one interior level of 16384 two-child vertices (hidden 1024, 4 slots, bf16 mode):
+    python -m cavs_b200.cases cell    one interior level of 32768 two-child vertices (hidden 1024, 2 slots, bf16 mode):
                                       child-state gather, cell forward, cell backward, child-gradient scatter
     python -m cavs_b200.cases shard   two training steps of the Tree-LSTM engine on one rank's shard of the
                                       benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB);
@@ -64,7 +64,7 @@ def loss(iters: int = 3) -> None:
 
 def cell(iters: int = 3) -> None:
     L, dev = lib(), torch.device("cuda")
-    R, H, K = 16384, 1024, 4
+    R, H, K = 32768, 1024, 2
     n = 3 * R                                   # children occupy rows [0, 2R), the level rows [2R, 3R)
     bf, hf = torch.bfloat16, torch.float16
     child = torch.full((K, n), -1, dtype=torch.int32)

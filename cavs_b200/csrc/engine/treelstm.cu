@@ -58,10 +58,17 @@ struct cavs_treelstm {
   // wide loss head (classes > 8): logits / dz [N, Cp] fp32, bf16 copies of dz and of the pushed h rows
   float* logits = nullptr;
   uint8_t *dz_bf = nullptr, *h_bf = nullptr;
+  // Layer stacking: dense per-vertex inputs instead of an embedding table (cfg.vocab == 0) and an
+  // output gradient handed in by the layer above instead of a loss head (cfg.classes == 0).
+  const float* x_dense = nullptr;   // [n, embed] rows in tensor-id order, pitch x_pitch
+  long long x_pitch = 0;
+  const float* dh_ext = nullptr;    // [n, hidden] dense
+  bool Dense() const { return cfg.vocab == 0; }
+  bool Headless() const { return cfg.classes == 0; }
   int Cp() const { return (cfg.classes + 7) & ~7; }
   bool WideHead() const { return cfg.classes > 8; }
   // d(pushed h) is rebuilt inside the cell gradient from d(logits) rows when the classifier fits its shared-memory copy
-  bool FusedDh() const { return !WideHead() && static_cast<long long>(cfg.classes) * cfg.hidden <= 8192; }
+  bool FusedDh() const { return !Headless() && !WideHead() && static_cast<long long>(cfg.classes) * cfg.hidden <= 8192; }
   // TMA maps of the per-level GEMM operands, encoded once over whole arenas (bf16 mode).
   TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
@@ -146,7 +153,8 @@ enum ProfClass { kProfGemm = 0, kProfCellFwd, kProfCellBwd, kProfGatherH, kProfS
 
 int CheckConfig(const cavs_treelstm_config* c) {
   CAVS_REQUIRE(c, CAVS_ERR_BAD_ARG, "treelstm: null config");
-  CAVS_REQUIRE(c->hidden > 0 && c->embed > 0 && c->vocab > 0 && c->classes > 0, CAVS_ERR_BAD_ARG, "treelstm: sizes must be positive");
+  CAVS_REQUIRE(c->hidden > 0 && c->embed > 0 && c->vocab >= 0 && c->classes >= 0, CAVS_ERR_BAD_ARG,
+               "treelstm: hidden and embed must be positive, vocab and classes non-negative");
   CAVS_REQUIRE(c->n_slots >= 1 && c->n_slots <= kMaxSlots, CAVS_ERR_BAD_ARG, "treelstm: child slots must be 1..4");
   CAVS_REQUIRE(c->max_vertices > 0 && c->max_level_rows > 0 && c->max_level_rows <= c->max_vertices, CAVS_ERR_BAD_ARG,
                "treelstm: capacities must be positive and max_level_rows <= max_vertices");
@@ -156,7 +164,8 @@ int CheckConfig(const cavs_treelstm_config* c) {
   return CAVS_OK;
 }
 
-size_t MaxSegments(const cavs_treelstm_config& c) { return std::min<size_t>(c.max_vertices, c.vocab); }
+// Rows of the input projection: distinct tokens of a batch, or every vertex with dense inputs.
+size_t MaxSegments(const cavs_treelstm_config& c) { return c.vocab == 0 ? c.max_vertices : std::min<size_t>(c.max_vertices, c.vocab); }
 size_t MaxChunks(const cavs_treelstm_config& c) { return MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
@@ -189,14 +198,14 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->dA = w.Take<uint8_t>(N * 4 * H * elt);
   e->ZF = w.Take<uint8_t>(N * K * H * elt);
   e->A = w.Take<uint8_t>(T * 4 * H * elt);
-  e->dAtok = w.Take<uint8_t>(T * 4 * H * elt);
+  e->dAtok = w.Take<uint8_t>(c.vocab == 0 ? 0 : T * 4 * H * elt);
   e->P = w.Take<uint8_t>(L * 3 * H * elt);
   e->Q = w.Take<uint8_t>(L * K * H * elt);
   e->gates = w.Take<uint8_t>(N * (3 + K) * H * elt);
   e->state = w.Take<float>(N * 2 * H);
   e->mailbox = w.Take<float>(N * 2 * H);
   // d(pushed h): materialised only by the wide loss head; the fused head hands d(logits) rows (dz8) to the cell gradient
-  e->dOut = w.Take<float>(e->FusedDh() ? 0 : N * H);
+  e->dOut = w.Take<float>(e->FusedDh() || e->Headless() ? 0 : N * H);
   e->dz8 = w.Take<float>(e->FusedDh() ? N * kHeadDzPitch : 0);
   e->ds = w.Take<float>(L * H);
   e->dq = w.Take<float>(L * K * H);
@@ -206,13 +215,13 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->tail = w.Take<float>(4);
   const bool wide = c.classes > 8;
   const size_t Cp = (c.classes + 7) & ~static_cast<size_t>(7);
-  e->loss_scratch = w.Take<float>(wide ? 0 : LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
+  e->loss_scratch = w.Take<float>(wide || c.classes == 0 ? 0 : LossHeadScratchBytes(c.hidden, c.classes) / sizeof(float));
   e->logits = w.Take<float>(wide ? N * Cp : 0);
   e->dz_bf = w.Take<uint8_t>(wide && c.gemm_bf16 ? N * Cp * 2 : 0);
   e->h_bf = w.Take<uint8_t>(wide && c.gemm_bf16 ? N * H * 2 : 0);
   e->Wc_bf = w.Take<uint8_t>(wide && c.gemm_bf16 ? static_cast<size_t>(c.classes) * H * 2 : 0);
   e->col_scratch = w.Take<float>(ColumnSumScratchBytes(std::max(4 * c.hidden, c.classes)) / sizeof(float));
-  e->emb_scratch = w.Take<float>(MaxChunks(c) * 4 * H);
+  e->emb_scratch = w.Take<float>(c.vocab == 0 ? 0 : MaxChunks(c) * 4 * H);
   e->splitk_bytes = SplitKBytes(c);
   e->splitk_scratch = w.Take<float>(e->splitk_bytes / sizeof(float));
   e->W_bf = w.Take<uint8_t>(c.gemm_bf16 ? static_cast<size_t>(E) * 4 * H * 2 : 0);
@@ -368,7 +377,9 @@ extern "C" int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream) {
 
 extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job,
                                         const int32_t* label_job, int loss_rows, void* stream) {
-  CAVS_REQUIRE(e && s && s->loaded && tok_job && label_job, CAVS_ERR_BAD_ARG, "treelstm_load_batch: null pointer or empty schedule");
+  CAVS_REQUIRE(e && s && s->loaded, CAVS_ERR_BAD_ARG, "treelstm_load_batch: null pointer or empty schedule");
+  CAVS_REQUIRE((tok_job || e->Dense()) && (label_job || e->Headless()), CAVS_ERR_BAD_ARG,
+               "treelstm_load_batch: tokens are required with an embedding table, labels with a loss head");
   const LevelSchedule& sch = s->impl;
   const int n = sch.n_scheduled(), nt = sch.n_total(), K = e->cfg.n_slots;
   CAVS_REQUIRE(sch.n_slots() == K, CAVS_ERR_BAD_ARG, "treelstm_load_batch: schedule was built with a different slot count");
@@ -403,16 +414,22 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   // Pull (op_impl_graphop.cu:214-254) and the label permutation FunctionPopRet implies
   // (:275-327) are folded into this host-side reorder to tensor-id order.
   for (int t = 0; t < n; ++t) {
-    int id = tok_job[t2j[t]];
+    const int id = tok_job ? tok_job[t2j[t]] : 0;
     h_tok[t] = (id < 0 || id >= V) ? 0 : id;
-    h_label[t] = label_job[t2j[t]];
+    h_label[t] = label_job ? label_job[t2j[t]] : -1;
   }
+  int n_seg = 0, n_chunks = 0;
+  if (e->Dense()) {
+    // Dense inputs: one projection row per vertex, no token grouping.
+    bt.chunk_off = bt.seg_first_chunk = bt.seg_tok = nullptr;
+    bt.tok_slot = nullptr;
+    n_seg = n;
+    CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
+  } else {
   // Stable counting sort of rows by token -> segments and chunks for the embedding gradient.
   e->bucket.assign(static_cast<size_t>(V) + 1, 0);
   for (int t = 0; t < n; ++t) ++e->bucket[h_tok[t] + 1];
-  int n_seg = 0;
   for (int v = 0; v < V; ++v) { if (e->bucket[v + 1]) ++n_seg; e->bucket[v + 1] += e->bucket[v]; }
-  int n_chunks = 0;
   for (int v = 0; v < V; ++v) n_chunks += (e->bucket[v + 1] - e->bucket[v] + kEmbedChunk - 1) / kEmbedChunk;
   int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_off);
   int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.seg_first_chunk);
@@ -433,6 +450,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   for (int t = 0; t < n; ++t) {
     h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
     h_slot[t] = e->slot_of_token[h_tok[t]];
+  }
   }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
   // The device half is free once the last backward pass that read it has finished.
@@ -466,11 +484,23 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   const double elt = static_cast<double>(e->elt);
   const int n_tok = bt.n_seg;        // distinct tokens of the batch
   ChainHint(false);
-  // X = Emb[distinct tokens]; A = X.W: one row per token, shared by every vertex carrying it.
-  PROF(e, kProfEmbedFwd, static_cast<double>(n_tok) * (4 + 4.0 * E + elt * E), st,
-       LaunchEmbedFwd(e->X, e->bf16, Emb, bt.seg_tok, n_tok, E, e->cfg.vocab, st));
   const int pre = e->bf16 ? 2 : 0;   // pre-activations are stored in the GEMM operand precision
-  if ((rc = Gemm(e, e->A, 4 * H, pre, e->X, E, false, W, 4 * H, false, n_tok, 4 * H, E, false, st))) return rc;
+  const void* Xop = e->X;
+  long long ldx = E;
+  if (e->Dense()) {
+    // Dense inputs (a stacked layer): one projection row per vertex, A = x.W over all rows.
+    CAVS_REQUIRE(e->x_dense, CAVS_ERR_BAD_ARG, "treelstm_forward: dense inputs not set (cavs_treelstm_set_dense_input)");
+    if (e->bf16) {
+      if ((rc = LaunchCastRowsBf16(e->X, e->x_dense, n, E, e->x_pitch, st))) return rc;
+    } else {
+      Xop = e->x_dense; ldx = e->x_pitch;
+    }
+  } else {
+    // X = Emb[distinct tokens]; A = X.W: one row per token, shared by every vertex carrying it.
+    PROF(e, kProfEmbedFwd, static_cast<double>(n_tok) * (4 + 4.0 * E + elt * E), st,
+         LaunchEmbedFwd(e->X, e->bf16, Emb, bt.seg_tok, n_tok, E, e->cfg.vocab, st));
+  }
+  if ((rc = Gemm(e, e->A, 4 * H, pre, Xop, ldx, false, W, 4 * H, false, n_tok, 4 * H, E, false, st))) return rc;
   for (int l = 0; l < bt.n_levels; ++l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     if (l == 0) {
@@ -519,7 +549,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   int rc;
   const double elt = static_cast<double>(e->elt);
   ChainHint(false);
-  if (!e->WideHead()) {
+  if (e->Headless()) {
+    // No loss head: d(h) of every vertex comes from the layer above.
+    CAVS_REQUIRE(e->dh_ext, CAVS_ERR_BAD_ARG, "treelstm_backward: output gradient not set (cavs_treelstm_set_output_grad)");
+    CAVS_CUDA(cudaMemsetAsync(e->tail, 0, sizeof(float), st));
+    CAVS_CUDA(cudaMemsetAsync(e->loss, 0, static_cast<size_t>(n) * sizeof(float), st));
+  } else if (!e->WideHead()) {
     // Fused loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
     // write loss and the d(logits) row; d(h) = dz Wc is rebuilt inside the cell gradient, never stored.
     const bool fdh = e->FusedDh();
@@ -561,7 +596,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
                                      : rows * (H * (4.0 * (2 + 1 + K + K) + elt * (3 + K + 4 + K)) + dh_bytes);
     ChainHint(l > 0);      // cell gradient -> ds GEMM -> dq GEMM
     PROF(e, kProfCellBwd, cell_bytes, st,
-         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->FusedDh() ? nullptr : e->dOut,
+         LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->FusedDh() ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
                        e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
                        e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C));
     if (l == 0) break;
@@ -582,14 +617,24 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   // dA rows are first summed per distinct token (fixed order); dEmb[token] = dAtok W^T and dW = X^T dAtok
   // then run over tokens, not vertices.
   const int n_tok = bt.n_seg;
-  PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
-       LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
-                             bt.seg_first_chunk, n_tok, e->emb_scratch, st));
-  if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
-  CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
-  if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
-  CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
-  if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
+  if (e->Dense()) {
+    // Dense inputs: d(x) = dA W^T for every vertex (the layer below takes it as its output gradient) and
+    // dW = x^T dA over all rows.
+    const void* Xop = e->bf16 ? static_cast<const void*>(e->X) : e->x_dense;
+    const long long ldx = e->bf16 ? E : e->x_pitch;
+    if ((rc = Gemm(e, e->dX, E, 0, e->dA, 4 * H, false, W, 4 * H, true, n, E, 4 * H, false, st))) return rc;
+    CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
+    if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, Xop, ldx, true, e->dA, 4 * H, false, E, 4 * H, n, true, st))) return rc;
+  } else {
+    PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
+         LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
+                               bt.seg_first_chunk, n_tok, e->emb_scratch, st));
+    if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
+    CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
+    if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
+    CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
+    if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
+  }
   const int off1 = bt.n_levels > 1 ? bt.level_off[1] : n;   // first internal row
   const int n_int = n - off1;
   float* dU = g + e->OffU();
@@ -614,6 +659,22 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   (void)rc;
   CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
   e->slot_used[e->active] = true;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_set_dense_input(cavs_treelstm* e, const float* x, long long pitch) {
+  CAVS_REQUIRE(e && e->Dense(), CAVS_ERR_BAD_ARG, "treelstm_set_dense_input: the engine was created with an embedding table (vocab > 0)");
+  CAVS_REQUIRE(x && pitch >= e->cfg.embed && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && pitch % 4 == 0, CAVS_ERR_BAD_ARG,
+               "treelstm_set_dense_input: rows must be 16-byte aligned with pitch >= embed");
+  e->x_dense = x;
+  e->x_pitch = pitch;
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_set_output_grad(cavs_treelstm* e, const float* dh) {
+  CAVS_REQUIRE(e && e->Headless(), CAVS_ERR_BAD_ARG, "treelstm_set_output_grad: the engine was created with a loss head (classes > 0)");
+  CAVS_REQUIRE(dh && (reinterpret_cast<uintptr_t>(dh) & 15u) == 0, CAVS_ERR_BAD_ARG, "treelstm_set_output_grad: rows must be 16-byte aligned");
+  e->dh_ext = dh;
   return CAVS_OK;
 }
 
@@ -673,6 +734,9 @@ extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_p
       *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;
     case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
     case 4: *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
+    case 5:                                                                      // d(loss)/d(dense input)
+      if (!e->Dense()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(x) exists only with dense inputs");
+      *dev_ptr = e->dX; *bytes = n * e->cfg.embed * sizeof(float); break;
     default: return Fail(CAVS_ERR_BAD_ARG, "treelstm_peek: unknown array id");
   }
   return CAVS_OK;

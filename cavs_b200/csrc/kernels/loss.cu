@@ -414,15 +414,26 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
   }
 }
 
+// Eight lanes share one output element: lane q sums the partials p = q, q + 8, ... in order, then the eight
+// sub-sums are folded in a fixed butterfly, so the result does not depend on the launch shape.
+constexpr int kReduceLanes = 8;
 __global__ void __launch_bounds__(kThreads)
 LossHeadReduce(float* __restrict__ dWc, float* __restrict__ dbc, float* __restrict__ loss_sum,
                const float* __restrict__ partial, int n_parts, int CH, int C, int stride, int accumulate) {
   const int width = CH + C + 1;
-  for (int i = blockIdx.x * kThreads + threadIdx.x; i < width; i += gridDim.x * kThreads) {
+  const int q = threadIdx.x % kReduceLanes;
+  const int per_cta = kThreads / kReduceLanes;
+  const int padded = (width + per_cta - 1) / per_cta * per_cta;   // whole groups stay in the loop together
+  for (int i = blockIdx.x * per_cta + threadIdx.x / kReduceLanes; i < padded; i += gridDim.x * per_cta) {
     float s = 0.0f;
-    for (int p = 0; p < n_parts; ++p) s += partial[static_cast<size_t>(p) * stride + i];
-    float* dst = i < CH ? dWc + i : (i < CH + C ? dbc + (i - CH) : loss_sum);
-    if (dst) *dst = accumulate ? *dst + s : s;
+    if (i < width)
+      for (int p = q; p < n_parts; p += kReduceLanes) s += partial[static_cast<size_t>(p) * stride + i];
+#pragma unroll
+    for (int o = kReduceLanes / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (q == 0 && i < width) {
+      float* dst = i < CH ? dWc + i : (i < CH + C ? dbc + (i - CH) : loss_sum);
+      if (dst) *dst = accumulate ? *dst + s : s;
+    }
   }
 }
 
@@ -466,7 +477,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
 #undef STREAM_CASE
     CAVS_LAUNCH_CHECK("loss_head stream");
     const int swidth = C * H + C + 1;
-    LossHeadReduce<<<std::min((swidth + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, sgrid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
+    LossHeadReduce<<<std::min((swidth * kReduceLanes + kThreads - 1) / kThreads, 4 * SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, sgrid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
     CAVS_LAUNCH_CHECK("loss_head reduce");
     return CAVS_OK;
   }
@@ -497,7 +508,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
 #undef LOSS_CASE
   CAVS_LAUNCH_CHECK("loss_head");
   const int width = C * H + C + 1;
-  LossHeadReduce<<<std::min((width + kThreads - 1) / kThreads, SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
+  LossHeadReduce<<<std::min((width * kReduceLanes + kThreads - 1) / kThreads, 4 * SmCount()), kThreads, 0, st>>>(dWc, dbc, loss_sum, scratch, grid, C * H, C, PartialStride(C, H), accumulate ? 1 : 0);
   CAVS_LAUNCH_CHECK("loss_head reduce");
   return CAVS_OK;
 }

@@ -66,16 +66,19 @@ class TreeLSTM:
 
     def set_params(self, params: dict) -> None:
         for k in self.PARAM_NAMES:
-            self.view(self.params, k).copy_(torch.from_numpy(np.ascontiguousarray(params[k], np.float32).ravel()))
+            if self.sizes[k]:
+                self.view(self.params, k).copy_(torch.from_numpy(np.ascontiguousarray(params[k], np.float32).ravel()))
         self.refresh_weights()
 
     def refresh_weights(self) -> None:
         check(lib().cavs_treelstm_refresh_weights(self._h, _stream()))
 
-    def load_batch(self, sched: Schedule, tok_job: np.ndarray, label_job: np.ndarray, loss_rows: int = 0) -> None:
-        tok_job = np.ascontiguousarray(tok_job, np.int32)
-        label_job = np.ascontiguousarray(label_job, np.int32)
-        assert tok_job.size >= sched.n_total and label_job.size >= sched.n_total
+    def load_batch(self, sched: Schedule, tok_job=None, label_job=None, loss_rows: int = 0) -> None:
+        # tokens are ignored by a dense-input engine (vocab == 0), labels by a headless one (classes == 0)
+        tok_job = np.ascontiguousarray(tok_job, np.int32) if self.cfg.vocab else None
+        label_job = np.ascontiguousarray(label_job, np.int32) if self.cfg.classes else None
+        assert tok_job is None or tok_job.size >= sched.n_total
+        assert label_job is None or label_job.size >= sched.n_total
         check(lib().cavs_treelstm_load_batch(self._h, sched._h, ptr(tok_job), ptr(label_job), loss_rows, _stream()))
         self.n = sched.n_scheduled
 
@@ -84,6 +87,25 @@ class TreeLSTM:
 
     def backward(self) -> None:
         check(lib().cavs_treelstm_backward(self._h, _stream()))
+
+    def device_view(self, what: int, shape) -> torch.Tensor:
+        """A float32 view of one of the engine's arrays (cavs_treelstm_peek) inside its workspace tensor."""
+        p, nbytes = ctypes.c_void_p(), ctypes.c_size_t()
+        check(lib().cavs_treelstm_peek(self._h, what, ctypes.byref(p), ctypes.byref(nbytes)))
+        off = p.value - self.workspace.data_ptr()
+        return self.workspace[off:off + nbytes.value].view(torch.float32).view(*shape)
+
+    def set_dense_input(self, x: torch.Tensor) -> None:
+        """x: float32 device rows [n, embed] (any row pitch), e.g. the h columns of the layer below."""
+        assert x.dtype == torch.float32 and x.stride(1) == 1
+        self._x_keep = x
+        check(lib().cavs_treelstm_set_dense_input(self._h, ctypes.c_void_p(x.data_ptr()), ctypes.c_longlong(x.stride(0))))
+
+    def set_output_grad(self, dh: torch.Tensor) -> None:
+        """dh: dense float32 device rows [n, hidden], e.g. d(x) of the layer above."""
+        assert dh.dtype == torch.float32 and dh.is_contiguous()
+        self._dh_keep = dh
+        check(lib().cavs_treelstm_set_output_grad(self._h, ctypes.c_void_p(dh.data_ptr())))
 
     def wait_embed_grad(self, stream) -> None:
         """Makes `stream` (a torch.cuda.Stream) wait for the embedding-gradient block of the last backward()."""

@@ -248,6 +248,15 @@ CAVS_API int cavs_treelstm_forward(cavs_treelstm* e, void* stream);
 /* Loss head, level loop in reverse, deferred weight / bias / embedding gradients (overwrites grads). */
 CAVS_API int cavs_treelstm_backward(cavs_treelstm* e, void* stream);
 /* Copies the loss sum and the device status word to the host; synchronises `stream`. */
+/* Layer stacking (apps/lstm stacks LSTM layers by feeding a layer's h to the next layer's input).  An engine
+ * created with vocab == 0 has no embedding table: its inputs are dense rows x [n, embed] in tensor-id order
+ * (pitch in floats), set here before forward -- typically the h columns of the layer below (cavs_treelstm_peek
+ * array 0, pitch 2*hidden).  Its backward leaves d(loss)/d(x) in peek array 5 ([n, embed], dense).  An engine
+ * created with classes == 0 has no loss head: d(loss)/d(h) [n, hidden] (dense) is set here before backward --
+ * typically array 5 of the layer above.  Flat parameter layout is unchanged; the absent blocks are empty.
+ * Both engines load the same schedule; tokens may be NULL for a dense layer, labels for a headless one. */
+CAVS_API int cavs_treelstm_set_dense_input(cavs_treelstm* e, const float* x, long long pitch);
+CAVS_API int cavs_treelstm_set_output_grad(cavs_treelstm* e, const float* dh);
 /* Makes `stream` wait until the embedding-gradient block (the first vocab*embed floats of the bound gradient
  * buffer) written by the most recent cavs_treelstm_backward is complete.  backward produces that block before
  * the weight gradients, so a data-parallel caller can start its cross-GPU reduction on another stream
@@ -262,7 +271,7 @@ CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int
 CAVS_API int cavs_treelstm_profile(cavs_treelstm* e, int enable);
 CAVS_API int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes);
 /* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H] (classes > 8 only: the fused
- * loss head does not materialise it), 3 mailbox [n,2H], 4 gates. */
+ * loss head does not materialise it), 3 mailbox [n,2H], 4 gates, 5 d(x) [n,E] (dense-input engines). */
 CAVS_API int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes);
 
 /* ------------------------------------------------------------------------ */

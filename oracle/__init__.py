@@ -119,6 +119,33 @@ def treelstm_fwd_bwd(tb: dict, tok, label, params: dict, H, E, V, C, K=2, gemm_b
     return out
 
 
+def treelstm_layer(tb: dict, params: dict, H, E, K=1, tok=None, x_dense=None, label=None, dh_ext=None, V=0, C=0,
+                   gemm_bf16=False, loss_rows=0, preact_bf16=False):
+    """One layer of a stack: inputs are either tokens (Emb lookup) or dense rows x_dense [n,E]; the output
+    gradient is either the layer's own loss head (label, Wc, bc) or dh_ext [n,H] from the layer above.
+    Returns state, loss, dW, dU, dB, dX ([n,E]) and, where they exist, dEmb, dWc, dbc."""
+    n = int(tb["n"])
+    cfg = Cfg(n, int(tb["n_levels"]), H, E, max(V, 1), C, K, int(gemm_bf16), int(loss_rows), int(preact_bf16))
+    f32 = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
+    i32 = lambda a: None if a is None else np.ascontiguousarray(a, np.int32)
+    Emb, W, U, B, Wc, bc = (f32(params.get(k)) for k in ("Emb", "W", "U", "B", "Wc", "bc"))
+    assert (tok is None) != (x_dense is None) and (label is None) != (dh_ext is None)
+    out = dict(state=np.zeros((n, 2 * H), np.float32), loss=np.zeros(n, np.float32), dW=np.zeros_like(W), dU=np.zeros_like(U),
+               dB=np.zeros_like(B), dX=np.zeros((n, E), np.float32))
+    if x_dense is None:
+        out["dEmb"] = np.zeros_like(Emb)
+    if dh_ext is None:
+        out["dWc"], out["dbc"] = np.zeros_like(Wc), np.zeros_like(bc)
+    lo, fg, fs, bg, bs = (i32(tb[k]) for k in ("level_off", "fg", "fs", "bg", "bs"))
+    tok, label, x_dense, dh_ext = i32(tok), i32(label), f32(x_dense), f32(dh_ext)
+    rc = oracle_lib().cavs_oracle_treelstm_layer(
+        ctypes.byref(cfg), _p(lo), _p(fg), _p(fs), _p(bg), _p(bs), _p(tok), _p(label), _p(Emb), _p(W), _p(U), _p(B), _p(Wc), _p(bc),
+        _p(out["state"]), _p(out["loss"]), _p(out.get("dEmb")), _p(out["dW"]), _p(out["dU"]), _p(out["dB"]), _p(out.get("dWc")),
+        _p(out.get("dbc")), _p(x_dense), _p(dh_ext), _p(out["dX"]))
+    assert rc == 0
+    return out
+
+
 def treegru_fwd_bwd(tb: dict, tok, label, params: dict, H, E, V, C, K=4, gemm_bf16=False, loss_rows=0, preact_bf16=False):
     """Child-sum Tree-GRU forward + loss + backward (an extension defined by the oracle).  params: Emb [V,E],
     W [E*3H] (r,z,n), U [3*H*H] (U_r|U_z|U_n), B [3H], Wc [C,H], bc [C]."""

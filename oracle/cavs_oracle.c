@@ -381,11 +381,42 @@ typedef struct {
 /* Forward + loss + backward.  Outputs: state [n,2H], loss [n], and the gradients
  * (overwritten, not accumulated).  label < 0 marks a row without a loss term
  * (root-only losses, an extension).  Returns 0. */
+/* One layer of a stack (apps/lstm stacks layers by feeding a layer's h into the next one's input):
+ *   x_dense != NULL: the inputs are the rows x_dense[t,:] ([n,E], tensor-id order) instead of Emb[tok[t]];
+ *                    tok, Emb and dEmb are ignored; dx_out ([n,E], optional) receives d(loss)/d(x_dense);
+ *   dh_ext  != NULL: d(loss)/d(h) of every vertex comes from the layer above ([n,H]) and the loss head is
+ *                    skipped; label, Wc, bc, dWc, dbc are ignored and loss_out is zero. */
+static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, const int *fg, const int *fs,
+                          const int *bg, const int *bs, const int *tok, const int *label, const float *Emb,
+                          const float *W, const float *U, const float *B, const float *Wc, const float *bc,
+                          float *state_out, float *loss_out, float *dEmb, float *dW, float *dU, float *dB,
+                          float *dWc, float *dbc, float *dstate_dbg, const float *x_dense, const float *dh_ext,
+                          float *dx_out);
+
 int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_off, const int *fg, const int *fs,
                                  const int *bg, const int *bs, const int *tok, const int *label, const float *Emb,
                                  const float *W, const float *U, const float *B, const float *Wc, const float *bc,
                                  float *state_out, float *loss_out, float *dEmb, float *dW, float *dU, float *dB,
                                  float *dWc, float *dbc, float *dstate_dbg /* optional [n,2H]: d(h|c) seen by each row */) {
+  return treelstm_layer(cfg, level_off, fg, fs, bg, bs, tok, label, Emb, W, U, B, Wc, bc, state_out, loss_out, dEmb, dW, dU,
+                        dB, dWc, dbc, dstate_dbg, NULL, NULL, NULL);
+}
+
+int cavs_oracle_treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, const int *fg, const int *fs,
+                               const int *bg, const int *bs, const int *tok, const int *label, const float *Emb,
+                               const float *W, const float *U, const float *B, const float *Wc, const float *bc,
+                               float *state_out, float *loss_out, float *dEmb, float *dW, float *dU, float *dB,
+                               float *dWc, float *dbc, const float *x_dense, const float *dh_ext, float *dx_out) {
+  return treelstm_layer(cfg, level_off, fg, fs, bg, bs, tok, label, Emb, W, U, B, Wc, bc, state_out, loss_out, dEmb, dW, dU,
+                        dB, dWc, dbc, NULL, x_dense, dh_ext, dx_out);
+}
+
+static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, const int *fg, const int *fs,
+                          const int *bg, const int *bs, const int *tok, const int *label, const float *Emb,
+                          const float *W, const float *U, const float *B, const float *Wc, const float *bc,
+                          float *state_out, float *loss_out, float *dEmb, float *dW, float *dU, float *dB,
+                          float *dWc, float *dbc, float *dstate_dbg, const float *x_dense, const float *dh_ext,
+                          float *dx_out) {
   const int n = cfg->n, H = cfg->hidden, E = cfg->embed, C = cfg->classes, K = cfg->n_slots, V = cfg->vocab;
   const int bf = cfg->gemm_bf16;
   const size_t G = (size_t)(3 + K) * H;
@@ -415,9 +446,15 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
    * then the input projection.  x does not depend on the level, so one product over
    * all rows equals the reference's per-level products row for row. */
   for (int t = 0; t < n; t++) {
-    int id = tok[t];
-    if (id < 0 || id >= V) id = 0;
-    for (int e = 0; e < E; e++) x[(size_t)t * E + e] = bf ? bf16_round(Emb[(size_t)id * E + e]) : Emb[(size_t)id * E + e];
+    const float *src;
+    if (x_dense) {
+      src = x_dense + (size_t)t * E;
+    } else {
+      int id = tok[t];
+      if (id < 0 || id >= V) id = 0;
+      src = Emb + (size_t)id * E;
+    }
+    for (int e = 0; e < E; e++) x[(size_t)t * E + e] = bf ? bf16_round(src[e]) : src[e];
   }
   gemm_nn(a, x, Wr, n, 4 * H, E, 0);
   if (cfg->preact_bf16) for (size_t i = 0; i < (size_t)n * 4 * H; i++) a[i] = bf16_round(a[i]);
@@ -479,10 +516,14 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
 
   /* Loss head over the pushed h rows. */
   float *dOut = (float *)calloc(nn * H, sizeof(float));
-  float *dz = (float *)calloc(nn * C, sizeof(float));
+  float *dz = (float *)calloc(nn * (size_t)(C > 0 ? C : 1), sizeof(float));
   const float inv_rows = 1.0f / (float)(cfg->loss_rows > 0 ? cfg->loss_rows : (n > 0 ? n : 1));
+  if (dh_ext) {
+    memcpy(dOut, dh_ext, sizeof(float) * (size_t)n * H);
+    if (loss_out) memset(loss_out, 0, sizeof(float) * (size_t)n);
+  }
 #pragma omp parallel for schedule(static)
-  for (int t = 0; t < n; t++) {
+  for (int t = 0; t < (dh_ext ? 0 : n); t++) {
     float z[64];
     float *zz = C <= 64 ? z : (float *)malloc(sizeof(float) * C);
     const float *h = state + (size_t)t * 2 * H;
@@ -512,7 +553,7 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
     if (zz != z) free(zz);
   }
   /* dWc = dz^T h, dbc = column sums (op_impl_fullyconnected_cublas.cc:157-167). */
-  for (int c = 0; c < C; c++) {
+  for (int c = 0; c < (dh_ext ? 0 : C); c++) {
     float accb = 0.0f;
     for (int t = 0; t < n; t++) accb += dz[(size_t)t * C + c];
     dbc[c] = accb;
@@ -607,11 +648,14 @@ int cavs_oracle_treelstm_fwd_bwd(const cavs_oracle_cfg *cfg, const int *level_of
    * same up to fp32 reassociation). */
   float *dX = (float *)malloc(sizeof(float) * nn * E);
   gemm_nt(dX, dA_r, Wr, n, E, 4 * H, 0);
-  memset(dEmb, 0, sizeof(float) * (size_t)V * E);
-  for (int t = 0; t < n; t++) {
-    int id = tok[t];
-    if (id < 0 || id >= V) id = 0;
-    for (int e = 0; e < E; e++) dEmb[(size_t)id * E + e] += dX[(size_t)t * E + e];
+  if (dx_out) memcpy(dx_out, dX, sizeof(float) * (size_t)n * E);
+  if (!x_dense) {
+    memset(dEmb, 0, sizeof(float) * (size_t)V * E);
+    for (int t = 0; t < n; t++) {
+      int id = tok[t];
+      if (id < 0 || id >= V) id = 0;
+      for (int e = 0; e < E; e++) dEmb[(size_t)id * E + e] += dX[(size_t)t * E + e];
+    }
   }
 
   free(Wr); free(Ur); free(x); free(a); free(gath); free(gates); free(state); free(mailbox);

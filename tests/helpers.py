@@ -85,3 +85,46 @@ def root_only_labels(parents, label_job):
     ends = np.cumsum(lens) - 1
     out[ends] = label_job[ends]
     return out
+
+
+def make_stack_params(seed, dims, V, C, scale=0.1, bias_scale=0.05):
+    """Parameters of a stack of LSTM layers: dims = [(H, E), ...] with E of layer i > 0 equal to H of layer i-1.
+    Layer 0 holds Emb, the last layer Wc and bc."""
+    layers = []
+    for li, (H, E) in enumerate(dims):
+        p = dict(W=S.synth_uniform_float(seed + 20 * li + 11, scale, (E * 4 * H,)),
+                 U=S.synth_uniform_float(seed + 20 * li + 12, scale, (4 * H * H,)),
+                 B=S.synth_uniform_float(seed + 20 * li + 14, bias_scale, (4 * H,)))
+        if li == 0:
+            p["Emb"] = S.synth_uniform_float(seed + 10, scale, (V, E))
+        if li == len(dims) - 1:
+            p["Wc"] = S.synth_uniform_float(seed + 13, scale, (C, H))
+            p["bc"] = S.synth_uniform_float(seed + 15, bias_scale, (C,))
+        layers.append(p)
+    return layers
+
+
+def oracle_stack(oracle, tb, tok, label, layers, dims, V, C, K=1, gemm_bf16=False, loss_rows=0):
+    """Runs a layer stack through the oracle's single-layer entry: forward sweeps bottom-up (a forward-only call
+    is a call with a zero output gradient), then top-down with each layer's d(input) as the next one's d(h)."""
+    n = int(tb["n"])
+    kw = dict(K=K, gemm_bf16=gemm_bf16, preact_bf16=gemm_bf16)
+    x, fwd = None, []
+    for li, (H, E) in enumerate(dims[:-1]):
+        r = oracle.treelstm_layer(tb, layers[li], H, E, tok=tok if li == 0 else None, x_dense=x, V=V if li == 0 else 0,
+                                  dh_ext=np.zeros((n, H), np.float32), **kw)
+        x = np.ascontiguousarray(r["state"][:, :H])
+        fwd.append(x)
+    outs = [None] * len(dims)
+    H, E = dims[-1]
+    top = oracle.treelstm_layer(tb, layers[-1], H, E, tok=tok if len(dims) == 1 else None, x_dense=x, label=label, C=C,
+                                V=V if len(dims) == 1 else 0, loss_rows=loss_rows, **kw)
+    outs[-1] = top
+    dh = top["dX"]
+    for li in range(len(dims) - 2, -1, -1):
+        H, E = dims[li]
+        r = oracle.treelstm_layer(tb, layers[li], H, E, tok=tok if li == 0 else None, x_dense=None if li == 0 else fwd[li - 1],
+                                  V=V if li == 0 else 0, dh_ext=dh, **kw)
+        outs[li] = r
+        dh = r["dX"]
+    return outs

@@ -8,7 +8,7 @@ import pytest
 import oracle
 from cavs_b200 import schedule as S
 from helpers import make_params, make_tree_batch, rel_err, tables_from_schedule
-from torch_ref import treegru_autograd, treelstm_autograd
+from torch_ref import stacked_lstm_autograd, treegru_autograd, treelstm_autograd
 
 GOLD = Path(__file__).parent / "golden" / "treelstm_small.npz"
 KEYS = ("state", "loss", "dEmb", "dW", "dU", "dB", "dWc", "dbc")
@@ -132,3 +132,24 @@ def test_treegru_against_autograd(K, arity, root_only):
     ref = treegru_autograd(tb, tok, lab, params, H, E, V, C, K=K, loss_rows=rows)
     for k in KEYS:
         assert rel_err(got[k], ref[k]) < 2e-5, k
+
+
+def test_stacked_chain_lstm_against_autograd():
+    """Two stacked LSTM layers over ragged chains (the variable-length chain configuration, scaled down): the
+    oracle's single-layer entry chained through dense inputs / external output gradients vs autograd in fp64."""
+    from helpers import make_stack_params, oracle_stack
+    V, C, dims = 40, 40, [(10, 8), (12, 10)]
+    parents = S.synth_chains(31, 6, 3, 9)
+    lens = (parents == -1).argmax(1) + 1
+    tok_job = S.synth_zipf(32, 1.1, V, int(lens.sum()))
+    label_job = S.synth_uniform_int(33, C, int(lens.sum()))
+    s = S.Schedule().load(parents, n_slots=1)
+    tb = tables_from_schedule(s)
+    tok, lab = tok_job[tb["t2j"]], label_job[tb["t2j"]]
+    layers = make_stack_params(7, dims, V, C, scale=0.3)
+    got = oracle_stack(oracle, tb, tok, lab, layers, dims, V, C)
+    ref, ref_loss = stacked_lstm_autograd(tb, tok, lab, layers, dims, V, C)
+    assert rel_err(got[-1]["loss"], ref_loss) < 2e-5
+    for li in range(2):
+        for k in ref[li]:
+            assert rel_err(got[li][k], ref[li][k]) < 2e-5, (li, k)
