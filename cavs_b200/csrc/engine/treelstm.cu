@@ -604,10 +604,25 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
     if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k, &e->map_ds, &e->map_Uiou_k64))) return rc;
-    ChainHint(rows <= kChainSmallRows);   // dq GEMM -> scatter -> next level's cell gradient
-    if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq, &e->map_Uf_k64))) return rc;
-    PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
-         LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
+    ChainHint(rows <= kChainSmallRows);   // dq GEMM (-> scatter) -> next level's cell gradient
+    if (e->bf16) {
+      // dq = Zf U_f^T with the child-gradient scatter in its epilogue: row (t, c) of the product plus ds[t] goes
+      // straight to the h half of mailbox[child_c(t)] (Scatter(Child=c), cavs/backend/op_decl_graphop.cc:25-41),
+      // so dq is never stored and no separate scatter pass runs.
+      GemmBf16MappedArgs ga;
+      ga.c = e->mailbox; ga.ldc = 2 * H; ga.out_mode = 3;
+      ga.a = &e->map_ZF; ga.a_row_off = off * K; ga.b = &e->map_Uf_k; ga.b_small = &e->map_Uf_k64;
+      ga.m = rows * K; ga.n = H; ga.k = H;
+      ga.status = e->Status();
+      ga.scatter_child = bt.child; ga.scatter_n_total = nt; ga.scatter_off = off; ga.scatter_slots = K;
+      ga.scatter_addend = e->ds; ga.scatter_addend_ld = H;
+      // work: the product's flops; the bytes the separate scatter used to move are no longer moved
+      PROF(e, kProfGemm, 2.0 * rows * K * H * H, st, GemmBf16Mapped(ga, st));
+    } else {
+      if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq, &e->map_Uf_k64))) return rc;
+      PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
+           LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
+    }
   }
   ChainHint(false);
   // Deferred gradients, one pass per weight over all rows (cavs/midend/batch_weight_updater.h:10-85).  The

@@ -54,6 +54,12 @@ struct GemmBf16MappedArgs {
   // Optional second map of a K-major B encoded for 64-row tiles (the small-problem tiling); without it a
   // K-major B keeps the default tiling.  An MN-major B needs no second map.
   const TcOperandMap* b_small = nullptr;
+  // out_mode 3 (scatter): row r = t * scatter_slots + c of the product, plus scatter_addend[t, :], is written to
+  // row scatter_child[c * scatter_n_total + scatter_off + t] of c (pitch ldc); negative targets are skipped.
+  const int32_t* scatter_child = nullptr;
+  const float* scatter_addend = nullptr;
+  long long scatter_addend_ld = 0;
+  int scatter_n_total = 0, scatter_off = 0, scatter_slots = 0;
   // Optional pre-encoded map of the output (EncodeTcOutput over [>= m rows, n] at c); when null and
   // the TMA-store epilogue applies, one is encoded per call.  The map's row extent clips the M tail,
   // so it must cover exactly the rows this GEMM may write.

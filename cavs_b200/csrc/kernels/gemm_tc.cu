@@ -167,8 +167,14 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   if (g.m == 0 || g.n == 0) return CAVS_OK;
   CAVS_REQUIRE(g.k > 0, CAVS_ERR_BAD_ARG, "gemm_bf16: k must be positive");
   CAVS_REQUIRE(g.a && g.b && g.c, CAVS_ERR_BAD_ARG, "gemm_bf16: null pointer");
-  CAVS_REQUIRE(g.out_mode >= 0 && g.out_mode <= 2, CAVS_ERR_BAD_ARG, "gemm_bf16: bad out_mode");
+  CAVS_REQUIRE(g.out_mode >= 0 && g.out_mode <= 3, CAVS_ERR_BAD_ARG, "gemm_bf16: bad out_mode");
   CAVS_REQUIRE(g.ldc >= g.n, CAVS_ERR_BAD_ARG, "gemm_bf16: ldc < n");
+  CAVS_REQUIRE(g.out_mode != tc::kScatterF32 ||
+                   (g.scatter_child && g.scatter_addend && g.scatter_slots >= 1 && g.scatter_addend_ld >= g.n &&
+                    std::max(1, g.splits) == 1 && g.n % 4 == 0 && g.ldc % 4 == 0 && g.scatter_addend_ld % 4 == 0 &&
+                    Aligned16(g.c) && Aligned16(g.scatter_addend)),
+               CAVS_ERR_BAD_ARG,
+               "gemm_bf16: scatter output needs the child table, 16-byte aligned addend / output rows (n, pitches multiples of 4) and no K split");
   CAVS_REQUIRE(g.a_row_off == 0 || g.a->major == tc::kMajorK, CAVS_ERR_BAD_ARG, "gemm_bf16: row offsets need a K-major A");
   const int splits = std::max(1, g.splits);
   int bn = GemmBf16TileN(g.n);
@@ -196,6 +202,8 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   p.a_row_off = g.a_row_off;
   p.status = g.status;
   p.chain_early = ChainEarly();
+  p.sc_child = g.scatter_child; p.sc_addend = g.scatter_addend; p.sc_addend_ld = g.scatter_addend_ld;
+  p.sc_n_total = g.scatter_n_total; p.sc_off = g.scatter_off; p.sc_slots = std::max(1, g.scatter_slots);
   if (eff_splits > 1) {
     p.c = g.scratch; p.ldc = g.n; p.split_stride = static_cast<long long>(g.m) * g.n; p.out_mode = tc::kStoreF32;
   } else {
@@ -206,7 +214,7 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   const CUtensorMap* mc = &ma;   // placeholder when unused
   const size_t c_elt = g.out_mode == tc::kStoreBf16 ? 2 : 4;
   p.tma_store = 0;
-  if (eff_splits == 1 && g.out_mode != tc::kAccumF32 && Aligned16(g.c) && (g.ldc * c_elt) % 16 == 0) {
+  if (eff_splits == 1 && g.out_mode != tc::kAccumF32 && g.out_mode != tc::kScatterF32 && Aligned16(g.c) && (g.ldc * c_elt) % 16 == 0) {
     if (g.c_map) {
       mc = reinterpret_cast<const CUtensorMap*>(g.c_map->bytes);
     } else {

@@ -36,7 +36,7 @@ constexpr int kThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 21;
 
 enum Major : int { kMajorK = 0, kMajorMN = 1 };
-enum OutMode : int { kStoreF32 = 0, kAccumF32 = 1, kStoreBf16 = 2 };
+enum OutMode : int { kStoreF32 = 0, kAccumF32 = 1, kStoreBf16 = 2, kScatterF32 = 3 };
 
 struct Params {
   void* c;            // output, row-major
@@ -49,6 +49,12 @@ struct Params {
   int a_row_off;      // added to the row coordinate of K-major A tiles (a level's view into an arena map)
   int tma_store;      // 1: the epilogue stages C in shared memory and writes it with TMA (map_c valid)
   int chain_early;    // 1: release the following kernel at once (chained launches, kernels/launch.h)
+  // kScatterF32: GEMM row r = t * sc_slots + c goes to output row child[c * sc_n_total + sc_off + t] (skipped when
+  // negative) after adding sc_addend[t, col]: the child-gradient scatter of a level done by the epilogue.
+  const int32_t* sc_child;
+  const float* sc_addend;
+  long long sc_addend_ld;
+  int sc_n_total, sc_off, sc_slots;
   int* status;        // device word, set non-zero when a bounded wait expires
 };
 
@@ -242,6 +248,49 @@ __device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[
   }
 }
 
+// Scatter epilogue.  A lane serves row i = it * 4 + lane / 8 of the warp's 32 rows (it = 0..7) and the 16-byte
+// column group lane % 8, so eight lanes cover a row's 128 bytes and every global access is a full line.
+// ScatterTargets: output row and addend row of the lane's eight rows, loaded once per tile.
+__device__ __forceinline__ void ScatterTargets(const Params& p, int lane, int row0, int (&dst_row)[8], int (&add_row)[8]) {
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int gr = row0 + it * 4 + (lane >> 3);
+    const int t = gr / p.sc_slots, c = gr - t * p.sc_slots;
+    add_row[it] = t;
+    dst_row[it] = gr < p.m ? __ldg(p.sc_child + static_cast<long long>(c) * p.sc_n_total + p.sc_off + t) : -1;
+  }
+}
+// ScatterAddends: the addend values of a 32-column chunk for the lane's eight rows (issued early: the loads are
+// in flight while the accumulator chunk is read and staged).
+__device__ __forceinline__ void ScatterAddends(const Params& p, int lane, int col0, const int (&dst_row)[8], const int (&add_row)[8],
+                                               float4 (&a)[8]) {
+  const int col = col0 + (lane & 7) * 4;
+#pragma unroll
+  for (int it = 0; it < 8; ++it)
+    a[it] = (dst_row[it] >= 0 && col + 4 <= p.n)
+                ? __ldg(reinterpret_cast<const float4*>(p.sc_addend + static_cast<long long>(add_row[it]) * p.sc_addend_ld + col))
+                : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+// ScatterRows: staged rows leave shared memory four per instruction:
+//   out[dst_row][col..] = addend + staged value  (addend first: the separate scatter kernel computes ds + dq).
+__device__ __forceinline__ void ScatterRows(const Params& p, uint32_t slot, int lane, int col0, const int (&dst_row)[8],
+                                            const float4 (&a)[8]) {
+  const int q = lane & 7;
+  const int col = col0 + q * 4;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int i = it * 4 + (lane >> 3);
+    if (dst_row[it] < 0 || col + 4 > p.n) continue;
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(slot + i * 128 + ((q ^ (i & 7)) << 4))
+                 : "memory");
+    *reinterpret_cast<float4*>(static_cast<float*>(p.c) + static_cast<long long>(dst_row[it]) * p.ldc + col) =
+        make_float4(a[it].x + v.x, a[it].y + v.y, a[it].z + v.z, a[it].w + v.w);
+  }
+}
+
 // Persistent kernel: each CTA walks work items w = blockIdx.x, blockIdx.x + gridDim.x, ...;
 // work item -> (tile, K-split) with the N tile index fastest, so the CTAs of one wave share A
 // row blocks through L2.  Two TMEM accumulators alternate between tiles: while the epilogue
@@ -369,6 +418,8 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int z = w % p.n_splits, tile = w / p.n_splits;
       const int m0 = (tile / n_tiles_n) * kBM, n0 = (tile % n_tiles_n) * kBN;
       const uint32_t acc = t_local & 1, acc_phase = (t_local >> 1) & 1;
+      int sc_dst[8], sc_add[8];
+      if (p.out_mode == kScatterF32) ScatterTargets(p, lane, m0 + quarter * 32, sc_dst, sc_add);   // before the wait
       ok = MbarWait(SmemAddr(acc_full + acc), acc_phase);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -427,6 +478,27 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
               }
             }
+          }
+        }
+      } else if (p.out_mode == kScatterF32) {
+        // Registers -> swizzled shared staging (one 128-byte row per lane) -> coalesced row scatter.  The
+        // addends of a 64-column step are requested before the accumulator chunk is read.
+        const uint32_t slot = SmemAddr(smem + S::kCOff) + (warp - 2) * 2 * S::kCSlot;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 64) {
+          if (n0 + c0 >= p.n) break;   // warp-uniform
+          float4 add0[8], add1[8];
+          ScatterAddends(p, lane, n0 + c0, sc_dst, sc_add, add0);
+          ScatterAddends(p, lane, n0 + c0 + 32, sc_dst, sc_add, add1);
+          uint32_t r[64];
+          TmemLoad64(t_addr + c0, r);
+          if (m0 + quarter * 32 < p.m) {
+            __syncwarp();                      // the previous step has been read out of both slots
+            StageRow<0, false>(slot, lane, r);
+            StageRow<32, false>(slot + S::kCSlot, lane, r);
+            __syncwarp();
+            ScatterRows(p, slot, lane, n0 + c0, sc_dst, add0);
+            ScatterRows(p, slot + S::kCSlot, lane, n0 + c0 + 32, sc_dst, add1);
           }
         }
       } else {
