@@ -148,13 +148,17 @@ __device__ __forceinline__ void Load4(const TIn* p, float (&v)[4]) {
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
   }
 }
-// One CTA per chunk; width must be a multiple of 4.  partial[chunk,:] in fp32.
-template <typename TIn>
+// One CTA per chunk; width must be a multiple of 4.  partial[chunk,:] in fp32 -- except for a chunk that is its
+// segment's only one (chunk_out[chunk] = segment index, else -1; optional table): its sums are final and go
+// straight to out[segment,:], skipping the partial round trip (most tokens of a batch occur a few times).
+template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(kThreads)
-SegSumChunks(float* __restrict__ partial, const TIn* __restrict__ x, long long pitch, const int32_t* __restrict__ order,
+SegSumChunks(float* __restrict__ partial, TOut* __restrict__ out, const int32_t* __restrict__ chunk_out,
+             const TIn* __restrict__ x, long long pitch, const int32_t* __restrict__ order,
              const int32_t* __restrict__ chunk_off, int width) {
   __shared__ int32_t rows_sm[kEmbedChunk];
   const int chunk = blockIdx.x;
+  const int direct = chunk_out != nullptr ? chunk_out[chunk] : -1;
   const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
   for (int r = threadIdx.x; r < cnt; r += kThreads) rows_sm[r] = order[begin + r];
   __syncthreads();
@@ -180,9 +184,22 @@ SegSumChunks(float* __restrict__ partial, const TIn* __restrict__ x, long long p
 #pragma unroll
       for (int v = 0; v < 4; ++v) acc[u][v] += t[v];
     }
-    *reinterpret_cast<float4*>(partial + static_cast<size_t>(chunk) * width + e) =
+    const float4 sum =
         make_float4((acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]), (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]),
                     (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]), (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]));
+    if (direct < 0) {
+      *reinterpret_cast<float4*>(partial + static_cast<size_t>(chunk) * width + e) = sum;
+    } else {
+      // 0 + sum, as the second pass would compute it for a single chunk
+      TOut* dst = out + static_cast<size_t>(direct) * width + e;
+      if constexpr (sizeof(TOut) == 4) {
+        *reinterpret_cast<float4*>(dst) = sum;
+      } else {
+        __nv_bfloat162 a = __floats2bfloat162_rn(sum.x, sum.y), b = __floats2bfloat162_rn(sum.z, sum.w);
+        uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(dst) = u;
+      }
+    }
   }
 }
 // Scalar forms of the two passes for widths or pitches that are not multiples of 4 (same summation order
@@ -213,9 +230,11 @@ SegSumFinalScalar(TOut* __restrict__ out, const float* __restrict__ partial, con
 // One CTA per segment: out[seg,:] = sum of its chunks' partials in chunk order (fp32 or bf16 output).
 template <typename TOut>
 __global__ void __launch_bounds__(kThreads)
-SegSumFinal(TOut* __restrict__ out, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk, int width) {
+SegSumFinal(TOut* __restrict__ out, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk, int width,
+            int skip_single) {
   const int seg = blockIdx.x;
   const int c0 = seg_first_chunk[seg], c1 = seg_first_chunk[seg + 1];
+  if (skip_single && c1 - c0 == 1) return;   // written by the first pass
   for (int e = threadIdx.x * 4; e < width; e += kThreads * 4) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int c = c0;
@@ -245,7 +264,7 @@ SegSumFinal(TOut* __restrict__ out, const float* __restrict__ partial, const int
 
 int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16, long long pitch, int width, const int32_t* order,
                           const int32_t* chunk_off, int n_chunks, const int32_t* seg_first_chunk, int n_seg, float* scratch,
-                          cudaStream_t st) {
+                          cudaStream_t st, const int32_t* chunk_out) {
   CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && width > 0 && pitch >= width, CAVS_ERR_BAD_ARG,
                "segmented_row_sum: width must be positive and pitch >= width");
   if (n_chunks == 0 || n_seg == 0) return CAVS_OK;
@@ -262,11 +281,14 @@ int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16,
     CAVS_LAUNCH_CHECK("segmented_row_sum final");
     return CAVS_OK;
   }
-  if (in_bf16) SegSumChunks<__nv_bfloat16><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const __nv_bfloat16*>(x), pitch, order, chunk_off, width);
-  else SegSumChunks<float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<const float*>(x), pitch, order, chunk_off, width);
+  const int skip = chunk_out != nullptr ? 1 : 0;
+  if (in_bf16 && out_bf16) SegSumChunks<bf, bf><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<bf*>(out), chunk_out, static_cast<const bf*>(x), pitch, order, chunk_off, width);
+  else if (in_bf16) SegSumChunks<bf, float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<float*>(out), chunk_out, static_cast<const bf*>(x), pitch, order, chunk_off, width);
+  else if (out_bf16) SegSumChunks<float, bf><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<bf*>(out), chunk_out, static_cast<const float*>(x), pitch, order, chunk_off, width);
+  else SegSumChunks<float, float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<float*>(out), chunk_out, static_cast<const float*>(x), pitch, order, chunk_off, width);
   CAVS_LAUNCH_CHECK("segmented_row_sum chunks");
-  if (out_bf16) SegSumFinal<__nv_bfloat16><<<n_seg, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(out), scratch, seg_first_chunk, width);
-  else SegSumFinal<float><<<n_seg, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, width);
+  if (out_bf16) SegSumFinal<__nv_bfloat16><<<n_seg, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(out), scratch, seg_first_chunk, width, skip);
+  else SegSumFinal<float><<<n_seg, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, width, skip);
   CAVS_LAUNCH_CHECK("segmented_row_sum final");
   return CAVS_OK;
 }

@@ -271,7 +271,9 @@ CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int
 CAVS_API int cavs_treelstm_profile(cavs_treelstm* e, int enable);
 CAVS_API int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes);
 /* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H] (classes > 8 only: the fused
- * loss head does not materialise it), 3 mailbox [n,2H], 4 gates, 5 d(x) [n,E] (dense-input engines). */
+ * loss head does not materialise it), 3 mailbox [n,2H], 4 gates, 5 d(x) [n,E] (dense-input engines),
+ * 6 the two words cavs_treelstm_read_loss copies: loss sum (float) and status (int) -- for callers that fetch
+ * them with their own asynchronous copy instead of the blocking read. */
 CAVS_API int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes);
 
 /* ------------------------------------------------------------------------ */
