@@ -81,7 +81,8 @@ struct cavs_treelstm {
     int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
     std::vector<int32_t> level_off;
     int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
-            *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr;
+            *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr;
+    int n_multi = 0;
   };
   Batch slot[2];
   int active = -1, staged = -1;
@@ -169,7 +170,7 @@ size_t MaxSegments(const cavs_treelstm_config& c) { return c.vocab == 0 ? c.max_
 size_t MaxChunks(const cavs_treelstm_config& c) { return MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
-  return (c.n_slots + 5) * n + 2 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
+  return (c.n_slots + 5) * n + 3 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -421,7 +422,8 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   int n_seg = 0, n_chunks = 0;
   if (e->Dense()) {
     // Dense inputs: one projection row per vertex, no token grouping.
-    bt.chunk_off = bt.seg_first_chunk = bt.seg_tok = bt.chunk_out = nullptr;
+    bt.chunk_off = bt.seg_first_chunk = bt.seg_tok = bt.chunk_out = bt.multi_seg = nullptr;
+    bt.n_multi = 0;
     bt.tok_slot = nullptr;
     n_seg = n;
     CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
@@ -435,8 +437,9 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.seg_first_chunk);
   int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
   int32_t* h_chunk_out = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_out);
+  int32_t* h_multi = view(static_cast<size_t>(n_chunks) + 1, &bt.multi_seg);   // each listed segment has >= 2 chunks
   CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
-  int si = 0, ci = 0;
+  int si = 0, ci = 0, n_multi = 0;
   e->slot_of_token.resize(V);
   for (int v = 0; v < V; ++v) {
     const int b0 = e->bucket[v], b1 = e->bucket[v + 1];
@@ -445,11 +448,13 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     h_seg_tok[si] = v;
     // a token whose rows fit one chunk gets its sum written by the first pass of the segmented sums
     const bool single = b1 - b0 <= kEmbedChunk;
+    if (!single) h_multi[n_multi++] = si;
     for (int b = b0; b < b1; b += kEmbedChunk) { h_chunk_out[ci] = single ? si : -1; h_chunk_off[ci++] = b; }
     h_seg_first[si++] = ci - (b1 - b0 + kEmbedChunk - 1) / kEmbedChunk;
   }
   h_seg_first[si] = ci;
   h_chunk_off[ci] = n;
+  bt.n_multi = n_multi;
   for (int t = 0; t < n; ++t) {
     h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
     h_slot[t] = e->slot_of_token[h_tok[t]];
@@ -646,7 +651,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   } else {
     PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
          LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
-                               bt.seg_first_chunk, n_tok, e->emb_scratch, st, bt.chunk_out));
+                               bt.seg_first_chunk, n_tok, e->emb_scratch, st, bt.chunk_out, bt.multi_seg, bt.n_multi));
     if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
     CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
     if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;

@@ -50,9 +50,11 @@ int LaunchEmbedBwd(float* dtable, const float* dX, const int32_t* order, const i
 // LaunchEmbedBwd); fp32 accumulation in a fixed order; scratch: [n_chunks, width] fp32.
 int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16, long long pitch, int width, const int32_t* order,
                           const int32_t* chunk_off, int n_chunks, const int32_t* seg_first_chunk, int n_seg, float* scratch,
-                          cudaStream_t st, const int32_t* chunk_out = nullptr);
+                          cudaStream_t st, const int32_t* chunk_out = nullptr, const int32_t* multi_seg = nullptr,
+                          int n_multi = 0);
 // chunk_out (optional, [n_chunks]): segment index for a chunk that is its segment's only chunk, else -1; such
-// chunks write their output row in the first pass.
+// chunks write their output row in the first pass.  multi_seg (optional with chunk_out, [n_multi]): the segments
+// with more than one chunk; the second pass then runs only over them, several CTAs per segment.
 
 // Fused classifier + softmax cross-entropy for small class counts (C <= 32), forward and backward
 // in one pass over the pushed hidden rows.  h rows are read with pitch h_pitch (state is [n,2H]).

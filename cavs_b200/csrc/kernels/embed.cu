@@ -169,6 +169,20 @@ SegSumChunks(float* __restrict__ partial, TOut* __restrict__ out, const int32_t*
 #pragma unroll
       for (int v = 0; v < 4; ++v) acc[u][v] = 0.0f;
     int r = 0;
+    // Eight row loads in flight per thread; accumulator u still takes rows u, u + 4, u + 8, ... in order.
+    for (; r + 8 <= cnt; r += 8) {
+      float t[8][4];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) Load4(x + static_cast<long long>(rows_sm[r + u]) * pitch + e, t[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[u][v] += t[u][v];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) acc[u][v] += t[u + 4][v];
+    }
     for (; r + 4 <= cnt; r += 4) {
       float t[4][4];
 #pragma unroll
@@ -260,11 +274,60 @@ SegSumFinal(TOut* __restrict__ out, const float* __restrict__ partial, const int
   }
 }
 
+// Second pass for the segments that have more than one chunk (listed in multi_seg).  A CTA takes one such
+// segment and 128 columns: its eight groups of 32 lanes each sum every eighth chunk partial (group g: chunks
+// c0 + g, c0 + g + 8, ...), four loads in flight, and the eight group sums are folded in group order -- a fixed
+// tree, so the result is deterministic, and the longest segment of a batch (the token shared by all internal
+// vertices has ~1000 chunks) is no longer one serial chain.
+template <typename TOut>
+__global__ void __launch_bounds__(kThreads)
+SegSumFinalMulti(TOut* __restrict__ out, const float* __restrict__ partial, const int32_t* __restrict__ seg_first_chunk,
+                 const int32_t* __restrict__ multi_seg, int width) {
+  __shared__ float4 fold[kThreads];
+  const int seg = multi_seg[blockIdx.x];
+  const int c0 = seg_first_chunk[seg], c1 = seg_first_chunk[seg + 1];
+  const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.y * 128 + lane * 4;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (e < width) {
+    int c = c0 + g;
+    for (; c + 24 < c1; c += 32) {
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) t[u] = *reinterpret_cast<const float4*>(partial + static_cast<size_t>(c + 8 * u) * width + e);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { acc.x += t[u].x; acc.y += t[u].y; acc.z += t[u].z; acc.w += t[u].w; }
+    }
+    for (; c < c1; c += 8) {
+      const float4 t = *reinterpret_cast<const float4*>(partial + static_cast<size_t>(c) * width + e);
+      acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+    }
+  }
+  fold[threadIdx.x] = acc;
+  __syncthreads();
+  if (g == 0 && e < width) {
+    float4 s = fold[lane];
+#pragma unroll
+    for (int k = 1; k < kThreads / 32; ++k) {
+      const float4 t = fold[k * 32 + lane];
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    TOut* dst = out + static_cast<size_t>(seg) * width + e;
+    if constexpr (sizeof(TOut) == 4) {
+      *reinterpret_cast<float4*>(dst) = s;
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(s.x, s.y), b = __floats2bfloat162_rn(s.z, s.w);
+      uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(dst) = u;
+    }
+  }
+}
+
 }  // namespace
 
 int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16, long long pitch, int width, const int32_t* order,
                           const int32_t* chunk_off, int n_chunks, const int32_t* seg_first_chunk, int n_seg, float* scratch,
-                          cudaStream_t st, const int32_t* chunk_out) {
+                          cudaStream_t st, const int32_t* chunk_out, const int32_t* multi_seg, int n_multi) {
   CAVS_REQUIRE(n_chunks >= 0 && n_seg >= 0 && width > 0 && pitch >= width, CAVS_ERR_BAD_ARG,
                "segmented_row_sum: width must be positive and pitch >= width");
   if (n_chunks == 0 || n_seg == 0) return CAVS_OK;
@@ -287,8 +350,18 @@ int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16,
   else if (out_bf16) SegSumChunks<float, bf><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<bf*>(out), chunk_out, static_cast<const float*>(x), pitch, order, chunk_off, width);
   else SegSumChunks<float, float><<<n_chunks, kThreads, 0, st>>>(scratch, static_cast<float*>(out), chunk_out, static_cast<const float*>(x), pitch, order, chunk_off, width);
   CAVS_LAUNCH_CHECK("segmented_row_sum chunks");
-  if (out_bf16) SegSumFinal<__nv_bfloat16><<<n_seg, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(out), scratch, seg_first_chunk, width, skip);
-  else SegSumFinal<float><<<n_seg, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, width, skip);
+  if (skip && multi_seg != nullptr) {
+    // every single-chunk segment is done; only the listed multi-chunk ones need the second pass
+    if (n_multi > 0) {
+      const dim3 grid(n_multi, (width + 127) / 128);
+      if (out_bf16) SegSumFinalMulti<bf><<<grid, kThreads, 0, st>>>(static_cast<bf*>(out), scratch, seg_first_chunk, multi_seg, width);
+      else SegSumFinalMulti<float><<<grid, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, multi_seg, width);
+    }
+  } else if (out_bf16) {
+    SegSumFinal<__nv_bfloat16><<<n_seg, kThreads, 0, st>>>(static_cast<__nv_bfloat16*>(out), scratch, seg_first_chunk, width, skip);
+  } else {
+    SegSumFinal<float><<<n_seg, kThreads, 0, st>>>(static_cast<float*>(out), scratch, seg_first_chunk, width, skip);
+  }
   CAVS_LAUNCH_CHECK("segmented_row_sum final");
   return CAVS_OK;
 }

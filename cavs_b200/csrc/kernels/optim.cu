@@ -37,9 +37,12 @@ AdagradKernel(float* __restrict__ w, float* __restrict__ acc, const float* __res
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
   const size_t n4 = n / 4;
   for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n4; i += stride) {
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    // Zero gradient: neither the accumulator nor the weight changes (w - lr * 0 / (sqrt(acc) + eps) == w), so the
+    // rows of an embedding table that the batch did not touch cost one read instead of three reads and two writes.
+    if (gv.x == 0.0f && gv.y == 0.0f && gv.z == 0.0f && gv.w == 0.0f) continue;
     float4 wv = reinterpret_cast<float4*>(w)[i];
     float4 av = reinterpret_cast<float4*>(acc)[i];
-    const float4 gv = reinterpret_cast<const float4*>(g)[i];
     av.x += gv.x * gv.x; av.y += gv.y * gv.y; av.z += gv.z * gv.z; av.w += gv.w * gv.w;
     wv.x -= lr * gv.x / (sqrtf(av.x) + eps); wv.y -= lr * gv.y / (sqrtf(av.y) + eps);
     wv.z -= lr * gv.z / (sqrtf(av.z) + eps); wv.w -= lr * gv.w / (sqrtf(av.w) + eps);
