@@ -236,7 +236,23 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
   __shared__ float fold[kThreads * 4 * V];
   extern __shared__ __align__(16) float s_wc[];   // kHead: the classifier [C, H]
   if (kHead) {
-    for (int i = threadIdx.x; i < C * H; i += kThreads) s_wc[i] = Wc[i];
+    // All of a thread's loads are issued before the first store: one L2 round trip for the whole copy.
+    if (V == 4 && C <= kHeadDzPitch && H <= kThreads * 4 && (reinterpret_cast<uintptr_t>(Wc) & 15u) == 0) {
+      float4 w[kHeadDzPitch];
+      const int n4 = C * H / 4;
+#pragma unroll
+      for (int c = 0; c < kHeadDzPitch; ++c) {
+        const int i = threadIdx.x + c * kThreads;
+        if (i < n4) w[c] = __ldg(reinterpret_cast<const float4*>(Wc) + i);
+      }
+#pragma unroll
+      for (int c = 0; c < kHeadDzPitch; ++c) {
+        const int i = threadIdx.x + c * kThreads;
+        if (i < n4) reinterpret_cast<float4*>(s_wc)[i] = w[c];
+      }
+    } else {
+      for (int i = threadIdx.x; i < C * H; i += kThreads) s_wc[i] = Wc[i];
+    }
     __syncthreads();
   }
   const int tpr = H / V;
