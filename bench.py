@@ -153,6 +153,9 @@ def run_reference(args, wl, rank, world):
     """The reference arm: the oracle port on the host cores (rank 0 only)."""
     if rank != 0:
         return
+    # torchrun pins every rank to one OpenMP thread; this arm is the only work on the host, so it takes all cores.
+    if os.environ.get("OMP_NUM_THREADS") == "1" and world > 1:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import oracle
     oracle.oracle_lib()
     n_trees = args.sample_trees
