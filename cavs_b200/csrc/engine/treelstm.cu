@@ -512,9 +512,11 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   for (int l = 0; l < bt.n_levels; ++l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     if (l == 0) {
-      // leaf rows: read the token row's i,o,u blocks (3H) + its index, write gates i,o,u (3H) and h|c (2H)
-      PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (3 + 3) + 4.0 * 2) + 4), st,
-           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, true, st));
+      // leaf rows: read the token row's i,o,u blocks (3H) + its index, write h|c (2H); the gates are recomputed by
+      // the backward pass, not stored
+      PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * 3 + 4.0 * 2) + 4), st,
+           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, true, st,
+                         false));
       continue;
     }
     // Chained launches: a kernel releases its successor early when that successor is a GEMM (one CTA per
@@ -600,13 +602,15 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     // read d(h) (H; or the dz row with the fused head), mailbox (2H), gates, own c (H) [+ child c (KH)];
     // write dA (4H) [+ ZF (KH), child dc (KH)]
     const double dh_bytes = e->FusedDh() ? 4.0 * kHeadDzPitch : 4.0 * H;
-    const double cell_bytes = l == 0 ? rows * (H * (4.0 * (2 + 1) + elt * (3 + 4)) + dh_bytes)
+    // leaves: mailbox (2H) and the token row's i,o,u blocks (3H) in, dA (4H) out
+    const double cell_bytes = l == 0 ? rows * (H * (4.0 * 2 + elt * (3 + 4)) + dh_bytes + 4)
                                      : rows * (H * (4.0 * (2 + 1 + K + K) + elt * (3 + K + 4 + K)) + dh_bytes);
     ChainHint(l > 0);      // cell gradient -> ds GEMM -> dq GEMM
     PROF(e, kProfCellBwd, cell_bytes, st,
          LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->FusedDh() ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
                        e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
-                       e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C));
+                       e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C, l == 0 ? e->A : nullptr,
+                       l == 0 ? bt.tok_slot : nullptr, l == 0 ? e->params + e->OffB() : nullptr));
     if (l == 0) break;
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
@@ -756,7 +760,7 @@ extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_p
       if (e->FusedDh()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(h) is not materialised with the fused loss head");
       *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;
     case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
-    case 4: *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
+    case 4: *dev_ptr = e->gates;   // leaf rows are not written (their gates are recomputed) *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
     case 6: *dev_ptr = e->tail; *bytes = 2 * sizeof(float); break;               // [0] loss sum, [1] status word (int)
     case 5:                                                                      // d(loss)/d(dense input)
       if (!e->Dense()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(x) exists only with dense inputs");

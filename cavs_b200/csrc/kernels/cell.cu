@@ -159,7 +159,7 @@ template <typename TP, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
 CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
         const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child,
-        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H, int chain_early) {
+        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H, int chain_early, int store_leaf_gates) {
   ChainRelease(chain_early);
   ChainAcquire();
   constexpr bool kFast = sizeof(TP) == 2;
@@ -209,7 +209,9 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
     }
 #pragma unroll
     for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * TanhT<kFast>(cc.v[e]);
-    Store<V>(g, gi); Store<V>(g + H, go); Store<V>(g + 2 * H, gu);
+    // A leaf's gates are a function of its input-projection row alone: when the backward pass recomputes them
+    // (LaunchCellBwd with A), they are not stored.
+    if (!kLeaf || store_leaf_gates) { Store<V>(g, gi); Store<V>(g + H, go); Store<V>(g + 2 * H, gu); }
     Store<V>(state + t * 2 * H + j, hh);
     Store<V>(state + t * 2 * H + H + j, cc);
   }
@@ -230,7 +232,8 @@ __global__ void __launch_bounds__(kThreads)
 CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, float* __restrict__ dB_part,
         const float* __restrict__ dOut, const typename GateType<T>::type* __restrict__ gates, const float* __restrict__ state,
         const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H,
-        const float* __restrict__ dz, const float* __restrict__ Wc, int C, int chain_early) {
+        const float* __restrict__ dz, const float* __restrict__ Wc, int C, int chain_early,
+        const T* __restrict__ A, const int32_t* __restrict__ a_row, const float* __restrict__ bias) {
   ChainRelease(chain_early);
   ChainAcquire();
   __shared__ float fold[kThreads * 4 * V];
@@ -296,8 +299,26 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
         dOutv = LoadF<V>(dOut + t * H + j);
       }
       const typename GateType<T>::type* g = gates + t * G + j;
-      const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
-      const Vec<V> cown = LoadF<V>(state + t * 2 * H + H + j);
+      Vec<V> gi, go, gu, cown;
+      if (kLeaf && A != nullptr) {
+        // Leaf with recomputation: i, o, u and c = i o u follow from the input-projection row (shared by every
+        // vertex carrying the token, so mostly an L2 hit) exactly as the forward pass computed them; neither the
+        // saved gates nor the saved cell state are read.
+        const size_t ar = a_row ? static_cast<size_t>(__ldg(a_row + t)) : t;
+        const T* a = A + ar * 4 * H + j;
+        const Vec<V> ai = LoadF<V>(a), ao = LoadF<V>(a + H), au = LoadF<V>(a + 2 * H);
+        const Vec<V> bi = LoadF<V>(bias + j), bu = LoadF<V>(bias + 2 * H + j), bo = LoadF<V>(bias + 3 * H + j);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          gi.v[e] = SigmoidT<sizeof(T) == 2>((ai.v[e] + 0.0f) + bi.v[e]);
+          go.v[e] = SigmoidT<sizeof(T) == 2>((ao.v[e] + 0.0f) + bo.v[e]);
+          gu.v[e] = TanhT<sizeof(T) == 2>((au.v[e] + 0.0f) + bu.v[e]);
+          cown.v[e] = gi.v[e] * gu.v[e];
+        }
+      } else {
+        gi = LoadF<V>(g); go = LoadF<V>(g + H); gu = LoadF<V>(g + 2 * H);
+        cown = LoadF<V>(state + t * 2 * H + H + j);
+      }
       Vec<V> zi, zo, zu, dc, zfs = Zero<V>();
 #pragma unroll
       for (int e = 0; e < V; ++e) {
@@ -432,7 +453,8 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 }
 
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
-                  const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st) {
+                  const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
+                  bool store_leaf_gates) {
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
@@ -441,12 +463,12 @@ int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const
     if (preact_bf16) {
       using TP = __nv_bfloat16;
       auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
-      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
-      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
+      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
+      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
     } else {
       auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
-      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
-      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly());
+      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
+      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
@@ -462,10 +484,13 @@ int CellBwdGrid(int rows, int H) {
 
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
-                  int K, bool leaf, cudaStream_t st, const float* dz, const float* Wc, int C) {
+                  int K, bool leaf, cudaStream_t st, const float* dz, const float* Wc, int C, const void* A,
+                  const int32_t* a_row, const float* bias) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const bool head = dz != nullptr;
+  CAVS_REQUIRE(A == nullptr || (leaf && bias != nullptr), CAVS_ERR_BAD_ARG,
+               "treelstm_cell_bwd: gate recomputation applies to leaf levels and needs the bias");
   CAVS_REQUIRE(head ? (Wc && C >= 1 && C <= kHeadDzPitch && (reinterpret_cast<uintptr_t>(dz) & 15u) == 0) : dOut != nullptr,
                CAVS_ERR_BAD_ARG, "treelstm_cell_bwd: needs dOut, or 16-byte aligned dz rows with Wc and 1..8 classes");
   const int v = VecWidth(H);
@@ -477,7 +502,7 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 #define CELL_BWD(TT, GT, LEAF, HEAD)                                                                                   \
   LaunchChained(CellBwd<TT, K, V, LEAF, HEAD>, dim3(grid), dim3(kThreads), head_smem, st, static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
                                                            static_cast<const GT*>(gates), state, child, parent, n_total, off,  \
-                                                           rows, H, dz, Wc, C, ChainEarly())
+                                                           rows, H, dz, Wc, C, ChainEarly(), static_cast<const TT*>(A), a_row, bias)
   DISPATCH_KV(K, v, {
     if (bf16) {
       if (leaf) { if (head) CELL_BWD(__nv_bfloat16, __half, true, true); else CELL_BWD(__nv_bfloat16, __half, true, false); }

@@ -20,7 +20,10 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 // gates: fp32, or fp16 when preact_bf16 / bf16 is set (the bf16-GEMM configurations).
 // a_row (optional): [n_total] row of A for each vertex (A then holds one row per distinct token).
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
-                  const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st);
+                  const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
+                  bool store_leaf_gates = true);
+// store_leaf_gates = false (leaf levels): the gates are not saved; the backward pass must then be given A, a_row and
+// bias and recomputes them (a leaf's gates depend on its input-projection row only).
 // dB_part (optional): [CellBwdMaxGrid(), 4H] fp32, zeroed by the caller before the first level of a
 // backward sweep; every launch adds its per-CTA column sums of (zi, zo, zu, sum zf) into it, and a
 // final column sum over its rows gives the bias gradient.  Needs CellBwdFusesBias(H).
@@ -29,7 +32,10 @@ int CellBwdMaxGrid();
 bool CellBwdFusesBias(int H);
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
-                  int K, bool leaf, cudaStream_t st, const float* dz = nullptr, const float* Wc = nullptr, int C = 0);
+                  int K, bool leaf, cudaStream_t st, const float* dz = nullptr, const float* Wc = nullptr, int C = 0,
+                  const void* A = nullptr, const int32_t* a_row = nullptr, const float* bias = nullptr);
+// A / a_row / bias (optional, leaf levels only): recompute i, o, u and c from the input-projection rows instead of
+// reading the saved gates and cell state (A in the same precision as dA).
 // dz / Wc / C (optional): rebuild d(pushed h) = dz[t,:] . Wc inside the kernel instead of reading dOut
 // (dz: [n_total, kHeadDzPitch] rows from LaunchLossHead's dz_out; Wc: [C, H], C <= 8); dOut may then be NULL.
 int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,
