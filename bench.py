@@ -213,6 +213,10 @@ def main():
 
     L = lib()
     L.cavs_launch_count.restype = ctypes.c_ulonglong
+
+    def lib_check(rc):
+        if rc != 0:
+            raise RuntimeError(L.cavs_last_error().decode())
     pool = [make_batch(wl, i, rank, world) for i in range(POOL)]
     scheds = [S.Schedule().load(p[0]) for p in pool]
     max_n = max(s.n_total for s in scheds)
@@ -370,6 +374,40 @@ def main():
         roofline = dict(bound="hbm", kernel=dominant, achieved=d["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=d["frac"],
                         traffic=None, peak_source=peaks["source"])
 
+    # ---- the graph-op row kernels on their own (Gather / Scatter of child state rows, the reference's
+    # BatchedDynamicSelected*Copy kernels): the widest internal level's gather list of slot 0, rows of h|c ----
+    graph_ops = None
+    if rank == 0 and scheds[0].n_levels > 1:
+        lvl_rows = np.diff(scheds[0].level_off)
+        lvl = 1 + int(np.argmax(lvl_rows[1:]))
+        ids_h = scheds[0].ref_gather(lvl, 0)
+        n_ids, row_bytes = int(ids_h.size), 2 * wl["hidden"] * 4
+        ids_d = torch.from_numpy(ids_h).to(dev)
+        src = torch.randn((int(scheds[0].n_total), 2 * wl["hidden"]), device=dev)
+        dst = torch.empty((n_ids, 2 * wl["hidden"]), device=dev)
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+
+        def run_rows(fn, reps=10):
+            for _ in range(3):
+                fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / reps * 1e-3
+
+        work = n_ids * (2 * row_bytes + 4)
+        t_g = run_rows(lambda: lib_check(L.cavs_gather_rows(vp(dst), vp(src), vp(ids_d), n_ids, ctypes.c_size_t(row_bytes), st)))
+        t_s = run_rows(lambda: lib_check(L.cavs_scatter_rows(vp(src), vp(ids_d), vp(dst), n_ids, ctypes.c_size_t(row_bytes), st)))
+        graph_ops = dict(rows=n_ids, row_bytes=row_bytes, level=lvl, gather_gbs=work / t_g / 1e9, scatter_gbs=work / t_s / 1e9,
+                         gather_frac=work / t_g / 1e9 / peaks["hbm_gbs"], scatter_frac=work / t_s / 1e9 / peaks["hbm_gbs"],
+                         note="cavs_gather_rows / cavs_scatter_rows on the widest internal level's child list; "
+                              "bytes = rows x (read + write of a row + its index); source and target exceed L2")
+        del src, dst
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -387,7 +425,8 @@ def main():
                             parallelism=f"dp{world}", l2="working set per step (tens of GB) exceeds L2; no flush needed"),
                 e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8,
                          host_schedule_ms=host_ms[0] / max(host_ms[2], 1), host_pack_ms=host_ms[1] / max(host_ms[2], 1)),
-                gpu_launches=int(launches), loss_sum=loss_dev, clocks=clocks, roofline=roofline, kernel_classes=classes)
+                gpu_launches=int(launches), loss_sum=loss_dev, clocks=clocks, roofline=roofline, kernel_classes=classes,
+                graph_ops=graph_ops)
     if not args.no_cpu_baseline and world == 1:   # torchrun pins ranks to one host thread: the CPU arm runs at N=1 only
         rate, secs = cpu_baseline_sample(wl, args.sample_trees)
         import oracle
