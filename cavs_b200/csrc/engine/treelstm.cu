@@ -73,7 +73,7 @@ struct cavs_treelstm {
   TcOperandMap map_S, map_HK, map_dA3, map_ZF;              // K-major A operands: [rows, k]
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
   TcOperandMap map_Uiou_k64, map_Uf_k64;                     // the dgrad maps again for 64-column tiles (small levels)
-  TcOperandMap map_P, map_Q, map_ds, map_dq;                 // level-local outputs (rows past a level's end are scratch)
+  TcOperandMap map_P, map_Q, map_ds;                         // level-local outputs (rows past a level's end are scratch)
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
   // ---- batches: two slots so the tables of the next batch can be packed and uploaded while the
   // current one executes; forward() promotes the staged slot ----
@@ -209,7 +209,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->dOut = w.Take<float>(e->FusedDh() || e->Headless() ? 0 : N * H);
   e->dz8 = w.Take<float>(e->FusedDh() ? N * kHeadDzPitch : 0);
   e->ds = w.Take<float>(L * H);
-  e->dq = w.Take<float>(L * K * H);
+  e->dq = w.Take<float>(c.gemm_bf16 ? 0 : L * K * H);   // bf16 mode: the dq product is scattered by its own epilogue
   e->dX = w.Take<float>(T * E);
   e->loss = w.Take<float>(N);
   e->dB_tmp = w.Take<float>(CellBwdFusesBias(c.hidden) ? static_cast<size_t>(CellBwdMaxGrid()) * 4 * H : 4 * H);
@@ -317,7 +317,6 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     if (!rc) rc = EncodeTcOutput(&e->map_P, e->P, L, 3 * H, 3 * H, true);
     if (!rc) rc = EncodeTcOutput(&e->map_Q, e->Q, L * K, H, H, true);
     if (!rc) rc = EncodeTcOutput(&e->map_ds, e->ds, L, H, H, false);
-    if (!rc) rc = EncodeTcOutput(&e->map_dq, e->dq, L * K, H, H, false);
     if (rc) { delete e; return rc; }
   }
   cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), 2 * e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
@@ -428,37 +427,37 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     n_seg = n;
     CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
   } else {
-  // Stable counting sort of rows by token -> segments and chunks for the embedding gradient.
-  e->bucket.assign(static_cast<size_t>(V) + 1, 0);
-  for (int t = 0; t < n; ++t) ++e->bucket[h_tok[t] + 1];
-  for (int v = 0; v < V; ++v) { if (e->bucket[v + 1]) ++n_seg; e->bucket[v + 1] += e->bucket[v]; }
-  for (int v = 0; v < V; ++v) n_chunks += (e->bucket[v + 1] - e->bucket[v] + kEmbedChunk - 1) / kEmbedChunk;
-  int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_off);
-  int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.seg_first_chunk);
-  int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
-  int32_t* h_chunk_out = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_out);
-  int32_t* h_multi = view(static_cast<size_t>(n_chunks) + 1, &bt.multi_seg);   // each listed segment has >= 2 chunks
-  CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
-  int si = 0, ci = 0, n_multi = 0;
-  e->slot_of_token.resize(V);
-  for (int v = 0; v < V; ++v) {
-    const int b0 = e->bucket[v], b1 = e->bucket[v + 1];
-    if (b0 == b1) continue;
-    e->slot_of_token[v] = si;
-    h_seg_tok[si] = v;
-    // a token whose rows fit one chunk gets its sum written by the first pass of the segmented sums
-    const bool single = b1 - b0 <= kEmbedChunk;
-    if (!single) h_multi[n_multi++] = si;
-    for (int b = b0; b < b1; b += kEmbedChunk) { h_chunk_out[ci] = single ? si : -1; h_chunk_off[ci++] = b; }
-    h_seg_first[si++] = ci - (b1 - b0 + kEmbedChunk - 1) / kEmbedChunk;
-  }
-  h_seg_first[si] = ci;
-  h_chunk_off[ci] = n;
-  bt.n_multi = n_multi;
-  for (int t = 0; t < n; ++t) {
-    h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
-    h_slot[t] = e->slot_of_token[h_tok[t]];
-  }
+    // Stable counting sort of rows by token -> segments and chunks for the embedding gradient.
+    e->bucket.assign(static_cast<size_t>(V) + 1, 0);
+    for (int t = 0; t < n; ++t) ++e->bucket[h_tok[t] + 1];
+    for (int v = 0; v < V; ++v) { if (e->bucket[v + 1]) ++n_seg; e->bucket[v + 1] += e->bucket[v]; }
+    for (int v = 0; v < V; ++v) n_chunks += (e->bucket[v + 1] - e->bucket[v] + kEmbedChunk - 1) / kEmbedChunk;
+    int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_off);
+    int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.seg_first_chunk);
+    int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
+    int32_t* h_chunk_out = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_out);
+    int32_t* h_multi = view(static_cast<size_t>(n_chunks) + 1, &bt.multi_seg);   // each listed segment has >= 2 chunks
+    CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
+    int si = 0, ci = 0, n_multi = 0;
+    e->slot_of_token.resize(V);
+    for (int v = 0; v < V; ++v) {
+      const int b0 = e->bucket[v], b1 = e->bucket[v + 1];
+      if (b0 == b1) continue;
+      e->slot_of_token[v] = si;
+      h_seg_tok[si] = v;
+      // a token whose rows fit one chunk gets its sum written by the first pass of the segmented sums
+      const bool single = b1 - b0 <= kEmbedChunk;
+      if (!single) h_multi[n_multi++] = si;
+      for (int b = b0; b < b1; b += kEmbedChunk) { h_chunk_out[ci] = single ? si : -1; h_chunk_off[ci++] = b; }
+      h_seg_first[si++] = ci - (b1 - b0 + kEmbedChunk - 1) / kEmbedChunk;
+    }
+    h_seg_first[si] = ci;
+    h_chunk_off[ci] = n;
+    bt.n_multi = n_multi;
+    for (int t = 0; t < n; ++t) {
+      h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
+      h_slot[t] = e->slot_of_token[h_tok[t]];
+    }
   }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
   // The device half is free once the last backward pass that read it has finished.
@@ -631,7 +630,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
       // work: the product's flops; the bytes the separate scatter used to move are no longer moved
       PROF(e, kProfGemm, 2.0 * rows * K * H * H, st, GemmBf16Mapped(ga, st));
     } else {
-      if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, &e->map_dq, &e->map_Uf_k64))) return rc;
+      if ((rc = Gemm(e, e->dq, H, 0, ZF_l, H, false, U_f, H, true, rows * K, H, H, false, st, &e->map_ZF, off * K, &e->map_Uf_k, nullptr, &e->map_Uf_k64))) return rc;
       PROF(e, kProfScatterGrad, static_cast<double>(rows) * (4.0 * H * (1 + K + K) + 4.0 * K), st,
            LaunchScatterChildGrad(e->mailbox, e->ds, e->dq, bt.child, nt, off, rows, H, K, st));
     }

@@ -152,6 +152,22 @@ CAVS_API int cavs_treelstm_cell_fwd(float* state, void* gates, const void* A, co
 CAVS_API int cavs_treelstm_cell_bwd(void* dA, void* ZF, int bf16, float* mailbox, const float* dOut, const void* gates,
                                     const float* state, const int32_t* child, const int32_t* parent, int n_total, int off,
                                     int rows, int hidden, int n_slots, int leaf, void* stream);
+/* The fused cell in operator form, for hosts that keep the reference's op-by-op dataflow inside Node(): every
+ * input is a dense level-local tensor (fp32, like all of the reference's ops).  Forward: A [rows,4H] = x.W
+ * (i,o,u,f), P [rows,3H] = (sum h).U_iou, Q[c] [rows,H] = h_c.U_f, child_hc[c] [rows,2H] = Gather(Child=c) (h|c);
+ * a NULL entry of Q / child_hc stands for a slot without children in this level (zeros, as the zero-filled Gather
+ * gives, op_impl_graphop.cu:77-86).  Writes hc [rows,2H] (what Scatter takes) and gates [rows,(3+n_slots)H].
+ * One launch instead of the elementwise / slice / concat ops of apps/paper/tree-lstm-cavs.cc:150-171.
+ * Backward: d_hc [rows,2H] = the gradient the parents left (NULL for a level of roots), dOut [rows,H] = the pushed
+ * h's gradient (NULL if none); writes dA [rows,4H] (zi|zo|zu|sum zf: the gradients of A; its first 3H columns are
+ * the gradient of P), ZF[c] [rows,H] (gradient of Q[c]) and d_child_c[c] [rows,H] (the c half of what is scattered
+ * to child c; the h half is the sum of the MatMul gradients of P and Q[c]).  NULL entries are not written. */
+CAVS_API int cavs_treelstm_cell_dense_fwd(float* hc, float* gates, const float* A, const float* P, const float* const* Q,
+                                          const float* const* child_hc, const float* bias, int rows, int hidden, int n_slots,
+                                          void* stream);
+CAVS_API int cavs_treelstm_cell_dense_bwd(float* dA, float* const* ZF, float* const* d_child_c, const float* d_hc,
+                                          const float* dOut, const float* gates, const float* hc, const float* const* child_hc,
+                                          int rows, int hidden, int n_slots, void* stream);
 /* mailbox[child_c(t)].h = ds[b] + dq[b,c]: the child-state gradient scatter. */
 CAVS_API int cavs_scatter_child_grad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total,
                                      int off, int rows, int hidden, int n_slots, void* stream);

@@ -3,11 +3,13 @@
 //
 //   graph_ops_test cpu   registry, gradient pairing and the scheduler facade (no CUDA call)
 //   graph_ops_test gpu   Gather / Scatter / Pull / Push / FunctionPopRet on a device, compared
-//                        bit-for-bit with the CPU oracle's row ops driven by the same lists
+//                        bit-for-bit with the CPU oracle's row ops driven by the same lists; the fused
+//                        TreeLSTMCell / TreeLSTMCell_grad operators against a host restatement
 //
 // Links the product host library and the test oracle (oracle/libcavs_oracle.so).
 #include <cuda_runtime.h>
 
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -246,13 +248,111 @@ static void TestGraphOpsOnDevice(bool aligned) {
   EXPECT(cudaGetLastError() == cudaSuccess);
 }
 
+// The fused cell operators: registration, shape inference and gradient definition (no CUDA call).
+static OpDef FusedCellDef(int k) {
+  OpDefBuilder b("TreeLSTMCell");
+  b.Input("xW").Input("sU");
+  for (int c = 0; c < k; ++c) b.Input("hUf" + std::to_string(c));
+  for (int c = 0; c < k; ++c) b.Input("child" + std::to_string(c));
+  b.Input("B").Output("hc").Output("gates").AttrSingle("Slots", k);
+  return b.Device("GPU").Finalize();
+}
+static void TestFusedCellDecl() {
+  const int K = 2, H = 6, n = 5;
+  OpDef def = FusedCellDef(K);
+  std::unique_ptr<OpImpl> op(CreateOp(def));
+  EXPECT(op != nullptr);
+  auto shape = [](int a, int b) { TensorShapeDef s; s.add_dim(a); s.add_dim(b); return s; };
+  std::vector<TensorShapeDef> in = {shape(n, 4 * H), shape(n, 3 * H), shape(n, H), shape(n, H), shape(n, 2 * H), shape(n, 2 * H)};
+  TensorShapeDef bias; bias.add_dim(4 * H); in.push_back(bias);
+  std::vector<TensorShapeDef> out = backend::ShapeInference(def, in);
+  EXPECT(out.size() == 2 && out[0].dim(0) == n && out[0].dim(1) == 2 * H && out[1].dim(1) == (3 + K) * H);
+  std::vector<OpDef> g = backend::MakeGradient(def);
+  EXPECT(g.size() == 1 && g[0].name() == GetGradientName("TreeLSTMCell"));
+  EXPECT(g[0].input_size() == 3 + K && g[0].output_size() == 1 + 2 * K);
+  EXPECT(g[0].input(0) == GetGradientName("hc") && g[0].input(1) == "gates" && g[0].input(3) == "child0");
+  EXPECT(g[0].output(0) == GetGradientName("xW") && g[0].output(1) == GetGradientName("hUf0"));
+  EXPECT(GetSingleArg<int>(g[0], "Slots") == K);
+  std::unique_ptr<OpImpl> gop(CreateOp(g[0]));
+  EXPECT(gop != nullptr);
+}
+
+// Forward and gradient of the fused cell on a device against a host restatement of
+// apps/paper/tree-lstm-cavs.cc:150-171 and its gradient rules.
+static void TestFusedCellOnDevice() {
+  const int K = 2, H = 20, n = 7, G = (3 + K) * H;
+  auto fill = [](std::vector<float>& v, unsigned seed, float scale) {
+    for (size_t i = 0; i < v.size(); i++) { seed = seed * 1664525u + 1013904223u; v[i] = scale * ((float)(seed >> 8) / 8388608.0f - 1.0f); }
+  };
+  std::vector<float> hA((size_t)n * 4 * H), hP((size_t)n * 3 * H), hQ[2], hC[2], hB(4 * H), hD((size_t)n * 2 * H);
+  fill(hA, 1, 1.0f); fill(hP, 2, 1.0f); fill(hB, 3, 0.3f); fill(hD, 4, 0.5f);
+  for (int c = 0; c < K; c++) { hQ[c].resize((size_t)n * H); hC[c].resize((size_t)n * 2 * H); fill(hQ[c], 10 + c, 1.0f); fill(hC[c], 20 + c, 1.0f); }
+  auto dev = [&](const char* name, std::vector<int> shape, const std::vector<float>* src) {
+    Tensor t(name, GPU, DT_FLOAT, TensorShape(shape));
+    if (src) cudaMemcpy(t.mutable_data<float>(), src->data(), src->size() * sizeof(float), cudaMemcpyHostToDevice);
+    return t;
+  };
+  Tensor A = dev("xW", {n, 4 * H}, &hA), P = dev("sU", {n, 3 * H}, &hP), B = dev("B", {4 * H}, &hB), D = dev("d_hc", {n, 2 * H}, &hD);
+  Tensor Q0 = dev("q0", {n, H}, &hQ[0]), Q1 = dev("q1", {n, H}, &hQ[1]), C0 = dev("c0", {n, 2 * H}, &hC[0]), C1 = dev("c1", {n, 2 * H}, &hC[1]);
+  Tensor hc = dev("hc", {n, 2 * H}, nullptr), gates = dev("gates", {n, G}, nullptr);
+  Tensor dA = dev("dA", {n, 4 * H}, nullptr), zf0 = dev("zf0", {n, H}, nullptr), zf1 = dev("zf1", {n, H}, nullptr);
+  Tensor dc0 = dev("dc0", {n, H}, nullptr), dc1 = dev("dc1", {n, H}, nullptr);
+  OpDef def = FusedCellDef(K);
+  std::unique_ptr<OpImpl> op(CreateOp(def)), gop(CreateOp(backend::MakeGradient(def)[0]));
+  OpContext fwd, bwd;
+  for (const Tensor* t : {&A, &P, &Q0, &Q1, &C0, &C1, &B}) fwd.AppendInput(t);
+  fwd.AppendOutput(&hc); fwd.AppendOutput(&gates);
+  for (const Tensor* t : {&D, &gates, &hc, &C0, &C1}) bwd.AppendInput(t);
+  for (Tensor* t : {&dA, &zf0, &zf1, &dc0, &dc1}) bwd.AppendOutput(t);
+  op->Compute(&fwd);
+  gop->Compute(&bwd);
+  EXPECT(cudaDeviceSynchronize() == cudaSuccess);
+  auto host = [&](const Tensor& t) { std::vector<float> v(t.count()); cudaMemcpy(v.data(), t.data<float>(), v.size() * sizeof(float), cudaMemcpyDeviceToHost); return v; };
+  std::vector<float> g_hc = host(hc), g_dA = host(dA), g_zf[2] = {host(zf0), host(zf1)}, g_dc[2] = {host(dc0), host(dc1)};
+  auto sig = [](float x) { return 1.0f / (1.0f + std::exp(-x)); };
+  // max-norm relative error over everything compared (the contract of the fp32 configurations)
+  double max_diff = 0, max_want = 0;
+  auto cmp = [&](float got, float want) {
+    max_diff = std::fmax(max_diff, std::fabs((double)got - want));
+    max_want = std::fmax(max_want, std::fabs((double)want));
+  };
+  for (int b = 0; b < n; b++)
+    for (int j = 0; j < H; j++) {
+      const float* a = &hA[(size_t)b * 4 * H];
+      const float* p = &hP[(size_t)b * 3 * H];
+      float gi = sig((a[j] + p[j]) + hB[j]), go = sig((a[H + j] + p[H + j]) + hB[3 * H + j]);
+      float gu = std::tanh((a[2 * H + j] + p[2 * H + j]) + hB[2 * H + j]);
+      float gf[2], cc = gi * gu;
+      for (int c = 0; c < K; c++) { gf[c] = sig((a[3 * H + j] + hQ[c][(size_t)b * H + j]) + hB[H + j]); cc = cc + gf[c] * hC[c][(size_t)b * 2 * H + H + j]; }
+      float th = std::tanh(cc);
+      cmp(g_hc[(size_t)b * 2 * H + j], go * th);
+      cmp(g_hc[(size_t)b * 2 * H + H + j], cc);
+      float dh = hD[(size_t)b * 2 * H + j], mc = hD[(size_t)b * 2 * H + H + j];
+      float dc = mc + (dh * go) * (1.0f - th * th);
+      float zfs = 0;
+      for (int c = 0; c < K; c++) {
+        float z = (dc * hC[c][(size_t)b * 2 * H + H + j]) * gf[c] * (1.0f - gf[c]);
+        zfs += z;
+        cmp(g_zf[c][(size_t)b * H + j], z);
+        cmp(g_dc[c][(size_t)b * H + j], dc * gf[c]);
+      }
+      cmp(g_dA[(size_t)b * 4 * H + j], (dc * gu) * gi * (1.0f - gi));
+      cmp(g_dA[(size_t)b * 4 * H + H + j], (dh * th) * go * (1.0f - go));
+      cmp(g_dA[(size_t)b * 4 * H + 2 * H + j], (dc * gi) * (1.0f - gu * gu));
+      cmp(g_dA[(size_t)b * 4 * H + 3 * H + j], zfs);
+    }
+  EXPECT(max_want > 0.1 && max_diff / max_want < 1e-5);
+}
+
 int main(int argc, char** argv) {
   const std::string mode = argc > 1 ? argv[1] : "cpu";
   TestRegistryAndDecls();
+  TestFusedCellDecl();
   TestSchedulerFacade();
   if (mode == "gpu") {
     TestGraphOpsOnDevice(false);   // the reference's positional lists
     TestGraphOpsOnDevice(true);    // aligned lists
+    TestFusedCellOnDevice();
   }
   if (g_failures == 0) std::printf("graph_ops_test %s: ok\n", mode.c_str());
   return g_failures == 0 ? 0 : 1;
