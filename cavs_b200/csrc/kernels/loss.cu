@@ -233,8 +233,8 @@ LossHeadKernel(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
 // hidden without occupancy.  Each thread owns four columns for the CTA's whole life: its slice of the
 // classifier and its dWc accumulators live in registers, every row is read from DRAM exactly once and
 // from shared memory once.  Per batch: partial logits per thread -> transpose-reduce inside the warp
-// (lane l ends up with row l/4) -> shared memory across the 8 warps -> one thread per row finishes the
-// softmax -> every thread adds dz^T h for its columns from registers.  Same per-CTA partial record as
+// (lane l ends up with row l/4) -> shared memory across the 8 warps -> one barrier -> every warp finishes
+// the softmax of the 8 rows -> every thread adds dz^T h for its columns from registers.  Same per-CTA partial record as
 // LossHeadKernel.  A bulk copy that does not land within the wait limit raises *status (if given),
 // poisons the CTA's loss sum with NaN and ends the CTA's loop.
 constexpr int kStreamRows = 8;
@@ -248,10 +248,8 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
                int* __restrict__ status) {
   extern __shared__ __align__(16) float sm[];
   float* stage = sm;                                                  // [kStreamStages][kStreamRows][H]
-  float* red = sm + kStreamStages * kStreamRows * H;                  // [kWarps][kStreamRows][C]
-  float* sdz = red + kWarps * kStreamRows * C;                        // [kStreamRows][C]
+  float* red = sm + kStreamStages * kStreamRows * H;                  // [2][kWarps][kStreamRows][C], by batch parity
   __shared__ __align__(8) unsigned long long bars[kStreamStages];
-  __shared__ int s_abort;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int j = tid * 4;
   const bool col_ok = j < H;
@@ -269,7 +267,6 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
       bulk::Load(bulk::SmemAddr(stage + (s * kStreamRows + r) * H), h + static_cast<long long>(r0 + r) * h_pitch, row_bytes, bar);
   };
   if (tid == 0) {
-    s_abort = 0;
     for (int s = 0; s < kStreamStages; ++s) bulk::MbarInit(bulk::SmemAddr(&bars[s]), 1);
     bulk::FenceMbarInit();
   }
@@ -287,12 +284,13 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
   }
   float accb = 0.0f;       // thread c < C: bias gradient of class c
   float loss_acc = 0.0f;   // thread r < kStreamRows: loss of the rows it finished
+  bool aborted = false;    // uniform across the CTA (decided at the batch barrier)
 
   for (int k = 0; k < my_batches; ++k) {
     const int s = k % kStreamStages;
     const int r0 = (blockIdx.x + k * gridDim.x) * kStreamRows;
     const int cnt = min(kStreamRows, rows - r0);
-    if (!bulk::MbarWait(bulk::SmemAddr(&bars[s]), (k / kStreamStages) & 1)) s_abort = 1;
+    const bool landed = bulk::MbarWait(bulk::SmemAddr(&bars[s]), (k / kStreamStages) & 1);
     float hr[kStreamRows][4];
 #pragma unroll
     for (int r = 0; r < kStreamRows; ++r) {
@@ -324,57 +322,60 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
       y += __shfl_xor_sync(0xffffffffu, y, 2);
       y += __shfl_xor_sync(0xffffffffu, y, 1);
       // lane l now holds the warp's sum for row ((l>>2)&1) + 2*((l>>3)&1) + 4*((l>>4)&1) = l >> 2
-      if ((lane & 3) == 0) red[(warp * kStreamRows + (lane >> 2)) * C + c] = y;
+      if ((lane & 3) == 0) red[(((k & 1) * kWarps + warp) * kStreamRows + (lane >> 2)) * C + c] = y;
     }
-    __syncthreads();   // the stage has been read by everyone and the partial logits are visible
-    if (tid == 0 && k + kStreamStages < my_batches && !s_abort) issue(k + kStreamStages);
-    if (tid < kStreamRows) {
-      const int t = r0 + tid;
-      float dz[C];
+    // The barrier: the stage has been read by everyone and the partial logits are visible.  It also carries
+    // every thread's wait result, so all threads agree on whether to go on.
+    aborted = __syncthreads_or(landed ? 0 : 1) != 0;
+    if (aborted) break;
+    if (tid == 0 && k + kStreamStages < my_batches) issue(k + kStreamStages);
+    // Every warp finishes the softmax of all eight rows itself (lane l takes row l & 7; the four copies per
+    // row are identical), so there is no second barrier and no phase in which eight threads work while the
+    // rest wait; the d(logits) values then travel by shuffle.  red is double-buffered by batch parity: a
+    // warp may already write the next batch's partials while a slower one still reads these.
+    const int rr = lane & (kStreamRows - 1);
+    const int t = r0 + rr;
+    float dz[C];
+    float lrow = 0.0f;
+    {
+      float z[C], mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < C; ++c) dz[c] = 0.0f;
-      if (tid < cnt) {
-        float z[C], mx = -INFINITY;
+      for (int c = 0; c < C; ++c) {
+        float a = 0.0f;
 #pragma unroll
-        for (int c = 0; c < C; ++c) {
-          float a = 0.0f;
-#pragma unroll
-          for (int w = 0; w < kWarps; ++w) a += red[(w * kStreamRows + tid) * C + c];
-          z[c] = a + bc[c];
-          mx = fmaxf(mx, z[c]);
-        }
-        float den = 0.0f;
-#pragma unroll
-        for (int c = 0; c < C; ++c) { z[c] = expf(z[c] - mx); den += z[c]; }
-        const int y = label[t];
-        float lrow = 0.0f;
-#pragma unroll
-        for (int c = 0; c < C; ++c) {
-          const float pc = z[c] / den;
-          dz[c] = (y >= 0) ? (pc - (c == y ? 1.0f : 0.0f)) * inv_rows : 0.0f;
-          if (c == y) lrow = -logf(pc);
-        }
-        loss[t] = lrow;
-        loss_acc += lrow;
-        if (dz_out != nullptr) {
-          float pad[kMaxC];
-#pragma unroll
-          for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? dz[c < C ? c : 0] : 0.0f;
-          float4* dst = reinterpret_cast<float4*>(dz_out + static_cast<long long>(t) * kMaxC);
-          dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
-          dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
-        }
+        for (int w = 0; w < kWarps; ++w) a += red[(((k & 1) * kWarps + w) * kStreamRows + rr) * C + c];
+        z[c] = a + bc[c];
+        mx = fmaxf(mx, z[c]);
       }
+      float den = 0.0f;
 #pragma unroll
-      for (int c = 0; c < C; ++c) sdz[tid * C + c] = dz[c];
+      for (int c = 0; c < C; ++c) { z[c] = expf(z[c] - mx); den += z[c]; }
+      const int y = rr < cnt ? label[t] : -1;
+      const float inv_den = 1.0f / den;
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const float pc = z[c] * inv_den;
+        dz[c] = (y >= 0) ? (pc - (c == y ? 1.0f : 0.0f)) * inv_rows : 0.0f;
+        if (c == y) lrow = -logf(pc);
+      }
     }
-    __syncthreads();
-    if (s_abort) break;   // uniform: read after the barrier that follows every write
+    if (tid < kStreamRows && tid < cnt) {   // warp 0, one lane per row, publishes the row's results
+      loss[t] = lrow;
+      loss_acc += lrow;
+      if (dz_out != nullptr) {
+        float pad[kMaxC];
+#pragma unroll
+        for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? dz[c < C ? c : 0] : 0.0f;
+        float4* dst = reinterpret_cast<float4*>(dz_out + static_cast<long long>(t) * kMaxC);
+        dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
+        dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
+      }
+    }
 #pragma unroll
     for (int r = 0; r < kStreamRows; ++r) {
       float d[C];
 #pragma unroll
-      for (int c = 0; c < C; ++c) d[c] = sdz[r * C + c];
+      for (int c = 0; c < C; ++c) d[c] = __shfl_sync(0xffffffffu, dz[c], r);
 #pragma unroll
       for (int c = 0; c < C; ++c)
 #pragma unroll
@@ -387,11 +388,11 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
           for (int e = 0; e < 4; ++e) a[e] = fmaf(d[c], wc[c][e], a[e]);
         __stcs(reinterpret_cast<float4*>(dOut + static_cast<long long>(r0 + r) * H + j), make_float4(a[0], a[1], a[2], a[3]));
       }
-      if (tid < C) accb += sdz[r * C + tid];
+      // bias gradient: thread c < C of warp 0 adds d(logits)[r][c], rows in order
+#pragma unroll
+      for (int c = 0; c < C; ++c)
+        if (tid == c) accb += d[c];
     }
-    // No barrier here: red is rewritten before the next batch's first barrier, by threads that have passed
-    // this batch's second one (its readers finished before it); sdz is rewritten after the next batch's
-    // first barrier, which every thread reaches only after this loop.
   }
   float* mine = partial + static_cast<size_t>(blockIdx.x) * PartialStride(C, H);
   if (col_ok) {
@@ -406,7 +407,7 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
   if (tid == 0) {
     float sum = 0.0f;
     for (int r = 0; r < kStreamRows; ++r) sum += sloss[r];
-    if (s_abort) {
+    if (aborted) {
       sum = NAN;
       if (status != nullptr) atomicExch(status, 1);
     }
@@ -463,7 +464,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   if (stream_ok && rows > 0) {
     const int n_batches = (rows + kStreamRows - 1) / kStreamRows;
     const int sgrid = std::max(1, std::min(n_batches, SmCount() * kCtasPerSm));
-    const size_t ssmem = (static_cast<size_t>(kStreamStages) * kStreamRows * H + (kWarps + 1) * kStreamRows * C) * sizeof(float);
+    const size_t ssmem = (static_cast<size_t>(kStreamStages) * kStreamRows * H + 2 * kWarps * kStreamRows * C) * sizeof(float);
 #define STREAM_CASE(CC)                                                                                              \
   case CC:                                                                                                           \
     if (ssmem > 48 * 1024)                                                                                           \
