@@ -144,3 +144,25 @@ def test_embedding_gradient_is_announced_before_the_weight_gradients(cuda):
         assert torch.equal(early, eng.grads[:V * E])
     ref = _oracle(s, tok_job, label_job, params, H, E, V, C)
     assert rel_err(early.cpu().numpy(), ref["dEmb"]) < 1e-5
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_training_reduces_the_loss(cuda, bf16):
+    """Forward + backward + Adagrad on one fixed batch: the loss falls step after step at a small learning rate
+    (the whole step loop, not one gradient)."""
+    H, E, V, C = 64, 64, 200, 5
+    parents, tok_job, label_job = make_tree_batch(31, 32, 2, 20, V, C)
+    params = make_params(8, H, E, V, C, scale=0.1)
+    s = S.Schedule().load(parents)
+    eng = TreeLSTM(H, E, V, C, gemm_bf16=bf16, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+    eng.set_params(params)
+    acc = torch.zeros_like(eng.params)
+    losses = []
+    for _ in range(40):
+        eng.load_batch(s, tok_job, label_job)
+        eng.forward()
+        eng.backward()
+        losses.append(eng.read_loss() / s.n_total)
+        eng.adagrad(acc, 0.01)
+    assert all(b < a for a, b in zip(losses[:5], losses[1:6])), losses
+    assert losses[-1] < 0.97 * losses[0], losses
