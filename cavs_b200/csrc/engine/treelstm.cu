@@ -63,6 +63,14 @@ struct cavs_treelstm {
   const float* x_dense = nullptr;   // [n, embed] rows in tensor-id order, pitch x_pitch
   long long x_pitch = 0;
   const float* dh_ext = nullptr;    // [n, hidden] dense
+  // Leaf states per token: a leaf's h|c depends only on its token, so the leaf level is computed once per distinct
+  // token into rows [max_vertices, max_vertices + tokens) of `state`, and everything that reads a leaf's state
+  // (the parents' gather and cell kernels, the loss head) goes through remapped row indices.  Needs the
+  // streaming loss head (it reads rows by index) and a caller that does not read `state` rows directly.
+  bool leaf_tok = false;
+  bool LeafTokEligible() const {
+    return cfg.vocab > 0 && cfg.classes > 0 && !WideHead() && cfg.hidden % 4 == 0 && cfg.hidden <= 1024 && OffWc() % 4 == 0;
+  }
   bool Dense() const { return cfg.vocab == 0; }
   bool Headless() const { return cfg.classes == 0; }
   int Cp() const { return (cfg.classes + 7) & ~7; }
@@ -80,6 +88,7 @@ struct cavs_treelstm {
   struct Batch {
     int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
     std::vector<int32_t> level_off;
+    int32_t *child_st = nullptr, *state_row = nullptr;   // leaf_tok: state rows of the children / of every vertex
     int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
             *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr;
     int n_multi = 0;
@@ -170,7 +179,7 @@ size_t MaxSegments(const cavs_treelstm_config& c) { return c.vocab == 0 ? c.max_
 size_t MaxChunks(const cavs_treelstm_config& c) { return MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
-  return (c.n_slots + 5) * n + 3 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
+  return (2 * c.n_slots + 6) * n + 3 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -183,6 +192,15 @@ size_t SplitKBytes(const cavs_treelstm_config& c) {
   if (c.classes > 8) b = std::max(b, GemmBf16ScratchBytes(c.classes, H, 16));
   (void)N; (void)K;
   return b;
+}
+
+// Everything about an engine that follows from its configuration (and the environment) alone.
+void InitModes(cavs_treelstm* e, const cavs_treelstm_config& cfg) {
+  e->cfg = cfg;
+  e->bf16 = cfg.gemm_bf16 != 0;
+  e->elt = e->bf16 ? 2 : 4;
+  const char* v = std::getenv("CAVS_LEAF_BY_TOKEN");   // "0": keep one state row per leaf vertex
+  e->leaf_tok = e->LeafTokEligible() && !(v != nullptr && v[0] == '0');
 }
 
 // Carves every device array out of the workspace; with base == nullptr it only sizes it.
@@ -203,7 +221,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->P = w.Take<uint8_t>(L * 3 * H * elt);
   e->Q = w.Take<uint8_t>(L * K * H * elt);
   e->gates = w.Take<uint8_t>(N * (3 + K) * H * elt);
-  e->state = w.Take<float>(N * 2 * H);
+  e->state = w.Take<float>((N + (e->leaf_tok ? T : 0)) * 2 * H);   // per-token leaf rows follow the vertex rows
   e->mailbox = w.Take<float>(N * 2 * H);
   // d(pushed h): materialised only by the wide loss head; the fused head hands d(logits) rows (dz8) to the cell gradient
   e->dOut = w.Take<float>(e->FusedDh() || e->Headless() ? 0 : N * H);
@@ -281,7 +299,8 @@ extern "C" size_t cavs_treelstm_param_count(const cavs_treelstm_config* cfg) {
 
 extern "C" size_t cavs_treelstm_workspace_bytes(const cavs_treelstm_config* cfg) {
   if (CheckConfig(cfg) != CAVS_OK) return 0;
-  cavs_treelstm tmp; tmp.cfg = *cfg;
+  cavs_treelstm tmp;
+  InitModes(&tmp, *cfg);
   return Carve(&tmp, nullptr);
 }
 
@@ -291,9 +310,7 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
   CAVS_REQUIRE(out && workspace, CAVS_ERR_BAD_ARG, "treelstm_create: null pointer");
   CAVS_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, CAVS_ERR_BAD_ARG, "treelstm_create: workspace must be 256-byte aligned");
   auto* e = new cavs_treelstm();
-  e->cfg = *cfg;
-  e->bf16 = cfg->gemm_bf16 != 0;
-  e->elt = e->bf16 ? 2 : 4;
+  InitModes(e, *cfg);
   const size_t need = Carve(e, workspace);
   if (need > workspace_bytes) {
     delete e;
@@ -407,6 +424,8 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   int32_t* h_label = view(nt, &bt.label);
   int32_t* h_order = view(nt, &bt.order);
   int32_t* h_slot = view(nt, &bt.tok_slot);
+  int32_t* h_child_st = e->leaf_tok ? view(static_cast<size_t>(K) * nt, &bt.child_st) : nullptr;
+  int32_t* h_state_row = e->leaf_tok ? view(nt, &bt.state_row) : nullptr;
   std::memcpy(h_child, sch.child_t().data(), sizeof(int32_t) * K * nt);
   std::memcpy(h_parent, sch.parent_t().data(), sizeof(int32_t) * nt);
   const int32_t* t2j = sch.t2j().data();
@@ -457,6 +476,16 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     for (int t = 0; t < n; ++t) {
       h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
       h_slot[t] = e->slot_of_token[h_tok[t]];
+    }
+  }
+  if (e->leaf_tok) {
+    // State rows: a leaf (level 0) lives in its token's row behind the vertex rows, every other vertex in its own.
+    const int n_leaf = sch.n_levels() > 0 ? bt.level_off[1] : 0;
+    const int base = e->cfg.max_vertices;
+    for (int t = 0; t < nt; ++t) h_state_row[t] = t < n_leaf ? base + h_slot[t] : t;
+    for (size_t i = 0; i < static_cast<size_t>(K) * nt; ++i) {
+      const int ch = h_child[i];
+      h_child_st[i] = ch >= 0 ? h_state_row[ch] : ch;
     }
   }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
@@ -513,9 +542,13 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     if (l == 0) {
       // leaf rows: read the token row's i,o,u blocks (3H) + its index, write h|c (2H); the gates are recomputed by
       // the backward pass, not stored
-      PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * 3 + 4.0 * 2) + 4), st,
-           LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, true, st,
-                         false));
+      PROF(e, kProfCellFwd, static_cast<double>(e->leaf_tok ? n_tok : rows) * (H * (elt * 3 + 4.0 * 2) + 4), st,
+           e->leaf_tok
+               // one state row per distinct token (row s of A -> row max_vertices + s of state), not per leaf
+               ? LaunchCellFwd(e->state + static_cast<size_t>(e->cfg.max_vertices) * 2 * H, e->gates, e->A, nullptr, nullptr, e->bf16,
+                               B, bt.child, nullptr, n_tok, 0, n_tok, H, K, true, st, false)
+               : LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K,
+                               true, st, false));
       continue;
     }
     // Chained launches: a kernel releases its successor early when that successor is a GEMM (one CTA per
@@ -524,7 +557,7 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     ChainHint(true);       // gather -> P GEMM -> Q GEMM
     // read K child h rows (fp32) + K indices, write S and HK
     PROF(e, kProfGatherH, static_cast<double>(rows) * (4.0 * K * H + 4.0 * K + elt * (1 + K) * H), st,
-         LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, bt.child, nt, off, rows, H, K, st));
+         LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, e->leaf_tok ? bt.child_st : bt.child, nt, off, rows, H, K, st));
     const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
     if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn, &e->map_P))) return rc;
@@ -532,7 +565,8 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     if ((rc = Gemm(e, e->Q, H, pre, HK_l, H, false, U_f, H, false, rows * K, H, H, false, st, &e->map_HK, off * K, &e->map_Uf_mn, &e->map_Q))) return rc;
     // read the token row (4H) + index, P (3H), Q (KH), child c (KH); write gates ((3+K)H), h|c (2H)
     PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (4 + 3 + K + 3 + K) + 4.0 * (K + 2)) + 4), st,
-         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K, false, st));
+         LaunchCellFwd(e->state, e->gates, e->A, e->P, e->Q, e->bf16, B, e->leaf_tok ? bt.child_st : bt.child, bt.tok_slot, nt, off, rows,
+                       H, K, false, st));
   }
   ChainHint(false);
   (void)rc;
@@ -570,7 +604,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     PROF(e, kProfLossHead, static_cast<double>(n) * (4.0 * H + 8 + (fdh ? 4.0 * kHeadDzPitch : 4.0 * H)), st,
          LaunchLossHead(e->loss, e->tail, fdh ? nullptr : e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
                         e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
-                        e->loss_scratch, st, false, fdh ? e->dz8 : nullptr, e->Status()));
+                        e->loss_scratch, st, false, fdh ? e->dz8 : nullptr, e->Status(), e->leaf_tok ? bt.state_row : nullptr));
   } else {
     // Wide head (vocabulary-sized class count): logits = h Wc^T, row softmax cross-entropy, then
     // dH = dz Wc, dWc = dz^T h, dbc = column sums of dz -- FullyConnected + SoftmaxEntropyLoss and their
@@ -609,7 +643,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
          LaunchCellBwd(e->dA, e->ZF, e->bf16, e->mailbox, fuse_bias ? e->dB_tmp : nullptr, e->FusedDh() ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
                        e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
                        e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C, l == 0 ? e->A : nullptr,
-                       l == 0 ? bt.tok_slot : nullptr, l == 0 ? e->params + e->OffB() : nullptr));
+                       l == 0 ? bt.tok_slot : nullptr, l == 0 ? e->params + e->OffB() : nullptr,
+                       e->leaf_tok ? bt.child_st : nullptr));
     if (l == 0) break;
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
@@ -702,6 +737,15 @@ extern "C" int cavs_treelstm_set_output_grad(cavs_treelstm* e, const float* dh) 
   CAVS_REQUIRE(dh && (reinterpret_cast<uintptr_t>(dh) & 15u) == 0, CAVS_ERR_BAD_ARG, "treelstm_set_output_grad: rows must be 16-byte aligned");
   e->dh_ext = dh;
   return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e, CAVS_ERR_BAD_ARG, "treelstm_materialize_state: null handle");
+  if (!e->leaf_tok || e->active < 0) return CAVS_OK;
+  const cavs_treelstm::Batch& bt = e->slot[e->active];
+  const int n_leaf = bt.n_levels > 0 ? bt.level_off[1] : 0;
+  // leaf vertex t <- its token's row: rows [0, n_leaf) of state_row are exactly those source rows
+  return cavs_gather_rows(e->state, e->state, bt.state_row, n_leaf, static_cast<size_t>(2) * e->cfg.hidden * sizeof(float), stream);
 }
 
 extern "C" int cavs_treelstm_wait_embed_grad(cavs_treelstm* e, void* stream) {

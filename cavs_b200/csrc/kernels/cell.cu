@@ -233,7 +233,8 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
         const float* __restrict__ dOut, const typename GateType<T>::type* __restrict__ gates, const float* __restrict__ state,
         const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H,
         const float* __restrict__ dz, const float* __restrict__ Wc, int C, int chain_early,
-        const T* __restrict__ A, const int32_t* __restrict__ a_row, const float* __restrict__ bias) {
+        const T* __restrict__ A, const int32_t* __restrict__ a_row, const float* __restrict__ bias,
+        const int32_t* __restrict__ child_state) {
   ChainRelease(chain_early);
   ChainAcquire();
   __shared__ float fold[kThreads * 4 * V];
@@ -339,7 +340,8 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
           if (ch >= 0) {
             // c of the child is read from the state array, then d(c_child) = dc * f_c goes to the
             // child's mailbox row (a different array; the child's level runs in a later launch).
-            const Vec<V> cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
+            const int chs = child_state ? __ldg(child_state + static_cast<size_t>(c) * n_total + t) : ch;
+            const Vec<V> cch = LoadF<V>(state + static_cast<size_t>(chs) * 2 * H + H + j);
             Vec<V> dcc;
 #pragma unroll
             for (int e = 0; e < V; ++e) {
@@ -485,7 +487,7 @@ int CellBwdGrid(int rows, int H) {
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st, const float* dz, const float* Wc, int C, const void* A,
-                  const int32_t* a_row, const float* bias) {
+                  const int32_t* a_row, const float* bias, const int32_t* child_state) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const bool head = dz != nullptr;
@@ -502,7 +504,7 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 #define CELL_BWD(TT, GT, LEAF, HEAD)                                                                                   \
   LaunchChained(CellBwd<TT, K, V, LEAF, HEAD>, dim3(grid), dim3(kThreads), head_smem, st, static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
                                                            static_cast<const GT*>(gates), state, child, parent, n_total, off,  \
-                                                           rows, H, dz, Wc, C, ChainEarly(), static_cast<const TT*>(A), a_row, bias)
+                                                           rows, H, dz, Wc, C, ChainEarly(), static_cast<const TT*>(A), a_row, bias, child_state)
   DISPATCH_KV(K, v, {
     if (bf16) {
       if (leaf) { if (head) CELL_BWD(__nv_bfloat16, __half, true, true); else CELL_BWD(__nv_bfloat16, __half, true, false); }

@@ -33,7 +33,10 @@ bool CellBwdFusesBias(int H);
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st, const float* dz = nullptr, const float* Wc = nullptr, int C = 0,
-                  const void* A = nullptr, const int32_t* a_row = nullptr, const float* bias = nullptr);
+                  const void* A = nullptr, const int32_t* a_row = nullptr, const float* bias = nullptr,
+                  const int32_t* child_state = nullptr);
+// child_state (optional, [K, n_total]): rows of `state` holding the children's cell state when they differ from
+// the children's tensor ids (leaf states shared per token); the mailbox is always addressed by `child`.
 // A / a_row / bias (optional, leaf levels only): recompute i, o, u and c from the input-projection rows instead of
 // reading the saved gates and cell state (A in the same precision as dA).
 // dz / Wc / C (optional): rebuild d(pushed h) = dz[t,:] . Wc inside the kernel instead of reading dOut
@@ -70,7 +73,9 @@ size_t LossHeadScratchBytes(int H, int C);
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
                    float* scratch, cudaStream_t st, bool accumulate = false,    // accumulate: add into dWc / dbc / loss_sum
-                   float* dz_out = nullptr, int* status = nullptr);
+                   float* dz_out = nullptr, int* status = nullptr, const int32_t* row_index = nullptr);
+// row_index (optional, [rows]): loss row t reads its hidden row at h[row_index[t]] (streaming form only).
+bool LossHeadStreams(const float* h, long long h_pitch, int H);   // would this shape take the streaming form?
 // status (optional, device): raised to 1 if a bounded wait on an asynchronous row copy expires.
 // dz_out (optional, [rows, 8]): d(logits) rows zero-padded to 8 floats.  With dz_out set, dOut may be NULL:
 // the cell-gradient kernel then rebuilds d(hidden) = dz Wc on the fly (LaunchCellBwd's head arguments)

@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ dz_out, float* __restrict__ partial,
                const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
                const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows,
-               int* __restrict__ status) {
+               int* __restrict__ status, const int32_t* __restrict__ row_index) {
   extern __shared__ __align__(16) float sm[];
   float* stage = sm;                                                  // [kStreamStages][kStreamRows][H]
   float* red = sm + kStreamStages * kStreamRows * H;                  // [2][kWarps][kStreamRows][C], by batch parity
@@ -263,8 +263,11 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
     const int cnt = min(kStreamRows, rows - r0);
     const uint32_t bar = bulk::SmemAddr(&bars[s]);
     bulk::MbarExpectTx(bar, row_bytes * cnt);
-    for (int r = 0; r < cnt; ++r)
-      bulk::Load(bulk::SmemAddr(stage + (s * kStreamRows + r) * H), h + static_cast<long long>(r0 + r) * h_pitch, row_bytes, bar);
+    for (int r = 0; r < cnt; ++r) {
+      // row_index (optional): the hidden row of loss row t lives at h[row_index[t]] (rows shared between vertices)
+      const long long src = row_index != nullptr ? row_index[r0 + r] : r0 + r;
+      bulk::Load(bulk::SmemAddr(stage + (s * kStreamRows + r) * H), h + src * h_pitch, row_bytes, bar);
+    }
   };
   if (tid == 0) {
     for (int s = 0; s < kStreamStages; ++s) bulk::MbarInit(bulk::SmemAddr(&bars[s]), 1);
@@ -445,13 +448,17 @@ int LossGrid(int rows) {
 
 }  // namespace
 
+bool LossHeadStreams(const float* h, long long h_pitch, int H) {
+  return H % 4 == 0 && H <= kThreads * 4 && h_pitch % 4 == 0 && (reinterpret_cast<uintptr_t>(h) & 15u) == 0;
+}
+
 size_t LossHeadScratchBytes(int H, int C) {
   return static_cast<size_t>(SmCount()) * kCtasPerSm * PartialStride(C, H) * sizeof(float);
 }
 
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
-                   float* scratch, cudaStream_t st, bool accumulate, float* dz_out, int* status) {
+                   float* scratch, cudaStream_t st, bool accumulate, float* dz_out, int* status, const int32_t* row_index) {
   CAVS_REQUIRE(rows >= 0 && H > 0 && C > 0, CAVS_ERR_BAD_ARG, "loss_head: bad shape");
   CAVS_REQUIRE(C <= kMaxC, CAVS_ERR_UNSUPPORTED, "loss_head: fused path supports at most 8 classes");
   CAVS_REQUIRE(H <= kThreads * kMaxColsPerThread, CAVS_ERR_UNSUPPORTED, "loss_head: hidden size above 2048");
@@ -461,6 +468,8 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   const bool stream_ok = H % 4 == 0 && H <= kThreads * 4 && h_pitch % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dOut) | reinterpret_cast<uintptr_t>(scratch) |
                            reinterpret_cast<uintptr_t>(Wc)) & 15u) == 0;
+  CAVS_REQUIRE(row_index == nullptr || stream_ok, CAVS_ERR_UNSUPPORTED,
+               "loss_head: indexed hidden rows need the streaming form (hidden a multiple of 4, at most 1024, 16-byte aligned rows)");
   if (stream_ok && rows > 0) {
     const int n_batches = (rows + kStreamRows - 1) / kStreamRows;
     const int sgrid = std::max(1, std::min(n_batches, SmCount() * kCtasPerSm));
@@ -469,7 +478,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   case CC:                                                                                                           \
     if (ssmem > 48 * 1024)                                                                                           \
       CAVS_CUDA(cudaFuncSetAttribute(LossHeadStream<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssmem));  \
-    LossHeadStream<CC><<<sgrid, kThreads, ssmem, st>>>(loss, dOut, dz_out, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows, status); \
+    LossHeadStream<CC><<<sgrid, kThreads, ssmem, st>>>(loss, dOut, dz_out, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows, status, row_index); \
     break;
     switch (C) {
       STREAM_CASE(1) STREAM_CASE(2) STREAM_CASE(3) STREAM_CASE(4) STREAM_CASE(5) STREAM_CASE(6) STREAM_CASE(7) STREAM_CASE(8)

@@ -138,6 +138,7 @@ class TreeLSTM:
         return t.cpu().numpy().reshape(shape)
 
     def state(self) -> np.ndarray:
+        check(lib().cavs_treelstm_materialize_state(self._h, _stream()))   # leaf rows may live per token
         return self.peek(0, (self.n, 2 * self.cfg.hidden))
 
     def loss_rows(self) -> np.ndarray:

@@ -273,6 +273,12 @@ CAVS_API int cavs_treelstm_backward(cavs_treelstm* e, void* stream);
  * Both engines load the same schedule; tokens may be NULL for a dense layer, labels for a headless one. */
 CAVS_API int cavs_treelstm_set_dense_input(cavs_treelstm* e, const float* x, long long pitch);
 CAVS_API int cavs_treelstm_set_output_grad(cavs_treelstm* e, const float* dh);
+/* With an embedding table and a fused loss head the engine keeps ONE state row per distinct leaf token (a leaf's h|c
+ * depends on nothing else) and reads leaf states through remapped row indices; the per-vertex rows of the leaves in
+ * peek array 0 are then not written by forward.  This call fills them in (a row gather on `stream`), for callers
+ * that want to look at every vertex's state.  A no-op for engines that keep per-vertex leaf rows (dense inputs, no
+ * loss head, more than 8 classes, hidden not a multiple of 4 or above 1024, or CAVS_LEAF_BY_TOKEN=0). */
+CAVS_API int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream);
 /* Makes `stream` wait until the embedding-gradient block (the first vocab*embed floats of the bound gradient
  * buffer) written by the most recent cavs_treelstm_backward is complete.  backward produces that block before
  * the weight gradients, so a data-parallel caller can start its cross-GPU reduction on another stream
