@@ -71,6 +71,9 @@ struct cavs_treelstm {
   bool LeafTokEligible() const {
     return cfg.vocab > 0 && cfg.classes > 0 && !WideHead() && cfg.hidden % 4 == 0 && cfg.hidden <= 1024 && OffWc() % 4 == 0;
   }
+  // Token inputs with hidden a multiple of 4: the leaf level's backward cell is folded into the per-token sums of dA
+  // (the leaves' dA rows are never stored) and the bias gradient is the column sum of the chunk partials.
+  bool TokGrad() const { return cfg.vocab > 0 && cfg.hidden % 4 == 0; }
   bool Dense() const { return cfg.vocab == 0; }
   bool Headless() const { return cfg.classes == 0; }
   int Cp() const { return (cfg.classes + 7) & ~7; }
@@ -90,7 +93,7 @@ struct cavs_treelstm {
     std::vector<int32_t> level_off;
     int32_t *child_st = nullptr, *state_row = nullptr;   // leaf_tok: state rows of the children / of every vertex
     int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
-            *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr;
+            *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr, *chunk_seg = nullptr;
     int n_multi = 0;
   };
   Batch slot[2];
@@ -101,7 +104,7 @@ struct cavs_treelstm {
   cudaEvent_t copied[2] = {nullptr, nullptr}, slot_done[2] = {nullptr, nullptr};
   cudaEvent_t emb_ready = nullptr;   // recorded in backward once the embedding gradient is complete
   bool slot_used[2] = {false, false};
-  std::vector<int32_t> bucket, slot_of_token;
+  std::vector<int32_t> bucket, slot_of_token, leaf_count;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
   bool prof_on = false;
   std::vector<cudaEvent_t> ev_pool;
@@ -176,10 +179,11 @@ int CheckConfig(const cavs_treelstm_config* c) {
 
 // Rows of the input projection: distinct tokens of a batch, or every vertex with dense inputs.
 size_t MaxSegments(const cavs_treelstm_config& c) { return c.vocab == 0 ? c.max_vertices : std::min<size_t>(c.max_vertices, c.vocab); }
-size_t MaxChunks(const cavs_treelstm_config& c) { return MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
+// A token's rows are cut into chunks of kEmbedChunk, separately for its leaves and its internal vertices.
+size_t MaxChunks(const cavs_treelstm_config& c) { return 2 * MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
-  return (2 * c.n_slots + 6) * n + 3 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
+  return (2 * c.n_slots + 6) * n + 4 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -446,15 +450,25 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     n_seg = n;
     CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
   } else {
-    // Stable counting sort of rows by token -> segments and chunks for the embedding gradient.
+    // Stable counting sort of rows by token -> segments and chunks for the per-token gradient sums.  Within a
+    // token the rows are in tensor-id order, so its leaves (level 0) come first; leaves and internal vertices get
+    // separate chunks.
+    const int n_leaf = sch.n_levels() > 0 ? bt.level_off[1] : 0;
     e->bucket.assign(static_cast<size_t>(V) + 1, 0);
+    e->leaf_count.assign(static_cast<size_t>(V), 0);
     for (int t = 0; t < n; ++t) ++e->bucket[h_tok[t] + 1];
-    for (int v = 0; v < V; ++v) { if (e->bucket[v + 1]) ++n_seg; e->bucket[v + 1] += e->bucket[v]; }
-    for (int v = 0; v < V; ++v) n_chunks += (e->bucket[v + 1] - e->bucket[v] + kEmbedChunk - 1) / kEmbedChunk;
+    for (int t = 0; t < n_leaf; ++t) ++e->leaf_count[h_tok[t]];
+    auto chunks_of = [](int rows) { return (rows + kEmbedChunk - 1) / kEmbedChunk; };
+    for (int v = 0; v < V; ++v) {
+      const int cnt = e->bucket[v + 1];
+      if (cnt) { ++n_seg; n_chunks += chunks_of(e->leaf_count[v]) + chunks_of(cnt - e->leaf_count[v]); }
+      e->bucket[v + 1] += e->bucket[v];
+    }
     int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_off);
     int32_t* h_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.seg_first_chunk);
     int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
     int32_t* h_chunk_out = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_out);
+    int32_t* h_chunk_seg = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_seg);
     int32_t* h_multi = view(static_cast<size_t>(n_chunks) + 1, &bt.multi_seg);   // each listed segment has >= 2 chunks
     CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
     int si = 0, ci = 0, n_multi = 0;
@@ -464,11 +478,18 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
       if (b0 == b1) continue;
       e->slot_of_token[v] = si;
       h_seg_tok[si] = v;
-      // a token whose rows fit one chunk gets its sum written by the first pass of the segmented sums
-      const bool single = b1 - b0 <= kEmbedChunk;
+      h_seg_first[si] = ci;
+      const int mid = b0 + e->leaf_count[v];                    // leaves [b0, mid), internal vertices [mid, b1)
+      // a token whose rows form one chunk gets its sum written by the first pass of the segmented sums
+      const bool single = chunks_of(mid - b0) + chunks_of(b1 - mid) == 1;
       if (!single) h_multi[n_multi++] = si;
-      for (int b = b0; b < b1; b += kEmbedChunk) { h_chunk_out[ci] = single ? si : -1; h_chunk_off[ci++] = b; }
-      h_seg_first[si++] = ci - (b1 - b0 + kEmbedChunk - 1) / kEmbedChunk;
+      for (int part = 0; part < 2; ++part)
+        for (int b = part ? mid : b0; b < (part ? b1 : mid); b += kEmbedChunk) {
+          h_chunk_out[ci] = single ? si : -1;
+          h_chunk_seg[ci] = si;
+          h_chunk_off[ci++] = b;
+        }
+      ++si;
     }
     h_seg_first[si] = ci;
     h_chunk_off[ci] = n;
@@ -627,10 +648,13 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     if ((rc = LaunchColumnSum(g + e->Offbc(), e->logits, false, Cp, n, C, e->col_scratch, st))) return rc;
     if ((rc = LaunchColumnSum(e->tail, e->loss, false, 1, n, 1, e->col_scratch, st))) return rc;
   }
-  const bool fuse_bias = CellBwdFusesBias(H);
+  // With token inputs (TokGrad) the leaf level has no backward cell launch of its own: its gate gradients are
+  // formed inside the per-token sums below, and the bias gradient is the column sum of those sums' partials.
+  const bool tok_grad = e->TokGrad();
+  const bool fuse_bias = !tok_grad && CellBwdFusesBias(H);
   const size_t dB_rows = static_cast<size_t>(CellBwdMaxGrid());
   if (fuse_bias) CAVS_CUDA(cudaMemsetAsync(e->dB_tmp, 0, dB_rows * 4 * H * sizeof(float), st));
-  for (int l = bt.n_levels - 1; l >= 0; --l) {
+  for (int l = bt.n_levels - 1; l >= (tok_grad ? 1 : 0); --l) {
     const int off = bt.level_off[l], rows = bt.level_off[l + 1] - off;
     // read d(h) (H; or the dz row with the fused head), mailbox (2H), gates, own c (H) [+ child c (KH)];
     // write dA (4H) [+ ZF (KH), child dc (KH)]
@@ -687,9 +711,25 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
     if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, Xop, ldx, true, e->dA, 4 * H, false, E, 4 * H, n, true, st))) return rc;
   } else {
-    PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
-         LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
-                               bt.seg_first_chunk, n_tok, e->emb_scratch, st, bt.chunk_out, bt.multi_seg, bt.n_multi));
+    if (tok_grad) {
+      const int n_leaf = bt.n_levels > 0 ? bt.level_off[1] : 0;
+      const bool fdh = e->FusedDh();
+      // leaves: mailbox (2H) + d(logits) row (or d(h)) in; internal rows: dA (4H) in; per chunk 4H fp32 out;
+      // per token 4H out
+      const double bytes = static_cast<double>(n_leaf) * (4.0 * 2 * H + (fdh ? 4.0 * kHeadDzPitch : 4.0 * H) + 4) +
+                           static_cast<double>(n - n_leaf) * (4 + 4.0 * H * elt) + static_cast<double>(bt.n_chunks) * 16.0 * H +
+                           static_cast<double>(n_tok) * 4 * H * elt;
+      PROF(e, kProfEmbedBwd, bytes, st,
+           LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
+                                 bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
+                                 fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), bt.parent, n_leaf, H, st));
+      if ((rc = LaunchSegmentedRowSumFinal(e->dAtok, e->bf16, e->emb_scratch, bt.seg_first_chunk, bt.multi_seg, bt.n_multi, 4 * H, st)))
+        return rc;
+    } else {
+      PROF(e, kProfEmbedBwd, static_cast<double>(n) * (4 + 4.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt, st,
+           LaunchSegmentedRowSum(e->dAtok, e->bf16, e->dA, e->bf16, 4 * H, 4 * H, bt.order, bt.chunk_off, bt.n_chunks,
+                                 bt.seg_first_chunk, n_tok, e->emb_scratch, st, bt.chunk_out, bt.multi_seg, bt.n_multi));
+    }
     if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
     CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
     if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
@@ -710,7 +750,10 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     CAVS_CUDA(cudaMemsetAsync(dU, 0, static_cast<size_t>(4) * H * H * sizeof(float), st));
   }
   // Bias gradient: column sums of dA, gate order i,o,u,f -> bias order i,f,u,o.
-  if (fuse_bias) {
+  if (tok_grad) {
+    PROF(e, kProfColumnSum, static_cast<double>(bt.n_chunks) * 4 * H * 4, st,
+         LaunchColumnSum(g + e->OffB(), e->emb_scratch, false, 4 * H, bt.n_chunks, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
+  } else if (fuse_bias) {
     PROF(e, kProfColumnSum, static_cast<double>(dB_rows) * 4 * H * 4, st,
          LaunchColumnSum(g + e->OffB(), e->dB_tmp, false, 4 * H, static_cast<int>(dB_rows), 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
   } else {

@@ -408,6 +408,130 @@ ScatterChildGrad(float* __restrict__ mailbox, const float* __restrict__ ds, cons
   }
 }
 
+// Per-token sums of the gate gradients dA (the first pass of the segmented sums, one CTA per chunk of at most
+// kEmbedChunk rows of one token) with the leaf level's backward cell folded in.  Rows are sorted by token and, within
+// a token, by tensor id, and a chunk never mixes leaves and internal vertices:
+//   * a chunk of internal vertices sums their stored dA rows (accumulator u takes rows u, u+4, ... in order);
+//   * a chunk of leaves never had its dA rows stored: each thread owns four hidden units, rebuilds the token's
+//     i, o, u gates and cell state from its input-projection row once, then for every leaf of the chunk reads the
+//     parent's d(h|c) from the mailbox and d(logits) (or the stored d(h)), forms zi, zo, zu exactly as CellBwd
+//     does, and accumulates them in row order.  The forget-gate block of a leaf is zero.
+// Every chunk writes its fp32 sums to partial[chunk, 4H] (their column sums are the bias gradient); a chunk that is
+// its token's only one also writes the final row out[token, 4H].
+struct LeafGradArgs {
+  const float* mailbox;      // [n_total, 2H]
+  const float* dOut;         // [n_total, H] or NULL when dz is given
+  const float* dz;           // [n_total, kHeadDzPitch] or NULL
+  const float* Wc;           // [C, H]
+  const float* bias;         // [4H] i,f,u,o
+  const int32_t* parent;     // [n_total]
+  const int32_t* chunk_seg;  // [n_chunks] token row of A for each chunk
+  int C, n_leaf, H;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* __restrict__ chunk_out, const T* __restrict__ dA,
+                const T* __restrict__ A, const int32_t* __restrict__ order, const int32_t* __restrict__ chunk_off, LeafGradArgs lg) {
+  __shared__ int32_t rows_sm[kEmbedChunk];
+  constexpr int V = 4;
+  constexpr bool kFast = sizeof(T) == 2;
+  const int chunk = blockIdx.x, H = lg.H, width = 4 * H;
+  const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
+  const int direct = chunk_out[chunk];
+  for (int r = threadIdx.x; r < cnt; r += kThreads) rows_sm[r] = order[begin + r];
+  __syncthreads();
+  float* mine = partial + static_cast<size_t>(chunk) * width;
+  T* final_row = direct >= 0 ? out + static_cast<size_t>(direct) * width : nullptr;
+  if (rows_sm[0] >= lg.n_leaf) {
+    // internal vertices: sum the stored rows
+    for (int e = threadIdx.x * V; e < width; e += kThreads * V) {
+      Vec<V> acc[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = Zero<V>();
+      int r = 0;
+      for (; r + 8 <= cnt; r += 8) {
+        Vec<V> t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = LoadF<V>(dA + static_cast<size_t>(rows_sm[r + u]) * width + e);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[u].v[v] += t[u].v[v];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[u].v[v] += t[u + 4].v[v];
+      }
+      for (int u = 0; r < cnt; ++r, u = (u + 1) & 3) {
+        const Vec<V> t = LoadF<V>(dA + static_cast<size_t>(rows_sm[r]) * width + e);
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[u].v[v] += t.v[v];
+      }
+      Vec<V> sum;
+#pragma unroll
+      for (int v = 0; v < V; ++v) sum.v[v] = (acc[0].v[v] + acc[1].v[v]) + (acc[2].v[v] + acc[3].v[v]);
+      Store<V>(mine + e, sum);
+      if (final_row) Store<V>(final_row + e, sum);
+    }
+    return;
+  }
+  // leaves of one token
+  const T* a = A + static_cast<size_t>(lg.chunk_seg[chunk]) * width;
+  for (int j = threadIdx.x * V; j < H; j += kThreads * V) {
+    const Vec<V> ai = LoadF<V>(a + j), ao = LoadF<V>(a + H + j), au = LoadF<V>(a + 2 * H + j);
+    const Vec<V> bi = LoadF<V>(lg.bias + j), bu = LoadF<V>(lg.bias + 2 * H + j), bo = LoadF<V>(lg.bias + 3 * H + j);
+    Vec<V> gi, go, gu, th;
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      gi.v[e] = SigmoidT<kFast>((ai.v[e] + 0.0f) + bi.v[e]);
+      go.v[e] = SigmoidT<kFast>((ao.v[e] + 0.0f) + bo.v[e]);
+      gu.v[e] = TanhT<kFast>((au.v[e] + 0.0f) + bu.v[e]);
+      th.v[e] = TanhT<kFast>(gi.v[e] * gu.v[e]);
+    }
+    Vec<V> wc[kHeadDzPitch];
+    if (lg.dz != nullptr) {
+#pragma unroll
+      for (int c = 0; c < kHeadDzPitch; ++c) wc[c] = c < lg.C ? LoadF<V>(lg.Wc + static_cast<size_t>(c) * H + j) : Zero<V>();
+    }
+    Vec<V> si = Zero<V>(), so = Zero<V>(), su = Zero<V>();
+    for (int r = 0; r < cnt; ++r) {
+      const size_t t = static_cast<size_t>(rows_sm[r]);
+      const bool has_parent = __ldg(lg.parent + t) >= 0;
+      const Vec<V> mh = has_parent ? LoadF<V>(lg.mailbox + t * 2 * H + j) : Zero<V>();
+      const Vec<V> mc = has_parent ? LoadF<V>(lg.mailbox + t * 2 * H + H + j) : Zero<V>();
+      Vec<V> dOutv;
+      if (lg.dz != nullptr) {
+        const float4 d0 = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch));
+        const float4 d1 = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch) + 1);
+        const float dzr[kHeadDzPitch] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+        dOutv = Zero<V>();
+#pragma unroll
+        for (int c = 0; c < kHeadDzPitch; ++c)
+#pragma unroll
+          for (int e = 0; e < V; ++e) dOutv.v[e] = fmaf(dzr[c], wc[c].v[e], dOutv.v[e]);
+      } else {
+        dOutv = LoadF<V>(lg.dOut + t * H + j);
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float dh = dOutv.v[e] + mh.v[e];
+        const float d_o = dh * th.v[e];
+        const float dc = mc.v[e] + (dh * go.v[e]) * (1.0f - th.v[e] * th.v[e]);
+        si.v[e] += (dc * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
+        so.v[e] += d_o * go.v[e] * (1.0f - go.v[e]);
+        su.v[e] += (dc * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
+      }
+    }
+    const Vec<V> zero = Zero<V>();
+    Store<V>(mine + j, si); Store<V>(mine + H + j, so); Store<V>(mine + 2 * H + j, su); Store<V>(mine + 3 * H + j, zero);
+    if (final_row) {
+      Store<V>(final_row + j, si); Store<V>(final_row + H + j, so); Store<V>(final_row + 2 * H + j, su);
+      Store<V>(final_row + 3 * H + j, zero);
+    }
+  }
+}
+
 int VecWidth(int H) { return H % 4 == 0 ? 4 : (H % 2 == 0 ? 2 : 1); }
 
 
@@ -516,6 +640,28 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
   });
 #undef CELL_BWD
   CAVS_LAUNCH_CHECK("treelstm_cell_bwd");
+  return CAVS_OK;
+}
+
+int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
+                          const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
+                          const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
+                          const int32_t* parent, int n_leaf, int H, cudaStream_t st) {
+  CAVS_REQUIRE(n_chunks >= 0 && H > 0 && H % 4 == 0, CAVS_ERR_BAD_ARG, "token_grad_chunks: hidden must be a positive multiple of 4");
+  if (n_chunks == 0) return CAVS_OK;
+  CAVS_REQUIRE(partial && out && chunk_out && dA && A && order && chunk_off && chunk_seg && mailbox && bias && parent &&
+                   (dz ? (Wc && C >= 1 && C <= kHeadDzPitch) : dOut != nullptr),
+               CAVS_ERR_BAD_ARG, "token_grad_chunks: null pointer");
+  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, parent, chunk_seg, C, n_leaf, H};
+  if (bf16) {
+    using bf = __nv_bfloat16;
+    TokenGradChunks<bf><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<bf*>(out), chunk_out, static_cast<const bf*>(dA),
+                                                       static_cast<const bf*>(A), order, chunk_off, lg);
+  } else {
+    TokenGradChunks<float><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<float*>(out), chunk_out, static_cast<const float*>(dA),
+                                                          static_cast<const float*>(A), order, chunk_off, lg);
+  }
+  CAVS_LAUNCH_CHECK("token_grad_chunks");
   return CAVS_OK;
 }
 

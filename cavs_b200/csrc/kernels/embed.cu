@@ -366,6 +366,19 @@ int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16,
   return CAVS_OK;
 }
 
+int LaunchSegmentedRowSumFinal(void* out, bool out_bf16, const float* partial, const int32_t* seg_first_chunk,
+                               const int32_t* multi_seg, int n_multi, int width, cudaStream_t st) {
+  CAVS_REQUIRE(n_multi >= 0 && width > 0 && width % 4 == 0, CAVS_ERR_BAD_ARG, "segmented_row_sum_final: width must be a positive multiple of 4");
+  if (n_multi == 0) return CAVS_OK;
+  CAVS_REQUIRE(out && partial && seg_first_chunk && multi_seg, CAVS_ERR_BAD_ARG, "segmented_row_sum_final: null pointer");
+  using bf = __nv_bfloat16;
+  const dim3 grid(n_multi, (width + 127) / 128);
+  if (out_bf16) SegSumFinalMulti<bf><<<grid, kThreads, 0, st>>>(static_cast<bf*>(out), partial, seg_first_chunk, multi_seg, width);
+  else SegSumFinalMulti<float><<<grid, kThreads, 0, st>>>(static_cast<float*>(out), partial, seg_first_chunk, multi_seg, width);
+  CAVS_LAUNCH_CHECK("segmented_row_sum_final");
+  return CAVS_OK;
+}
+
 int LaunchEmbedFwd(void* out, bool bf16, const float* table, const int32_t* tok, int rows, int E, int vocab, cudaStream_t st) {
   CAVS_REQUIRE(rows >= 0 && E > 0 && vocab > 0, CAVS_ERR_BAD_ARG, "embed_fwd: bad shape");
   if (rows == 0) return CAVS_OK;
