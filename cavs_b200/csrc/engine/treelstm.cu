@@ -722,7 +722,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
       PROF(e, kProfEmbedBwd, bytes, st,
            LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
                                  bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
-                                 fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), bt.parent, n_leaf, H, st));
+                                 fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), n_leaf, H, st));
       if ((rc = LaunchSegmentedRowSumFinal(e->dAtok, e->bf16, e->emb_scratch, bt.seg_first_chunk, bt.multi_seg, bt.n_multi, 4 * H, st)))
         return rc;
     } else {

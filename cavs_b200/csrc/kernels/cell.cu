@@ -424,7 +424,6 @@ struct LeafGradArgs {
   const float* dz;           // [n_total, kHeadDzPitch] or NULL
   const float* Wc;           // [C, H]
   const float* bias;         // [4H] i,f,u,o
-  const int32_t* parent;     // [n_total]
   const int32_t* chunk_seg;  // [n_chunks] token row of A for each chunk
   int C, n_leaf, H;
 };
@@ -495,32 +494,46 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
       for (int c = 0; c < kHeadDzPitch; ++c) wc[c] = c < lg.C ? LoadF<V>(lg.Wc + static_cast<size_t>(c) * H + j) : Zero<V>();
     }
     Vec<V> si = Zero<V>(), so = Zero<V>(), su = Zero<V>();
-    for (int r = 0; r < cnt; ++r) {
-      const size_t t = static_cast<size_t>(rows_sm[r]);
-      const bool has_parent = __ldg(lg.parent + t) >= 0;
-      const Vec<V> mh = has_parent ? LoadF<V>(lg.mailbox + t * 2 * H + j) : Zero<V>();
-      const Vec<V> mc = has_parent ? LoadF<V>(lg.mailbox + t * 2 * H + H + j) : Zero<V>();
-      Vec<V> dOutv;
-      if (lg.dz != nullptr) {
-        const float4 d0 = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch));
-        const float4 d1 = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch) + 1);
-        const float dzr[kHeadDzPitch] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
-        dOutv = Zero<V>();
+    // Rows in pairs: the loads of a pair are issued together (a chunk of a frequent token is a long
+    // serial loop otherwise), the accumulation stays in row order.
+    constexpr int kGroup = 2;
+    for (int r0 = 0; r0 < cnt; r0 += kGroup) {
+      Vec<V> mh[kGroup], mc[kGroup], dOutv[kGroup];
+      float4 d0[kGroup], d1[kGroup];
 #pragma unroll
-        for (int c = 0; c < kHeadDzPitch; ++c)
-#pragma unroll
-          for (int e = 0; e < V; ++e) dOutv.v[e] = fmaf(dzr[c], wc[c].v[e], dOutv.v[e]);
-      } else {
-        dOutv = LoadF<V>(lg.dOut + t * H + j);
+      for (int u = 0; u < kGroup; ++u) {
+        // A scheduled leaf always has a parent (a single-vertex sample is never scheduled), so its mailbox row is
+        // valid and the loads do not wait for a parent lookup.
+        const size_t t = static_cast<size_t>(rows_sm[r0 + u < cnt ? r0 + u : r0]);
+        mh[u] = LoadF<V>(lg.mailbox + t * 2 * H + j);
+        mc[u] = LoadF<V>(lg.mailbox + t * 2 * H + H + j);
+        if (lg.dz != nullptr) {
+          d0[u] = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch));
+          d1[u] = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch) + 1);
+        } else {
+          dOutv[u] = LoadF<V>(lg.dOut + t * H + j);
+        }
       }
 #pragma unroll
-      for (int e = 0; e < V; ++e) {
-        const float dh = dOutv.v[e] + mh.v[e];
-        const float d_o = dh * th.v[e];
-        const float dc = mc.v[e] + (dh * go.v[e]) * (1.0f - th.v[e] * th.v[e]);
-        si.v[e] += (dc * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
-        so.v[e] += d_o * go.v[e] * (1.0f - go.v[e]);
-        su.v[e] += (dc * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
+      for (int u = 0; u < kGroup; ++u) {
+        if (r0 + u >= cnt) break;
+        if (lg.dz != nullptr) {
+          const float dzr[kHeadDzPitch] = {d0[u].x, d0[u].y, d0[u].z, d0[u].w, d1[u].x, d1[u].y, d1[u].z, d1[u].w};
+          dOutv[u] = Zero<V>();
+#pragma unroll
+          for (int c = 0; c < kHeadDzPitch; ++c)
+#pragma unroll
+            for (int e = 0; e < V; ++e) dOutv[u].v[e] = fmaf(dzr[c], wc[c].v[e], dOutv[u].v[e]);
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float dh = dOutv[u].v[e] + mh[u].v[e];
+          const float d_o = dh * th.v[e];
+          const float dc = mc[u].v[e] + (dh * go.v[e]) * (1.0f - th.v[e] * th.v[e]);
+          si.v[e] += (dc * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
+          so.v[e] += d_o * go.v[e] * (1.0f - go.v[e]);
+          su.v[e] += (dc * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
+        }
       }
     }
     const Vec<V> zero = Zero<V>();
@@ -646,13 +659,13 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
-                          const int32_t* parent, int n_leaf, int H, cudaStream_t st) {
+                          int n_leaf, int H, cudaStream_t st) {
   CAVS_REQUIRE(n_chunks >= 0 && H > 0 && H % 4 == 0, CAVS_ERR_BAD_ARG, "token_grad_chunks: hidden must be a positive multiple of 4");
   if (n_chunks == 0) return CAVS_OK;
-  CAVS_REQUIRE(partial && out && chunk_out && dA && A && order && chunk_off && chunk_seg && mailbox && bias && parent &&
+  CAVS_REQUIRE(partial && out && chunk_out && dA && A && order && chunk_off && chunk_seg && mailbox && bias &&
                    (dz ? (Wc && C >= 1 && C <= kHeadDzPitch) : dOut != nullptr),
                CAVS_ERR_BAD_ARG, "token_grad_chunks: null pointer");
-  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, parent, chunk_seg, C, n_leaf, H};
+  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H};
   if (bf16) {
     using bf = __nv_bfloat16;
     TokenGradChunks<bf><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<bf*>(out), chunk_out, static_cast<const bf*>(dA),

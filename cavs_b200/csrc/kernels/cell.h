@@ -43,13 +43,13 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 // (dz: [n_total, kHeadDzPitch] rows from LaunchLossHead's dz_out; Wc: [C, H], C <= 8); dOut may then be NULL.
 // First pass of the per-token sums of dA with the leaf level's backward cell folded in (kernels/cell.cu,
 // TokenGradChunks): chunk_out / chunk_seg [n_chunks] give a single-chunk token's output row (else -1) and every
-// chunk's token row; leaves are the rows below n_leaf and are recomputed from A, bias, the mailbox and dz (or
-// dOut); internal rows are read from dA.  partial: [n_chunks, 4H] fp32, always written; out: [tokens, 4H].
+// chunk's token row; leaves are the rows below n_leaf (every scheduled leaf has a parent, so its mailbox row is
+// valid) and are recomputed from A, bias, the mailbox and dz (or dOut); internal rows are read from dA.  partial: [n_chunks, 4H] fp32, always written; out: [tokens, 4H].
 // The second pass over multi-chunk tokens is LaunchSegmentedRowSumFinal.
 int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
-                          const int32_t* parent, int n_leaf, int H, cudaStream_t st);
+                          int n_leaf, int H, cudaStream_t st);
 int LaunchSegmentedRowSumFinal(void* out, bool out_bf16, const float* partial, const int32_t* seg_first_chunk,
                                const int32_t* multi_seg, int n_multi, int width, cudaStream_t st);
 int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,
