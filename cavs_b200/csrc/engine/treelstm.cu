@@ -95,6 +95,7 @@ struct cavs_treelstm {
     int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
             *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr, *chunk_seg = nullptr;
     int n_multi = 0;
+    int shared_chunk = -1;   // chunk whose partial row is the column sum over the internal vertices, or -1
   };
   Batch slot[2];
   int active = -1, staged = -1;
@@ -446,6 +447,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     // Dense inputs: one projection row per vertex, no token grouping.
     bt.chunk_off = bt.seg_first_chunk = bt.seg_tok = bt.chunk_out = bt.multi_seg = nullptr;
     bt.n_multi = 0;
+    bt.shared_chunk = -1;
     bt.tok_slot = nullptr;
     n_seg = n;
     CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
@@ -454,14 +456,28 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     // token the rows are in tensor-id order, so its leaves (level 0) come first; leaves and internal vertices get
     // separate chunks.
     const int n_leaf = sch.n_levels() > 0 ? bt.level_off[1] : 0;
+    // When every internal vertex carries the same token (the reference's zero-filled inputs: only leaves have
+    // words) and the backward cell keeps per-CTA column sums, the sum of dA over the internal vertices is exactly
+    // those column sums: the internal rows are left out of the lists below, and the token gets one extra, empty
+    // chunk whose partial row backward fills from the column sums.
+    int shared_tok = -1;
+    if (e->TokGrad() && CellBwdFusesBias(e->cfg.hidden) && n > n_leaf) {
+      shared_tok = h_tok[n_leaf];
+      for (int t = n_leaf + 1; t < n && shared_tok >= 0; ++t)
+        if (h_tok[t] != shared_tok) shared_tok = -1;
+    }
+    const int n_listed = shared_tok >= 0 ? n_leaf : n;   // rows that appear in `order`
     e->bucket.assign(static_cast<size_t>(V) + 1, 0);
     e->leaf_count.assign(static_cast<size_t>(V), 0);
-    for (int t = 0; t < n; ++t) ++e->bucket[h_tok[t] + 1];
+    for (int t = 0; t < n_listed; ++t) ++e->bucket[h_tok[t] + 1];
     for (int t = 0; t < n_leaf; ++t) ++e->leaf_count[h_tok[t]];
     auto chunks_of = [](int rows) { return (rows + kEmbedChunk - 1) / kEmbedChunk; };
     for (int v = 0; v < V; ++v) {
       const int cnt = e->bucket[v + 1];
-      if (cnt) { ++n_seg; n_chunks += chunks_of(e->leaf_count[v]) + chunks_of(cnt - e->leaf_count[v]); }
+      if (cnt || v == shared_tok) {
+        ++n_seg;
+        n_chunks += chunks_of(e->leaf_count[v]) + chunks_of(cnt - e->leaf_count[v]) + (v == shared_tok ? 1 : 0);
+      }
       e->bucket[v + 1] += e->bucket[v];
     }
     int32_t* h_chunk_off = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_off);
@@ -469,19 +485,20 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     int32_t* h_seg_tok = view(n_seg, &bt.seg_tok);
     int32_t* h_chunk_out = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_out);
     int32_t* h_chunk_seg = view(static_cast<size_t>(n_chunks) + 1, &bt.chunk_seg);
-    int32_t* h_multi = view(static_cast<size_t>(n_chunks) + 1, &bt.multi_seg);   // each listed segment has >= 2 chunks
+    int32_t* h_multi = view(static_cast<size_t>(n_chunks) + 1, &bt.multi_seg);   // segments folded by the second pass
     CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
     int si = 0, ci = 0, n_multi = 0;
+    bt.shared_chunk = -1;
     e->slot_of_token.resize(V);
     for (int v = 0; v < V; ++v) {
       const int b0 = e->bucket[v], b1 = e->bucket[v + 1];
-      if (b0 == b1) continue;
+      if (b0 == b1 && v != shared_tok) continue;
       e->slot_of_token[v] = si;
       h_seg_tok[si] = v;
       h_seg_first[si] = ci;
       const int mid = b0 + e->leaf_count[v];                    // leaves [b0, mid), internal vertices [mid, b1)
       // a token whose rows form one chunk gets its sum written by the first pass of the segmented sums
-      const bool single = chunks_of(mid - b0) + chunks_of(b1 - mid) == 1;
+      const bool single = v != shared_tok && chunks_of(mid - b0) + chunks_of(b1 - mid) == 1;
       if (!single) h_multi[n_multi++] = si;
       for (int part = 0; part < 2; ++part)
         for (int b = part ? mid : b0; b < (part ? b1 : mid); b += kEmbedChunk) {
@@ -489,13 +506,19 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
           h_chunk_seg[ci] = si;
           h_chunk_off[ci++] = b;
         }
+      if (v == shared_tok) {   // the empty chunk that receives the internal vertices' column sums
+        bt.shared_chunk = ci;
+        h_chunk_out[ci] = -1;
+        h_chunk_seg[ci] = si;
+        h_chunk_off[ci++] = b1;
+      }
       ++si;
     }
     h_seg_first[si] = ci;
-    h_chunk_off[ci] = n;
+    h_chunk_off[ci] = n_listed;
     bt.n_multi = n_multi;
     for (int t = 0; t < n; ++t) {
-      h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
+      if (t < n_listed) h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
       h_slot[t] = e->slot_of_token[h_tok[t]];
     }
   }
@@ -651,7 +674,9 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   // With token inputs (TokGrad) the leaf level has no backward cell launch of its own: its gate gradients are
   // formed inside the per-token sums below, and the bias gradient is the column sum of those sums' partials.
   const bool tok_grad = e->TokGrad();
-  const bool fuse_bias = !tok_grad && CellBwdFusesBias(H);
+  // The backward cell keeps per-CTA column sums of dA either for the bias gradient (no token sums) or, when all
+  // internal vertices share one token, as that token's sum over the internal vertices.
+  const bool fuse_bias = tok_grad ? bt.shared_chunk >= 0 : CellBwdFusesBias(H);
   const size_t dB_rows = static_cast<size_t>(CellBwdMaxGrid());
   if (fuse_bias) CAVS_CUDA(cudaMemsetAsync(e->dB_tmp, 0, dB_rows * 4 * H * sizeof(float), st));
   for (int l = bt.n_levels - 1; l >= (tok_grad ? 1 : 0); --l) {
@@ -723,6 +748,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
            LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
                                  bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
                                  fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), n_leaf, H, st));
+      if (bt.shared_chunk >= 0) {
+        // the internal vertices' column sums become the partial row of their token's extra chunk
+        if ((rc = LaunchColumnSum(e->emb_scratch + static_cast<size_t>(bt.shared_chunk) * 4 * H, e->dB_tmp, false, 4 * H,
+                                  static_cast<int>(dB_rows), 4 * H, e->col_scratch, st)))
+          return rc;
+      }
       if ((rc = LaunchSegmentedRowSumFinal(e->dAtok, e->bf16, e->emb_scratch, bt.seg_first_chunk, bt.multi_seg, bt.n_multi, 4 * H, st)))
         return rc;
     } else {
@@ -753,7 +784,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   if (tok_grad) {
     PROF(e, kProfColumnSum, static_cast<double>(bt.n_chunks) * 4 * H * 4, st,
          LaunchColumnSum(g + e->OffB(), e->emb_scratch, false, 4 * H, bt.n_chunks, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
-  } else if (fuse_bias) {
+  } else if (fuse_bias) {   // no token sums: the column sums are the bias gradient
     PROF(e, kProfColumnSum, static_cast<double>(dB_rows) * 4 * H * 4, st,
          LaunchColumnSum(g + e->OffB(), e->dB_tmp, false, 4 * H, static_cast<int>(dB_rows), 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
   } else {

@@ -438,6 +438,7 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
   const int chunk = blockIdx.x, H = lg.H, width = 4 * H;
   const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
   const int direct = chunk_out[chunk];
+  if (cnt == 0) return;   // an empty chunk's partial row is filled by the caller (column sums kept by the backward cell)
   for (int r = threadIdx.x; r < cnt; r += kThreads) rows_sm[r] = order[begin + r];
   __syncthreads();
   float* mine = partial + static_cast<size_t>(chunk) * width;

@@ -74,6 +74,10 @@ int EncodeTcOutput(TcOperandMap* out, void* base, long long m, long long n, long
 int GemmBf16Mapped(const GemmBf16MappedArgs& args, cudaStream_t stream);
 size_t GemmBf16ScratchBytes(int m, int n, int splits);
 int GemmBf16SplitsFor(int m, int n, int k);
+int GemmBf16SplitsForTile(int m, int n, int k, int tile_m);   // the same choice for tiles of tile_m rows
+// Long-K products of two MN-major operands (weight gradients) into fp32 run 256 x 256 tiles when split-K scratch
+// is available: a third fewer operand bytes per flop out of L2.
+bool GemmBf16UsesTallTiles(int m, int n, int k, int a_major, int b_major, int out_mode);
 
 // fp32 GEMM on the CUDA cores with arbitrary element strides:
 // C[i,j] (+)= sum_p A[i*a_rs + p*a_cs] * B[p*b_rs + j*b_cs].

@@ -81,10 +81,10 @@ __global__ void __launch_bounds__(256) SplitKReduce(float* __restrict__ c, long 
   }
 }
 
-template <int kBN, int kAMajor, int kBMajor>
+template <int kBN, int kAMajor, int kBMajor, int kMB = 1>
 int Launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const tc::Params& p, dim3 grid, cudaStream_t stream) {
-  using S = tc::Smem<kBN>;
-  auto kern = tc::GemmBf16Kernel<kBN, kAMajor, kBMajor>;
+  using S = tc::Smem<kBN, kMB>;
+  auto kern = tc::GemmBf16Kernel<kBN, kAMajor, kBMajor, kMB>;
   static bool configured = false;   // per instantiation
   if (!configured) {
     CAVS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
@@ -119,13 +119,23 @@ int GemmBf16TileNFor(int m, int n, int k) {
   return (n > 64 && nkb <= 64 && tiles64 <= SmCount()) ? 64 : base;   // one wave of 64-column tiles
 }
 
+// 256 x 256 tiles: long-K products with both operands MN-major (the weight gradients X^T dY) and an fp32 output.
+bool GemmBf16UsesTallTiles(int m, int n, int k, int a_major, int b_major, int out_mode) {
+  return a_major == tc::kMajorMN && b_major == tc::kMajorMN && out_mode != tc::kStoreBf16 && out_mode != tc::kScatterF32 &&
+         m >= 256 && n > 128 && k >= 64 * tc::kBK;
+}
+
 int GemmBf16SplitsFor(int m, int n, int k) {
+  return GemmBf16SplitsForTile(m, n, k, tc::kBM);
+}
+
+int GemmBf16SplitsForTile(int m, int n, int k, int tile_m) {
   // The kernel is persistent over (tile, split) work items.  Splitting K costs partial traffic, a
   // plain-store epilogue and a reduce pass, so it is used only when the tile grid leaves more than a
   // quarter of the SMs idle; then the smallest split count that fills whole waves to >= 90 % wins,
   // keeping each split >= 32 K blocks.
   const int bn = GemmBf16TileN(n);
-  const long long tiles = static_cast<long long>((m + tc::kBM - 1) / tc::kBM) * ((n + bn - 1) / bn);
+  const long long tiles = static_cast<long long>((m + tile_m - 1) / tile_m) * ((n + bn - 1) / bn);
   const int nkb = (k + tc::kBK - 1) / tc::kBK;
   const int sms = SmCount();
   auto fill = [&](long long items) { return static_cast<double>(items) / (((items + sms - 1) / sms) * sms); };
@@ -176,7 +186,7 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
                CAVS_ERR_BAD_ARG,
                "gemm_bf16: scatter output needs the child table, 16-byte aligned addend / output rows (n, pitches multiples of 4) and no K split");
   CAVS_REQUIRE(g.a_row_off == 0 || g.a->major == tc::kMajorK, CAVS_ERR_BAD_ARG, "gemm_bf16: row offsets need a K-major A");
-  const int splits = std::max(1, g.splits);
+  int splits = std::max(1, g.splits);
   int bn = GemmBf16TileN(g.n);
   const TcOperandMap* bmap = g.b;
   if (splits == 1 && GemmBf16TileNFor(g.m, g.n, g.k) == 64) {
@@ -184,6 +194,15 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
     else if (g.b->tile_rows == 64) bn = 64;
     else if (g.b_small != nullptr && g.b_small->major == tc::kMajorK && g.b_small->tile_rows == 64) { bn = 64; bmap = g.b_small; }
   }
+  // Long-K weight gradients with split-K scratch available run 256 x 256 tiles; the split count is then chosen for
+  // that tile grid.
+  const bool tall = bn == 256 && g.scratch != nullptr && splits > 1 &&
+                    GemmBf16UsesTallTiles(g.m, g.n, g.k, g.a->major, bmap->major, g.out_mode);
+  if (tall) {
+    splits = GemmBf16SplitsForTile(g.m, g.n, g.k, 2 * tc::kBM);
+    while (splits > 1 && g.scratch_bytes < GemmBf16ScratchBytes(g.m, g.n, splits)) --splits;
+  }
+  const int tile_m = tall ? 2 * tc::kBM : tc::kBM;
   CAVS_REQUIRE(g.a->major != tc::kMajorK || g.a->tile_rows == tc::kBM, CAVS_ERR_BAD_ARG, "gemm_bf16: A map was not encoded for 128-row tiles");
   CAVS_REQUIRE(bmap->major != tc::kMajorK || bmap->tile_rows == bn, CAVS_ERR_BAD_ARG, "gemm_bf16: B map was encoded for a different N tile");
   CAVS_REQUIRE(splits == 1 || g.out_mode != tc::kStoreBf16, CAVS_ERR_BAD_ARG, "gemm_bf16: split-K needs an fp32 output");
@@ -223,9 +242,10 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
     }
     p.tma_store = 1;
   }
-  const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tc::kBM - 1) / tc::kBM) * eff_splits;
+  const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tile_m - 1) / tile_m) * eff_splits;
   dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
-  int rc = bn == 256   ? Dispatch<256>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
+  int rc = tall        ? Launch<256, 1, 1, 2>(ma, mb, *mc, p, grid, stream)
+           : bn == 256 ? Dispatch<256>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
            : bn == 128 ? Dispatch<128>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
                        : Dispatch<64>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream);
   if (rc) return rc;

@@ -58,12 +58,16 @@ struct Params {
   int* status;        // device word, set non-zero when a bounded wait expires
 };
 
-template <int kBN>
+// kMB: 128-row blocks of C per tile.  kMB = 2 (256 x 256 tiles, long-K weight gradients only): the operand bytes a
+// CTA pulls out of L2 per flop drop by a third, which is what bounds those GEMMs; the two accumulators fill all
+// 512 TMEM columns, so the epilogue is not overlapped with the next tile's MMAs (irrelevant at thousands of
+// k-blocks per tile).
+template <int kBN, int kMB = 1>
 struct Smem {
-  static constexpr int kATile = kBM * kBK * 2;
+  static constexpr int kATile = kMB * kBM * kBK * 2;
   static constexpr int kBTile = kBN * kBK * 2;
   static constexpr int kStage = kATile + kBTile;
-  static constexpr int kStages = (kBN == 256) ? 4 : (kBN == 128 ? 6 : 7);
+  static constexpr int kStages = kMB == 2 ? 3 : ((kBN == 256) ? 4 : (kBN == 128 ? 6 : 7));
   // Epilogue staging: 4 warps x 2 slots x (32 rows x 128 bytes), 128-byte swizzled for the TMA store.
   static constexpr int kCSlot = 32 * 128;
   static constexpr int kCOff = kStages * kStage;
@@ -295,11 +299,13 @@ __device__ __forceinline__ void ScatterRows(const Params& p, uint32_t slot, int 
 // work item -> (tile, K-split) with the N tile index fastest, so the CTAs of one wave share A
 // row blocks through L2.  Two TMEM accumulators alternate between tiles: while the epilogue
 // warps drain one, the MMA warp already fills the other, and the TMA ring never drains.
-template <int kBN, int kAMajor, int kBMajor>
+template <int kBN, int kAMajor, int kBMajor, int kMB = 1>
 __global__ void __launch_bounds__(kThreads, 1)
 GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const Params p) {
-  using S = Smem<kBN>;
+  using S = Smem<kBN, kMB>;
+  static_assert(kMB == 1 || (kMB == 2 && kBN == 256), "two row blocks need both 256-column accumulators");
+  constexpr int kTileM = kBM * kMB;
   ChainRelease(p.chain_early);
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tiles.
@@ -314,7 +320,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles_n = (p.n + kBN - 1) / kBN;
-  const int n_tiles_m = (p.m + kBM - 1) / kBM;
+  const int n_tiles_m = (p.m + kTileM - 1) / kTileM;
   const int nkb_total = (p.k + kBK - 1) / kBK;
   const int n_work = n_tiles_m * n_tiles_n * p.n_splits;
 
@@ -347,7 +353,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       uint32_t it = 0;   // ring position, continuous across work items
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         const int z = w % p.n_splits, tile = w / p.n_splits;
-        const int m0 = (tile / n_tiles_n) * kBM, n0 = (tile % n_tiles_n) * kBN;
+        const int m0 = (tile / n_tiles_n) * kTileM, n0 = (tile % n_tiles_n) * kBN;
         const int kb_begin = z * p.kb_per_split;
         const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
         for (int i = 0; i < kb_count; ++i, ++it) {
@@ -361,10 +367,12 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint32_t b_dst = a_dst + S::kATile;
           const int k0 = (kb_begin + i) * kBK;
           if (kAMajor == kMajorK) {
-            TmaLoad2d(a_dst, &map_a, bar, k0, m0 + p.a_row_off);                      // box {64 k, 128 rows}
+#pragma unroll
+            for (int mb = 0; mb < kMB; ++mb)                                          // box {64 k, 128 rows}
+              TmaLoad2d(a_dst + mb * (kBM * kBK * 2), &map_a, bar, k0, m0 + kBM * mb + p.a_row_off);
           } else {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j, k0);  // box {64 mn, 64 k}
+            for (int j = 0; j < kTileM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j, k0);  // box {64 mn, 64 k}
           }
           if (kBMajor == kMajorK) {
             TmaLoad2d(b_dst, &map_b, bar, k0, n0);                                    // box {64 k, kBN rows}
@@ -386,7 +394,8 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int z = w % p.n_splits;
         const int kb_begin = z * p.kb_per_split;
         const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
-        const uint32_t acc = t_local & 1, acc_phase = (t_local >> 1) & 1;
+        // kMB = 1: two accumulators alternate between tiles; kMB = 2: one accumulator pair, reused by every tile
+        const uint32_t acc = kMB == 2 ? 0 : (t_local & 1), acc_phase = kMB == 2 ? (t_local & 1) : ((t_local >> 1) & 1);
         ok = MbarWait(SmemAddr(acc_empty + acc), acc_phase ^ 1);   // epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -402,7 +411,10 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const uint64_t b_desc = SmemDesc(a_addr + S::kATile, kBMajor);
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk)
-            UmmaBf16(d_tmem, a_desc + kk * a_step, b_desc + kk * b_step, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+            for (int mb = 0; mb < kMB; ++mb)   // row block mb: its A half starts 16 KB further, its accumulator kBN columns further
+              UmmaBf16(d_tmem + mb * kBN, a_desc + mb * ((kBM * kBK * 2) >> 4) + kk * a_step, b_desc + kk * b_step, idesc,
+                       (i > 0 || kk > 0) ? 1u : 0u);
           UmmaCommit(SmemAddr(empty_bar + s));   // frees the stage once these MMAs have read it
         }
         if (ok) UmmaCommit(SmemAddr(acc_full + acc));   // accumulator complete
@@ -416,16 +428,19 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t n_stores = 0;   // bulk stores issued by this warp; picks the staging slot (alternating)
     for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++t_local) {
       const int z = w % p.n_splits, tile = w / p.n_splits;
-      const int m0 = (tile / n_tiles_n) * kBM, n0 = (tile % n_tiles_n) * kBN;
-      const uint32_t acc = t_local & 1, acc_phase = (t_local >> 1) & 1;
+      const int m0_tile = (tile / n_tiles_n) * kTileM, n0 = (tile % n_tiles_n) * kBN;
+      const uint32_t acc = kMB == 2 ? 0 : (t_local & 1), acc_phase = kMB == 2 ? (t_local & 1) : ((t_local >> 1) & 1);
       int sc_dst[8], sc_add[8];
-      if (p.out_mode == kScatterF32) ScatterTargets(p, lane, m0 + quarter * 32, sc_dst, sc_add);   // before the wait
+      if (p.out_mode == kScatterF32) ScatterTargets(p, lane, m0_tile + quarter * 32, sc_dst, sc_add);   // before the wait (kMB = 1 only)
       ok = MbarWait(SmemAddr(acc_full + acc), acc_phase);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = m0 + quarter * 32 + lane;
       const long long zoff = static_cast<long long>(z) * p.split_stride;
-      const uint32_t t_addr = tmem_base + acc * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int mb = 0; mb < kMB; ++mb) {
+      const int m0 = m0_tile + mb * kBM;
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + (acc + mb) * kBN + (static_cast<uint32_t>(quarter * 32) << 16);
       if (p.tma_store) {
         // Registers -> swizzled shared staging -> TMA store: every global write is a full 128-byte
         // row segment, and the tensor map clips the M / N tails.  Two slots per warp alternate on
@@ -511,6 +526,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           StoreChunk<32>(p, r, row, n0 + c0 + 32, zoff);
         }
       }
+      }   // row blocks
       // All of this warp's TMEM reads are complete (wait::ld above): hand the accumulator back.
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();

@@ -76,6 +76,13 @@ def test_bf16_split_k_weight_gradient_shape(cuda, splits):
     assert torch.equal(C, C2), "split-K reduction must be bit-reproducible"
 
 
+@pytest.mark.parametrize("m,n,k,out_mode", [(1000, 600, 9000, 0), (512, 3072, 20000, 0), (304, 256, 4500, 1)])
+def test_bf16_tall_tile_weight_gradients(cuda, m, n, k, out_mode):
+    # long-K X^T dY with split-K scratch: the 256 x 256 tile path, with ragged M and N edges and with accumulation
+    C, ref = _run_bf16(cuda, m, n, k, 1, 1, splits=4, out_mode=out_mode)
+    _check(C, ref, 2e-5, f"tall tiles {m}x{n}x{k} mode {out_mode}")
+
+
 def test_bf16_rejects_misaligned_pitch(cuda):
     from cavs_b200 import CavsError
     with pytest.raises(CavsError):
