@@ -114,7 +114,7 @@ class ClockSampler:
         return out
 
 
-GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.957e9 / 31744
+GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.734e9 / 31744
 
 
 def measured_peaks():
@@ -362,7 +362,7 @@ def main():
     d = classes[dominant]
     if dominant == "gate_gemm":
         # DRAM bytes per GEMM launch: captured with ncu on one rank's shard at 8 GPUs (all 81 GEMM launches of a step:
-        # 1.957 GB for 31,744 internal vertices, profiles/gemm_dram_traffic_shard_512_trees.md) and scaled by internal
+        # 1.734 GB for 31,744 internal vertices, profiles/gemm_dram_traffic_shard_512_trees.md) and scaled by internal
         # vertices, to which every per-level operand and output is proportional.
         internal_rows = int(scheds[0].n_total - scheds[0].level_off[1]) if scheds[0].n_levels > 1 else 0
         traffic = GEMM_DRAM_BYTES_PER_INTERNAL_ROW * internal_rows / max(d["launches_per_step"], 1)
