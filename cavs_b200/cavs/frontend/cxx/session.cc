@@ -348,6 +348,8 @@ void Session::Run(std::vector<Sym> outputs, const std::initializer_list<std::pai
     if (name == r.loss) {
       // per-vertex loss, permuted from execution order back to job order (FunctionPopRet)
       const void* dev = nullptr; size_t bytes = 0;
+      // leaves may share loss-head rows per token: have the per-vertex values written out first
+      Must(cavs_treelstm_materialize_state(m.engine, nullptr), "cavs_treelstm_materialize_state");
       Must(cavs_treelstm_peek(m.engine, 1, &dev, &bytes), "cavs_treelstm_peek");
       std::vector<float> tid(n_sched);
       MustCuda(cudaMemcpy(tid.data(), dev, n_sched * sizeof(float), cudaMemcpyDeviceToHost), "fetch loss");
@@ -362,6 +364,8 @@ void Session::Run(std::vector<Sym> outputs, const std::initializer_list<std::pai
       std::memcpy(raw->data(), &v, sizeof(float));
     } else if (name == r.graph_output) {
       const void* dev = nullptr; size_t bytes = 0;
+      // leaves may share state rows per token: have the per-vertex rows written out first
+      Must(cavs_treelstm_materialize_state(m.engine, nullptr), "cavs_treelstm_materialize_state");
       Must(cavs_treelstm_peek(m.engine, 0, &dev, &bytes), "cavs_treelstm_peek");
       std::vector<float> state(static_cast<size_t>(n_sched) * 2 * r.H);
       MustCuda(cudaMemcpy(state.data(), dev, state.size() * sizeof(float), cudaMemcpyDeviceToHost), "fetch graph output");

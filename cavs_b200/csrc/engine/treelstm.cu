@@ -74,6 +74,10 @@ struct cavs_treelstm {
   // Token inputs with hidden a multiple of 4: the leaf level's backward cell is folded into the per-token sums of dA
   // (the leaves' dA rows are never stored) and the bias gradient is the column sum of the chunk partials.
   bool TokGrad() const { return cfg.vocab > 0 && cfg.hidden % 4 == 0; }
+  // With per-token leaf states, a fused loss head and token gradient sums, the loss head also runs once per distinct
+  // leaf token instead of once per leaf (weighted by the token's label histogram).
+  bool TokHead() const { return leaf_tok && FusedDh() && TokGrad(); }
+  float* ptok = nullptr;        // [tokens, 8] class probabilities of the leaf tokens (TokHead)
   bool Dense() const { return cfg.vocab == 0; }
   bool Headless() const { return cfg.classes == 0; }
   int Cp() const { return (cfg.classes + 7) & ~7; }
@@ -92,6 +96,7 @@ struct cavs_treelstm {
     int n = 0, n_total = 0, n_levels = 0, loss_rows = 0, n_chunks = 0, n_seg = 0;
     std::vector<int32_t> level_off;
     int32_t *child_st = nullptr, *state_row = nullptr;   // leaf_tok: state rows of the children / of every vertex
+    int32_t *tok_hist = nullptr, *head_row = nullptr;    // TokHead: label histogram per token; state rows of the loss rows
     int32_t *child = nullptr, *parent = nullptr, *tok = nullptr, *label = nullptr, *order = nullptr, *chunk_off = nullptr,
             *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr, *chunk_seg = nullptr;
     int n_multi = 0;
@@ -184,7 +189,7 @@ size_t MaxSegments(const cavs_treelstm_config& c) { return c.vocab == 0 ? c.max_
 size_t MaxChunks(const cavs_treelstm_config& c) { return 2 * MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
-  return (2 * c.n_slots + 6) * n + 4 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + MaxSegments(c) + 64;
+  return (2 * c.n_slots + 7) * n + 4 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + 10 * MaxSegments(c) + 64;
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -231,6 +236,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   // d(pushed h): materialised only by the wide loss head; the fused head hands d(logits) rows (dz8) to the cell gradient
   e->dOut = w.Take<float>(e->FusedDh() || e->Headless() ? 0 : N * H);
   e->dz8 = w.Take<float>(e->FusedDh() ? N * kHeadDzPitch : 0);
+  e->ptok = w.Take<float>(e->TokHead() ? T * kHeadDzPitch : 0);
   e->ds = w.Take<float>(L * H);
   e->dq = w.Take<float>(c.gemm_bf16 ? 0 : L * K * H);   // bf16 mode: the dq product is scattered by its own epilogue
   e->dX = w.Take<float>(T * E);
@@ -532,6 +538,20 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
       h_child_st[i] = ch >= 0 ? h_state_row[ch] : ch;
     }
   }
+  if (e->TokHead()) {
+    // Loss rows: the internal vertices in tensor-id order, then one row per distinct token standing for its leaves.
+    const int n_leaf = sch.n_levels() > 0 ? bt.level_off[1] : 0;
+    int32_t* h_hist = view(static_cast<size_t>(n_seg) * kHeadDzPitch, &bt.tok_hist);
+    int32_t* h_head_row = view(static_cast<size_t>(n - n_leaf) + n_seg, &bt.head_row);
+    CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
+    std::memset(h_hist, 0, sizeof(int32_t) * n_seg * kHeadDzPitch);
+    for (int t = 0; t < n_leaf; ++t) {
+      const int y = h_label[t];
+      if (y >= 0 && y < e->cfg.classes) ++h_hist[static_cast<size_t>(h_slot[t]) * kHeadDzPitch + y];
+    }
+    for (int t = n_leaf; t < n; ++t) h_head_row[t - n_leaf] = t;
+    for (int sidx = 0; sidx < n_seg; ++sidx) h_head_row[n - n_leaf + sidx] = e->cfg.max_vertices + sidx;
+  }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
   // The device half is free once the last backward pass that read it has finished.
   (void)stream;
@@ -645,10 +665,23 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     // Fused loss head over the pushed rows (h part of the state), in tensor-id order: read h (H), label,
     // write loss and the d(logits) row; d(h) = dz Wc is rebuilt inside the cell gradient, never stored.
     const bool fdh = e->FusedDh();
+    if (e->TokHead()) {
+      // internal vertices one by one, leaves once per distinct token
+      const int n_leaf = bt.n_levels > 0 ? bt.level_off[1] : 0;
+      const int rows_v = n - n_leaf, rows = rows_v + bt.n_seg;
+      LossTokenRows tr;
+      tr.hist = bt.tok_hist; tr.ptok = e->ptok; tr.rows_v = rows_v;
+      PROF(e, kProfLossHead, static_cast<double>(rows) * (4.0 * H + 8 + 4.0 * kHeadDzPitch), st,
+           LaunchLossHead(e->loss + n_leaf, e->tail, nullptr, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label + n_leaf,
+                          e->params + e->OffWc(), e->params + e->Offbc(), rows, H, C, 1.0f / static_cast<float>(bt.loss_rows),
+                          e->loss_scratch, st, false, e->dz8 + static_cast<size_t>(n_leaf) * kHeadDzPitch, e->Status(),
+                          bt.head_row, tr));
+    } else {
     PROF(e, kProfLossHead, static_cast<double>(n) * (4.0 * H + 8 + (fdh ? 4.0 * kHeadDzPitch : 4.0 * H)), st,
          LaunchLossHead(e->loss, e->tail, fdh ? nullptr : e->dOut, g + e->OffWc(), g + e->Offbc(), e->state, 2 * H, bt.label,
                         e->params + e->OffWc(), e->params + e->Offbc(), n, H, C, 1.0f / static_cast<float>(bt.loss_rows),
                         e->loss_scratch, st, false, fdh ? e->dz8 : nullptr, e->Status(), e->leaf_tok ? bt.state_row : nullptr));
+    }
   } else {
     // Wide head (vocabulary-sized class count): logits = h Wc^T, row softmax cross-entropy, then
     // dH = dz Wc, dWc = dz^T h, dbc = column sums of dz -- FullyConnected + SoftmaxEntropyLoss and their
@@ -747,7 +780,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
       PROF(e, kProfEmbedBwd, bytes, st,
            LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
                                  bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
-                                 fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), n_leaf, H, st));
+                                 fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), n_leaf, H, st,
+                                 e->TokHead() ? e->ptok : nullptr, bt.label, 1.0f / static_cast<float>(bt.loss_rows)));
       if (bt.shared_chunk >= 0) {
         // the internal vertices' column sums become the partial row of their token's extra chunk
         if ((rc = LaunchColumnSum(e->emb_scratch + static_cast<size_t>(bt.shared_chunk) * 4 * H, e->dB_tmp, false, 4 * H,
@@ -819,7 +853,11 @@ extern "C" int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream) {
   const cavs_treelstm::Batch& bt = e->slot[e->active];
   const int n_leaf = bt.n_levels > 0 ? bt.level_off[1] : 0;
   // leaf vertex t <- its token's row: rows [0, n_leaf) of state_row are exactly those source rows
-  return cavs_gather_rows(e->state, e->state, bt.state_row, n_leaf, static_cast<size_t>(2) * e->cfg.hidden * sizeof(float), stream);
+  if (int rc = cavs_gather_rows(e->state, e->state, bt.state_row, n_leaf, static_cast<size_t>(2) * e->cfg.hidden * sizeof(float), stream))
+    return rc;
+  // and the leaves' loss values, which the loss head's token rows do not write (valid after backward)
+  if (e->TokHead()) return LaunchLeafLossFill(e->loss, e->ptok, bt.tok_slot, bt.label, n_leaf, e->cfg.classes, static_cast<cudaStream_t>(stream));
+  return CAVS_OK;
 }
 
 extern "C" int cavs_treelstm_wait_embed_grad(cavs_treelstm* e, void* stream) {

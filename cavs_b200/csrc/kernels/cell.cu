@@ -426,9 +426,14 @@ struct LeafGradArgs {
   const float* bias;         // [4H] i,f,u,o
   const int32_t* chunk_seg;  // [n_chunks] token row of A for each chunk
   int C, n_leaf, H;
+  const float* ptok;         // [tokens, kHeadDzPitch] class probabilities per token, or NULL (then dz / dOut)
+  const int32_t* label;      // [n_total]
+  float inv_rows;
 };
 
-template <typename T>
+// kMode: where a leaf's d(h) comes from -- 0 stored d(h) rows, 1 stored d(logits) rows, 2 the token's class
+// probabilities and the leaf's label (one instantiation each, so no path carries the other paths' registers).
+template <typename T, int kMode>
 __global__ void __launch_bounds__(kThreads)
 TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* __restrict__ chunk_out, const T* __restrict__ dA,
                 const T* __restrict__ A, const int32_t* __restrict__ order, const int32_t* __restrict__ chunk_off, LeafGradArgs lg) {
@@ -489,10 +494,27 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
       gu.v[e] = TanhT<kFast>((au.v[e] + 0.0f) + bu.v[e]);
       th.v[e] = TanhT<kFast>(gi.v[e] * gu.v[e]);
     }
+    constexpr bool by_token = kMode == 2;   // d(logits) of a leaf = (p[token] - onehot(label)) * inv_rows
+    constexpr bool by_dz = kMode == 1;
+    float ptk[kHeadDzPitch];
+    if (by_token) {
+      const float4 p0 = __ldg(reinterpret_cast<const float4*>(lg.ptok + static_cast<size_t>(lg.chunk_seg[chunk]) * kHeadDzPitch));
+      const float4 p1 = __ldg(reinterpret_cast<const float4*>(lg.ptok + static_cast<size_t>(lg.chunk_seg[chunk]) * kHeadDzPitch) + 1);
+      ptk[0] = p0.x; ptk[1] = p0.y; ptk[2] = p0.z; ptk[3] = p0.w; ptk[4] = p1.x; ptk[5] = p1.y; ptk[6] = p1.z; ptk[7] = p1.w;
+    }
     Vec<V> wc[kHeadDzPitch];
-    if (lg.dz != nullptr) {
+    if (by_dz || by_token) {
 #pragma unroll
       for (int c = 0; c < kHeadDzPitch; ++c) wc[c] = c < lg.C ? LoadF<V>(lg.Wc + static_cast<size_t>(c) * H + j) : Zero<V>();
+    }
+    // by_token: d(h) of a leaf = d(logits) . Wc = ((sum_c p[c] Wc[c]) - Wc[label]) * inv_rows; the first term is the
+    // same for every leaf of the token.
+    Vec<V> pw = Zero<V>();
+    if (by_token) {
+#pragma unroll
+      for (int c = 0; c < kHeadDzPitch; ++c)
+#pragma unroll
+        for (int e = 0; e < V; ++e) pw.v[e] = fmaf(ptk[c], wc[c].v[e], pw.v[e]);
     }
     Vec<V> si = Zero<V>(), so = Zero<V>(), su = Zero<V>();
     // Rows in pairs: the loads of a pair are issued together (a chunk of a frequent token is a long
@@ -501,6 +523,7 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
     for (int r0 = 0; r0 < cnt; r0 += kGroup) {
       Vec<V> mh[kGroup], mc[kGroup], dOutv[kGroup];
       float4 d0[kGroup], d1[kGroup];
+      int yl[kGroup];
 #pragma unroll
       for (int u = 0; u < kGroup; ++u) {
         // A scheduled leaf always has a parent (a single-vertex sample is never scheduled), so its mailbox row is
@@ -508,7 +531,9 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
         const size_t t = static_cast<size_t>(rows_sm[r0 + u < cnt ? r0 + u : r0]);
         mh[u] = LoadF<V>(lg.mailbox + t * 2 * H + j);
         mc[u] = LoadF<V>(lg.mailbox + t * 2 * H + H + j);
-        if (lg.dz != nullptr) {
+        if (by_token) {
+          yl[u] = __ldg(lg.label + t);
+        } else if (by_dz) {
           d0[u] = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch));
           d1[u] = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch) + 1);
         } else {
@@ -518,7 +543,17 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
 #pragma unroll
       for (int u = 0; u < kGroup; ++u) {
         if (r0 + u >= cnt) break;
-        if (lg.dz != nullptr) {
+        if (by_token) {
+          const int y = yl[u];
+          const bool labelled = y >= 0 && y < lg.C;   // labels outside [0, C) carry no loss, as in the token histogram
+          Vec<V> sel = Zero<V>();
+#pragma unroll
+          for (int c = 0; c < kHeadDzPitch; ++c)
+#pragma unroll
+            for (int e = 0; e < V; ++e) sel.v[e] += (c == y) ? wc[c].v[e] : 0.0f;
+#pragma unroll
+          for (int e = 0; e < V; ++e) dOutv[u].v[e] = labelled ? (pw.v[e] - sel.v[e]) * lg.inv_rows : 0.0f;
+        } else if (by_dz) {
           const float dzr[kHeadDzPitch] = {d0[u].x, d0[u].y, d0[u].z, d0[u].w, d1[u].x, d1[u].y, d1[u].z, d1[u].w};
           dOutv[u] = Zero<V>();
 #pragma unroll
@@ -660,21 +695,23 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
-                          int n_leaf, int H, cudaStream_t st) {
+                          int n_leaf, int H, cudaStream_t st, const float* ptok, const int32_t* label, float inv_rows) {
   CAVS_REQUIRE(n_chunks >= 0 && H > 0 && H % 4 == 0, CAVS_ERR_BAD_ARG, "token_grad_chunks: hidden must be a positive multiple of 4");
   if (n_chunks == 0) return CAVS_OK;
   CAVS_REQUIRE(partial && out && chunk_out && dA && A && order && chunk_off && chunk_seg && mailbox && bias &&
-                   (dz ? (Wc && C >= 1 && C <= kHeadDzPitch) : dOut != nullptr),
+                   ((dz || ptok) ? (Wc && C >= 1 && C <= kHeadDzPitch && (!ptok || label)) : dOut != nullptr),
                CAVS_ERR_BAD_ARG, "token_grad_chunks: null pointer");
-  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H};
+  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H, ptok, label, inv_rows};
+#define TOKEN_GRAD(TT, MODE)                                                                                              \
+  TokenGradChunks<TT, MODE><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<TT*>(out), chunk_out, static_cast<const TT*>(dA), \
+                                                           static_cast<const TT*>(A), order, chunk_off, lg)
+  const int mode = ptok ? 2 : (dz ? 1 : 0);
   if (bf16) {
-    using bf = __nv_bfloat16;
-    TokenGradChunks<bf><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<bf*>(out), chunk_out, static_cast<const bf*>(dA),
-                                                       static_cast<const bf*>(A), order, chunk_off, lg);
+    if (mode == 2) TOKEN_GRAD(__nv_bfloat16, 2); else if (mode == 1) TOKEN_GRAD(__nv_bfloat16, 1); else TOKEN_GRAD(__nv_bfloat16, 0);
   } else {
-    TokenGradChunks<float><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<float*>(out), chunk_out, static_cast<const float*>(dA),
-                                                          static_cast<const float*>(A), order, chunk_off, lg);
+    if (mode == 2) TOKEN_GRAD(float, 2); else if (mode == 1) TOKEN_GRAD(float, 1); else TOKEN_GRAD(float, 0);
   }
+#undef TOKEN_GRAD
   CAVS_LAUNCH_CHECK("token_grad_chunks");
   return CAVS_OK;
 }

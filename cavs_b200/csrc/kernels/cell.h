@@ -49,7 +49,13 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
-                          int n_leaf, int H, cudaStream_t st);
+                          int n_leaf, int H, cudaStream_t st, const float* ptok = nullptr, const int32_t* label = nullptr,
+                          float inv_rows = 0.0f);
+// ptok / label / inv_rows (optional, instead of dz): a leaf's d(logits) is (ptok[token] - onehot(label)) * inv_rows.
+// loss[t] = -log ptok[tok_slot[t]][label[t]] for the leaves t < n_leaf (0 without a label): fills in what the loss
+// head's token rows do not write.
+int LaunchLeafLossFill(float* loss, const float* ptok, const int32_t* tok_slot, const int32_t* label, int n_leaf, int C,
+                       cudaStream_t st);
 int LaunchSegmentedRowSumFinal(void* out, bool out_bf16, const float* partial, const int32_t* seg_first_chunk,
                                const int32_t* multi_seg, int n_multi, int width, cudaStream_t st);
 int LaunchScatterChildGrad(float* mailbox, const float* ds, const float* dq, const int32_t* child, int n_total, int off,
@@ -81,10 +87,20 @@ int LaunchSegmentedRowSum(void* out, bool out_bf16, const void* x, bool in_bf16,
 // Writes loss[t], dOut[t,:] = dz Wc; per-CTA partials of dWc / dbc / loss sum go to scratch and are
 // reduced in fixed order.  inv_rows scales dz (the reference divides by the logits' row count).
 size_t LossHeadScratchBytes(int H, int C);
+// Token rows of the loss head (streaming form): loss rows at and above rows_v each stand for all leaves that carry one
+// token (they share a hidden row).  hist [tokens, 8] (int32): how many of the token's leaves have each label; ptok
+// [tokens, 8] receives the token's class probabilities, from which each leaf's own d(logits) and loss follow.  No
+// loss / dz row is written for a token row; its d(logits) = (count * p - hist) / rows feeds dWc, dbc and the loss sum.
+struct LossTokenRows {
+  const int32_t* hist = nullptr;
+  float* ptok = nullptr;
+  int rows_v = 0;
+};
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
                    float* scratch, cudaStream_t st, bool accumulate = false,    // accumulate: add into dWc / dbc / loss_sum
-                   float* dz_out = nullptr, int* status = nullptr, const int32_t* row_index = nullptr);
+                   float* dz_out = nullptr, int* status = nullptr, const int32_t* row_index = nullptr,
+                   LossTokenRows token_rows = LossTokenRows());
 // row_index (optional, [rows]): loss row t reads its hidden row at h[row_index[t]] (streaming form only).
 bool LossHeadStreams(const float* h, long long h_pitch, int H);   // would this shape take the streaming form?
 // status (optional, device): raised to 1 if a bounded wait on an asynchronous row copy expires.

@@ -245,7 +245,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __restrict__ dz_out, float* __restrict__ partial,
                const float* __restrict__ h, long long h_pitch, const int32_t* __restrict__ label,
                const float* __restrict__ Wc, const float* __restrict__ bc, int rows, int H, float inv_rows,
-               int* __restrict__ status, const int32_t* __restrict__ row_index) {
+               int* __restrict__ status, const int32_t* __restrict__ row_index, LossTokenRows tr) {
   extern __shared__ __align__(16) float sm[];
   float* stage = sm;                                                  // [kStreamStages][kStreamRows][H]
   float* red = sm + kStreamStages * kStreamRows * H;                  // [2][kWarps][kStreamRows][C], by batch parity
@@ -353,25 +353,54 @@ LossHeadStream(float* __restrict__ loss, float* __restrict__ dOut, float* __rest
       float den = 0.0f;
 #pragma unroll
       for (int c = 0; c < C; ++c) { z[c] = expf(z[c] - mx); den += z[c]; }
-      const int y = rr < cnt ? label[t] : -1;
       const float inv_den = 1.0f / den;
+      const bool token_row = tr.hist != nullptr && t >= tr.rows_v;
+      if (!token_row) {
+        const int y = rr < cnt ? label[t] : -1;
 #pragma unroll
-      for (int c = 0; c < C; ++c) {
-        const float pc = z[c] * inv_den;
-        dz[c] = (y >= 0) ? (pc - (c == y ? 1.0f : 0.0f)) * inv_rows : 0.0f;
-        if (c == y) lrow = -logf(pc);
+        for (int c = 0; c < C; ++c) {
+          const float pc = z[c] * inv_den;
+          dz[c] = (y >= 0) ? (pc - (c == y ? 1.0f : 0.0f)) * inv_rows : 0.0f;
+          if (c == y) lrow = -logf(pc);
+          z[c] = pc;
+        }
+      } else {
+        // A token row stands for all leaves that carry the token (they share the hidden row): hist[c] of them have
+        // label c, so d(logits) = (count * p - hist) / rows and the loss is -sum_c hist[c] log p[c].
+        float hist[C], count = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          hist[c] = rr < cnt ? static_cast<float>(tr.hist[static_cast<long long>(t - tr.rows_v) * kMaxC + c]) : 0.0f;
+          count += hist[c];
+        }
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          const float pc = z[c] * inv_den;
+          dz[c] = (count * pc - hist[c]) * inv_rows;
+          if (hist[c] > 0.0f) lrow -= hist[c] * logf(pc);
+          z[c] = pc;
+        }
       }
-    }
-    if (tid < kStreamRows && tid < cnt) {   // warp 0, one lane per row, publishes the row's results
-      loss[t] = lrow;
-      loss_acc += lrow;
-      if (dz_out != nullptr) {
+      if (tid < kStreamRows && tid < cnt) {   // warp 0, one lane per row, publishes the row's results
+        loss_acc += lrow;
         float pad[kMaxC];
+        if (!token_row) {
+          loss[t] = lrow;
+          if (dz_out != nullptr) {
 #pragma unroll
-        for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? dz[c < C ? c : 0] : 0.0f;
-        float4* dst = reinterpret_cast<float4*>(dz_out + static_cast<long long>(t) * kMaxC);
-        dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
-        dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
+            for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? dz[c < C ? c : 0] : 0.0f;
+            float4* dst = reinterpret_cast<float4*>(dz_out + static_cast<long long>(t) * kMaxC);
+            dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
+            dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
+          }
+        } else {
+          // the token's class probabilities: each of its leaves derives its own d(logits) and loss from them
+#pragma unroll
+          for (int c = 0; c < kMaxC; ++c) pad[c] = c < C ? z[c < C ? c : 0] : 0.0f;
+          float4* dst = reinterpret_cast<float4*>(tr.ptok + static_cast<long long>(t - tr.rows_v) * kMaxC);
+          dst[0] = make_float4(pad[0], pad[1], pad[2], pad[3]);
+          dst[1] = make_float4(pad[4], pad[5], pad[6], pad[7]);
+        }
       }
     }
 #pragma unroll
@@ -448,6 +477,26 @@ int LossGrid(int rows) {
 
 }  // namespace
 
+namespace {
+__global__ void __launch_bounds__(kThreads)
+LeafLossFill(float* __restrict__ loss, const float* __restrict__ ptok, const int32_t* __restrict__ tok_slot,
+             const int32_t* __restrict__ label, int n_leaf, int C) {
+  for (int t = blockIdx.x * kThreads + threadIdx.x; t < n_leaf; t += gridDim.x * kThreads) {
+    const int y = label[t];
+    loss[t] = (y >= 0 && y < C) ? -logf(ptok[static_cast<size_t>(tok_slot[t]) * kMaxC + y]) : 0.0f;
+  }
+}
+}  // namespace
+
+int LaunchLeafLossFill(float* loss, const float* ptok, const int32_t* tok_slot, const int32_t* label, int n_leaf, int C,
+                       cudaStream_t st) {
+  if (n_leaf <= 0) return CAVS_OK;
+  CAVS_REQUIRE(loss && ptok && tok_slot && label, CAVS_ERR_BAD_ARG, "leaf_loss_fill: null pointer");
+  LeafLossFill<<<GridForElems(static_cast<size_t>(n_leaf), kThreads), kThreads, 0, st>>>(loss, ptok, tok_slot, label, n_leaf, C);
+  CAVS_LAUNCH_CHECK("leaf_loss_fill");
+  return CAVS_OK;
+}
+
 bool LossHeadStreams(const float* h, long long h_pitch, int H) {
   return H % 4 == 0 && H <= kThreads * 4 && h_pitch % 4 == 0 && (reinterpret_cast<uintptr_t>(h) & 15u) == 0;
 }
@@ -458,7 +507,8 @@ size_t LossHeadScratchBytes(int H, int C) {
 
 int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float* dbc, const float* h, long long h_pitch,
                    const int32_t* label, const float* Wc, const float* bc, int rows, int H, int C, float inv_rows,
-                   float* scratch, cudaStream_t st, bool accumulate, float* dz_out, int* status, const int32_t* row_index) {
+                   float* scratch, cudaStream_t st, bool accumulate, float* dz_out, int* status, const int32_t* row_index,
+                   LossTokenRows token_rows) {
   CAVS_REQUIRE(rows >= 0 && H > 0 && C > 0, CAVS_ERR_BAD_ARG, "loss_head: bad shape");
   CAVS_REQUIRE(C <= kMaxC, CAVS_ERR_UNSUPPORTED, "loss_head: fused path supports at most 8 classes");
   CAVS_REQUIRE(H <= kThreads * kMaxColsPerThread, CAVS_ERR_UNSUPPORTED, "loss_head: hidden size above 2048");
@@ -468,6 +518,8 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   const bool stream_ok = H % 4 == 0 && H <= kThreads * 4 && h_pitch % 4 == 0 &&
                          ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(dOut) | reinterpret_cast<uintptr_t>(scratch) |
                            reinterpret_cast<uintptr_t>(Wc)) & 15u) == 0;
+  CAVS_REQUIRE(token_rows.hist == nullptr || (stream_ok && token_rows.ptok != nullptr && row_index != nullptr), CAVS_ERR_UNSUPPORTED,
+               "loss_head: token rows need the streaming form, indexed hidden rows and a probability table");
   CAVS_REQUIRE(row_index == nullptr || stream_ok, CAVS_ERR_UNSUPPORTED,
                "loss_head: indexed hidden rows need the streaming form (hidden a multiple of 4, at most 1024, 16-byte aligned rows)");
   if (stream_ok && rows > 0) {
@@ -478,7 +530,7 @@ int LaunchLossHead(float* loss, float* loss_sum, float* dOut, float* dWc, float*
   case CC:                                                                                                           \
     if (ssmem > 48 * 1024)                                                                                           \
       CAVS_CUDA(cudaFuncSetAttribute(LossHeadStream<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ssmem));  \
-    LossHeadStream<CC><<<sgrid, kThreads, ssmem, st>>>(loss, dOut, dz_out, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows, status, row_index); \
+    LossHeadStream<CC><<<sgrid, kThreads, ssmem, st>>>(loss, dOut, dz_out, scratch, h, h_pitch, label, Wc, bc, rows, H, inv_rows, status, row_index, token_rows); \
     break;
     switch (C) {
       STREAM_CASE(1) STREAM_CASE(2) STREAM_CASE(3) STREAM_CASE(4) STREAM_CASE(5) STREAM_CASE(6) STREAM_CASE(7) STREAM_CASE(8)

@@ -142,6 +142,7 @@ class TreeLSTM:
         return self.peek(0, (self.n, 2 * self.cfg.hidden))
 
     def loss_rows(self) -> np.ndarray:
+        check(lib().cavs_treelstm_materialize_state(self._h, _stream()))   # leaf losses may live per token
         return self.peek(1, (self.n,))
 
     def grad_dict(self) -> dict:

@@ -275,8 +275,9 @@ CAVS_API int cavs_treelstm_set_dense_input(cavs_treelstm* e, const float* x, lon
 CAVS_API int cavs_treelstm_set_output_grad(cavs_treelstm* e, const float* dh);
 /* With an embedding table and a fused loss head the engine keeps ONE state row per distinct leaf token (a leaf's h|c
  * depends on nothing else) and reads leaf states through remapped row indices; the per-vertex rows of the leaves in
- * peek array 0 are then not written by forward.  This call fills them in (a row gather on `stream`), for callers
- * that want to look at every vertex's state.  A no-op for engines that keep per-vertex leaf rows (dense inputs, no
+ * peek array 0 are then not written by forward, and the leaves' entries of peek array 1 (per-vertex loss) not by
+ * backward (the loss head runs once per distinct leaf token).  This call fills both in on `stream`, for callers
+ * that want to look at every vertex's state or loss.  A no-op for engines that keep per-vertex leaf rows (dense inputs, no
  * loss head, more than 8 classes, hidden not a multiple of 4 or above 1024, or CAVS_LEAF_BY_TOKEN=0). */
 CAVS_API int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream);
 /* Makes `stream` wait until the embedding-gradient block (the first vocab*embed floats of the bound gradient
