@@ -415,7 +415,9 @@ def main():
     trees = wl["batch"]
     value = trees * args.steps / (ms_dev * 1e-3)
     e2e_value = trees * args.steps / (ms_e2e * 1e-3)
-    h2d = int((2 + 5) * max_n * 4)      # child x2, parent, tok, label, order (+ small segment tables)
+    # tables uploaded per step: child and child-state rows (2 slots each), parent, token, label, order, token row,
+    # state row, loss-head row (+ the per-token chunk / histogram tables, a few hundred KB)
+    h2d = int((2 * 2 + 7) * max_n * 4)
     line = dict(metric="treelstm_train_trees_per_sec", value=value, unit="trees/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                 ms_per_step=ms_dev / args.steps, higher_is_better=True, scaling="strong", vs_baseline=None,
                 dtype="bf16" if wl["bf16"] else "f32", data="synthetic",
