@@ -166,3 +166,31 @@ def test_training_reduces_the_loss(cuda, bf16):
         eng.adagrad(acc, 0.01)
     assert all(b < a for a, b in zip(losses[:5], losses[1:6])), losses
     assert losses[-1] < 0.97 * losses[0], losses
+
+
+@pytest.mark.parametrize("bf16,K,arity", [(False, 2, 2), (True, 4, 4)])
+def test_root_only_labels(cuda, bf16, K, arity):
+    """Only the root of every tree carries a label (the other vertices have -1, no loss term), the loss is normalised by
+    the number of trees: leaves contribute nothing to the loss head, their token rows must come out as zeros."""
+    from helpers import root_only_labels
+    H, E, V, C = (128, 64, 300, 5) if bf16 else (40, 24, 120, 3)
+    batch = 20
+    parents, tok_job, label_job = make_tree_batch(47, batch, 2, 16, V, C, max_arity=arity)
+    label_job = root_only_labels(parents, label_job)
+    params = make_params(6, H, E, V, C, scale=0.2 if not bf16 else 0.08, bias_scale=0.05)
+    s = S.Schedule().load(parents, n_slots=K)
+    eng = TreeLSTM(H, E, V, C, n_slots=K, gemm_bf16=bf16, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+    eng.set_params(params)
+    eng.load_batch(s, tok_job, label_job, loss_rows=batch)
+    eng.forward()
+    eng.backward()
+    loss_sum = eng.read_loss()
+    out = dict(state=eng.state(), loss=eng.loss_rows(), **eng.grad_dict())
+    tb = tables_from_schedule(s)
+    ref = oracle.treelstm_fwd_bwd(tb, tok_job[tb["t2j"]], label_job[tb["t2j"]], params, H, E, V, C, K=K, gemm_bf16=bf16,
+                                  preact_bf16=bf16, loss_rows=batch)
+    tol = 5e-3 if bf16 else 1e-5
+    for k in KEYS:
+        assert rel_err(out[k], ref[k]) < tol, k
+    assert abs(loss_sum - ref["loss"].sum()) <= tol * abs(ref["loss"].sum())
+    assert np.count_nonzero(out["loss"]) == batch
