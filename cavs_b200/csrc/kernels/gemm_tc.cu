@@ -196,12 +196,18 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   }
   // Long-K weight gradients with split-K scratch available run 256 x 256 tiles; the split count is then chosen for
   // that tile grid.
-  const bool tall = bn == 256 && g.scratch != nullptr && splits > 1 &&
-                    GemmBf16UsesTallTiles(g.m, g.n, g.k, g.a->major, bmap->major, g.out_mode);
-  if (tall) {
+  const bool tall_wgrad = bn == 256 && g.scratch != nullptr && splits > 1 &&
+                          GemmBf16UsesTallTiles(g.m, g.n, g.k, g.a->major, bmap->major, g.out_mode);
+  if (tall_wgrad) {
     splits = GemmBf16SplitsForTile(g.m, g.n, g.k, 2 * tc::kBM);
     while (splits > 1 && g.scratch_bytes < GemmBf16ScratchBytes(g.m, g.n, splits)) --splits;
   }
+  // The same tiles for the deep-K gradient products of large levels (dY W^T with both operands K-major, fp32 out):
+  // 32+ k-blocks per tile make the unhidden epilogue cheap, and there is at least one full wave of tiles.
+  const bool tall_dgrad = bn == 256 && splits == 1 && g.a->major == tc::kMajorK && bmap->major == tc::kMajorK &&
+                          g.out_mode == tc::kStoreF32 && g.k >= 32 * tc::kBK &&
+                          static_cast<long long>((g.m + 2 * tc::kBM - 1) / (2 * tc::kBM)) * ((g.n + bn - 1) / bn) >= SmCount();
+  const bool tall = tall_wgrad || tall_dgrad;
   const int tile_m = tall ? 2 * tc::kBM : tc::kBM;
   CAVS_REQUIRE(g.a->major != tc::kMajorK || g.a->tile_rows == tc::kBM, CAVS_ERR_BAD_ARG, "gemm_bf16: A map was not encoded for 128-row tiles");
   CAVS_REQUIRE(bmap->major != tc::kMajorK || bmap->tile_rows == bn, CAVS_ERR_BAD_ARG, "gemm_bf16: B map was encoded for a different N tile");
@@ -244,7 +250,8 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   }
   const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tile_m - 1) / tile_m) * eff_splits;
   dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
-  int rc = tall        ? Launch<256, 1, 1, 2>(ma, mb, *mc, p, grid, stream)
+  int rc = tall_wgrad  ? Launch<256, 1, 1, 2>(ma, mb, *mc, p, grid, stream)
+           : tall_dgrad ? Launch<256, 0, 0, 2>(ma, mb, *mc, p, grid, stream)
            : bn == 256 ? Dispatch<256>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
            : bn == 128 ? Dispatch<128>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
                        : Dispatch<64>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream);

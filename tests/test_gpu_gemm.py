@@ -83,6 +83,13 @@ def test_bf16_tall_tile_weight_gradients(cuda, m, n, k, out_mode):
     _check(C, ref, 2e-5, f"tall tiles {m}x{n}x{k} mode {out_mode}")
 
 
+def test_bf16_tall_tile_deep_k_gradient_product(cuda):
+    # dY W^T on a large level: both operands K-major, fp32 out through the TMA-store epilogue, 256 x 256 tiles
+    # (ragged last row block)
+    C, ref = _run_bf16(cuda, 38000, 1024, 3072, 0, 0)
+    _check(C, ref, 2e-5, "tall tiles, deep-K gradient product")
+
+
 def test_bf16_rejects_misaligned_pitch(cuda):
     from cavs_b200 import CavsError
     with pytest.raises(CavsError):
