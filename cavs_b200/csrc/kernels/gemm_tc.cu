@@ -204,8 +204,8 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   }
   // The same tiles for the deep-K gradient products of large levels (dY W^T with both operands K-major, fp32 out):
   // 32+ k-blocks per tile make the unhidden epilogue cheap, and there is at least one full wave of tiles.
-  const bool tall_dgrad = bn == 256 && splits == 1 && g.a->major == tc::kMajorK && bmap->major == tc::kMajorK &&
-                          g.out_mode == tc::kStoreF32 && g.k >= 32 * tc::kBK &&
+  const bool tall_dgrad = bn == 256 && splits == 1 && g.a->major == tc::kMajorK &&
+                          (g.out_mode == tc::kStoreF32 || g.out_mode == tc::kStoreBf16) && g.k >= 16 * tc::kBK &&
                           static_cast<long long>((g.m + 2 * tc::kBM - 1) / (2 * tc::kBM)) * ((g.n + bn - 1) / bn) >= SmCount();
   const bool tall = tall_wgrad || tall_dgrad;
   const int tile_m = tall ? 2 * tc::kBM : tc::kBM;
@@ -251,7 +251,8 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tile_m - 1) / tile_m) * eff_splits;
   dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
   int rc = tall_wgrad  ? Launch<256, 1, 1, 2>(ma, mb, *mc, p, grid, stream)
-           : tall_dgrad ? Launch<256, 0, 0, 2>(ma, mb, *mc, p, grid, stream)
+           : tall_dgrad ? (bmap->major == tc::kMajorK ? Launch<256, 0, 0, 2>(ma, mb, *mc, p, grid, stream)
+                                                      : Launch<256, 0, 1, 2>(ma, mb, *mc, p, grid, stream))
            : bn == 256 ? Dispatch<256>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
            : bn == 128 ? Dispatch<128>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream)
                        : Dispatch<64>(g.a->major, bmap->major, ma, mb, *mc, p, grid, stream);
