@@ -114,7 +114,7 @@ class ClockSampler:
         return out
 
 
-GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.734e9 / 31744
+GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.724e9 / 31744
 
 
 def measured_peaks():
