@@ -8,6 +8,10 @@
     python -m cavs_b200.cases shard   two training steps of the Tree-LSTM engine on one rank's shard of the
                                       benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB);
                                       `shard 50` also times 50 further steps with CUDA events
+    python -m cavs_b200.cases unbatched [steps]
+                                      what level batching buys: the binary Tree-LSTM configuration (64 trees of 2..50
+                                      leaves, hidden 150, embedding 300, fp32) stepped with the level schedule and with the
+                                      one-vertex-per-round schedule (the reference's serial scheduler), CUDA-event times
 """
 from __future__ import annotations
 
@@ -125,7 +129,40 @@ def shard(steps: int = 2) -> None:
         print("ms_per_step", a.elapsed_time(b) / steps)
 
 
+def unbatched(steps: int = 10) -> None:
+    import numpy as np
+    H, E, V, C, batch = 150, 300, 21701, 5, 64
+    parents, is_leaf = S.synth_trees(2, batch, 2, 50)
+    lens = (parents == -1).argmax(1) + 1
+    tok_pad = S.synth_zipf(3, 1.1, V, parents.size).reshape(parents.shape) * is_leaf
+    tok = np.concatenate([tok_pad[i, :lens[i]] for i in range(batch)]).astype(np.int32)
+    lab = S.synth_uniform_int(4, C, int(lens.sum()))
+    params = dict(Emb=S.synth_uniform_float(10, 0.05, (V, E)), W=S.synth_uniform_float(11, 0.05, (E * 4 * H,)),
+                  U=S.synth_uniform_float(12, 0.05, (4 * H * H,)), Wc=S.synth_uniform_float(13, 0.05, (C, H)),
+                  B=np.zeros(4 * H, np.float32), bc=np.zeros(C, np.float32))
+    for order, name in ((S.BATCHED, "level schedule"), (S.UNBATCHED, "one vertex per round")):
+        s = S.Schedule().set_order(order).load(parents)
+        eng = TreeLSTM(H, E, V, C, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+        eng.set_params(params)
+        eng.load_batch(s, tok, lab)
+        for _ in range(2):
+            eng.forward()
+            eng.backward()
+        loss_sum = eng.read_loss()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            eng.forward()
+            eng.backward()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        print(f"{name}: {s.n_levels} rounds, {s.n_total} vertices, loss {loss_sum:.4f}, {ms:.3f} ms per forward+backward, "
+              f"{batch / ms * 1e3:.0f} trees/s")
+
+
 if __name__ == "__main__":
-    fn = {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard}[sys.argv[1]]
+    fn = {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard, "unbatched": unbatched}[sys.argv[1]]
     fn(*(int(a) for a in sys.argv[2:3]))   # optional iteration / step count
     print("ok", sys.argv[1])

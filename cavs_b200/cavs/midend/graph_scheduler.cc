@@ -18,6 +18,11 @@ struct GraphSchedulerBase::Impl {
   int* dev = nullptr;
   bool dev_fresh = false;    // device copy matches `blob`
   size_t dev_cap = 0, off_fg = 0, off_fs = 0, off_roots = 0;
+  // One-vertex-per-round mode (tensor id == job id).  Blob: identity [N] | forward jobs | backward jobs |
+  // child 0 by job [N] | child 1 by job [N] | own id where the vertex has a parent, else -1 [N].
+  bool serial = false;
+  std::vector<int> sweep[2], sweep_init[2], parent_j, child_j[2];
+  size_t off_sweep[2] = {0, 0}, off_child[2] = {0, 0}, off_self = 0;
   // Uploads the blob on first use after a LoadGraph, so host-only users never touch CUDA.
   const int* Device() {
     if (!dev_fresh) {
@@ -93,6 +98,31 @@ int GraphSchedulerBase::LoadGraph(const Tensor& graph_struct) {
     lv.dev_s = blob.size();
     blob.insert(blob.end(), lv.s.begin(), lv.s.end());
   }
+  m.serial = OneVertexPerRound();
+  if (m.serial) {
+    const int cap = n > 0 ? n : 1;
+    m.parent_j.assign(cap, -1);
+    std::vector<int> child(2 * static_cast<size_t>(cap), -1);
+    if (n > 0) CHECK(cavs_sched_adjacency(m.sched, m.parent_j.data(), child.data(), cap) == CAVS_OK);
+    for (int c = 0; c < 2; c++) m.child_j[c].assign(child.begin() + c * cap, child.begin() + (c + 1) * cap);
+    for (int d = 0; d < 2; d++) {
+      int rounds = 0;
+      m.sweep[d].assign(cap, 0);
+      m.sweep_init[d].assign(cap, -1);
+      CHECK(cavs_sched_serial_rounds(m.sched, d, m.sweep[d].data(), m.sweep_init[d].data(), cap, &rounds) == CAVS_OK);
+      m.sweep[d].resize(rounds);
+      m.sweep_init[d].resize(rounds);
+    }
+    if (m.sweep[0].empty()) m.sweep[1].clear();     // nothing ran forward: nothing to differentiate
+    tids_to_jobids_.assign(n, 0);
+    for (int g : m.sweep[0]) tids_to_jobids_[g] = g;
+    blob.clear();
+    for (int g = 0; g < n; g++) blob.push_back(g);
+    for (int d = 0; d < 2; d++) { m.off_sweep[d] = blob.size(); blob.insert(blob.end(), m.sweep[d].begin(), m.sweep[d].end()); }
+    for (int c = 0; c < 2; c++) { m.off_child[c] = blob.size(); blob.insert(blob.end(), m.child_j[c].begin(), m.child_j[c].begin() + n); }
+    m.off_self = blob.size();
+    for (int g = 0; g < n; g++) blob.push_back(m.parent_j[g] >= 0 ? g : -1);
+  }
   m.dev_fresh = false;
   round_ = -1;
   forward_ = true;
@@ -110,6 +140,7 @@ bool GraphSchedulerBase::HasChild(int job_id) const {
   // forward graph: a vertex has children iff it is not on level 0
   CHECK(job_id >= 0 && job_id < total_length_);
   const Impl& m = *impl_;
+  if (m.serial) return forward_ ? m.child_j[0][job_id] >= 0 : m.parent_j[job_id] >= 0;   // the reversed graph swaps the roles
   for (int t = 0; t < (m.n_levels > 0 ? m.level_off[1] : 0); t++)
     if (m.t2j[t] == job_id) return false;
   return true;
@@ -138,6 +169,28 @@ void GraphSchedulerBase::SetRound(int level, bool forward) {
   tids_for_gather_init_[1] = m.roots;
 }
 
+void GraphSchedulerBase::SetSerialRound(int round, bool forward) {
+  const Impl& m = *impl_;
+  const std::vector<int>& order = m.sweep[forward ? 0 : 1];
+  round_ = round;
+  for (auto& v : tids_for_gather_) v.clear();
+  for (auto& v : tids_for_scatter_) v.clear();
+  ready_to_execute_ids_.clear();
+  if (round < 0 || round >= static_cast<int>(order.size())) return;
+  const int g = order[round];
+  ready_to_execute_ids_.push_back(g);
+  // graph_scheduler.cc:143-166: the lists of children hold the children's ids, the list towards the
+  // parent holds the vertex's own id once per parent ("only a count number").
+  std::vector<std::vector<int>>& kids = forward ? tids_for_gather_ : tids_for_scatter_;
+  std::vector<std::vector<int>>& self = forward ? tids_for_scatter_ : tids_for_gather_;
+  for (int c = 0; c < 2; c++)
+    if (m.child_j[c][g] >= 0) kids[c].push_back(m.child_j[c][g]);
+  if (m.parent_j[g] >= 0) self[0].push_back(g);
+  const int init = m.sweep_init[forward ? 0 : 1][round];
+  tids_for_gather_init_[forward ? 0 : 1].clear();
+  if (init >= 0) tids_for_gather_init_[forward ? 0 : 1].push_back(init);
+}
+
 const std::vector<int>& GraphSchedulerBase::CurrentRoundTensorIdsForGatherInitialization() const {
   return forward_ ? tids_for_gather_init_[0] : tids_for_gather_init_[1];
 }
@@ -152,16 +205,37 @@ const std::vector<int>& GraphSchedulerBase::CurrentRoundTensorIdsForScatter(int 
 
 const int* GraphSchedulerBase::DeviceJobIds(int* count) const {
   Impl& m = *impl_;
+  if (m.serial) {
+    CHECK(!ready_to_execute_ids_.empty());
+    *count = 1;
+    return m.Device() + m.off_sweep[forward_ ? 0 : 1] + round_;
+  }
   CHECK(round_ >= 0 && round_ < m.n_levels);
   *count = m.level_off[round_ + 1] - m.level_off[round_];
   return m.Device() + m.level_off[round_];
 }
 const int* GraphSchedulerBase::DeviceTensorIdsToJobIds(int* count) const {
+  if (impl_->serial) { *count = impl_->n_total; return impl_->Device(); }   // identity
   *count = impl_->n_sched;
   return impl_->Device();
 }
+// One-vertex rounds: the list is the single table entry of the round's vertex (or empty when that
+// entry is -1 and the caller wants the reference's compact lists).
+static const int* SerialEntry(const int* dev, size_t table, const std::vector<int>& host, int job, bool aligned, int* count) {
+  *count = (aligned || host[job] >= 0) ? 1 : 0;
+  return dev + table + job;
+}
+
 const int* GraphSchedulerBase::DeviceIdsForGather(int child_offset, int* count) const {
   Impl& m = *impl_;
+  if (m.serial) {
+    CHECK(!ready_to_execute_ids_.empty());
+    CHECK(child_offset >= 0 && child_offset < 2);
+    const int g = ready_to_execute_ids_[0];
+    if (forward_) return SerialEntry(m.Device(), m.off_child[child_offset], m.child_j[child_offset], g, aligned_, count);
+    CHECK(child_offset == 0);
+    return SerialEntry(m.Device(), m.off_self, m.parent_j, g, aligned_, count);
+  }
   CHECK(round_ >= 0 && round_ < m.n_levels);
   CHECK(child_offset >= 0 && child_offset < 2);
   const int off = m.level_off[round_], rows = m.level_off[round_ + 1] - off;
@@ -177,6 +251,14 @@ const int* GraphSchedulerBase::DeviceIdsForGather(int child_offset, int* count) 
 }
 const int* GraphSchedulerBase::DeviceIdsForScatter(int child_offset, int* count) const {
   Impl& m = *impl_;
+  if (m.serial) {
+    CHECK(!ready_to_execute_ids_.empty());
+    CHECK(child_offset >= 0 && child_offset < 2);
+    const int g = ready_to_execute_ids_[0];
+    if (!forward_) return SerialEntry(m.Device(), m.off_child[child_offset], m.child_j[child_offset], g, aligned_, count);
+    CHECK(child_offset == 0);
+    return SerialEntry(m.Device(), m.off_self, m.parent_j, g, aligned_, count);
+  }
   CHECK(round_ >= 0 && round_ < m.n_levels);
   CHECK(child_offset >= 0 && child_offset < 2);
   const int off = m.level_off[round_], rows = m.level_off[round_ + 1] - off;
@@ -200,5 +282,11 @@ int BatchGraphScheduler::GetCurrentRoundOffset() const {
   CHECK(round_ >= 0 && round_ < impl_->n_levels);
   return impl_->level_off[round_];
 }
+
+void SerialGraphScheduler::Initialize() {
+  CHECK(Terminate());
+  SetSerialRound(0, forward_);
+}
+void SerialGraphScheduler::ActivateNext() { SetSerialRound(round_ + 1, forward_); }
 
 }  // namespace midend

@@ -64,7 +64,11 @@ class GraphSchedulerBase {
  protected:
   struct Impl;
   std::unique_ptr<Impl> impl_;
+  // true: one vertex per round with tensor id == job id (SerialGraphScheduler); LoadGraph then also
+  // prepares the serial sweeps.
+  virtual bool OneVertexPerRound() const { return false; }
   void SetRound(int level, bool forward);   // fills the per-round host vectors for `level`
+  void SetSerialRound(int round, bool forward);
   std::vector<int> ready_to_execute_ids_;
   std::vector<std::vector<int>> tids_for_gather_init_, tids_for_gather_, tids_for_scatter_;
   std::vector<int> tids_to_jobids_;
@@ -81,6 +85,21 @@ class BatchGraphScheduler : public GraphSchedulerBase {
   void ActivateNext() override;
   bool Terminate() const override { return ready_to_execute_ids_.empty(); }
   int GetCurrentRoundOffset() const override;
+};
+
+// One vertex per round, sample after sample, tensor id == job id: the reference's scheduler for a
+// Session without OPT_BATCHING (cavs/midend/graph_scheduler.h:122-138, graph_scheduler.cc:83-167).
+// Round order and every per-round list are the reference's, including its work-list details (the
+// backward sweep interleaves samples; a single-vertex sample ends the forward sweep).
+class SerialGraphScheduler : public GraphSchedulerBase {
+ public:
+  void Initialize() override;
+  void ActivateNext() override;
+  bool Terminate() const override { return ready_to_execute_ids_.empty(); }
+  int GetCurrentRoundOffset() const override { return GetJobId()[0]; }
+
+ protected:
+  bool OneVertexPerRound() const override { return true; }
 };
 
 }  // namespace midend

@@ -55,6 +55,13 @@ extern "C" int cavs_sched_load(cavs_sched* s, const int32_t* parents, int batch,
   return CAVS_OK;
 }
 
+extern "C" int cavs_sched_set_order(cavs_sched* s, int order) {
+  CAVS_REQUIRE(s, CAVS_ERR_BAD_ARG, "sched_set_order: null handle");
+  CAVS_REQUIRE(order == 0 || order == 1, CAVS_ERR_BAD_ARG, "sched_set_order: order must be 0 (batched) or 1 (one vertex per round)");
+  s->impl.SetOrder(order == 1 ? cavs_b200::kUnbatched : cavs_b200::kBatched);
+  return CAVS_OK;
+}
+
 #define SCHED_READY(name) CAVS_REQUIRE(s && s->loaded, CAVS_ERR_BAD_ARG, name ": no graph loaded")
 
 extern "C" int cavs_sched_counts(const cavs_sched* s, int* n_total, int* n_scheduled, int* n_levels, int* max_level_rows) {
@@ -116,6 +123,42 @@ extern "C" int cavs_sched_ref_stream(const cavs_sched* s, int32_t* out, int capa
   s->impl.RefStream(&v);
   *n = static_cast<int>(v.size());
   CAVS_REQUIRE(out && capacity >= *n, CAVS_ERR_CAPACITY, "sched_ref_stream: capacity");
+  std::memcpy(out, v.data(), v.size() * sizeof(int32_t));
+  return CAVS_OK;
+}
+
+extern "C" int cavs_sched_adjacency(const cavs_sched* s, int32_t* parent_job, int32_t* child_job, int capacity) {
+  SCHED_READY("sched_adjacency");
+  const int n = s->impl.n_total();
+  CAVS_REQUIRE(capacity >= n, CAVS_ERR_CAPACITY, "sched_adjacency: capacity below n_total");
+  if (parent_job && n) std::memcpy(parent_job, s->impl.parent_j().data(), sizeof(int32_t) * n);
+  if (child_job && n) {
+    // the library's arrays are packed at pitch n_total; the caller's at pitch `capacity`
+    for (int c = 0; c < s->impl.n_slots(); ++c)
+      std::memcpy(child_job + static_cast<size_t>(c) * capacity, s->impl.child_j().data() + static_cast<size_t>(c) * n, sizeof(int32_t) * n);
+  }
+  return CAVS_OK;
+}
+extern "C" int cavs_sched_serial_rounds(const cavs_sched* s, int backward, int32_t* jobs, int32_t* init, int capacity, int* n) {
+  SCHED_READY("sched_serial_rounds");
+  CAVS_REQUIRE(n, CAVS_ERR_BAD_ARG, "sched_serial_rounds: null n");
+  std::vector<cavs_b200::LevelSchedule::SerialRound> rounds;
+  s->impl.SerialSweep(backward != 0, &rounds);
+  *n = static_cast<int>(rounds.size());
+  CAVS_REQUIRE(capacity >= *n && (jobs || *n == 0), CAVS_ERR_CAPACITY, "sched_serial_rounds: capacity");
+  for (int r = 0; r < *n; ++r) {
+    jobs[r] = rounds[r].job;
+    if (init) init[r] = rounds[r].init;
+  }
+  return CAVS_OK;
+}
+extern "C" int cavs_sched_ref_serial_stream(const cavs_sched* s, int32_t* out, int capacity, int* n) {
+  SCHED_READY("sched_ref_serial_stream");
+  CAVS_REQUIRE(n, CAVS_ERR_BAD_ARG, "sched_ref_serial_stream: null n");
+  std::vector<int32_t> v;
+  s->impl.RefSerialStream(&v);
+  *n = static_cast<int>(v.size());
+  CAVS_REQUIRE(out && capacity >= *n, CAVS_ERR_CAPACITY, "sched_ref_serial_stream: capacity");
   std::memcpy(out, v.data(), v.size() * sizeof(int32_t));
   return CAVS_OK;
 }

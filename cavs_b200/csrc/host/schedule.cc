@@ -139,12 +139,23 @@ int LevelSchedule::Load(const int32_t* parents, int batch, int max_len, int n_sl
   }
   n_sched_ = level_off_[n_levels];
   // level_cnt_[i][l] becomes the global tensor id of sample i's first vertex on level l
-  {
+  if (order_ == kBatched) {
     std::vector<int32_t> running(level_off_.begin(), level_off_.end() - 1);
     for (int i = 0; i < batch; ++i) {
       int32_t* cnt = level_cnt_.data() + static_cast<size_t>(i) * max_len;
       for (int l = 0; l < sample_levels_[i]; ++l) { const int c = cnt[l]; cnt[l] = running[l]; running[l] += c; }
     }
+  } else {
+    // One vertex per round: a sample's wavefront levels follow one another (the order a first-in
+    // first-out work list visits them), samples follow one another.
+    int32_t running = 0;
+    for (int i = 0; i < batch; ++i) {
+      int32_t* cnt = level_cnt_.data() + static_cast<size_t>(i) * max_len;
+      for (int l = 0; l < sample_levels_[i]; ++l) { const int c = cnt[l]; cnt[l] = running; running += c; }
+    }
+    level_off_.resize(static_cast<size_t>(n_sched_) + 1);
+    for (int t = 0; t <= n_sched_; ++t) level_off_[t] = t;
+    max_level_rows_ = n_sched_ > 0 ? 1 : 0;
   }
 
   // Phase C (parallel over samples): global tensor ids and tensor-id-space adjacency.
@@ -152,6 +163,8 @@ int LevelSchedule::Load(const int32_t* parents, int batch, int max_len, int n_sl
   j2t_.assign(nz, -1);
   child_t_.assign(nz * n_slots, -1);
   parent_t_.assign(nz, -1);
+  child_j_.assign(nz * n_slots, -1);
+  parent_j_.assign(nz, -1);
   std::vector<int> roots_per_thread_sample(batch, 0);
   ParallelFor(batch, threads, [&](int b0, int b1) {
     std::vector<int32_t> slot_used(max_len);
@@ -172,6 +185,8 @@ int LevelSchedule::Load(const int32_t* parents, int batch, int max_len, int n_sl
           const int pt = tid_of(p);
           parent_t_[t] = pt;
           // children land in ascending id order: v ascends, so the next free slot of p is v's slot
+          child_j_[static_cast<size_t>(slot_used[p]) * nz + base + p] = base + v;
+          parent_j_[base + v] = base + p;
           child_t_[static_cast<size_t>(slot_used[p]++) * nz + pt] = t;
         } else {
           roots_per_thread_sample[i] = 1;
@@ -262,6 +277,93 @@ void LevelSchedule::RefStream(std::vector<int32_t>* out) const {
     RefScatter(l, &list); put(list);
     for (int c = 0; c < 2; ++c) { RefGather(l, c, &list); put(list); }
     put(roots);
+  }
+}
+
+// The serial sweep as a work list over job ids.  "wake" edges are followed when a vertex finishes,
+// "wait" edges must all have finished before a vertex runs; forward: wake = parent, wait = children,
+// backward: the reverse (graph_scheduler.cc:73-81).  Details that shape the order:
+//  * the list is first-in first-out and starts with sample 0's vertices that wait on nothing but wake
+//    someone (:108-118), ascending id;
+//  * the next sample joins when a vertex WITHOUT wake edges finishes (:135-137) -- its root in the
+//    forward sweep, but every forward leaf in the backward sweep, so backward samples interleave;
+//  * a sample of one vertex contributes nothing, and the sweep ends when the list runs empty (:141),
+//    so forward execution stops at the first single-vertex sample;
+//  * the gather-initialisation list holds the last vertex seen so far that waits on nothing (:101,153).
+void LevelSchedule::SerialSweep(bool backward, std::vector<SerialRound>* rounds) const {
+  rounds->clear();
+  const size_t nz = static_cast<size_t>(n_total_);
+  auto n_children = [&](int g) {
+    int c = 0;
+    while (c < n_slots_ && child_j_[static_cast<size_t>(c) * nz + g] >= 0) ++c;
+    return c;
+  };
+  auto has_parent = [&](int g) { return parent_j_[g] >= 0 ? 1 : 0; };
+  auto n_wake = [&](int g) { return backward ? n_children(g) : has_parent(g); };
+  auto n_wait = [&](int g) { return backward ? has_parent(g) : n_children(g); };
+  std::vector<int32_t> work, done(nz, 0);
+  work.reserve(nz);
+  auto admit = [&](int sample) {
+    for (int g = sample_off_[sample]; g < sample_off_[sample + 1]; ++g)
+      if (n_wait(g) == 0 && n_wake(g) > 0) work.push_back(g);
+  };
+  int sample = 0;
+  int32_t init = -1;
+  if (batch_ > 0) admit(0);
+  for (size_t head = 0; head < work.size(); ++head) {
+    const int g = work[head];
+    SerialRound r;
+    r.job = g;
+    r.n_wake = n_wake(g);
+    r.n_wait = n_wait(g);
+    r.child[0] = r.child[1] = -1;
+    // The two lists of neighbours a round reports: children in slot order in either direction.
+    for (int c = 0; c < 2 && c < n_slots_; ++c) r.child[c] = child_j_[static_cast<size_t>(c) * nz + g];
+    if (r.n_wait == 0) init = g;
+    r.init = init;
+    rounds->push_back(r);
+    if (r.n_wake > 0) {
+      if (backward) {
+        for (int c = 0; c < r.n_wake; ++c) {
+          const int p = child_j_[static_cast<size_t>(c) * nz + g];
+          if (++done[p] == n_wait(p)) work.push_back(p);
+        }
+      } else {
+        const int p = parent_j_[g];
+        if (++done[p] == n_wait(p)) work.push_back(p);
+      }
+    } else if (++sample < batch_) {
+      admit(sample);
+    }
+  }
+}
+
+void LevelSchedule::RefSerialStream(std::vector<int32_t>* out) const {
+  out->clear();
+  std::vector<SerialRound> fwd, bwd;
+  SerialSweep(false, &fwd);
+  if (!fwd.empty()) SerialSweep(true, &bwd);
+  auto list = [out](int count, int32_t value) {
+    out->push_back(count);
+    for (int i = 0; i < count; ++i) out->push_back(value);
+  };
+  out->push_back(n_total_);
+  out->push_back(static_cast<int32_t>(fwd.size()));
+  std::vector<int32_t> ran(static_cast<size_t>(n_total_), 0);
+  for (const SerialRound& r : fwd) {
+    out->push_back(r.job);
+    for (int c = 0; c < 2; ++c) list(r.child[c] >= 0 ? 1 : 0, r.child[c]);   // gather(c): the slot-c child
+    list(r.n_wake, r.job);                                                // scatter(0): own id, once per parent
+    list(r.init >= 0 ? 1 : 0, r.init);
+    ran[r.job] = r.job;
+  }
+  out->insert(out->end(), ran.begin(), ran.end());
+  out->push_back(static_cast<int32_t>(bwd.size()));
+  for (const SerialRound& r : bwd) {
+    out->push_back(r.job);
+    list(r.n_wait, r.job);                                                // gather(0): own id, once per parent
+    for (int c = 0; c < 2; ++c) list(r.child[c] >= 0 ? 1 : 0, r.child[c]);   // scatter(c): the slot-c child
+    list(r.init >= 0 ? 1 : 0, r.init);
   }
 }
 

@@ -28,8 +28,19 @@ enum TableMode {
   kRefCompat = 1,  // the reference's positional pairing of compact lists with level rows
 };
 
+// How vertices are grouped into rounds.
+enum RoundOrder {
+  kBatched = 0,    // one round per level of the whole batch (BatchGraphScheduler)
+  kUnbatched = 1,  // one vertex per round, sample after sample (the reference's serial mode as an
+                   // execution order: tensor ids follow execution, single-vertex samples are skipped)
+};
+
 class LevelSchedule {
  public:
+  // Takes effect at the next Load().
+  void SetOrder(RoundOrder order) { order_ = order; }
+  RoundOrder order() const { return order_; }
+
   // parents: [batch, max_len] int32, local parent index per vertex, -1 marks the root
   // and ends the sample (graph_scheduler.cc:39).  Returns 0 or a CAVS_ERR_* code and
   // leaves a message in *err.
@@ -62,10 +73,22 @@ class LevelSchedule {
   // Full schedule stream in the oracle's documented layout (two child slots).
   void RefStream(std::vector<int32_t>* out) const;
 
+  // Job-id-space adjacency (independent of the round order): parent_j[g] or -1, child_j[c*N + g] or -1.
+  const std::vector<int32_t>& parent_j() const { return parent_j_; }
+  const std::vector<int32_t>& child_j() const { return child_j_; }
+  // The reference's SerialGraphScheduler (cavs/midend/graph_scheduler.cc:83-167): job ids in the order
+  // its forward (backward = false) or backward sweep runs them, one per round, with the lists each
+  // round reports.  Tensor id == job id in that mode.  Independent of SetOrder().
+  struct SerialRound { int32_t job; int32_t n_wake; int32_t child[2]; int32_t n_wait; int32_t init; };
+  void SerialSweep(bool backward, std::vector<SerialRound>* rounds) const;
+  // Both sweeps serialised in the oracle's "serial schedule stream" layout.
+  void RefSerialStream(std::vector<int32_t>* out) const;
+
  private:
   int batch_ = 0, max_len_ = 0, n_slots_ = 2;
   int n_total_ = 0, n_sched_ = 0, max_level_rows_ = 0, n_roots_ = 0;
-  std::vector<int32_t> sample_off_, level_off_, t2j_, j2t_, child_t_, parent_t_;
+  RoundOrder order_ = kBatched;
+  std::vector<int32_t> sample_off_, level_off_, t2j_, j2t_, child_t_, parent_t_, parent_j_, child_j_;
   // scratch kept between Load() calls so steady-state loads do not allocate
   std::vector<int32_t> local_, sample_len_, sample_levels_, level_cnt_;
 };

@@ -8,6 +8,7 @@ import numpy as np
 from ._abi import check, lib, ptr
 
 ALIGNED, REF_COMPAT = 0, 1
+BATCHED, UNBATCHED = 0, 1
 
 
 class Schedule:
@@ -27,6 +28,12 @@ class Schedule:
                 lib().cavs_sched_destroy(h)
             except Exception:
                 pass
+
+    def set_order(self, order: int) -> "Schedule":
+        """Round order of the next load(): BATCHED (one round per level) or UNBATCHED (one vertex per
+        round, the reference's serial scheduling, cavs/midend/graph_scheduler.cc:83-167)."""
+        check(lib().cavs_sched_set_order(self._h, order))
+        return self
 
     def load(self, parents: np.ndarray, n_slots: int = 2) -> "Schedule":
         parents = np.ascontiguousarray(parents, dtype=np.int32)
@@ -77,6 +84,30 @@ class Schedule:
         out = np.empty(min(cap, 2**31 - 1), np.int32)
         n = ctypes.c_int()
         check(lib().cavs_sched_ref_stream(self._h, ptr(out), out.size, ctypes.byref(n)))
+        return out[: n.value].copy()
+
+
+    def adjacency(self):
+        """(parent_job [N], child_job [slots, N]) in job-id space."""
+        n, k = self.n_total, self.n_slots
+        parent = np.empty(n, np.int32)
+        child = np.empty((k, n), np.int32)
+        check(lib().cavs_sched_adjacency(self._h, ptr(parent), ptr(child), n))
+        return parent, child
+
+    def serial_rounds(self, backward: bool = False):
+        """Job ids in the order the reference's SerialGraphScheduler runs them, and per round the
+        entry of its gather-initialisation list (-1 = empty)."""
+        jobs = np.empty(max(self.n_total, 1), np.int32)
+        init = np.empty(max(self.n_total, 1), np.int32)
+        n = ctypes.c_int()
+        check(lib().cavs_sched_serial_rounds(self._h, int(backward), ptr(jobs), ptr(init), jobs.size, ctypes.byref(n)))
+        return jobs[: n.value].copy(), init[: n.value].copy()
+
+    def ref_serial_stream(self) -> np.ndarray:
+        out = np.empty(16 + 24 * max(self.n_total, 1), np.int32)
+        n = ctypes.c_int()
+        check(lib().cavs_sched_ref_serial_stream(self._h, ptr(out), out.size, ctypes.byref(n)))
         return out[: n.value].copy()
 
 

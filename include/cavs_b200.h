@@ -79,6 +79,26 @@ CAVS_API int cavs_sched_ref_scatter(const cavs_sched* s, int level, int32_t* ids
  * oracle/refsched_driver.cc); *n receives the length, CAVS_ERR_CAPACITY if it does not fit. */
 CAVS_API int cavs_sched_ref_stream(const cavs_sched* s, int32_t* out, int capacity, int* n);
 
+/* Round order of the NEXT cavs_sched_load: 0 = one round per level of the batch (default), 1 = one
+ * vertex per round, sample after sample -- the execution order of SerialGraphScheduler
+ * (graph_scheduler.cc:83-167), i.e. the reference's Session without OPT_BATCHING
+ * (cavs/proto/opt.proto:3-8).  Tensor ids follow execution order in both modes, every "level" then
+ * holds one row, and single-vertex samples are skipped (never truncating the sweep).  The engines run
+ * such a schedule unchanged; it exists to measure what batching buys. */
+CAVS_API int cavs_sched_set_order(cavs_sched* s, int order);
+/* Job-id-space adjacency of the loaded batch: parent_job[g] or -1; child_job[c*capacity + g] = the
+ * slot-c child or -1 (children_ / parents_, graph_scheduler.cc:44-59).  Either pointer may be null. */
+CAVS_API int cavs_sched_adjacency(const cavs_sched* s, int32_t* parent_job, int32_t* child_job, int capacity);
+/* The reference's SerialGraphScheduler itself, where tensor id == job id: jobs[r] is the vertex of
+ * round r of the forward (backward = 0) or backward sweep and init[r] (optional) the single entry of
+ * CurrentRoundTensorIdsForGatherInitialization() in that round, -1 for none.  A round's gather /
+ * scatter lists follow from the adjacency: forward gather(c) = the slot-c child, scatter(0) = the
+ * vertex itself if it has a parent; backward the reverse.  The sweep reproduces the reference's
+ * work-list order, including its early end at a single-vertex sample. */
+CAVS_API int cavs_sched_serial_rounds(const cavs_sched* s, int backward, int32_t* jobs, int32_t* init, int capacity, int* n);
+/* Both serial sweeps serialised as one int32 stream (layout documented in oracle/refsched_driver.cc). */
+CAVS_API int cavs_sched_ref_serial_stream(const cavs_sched* s, int32_t* out, int capacity, int* n);
+
 /* ------------------------------------------------------------------------ */
 /* Row movement behind the graph ops (device).  HBM-bound, 128-bit accesses. */
 /* ------------------------------------------------------------------------ */

@@ -71,6 +71,19 @@ def schedule_stream(parents: np.ndarray) -> np.ndarray:
     return _stream(oracle_lib().cavs_oracle_schedule_stream, parents)
 
 
+def ref_serial_stream(parents: np.ndarray) -> np.ndarray:
+    """The reference's SerialGraphScheduler, driven through one forward and one backward sweep."""
+    lib = refsched_lib()
+    if lib is None or not hasattr(lib, "refsched_serial_stream"):
+        raise FileNotFoundError("oracle/_ref/libcavs_refsched.so not built")
+    return _stream(lib.refsched_serial_stream, parents)
+
+
+def serial_stream(parents: np.ndarray) -> np.ndarray:
+    """Restatement of the serial sweep (layout: oracle/refsched_driver.cc)."""
+    return _stream(oracle_lib().cavs_oracle_serial_stream, parents)
+
+
 def tables(parents: np.ndarray, n_slots: int = 2, mode: int = 0):
     parents = np.ascontiguousarray(parents, np.int32)
     b, m = parents.shape

@@ -209,6 +209,105 @@ int cavs_oracle_schedule_stream(const int *parents, int batch, int max_len, int 
   return (int)w;
 }
 
+/* ------------------------------------------------------------------------- */
+/* Serial (one vertex per round) sweep: restatement of SerialGraphScheduler   */
+/* (cavs/midend/graph_scheduler.cc:83-167, graph_scheduler.h:122-138).        */
+/* Tensor id == job id there (:90,138), a round's offset is its job id.       */
+/* ------------------------------------------------------------------------- */
+
+/* One sweep.  `up` are the edges a finished vertex follows to wake others, `down` the
+ * edges that must all have finished before a vertex runs: forward up = parent, down =
+ * children; after ReverseGraph (graph_scheduler.cc:73-81) the two swap.  The work list is
+ * first-in first-out (:89,131,139-142).  A sample enters the list when the previous
+ * sample's last vertex (one without `up` edges) leaves it (:135-137) -- so in the backward
+ * sweep every forward leaf pulls in the next sample -- and a sample contributes its
+ * vertices that have no `down` but some `up` edge (:110-114), which is nothing for a
+ * single-vertex sample: if the list is empty at that point the sweep ends early (:141).
+ * Emits, per round: job id, then the four lists in the order the caller asks for. */
+static long serial_sweep(const oracle_sched *s, const int *base, const int *len, int batch, int backward,
+                         int *out, long w, long capacity, int *n_rounds, int *seen) {
+  const int K = s->n_slots;
+  int nt = s->n_total > 0 ? s->n_total : 1;
+  int *queue = (int *)malloc(sizeof(int) * (size_t)nt * 2);
+  int *hits = (int *)calloc((size_t)nt, sizeof(int));
+  int head = 0, tail = 0, sample = 0, rounds = 0;
+  int last_init = -1;
+#define N_UP(g) (backward ? s->n_child[g] : (s->parent[g] >= 0 ? 1 : 0))
+#define N_DOWN(g) (backward ? (s->parent[g] >= 0 ? 1 : 0) : s->n_child[g])
+#define UP(g, i) (backward ? s->child[(size_t)(g) * K + (i)] : s->parent[g])
+#define DOWN(g, i) (backward ? s->parent[g] : s->child[(size_t)(g) * K + (i)])
+#define ENTER(sid) do { for (int _j = 0; _j < len[sid]; _j++) { int _g = base[sid] + _j; \
+      if (N_DOWN(_g) == 0 && N_UP(_g) > 0) queue[tail++] = _g; } } while (0)
+  if (batch > 0) ENTER(0);
+  while (head < tail) {
+    const int g = queue[head];
+    if (N_DOWN(g) == 0) last_init = g;                       /* :101,105,153,165: never cleared otherwise */
+    EMIT(g);
+    if (!backward) {
+      for (int c = 0; c < 2; c++) { if (c < N_DOWN(g)) { EMIT(1); EMIT(DOWN(g, c)); } else EMIT(0); }   /* :150-152 */
+      { int n = N_UP(g); EMIT(n); for (int i = 0; i < n; i++) EMIT(g); }                                 /* :146-149 */
+    } else {
+      { int n = N_DOWN(g); EMIT(n); for (int i = 0; i < n; i++) EMIT(g); }                               /* :157-160 */
+      for (int c = 0; c < 2; c++) { if (c < N_UP(g)) { EMIT(1); EMIT(UP(g, c)); } else EMIT(0); }        /* :161-163 */
+    }
+    if (last_init >= 0) { EMIT(1); EMIT(last_init); } else EMIT(0);
+    if (seen) seen[g] = 1;
+    rounds++;
+    /* ActivateNext, :121-139 */
+    if (N_UP(g) > 0) {
+      for (int i = 0; i < N_UP(g); i++) { int p = UP(g, i); if (++hits[p] == N_DOWN(p)) queue[tail++] = p; }
+    } else if (++sample < batch) {
+      ENTER(sample);
+    }
+    head++;
+  }
+#undef N_UP
+#undef N_DOWN
+#undef UP
+#undef DOWN
+#undef ENTER
+  free(queue); free(hits);
+  *n_rounds = rounds;
+  return w;
+}
+
+/* Stream layout ("serial schedule stream"), all int32 (lists are written as count, entries):
+ *   N
+ *   RF, then per forward round:  job  gather(0)  gather(1)  scatter(0)  gather-initialisation
+ *   t2j[N]                       identity for vertices that ran, 0 otherwise (a fresh scheduler)
+ *   RB, then per backward round: job  gather(0)  scatter(0)  scatter(1)  gather-initialisation
+ * Returns the length, -(needed) if capacity is too small, -1000000-k for malformed graphs. */
+int cavs_oracle_serial_stream(const int *parents, int batch, int max_len, int *out, int capacity) {
+  oracle_sched s;
+  int rc = oracle_sched_build(parents, batch, max_len, 2, &s);
+  if (rc < 0) return -1000000 + rc;
+  int nb = batch > 0 ? batch : 1;
+  int *base = (int *)malloc(sizeof(int) * (size_t)nb), *len = (int *)malloc(sizeof(int) * (size_t)nb);
+  int total = 0;
+  for (int i = 0; i < batch; i++) {
+    const int *row = parents + (size_t)i * max_len;
+    int k = 0;
+    while (row[k] != -1) k++;
+    base[i] = total; len[i] = k + 1; total += k + 1;
+  }
+  int *seen = (int *)calloc((size_t)(total > 0 ? total : 1), sizeof(int));
+  long w = 0;
+  int rounds = 0;
+  EMIT(s.n_total);
+  long at = w; EMIT(0);
+  w = serial_sweep(&s, base, len, batch, 0, out, w, capacity, &rounds, seen);
+  if (at < capacity) out[at] = rounds;
+  for (int g = 0; g < s.n_total; g++) EMIT(seen[g] ? g : 0);
+  at = w; EMIT(0);
+  if (rounds > 0) w = serial_sweep(&s, base, len, batch, 1, out, w, capacity, &rounds, NULL);
+  else rounds = 0;
+  if (at < capacity) out[at] = rounds;
+  free(base); free(len); free(seen);
+  oracle_sched_free(&s);
+  if (w > capacity) return (int)-w;
+  return (int)w;
+}
+
 /* Per-vertex index tables in tensor-id space, the form the numerics below (and the
  * product engine) consume.  All arrays are [n] or [n_slots * n] (slot-major).
  *   fg[c][t]  forward gather source: mailbox row read into row t's slot-c child state, -1 = zeros

@@ -76,3 +76,56 @@ extern "C" int refsched_stream(const int* parents, int batch, int max_len, int* 
   for (int v : body) *w++ = v;
   return need;
 }
+
+// The same for the reference's SerialGraphScheduler (one vertex per round, tensor id == job id).
+// Stream layout ("serial schedule stream"), all int32:
+//   N
+//   RF, then per forward round:  job  gather(0)  gather(1)  scatter(0)  gather-initialisation
+//   t2j[N]
+//   RB, then per backward round: job  gather(0)  scatter(0)  scatter(1)  gather-initialisation
+// A first sample of one vertex would make the reference read the front of an empty list
+// (graph_scheduler.cc:89); the driver reports zero rounds for it instead of calling in.
+extern "C" int refsched_serial_stream(const int* parents, int batch, int max_len, int* out, int capacity) {
+  midend::Tensor graph(parents, batch, max_len);
+  midend::SerialGraphScheduler gs;
+  const int total = gs.LoadGraph(graph);
+  std::vector<int> fwd, bwd;
+  int rf = 0, rb = 0;
+  const bool runnable = batch > 0 && parents[0] != -1;
+  if (runnable) {
+    gs.Initialize();
+    while (!gs.Terminate()) {
+      fwd.push_back(gs.GetCurrentRoundOffset());
+      put(&fwd, gs.CurrentRoundTensorIdsForGather(0));
+      put(&fwd, gs.CurrentRoundTensorIdsForGather(1));
+      put(&fwd, gs.CurrentRoundTensorIdsForScatter(0));
+      put(&fwd, gs.CurrentRoundTensorIdsForGatherInitialization());
+      gs.ActivateNext();
+      ++rf;
+    }
+  }
+  std::vector<int> t2j = gs.TensorIdsToJobIds();
+  if (rf > 0) {
+    gs.ReverseGraph();
+    gs.Initialize();
+    while (!gs.Terminate()) {
+      bwd.push_back(gs.GetCurrentRoundOffset());
+      put(&bwd, gs.CurrentRoundTensorIdsForGather(0));
+      put(&bwd, gs.CurrentRoundTensorIdsForScatter(0));
+      put(&bwd, gs.CurrentRoundTensorIdsForScatter(1));
+      put(&bwd, gs.CurrentRoundTensorIdsForGatherInitialization());
+      gs.ActivateNext();
+      ++rb;
+    }
+  }
+  const int need = 3 + static_cast<int>(fwd.size() + t2j.size() + bwd.size());
+  if (need > capacity) return -need;
+  int* w = out;
+  *w++ = total;
+  *w++ = rf;
+  for (int v : fwd) *w++ = v;
+  for (int v : t2j) *w++ = v;
+  *w++ = rb;
+  for (int v : bwd) *w++ = v;
+  return need;
+}

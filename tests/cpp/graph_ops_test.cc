@@ -22,6 +22,7 @@
 
 extern "C" {
 int cavs_oracle_schedule_stream(const int* parents, int batch, int max_len, int* out, int capacity);
+int cavs_oracle_serial_stream(const int* parents, int batch, int max_len, int* out, int capacity);
 void cavs_oracle_gather_rows(float* out, const float* inp, const int* ids, int n_ids, int row);
 void cavs_oracle_scatter_rows(float* out, const int* ids, const float* inp, int n_ids, int row);
 void cavs_oracle_zero_rows(float* out, int n_ids, int row);
@@ -31,6 +32,7 @@ using backend::CreateOp;
 using backend::OpImpl;
 using midend::BatchGraphScheduler;
 using midend::OpContext;
+using midend::SerialGraphScheduler;
 using midend::Tensor;
 using midend::TensorShape;
 
@@ -131,6 +133,56 @@ static void TestSchedulerFacade() {
   const int n = cavs_oracle_schedule_stream(&kSkew[0][0], kBatch, kMaxLen, want.data(), (int)want.size());
   EXPECT(n == (int)mine.size());
   EXPECT(n > 0 && std::memcmp(want.data(), mine.data(), sizeof(int) * mine.size()) == 0);
+}
+
+// The same walk over the one-vertex-per-round scheduler, against the oracle's serial stream.  The
+// second batch holds a single-vertex sample in the middle: the forward sweep ends there, the backward
+// sweep (which admits a new sample at every leaf) does not.
+static const int kHole[3][5] = {{2, 2, -1, -1, -1}, {-1, -1, -1, -1, -1}, {3, 3, 4, 4, -1}};
+static void SerialFacadeCase(const int* parents, int batch) {
+  Tensor graph("graph", CPU, DT_INT32, TensorShape({batch, kMaxLen}), const_cast<int*>(parents));
+  SerialGraphScheduler gs;
+  const int total = gs.LoadGraph(graph);
+  std::vector<int> mine = {total, 0};
+  auto put = [&mine](const std::vector<int>& v) { mine.push_back((int)v.size()); mine.insert(mine.end(), v.begin(), v.end()); };
+  int rounds = 0;
+  gs.Initialize();
+  while (!gs.Terminate()) {
+    EXPECT(gs.GetJobId().size() == 1);
+    mine.push_back(gs.GetCurrentRoundOffset());
+    put(gs.CurrentRoundTensorIdsForGather(0));
+    put(gs.CurrentRoundTensorIdsForGather(1));
+    put(gs.CurrentRoundTensorIdsForScatter(0));
+    put(gs.CurrentRoundTensorIdsForGatherInitialization());
+    EXPECT(gs.HasChild(gs.GetJobId()[0]) == !gs.CurrentRoundTensorIdsForGather(0).empty());
+    gs.ActivateNext();
+    ++rounds;
+  }
+  mine[1] = rounds;
+  mine.insert(mine.end(), gs.TensorIdsToJobIds().begin(), gs.TensorIdsToJobIds().end());
+  const size_t at = mine.size();
+  mine.push_back(0);
+  rounds = 0;
+  gs.ReverseGraph();
+  gs.Initialize();
+  while (!gs.Terminate()) {
+    mine.push_back(gs.GetCurrentRoundOffset());
+    put(gs.CurrentRoundTensorIdsForGather(0));
+    put(gs.CurrentRoundTensorIdsForScatter(0));
+    put(gs.CurrentRoundTensorIdsForScatter(1));
+    put(gs.CurrentRoundTensorIdsForGatherInitialization());
+    gs.ActivateNext();
+    ++rounds;
+  }
+  mine[at] = rounds;
+  std::vector<int> want(4096);
+  const int n = cavs_oracle_serial_stream(parents, batch, kMaxLen, want.data(), (int)want.size());
+  EXPECT(n == (int)mine.size());
+  EXPECT(n > 0 && std::memcmp(want.data(), mine.data(), sizeof(int) * mine.size()) == 0);
+}
+static void TestSerialSchedulerFacade() {
+  SerialFacadeCase(&kSkew[0][0], kBatch);
+  SerialFacadeCase(&kHole[0][0], 3);
 }
 
 static std::vector<float> ToHost(const Tensor& t, size_t elems) {
@@ -248,6 +300,82 @@ static void TestGraphOpsOnDevice(bool aligned) {
   EXPECT(cudaGetLastError() == cudaSuccess);
 }
 
+// The forward sweep of the same toy vertex function, one vertex per round (tensor id == job id), with the
+// reference's compact one-entry lists.
+static void TestSerialOpsOnDevice() {
+  const int W = 12;
+  Tensor graph("graph", CPU, DT_INT32, TensorShape({kBatch, kMaxLen}), const_cast<int*>(&kSkew[0][0]));
+  SerialGraphScheduler gs;
+  const int total = gs.LoadGraph(graph);
+  const int cap = kBatch * kMaxLen;
+  auto arena = [&](const char* name) { Tensor t(name, GPU, DT_FLOAT, TensorShape({cap, W})); t.SetAsDynamic(); return t; };
+  Tensor mailbox = arena("mailbox"), g0 = arena("g0"), g1 = arena("g1"), xin = arena("x"), y = arena("y"), pushed = arena("pushed");
+  Tensor func_arg("arg", GPU, DT_FLOAT, TensorShape({cap, W}));
+  Tensor graph_out("out", GPU, DT_FLOAT, TensorShape({cap, W}));
+  std::vector<float> h_arg((size_t)cap * W);
+  for (size_t i = 0; i < h_arg.size(); i++) h_arg[i] = 0.125f * (float)((i * 2246822519u) % 89) - 5.0f;
+  cudaMemcpy(func_arg.mutable_data<float>(), h_arg.data(), h_arg.size() * sizeof(float), cudaMemcpyHostToDevice);
+  gs.SetMessagePasser(mailbox);
+  std::unique_ptr<OpImpl> gather0(CreateOp(GraphOp("Gather", 0, {W}, true))), gather1(CreateOp(GraphOp("Gather", 1, {W}, true)));
+  std::unique_ptr<OpImpl> pull(CreateOp(GraphOp("Pull", -1, {W}, true))), scatter(CreateOp(GraphOp("Scatter", 0, {W}, false)));
+  std::unique_ptr<OpImpl> push(CreateOp(GraphOp("Push", -1, {W}, false)));
+  std::unique_ptr<OpImpl> pusharg(CreateOp(GraphOp("FunctionPushArg", -1, {W}, false))), popret(CreateOp(GraphOp("FunctionPopRet", -1, {W}, false)));
+  auto ctx = [&](std::vector<const Tensor*> in, std::vector<Tensor*> out) {
+    std::unique_ptr<OpContext> c(new OpContext());
+    for (auto* t : in) c->AppendInput(t);
+    for (auto* t : out) c->AppendOutput(t);
+    c->SetGraphScheduler(&gs);
+    return c;
+  };
+  auto c_g0 = ctx({}, {&g0}), c_g1 = ctx({}, {&g1}), c_pull = ctx({}, {&xin}), c_sc = ctx({&y}, {&mailbox}), c_push = ctx({&y}, {&pushed});
+  auto c_arg = ctx({&func_arg}, {}), c_ret = ctx({}, {&graph_out});
+  std::vector<float> m_mail((size_t)cap * W, 0.f), m_y((size_t)cap * W, 0.f), m_out((size_t)cap * W, 0.f);
+
+  pusharg->Compute(c_arg.get());
+  int rounds = 0;
+  gs.Initialize();
+  while (!gs.Terminate()) {
+    const int job = gs.GetCurrentRoundOffset();
+    for (OpContext* c : {c_g0.get(), c_g1.get(), c_pull.get(), c_sc.get(), c_push.get()}) c->SetTensorOffset();
+    gather0->Compute(c_g0.get());
+    gather1->Compute(c_g1.get());
+    pull->Compute(c_pull.get());
+    std::vector<float> want[2] = {std::vector<float>(W, 0.f), std::vector<float>(W, 0.f)};
+    for (int c = 0; c < 2; c++) {
+      const std::vector<int>& ids = gs.CurrentRoundTensorIdsForGather(c);
+      EXPECT(ids.size() <= 1);
+      if (!ids.empty()) cavs_oracle_gather_rows(want[c].data(), m_mail.data(), ids.data(), 1, W);
+    }
+    std::vector<float> d_g0 = ToHost(g0, W), d_g1 = ToHost(g1, W), d_x = ToHost(xin, W);
+    // a childless vertex zero-fills its gather outputs through the initialisation list; a vertex with
+    // one child leaves the other slot's row as the allocator left it (zero: fresh arena)
+    EXPECT(std::memcmp(d_g0.data(), want[0].data(), W * sizeof(float)) == 0);
+    EXPECT(std::memcmp(d_g1.data(), want[1].data(), W * sizeof(float)) == 0);
+    EXPECT(std::memcmp(d_x.data(), &h_arg[(size_t)job * W], W * sizeof(float)) == 0);
+    std::vector<float> hy(W);
+    for (int i = 0; i < W; i++) hy[i] = d_g0[i] + 2.0f * d_g1[i] + d_x[i];
+    std::memcpy(&m_y[(size_t)job * W], hy.data(), W * sizeof(float));
+    y.ScaleDynamicDimension(1);
+    cudaMemcpy(y.mutable_data<float>(), hy.data(), W * sizeof(float), cudaMemcpyHostToDevice);
+    scatter->Compute(c_sc.get());
+    push->Compute(c_push.get());
+    const std::vector<int>& sids = gs.CurrentRoundTensorIdsForScatter(0);
+    if (!sids.empty()) cavs_oracle_scatter_rows(m_mail.data(), sids.data(), hy.data(), 1, W);
+    gs.ActivateNext();
+    ++rounds;
+  }
+  EXPECT(rounds == total);
+  for (OpContext* c : {c_g0.get(), c_g1.get(), c_pull.get(), c_sc.get(), c_push.get()}) c->ResetTensorOffset();
+  popret->Compute(c_ret.get());
+  cavs_oracle_scatter_rows(m_out.data(), gs.TensorIdsToJobIds().data(), m_y.data(), total, W);
+  cudaDeviceSynchronize();
+  mailbox.SetOffsetWithId(0);
+  std::vector<float> d_mail = ToHost(mailbox, (size_t)cap * W), d_out = ToHost(graph_out, (size_t)cap * W);
+  EXPECT(std::memcmp(d_mail.data(), m_mail.data(), d_mail.size() * sizeof(float)) == 0);
+  EXPECT(std::memcmp(d_out.data(), m_out.data(), (size_t)total * W * sizeof(float)) == 0);
+  EXPECT(cudaGetLastError() == cudaSuccess);
+}
+
 // The fused cell operators: registration, shape inference and gradient definition (no CUDA call).
 static OpDef FusedCellDef(int k) {
   OpDefBuilder b("TreeLSTMCell");
@@ -349,9 +477,11 @@ int main(int argc, char** argv) {
   TestRegistryAndDecls();
   TestFusedCellDecl();
   TestSchedulerFacade();
+  TestSerialSchedulerFacade();
   if (mode == "gpu") {
     TestGraphOpsOnDevice(false);   // the reference's positional lists
     TestGraphOpsOnDevice(true);    // aligned lists
+    TestSerialOpsOnDevice();
     TestFusedCellOnDevice();
   }
   if (g_failures == 0) std::printf("graph_ops_test %s: ok\n", mode.c_str());

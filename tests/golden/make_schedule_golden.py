@@ -1,6 +1,7 @@
-"""Generates tests/golden/schedule_streams.json by running the reference's own graph scheduler
+"""Generates tests/golden/schedule_streams.json by running the reference's own graph schedulers
 (cavs/midend/graph_scheduler.{h,cc}, compiled by oracle/Makefile into oracle/_ref/) on a fixed
-set of small graphs.  Run where the reference checkout is present:
+set of small graphs: `stream` is BatchGraphScheduler's forward + backward sweep, `serial`
+SerialGraphScheduler's (layouts: oracle/refsched_driver.cc).  Run where the reference checkout is present:
 
     make -C oracle && python tests/golden/make_schedule_golden.py
 """
@@ -26,15 +27,25 @@ cases = [
     ("single_vertex_sample", [[-1, -1], [1, -1]]),
     ("unary_over_binary", [[2, 2, 3, -1]]),
     ("fixed_chains", [[1, 2, 3, -1]] * 3),
+    ("single_vertex_sample_in_the_middle", [[2, 2, -1, -1, -1], [-1, -1, -1, -1, -1], [3, 3, 4, 4, -1]]),
+    ("single_vertex_sample_last", [[1, 2, -1], [-1, -1, -1]]),
 ]
+
+
+def record(name, p):
+    p = np.array(p, np.int32)
+    return dict(name=name, parents=p.tolist(), stream=oracle.ref_schedule_stream(p).tolist(),
+                serial=oracle.ref_serial_stream(p).tolist())
+
+
 out = []
 for name, p in cases:
-    out.append(dict(name=name, parents=p, stream=oracle.ref_schedule_stream(np.array(p, np.int32)).tolist()))
+    out.append(record(name, p))
 for seed in range(12):
     p = S.synth_trees(1000 + seed, 3 + seed % 4, 1 + seed % 3, 3 + seed)[0]
-    out.append(dict(name=f"random_trees_{seed}", parents=p.tolist(), stream=oracle.ref_schedule_stream(p).tolist()))
+    out.append(record(f"random_trees_{seed}", p))
 for seed in range(4):
     p = S.synth_chains(2000 + seed, 4, 1, 6 + seed)
-    out.append(dict(name=f"random_chains_{seed}", parents=p.tolist(), stream=oracle.ref_schedule_stream(p).tolist()))
+    out.append(record(f"random_chains_{seed}", p))
 (Path(__file__).parent / "schedule_streams.json").write_text(json.dumps(out, separators=(",", ":")))
 print(len(out), "cases")

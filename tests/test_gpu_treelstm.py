@@ -194,3 +194,33 @@ def test_root_only_labels(cuda, bf16, K, arity):
         assert rel_err(out[k], ref[k]) < tol, k
     assert abs(loss_sum - ref["loss"].sum()) <= tol * abs(ref["loss"].sum())
     assert np.count_nonzero(out["loss"]) == batch
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_one_vertex_per_round_schedule_gives_the_same_step(cuda, bf16):
+    # The reference's serial scheduling (a Session without OPT_BATCHING) as a schedule of one-row levels:
+    # the engine runs it unchanged and must reproduce the batched step -- against the oracle on the same
+    # tables, and against the batched engine run job for job.
+    H, E, V, C = (64, 48, 300, 5) if bf16 else (32, 20, 100, 3)
+    parents, tok_job, label_job = make_tree_batch(77, 6, 2, 8, V, C)
+    params = make_params(5, H, E, V, C, scale=0.05, bias_scale=0.02)
+    s = S.Schedule().set_order(S.UNBATCHED).load(parents)
+    assert s.n_levels == s.n_scheduled and s.max_level_rows == 1
+    eng = TreeLSTM(H, E, V, C, gemm_bf16=bf16, max_vertices=s.n_total, max_level_rows=1)
+    eng.set_params(params)
+    eng.load_batch(s, tok_job, label_job)
+    eng.forward()
+    eng.backward()
+    eng.read_loss()
+    out = dict(state=eng.state(), loss=eng.loss_rows(), **eng.grad_dict())
+    ref = _oracle(s, tok_job, label_job, params, H, E, V, C, bf16=bf16)
+    tol = 5e-3 if bf16 else 1e-5
+    for k in KEYS:
+        assert rel_err(out[k], ref[k]) < tol, k
+    sb, _, outb, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, bf16=bf16)
+    t2j, _ = s.maps()
+    _, bj2t = sb.maps()
+    tol = 2e-2 if bf16 else 1e-5
+    assert rel_err(out["state"][: s.n_scheduled], outb["state"][bj2t[t2j[: s.n_scheduled]]]) < tol
+    for k in KEYS[2:]:
+        assert rel_err(out[k], outb[k]) < tol, k

@@ -31,6 +31,10 @@ def test_golden_streams_match_oracle_and_product():
         want = np.array(case["stream"], np.int32)
         assert np.array_equal(oracle.schedule_stream(parents), want), case["name"]
         assert np.array_equal(S.Schedule().load(parents).ref_stream(), want), case["name"]
+        # one vertex per round (SerialGraphScheduler)
+        want = np.array(case["serial"], np.int32)
+        assert np.array_equal(oracle.serial_stream(parents), want), case["name"]
+        assert np.array_equal(S.Schedule().load(parents).ref_serial_stream(), want), case["name"]
 
 
 @pytest.mark.skipif(oracle.refsched_lib() is None, reason="reference scheduler was not compiled on this machine")
@@ -40,6 +44,9 @@ def test_reference_scheduler_agrees_on_random_graphs():
         ref = oracle.ref_schedule_stream(parents)
         assert np.array_equal(oracle.schedule_stream(parents), ref), seed
         assert np.array_equal(S.Schedule().load(parents).ref_stream(), ref), seed
+        ref = oracle.ref_serial_stream(parents)
+        assert np.array_equal(oracle.serial_stream(parents), ref), seed
+        assert np.array_equal(S.Schedule().load(parents).ref_serial_stream(), ref), seed
 
 
 def test_tables_match_oracle_both_modes():
@@ -81,6 +88,38 @@ def test_n_ary_tables_extension():
     # every non-root is gathered exactly once
     gathered = fg[fg >= 0]
     assert len(np.unique(gathered)) == len(gathered) == s.n_total - parents.shape[0]
+
+
+def test_unbatched_order_runs_one_vertex_per_round():
+    # The execution order of the serial scheduler as a schedule the engines can run: tensor ids follow
+    # execution, every level holds one row, the tables stay consistent with the batched ones.
+    for seed in range(40):
+        parents = _random_graph(seed)
+        s = S.Schedule().set_order(S.UNBATCHED).load(parents)
+        b = S.Schedule().load(parents)
+        assert s.n_scheduled == b.n_scheduled and s.n_levels == s.n_scheduled
+        assert np.array_equal(s.level_off, np.arange(s.n_scheduled + 1))
+        t2j, j2t = s.maps()
+        fg, fs, bg, bs = s.tables(0)
+        bt2j, bj2t = b.maps()
+        bfg = b.tables(0)[0]
+        n = s.n_scheduled
+        for c in range(2):
+            m = fg[c][:n] >= 0
+            assert (fg[c][:n][m] < np.arange(n)[m]).all()              # children run strictly earlier
+            # same children, job for job
+            want = np.where(bfg[c][bj2t[t2j[:n]]] >= 0, bt2j[np.maximum(bfg[c][bj2t[t2j[:n]]], 0)], -1)
+            got = np.where(fg[c][:n] >= 0, t2j[np.maximum(fg[c][:n], 0)], -1)
+            assert np.array_equal(want, got)
+        # without single-vertex samples the order is the reference's serial forward sweep
+        lens = [list(row).index(-1) + 1 for row in parents]
+        if 1 not in lens:
+            assert np.array_equal(t2j[:n], s.serial_rounds()[0])
+        # samples run one after another
+        sample_of = np.searchsorted(np.cumsum(lens), t2j[:n], side="right")
+        assert (np.diff(sample_of) >= 0).all()
+        parent, child = s.adjacency()
+        assert ((parent >= 0).sum() == s.n_total - len(lens)) and child.shape == (2, s.n_total)
 
 
 def test_level_properties_full_size():
