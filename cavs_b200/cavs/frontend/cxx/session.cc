@@ -256,6 +256,8 @@ struct Session::Impl {
     Must(cavs_treelstm_create(&cfg, workspace, ws, &engine), "cavs_treelstm_create");
     Must(cavs_treelstm_bind(engine, params, grads), "cavs_treelstm_bind");
     Must(cavs_sched_create(&sched), "cavs_sched_create");
+    // cavs/midend/graph_session.h:20-24: OPT_BATCHING selects the level scheduler, its absence the serial one.
+    Must(cavs_sched_set_order(sched, (opt & OPT_BATCHING) ? 0 : 1), "cavs_sched_set_order");
     // Variable fillers (cavs/backend/functor_filler.h): constant or uniform; one seeded stream per variable.
     host_params.assign(n_params, 0.f);
     uint64_t seed = 0x5eed0000;

@@ -6,6 +6,12 @@
 // (apps/paper/seq-lstm-cavs.cc:62-86) -- and binds it to the fused engine behind the C ABI
 // (cavs_treelstm_*).  Any other program is a fatal error: there is no generic interpreter and no
 // CPU fallback.
+//
+// Optimisation bits (cavs/proto/opt.proto:3-8): OPT_BATCHING is honoured as in the reference
+// (cavs/midend/graph_session.h:20-24) -- with it every level of the batch is one round, without it the
+// vertices run one per round in the serial scheduler's order, with identical results.  OPT_FUSION and
+// OPT_STREAMMING are accepted and change nothing: the cell is always one fused kernel per level and
+// direction, and the launches of a step are already chained on one stream.
 #ifndef CAVS_FRONTEND_CXX_SESSION_H_
 #define CAVS_FRONTEND_CXX_SESSION_H_
 

@@ -134,8 +134,9 @@ static double RelErr(const std::vector<float>& a, const std::vector<float>& b) {
   return err / ref;
 }
 
-// One training step through Session::Run vs the oracle.  `chain`: which vertex function.
-static void TestTrainingStep(bool chain) {
+// One training step through Session::Run vs the oracle.  `chain`: which vertex function; `opt`: the
+// Session's optimisation bits (without OPT_BATCHING the vertices run one per round).
+static void TestTrainingStep(bool chain, int opt) {
   frontend::Program::Reset();
   const int H = kHidden, E = chain ? kHidden : kEmbed, V = kVocab, C = kClasses, K = chain ? 1 : 2;
   const int B = 3, L = 7;
@@ -163,7 +164,7 @@ static void TestTrainingStep(bool chain) {
   const float lr = 0.5f;
   Sym train = loss.Optimizer({}, lr);
   Sym mean_loss = loss.Reduce_mean();
-  Session sess(OPT_BATCHING);
+  Session sess(opt);
 
   // parameters in the DECLARED layouts
   std::vector<float> table = Uniform((size_t)V * E, 0.4f), bias = Uniform(4 * H, 0.2f), wc = Uniform((size_t)C * H, 0.4f), bc = Uniform(C, 0.2f);
@@ -244,8 +245,10 @@ int main(int argc, char** argv) {
   const std::string mode = argc > 1 ? argv[1] : "cpu";
   TestRecording();
   if (mode == "gpu") {
-    TestTrainingStep(false);
-    TestTrainingStep(true);
+    TestTrainingStep(false, OPT_BATCHING);
+    TestTrainingStep(true, OPT_BATCHING | OPT_FUSION | OPT_STREAMMING);
+    TestTrainingStep(false, OPT_NONE);
+    TestTrainingStep(true, OPT_FUSION);
   }
   if (g_failures == 0) std::printf("frontend_test %s: ok\n", mode.c_str());
   return g_failures == 0 ? 0 : 1;
