@@ -224,3 +224,65 @@ def test_one_vertex_per_round_schedule_gives_the_same_step(cuda, bf16):
     assert rel_err(out["state"][: s.n_scheduled], outb["state"][bj2t[t2j[: s.n_scheduled]]]) < tol
     for k in KEYS[2:]:
         assert rel_err(out[k], outb[k]) < tol, k
+
+
+def test_single_vertex_samples_never_execute(cuda):
+    # graph_scheduler.cc:180: a sample of one vertex is never scheduled.  Its vertex keeps a tensor-id-less
+    # slot, contributes no loss and no gradient; the rest of the batch is unaffected.
+    H, E, V, C = 32, 24, 50, 3
+    parents, tok_job, label_job = make_tree_batch(91, 5, 2, 7, V, C)
+    lens = (parents == -1).argmax(1) + 1
+    holes = np.full((2, parents.shape[1]), -1, np.int32)
+    mixed = np.concatenate([parents[:2], holes[:1], parents[2:], holes[1:]])
+    cut = int(lens[:2].sum())
+    tok_mixed = np.concatenate([tok_job[:cut], [7], tok_job[cut:], [9]]).astype(np.int32)
+    lab_mixed = np.concatenate([label_job[:cut], [1], label_job[cut:], [2]]).astype(np.int32)
+    params = make_params(4, H, E, V, C, scale=0.1, bias_scale=0.05)
+    s = S.Schedule().load(mixed)
+    assert s.n_total == int(lens.sum()) + 2 and s.n_scheduled == int(lens.sum())
+    eng = TreeLSTM(H, E, V, C, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+    eng.set_params(params)
+    eng.load_batch(s, tok_mixed, lab_mixed)
+    eng.forward(); eng.backward()
+    loss_sum = eng.read_loss()
+    got = eng.grad_dict()
+    _, _, want, want_loss = _run(cuda, parents, tok_job, label_job, params, H, E, V, C)
+    assert abs(loss_sum - want_loss) <= 1e-6 * abs(want_loss)
+    for k in KEYS[2:]:
+        assert np.array_equal(got[k], want[k]), k
+    assert np.array_equal(eng.state()[: s.n_scheduled], want["state"][: s.n_scheduled])
+
+
+def test_batch_of_nothing_but_single_vertices(cuda):
+    H, E, V, C = 16, 16, 20, 2
+    parents = np.full((3, 4), -1, np.int32)
+    s = S.Schedule().load(parents)
+    assert (s.n_total, s.n_scheduled, s.n_levels) == (3, 0, 0)
+    eng = TreeLSTM(H, E, V, C, max_vertices=8, max_level_rows=8)
+    eng.set_params(make_params(1, H, E, V, C))
+    eng.load_batch(s, np.zeros(3, np.int32), np.zeros(3, np.int32))
+    eng.forward(); eng.backward()
+    assert eng.read_loss() == 0.0
+    assert all(not g.any() for g in eng.grad_dict().values())
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_one_engine_many_batches(cuda, bf16):
+    # An engine sized for the largest batch steps through batches of different shapes (its two table slots
+    # alternate) and reproduces, bit for bit, what a fresh engine computes for each of them.
+    H, E, V, C = (64, 64, 400, 5) if bf16 else (24, 16, 60, 4)
+    params = make_params(8, H, E, V, C, scale=0.08, bias_scale=0.03)
+    batches = [make_tree_batch(300 + i, b, 2, hi, V, C) for i, (b, hi) in enumerate([(9, 12), (2, 3), (14, 20), (1, 2), (9, 12)])]
+    scheds = [S.Schedule().load(p) for p, _, _ in batches]
+    eng = TreeLSTM(H, E, V, C, gemm_bf16=bf16, max_vertices=max(s.n_total for s in scheds),
+                   max_level_rows=max(s.max_level_rows for s in scheds))
+    eng.set_params(params)
+    for (parents, tok_job, label_job), s in zip(batches, scheds):
+        eng.load_batch(s, tok_job, label_job)
+        eng.forward(); eng.backward()
+        loss_sum = eng.read_loss()
+        got = dict(state=eng.state()[: s.n_total], loss=eng.loss_rows()[: s.n_total], **eng.grad_dict())
+        _, _, want, want_loss = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, bf16=bf16)
+        assert loss_sum == want_loss
+        for k in KEYS:
+            assert np.array_equal(got[k], want[k][: len(got[k])] if k in ("state", "loss") else want[k]), k
