@@ -78,6 +78,14 @@ struct cavs_treelstm {
   // leaf token instead of once per leaf (weighted by the token's label histogram).
   bool TokHead() const { return leaf_tok && FusedDh() && TokGrad(); }
   float* ptok = nullptr;        // [tokens, 8] class probabilities of the leaf tokens (TokHead)
+  // Level 1 by token (l1_tok): every child of a level-1 vertex is a leaf, and a leaf's h depends on its token
+  // only, so every product of that level with the recurrent weights is formed once per distinct token instead of
+  // once per vertex -- forward h_tok.U (PQT), backward the per-token sums of the parents' gate gradients over
+  // parent-child links (ZT), d(h) per token (dh_tok = ZT.U^T) and the level's share of dU (h_tok^T ZT).  Exact
+  // algebra (linearity of the products), like the per-token input projection.
+  bool l1_tok = false;
+  uint8_t *htok_bf = nullptr, *PQT = nullptr, *ZT = nullptr;   // [tokens, H], [tokens, 4H], [tokens, 4H] (GEMM element type)
+  float *dh_tok = nullptr, *link_scratch = nullptr;            // [tokens, H]; [link chunks, 4H]
   bool Dense() const { return cfg.vocab == 0; }
   bool Headless() const { return cfg.classes == 0; }
   int Cp() const { return (cfg.classes + 7) & ~7; }
@@ -101,6 +109,10 @@ struct cavs_treelstm {
             *seg_first_chunk = nullptr, *seg_tok = nullptr, *tok_slot = nullptr, *chunk_out = nullptr, *multi_seg = nullptr, *chunk_seg = nullptr;
     int n_multi = 0;
     int shared_chunk = -1;   // chunk whose partial row is the column sum over the internal vertices, or -1
+    // l1_tok: links (t, c) of level 1 as t * K + c, grouped by the child's token row and cut into chunks
+    int32_t *l_order = nullptr, *l_chunk_off = nullptr, *l_chunk_out = nullptr, *l_seg_first = nullptr, *l_multi = nullptr;
+    int n_l_chunks = 0, n_l_multi = 0;
+    bool l1 = false;         // this batch runs level 1 by token (it has a level 1)
   };
   Batch slot[2];
   int active = -1, staged = -1;
@@ -110,7 +122,7 @@ struct cavs_treelstm {
   cudaEvent_t copied[2] = {nullptr, nullptr}, slot_done[2] = {nullptr, nullptr};
   cudaEvent_t emb_ready = nullptr;   // recorded in backward once the embedding gradient is complete
   bool slot_used[2] = {false, false};
-  std::vector<int32_t> bucket, slot_of_token, leaf_count;
+  std::vector<int32_t> bucket, slot_of_token, leaf_count, link_bucket;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
   bool prof_on = false;
   std::vector<cudaEvent_t> ev_pool;
@@ -187,9 +199,14 @@ int CheckConfig(const cavs_treelstm_config* c) {
 size_t MaxSegments(const cavs_treelstm_config& c) { return c.vocab == 0 ? c.max_vertices : std::min<size_t>(c.max_vertices, c.vocab); }
 // A token's rows are cut into chunks of kEmbedChunk, separately for its leaves and its internal vertices.
 size_t MaxChunks(const cavs_treelstm_config& c) { return 2 * MaxSegments(c) + c.max_vertices / kEmbedChunk + 2; }
+// Parent-child links of one level, grouped by the child's token: one chunk list per token plus the overflow chunks.
+size_t MaxLinkChunks(const cavs_treelstm_config& c) {
+  return MaxSegments(c) + static_cast<size_t>(c.n_slots) * c.max_vertices / kEmbedChunk + 2;
+}
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
-  return (2 * c.n_slots + 7) * n + 4 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + 10 * MaxSegments(c) + 64;
+  return (2 * c.n_slots + 7) * n + 4 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + 10 * MaxSegments(c) + 64 +
+         c.n_slots * n + 2 * (MaxLinkChunks(c) + 1) + 2 * (MaxSegments(c) + 1);   // link lists (level 1 by token)
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -211,6 +228,8 @@ void InitModes(cavs_treelstm* e, const cavs_treelstm_config& cfg) {
   e->elt = e->bf16 ? 2 : 4;
   const char* v = std::getenv("CAVS_LEAF_BY_TOKEN");   // "0": keep one state row per leaf vertex
   e->leaf_tok = e->LeafTokEligible() && !(v != nullptr && v[0] == '0');
+  const char* v1 = std::getenv("CAVS_LEVEL1_BY_TOKEN");   // "0": level 1 runs per vertex like every other level
+  e->l1_tok = e->TokHead() && e->bf16 && !(v1 != nullptr && v1[0] == '0');
 }
 
 // Carves every device array out of the workspace; with base == nullptr it only sizes it.
@@ -237,6 +256,11 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->dOut = w.Take<float>(e->FusedDh() || e->Headless() ? 0 : N * H);
   e->dz8 = w.Take<float>(e->FusedDh() ? N * kHeadDzPitch : 0);
   e->ptok = w.Take<float>(e->TokHead() ? T * kHeadDzPitch : 0);
+  e->htok_bf = w.Take<uint8_t>(e->l1_tok ? T * H * elt : 0);
+  e->PQT = w.Take<uint8_t>(e->l1_tok ? T * 4 * H * elt : 0);
+  e->ZT = w.Take<uint8_t>(e->l1_tok ? T * 4 * H * elt : 0);
+  e->dh_tok = w.Take<float>(e->l1_tok ? T * H : 0);
+  e->link_scratch = w.Take<float>(e->l1_tok ? MaxLinkChunks(c) * 4 * H : 0);
   e->ds = w.Take<float>(L * H);
   e->dq = w.Take<float>(c.gemm_bf16 ? 0 : L * K * H);   // bf16 mode: the dq product is scattered by its own epilogue
   e->dX = w.Take<float>(T * E);
@@ -552,6 +576,55 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     for (int t = n_leaf; t < n; ++t) h_head_row[t - n_leaf] = t;
     for (int sidx = 0; sidx < n_seg; ++sidx) h_head_row[n - n_leaf + sidx] = e->cfg.max_vertices + sidx;
   }
+  bt.l1 = e->l1_tok && sch.n_levels() >= 2;
+  bt.n_l_chunks = bt.n_l_multi = 0;
+  if (bt.l1) {
+    // Links of level 1 grouped by the token row of the child (stable counting sort: within a token, links stay in
+    // (vertex, slot) order), cut into chunks of kEmbedChunk; and the leaves below level 1 marked in `order`: their
+    // d(h) arrives per token, the h half of their mailbox rows is never written.
+    const int off1 = bt.level_off[1], off2 = bt.level_off[2];
+    e->link_bucket.assign(static_cast<size_t>(n_seg) + 1, 0);
+    for (int t = off1; t < off2; ++t)
+      for (int c = 0; c < K; ++c) {
+        const int ch = h_child[static_cast<size_t>(c) * nt + t];
+        if (ch >= 0) ++e->link_bucket[h_slot[ch] + 1];
+      }
+    int n_lc = 0, n_lm = 0;
+    for (int sidx = 0; sidx < n_seg; ++sidx) n_lc += (e->link_bucket[sidx + 1] + kEmbedChunk - 1) / kEmbedChunk;
+    int32_t* h_l_order = view(static_cast<size_t>(K) * (off2 - off1), &bt.l_order);
+    int32_t* h_l_chunk_off = view(static_cast<size_t>(n_lc) + 1, &bt.l_chunk_off);
+    int32_t* h_l_chunk_out = view(static_cast<size_t>(n_lc) + 1, &bt.l_chunk_out);
+    int32_t* h_l_seg_first = view(static_cast<size_t>(n_seg) + 1, &bt.l_seg_first);
+    int32_t* h_l_multi = view(static_cast<size_t>(n_seg) + 1, &bt.l_multi);
+    CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
+    int ci = 0, pos = 0;
+    for (int sidx = 0; sidx < n_seg; ++sidx) {
+      const int cnt = e->link_bucket[sidx + 1];
+      const int chunks = (cnt + kEmbedChunk - 1) / kEmbedChunk;
+      h_l_seg_first[sidx] = ci;
+      if (chunks > 1) h_l_multi[n_lm++] = sidx;
+      for (int b = 0; b < chunks; ++b) {
+        h_l_chunk_out[ci] = chunks == 1 ? sidx : -1;
+        h_l_chunk_off[ci++] = pos + b * kEmbedChunk;
+      }
+      e->link_bucket[sidx + 1] = pos;   // becomes the running write position of token row sidx
+      pos += cnt;
+    }
+    h_l_seg_first[n_seg] = ci;
+    h_l_chunk_off[ci] = pos;
+    for (int t = off1; t < off2; ++t)
+      for (int c = 0; c < K; ++c) {
+        const int ch = h_child[static_cast<size_t>(c) * nt + t];
+        if (ch >= 0) h_l_order[e->link_bucket[h_slot[ch] + 1]++] = t * K + c;
+      }
+    bt.n_l_chunks = n_lc; bt.n_l_multi = n_lm;
+    const int n_leaf = bt.level_off[1];
+    // `order` holds every leaf, and the internal vertices too unless they all share one token
+    for (int i = 0, lim = (bt.shared_chunk >= 0 ? n_leaf : n); i < lim; ++i) {
+      const int t = h_order[i];
+      if (t < n_leaf && h_parent[t] >= off1 && h_parent[t] < off2) h_order[i] = t | kOrderNoDh;
+    }
+  }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
   // The device half is free once the last backward pass that read it has finished.
   (void)stream;
@@ -613,6 +686,22 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
                                B, bt.child, nullptr, n_tok, 0, n_tok, H, K, true, st, false)
                : LaunchCellFwd(e->state, e->gates, e->A, nullptr, nullptr, e->bf16, B, bt.child, bt.tok_slot, nt, off, rows, H, K,
                                true, st, false));
+      if (bt.l1) {
+        // h_tok.U_iou | h_tok.U_f, one row per distinct leaf token: everything level 1 needs from the recurrent weights
+        float* h_tok = e->state + static_cast<size_t>(e->cfg.max_vertices) * 2 * H;
+        if ((rc = LaunchCastRowsBf16(e->htok_bf, h_tok, n_tok, H, 2 * H, st))) return rc;
+        if ((rc = Gemm(e, e->PQT, 4 * H, pre, e->htok_bf, H, false, U_iou, 3 * H, false, n_tok, 3 * H, H, false, st))) return rc;
+        if ((rc = Gemm(e, e->PQT + static_cast<size_t>(3) * H * e->elt, 4 * H, pre, e->htok_bf, H, false, U_f, H, false, n_tok, H, H, false, st)))
+          return rc;
+      }
+      continue;
+    }
+    if (l == 1 && bt.l1) {
+      // no gather, no per-row products: the cell reads its children's per-token product rows
+      ChainHint(rows <= kChainSmallRows);
+      PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (4 + 4 * K + 3 + K) + 4.0 * (K + 2)) + 4), st,
+           LaunchCellFwd(e->state, e->gates, e->A, e->PQT, nullptr, e->bf16, B, bt.child_st, bt.tok_slot, nt, off, rows, H, K, false, st,
+                         true, e->cfg.max_vertices));
       continue;
     }
     // Chained launches: a kernel releases its successor early when that successor is a GEMM (one CTA per
@@ -728,6 +817,21 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
                        l == 0 ? bt.tok_slot : nullptr, l == 0 ? e->params + e->OffB() : nullptr,
                        e->leaf_tok ? bt.child_st : nullptr));
     if (l == 0) break;
+    if (l == 1 && bt.l1) {
+      // The children are leaves: what they receive is summed per token first (fixed order), and the two products
+      // with the transposed recurrent weights run once per token.  dh_tok joins the leaves' other gradients inside
+      // the per-token sums of the tail below.
+      ChainHint(false);
+      CAVS_CUDA(cudaMemsetAsync(e->ZT, 0, static_cast<size_t>(bt.n_seg) * 4 * H * e->elt, st));
+      PROF(e, kProfEmbedBwd, static_cast<double>(rows) * K * (elt * 4 * H + 4) + static_cast<double>(bt.n_l_chunks) * 16.0 * H, st,
+           LaunchLinkSumChunks(e->link_scratch, e->ZT, e->bf16, bt.l_chunk_out, e->dA, e->ZF, bt.l_order, bt.l_chunk_off, bt.n_l_chunks,
+                               H, K, st));
+      if ((rc = LaunchSegmentedRowSumFinal(e->ZT, e->bf16, e->link_scratch, bt.l_seg_first, bt.l_multi, bt.n_l_multi, 4 * H, st))) return rc;
+      if ((rc = Gemm(e, e->dh_tok, H, 0, e->ZT, 4 * H, false, U_iou, 3 * H, true, bt.n_seg, H, 3 * H, false, st))) return rc;
+      if ((rc = Gemm(e, e->dh_tok, H, 1, e->ZT + static_cast<size_t>(3) * H * e->elt, 4 * H, false, U_f, H, true, bt.n_seg, H, H, false, st)))
+        return rc;
+      continue;
+    }
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
@@ -781,7 +885,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
            LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
                                  bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
                                  fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), n_leaf, H, st,
-                                 e->TokHead() ? e->ptok : nullptr, bt.label, 1.0f / static_cast<float>(bt.loss_rows)));
+                                 e->TokHead() ? e->ptok : nullptr, bt.label, 1.0f / static_cast<float>(bt.loss_rows),
+                                 bt.l1 ? e->dh_tok : nullptr, bt.seg_first_chunk));
       if (bt.shared_chunk >= 0) {
         // the internal vertices' column sums become the partial row of their token's extra chunk
         if ((rc = LaunchColumnSum(e->emb_scratch + static_cast<size_t>(bt.shared_chunk) * 4 * H, e->dB_tmp, false, 4 * H,
@@ -801,7 +906,9 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
     if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
   }
-  const int off1 = bt.n_levels > 1 ? bt.level_off[1] : n;   // first internal row
+  // first row of the per-vertex weight-gradient products: the first internal row, or with level 1 by token the
+  // first row of level 2
+  const int off1 = bt.l1 ? (bt.n_levels > 2 ? bt.level_off[2] : n) : (bt.n_levels > 1 ? bt.level_off[1] : n);
   const int n_int = n - off1;
   float* dU = g + e->OffU();
   if (n_int > 0) {
@@ -813,6 +920,13 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     if ((rc = Gemm(e, dU + static_cast<size_t>(3) * H * H, H, 0, HK1, H, true, ZF1, H, false, H, H, n_int * K, true, st))) return rc;
   } else {
     CAVS_CUDA(cudaMemsetAsync(dU, 0, static_cast<size_t>(4) * H * H * sizeof(float), st));
+  }
+  if (bt.l1) {
+    // level 1's share: sum over links of h_child^T dz = sum over tokens of h_tok^T (the token's link sums)
+    if ((rc = Gemm(e, dU, 3 * H, 1, e->htok_bf, H, true, e->ZT, 4 * H, false, H, 3 * H, bt.n_seg, true, st))) return rc;
+    if ((rc = Gemm(e, dU + static_cast<size_t>(3) * H * H, H, 1, e->htok_bf, H, true, e->ZT + static_cast<size_t>(3) * H * e->elt, 4 * H, false,
+                   H, H, bt.n_seg, true, st)))
+      return rc;
   }
   // Bias gradient: column sums of dA, gate order i,o,u,f -> bias order i,f,u,o.
   if (tok_grad) {

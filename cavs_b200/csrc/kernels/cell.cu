@@ -159,7 +159,8 @@ template <typename TP, int K, int V, bool kLeaf>
 __global__ void __launch_bounds__(kThreads)
 CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
         const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child,
-        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H, int chain_early, int store_leaf_gates) {
+        const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H, int chain_early, int store_leaf_gates,
+        int tok_base) {
   ChainRelease(chain_early);
   ChainAcquire();
   constexpr bool kFast = sizeof(TP) == 2;
@@ -178,8 +179,24 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
     const Vec<V> bi = LoadF<V>(bias + j), bf = LoadF<V>(bias + H + j), bu = LoadF<V>(bias + 2 * H + j), bo = LoadF<V>(bias + 3 * H + j);
     Vec<V> pi = Zero<V>(), po = Zero<V>(), pu = Zero<V>();
     if (!kLeaf) {
-      const TP* p = P + static_cast<size_t>(b) * 3 * H + j;
-      pi = LoadF<V>(p); po = LoadF<V>(p + H); pu = LoadF<V>(p + 2 * H);
+      if (tok_base >= 0) {
+        // A level whose children are all leaves with per-token states (child index = tok_base + token row): the
+        // products h_child.U depend on the child's token only, so P holds them once per token, [tokens, 4H] =
+        // h_tok.U_iou | h_tok.U_f, and the row's pre-activation is the sum over its children.
+#pragma unroll
+        for (int c = 0; c < K; ++c) {
+          const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+          if (ch >= 0) {
+            const TP* p = P + static_cast<size_t>(ch - tok_base) * 4 * H + j;
+            const Vec<V> xi = LoadF<V>(p), xo = LoadF<V>(p + H), xu = LoadF<V>(p + 2 * H);
+#pragma unroll
+            for (int e = 0; e < V; ++e) { pi.v[e] += xi.v[e]; po.v[e] += xo.v[e]; pu.v[e] += xu.v[e]; }
+          }
+        }
+      } else {
+        const TP* p = P + static_cast<size_t>(b) * 3 * H + j;
+        pi = LoadF<V>(p); po = LoadF<V>(p + H); pu = LoadF<V>(p + 2 * H);
+      }
     }
     Vec<V> gi, go, gu, cc, hh;
 #pragma unroll
@@ -195,8 +212,9 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
     if (!kLeaf) {
 #pragma unroll
       for (int c = 0; c < K; ++c) {
-        const Vec<V> q = LoadF<V>(Q + (static_cast<size_t>(b) * K + c) * H + j);
         const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+        const Vec<V> q = tok_base >= 0 ? (ch >= 0 ? LoadF<V>(P + static_cast<size_t>(ch - tok_base) * 4 * H + 3 * H + j) : Zero<V>())
+                                       : LoadF<V>(Q + (static_cast<size_t>(b) * K + c) * H + j);
         const Vec<V> cch = ch >= 0 ? LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j) : Zero<V>();
         Vec<V> gf;
 #pragma unroll
@@ -429,6 +447,11 @@ struct LeafGradArgs {
   const float* ptok;         // [tokens, kHeadDzPitch] class probabilities per token, or NULL (then dz / dOut)
   const int32_t* label;      // [n_total]
   float inv_rows;
+  // Leaves whose parents sit on a level that hands d(h) down per token instead of per leaf: their entries in
+  // `order` carry kOrderNoDh (the h half of their mailbox row is not written), and the token's share dh_tok[token row]
+  // ([tokens, H]) is added once, by the token's first chunk (seg_first_chunk[token row]).
+  const float* dh_tok;
+  const int32_t* seg_first_chunk;
 };
 
 // kMode: where a leaf's d(h) comes from -- 0 stored d(h) rows, 1 stored d(logits) rows, 2 the token's class
@@ -448,7 +471,7 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
   __syncthreads();
   float* mine = partial + static_cast<size_t>(chunk) * width;
   T* final_row = direct >= 0 ? out + static_cast<size_t>(direct) * width : nullptr;
-  if (rows_sm[0] >= lg.n_leaf) {
+  if ((rows_sm[0] & (kOrderNoDh - 1)) >= lg.n_leaf) {
     // internal vertices: sum the stored rows
     for (int e = threadIdx.x * V; e < width; e += kThreads * V) {
       Vec<V> acc[4];
@@ -528,8 +551,9 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
       for (int u = 0; u < kGroup; ++u) {
         // A scheduled leaf always has a parent (a single-vertex sample is never scheduled), so its mailbox row is
         // valid and the loads do not wait for a parent lookup.
-        const size_t t = static_cast<size_t>(rows_sm[r0 + u < cnt ? r0 + u : r0]);
-        mh[u] = LoadF<V>(lg.mailbox + t * 2 * H + j);
+        const int32_t entry = rows_sm[r0 + u < cnt ? r0 + u : r0];
+        const size_t t = static_cast<size_t>(entry & (kOrderNoDh - 1));
+        mh[u] = (entry & kOrderNoDh) ? Zero<V>() : LoadF<V>(lg.mailbox + t * 2 * H + j);
         mc[u] = LoadF<V>(lg.mailbox + t * 2 * H + H + j);
         if (by_token) {
           yl[u] = __ldg(lg.label + t);
@@ -572,12 +596,78 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
         }
       }
     }
+    if (lg.dh_tok != nullptr && __ldg(lg.seg_first_chunk + lg.chunk_seg[chunk]) == chunk) {
+      // d(h) handed down per token: one more term of the same linear map, with no d(c) of its own
+      const Vec<V> dt = LoadF<V>(lg.dh_tok + static_cast<size_t>(lg.chunk_seg[chunk]) * H + j);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float dh = dt.v[e];
+        const float dc = (dh * go.v[e]) * (1.0f - th.v[e] * th.v[e]);
+        si.v[e] += (dc * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
+        so.v[e] += (dh * th.v[e]) * go.v[e] * (1.0f - go.v[e]);
+        su.v[e] += (dc * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
+      }
+    }
     const Vec<V> zero = Zero<V>();
     Store<V>(mine + j, si); Store<V>(mine + H + j, so); Store<V>(mine + 2 * H + j, su); Store<V>(mine + 3 * H + j, zero);
     if (final_row) {
       Store<V>(final_row + j, si); Store<V>(final_row + H + j, so); Store<V>(final_row + 2 * H + j, su);
       Store<V>(final_row + 3 * H + j, zero);
     }
+  }
+}
+
+// Per-token sums over parent-child links.  Link (t, c) = entry t * K + c of `order` contributes the row
+// [ dA[t, 0:3H] | ZF[t * K + c, 0:H] ]: the parent's d(pre-activation) of i, o, u and of the forget gate of that child.
+// A chunk is at most kEmbedChunk links of one token (the token of the CHILD), summed in list order into
+// partial[chunk, 4H] (fp32); a chunk that is its token's only one also writes the final row out[chunk_out, 4H].
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+LinkSumChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* __restrict__ chunk_out, const T* __restrict__ dA,
+              const T* __restrict__ ZF, const int32_t* __restrict__ order, const int32_t* __restrict__ chunk_off, int H, int K) {
+  __shared__ int32_t link_sm[kEmbedChunk];
+  __shared__ int32_t row_sm[kEmbedChunk];
+  constexpr int V = 4;
+  const int chunk = blockIdx.x, width = 4 * H;
+  const int begin = chunk_off[chunk], cnt = chunk_off[chunk + 1] - begin;
+  if (cnt == 0) return;
+  for (int r = threadIdx.x; r < cnt; r += kThreads) {
+    const int32_t link = order[begin + r];
+    link_sm[r] = link;
+    row_sm[r] = link / K;
+  }
+  __syncthreads();
+  const int direct = chunk_out[chunk];
+  float* mine = partial + static_cast<size_t>(chunk) * width;
+  T* final_row = direct >= 0 ? out + static_cast<size_t>(direct) * width : nullptr;
+  for (int e = threadIdx.x * V; e < width; e += kThreads * V) {
+    const bool own = e >= 3 * H;                       // the forget-gate block comes from the link's own ZF row
+    const T* base = own ? ZF + (e - 3 * H) : dA + e;
+    const size_t pitch = own ? H : width;
+    const int32_t* idx = own ? link_sm : row_sm;
+    Vec<V> acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = Zero<V>();
+    int r = 0;
+    for (; r + 4 <= cnt; r += 4) {
+      Vec<V> t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) t[u] = LoadF<V>(base + static_cast<size_t>(idx[r + u]) * pitch);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[u].v[v] += t[u].v[v];
+    }
+    for (int u = 0; r < cnt; ++r, ++u) {
+      const Vec<V> t = LoadF<V>(base + static_cast<size_t>(idx[r]) * pitch);
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[u].v[v] += t.v[v];
+    }
+    Vec<V> sum;
+#pragma unroll
+    for (int v = 0; v < V; ++v) sum.v[v] = (acc[0].v[v] + acc[1].v[v]) + (acc[2].v[v] + acc[3].v[v]);
+    Store<V>(mine + e, sum);
+    if (final_row) Store<V>(final_row + e, sum);
   }
 }
 
@@ -629,7 +719,8 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
-                  bool store_leaf_gates) {
+                  bool store_leaf_gates, int tok_base) {
+  CAVS_REQUIRE(tok_base < 0 || (!leaf && P != nullptr), CAVS_ERR_BAD_ARG, "treelstm_cell_fwd: per-token products apply to an internal level");
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
@@ -638,12 +729,12 @@ int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const
     if (preact_bf16) {
       using TP = __nv_bfloat16;
       auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
-      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
-      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
+      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
+      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
     } else {
       auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
-      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
-      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0);
+      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
+      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
@@ -695,13 +786,15 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
-                          int n_leaf, int H, cudaStream_t st, const float* ptok, const int32_t* label, float inv_rows) {
+                          int n_leaf, int H, cudaStream_t st, const float* ptok, const int32_t* label, float inv_rows,
+                          const float* dh_tok, const int32_t* seg_first_chunk) {
   CAVS_REQUIRE(n_chunks >= 0 && H > 0 && H % 4 == 0, CAVS_ERR_BAD_ARG, "token_grad_chunks: hidden must be a positive multiple of 4");
+  CAVS_REQUIRE(dh_tok == nullptr || seg_first_chunk != nullptr, CAVS_ERR_BAD_ARG, "token_grad_chunks: per-token d(h) needs the tokens' first chunks");
   if (n_chunks == 0) return CAVS_OK;
   CAVS_REQUIRE(partial && out && chunk_out && dA && A && order && chunk_off && chunk_seg && mailbox && bias &&
                    ((dz || ptok) ? (Wc && C >= 1 && C <= kHeadDzPitch && (!ptok || label)) : dOut != nullptr),
                CAVS_ERR_BAD_ARG, "token_grad_chunks: null pointer");
-  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H, ptok, label, inv_rows};
+  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H, ptok, label, inv_rows, dh_tok, seg_first_chunk};
 #define TOKEN_GRAD(TT, MODE)                                                                                              \
   TokenGradChunks<TT, MODE><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<TT*>(out), chunk_out, static_cast<const TT*>(dA), \
                                                            static_cast<const TT*>(A), order, chunk_off, lg)
@@ -713,6 +806,22 @@ int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* c
   }
 #undef TOKEN_GRAD
   CAVS_LAUNCH_CHECK("token_grad_chunks");
+  return CAVS_OK;
+}
+
+int LaunchLinkSumChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* ZF,
+                        const int32_t* order, const int32_t* chunk_off, int n_chunks, int H, int K, cudaStream_t st) {
+  CAVS_REQUIRE(n_chunks >= 0 && H > 0 && H % 4 == 0 && K >= 1 && K <= 4, CAVS_ERR_BAD_ARG, "link_sum_chunks: bad shape");
+  if (n_chunks == 0) return CAVS_OK;
+  CAVS_REQUIRE(partial && out && chunk_out && dA && ZF && order && chunk_off, CAVS_ERR_BAD_ARG, "link_sum_chunks: null pointer");
+  if (bf16)
+    LinkSumChunks<__nv_bfloat16><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<__nv_bfloat16*>(out), chunk_out,
+                                                                static_cast<const __nv_bfloat16*>(dA),
+                                                                static_cast<const __nv_bfloat16*>(ZF), order, chunk_off, H, K);
+  else
+    LinkSumChunks<float><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<float*>(out), chunk_out, static_cast<const float*>(dA),
+                                                        static_cast<const float*>(ZF), order, chunk_off, H, K);
+  CAVS_LAUNCH_CHECK("link_sum_chunks");
   return CAVS_OK;
 }
 

@@ -21,7 +21,9 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 // a_row (optional): [n_total] row of A for each vertex (A then holds one row per distinct token).
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
-                  bool store_leaf_gates = true);
+                  bool store_leaf_gates = true, int tok_base = -1);
+// tok_base >= 0 (internal level whose children are all leaves with per-token states): `child` holds state rows
+// tok_base + token row, P is [tokens, 4H] = h_tok.U_iou | h_tok.U_f, Q is unused; the level's own P / Q are never formed.
 // store_leaf_gates = false (leaf levels): the gates are not saved; the backward pass must then be given A, a_row and
 // bias and recomputes them (a leaf's gates depend on its input-projection row only).
 // dB_part (optional): [CellBwdMaxGrid(), 4H] fp32, zeroed by the caller before the first level of a
@@ -50,7 +52,16 @@ int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* c
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
                           int n_leaf, int H, cudaStream_t st, const float* ptok = nullptr, const int32_t* label = nullptr,
-                          float inv_rows = 0.0f);
+                          float inv_rows = 0.0f, const float* dh_tok = nullptr, const int32_t* seg_first_chunk = nullptr);
+// An entry of `order` with this bit set is a leaf whose mailbox row holds no d(h) (its parent's level hands d(h) down
+// per token): only the c half of the row is read.  dh_tok [tokens, H] (optional) is that per-token d(h), added once per
+// token by the chunk seg_first_chunk[token row].
+constexpr int32_t kOrderNoDh = 1 << 30;
+// Per-token sums over parent-child links of a level whose children are all leaves: link t * K + c contributes
+// [ dA[t, 0:3H] | ZF[t * K + c, :] ]; chunks of <= 256 links of one child token; partial [n_chunks, 4H] fp32, and
+// out[chunk_out[chunk], 4H] for single-chunk tokens (the rest is folded by LaunchSegmentedRowSumFinal).
+int LaunchLinkSumChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* ZF,
+                        const int32_t* order, const int32_t* chunk_off, int n_chunks, int H, int K, cudaStream_t st);
 // ptok / label / inv_rows (optional, instead of dz): a leaf's d(logits) is (ptok[token] - onehot(label)) * inv_rows.
 // loss[t] = -log ptok[tok_slot[t]][label[t]] for the leaves t < n_leaf (0 without a label): fills in what the loss
 // head's token rows do not write.
