@@ -885,7 +885,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
            LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
                                  bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
                                  fdh ? e->dz8 : nullptr, e->params + e->OffWc(), C, e->params + e->OffB(), n_leaf, H, st,
-                                 e->TokHead() ? e->ptok : nullptr, bt.label, 1.0f / static_cast<float>(bt.loss_rows),
+                                 e->TokHead() ? e->ptok : nullptr, bt.tok_hist, 1.0f / static_cast<float>(bt.loss_rows),
                                  bt.l1 ? e->dh_tok : nullptr, bt.seg_first_chunk));
       if (bt.shared_chunk >= 0) {
         // the internal vertices' column sums become the partial row of their token's extra chunk

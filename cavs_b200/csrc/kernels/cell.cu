@@ -108,6 +108,18 @@ __device__ __forceinline__ void Store(__half* p, const Vec<V>& r) {
   }
 }
 
+// Store of a value that is next read much later (the saved gates: written forward, read backward): marked
+// evict-first so that it does not push the rows other CTAs re-read (hot token rows, the next level's children)
+// out of L2.
+template <int V, typename T>
+__device__ __forceinline__ void StoreStream(T* p, const Vec<V>& r) { Store<V>(p, r); }
+template <>
+__device__ __forceinline__ void StoreStream<4, __half>(__half* p, const Vec<4>& r) {
+  __half2 a = __floats2half2_rn(r.v[0], r.v[1]), b = __floats2half2_rn(r.v[2], r.v[3]);
+  uint2 u; u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+  __stcs(reinterpret_cast<uint2*>(p), u);
+}
+
 // Saved gates (values in [-1, 1]) are kept in fp16 in the bf16-GEMM configurations: 11 mantissa
 // bits cost ~5e-4 relative in the backward products and halve the largest forward-to-backward
 // tensor; the fp32 configurations keep fp32 gates.
@@ -222,14 +234,14 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
           gf.v[e] = SigmoidT<kFast>((af.v[e] + q.v[e]) + bf.v[e]);
           cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
         }
-        Store<V>(g + (3 + c) * H, gf);
+        StoreStream<V>(g + (3 + c) * H, gf);
       }
     }
 #pragma unroll
     for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * TanhT<kFast>(cc.v[e]);
     // A leaf's gates are a function of its input-projection row alone: when the backward pass recomputes them
     // (LaunchCellBwd with A), they are not stored.
-    if (!kLeaf || store_leaf_gates) { Store<V>(g, gi); Store<V>(g + H, go); Store<V>(g + 2 * H, gu); }
+    if (!kLeaf || store_leaf_gates) { StoreStream<V>(g, gi); StoreStream<V>(g + H, go); StoreStream<V>(g + 2 * H, gu); }
     Store<V>(state + t * 2 * H + j, hh);
     Store<V>(state + t * 2 * H + H + j, cc);
   }
@@ -445,7 +457,7 @@ struct LeafGradArgs {
   const int32_t* chunk_seg;  // [n_chunks] token row of A for each chunk
   int C, n_leaf, H;
   const float* ptok;         // [tokens, kHeadDzPitch] class probabilities per token, or NULL (then dz / dOut)
-  const int32_t* label;      // [n_total]
+  const int32_t* hist;       // [tokens, kHeadDzPitch] with ptok: how many of the token's leaves carry each label
   float inv_rows;
   // Leaves whose parents sit on a level that hands d(h) down per token instead of per leaf: their entries in
   // `order` carry kOrderNoDh (the h half of their mailbox row is not written), and the token's share dh_tok[token row]
@@ -455,7 +467,7 @@ struct LeafGradArgs {
 };
 
 // kMode: where a leaf's d(h) comes from -- 0 stored d(h) rows, 1 stored d(logits) rows, 2 the token's class
-// probabilities and the leaf's label (one instantiation each, so no path carries the other paths' registers).
+// probabilities and label histogram (one instantiation each, so no path carries the other paths' registers).
 template <typename T, int kMode>
 __global__ void __launch_bounds__(kThreads)
 TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* __restrict__ chunk_out, const T* __restrict__ dA,
@@ -506,6 +518,89 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
   }
   // leaves of one token
   const T* a = A + static_cast<size_t>(lg.chunk_seg[chunk]) * width;
+  if constexpr (kMode == 2) {
+    // All leaves of a token share their forward values, so the map from (d(h), d(c)) to the gate gradients is ONE linear
+    // map per token: the rows' d(h) and d(c) are summed first (fixed order) and the map is applied once.  The loss
+    // head's share of the summed d(h) follows from the token's class probabilities and label histogram,
+    //   sum over labelled leaves of (p - onehot(y)) . Wc / rows = (sum_c (n_lab p[c] - hist[c]) Wc[c]) / rows,
+    // and enters, like the d(h) handed down per token, through the token's first chunk.
+    const int seg = lg.chunk_seg[chunk];
+    const bool first = __ldg(lg.seg_first_chunk + seg) == chunk;
+    for (int j = threadIdx.x * V; j < H; j += kThreads * V) {
+      Vec<V> sh[2], sc[2];
+      sh[0] = sh[1] = sc[0] = sc[1] = Zero<V>();
+      constexpr int kRows = 4;
+      for (int r0 = 0; r0 < cnt; r0 += kRows) {
+        Vec<V> mh[kRows], mc[kRows];
+#pragma unroll
+        for (int u = 0; u < kRows; ++u) {
+          if (r0 + u < cnt) {
+            const int32_t entry = rows_sm[r0 + u];
+            const float* m = lg.mailbox + static_cast<size_t>(entry & (kOrderNoDh - 1)) * 2 * H + j;
+            mh[u] = (entry & kOrderNoDh) ? Zero<V>() : LoadF<V>(m);
+            mc[u] = LoadF<V>(m + H);
+          } else {
+            mh[u] = mc[u] = Zero<V>();
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kRows; ++u)
+#pragma unroll
+          for (int e = 0; e < V; ++e) { sh[u & 1].v[e] += mh[u].v[e]; sc[u & 1].v[e] += mc[u].v[e]; }
+      }
+      Vec<V> dh, dcm;
+#pragma unroll
+      for (int e = 0; e < V; ++e) { dh.v[e] = sh[0].v[e] + sh[1].v[e]; dcm.v[e] = sc[0].v[e] + sc[1].v[e]; }
+      if (first) {
+        const float4 p0 = __ldg(reinterpret_cast<const float4*>(lg.ptok + static_cast<size_t>(seg) * kHeadDzPitch));
+        const float4 p1 = __ldg(reinterpret_cast<const float4*>(lg.ptok + static_cast<size_t>(seg) * kHeadDzPitch) + 1);
+        const float pk[kHeadDzPitch] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        // the histogram lives in the index tables, which are only 4-byte aligned: scalar loads
+        int hk[kHeadDzPitch];
+        int n_lab = 0;
+#pragma unroll
+        for (int c = 0; c < kHeadDzPitch; ++c) { hk[c] = __ldg(lg.hist + static_cast<size_t>(seg) * kHeadDzPitch + c); n_lab += hk[c]; }
+        Vec<V> head = Zero<V>();
+#pragma unroll
+        for (int c = 0; c < kHeadDzPitch; ++c) {
+          if (c < lg.C) {
+            const Vec<V> w = LoadF<V>(lg.Wc + static_cast<size_t>(c) * H + j);
+            const float coef = static_cast<float>(n_lab) * pk[c] - static_cast<float>(hk[c]);
+#pragma unroll
+            for (int e = 0; e < V; ++e) head.v[e] = fmaf(coef, w.v[e], head.v[e]);
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) dh.v[e] += head.v[e] * lg.inv_rows;
+        if (lg.dh_tok != nullptr) {
+          const Vec<V> dt = LoadF<V>(lg.dh_tok + static_cast<size_t>(seg) * H + j);
+#pragma unroll
+          for (int e = 0; e < V; ++e) dh.v[e] += dt.v[e];
+        }
+      }
+      const Vec<V> ai = LoadF<V>(a + j), ao = LoadF<V>(a + H + j), au = LoadF<V>(a + 2 * H + j);
+      const Vec<V> bi = LoadF<V>(lg.bias + j), bu = LoadF<V>(lg.bias + 2 * H + j), bo = LoadF<V>(lg.bias + 3 * H + j);
+      Vec<V> si, so, su;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float gi = SigmoidT<kFast>((ai.v[e] + 0.0f) + bi.v[e]);
+        const float go = SigmoidT<kFast>((ao.v[e] + 0.0f) + bo.v[e]);
+        const float gu = TanhT<kFast>((au.v[e] + 0.0f) + bu.v[e]);
+        const float th = TanhT<kFast>(gi * gu);
+        const float dc = dcm.v[e] + (dh.v[e] * go) * (1.0f - th * th);
+        si.v[e] = (dc * gu) * gi * (1.0f - gi);
+        so.v[e] = (dh.v[e] * th) * go * (1.0f - go);
+        su.v[e] = (dc * gi) * (1.0f - gu * gu);
+      }
+      const Vec<V> zero = Zero<V>();
+      Store<V>(mine + j, si); Store<V>(mine + H + j, so); Store<V>(mine + 2 * H + j, su); Store<V>(mine + 3 * H + j, zero);
+      if (final_row) {
+        Store<V>(final_row + j, si); Store<V>(final_row + H + j, so); Store<V>(final_row + 2 * H + j, su);
+        Store<V>(final_row + 3 * H + j, zero);
+      }
+    }
+    return;
+  }
   for (int j = threadIdx.x * V; j < H; j += kThreads * V) {
     const Vec<V> ai = LoadF<V>(a + j), ao = LoadF<V>(a + H + j), au = LoadF<V>(a + 2 * H + j);
     const Vec<V> bi = LoadF<V>(lg.bias + j), bu = LoadF<V>(lg.bias + 2 * H + j), bo = LoadF<V>(lg.bias + 3 * H + j);
@@ -517,27 +612,12 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
       gu.v[e] = TanhT<kFast>((au.v[e] + 0.0f) + bu.v[e]);
       th.v[e] = TanhT<kFast>(gi.v[e] * gu.v[e]);
     }
-    constexpr bool by_token = kMode == 2;   // d(logits) of a leaf = (p[token] - onehot(label)) * inv_rows
+    // kMode 0 / 1: every leaf has its own d(h) row or d(logits) row, so the rows are mapped one by one.
     constexpr bool by_dz = kMode == 1;
-    float ptk[kHeadDzPitch];
-    if (by_token) {
-      const float4 p0 = __ldg(reinterpret_cast<const float4*>(lg.ptok + static_cast<size_t>(lg.chunk_seg[chunk]) * kHeadDzPitch));
-      const float4 p1 = __ldg(reinterpret_cast<const float4*>(lg.ptok + static_cast<size_t>(lg.chunk_seg[chunk]) * kHeadDzPitch) + 1);
-      ptk[0] = p0.x; ptk[1] = p0.y; ptk[2] = p0.z; ptk[3] = p0.w; ptk[4] = p1.x; ptk[5] = p1.y; ptk[6] = p1.z; ptk[7] = p1.w;
-    }
     Vec<V> wc[kHeadDzPitch];
-    if (by_dz || by_token) {
+    if (by_dz) {
 #pragma unroll
       for (int c = 0; c < kHeadDzPitch; ++c) wc[c] = c < lg.C ? LoadF<V>(lg.Wc + static_cast<size_t>(c) * H + j) : Zero<V>();
-    }
-    // by_token: d(h) of a leaf = d(logits) . Wc = ((sum_c p[c] Wc[c]) - Wc[label]) * inv_rows; the first term is the
-    // same for every leaf of the token.
-    Vec<V> pw = Zero<V>();
-    if (by_token) {
-#pragma unroll
-      for (int c = 0; c < kHeadDzPitch; ++c)
-#pragma unroll
-        for (int e = 0; e < V; ++e) pw.v[e] = fmaf(ptk[c], wc[c].v[e], pw.v[e]);
     }
     Vec<V> si = Zero<V>(), so = Zero<V>(), su = Zero<V>();
     // Rows in pairs: the loads of a pair are issued together (a chunk of a frequent token is a long
@@ -546,7 +626,6 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
     for (int r0 = 0; r0 < cnt; r0 += kGroup) {
       Vec<V> mh[kGroup], mc[kGroup], dOutv[kGroup];
       float4 d0[kGroup], d1[kGroup];
-      int yl[kGroup];
 #pragma unroll
       for (int u = 0; u < kGroup; ++u) {
         // A scheduled leaf always has a parent (a single-vertex sample is never scheduled), so its mailbox row is
@@ -555,9 +634,7 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
         const size_t t = static_cast<size_t>(entry & (kOrderNoDh - 1));
         mh[u] = (entry & kOrderNoDh) ? Zero<V>() : LoadF<V>(lg.mailbox + t * 2 * H + j);
         mc[u] = LoadF<V>(lg.mailbox + t * 2 * H + H + j);
-        if (by_token) {
-          yl[u] = __ldg(lg.label + t);
-        } else if (by_dz) {
+        if (by_dz) {
           d0[u] = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch));
           d1[u] = __ldg(reinterpret_cast<const float4*>(lg.dz + t * kHeadDzPitch) + 1);
         } else {
@@ -567,17 +644,7 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
 #pragma unroll
       for (int u = 0; u < kGroup; ++u) {
         if (r0 + u >= cnt) break;
-        if (by_token) {
-          const int y = yl[u];
-          const bool labelled = y >= 0 && y < lg.C;   // labels outside [0, C) carry no loss, as in the token histogram
-          Vec<V> sel = Zero<V>();
-#pragma unroll
-          for (int c = 0; c < kHeadDzPitch; ++c)
-#pragma unroll
-            for (int e = 0; e < V; ++e) sel.v[e] += (c == y) ? wc[c].v[e] : 0.0f;
-#pragma unroll
-          for (int e = 0; e < V; ++e) dOutv[u].v[e] = labelled ? (pw.v[e] - sel.v[e]) * lg.inv_rows : 0.0f;
-        } else if (by_dz) {
+        if (by_dz) {
           const float dzr[kHeadDzPitch] = {d0[u].x, d0[u].y, d0[u].z, d0[u].w, d1[u].x, d1[u].y, d1[u].z, d1[u].w};
           dOutv[u] = Zero<V>();
 #pragma unroll
@@ -786,15 +853,16 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
 int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* A,
                           const int32_t* order, const int32_t* chunk_off, const int32_t* chunk_seg, int n_chunks,
                           const float* mailbox, const float* dOut, const float* dz, const float* Wc, int C, const float* bias,
-                          int n_leaf, int H, cudaStream_t st, const float* ptok, const int32_t* label, float inv_rows,
+                          int n_leaf, int H, cudaStream_t st, const float* ptok, const int32_t* hist, float inv_rows,
                           const float* dh_tok, const int32_t* seg_first_chunk) {
   CAVS_REQUIRE(n_chunks >= 0 && H > 0 && H % 4 == 0, CAVS_ERR_BAD_ARG, "token_grad_chunks: hidden must be a positive multiple of 4");
-  CAVS_REQUIRE(dh_tok == nullptr || seg_first_chunk != nullptr, CAVS_ERR_BAD_ARG, "token_grad_chunks: per-token d(h) needs the tokens' first chunks");
+  CAVS_REQUIRE((dh_tok == nullptr && ptok == nullptr) || seg_first_chunk != nullptr, CAVS_ERR_BAD_ARG,
+               "token_grad_chunks: per-token terms need the tokens' first chunks");
   if (n_chunks == 0) return CAVS_OK;
   CAVS_REQUIRE(partial && out && chunk_out && dA && A && order && chunk_off && chunk_seg && mailbox && bias &&
-                   ((dz || ptok) ? (Wc && C >= 1 && C <= kHeadDzPitch && (!ptok || label)) : dOut != nullptr),
+                   ((dz || ptok) ? (Wc && C >= 1 && C <= kHeadDzPitch && (!ptok || hist)) : dOut != nullptr),
                CAVS_ERR_BAD_ARG, "token_grad_chunks: null pointer");
-  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H, ptok, label, inv_rows, dh_tok, seg_first_chunk};
+  LeafGradArgs lg{mailbox, dOut, dz, Wc, bias, chunk_seg, C, n_leaf, H, ptok, hist, inv_rows, dh_tok, seg_first_chunk};
 #define TOKEN_GRAD(TT, MODE)                                                                                              \
   TokenGradChunks<TT, MODE><<<n_chunks, kThreads, 0, st>>>(partial, static_cast<TT*>(out), chunk_out, static_cast<const TT*>(dA), \
                                                            static_cast<const TT*>(A), order, chunk_off, lg)
