@@ -366,10 +366,19 @@ def main():
         # vertices, to which every per-level operand and output is proportional.
         internal_rows = int(scheds[0].n_total - scheds[0].level_off[1]) if scheds[0].n_levels > 1 else 0
         traffic = GEMM_DRAM_BYTES_PER_INTERNAL_ROW * internal_rows / max(d["launches_per_step"], 1)
+        # `achieved` counts the flops the GEMM launches EXECUTE.  The per-vertex formula of the reference's algorithm
+        # (every vertex multiplies its own input and its own children's states: 3 x (2 N E 4H + N_int (2 H 3H + 2 K H H)))
+        # is reported beside it: the engine executes fewer flops than that, because products that depend on a vertex only
+        # through its token (the input projection, the leaves' states and everything level 1 does with them) run once per
+        # distinct token.
+        H_, E_, K_ = wl["hidden"], wl["embed"], 2
+        n_v = int(scheds[0].n_scheduled)
+        formula = 3.0 * (2.0 * n_v * E_ * 4 * H_ + internal_rows * (2.0 * H_ * 3 * H_ + 2.0 * K_ * H_ * H_))
         roofline = dict(bound="tensor", kernel="GemmBf16Kernel (all gate / gradient GEMMs of a step)", achieved=d["tflops"],
                         peak=peaks["tflops"], unit="TFLOP/s", frac=d["frac"], traffic=traffic,
                         traffic_unit="DRAM bytes per launch (ncu on a 512-tree shard, scaled by internal vertices)",
-                        peak_source=peaks["source"])
+                        peak_source=peaks["source"], flops_executed_per_step=work_c[0] / prof_steps,
+                        flops_per_vertex_formula_per_step=formula)
     else:
         roofline = dict(bound="hbm", kernel=dominant, achieved=d["gbs"], peak=peaks["hbm_gbs"], unit="GB/s", frac=d["frac"],
                         traffic=None, peak_source=peaks["source"])
@@ -415,9 +424,9 @@ def main():
     trees = wl["batch"]
     value = trees * args.steps / (ms_dev * 1e-3)
     e2e_value = trees * args.steps / (ms_e2e * 1e-3)
-    # tables uploaded per step: child and child-state rows (2 slots each), parent, token, label, order, token row,
-    # state row, loss-head row (+ the per-token chunk / histogram tables, a few hundred KB)
-    h2d = int((2 * 2 + 7) * max_n * 4)
+    # tables uploaded per step (child and child-state rows, parent, token, label, order, token row, state row,
+    # loss-head rows, the per-token chunk / histogram tables, the link lists of level 1): counted by the engine
+    h2d = eng.upload_bytes()
     line = dict(metric="treelstm_train_trees_per_sec", value=value, unit="trees/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                 ms_per_step=ms_dev / args.steps, higher_is_better=True, scaling="strong", vs_baseline=None,
                 dtype="bf16" if wl["bf16"] else "f32", data="synthetic",

@@ -27,6 +27,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "abi_common.h"
@@ -116,6 +117,7 @@ struct cavs_treelstm {
   };
   Batch slot[2];
   int active = -1, staged = -1;
+  size_t last_upload_bytes = 0;   // size of the table blob the most recent load_batch sent to the device
   // The table upload runs on its own stream so it overlaps the step in flight: copied[s] marks the
   // upload into slot s, slot_done[s] the end of the last backward pass that read slot s.
   cudaStream_t copy_stream = nullptr;
@@ -146,6 +148,31 @@ struct cavs_treelstm {
 namespace {
 
 size_t Align(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+// Host-side packing of a batch's tables runs next to the device step of the previous batch; its loops over vertices
+// that touch disjoint outputs are split over a few threads (CAVS_HOST_THREADS, default min(cores, 4); short loops
+// stay on the caller's thread).
+int PackThreads() {
+  static const int n = [] {
+    const char* env = std::getenv("CAVS_HOST_THREADS");
+    if (env) return std::max(1, std::min(16, std::atoi(env)));
+    return static_cast<int>(std::max(1u, std::min(std::thread::hardware_concurrency(), 4u)));
+  }();
+  return n;
+}
+template <typename F>
+void ParallelRanges(int n, F fn) {
+  const int threads = std::max(1, std::min(PackThreads(), n / 32768));
+  if (threads <= 1) { fn(0, n); return; }
+  const int step = (n + threads - 1) / threads;
+  std::vector<std::thread> pool;
+  for (int w = 1; w < threads; ++w) {
+    const int b = w * step, e2 = std::min(n, b + step);
+    if (b < e2) pool.emplace_back([=] { fn(b, e2); });
+  }
+  fn(0, std::min(n, step));
+  for (auto& th : pool) th.join();
+}
 
 struct Carver {
   uint8_t* base;
@@ -461,16 +488,23 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   int32_t* h_slot = view(nt, &bt.tok_slot);
   int32_t* h_child_st = e->leaf_tok ? view(static_cast<size_t>(K) * nt, &bt.child_st) : nullptr;
   int32_t* h_state_row = e->leaf_tok ? view(nt, &bt.state_row) : nullptr;
-  std::memcpy(h_child, sch.child_t().data(), sizeof(int32_t) * K * nt);
-  std::memcpy(h_parent, sch.parent_t().data(), sizeof(int32_t) * nt);
   const int32_t* t2j = sch.t2j().data();
   const int V = e->cfg.vocab;
-  // Pull (op_impl_graphop.cu:214-254) and the label permutation FunctionPopRet implies
-  // (:275-327) are folded into this host-side reorder to tensor-id order.
-  for (int t = 0; t < n; ++t) {
-    const int id = tok_job ? tok_job[t2j[t]] : 0;
-    h_tok[t] = (id < 0 || id >= V) ? 0 : id;
-    h_label[t] = label_job ? label_job[t2j[t]] : -1;
+  {
+    const int32_t* src_child = sch.child_t().data();
+    const int32_t* src_parent = sch.parent_t().data();
+    // Pull (op_impl_graphop.cu:214-254) and the label permutation FunctionPopRet implies
+    // (:275-327) are folded into this host-side reorder to tensor-id order.
+    ParallelRanges(nt, [=](int b0, int b1) {
+      for (int c = 0; c < K; ++c)
+        std::memcpy(h_child + static_cast<size_t>(c) * nt + b0, src_child + static_cast<size_t>(c) * nt + b0, sizeof(int32_t) * (b1 - b0));
+      std::memcpy(h_parent + b0, src_parent + b0, sizeof(int32_t) * (b1 - b0));
+      for (int t = b0; t < std::min(b1, n); ++t) {
+        const int id = tok_job ? tok_job[t2j[t]] : 0;
+        h_tok[t] = (id < 0 || id >= V) ? 0 : id;
+        h_label[t] = label_job ? label_job[t2j[t]] : -1;
+      }
+    });
   }
   int n_seg = 0, n_chunks = 0;
   if (e->Dense()) {
@@ -547,20 +581,24 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     h_seg_first[si] = ci;
     h_chunk_off[ci] = n_listed;
     bt.n_multi = n_multi;
-    for (int t = 0; t < n; ++t) {
-      if (t < n_listed) h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
-      h_slot[t] = e->slot_of_token[h_tok[t]];
+    for (int t = 0; t < n_listed; ++t) h_order[e->bucket[h_tok[t]]++] = t;   // bucket[v] advances to bucket end
+    {
+      const int32_t* slot_of = e->slot_of_token.data();
+      ParallelRanges(n, [=](int b0, int b1) { for (int t = b0; t < b1; ++t) h_slot[t] = slot_of[h_tok[t]]; });
     }
   }
   if (e->leaf_tok) {
     // State rows: a leaf (level 0) lives in its token's row behind the vertex rows, every other vertex in its own.
     const int n_leaf = sch.n_levels() > 0 ? bt.level_off[1] : 0;
     const int base = e->cfg.max_vertices;
-    for (int t = 0; t < nt; ++t) h_state_row[t] = t < n_leaf ? base + h_slot[t] : t;
-    for (size_t i = 0; i < static_cast<size_t>(K) * nt; ++i) {
-      const int ch = h_child[i];
-      h_child_st[i] = ch >= 0 ? h_state_row[ch] : ch;
-    }
+    ParallelRanges(nt, [=](int b0, int b1) { for (int t = b0; t < b1; ++t) h_state_row[t] = t < n_leaf ? base + h_slot[t] : t; });
+    ParallelRanges(nt, [=](int b0, int b1) {
+      for (int c = 0; c < K; ++c)
+        for (size_t i = static_cast<size_t>(c) * nt + b0, end = static_cast<size_t>(c) * nt + b1; i < end; ++i) {
+          const int ch = h_child[i];
+          h_child_st[i] = ch >= 0 ? h_state_row[ch] : ch;
+        }
+    });
   }
   if (e->TokHead()) {
     // Loss rows: the internal vertices in tensor-id order, then one row per distinct token standing for its leaves.
@@ -620,10 +658,12 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     bt.n_l_chunks = n_lc; bt.n_l_multi = n_lm;
     const int n_leaf = bt.level_off[1];
     // `order` holds every leaf, and the internal vertices too unless they all share one token
-    for (int i = 0, lim = (bt.shared_chunk >= 0 ? n_leaf : n); i < lim; ++i) {
-      const int t = h_order[i];
-      if (t < n_leaf && h_parent[t] >= off1 && h_parent[t] < off2) h_order[i] = t | kOrderNoDh;
-    }
+    ParallelRanges(bt.shared_chunk >= 0 ? n_leaf : n, [=](int b0, int b1) {
+      for (int i = b0; i < b1; ++i) {
+        const int t = h_order[i];
+        if (t < n_leaf && h_parent[t] >= off1 && h_parent[t] < off2) h_order[i] = t | kOrderNoDh;
+      }
+    });
   }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
   // The device half is free once the last backward pass that read it has finished.
@@ -632,6 +672,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   CAVS_CUDA(cudaMemcpyAsync(d, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, e->copy_stream));
   CAVS_CUDA(cudaEventRecord(e->copied[which], e->copy_stream));
   e->staged = which;
+  e->last_upload_bytes = o * sizeof(int32_t);
   return CAVS_OK;
 }
 
@@ -973,6 +1014,8 @@ extern "C" int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream) {
   if (e->TokHead()) return LaunchLeafLossFill(e->loss, e->ptok, bt.tok_slot, bt.label, n_leaf, e->cfg.classes, static_cast<cudaStream_t>(stream));
   return CAVS_OK;
 }
+
+extern "C" size_t cavs_treelstm_upload_bytes(const cavs_treelstm* e) { return e ? e->last_upload_bytes : 0; }
 
 extern "C" int cavs_treelstm_wait_embed_grad(cavs_treelstm* e, void* stream) {
   CAVS_REQUIRE(e, CAVS_ERR_BAD_ARG, "treelstm_wait_embed_grad: null handle");

@@ -107,6 +107,12 @@ class TreeLSTM:
         self._dh_keep = dh
         check(lib().cavs_treelstm_set_output_grad(self._h, ctypes.c_void_p(dh.data_ptr())))
 
+    def upload_bytes(self) -> int:
+        """Bytes of index tables the last load_batch() sent to the device."""
+        fn = lib().cavs_treelstm_upload_bytes
+        fn.restype = ctypes.c_size_t
+        return int(fn(self._h))
+
     def wait_embed_grad(self, stream) -> None:
         """Makes `stream` (a torch.cuda.Stream) wait for the embedding-gradient block of the last backward()."""
         check(lib().cavs_treelstm_wait_embed_grad(self._h, ctypes.c_void_p(stream.cuda_stream)))

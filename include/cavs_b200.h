@@ -305,6 +305,8 @@ CAVS_API int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream);
  * the weight gradients, so a data-parallel caller can start its cross-GPU reduction on another stream
  * while the rest of backward is still running.  Does not block the host. */
 CAVS_API int cavs_treelstm_wait_embed_grad(cavs_treelstm* e, void* stream);
+/* Bytes of index tables the most recent cavs_treelstm_load_batch copied from pinned host memory to the device. */
+CAVS_API size_t cavs_treelstm_upload_bytes(const cavs_treelstm* e);
 CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int* status_host, void* stream);
 /* Per-kernel-class timing with CUDA events on the launching stream.  While enabled, every launch
  * of forward / backward is bracketed by two events.  profile_read sums, per class, the elapsed
