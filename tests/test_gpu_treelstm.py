@@ -286,3 +286,26 @@ def test_one_engine_many_batches(cuda, bf16):
         assert loss_sum == want_loss
         for k in KEYS:
             assert np.array_equal(got[k], want[k][: len(got[k])] if k in ("state", "loss") else want[k]), k
+
+
+def test_level_one_by_token_with_few_distinct_tokens(cuda, monkeypatch):
+    # A tiny vocabulary makes every token own hundreds of leaves and of level-1 links, so the per-token link sums and
+    # the per-token gradient sums run through their multi-chunk paths; the result must match the oracle and the
+    # per-vertex form of level 1 (CAVS_LEVEL1_BY_TOKEN=0, read when an engine is created).
+    H, E, V, C = 64, 32, 7, 5
+    parents, tok_job, label_job = make_tree_batch(808, 64, 2, 40, V, C)
+    params = make_params(12, H, E, V, C, scale=0.05, bias_scale=0.02)
+    s, eng, out, loss_sum = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, bf16=True)
+    counts = np.bincount(tok_job[s.maps()[0][: s.level_off[1]]], minlength=V)
+    assert counts.max() > 256                                   # more than one chunk for the most frequent token
+    ref32 = _oracle(s, tok_job, label_job, params, H, E, V, C)
+    refbf = _oracle(s, tok_job, label_job, params, H, E, V, C, bf16=True)
+    for k in KEYS:
+        assert rel_err(out[k], ref32[k]) < 2e-2, k
+        assert rel_err(out[k], refbf[k]) < 5e-3, k
+    monkeypatch.setenv("CAVS_LEVEL1_BY_TOKEN", "0")
+    _, _, per_vertex, loss_pv = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, bf16=True)
+    monkeypatch.delenv("CAVS_LEVEL1_BY_TOKEN")
+    assert abs(loss_sum - loss_pv) < 2e-3 * abs(loss_pv)
+    for k in KEYS:
+        assert rel_err(out[k], per_vertex[k]) < 5e-3, k
