@@ -114,7 +114,7 @@ class ClockSampler:
         return out
 
 
-GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.724e9 / 31744
+GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.476e9 / 31744
 
 
 def measured_peaks():
@@ -361,8 +361,8 @@ def main():
     dominant = max(classes, key=lambda k: classes[k]["ms_per_step"])
     d = classes[dominant]
     if dominant == "gate_gemm":
-        # DRAM bytes per GEMM launch: captured with ncu on one rank's shard at 8 GPUs (all 81 GEMM launches of a step:
-        # 1.734 GB for 31,744 internal vertices, profiles/gemm_dram_traffic_shard_512_trees.md) and scaled by internal
+        # DRAM bytes per GEMM launch: captured with ncu on one rank's shard at 8 GPUs (all 83 GEMM launches of a step:
+        # 1.48 GB for 31,744 internal vertices, profiles/gemm_dram_traffic_shard_512_trees.md) and scaled by internal
         # vertices, to which every per-level operand and output is proportional.
         internal_rows = int(scheds[0].n_total - scheds[0].level_off[1]) if scheds[0].n_levels > 1 else 0
         traffic = GEMM_DRAM_BYTES_PER_INTERNAL_ROW * internal_rows / max(d["launches_per_step"], 1)

@@ -112,7 +112,7 @@ struct cavs_treelstm {
     int shared_chunk = -1;   // chunk whose partial row is the column sum over the internal vertices, or -1
     // l1_tok: links (t, c) of level 1 as t * K + c, grouped by the child's token row and cut into chunks
     int32_t *l_order = nullptr, *l_chunk_off = nullptr, *l_chunk_out = nullptr, *l_seg_first = nullptr, *l_multi = nullptr;
-    int n_l_chunks = 0, n_l_multi = 0;
+    int n_l_chunks = 0, n_l_multi = 0, n_links = 0;
     bool l1 = false;         // this batch runs level 1 by token (it has a level 1)
   };
   Batch slot[2];
@@ -615,7 +615,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     for (int sidx = 0; sidx < n_seg; ++sidx) h_head_row[n - n_leaf + sidx] = e->cfg.max_vertices + sidx;
   }
   bt.l1 = e->l1_tok && sch.n_levels() >= 2;
-  bt.n_l_chunks = bt.n_l_multi = 0;
+  bt.n_l_chunks = bt.n_l_multi = bt.n_links = 0;
   if (bt.l1) {
     // Links of level 1 grouped by the token row of the child (stable counting sort: within a token, links stay in
     // (vertex, slot) order), cut into chunks of kEmbedChunk; and the leaves below level 1 marked in `order`: their
@@ -655,7 +655,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
         const int ch = h_child[static_cast<size_t>(c) * nt + t];
         if (ch >= 0) h_l_order[e->link_bucket[h_slot[ch] + 1]++] = t * K + c;
       }
-    bt.n_l_chunks = n_lc; bt.n_l_multi = n_lm;
+    bt.n_l_chunks = n_lc; bt.n_l_multi = n_lm; bt.n_links = pos;
     const int n_leaf = bt.level_off[1];
     // `order` holds every leaf, and the internal vertices too unless they all share one token
     ParallelRanges(bt.shared_chunk >= 0 ? n_leaf : n, [=](int b0, int b1) {
@@ -864,7 +864,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
       // the per-token sums of the tail below.
       ChainHint(false);
       CAVS_CUDA(cudaMemsetAsync(e->ZT, 0, static_cast<size_t>(bt.n_seg) * 4 * H * e->elt, st));
-      PROF(e, kProfEmbedBwd, static_cast<double>(rows) * K * (elt * 4 * H + 4) + static_cast<double>(bt.n_l_chunks) * 16.0 * H, st,
+      // each parent's i,o,u gradient row (3H) once, each link's forget-gate row (H) and index; per chunk 4H fp32 out, per
+      // token 4H out
+      PROF(e, kProfEmbedBwd,
+           static_cast<double>(rows) * 3 * H * elt + static_cast<double>(bt.n_links) * (H * elt + 4) +
+               static_cast<double>(bt.n_l_chunks) * 16.0 * H + static_cast<double>(bt.n_seg) * 4 * H * elt,
+           st,
            LaunchLinkSumChunks(e->link_scratch, e->ZT, e->bf16, bt.l_chunk_out, e->dA, e->ZF, bt.l_order, bt.l_chunk_off, bt.n_l_chunks,
                                H, K, st));
       if ((rc = LaunchSegmentedRowSumFinal(e->ZT, e->bf16, e->link_scratch, bt.l_seg_first, bt.l_multi, bt.n_l_multi, 4 * H, st))) return rc;
@@ -919,9 +924,12 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
       const bool fdh = e->FusedDh();
       // leaves: mailbox (2H) + d(logits) row (or d(h)) in; internal rows: dA (4H) in; per chunk 4H fp32 out;
       // per token 4H out
-      const double bytes = static_cast<double>(n_leaf) * (4.0 * 2 * H + (fdh ? 4.0 * kHeadDzPitch : 4.0 * H) + 4) +
-                           static_cast<double>(n - n_leaf) * (4 + 4.0 * H * elt) + static_cast<double>(bt.n_chunks) * 16.0 * H +
-                           static_cast<double>(n_tok) * 4 * H * elt;
+      // (a leaf under level 1 by token has no d(h) half to read; with per-token loss rows no leaf reads a d(logits) row)
+      const double leaf_head = e->TokHead() ? 0.0 : (fdh ? 4.0 * kHeadDzPitch : 4.0 * H);
+      const double bytes = static_cast<double>(n_leaf - bt.n_links) * (4.0 * 2 * H + leaf_head + 4) +
+                           static_cast<double>(bt.n_links) * (4.0 * H + leaf_head + 4) +
+                           (bt.shared_chunk >= 0 ? 0.0 : static_cast<double>(n - n_leaf) * (4 + 4.0 * H * elt)) +
+                           static_cast<double>(bt.n_chunks) * (16.0 * H + 3.0 * H * elt) + static_cast<double>(n_tok) * 4 * H * elt;
       PROF(e, kProfEmbedBwd, bytes, st,
            LaunchTokenGradChunks(e->emb_scratch, e->dAtok, e->bf16, bt.chunk_out, e->dA, e->A, bt.order, bt.chunk_off, bt.chunk_seg,
                                  bt.n_chunks, e->mailbox, fdh ? nullptr : (e->Headless() ? e->dh_ext : e->dOut),
