@@ -84,7 +84,7 @@ struct cavs_treelstm {
   // once per vertex -- forward h_tok.U (PQT), backward the per-token sums of the parents' gate gradients over
   // parent-child links (ZT), d(h) per token (dh_tok = ZT.U^T) and the level's share of dU (h_tok^T ZT).  Exact
   // algebra (linearity of the products), like the per-token input projection.
-  bool l1_tok = false;
+  bool l1_tok = false, l1_always = false;
   uint8_t *htok_bf = nullptr, *PQT = nullptr, *ZT = nullptr;   // [tokens, H], [tokens, 4H], [tokens, 4H] (GEMM element type)
   float *dh_tok = nullptr, *link_scratch = nullptr;            // [tokens, H]; [link chunks, 4H]
   bool Dense() const { return cfg.vocab == 0; }
@@ -255,8 +255,12 @@ void InitModes(cavs_treelstm* e, const cavs_treelstm_config& cfg) {
   e->elt = e->bf16 ? 2 : 4;
   const char* v = std::getenv("CAVS_LEAF_BY_TOKEN");   // "0": keep one state row per leaf vertex
   e->leaf_tok = e->LeafTokEligible() && !(v != nullptr && v[0] == '0');
-  const char* v1 = std::getenv("CAVS_LEVEL1_BY_TOKEN");   // "0": level 1 runs per vertex like every other level
+  // "0": level 1 runs per vertex like every other level; "1": by token whenever possible; unset: by token for batches
+  // whose level 1 has at least twice as many rows as the batch has distinct tokens (below that the handful of extra
+  // launches costs what the smaller products save)
+  const char* v1 = std::getenv("CAVS_LEVEL1_BY_TOKEN");
   e->l1_tok = e->TokHead() && e->bf16 && !(v1 != nullptr && v1[0] == '0');
+  e->l1_always = v1 != nullptr && v1[0] == '1';
 }
 
 // Carves every device array out of the workspace; with base == nullptr it only sizes it.
@@ -614,7 +618,8 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     for (int t = n_leaf; t < n; ++t) h_head_row[t - n_leaf] = t;
     for (int sidx = 0; sidx < n_seg; ++sidx) h_head_row[n - n_leaf + sidx] = e->cfg.max_vertices + sidx;
   }
-  bt.l1 = e->l1_tok && sch.n_levels() >= 2;
+  bt.l1 = e->l1_tok && sch.n_levels() >= 2 &&
+          (e->l1_always || static_cast<long long>(bt.level_off[2] - bt.level_off[1]) >= 2LL * n_seg);
   bt.n_l_chunks = bt.n_l_multi = bt.n_links = 0;
   if (bt.l1) {
     // Links of level 1 grouped by the token row of the child (stable counting sort: within a token, links stay in

@@ -13,6 +13,13 @@ from cavs_b200.treelstm import TreeLSTM
 from helpers import make_params, make_tree_batch, rel_err, tables_from_schedule
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def level_one_by_token(monkeypatch):
+    # Small test batches have fewer level-1 rows than distinct tokens, where the engine would choose the per-vertex
+    # form of level 1 by itself: force the per-token form so that every bf16 case below runs it.
+    monkeypatch.setenv("CAVS_LEVEL1_BY_TOKEN", "1")
 KEYS = ("state", "loss", "dEmb", "dW", "dU", "dB", "dWc", "dbc")
 GOLD = Path(__file__).parent / "golden" / "treelstm_small.npz"
 
@@ -305,7 +312,7 @@ def test_level_one_by_token_with_few_distinct_tokens(cuda, monkeypatch):
         assert rel_err(out[k], refbf[k]) < 5e-3, k
     monkeypatch.setenv("CAVS_LEVEL1_BY_TOKEN", "0")
     _, _, per_vertex, loss_pv = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, bf16=True)
-    monkeypatch.delenv("CAVS_LEVEL1_BY_TOKEN")
+    monkeypatch.setenv("CAVS_LEVEL1_BY_TOKEN", "1")
     assert abs(loss_sum - loss_pv) < 2e-3 * abs(loss_pv)
     for k in KEYS:
         assert rel_err(out[k], per_vertex[k]) < 5e-3, k
