@@ -686,8 +686,8 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
 
 // Per-token sums over parent-child links.  Link (t, c) = entry t * K + c of `order` contributes the row
 // [ dA[t, 0:3H] | ZF[t * K + c, 0:H] ]: the parent's d(pre-activation) of i, o, u and of the forget gate of that child.
-// A chunk is at most kEmbedChunk links of one token (the token of the CHILD), summed in list order into
-// partial[chunk, 4H] (fp32); a chunk that is its token's only one also writes the final row out[chunk_out, 4H].
+// A chunk is at most kEmbedChunk links of one token (the token of the CHILD), summed in list order; a chunk that is its
+// token's only one writes the final row out[chunk_out, 4H], every other chunk its partial row partial[chunk, 4H] (fp32).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 LinkSumChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* __restrict__ chunk_out, const T* __restrict__ dA,
@@ -733,8 +733,9 @@ LinkSumChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* _
     Vec<V> sum;
 #pragma unroll
     for (int v = 0; v < V; ++v) sum.v[v] = (acc[0].v[v] + acc[1].v[v]) + (acc[2].v[v] + acc[3].v[v]);
-    Store<V>(mine + e, sum);
+    // only the second pass reads the partial rows, and it runs over multi-chunk tokens alone
     if (final_row) Store<V>(final_row + e, sum);
+    else Store<V>(mine + e, sum);
   }
 }
 

@@ -58,8 +58,8 @@ int LaunchTokenGradChunks(float* partial, void* out, bool bf16, const int32_t* c
 // token by the chunk seg_first_chunk[token row].
 constexpr int32_t kOrderNoDh = 1 << 30;
 // Per-token sums over parent-child links of a level whose children are all leaves: link t * K + c contributes
-// [ dA[t, 0:3H] | ZF[t * K + c, :] ]; chunks of <= 256 links of one child token; partial [n_chunks, 4H] fp32, and
-// out[chunk_out[chunk], 4H] for single-chunk tokens (the rest is folded by LaunchSegmentedRowSumFinal).
+// [ dA[t, 0:3H] | ZF[t * K + c, :] ]; chunks of <= 256 links of one child token; a single-chunk token's sum goes straight
+// to out[chunk_out[chunk], 4H], the other chunks write partial [chunk, 4H] fp32 for LaunchSegmentedRowSumFinal.
 int LaunchLinkSumChunks(float* partial, void* out, bool bf16, const int32_t* chunk_out, const void* dA, const void* ZF,
                         const int32_t* order, const int32_t* chunk_off, int n_chunks, int H, int K, cudaStream_t st);
 // ptok / label / inv_rows (optional, instead of dz): a leaf's d(logits) is (ptok[token] - onehot(label)) * inv_rows.
