@@ -14,7 +14,7 @@ namespace {
 // Runs fn(begin, end) over [0, n) on up to `threads` host threads (the caller's included).
 template <typename F>
 void ParallelFor(int n, int threads, F fn) {
-  threads = std::max(1, std::min(threads, n / 64 + 1));
+  threads = std::max(1, std::min(threads, n / 256 + 1));   // a thread costs tens of microseconds to start: few samples, few threads
   if (threads == 1) { fn(0, n); return; }
   std::vector<std::thread> pool;
   const int chunk = (n + threads - 1) / threads;
