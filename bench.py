@@ -114,7 +114,15 @@ class ClockSampler:
         return out
 
 
-GEMM_DRAM_BYTES_PER_INTERNAL_ROW = 1.476e9 / 31744
+def gemm_dram_bytes_per_internal_row():
+    """DRAM bytes all GEMM launches of a step move per internal vertex, from the committed figures of a profiler capture
+    (one rank's shard at 8 GPUs); None if the record is missing."""
+    rec = ROOT / "profiles" / "gemm_dram_traffic_shard_512_trees.json"
+    if not rec.exists():
+        return None
+    d = json.loads(rec.read_text())
+    return d["dram_bytes_per_step"] / d["internal_vertices"]
+
 
 
 def measured_peaks():
@@ -125,28 +133,65 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback")
 
 
-def cpu_baseline_sample(wl, n_trees, repeats=1):
-    """Times the CPU oracle (fwd + bwd + Adagrad) on the first n_trees trees of batch 0.  Returns (trees/s, seconds)."""
+def numpy_sample(wl, n_trees, seed=SEED):
+    """A sample of the workload generated with numpy alone (the CPU arm does not load the product library): random
+    binary trees by recursive uniform split, vertices in post-order (root last), Zipf(1.1) leaf tokens by inverse-CDF
+    lookup, token 0 on internal vertices, uniform labels; weights uniform in +-init_scale, zero biases."""
+    rng = np.random.default_rng(seed)
+    max_len = 2 * wl["leaf_hi"] - 1
+    parents = np.full((n_trees, max_len), -1, np.int32)
+    toks, labs = [], []
+    ranks = np.arange(1, wl["vocab"] + 1, dtype=np.float64) ** -1.1
+    cdf = np.cumsum(ranks) / ranks.sum()
+    for b in range(n_trees):
+        par, leaf = [], []
+
+        def rec(leaves):
+            if leaves == 1:
+                par.append(-1); leaf.append(True)
+                return len(par) - 1
+            split = int(rng.integers(1, leaves))
+            left, right = rec(split), rec(leaves - split)
+            par.append(-1); leaf.append(False)
+            par[left] = par[right] = len(par) - 1
+            return len(par) - 1
+
+        rec(int(rng.integers(wl["leaf_lo"], wl["leaf_hi"] + 1)))
+        parents[b, :len(par)] = par
+        is_leaf = np.array(leaf)
+        tok = np.minimum(np.searchsorted(cdf, rng.random(len(par))), wl["vocab"] - 1)
+        toks.append(np.where(is_leaf, tok, 0).astype(np.int32))
+        labs.append(rng.integers(0, wl["classes"], len(par)).astype(np.int32))
+    H, E, V, C, sc = wl["hidden"], wl["embed"], wl["vocab"], wl["classes"], wl["init_scale"]
+    u = lambda *shape: rng.uniform(-sc, sc, shape).astype(np.float32)
+    params = dict(Emb=u(V, E), W=u(E * 4 * H), U=u(4 * H * H), B=np.zeros(4 * H, np.float32), Wc=u(C, H), bc=np.zeros(C, np.float32))
+    return parents, np.concatenate(toks), np.concatenate(labs), params
+
+
+_cpu_state = {}
+
+
+def cpu_baseline_sample(wl, n_trees):
+    """One training step (level scheduling, forward, loss, backward, Adagrad) of the CPU oracle on a numpy-generated
+    sample of n_trees trees.  Returns (trees/s, seconds, executed GEMM GFLOP/s).  Nothing of the product runs here:
+    tables come from the oracle's own scheduler restatement."""
     import oracle
-    from cavs_b200 import schedule as S
     H, E, V, C = wl["hidden"], wl["embed"], wl["vocab"], wl["classes"]
-    parents, tok_job, label_job, _ = make_batch(dict(wl, batch=n_trees), 0, 0, 1)
-    params = make_params(wl)
-    flat = {k: v.copy() for k, v in params.items()}
-    acc = {k: np.zeros_like(v) for k, v in params.items()}
-    best = None
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        s = S.Schedule().load(parents)
-        fg, fs, bg, bs = s.tables(0)
-        t2j, _ = s.maps()
-        tb = dict(n=s.n_total, n_levels=s.n_levels, level_off=s.level_off, fg=fg, fs=fs, bg=bg, bs=bs)
-        out = oracle.treelstm_fwd_bwd(tb, tok_job[t2j], label_job[t2j], flat, H, E, V, C, gemm_bf16=wl["bf16"])
-        for k in flat:
-            oracle.adagrad(flat[k].reshape(-1), acc[k].reshape(-1), out["d" + k].reshape(-1), wl["lr"])
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return n_trees / best, best
+    key = (id(wl), n_trees)
+    if key not in _cpu_state:
+        parents, tok_job, label_job, params = numpy_sample(wl, n_trees)
+        _cpu_state.clear()
+        _cpu_state[key] = (parents, tok_job, label_job, params, {k: np.zeros_like(v) for k, v in params.items()})
+    parents, tok_job, label_job, flat, acc = _cpu_state[key]
+    t0 = time.perf_counter()
+    tb = oracle.tables(parents, 2, 0)
+    out = oracle.treelstm_fwd_bwd(tb, tok_job[tb["t2j"]], label_job[tb["t2j"]], flat, H, E, V, C, gemm_bf16=wl["bf16"])
+    for k in flat:
+        oracle.adagrad(flat[k].reshape(-1), acc[k].reshape(-1), out["d" + k].reshape(-1), wl["lr"])
+    dt = time.perf_counter() - t0
+    n, n_int = int(tb["n"]), int(tb["n"] - tb["level_off"][1])
+    flops = 3.0 * (2.0 * n * E * 4 * H + n_int * (2.0 * H * 3 * H + 4.0 * H * H))    # the per-vertex form the oracle executes
+    return n_trees / dt, dt, flops / dt / 1e9
 
 
 def run_reference(args, wl, rank, world):
@@ -158,11 +203,13 @@ def run_reference(args, wl, rank, world):
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     import oracle
     oracle.oracle_lib()
-    n_trees = args.sample_trees
-    for _ in range(max(args.warmup, 0) and 1):
-        cpu_baseline_sample(wl, max(2, n_trees // 4))
+    # One untimed step on a small sample warms the thread pool and measures the host; the timed steps then use the
+    # largest sample (at most --sample-trees) that keeps the whole run within about two minutes.
+    probe = min(32, args.sample_trees)
+    rate = cpu_baseline_sample(wl, probe)[0]
+    n_trees = int(max(probe, min(args.sample_trees, rate * 120.0 / max(args.steps, 1))))
     t0 = time.perf_counter()
-    rates = [cpu_baseline_sample(wl, n_trees)[0] for _ in range(args.steps)]
+    gflops = [cpu_baseline_sample(wl, n_trees)[2] for _ in range(args.steps)]
     total = time.perf_counter() - t0
     value = n_trees * args.steps / total
     line = dict(metric="treelstm_train_trees_per_sec", value=value, unit="trees/s", n_gpus=args.gpus, steps=args.steps,
@@ -171,10 +218,15 @@ def run_reference(args, wl, rank, world):
                 config=dict(workload=args.workload, global_batch=wl["batch"], hidden=wl["hidden"], embed=wl["embed"],
                             vocab=wl["vocab"], classes=wl["classes"], leaves=[wl["leaf_lo"], wl["leaf_hi"]]),
                 cpu_baseline=dict(value=value, unit="trees/s", cores=oracle.num_threads(), kind="port",
-                                  sample=f"{n_trees} trees of batch 0 per step, fwd+bwd+Adagrad, OpenMP over rows"),
+                                  gemm_gflops=statistics.median(gflops),
+                                  sample=f"{n_trees} trees per step (numpy-generated sample of the workload), level scheduling + "
+                                         "fwd + bwd + Adagrad, OpenMP over rows, cache-blocked GEMMs"),
                 e2e=dict(value=value, unit="trees/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 note="the reference has no CPU implementation of this path and its CUDA 8 sources do not build here; "
-                     "this arm times the CPU oracle port (oracle/cavs_oracle.c)")
+                     "this arm times the CPU oracle port (oracle/cavs_oracle.c) and loads nothing of the product. "
+                     "A step of the sample pays the per-step fixed costs (dense embedding-gradient block, full-table "
+                     "Adagrad) for fewer trees than a full batch would: trees/s understates the CPU at full batch size "
+                     "by the share of those costs; gemm_gflops is the size-independent figure")
     print(json.dumps(line))
 
 
@@ -185,7 +237,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="dp_treelstm", choices=sorted(WORKLOADS))
-    ap.add_argument("--sample-trees", type=int, default=24, help="trees per CPU-baseline sample")
+    ap.add_argument("--sample-trees", type=int, default=256, help="trees per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
@@ -228,35 +280,27 @@ def main():
     pinned = [tuple(torch.from_numpy(a).pin_memory() for a in p[:3]) for p in pool]
     host_sched = S.Schedule()
 
-    comm = torch.cuda.Stream(device=dev) if world > 1 else None
-    n_emb = wl["vocab"] * wl["embed"]
+    # The library's own communicator (NCCL from C++); torch.distributed only carries its 128-byte id to the ranks
+    # and the benchmark's barriers.
+    comm = None
+    if world > 1:
+        from cavs_b200.comm import Comm
+        comm = Comm.from_torch()
 
     def device_step():
-        eng.forward()
-        eng.backward()
-        if world > 1:
-            # backward finishes the embedding gradient (the bulk of the buffer) first: its all-reduce runs on a
-            # second stream under the rest of backward; the weight gradients follow on the main stream.
-            main = torch.cuda.current_stream()
-            eng.wait_embed_grad(comm)
-            with torch.cuda.stream(comm):
-                dist.all_reduce(eng.grads[:n_emb])
-            dist.all_reduce(eng.grads[n_emb:])
-            main.wait_stream(comm)
-        eng.adagrad(acc, wl["lr"])
+        # forward, backward, gradient sum over the ranks (embedding block on a side stream under the weight-gradient
+        # products), Adagrad, refresh of the bf16 weights: one call into the library
+        eng.step(comm, eng.OPT_ADAGRAD, acc, wl["lr"])
 
-    host_ms = [0.0, 0.0, 0]   # schedule ms, pack + upload-enqueue ms, calls
+    host_ms = [0.0, 0]   # host scheduling + packing + upload-enqueue ms, calls
 
     def stage(i):
-        """Host scheduling of batch i and the pinned upload of its tables (staged; forward() promotes it)."""
+        """Host scheduling of batch i and the pinned upload of its tables (staged; the next step promotes it)."""
         par, tok, lab = (t.numpy() for t in pinned[i % POOL])
         t0 = time.perf_counter()
-        host_sched.load(par)
-        t1 = time.perf_counter()
-        eng.load_batch(host_sched, tok, lab, loss_rows=pool[i % POOL][3])
-        host_ms[0] += (t1 - t0) * 1e3
-        host_ms[1] += (time.perf_counter() - t1) * 1e3
-        host_ms[2] += 1
+        eng.stage(host_sched, par, tok, lab, loss_rows=pool[i % POOL][3])
+        host_ms[0] += (time.perf_counter() - t0) * 1e3
+        host_ms[1] += 1
 
     tail_view = eng.device_view(6, (2,))                       # [loss sum, status word] on the device
     loss_pinned = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
@@ -328,6 +372,13 @@ def main():
         sampler.start()
     ms_dev, launches = timed(lambda k: [device_step() for _ in range(k)], args.steps)
     loss_dev = eng.read_loss()
+    # The loss of the GLOBAL batch: every rank's shard summed.  After the same number of steps it equals the 1-GPU
+    # run's loss_sum (same batch, same summed gradient, same updates) up to the rounding of the bf16 products.
+    global_loss = loss_dev
+    if world > 1:
+        t = torch.tensor([loss_dev], device=dev, dtype=torch.float64)
+        dist.all_reduce(t)
+        global_loss = float(t.item())
     # ---- end-to-end arm: host arrays in, loss out, every step ----
     e2e_loop(args.warmup)
     ms_e2e, _ = timed(e2e_loop, args.steps)
@@ -338,14 +389,14 @@ def main():
     prof_steps = 3
     eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3])
     for _ in range(prof_steps):
-        eng.forward(); eng.backward()
+        device_step()
     torch.cuda.synchronize()
-    n_cls = 9
+    n_cls = 13
     ms_c = (ctypes.c_double * n_cls)(); work_c = (ctypes.c_double * n_cls)(); cnt_c = (ctypes.c_int * n_cls)()
     L.cavs_treelstm_profile_read(eng._h, ms_c, work_c, cnt_c, n_cls)
     L.cavs_treelstm_profile(eng._h, 0)
     names = ["gate_gemm", "cell_fwd", "cell_bwd", "gather_child_h", "scatter_child_grad", "loss_head", "embed_fwd", "embed_bwd",
-             "column_sum"]
+             "column_sum", "allreduce_embedding", "allreduce_weights", "allreduce_exposed_wait", "optimizer"]
     peaks = measured_peaks()
     classes = {}
     for i, nm in enumerate(names):
@@ -358,14 +409,29 @@ def main():
         else:
             classes[nm] = dict(ms_per_step=ms_c[i] / prof_steps, launches_per_step=cnt_c[i] // prof_steps, gbs=rate / 1e9,
                                frac=rate / 1e9 / peaks["hbm_gbs"])
+    # communication and optimizer time per step: the embedding block's all-reduce runs on a side stream (hidden_ms of
+    # it lies under the weight-gradient products), the other blocks' and the wait for the side stream on the compute stream
+    ms_of = lambda nm: classes[nm]["ms_per_step"] if nm in classes else 0.0
+    comm_info = None
+    if world > 1:
+        comm_info = dict(allreduce_embedding_ms=ms_of("allreduce_embedding"), allreduce_weights_ms=ms_of("allreduce_weights"),
+                         exposed_wait_ms=ms_of("allreduce_exposed_wait"),
+                         hidden_ms=max(0.0, ms_of("allreduce_embedding") - ms_of("allreduce_exposed_wait")),
+                         on_compute_stream_ms=ms_of("allreduce_weights") + ms_of("allreduce_exposed_wait"),
+                         allreduce_bytes_per_step=4 * int(eng.params.numel()), nccl_version=comm.nccl_version(),
+                         issued_by="cavs_treelstm_step -> cavs_allreduce (ncclAllReduce called from the library)")
+    optimizer_ms = ms_of("optimizer")
+    for nm in ("allreduce_embedding", "allreduce_weights", "allreduce_exposed_wait", "optimizer"):
+        classes.pop(nm, None)      # not kernels of this library's level loop: reported as comm / optimizer_ms
     dominant = max(classes, key=lambda k: classes[k]["ms_per_step"])
     d = classes[dominant]
     if dominant == "gate_gemm":
-        # DRAM bytes per GEMM launch: captured with ncu on one rank's shard at 8 GPUs (all 83 GEMM launches of a step:
-        # 1.48 GB for 31,744 internal vertices, profiles/gemm_dram_traffic_shard_512_trees.md) and scaled by internal
-        # vertices, to which every per-level operand and output is proportional.
+        # DRAM bytes per GEMM launch: captured with the profiler on one rank's shard at 8 GPUs (all GEMM launches of a
+        # step) and scaled by internal vertices, to which every per-level operand and output is proportional: an
+        # extrapolation, not a measurement of this run.
         internal_rows = int(scheds[0].n_total - scheds[0].level_off[1]) if scheds[0].n_levels > 1 else 0
-        traffic = GEMM_DRAM_BYTES_PER_INTERNAL_ROW * internal_rows / max(d["launches_per_step"], 1)
+        per_row = gemm_dram_bytes_per_internal_row()
+        traffic = per_row * internal_rows / max(d["launches_per_step"], 1) if per_row is not None else None
         # `achieved` counts the flops the GEMM launches EXECUTE.  The per-vertex formula of the reference's algorithm
         # (every vertex multiplies its own input and its own children's states: 3 x (2 N E 4H + N_int (2 H 3H + 2 K H H)))
         # is reported beside it: the engine executes fewer flops than that, because products that depend on a vertex only
@@ -376,7 +442,7 @@ def main():
         formula = 3.0 * (2.0 * n_v * E_ * 4 * H_ + internal_rows * (2.0 * H_ * 3 * H_ + 2.0 * K_ * H_ * H_))
         roofline = dict(bound="tensor", kernel="GemmBf16Kernel (all gate / gradient GEMMs of a step)", achieved=d["tflops"],
                         peak=peaks["tflops"], unit="TFLOP/s", frac=d["frac"], traffic=traffic,
-                        traffic_unit="DRAM bytes per launch (ncu on a 512-tree shard, scaled by internal vertices)",
+                        traffic_unit="DRAM bytes per launch, extrapolated: profiler capture of a 512-tree shard scaled by internal vertices",
                         peak_source=peaks["source"], flops_executed_per_step=work_c[0] / prof_steps,
                         flops_per_vertex_formula_per_step=formula)
     else:
@@ -435,14 +501,16 @@ def main():
                             vertices_per_gpu=int(scheds[0].n_total), levels=int(scheds[0].n_levels), optimizer="adagrad",
                             parallelism=f"dp{world}", l2="working set per step (tens of GB) exceeds L2; no flush needed"),
                 e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8,
-                         host_schedule_ms=host_ms[0] / max(host_ms[2], 1), host_pack_ms=host_ms[1] / max(host_ms[2], 1)),
-                gpu_launches=int(launches), loss_sum=loss_dev, clocks=clocks, roofline=roofline, kernel_classes=classes,
-                graph_ops=graph_ops)
+                         host_stage_ms=host_ms[0] / max(host_ms[1], 1)),
+                gpu_launches=int(launches), gpu_launches_per_step=int(launches) // max(args.steps, 1), loss_sum=loss_dev,
+                global_loss_sum=global_loss, comm=comm_info, optimizer_ms=optimizer_ms, clocks=clocks, roofline=roofline,
+                kernel_classes=classes, graph_ops=graph_ops)
     if not args.no_cpu_baseline and world == 1:   # torchrun pins ranks to one host thread: the CPU arm runs at N=1 only
-        rate, secs = cpu_baseline_sample(wl, args.sample_trees)
+        rate, secs, gflops = cpu_baseline_sample(wl, args.sample_trees)
         import oracle
-        line["cpu_baseline"] = dict(value=rate, unit="trees/s", cores=oracle.num_threads(), kind="port",
-                                    sample=f"{args.sample_trees} trees of batch 0, one fwd+bwd+Adagrad step ({secs:.1f} s)")
+        line["cpu_baseline"] = dict(value=rate, unit="trees/s", cores=oracle.num_threads(), kind="port", gemm_gflops=gflops,
+                                    sample=f"{args.sample_trees} trees (numpy-generated sample of the workload), one step: level "
+                                           f"scheduling + fwd + bwd + Adagrad ({secs:.1f} s)")
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -70,7 +70,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for o in stale:
         o.unlink()
     if jobs or force or not LIB.exists():
-        cmd = [NVCC, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart", "-ldl", "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")

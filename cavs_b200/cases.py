@@ -1,4 +1,6 @@
-"""Small, self-contained cases of the library's kernels, sized for profiler captures
+"""A profiling harness, not part of the product: the commands recorded with the profiler summaries run it.
+
+Small, self-contained cases of the library's kernels, sized for profiler captures
 (inputs larger than L2, a few GB on the device at most, a handful of launches).
 
     python -m cavs_b200.cases gemm    one per-level gate product: [65536,1024] x [1024,3072], bf16 in / bf16 out

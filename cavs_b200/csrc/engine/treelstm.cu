@@ -119,10 +119,14 @@ struct cavs_treelstm {
   int active = -1, staged = -1;
   size_t last_upload_bytes = 0;   // size of the table blob the most recent load_batch sent to the device
   // The table upload runs on its own stream so it overlaps the step in flight: copied[s] marks the
-  // upload into slot s, slot_done[s] the end of the last backward pass that read slot s.
+  // upload into slot s, slot_done[s] the end of the last pass (forward, backward or state fill) that read slot s.
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t copied[2] = {nullptr, nullptr}, slot_done[2] = {nullptr, nullptr};
   cudaEvent_t emb_ready = nullptr;   // recorded in backward once the embedding gradient is complete
+  // cavs_treelstm_step: the embedding block of the gradient is reduced across GPUs on its own stream while the
+  // weight-gradient products still run; comm_done marks the end of that reduction
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t comm_done = nullptr;
   bool slot_used[2] = {false, false};
   std::vector<int32_t> bucket, slot_of_token, leaf_count, link_bucket;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
@@ -191,7 +195,7 @@ struct Carver {
 constexpr int kChainSmallRows = 4096;
 
 enum ProfClass { kProfGemm = 0, kProfCellFwd, kProfCellBwd, kProfGatherH, kProfScatterGrad, kProfLossHead, kProfEmbedFwd,
-                 kProfEmbedBwd, kProfColumnSum, kProfCount };
+                 kProfEmbedBwd, kProfColumnSum, kProfCommEmbed, kProfCommRest, kProfCommExposed, kProfOptimizer, kProfCount };
 
 // Runs `call` (an int-returning launch) bracketed by events when profiling is on.
 #define PROF(e, cls, work_expr, st, call)                                   \
@@ -413,6 +417,8 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->slot_done[i], cudaEventDisableTiming);
   }
   if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->emb_ready, cudaEventDisableTiming);
+  if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&e->comm_stream, cudaStreamNonBlocking);
+  if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->comm_done, cudaEventDisableTiming);
   if (err == cudaSuccess) err = cudaMemset(e->tail, 0, 4 * sizeof(float));
   if (err != cudaSuccess) {
     cudaFreeHost(e->h_idx);
@@ -432,6 +438,8 @@ extern "C" void cavs_treelstm_destroy(cavs_treelstm* e) {
     if (e->slot_done[i]) cudaEventDestroy(e->slot_done[i]);
   }
   if (e->emb_ready) cudaEventDestroy(e->emb_ready);
+  if (e->comm_done) cudaEventDestroy(e->comm_done);
+  if (e->comm_stream) cudaStreamDestroy(e->comm_stream);
   if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
   delete e;
 }
@@ -671,7 +679,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     });
   }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
-  // The device half is free once the last backward pass that read it has finished.
+  // The device half is free once the last pass that read it has finished.
   (void)stream;
   if (e->slot_used[which]) CAVS_CUDA(cudaStreamWaitEvent(e->copy_stream, e->slot_done[which], 0));
   CAVS_CUDA(cudaMemcpyAsync(d, h, o * sizeof(int32_t), cudaMemcpyHostToDevice, e->copy_stream));
@@ -769,6 +777,9 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   }
   ChainHint(false);
   (void)rc;
+  // a forward-only caller may load the batch after next into this slot without ever running backward
+  CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
+  e->slot_used[e->active] = true;
   return CAVS_OK;
 }
 
@@ -999,6 +1010,58 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
   return CAVS_OK;
 }
 
+extern "C" int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
+                                   const int32_t* tok_job, const int32_t* label_job, int loss_rows) {
+  CAVS_REQUIRE(e && s, CAVS_ERR_BAD_ARG, "treelstm_stage: null handle");
+  if (int rc = cavs_sched_load(s, parents, batch, max_len, e->cfg.n_slots)) return rc;
+  return cavs_treelstm_load_batch(e, s, tok_job, label_job, loss_rows, nullptr);
+}
+
+extern "C" int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimizer, float* opt_state, float lr, float eps,
+                                  void* stream) {
+  CAVS_REQUIRE(e && e->params && e->grads, CAVS_ERR_BAD_ARG, "treelstm_step: parameters / gradients not bound");
+  CAVS_REQUIRE(optimizer == 0 || optimizer == 1 || optimizer == 2, CAVS_ERR_BAD_ARG, "treelstm_step: optimizer must be 0 (none), 1 (SGD) or 2 (Adagrad)");
+  CAVS_REQUIRE(optimizer != 2 || opt_state, CAVS_ERR_BAD_ARG, "treelstm_step: Adagrad needs its accumulator");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = cavs_treelstm_forward(e, stream)) return rc;
+  if (int rc = cavs_treelstm_backward(e, stream)) return rc;
+  int world = 1;
+  if (comm) cavs_comm_info(comm, nullptr, &world, nullptr);
+  const size_t n_all = e->ParamCount(), n_emb = e->OffW();
+  if (world > 1) {
+    // Sum of the per-GPU gradients (cavs/midend/session_mpi.cc:31-80 inserts one all-reduce per variable gradient;
+    // here the flat buffer goes in two pieces).  backward finishes the embedding block -- the bulk of the buffer --
+    // first and announces it, so its reduction runs on a second stream under the weight-gradient products; the
+    // remaining blocks follow on the compute stream, which then waits for the first piece.
+    cudaEvent_t a0 = nullptr, a1 = nullptr, x0 = nullptr, x1 = nullptr;
+    CAVS_CUDA(cudaStreamWaitEvent(e->comm_stream, e->emb_ready, 0));
+    if (e->prof_on) { a0 = e->NextEvent(); a1 = e->NextEvent(); CAVS_CUDA(cudaEventRecord(a0, e->comm_stream)); }
+    if (int rc = cavs_allreduce(e->grads, n_emb, comm, e->comm_stream)) return rc;
+    if (e->prof_on) {
+      CAVS_CUDA(cudaEventRecord(a1, e->comm_stream));
+      e->recs.push_back({kProfCommEmbed, a0, a1, 4.0 * static_cast<double>(n_emb)});
+    }
+    CAVS_CUDA(cudaEventRecord(e->comm_done, e->comm_stream));
+    PROF(e, kProfCommRest, 4.0 * static_cast<double>(n_all - n_emb), st, cavs_allreduce(e->grads + n_emb, n_all - n_emb, comm, st));
+    // what the compute stream loses waiting for the embedding block's reduction (the part of it that was not hidden)
+    if (e->prof_on) { x0 = e->NextEvent(); x1 = e->NextEvent(); CAVS_CUDA(cudaEventRecord(x0, st)); }
+    CAVS_CUDA(cudaStreamWaitEvent(st, e->comm_done, 0));
+    if (e->prof_on) {
+      CAVS_CUDA(cudaEventRecord(x1, st));
+      e->recs.push_back({kProfCommExposed, x0, x1, 0.0});
+    }
+  }
+  if (optimizer != 0) {
+    // w <- w - lr g (SGD, cavs/backend/op_impl_sgd.cu:15-47) or the Adagrad form, over the whole flat buffer, then the
+    // bf16 shadows of the GEMM weights
+    const double bytes = (optimizer == 2 ? 20.0 : 12.0) * static_cast<double>(n_all);
+    PROF(e, kProfOptimizer, bytes, st,
+         optimizer == 2 ? LaunchAdagrad(e->params, opt_state, e->grads, n_all, lr, eps, st) : LaunchSgd(e->params, e->grads, n_all, lr, st));
+    if (int rc = cavs_treelstm_refresh_weights(e, stream)) return rc;
+  }
+  return CAVS_OK;
+}
+
 extern "C" int cavs_treelstm_set_dense_input(cavs_treelstm* e, const float* x, long long pitch) {
   CAVS_REQUIRE(e && e->Dense(), CAVS_ERR_BAD_ARG, "treelstm_set_dense_input: the engine was created with an embedding table (vocab > 0)");
   CAVS_REQUIRE(x && pitch >= e->cfg.embed && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && pitch % 4 == 0, CAVS_ERR_BAD_ARG,
@@ -1024,7 +1087,11 @@ extern "C" int cavs_treelstm_materialize_state(cavs_treelstm* e, void* stream) {
   if (int rc = cavs_gather_rows(e->state, e->state, bt.state_row, n_leaf, static_cast<size_t>(2) * e->cfg.hidden * sizeof(float), stream))
     return rc;
   // and the leaves' loss values, which the loss head's token rows do not write (valid after backward)
-  if (e->TokHead()) return LaunchLeafLossFill(e->loss, e->ptok, bt.tok_slot, bt.label, n_leaf, e->cfg.classes, static_cast<cudaStream_t>(stream));
+  if (e->TokHead())
+    if (int rc = LaunchLeafLossFill(e->loss, e->ptok, bt.tok_slot, bt.label, n_leaf, e->cfg.classes, static_cast<cudaStream_t>(stream)))
+      return rc;
+  CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], static_cast<cudaStream_t>(stream)));   // these launches read the slot's tables
+  e->slot_used[e->active] = true;
   return CAVS_OK;
 }
 
@@ -1046,7 +1113,7 @@ extern "C" int cavs_treelstm_profile(cavs_treelstm* e, int enable) {
 
 extern "C" int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes) {
   CAVS_REQUIRE(e && ms && work && launches && n_classes >= kProfCount, CAVS_ERR_BAD_ARG,
-               "treelstm_profile_read: need arrays of at least 9 entries");
+               "treelstm_profile_read: need arrays of at least 13 entries");
   for (int i = 0; i < n_classes; ++i) { ms[i] = 0; work[i] = 0; launches[i] = 0; }
   const bool dump = std::getenv("CAVS_PROF_DUMP") != nullptr;   // one line per launch on stderr
   for (const auto& r : e->recs) {
@@ -1085,7 +1152,8 @@ extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_p
       if (e->FusedDh()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(h) is not materialised with the fused loss head");
       *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;
     case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
-    case 4: *dev_ptr = e->gates;   // leaf rows are not written (their gates are recomputed) *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
+    case 4:                                                                      // saved gates; leaf rows are not written
+      *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
     case 6: *dev_ptr = e->tail; *bytes = 2 * sizeof(float); break;               // [0] loss sum, [1] status word (int)
     case 5:                                                                      // d(loss)/d(dense input)
       if (!e->Dense()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(x) exists only with dense inputs");

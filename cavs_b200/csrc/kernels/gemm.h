@@ -25,6 +25,10 @@ struct GemmBf16Args {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   int* status = nullptr;      // device word raised when a bounded wait expires
+  // Wait self-test (cavs_gemm_bf16_wait_selftest): polls per bounded wait (0 = default) and a producer that
+  // issues no operand load, so that every consumer wait runs out and the kernel's unwind path executes.
+  unsigned wait_poll_limit = 0;
+  int withhold_loads = 0;
 };
 int GemmBf16(const GemmBf16Args& args, cudaStream_t stream);
 
@@ -69,6 +73,8 @@ struct GemmBf16MappedArgs {
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   int* status = nullptr;
+  unsigned wait_poll_limit = 0;   // see GemmBf16Args
+  int withhold_loads = 0;
 };
 int EncodeTcOutput(TcOperandMap* out, void* base, long long m, long long n, long long ldc, bool bf16);
 int GemmBf16Mapped(const GemmBf16MappedArgs& args, cudaStream_t stream);

@@ -85,10 +85,11 @@ template <int kBN, int kAMajor, int kBMajor, int kMB = 1>
 int Launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const tc::Params& p, dim3 grid, cudaStream_t stream) {
   using S = tc::Smem<kBN, kMB>;
   auto kern = tc::GemmBf16Kernel<kBN, kAMajor, kBMajor, kMB>;
-  static bool configured = false;   // per instantiation
-  if (!configured) {
+  static bool configured[kMaxDevices] = {};   // per instantiation and device: the attribute belongs to the device's copy
+  const int dev = CurrentDevice();
+  if (!configured[dev]) {
     CAVS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
-    configured = true;
+    configured[dev] = true;
   }
   CAVS_CUDA(LaunchChained(kern, grid, dim3(tc::kThreads), S::kBytes, stream, ma, mb, mc, p));
   CAVS_LAUNCH_CHECK("gemm_bf16");
@@ -226,6 +227,8 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   p.n_splits = eff_splits;
   p.a_row_off = g.a_row_off;
   p.status = g.status;
+  p.spin_limit = g.wait_poll_limit;
+  p.withhold_loads = g.withhold_loads;
   p.chain_early = ChainEarly();
   p.sc_child = g.scatter_child; p.sc_addend = g.scatter_addend; p.sc_addend_ld = g.scatter_addend_ld;
   p.sc_n_total = g.scatter_n_total; p.sc_off = g.scatter_off; p.sc_slots = std::max(1, g.scatter_slots);
@@ -281,6 +284,7 @@ int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {
   a.a = &ma; a.b = &mb;
   a.m = g.m; a.n = g.n; a.k = g.k;
   a.splits = g.splits; a.scratch = g.scratch; a.scratch_bytes = g.scratch_bytes; a.status = g.status;
+  a.wait_poll_limit = g.wait_poll_limit; a.withhold_loads = g.withhold_loads;
   return GemmBf16Mapped(a, stream);
 }
 
@@ -295,6 +299,20 @@ extern "C" int cavs_gemm_bf16(void* c, long long ldc, int out_mode, const void* 
   g.b = b; g.ldb = ldb; g.b_major = b_major;
   g.m = m; g.n = n; g.k = k;
   g.splits = splits; g.scratch = scratch; g.scratch_bytes = scratch_bytes; g.status = status;
+  return cavs_b200::GemmBf16(g, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cavs_gemm_bf16_wait_selftest(void* c, long long ldc, const void* a, long long lda, const void* b, long long ldb, int m,
+                                            int n, int k, int* status, void* stream) {
+  CAVS_REQUIRE(status != nullptr, CAVS_ERR_BAD_ARG, "gemm_bf16_wait_selftest: a status word is required");
+  cavs_b200::GemmBf16Args g{};
+  g.c = c; g.ldc = ldc; g.out_mode = 0;
+  g.a = a; g.lda = lda; g.a_major = 0;
+  g.b = b; g.ldb = ldb; g.b_major = 1;
+  g.m = m; g.n = n; g.k = k;
+  g.status = status;
+  g.wait_poll_limit = 1u << 14;   // a few milliseconds per wait instead of a third of a second
+  g.withhold_loads = 1;
   return cavs_b200::GemmBf16(g, static_cast<cudaStream_t>(stream));
 }
 

@@ -56,6 +56,8 @@ struct Params {
   long long sc_addend_ld;
   int sc_n_total, sc_off, sc_slots;
   int* status;        // device word, set non-zero when a bounded wait expires
+  uint32_t spin_limit;    // polls per bounded wait; 0 = kSpinLimit
+  int withhold_loads;     // wait self-test: the producer issues no operand load, so every consumer wait runs out
 };
 
 // kMB: 128-row blocks of C per tile.  kMB = 2 (256 x 256 tiles, long-K weight gradients only): the operand bytes a
@@ -85,8 +87,8 @@ __device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes) {
 }
 // Bounded wait on a phase parity: non-blocking polls with a short sleep once the wait
 // is clearly not a pipeline hiccup.  Returns false if the limit expired (~0.3 s).
-__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, uint32_t limit = kSpinLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -343,13 +345,14 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  const uint32_t spin = p.spin_limit != 0 ? p.spin_limit : kSpinLimit;
   bool ok = true;
   // Everything above touched only this CTA's shared memory and TMEM; operands and outputs in global
   // memory belong to the preceding kernel until here.
   ChainAcquire();
 
   if (warp == 0) {
-    if (ElectOne()) {
+    if (ElectOne() && !p.withhold_loads) {
       uint32_t it = 0;   // ring position, continuous across work items
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
         const int z = w % p.n_splits, tile = w / p.n_splits;
@@ -359,7 +362,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int i = 0; i < kb_count; ++i, ++it) {
           const int s = it % S::kStages;
           const uint32_t phase = (it / S::kStages) & 1;
-          ok = MbarWait(SmemAddr(empty_bar + s), phase ^ 1);
+          ok = MbarWait(SmemAddr(empty_bar + s), phase ^ 1, spin);
           if (!ok) break;
           const uint32_t bar = SmemAddr(full_bar + s);
           MbarExpectTx(bar, S::kStage);
@@ -396,14 +399,14 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
         // kMB = 1: two accumulators alternate between tiles; kMB = 2: one accumulator pair, reused by every tile
         const uint32_t acc = kMB == 2 ? 0 : (t_local & 1), acc_phase = kMB == 2 ? (t_local & 1) : ((t_local >> 1) & 1);
-        ok = MbarWait(SmemAddr(acc_empty + acc), acc_phase ^ 1);   // epilogue has drained this accumulator
+        ok = MbarWait(SmemAddr(acc_empty + acc), acc_phase ^ 1, spin);   // epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem_base + acc * kBN;
         for (int i = 0; i < kb_count; ++i, ++it) {
           const int s = it % S::kStages;
           const uint32_t phase = (it / S::kStages) & 1;
-          ok = MbarWait(SmemAddr(full_bar + s), phase);
+          ok = MbarWait(SmemAddr(full_bar + s), phase, spin);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = SmemAddr(smem + s * S::kStage);
@@ -432,7 +435,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t acc = kMB == 2 ? 0 : (t_local & 1), acc_phase = kMB == 2 ? (t_local & 1) : ((t_local >> 1) & 1);
       int sc_dst[8], sc_add[8];
       if (p.out_mode == kScatterF32) ScatterTargets(p, lane, m0_tile + quarter * 32, sc_dst, sc_add);   // before the wait (kMB = 1 only)
-      ok = MbarWait(SmemAddr(acc_full + acc), acc_phase);
+      ok = MbarWait(SmemAddr(acc_full + acc), acc_phase, spin);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const long long zoff = static_cast<long long>(z) * p.split_stride;

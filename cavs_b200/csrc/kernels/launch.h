@@ -11,18 +11,25 @@
 
 namespace cavs_b200 {
 
-// SMs of the current device (148 on B200); queried once per process.
+// Most devices one process is expected to drive; per-device caches are arrays of this size.
+constexpr int kMaxDevices = 64;
+
+// Ordinal of the calling thread's current device, clamped into the per-device cache arrays.
+inline int CurrentDevice() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+  return dev < kMaxDevices ? dev : kMaxDevices - 1;
+}
+
+// SMs of the current device (148 on B200); queried once per device.
 inline int SmCount() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      cached = n;
-    else
-      cached = 148;
+  static int cached[kMaxDevices] = {};
+  const int dev = CurrentDevice();
+  if (cached[dev] == 0) {
+    int n = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
   }
-  return cached;
+  return cached[dev];
 }
 
 // CTAs of `threads` threads that fit on one SM by thread count (2048 threads per SM).

@@ -39,10 +39,14 @@ class Schedule:
         parents = np.ascontiguousarray(parents, dtype=np.int32)
         assert parents.ndim == 2
         check(lib().cavs_sched_load(self._h, ptr(parents), parents.shape[0], parents.shape[1], n_slots))
+        self.n_slots = n_slots
+        return self._refresh()
+
+    def _refresh(self) -> "Schedule":
+        """Re-reads the counts after the handle was loaded by another entry point (cavs_treelstm_stage)."""
         a, b, c, d = (ctypes.c_int() for _ in range(4))
         check(lib().cavs_sched_counts(self._h, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c), ctypes.byref(d)))
         self.n_total, self.n_scheduled, self.n_levels, self.max_level_rows = a.value, b.value, c.value, d.value
-        self.n_slots = n_slots
         return self
 
     @property

@@ -82,6 +82,23 @@ class TreeLSTM:
         check(lib().cavs_treelstm_load_batch(self._h, sched._h, ptr(tok_job), ptr(label_job), loss_rows, _stream()))
         self.n = sched.n_scheduled
 
+    def stage(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0) -> None:
+        """Level scheduling of `parents` into `sched` and the upload of the batch's tables, in one C call."""
+        assert parents.dtype == np.int32 and parents.flags.c_contiguous
+        check(lib().cavs_treelstm_stage(self._h, sched._h, ptr(parents), parents.shape[0], parents.shape[1],
+                                        ptr(tok_job) if self.cfg.vocab else ptr(None), ptr(label_job) if self.cfg.classes else ptr(None),
+                                        loss_rows))
+        sched._refresh()
+        self.n = sched.n_scheduled
+
+    OPT_NONE, OPT_SGD, OPT_ADAGRAD = 0, 1, 2
+
+    def step(self, comm=None, optimizer: int = 0, opt_state: torch.Tensor | None = None, lr: float = 0.0, eps: float = 1e-10) -> None:
+        """forward + backward + gradient sum over the ranks of `comm` + parameter update, one C call."""
+        check(lib().cavs_treelstm_step(self._h, comm._h if comm is not None else ctypes.c_void_p(0), optimizer,
+                                       ctypes.c_void_p(opt_state.data_ptr() if opt_state is not None else 0),
+                                       ctypes.c_float(lr), ctypes.c_float(eps), _stream()))
+
     def forward(self) -> None:
         check(lib().cavs_treelstm_forward(self._h, _stream()))
 

@@ -136,6 +136,13 @@ CAVS_API int cavs_gemm_bf16(void* c, long long ldc, int out_mode, const void* a,
                             const void* b, long long ldb, int b_major, int m, int n, int k, int splits, void* scratch,
                             size_t scratch_bytes, int* status, void* stream);
 CAVS_API size_t cavs_gemm_bf16_scratch_bytes(int m, int n, int splits);
+/* Self-test of the kernel's bounded waits.  Launches the same kernel as cavs_gemm_bf16 (A [m,k] and B [k,n]
+ * row-major, C fp32) with its operand loads withheld and a poll limit of a few milliseconds, so that every wait
+ * inside it runs out: the kernel must raise *status, free its tensor memory and return without writing C, and the
+ * context must stay usable.  For tests of the error path (CAVS_ERR_TIMEOUT); no counterpart in the reference, whose
+ * kernels never wait on one another. */
+CAVS_API int cavs_gemm_bf16_wait_selftest(void* c, long long ldc, const void* a, long long lda, const void* b, long long ldb,
+                                          int m, int n, int k, int* status, void* stream);
 /* fp32 GEMM on the CUDA cores with element strides (any transpose without a copy):
  * C[i,j] (+)= sum_p A[i*a_row_stride + p*a_col_stride] * B[p*b_row_stride + j*b_col_stride].
  * The fp32 configurations use it to stay within 1e-5 of the reference's cublasSgemm. */
@@ -247,6 +254,28 @@ CAVS_API int cavs_adagrad(float* w, float* acc, const float* g, size_t count, fl
 CAVS_API int cavs_cast_bf16(void* dst, const float* src, size_t count, void* stream);
 
 /* ------------------------------------------------------------------------ */
+/* Data-parallel training: one process per GPU, gradients summed with NCCL.   */
+/* Replaces MPIAllReduce through host memory                                  */
+/* (cavs/backend/op_impl_mpi.cc:29-49, inserted per variable gradient by       */
+/* MPISession, cavs/midend/session_mpi.cc:31-80) and the start-up broadcast of */
+/* the variables from rank 0 (cavs/backend/op_impl_variable.h:151-159).        */
+/* ------------------------------------------------------------------------ */
+typedef struct cavs_comm cavs_comm;
+/* Rank 0 makes a 128-byte id and hands it to every rank by whatever channel the host program has (the reference
+ * uses MPI; a PyTorch host its process-group store); every rank then creates its communicator with the device it
+ * will compute on current.  NCCL is bound on first use; CAVS_ERR_UNSUPPORTED if it cannot be loaded. */
+CAVS_API int cavs_comm_unique_id(void* id, size_t bytes);
+CAVS_API int cavs_comm_create(const void* id, size_t bytes, int rank, int world, cavs_comm** out);
+CAVS_API void cavs_comm_destroy(cavs_comm* comm);
+CAVS_API int cavs_comm_info(const cavs_comm* comm, int* rank, int* world, int* nccl_version);
+/* buf (fp32, device) <- sum over ranks, in place, on `stream`; a no-op for a world of one. */
+CAVS_API int cavs_allreduce(float* buf, size_t count, cavs_comm* comm, void* stream);
+/* buf <- rank `root`'s buf (parameters at start-up). */
+CAVS_API int cavs_broadcast(void* buf, size_t bytes, int root, cavs_comm* comm, void* stream);
+/* recv [world, bytes_per_rank] <- every rank's send [bytes_per_rank]. */
+CAVS_API int cavs_allgather(const void* send, void* recv, size_t bytes_per_rank, cavs_comm* comm, void* stream);
+
+/* ------------------------------------------------------------------------ */
 /* Tree-LSTM engine: the level loop, forward and backward.                   */
 /* Replaces GraphStatement::Run / GraphGradStatement::Run                    */
 /* (cavs/midend/statement.cc:43-123) for the child-sum Tree-LSTM vertex       */
@@ -279,6 +308,19 @@ CAVS_API int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream);
  * loss_rows: divisor of the loss gradient (0 = this batch's vertex count). */
 CAVS_API int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job, const int32_t* label_job,
                                       int loss_rows, void* stream);
+/* Level scheduling of a batch (cavs_sched_load into `s`, with the engine's slot count) and cavs_treelstm_load_batch
+ * in one call: everything the host does per batch before the device step. */
+CAVS_API int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
+                                 const int32_t* tok_job, const int32_t* label_job, int loss_rows);
+/* One training step in one call: forward, backward, the sum of the gradients over the ranks of `comm` (NULL or a
+ * world of one: none) and the update of the flat parameter buffer -- optimizer 0: none (gradients only), 1: SGD,
+ * 2: Adagrad with accumulator opt_state [param_count] -- followed by the refresh of the bf16 weight copies.  What
+ * Session::Run does for a fetched train op (cavs/midend/session_mpi.cc:84-138).  For the summed gradient to equal
+ * the single-GPU gradient of the global batch, every rank passes the GLOBAL loss-row count to load_batch / stage.
+ * The embedding block of the gradient is reduced on an internal stream while the weight gradients are still being
+ * computed.  Enqueues only; the loss of this rank's shard is read with cavs_treelstm_read_loss or peek array 6. */
+CAVS_API int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimizer, float* opt_state, float lr, float eps,
+                                void* stream);
 /* Embedding lookup and input projection over the batch's distinct tokens, then the forward level loop. */
 CAVS_API int cavs_treelstm_forward(cavs_treelstm* e, void* stream);
 /* Loss head, level loop in reverse, deferred weight / bias / embedding gradients (overwrites grads). */
@@ -312,7 +354,9 @@ CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int
  * of forward / backward is bracketed by two events.  profile_read sums, per class, the elapsed
  * milliseconds, the algorithmic work (flops for class 0, bytes otherwise) and the launch count
  * since the last read.  Classes: 0 gate GEMMs, 1 cell forward, 2 cell backward, 3 child-h gather,
- * 4 child-gradient scatter, 5 loss head, 6 embedding forward, 7 embedding backward, 8 column sum. */
+ * 4 child-gradient scatter, 5 loss head, 6 embedding forward, 7 embedding backward, 8 column sum; from
+ * cavs_treelstm_step: 9 all-reduce of the embedding block (on the side stream), 10 all-reduce of the other blocks,
+ * 11 time the compute stream waited for 9 to finish (its part that was not hidden), 12 optimizer.  n_classes >= 13. */
 CAVS_API int cavs_treelstm_profile(cavs_treelstm* e, int enable);
 CAVS_API int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes);
 /* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H] (classes > 8 only: the fused

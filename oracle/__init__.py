@@ -8,6 +8,7 @@ the smoke check and the benchmark's CPU-baseline leg import this package; the pr
 from __future__ import annotations
 
 import ctypes
+import os
 import subprocess
 from pathlib import Path
 
@@ -18,8 +19,17 @@ _oracle = None
 _ref = None
 
 
-def build() -> None:
-    subprocess.run(["make", "-C", str(HERE), "all"], check=True, capture_output=True)
+def reference_checkout() -> str:
+    """Where the reference project's sources lie: $CAVS_REFERENCE, else a directory named `reference` beside this
+    repository; empty if neither exists (the compiled reference scheduler is then kept as prebuilt)."""
+    for cand in (os.environ.get("CAVS_REFERENCE", ""), str(HERE.parent.parent / "reference")):
+        if cand and (Path(cand) / "cavs" / "midend" / "graph_scheduler.cc").is_file():
+            return cand
+    return ""
+
+
+def build(verbose: bool = False) -> None:
+    subprocess.run(["make", "-C", str(HERE), "all", f"REF={reference_checkout()}"], check=True, capture_output=not verbose)
 
 
 def oracle_lib() -> ctypes.CDLL:

@@ -395,51 +395,87 @@ static inline float bf16_round(float x) {
 }
 static void round_copy(float *dst, const float *src, size_t n, int bf16) {
   if (!bf16) { memcpy(dst, src, n * sizeof(float)); return; }
+#pragma omp parallel for schedule(static)
   for (size_t i = 0; i < n; i++) dst[i] = bf16_round(src[i]);
 }
 static inline float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); } /* expression.h:40-72 */
 
-/* C[m,n] (+)= A[m,k] * B[k,n], row-major, fp32 accumulate in k order. */
+/* C[m,n] (+)= A[m,k] * B[k,n], row-major.  Every C[i,j] is accumulated in ascending k order starting from its
+ * old value (or zero), exactly like the three-loop form; the loops are only blocked for the caches (C blocks of
+ * GEMM_MC x GEMM_NC, K in steps of GEMM_KC, register tiles of 4 rows x 16 columns that the compiler keeps in
+ * vector registers), so that the timed CPU baseline is bound by arithmetic, not by re-reading B from memory. */
+#define GEMM_MC 64
+#define GEMM_NC 256
+#define GEMM_KC 256
+typedef float gemm_v8 __attribute__((vector_size(32), aligned(4)));   /* eight floats, unaligned loads allowed */
+static void gemm_block(float *C, const float *A, const float *B, int n, int k, int i0, int i1, int j0, int j1, int p0, int p1) {
+  int i = i0;
+  for (; i + 4 <= i1; i += 4) {
+    const float *a0 = A + (size_t)i * k, *a1 = a0 + k, *a2 = a1 + k, *a3 = a2 + k;
+    int j = j0;
+    for (; j + 16 <= j1; j += 16) {
+      float *c0 = C + (size_t)i * n + j, *c1 = c0 + n, *c2 = c1 + n, *c3 = c2 + n;
+      gemm_v8 r00 = *(gemm_v8 *)c0, r01 = *(gemm_v8 *)(c0 + 8), r10 = *(gemm_v8 *)c1, r11 = *(gemm_v8 *)(c1 + 8);
+      gemm_v8 r20 = *(gemm_v8 *)c2, r21 = *(gemm_v8 *)(c2 + 8), r30 = *(gemm_v8 *)c3, r31 = *(gemm_v8 *)(c3 + 8);
+      for (int p = p0; p < p1; p++) {
+        const float *b = B + (size_t)p * n + j;
+        const gemm_v8 b0 = *(const gemm_v8 *)b, b1 = *(const gemm_v8 *)(b + 8);
+        r00 += a0[p] * b0; r01 += a0[p] * b1;
+        r10 += a1[p] * b0; r11 += a1[p] * b1;
+        r20 += a2[p] * b0; r21 += a2[p] * b1;
+        r30 += a3[p] * b0; r31 += a3[p] * b1;
+      }
+      *(gemm_v8 *)c0 = r00; *(gemm_v8 *)(c0 + 8) = r01; *(gemm_v8 *)c1 = r10; *(gemm_v8 *)(c1 + 8) = r11;
+      *(gemm_v8 *)c2 = r20; *(gemm_v8 *)(c2 + 8) = r21; *(gemm_v8 *)c3 = r30; *(gemm_v8 *)(c3 + 8) = r31;
+    }
+    for (; j < j1; j++)
+      for (int r = 0; r < 4; r++) {
+        float acc = C[(size_t)(i + r) * n + j];
+        for (int p = p0; p < p1; p++) acc += A[(size_t)(i + r) * k + p] * B[(size_t)p * n + j];
+        C[(size_t)(i + r) * n + j] = acc;
+      }
+  }
+  for (; i < i1; i++) {
+    float *c = C + (size_t)i * n;
+    for (int p = p0; p < p1; p++) {
+      const float av = A[(size_t)i * k + p];
+      const float *b = B + (size_t)p * n;
+      for (int j = j0; j < j1; j++) c[j] += av * b[j];
+    }
+  }
+}
 static void gemm_nn(float *C, const float *A, const float *B, int m, int n, int k, int accumulate) {
-#pragma omp parallel for schedule(static)
-  for (int i = 0; i < m; i++) {
-    float *c = C + (size_t)i * n;
-    if (!accumulate) memset(c, 0, sizeof(float) * (size_t)n);
-    const float *a = A + (size_t)i * k;
-    for (int p = 0; p < k; p++) {
-      float av = a[p];
-      if (av == 0.0f) continue;
-      const float *b = B + (size_t)p * n;
-      for (int j = 0; j < n; j++) c[j] += av * b[j];
-    }
+  const int mb = (m + GEMM_MC - 1) / GEMM_MC, nb = (n + GEMM_NC - 1) / GEMM_NC;
+#pragma omp parallel for schedule(dynamic)
+  for (int blk = 0; blk < mb * nb; blk++) {
+    const int i0 = (blk / nb) * GEMM_MC, j0 = (blk % nb) * GEMM_NC;
+    const int i1 = i0 + GEMM_MC < m ? i0 + GEMM_MC : m, j1 = j0 + GEMM_NC < n ? j0 + GEMM_NC : n;
+    if (!accumulate)
+      for (int i = i0; i < i1; i++) memset(C + (size_t)i * n + j0, 0, sizeof(float) * (size_t)(j1 - j0));
+    for (int p0 = 0; p0 < k; p0 += GEMM_KC)
+      gemm_block(C, A, B, n, k, i0, i1, j0, j1, p0, p0 + GEMM_KC < k ? p0 + GEMM_KC : k);
   }
 }
-/* C[m,n] (+)= A[m,k] * B[n,k]^T */
+/* dst[c,r] = src[r,c] for src [rows,cols] */
+static float *transposed(const float *src, int rows, int cols) {
+  float *dst = (float *)malloc(sizeof(float) * (size_t)rows * (size_t)cols + 4);
+#pragma omp parallel for schedule(static)
+  for (int c0 = 0; c0 < cols; c0 += 32)
+    for (int r = 0; r < rows; r++)
+      for (int c = c0; c < c0 + 32 && c < cols; c++) dst[(size_t)c * rows + r] = src[(size_t)r * cols + c];
+  return dst;
+}
+/* C[m,n] = A[m,k] * B[n,k]^T: B is transposed once, then the same k-ordered sums as gemm_nn. */
 static void gemm_nt(float *C, const float *A, const float *B, int m, int n, int k, int accumulate) {
-#pragma omp parallel for schedule(static)
-  for (int i = 0; i < m; i++) {
-    const float *a = A + (size_t)i * k;
-    for (int j = 0; j < n; j++) {
-      const float *b = B + (size_t)j * k;
-      float acc = 0.0f;
-      for (int p = 0; p < k; p++) acc += a[p] * b[p];
-      C[(size_t)i * n + j] = (accumulate ? C[(size_t)i * n + j] : 0.0f) + acc;
-    }
-  }
+  float *Bt = transposed(B, n, k);
+  gemm_nn(C, A, Bt, m, n, k, accumulate);
+  free(Bt);
 }
-/* C[m,n] (+)= A[k,m]^T * B[k,n]  (weight gradients: reduction over rows) */
+/* C[m,n] (+)= A[k,m]^T * B[k,n]  (weight gradients: reduction over rows, in row order) */
 static void gemm_tn(float *C, const float *A, const float *B, int m, int n, int k, int accumulate) {
-#pragma omp parallel for schedule(static)
-  for (int i = 0; i < m; i++) {
-    float *c = C + (size_t)i * n;
-    if (!accumulate) memset(c, 0, sizeof(float) * (size_t)n);
-    for (int p = 0; p < k; p++) {
-      float av = A[(size_t)p * m + i];
-      if (av == 0.0f) continue;
-      const float *b = B + (size_t)p * n;
-      for (int j = 0; j < n; j++) c[j] += av * b[j];
-    }
-  }
+  float *At = transposed(A, k, m);
+  gemm_nn(C, At, B, m, n, k, accumulate);
+  free(At);
 }
 
 /* ------------------------------------------------------------------------- */
@@ -544,6 +580,7 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
   /* Embedding lookup for every vertex, leaf or not (op_impl_embedding_lookup.cu:23-35),
    * then the input projection.  x does not depend on the level, so one product over
    * all rows equals the reference's per-level products row for row. */
+#pragma omp parallel for schedule(static)
   for (int t = 0; t < n; t++) {
     const float *src;
     if (x_dense) {
@@ -556,12 +593,13 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
     for (int e = 0; e < E; e++) x[(size_t)t * E + e] = bf ? bf16_round(src[e]) : src[e];
   }
   gemm_nn(a, x, Wr, n, 4 * H, E, 0);
-  if (cfg->preact_bf16) for (size_t i = 0; i < (size_t)n * 4 * H; i++) a[i] = bf16_round(a[i]);
+  if (cfg->preact_bf16) round_copy(a, a, (size_t)n * 4 * H, 1);
 
   for (int l = 0; l < cfg->n_levels; l++) {
     const int off = level_off[l], cnt = level_off[l + 1] - off;
     /* Gather (op_impl_graphop.cu:32-90): child state rows out of the mailbox. */
     for (int c = 0; c < K; c++)
+#pragma omp parallel for schedule(static)
       for (int t = off; t < off + cnt; t++) {
         float *dst = gath + ((size_t)c * n + t) * 2 * H;
         int src = fg[(size_t)c * n + t];
@@ -569,6 +607,7 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
         else memset(dst, 0, sizeof(float) * 2 * H);
       }
     /* h_lr = h_l + h_r (tree-lstm-cavs.cc:136) and the recurrent products. */
+#pragma omp parallel for schedule(static)
     for (int t = off; t < off + cnt; t++)
       for (int j = 0; j < H; j++) {
         float acc = gath[((size_t)0 * n + t) * 2 * H + j];
@@ -583,9 +622,9 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
     for (int c = 0; c < K; c++)
       gemm_nn(q + ((size_t)c * n + off) * H, hk + ((size_t)c * n + off) * H, Ur_f, cnt, H, H, 0);
     if (cfg->preact_bf16) {
-      for (size_t i = (size_t)off * 3 * H; i < (size_t)(off + cnt) * 3 * H; i++) p[i] = bf16_round(p[i]);
+      round_copy(p + (size_t)off * 3 * H, p + (size_t)off * 3 * H, (size_t)cnt * 3 * H, 1);
       for (int c = 0; c < K; c++)
-        for (size_t i = ((size_t)c * n + off) * H; i < ((size_t)c * n + off + cnt) * H; i++) q[i] = bf16_round(q[i]);
+        round_copy(q + ((size_t)c * n + off) * H, q + ((size_t)c * n + off) * H, (size_t)cnt * H, 1);
     }
     /* Gates and cell (tree-lstm-cavs.cc:159-168), add order (xW + hU) + b. */
 #pragma omp parallel for schedule(static)
@@ -607,7 +646,8 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
         st[j] = go * tanhf(cc);
       }
     }
-    /* Scatter (op_impl_graphop.cu:108-161): h|c into the mailbox. */
+    /* Scatter (op_impl_graphop.cu:108-161): h|c into the mailbox (one target row per vertex). */
+#pragma omp parallel for schedule(static)
     for (int t = off; t < off + cnt; t++)
       if (fs[t] >= 0) memcpy(mailbox + (size_t)fs[t] * 2 * H, state + (size_t)t * 2 * H, sizeof(float) * 2 * H);
   }
@@ -656,6 +696,7 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
     float accb = 0.0f;
     for (int t = 0; t < n; t++) accb += dz[(size_t)t * C + c];
     dbc[c] = accb;
+#pragma omp parallel for schedule(static)
     for (int j = 0; j < H; j++) {
       float acc = 0.0f;
       for (int t = 0; t < n; t++) acc += dz[(size_t)t * C + c] * state[(size_t)t * 2 * H + j];
@@ -710,8 +751,9 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
     gemm_nt(ds + (size_t)off * H, dP_r + (size_t)off * 3 * H, Ur_iou, cnt, H, 3 * H, 0);
     for (int c = 0; c < K; c++)
       gemm_nt(dq + ((size_t)c * n + off) * H, zf_r + ((size_t)c * n + off) * H, Ur_f, cnt, H, H, 0);
-    /* Scatter(Child=c) of d(h_c|c_c) (op_decl_graphop.cc:25-41). */
+    /* Scatter(Child=c) of d(h_c|c_c) (op_decl_graphop.cc:25-41); a vertex has one parent, so targets are distinct. */
     for (int c = 0; c < K; c++)
+#pragma omp parallel for schedule(static)
       for (int t = off; t < off + cnt; t++) {
         int dst = bs[(size_t)c * n + t];
         if (dst < 0) continue;
@@ -734,6 +776,7 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
   for (int c = 0; c < K; c++)
     gemm_tn(dU + (size_t)3 * H * H, hk + (size_t)c * n * H, zf_r + (size_t)c * n * H, H, H, n, c > 0);
   /* Bias gradient = column sums, bias order i,f,u,o (tree-lstm-cavs.cc:120-123). */
+#pragma omp parallel for schedule(static)
   for (int j = 0; j < H; j++) {
     float si = 0, so = 0, su = 0, sf = 0;
     for (int t = 0; t < n; t++) {
@@ -750,11 +793,14 @@ static int treelstm_layer(const cavs_oracle_cfg *cfg, const int *level_off, cons
   if (dx_out) memcpy(dx_out, dX, sizeof(float) * (size_t)n * E);
   if (!x_dense) {
     memset(dEmb, 0, sizeof(float) * (size_t)V * E);
-    for (int t = 0; t < n; t++) {
-      int id = tok[t];
-      if (id < 0 || id >= V) id = 0;
-      for (int e = 0; e < E; e++) dEmb[(size_t)id * E + e] += dX[(size_t)t * E + e];
-    }
+    /* column blocks in parallel; within a column the rows are still added in ascending order */
+#pragma omp parallel for schedule(static)
+    for (int e0 = 0; e0 < E; e0 += 64)
+      for (int t = 0; t < n; t++) {
+        int id = tok[t];
+        if (id < 0 || id >= V) id = 0;
+        for (int e = e0; e < e0 + 64 && e < E; e++) dEmb[(size_t)id * E + e] += dX[(size_t)t * E + e];
+      }
   }
 
   free(Wr); free(Ur); free(x); free(a); free(gath); free(gates); free(state); free(mailbox);

@@ -36,9 +36,29 @@ def tables_from_schedule(s, mode=0):
 
 
 def rel_err(a, b):
+    """Max-norm relative error of a whole tensor: max|a-b| / max|b|."""
     a = np.asarray(a, np.float64).ravel()
     b = np.asarray(b, np.float64).ravel()
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def value_err(a, b):
+    """Per-value relative error: max over entries of |a-b| / (|b| + rms(b)).  An entry passes a tolerance `tol`
+    exactly when |a-b| <= tol*|b| + tol*rms(b), so entries far below the tensor's largest value are checked against
+    their own size (plus the tensor's typical size, which absorbs the rounding of sums that cancel to nearly zero)."""
+    a = np.asarray(a, np.float64).ravel()
+    b = np.asarray(b, np.float64).ravel()
+    if b.size == 0:
+        return 0.0
+    rms = float(np.sqrt(np.mean(b * b)))
+    return float((np.abs(a - b) / (np.abs(b) + max(rms, 1e-30))).max())
+
+
+def assert_close(got, want, tol, name="", value_tol=None):
+    """Both statements of "within tol relative": over the tensor's max norm and value by value."""
+    e_norm, e_val = rel_err(got, want), value_err(got, want)
+    vt = tol if value_tol is None else value_tol
+    assert e_norm < tol and e_val < vt, f"{name}: max-norm error {e_norm:.3e} (tol {tol:g}), per-value error {e_val:.3e} (tol {vt:g})"
 
 
 def chain_to_tree_params(Uc, Wc_rec, b, H):
@@ -128,3 +148,23 @@ def oracle_stack(oracle, tb, tok, label, layers, dims, V, C, K=1, gemm_bf16=Fals
         outs[li] = r
         dh = r["dX"]
     return outs
+
+
+def loss_head_reference(h, label, Wc, bc, inv_rows):
+    """float64 restatement of the reference's loss head: FullyConnected (logits = h Wc^T + bc,
+    cavs/backend/op_impl_fullyconnected_cublas.cc:33-85) + SoftmaxEntropyLoss (loss_r = -log softmax(z_r)[y_r],
+    cavs/backend/op_impl_softmax_entropy_logits_loss.cu:106-140), and their gradients (:213-250: dz = (softmax - onehot)
+    scaled by 1/rows, the upstream gradient ignored; op_impl_fullyconnected_cublas.cc:104-176: dH = dz Wc,
+    dWc = dz^T h, dbc = column sums of dz).  A row with label < 0 has no loss term (an extension of this library)."""
+    h = np.asarray(h, np.float64); Wc = np.asarray(Wc, np.float64); bc = np.asarray(bc, np.float64)
+    label = np.asarray(label)
+    z = h @ Wc.T + bc
+    z -= z.max(axis=1, keepdims=True)
+    p = np.exp(z); p /= p.sum(axis=1, keepdims=True)
+    has = label >= 0
+    rows = np.arange(h.shape[0])
+    loss = np.where(has, -np.log(p[rows, np.maximum(label, 0)]), 0.0)
+    dz = p.copy()
+    dz[rows, np.maximum(label, 0)] -= 1.0
+    dz *= has[:, None] * inv_rows
+    return dict(loss=loss, loss_sum=np.array([loss.sum()]), dH=dz @ Wc, dWc=dz.T @ h, dbc=dz.sum(axis=0))

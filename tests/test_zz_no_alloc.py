@@ -4,7 +4,9 @@ Some callers of this library must not allocate device memory at all: a host that
 whole GPU to its own pool, or a step loop where cudaMalloc / cudaFree are off limits because they
 stall the device.  For them the loss head keeps its partial-sum buffer inside the library.  This
 test calls it through the C ABI twice in a row (the buffer is shared between calls and keeps the
-previous call's contents) and compares every output with cavs_fc_softmax_xent given caller scratch.
+previous call's contents) and compares every output with cavs_fc_softmax_xent given caller scratch,
+and the second call's outputs also with a float64 restatement of the reference's loss head, so that a
+fault shared by both entry points cannot pass.
 Collected last so that a run stopping at the first failure has already run every other test.
 """
 import ctypes
@@ -13,6 +15,7 @@ import pytest
 import torch
 
 from cavs_b200 import CavsError, check, lib
+from helpers import assert_close, loss_head_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -41,15 +44,18 @@ def _run(cuda, entry, rows, H, C, seed, with_scratch):
     check(getattr(L, entry)(*args, st))
     torch.cuda.synchronize()
     out["loss_sum"] = out["loss_sum"][:1]
-    return {k: v.cpu() for k, v in out.items()}
+    ref = loss_head_reference(state[:, :H].cpu().numpy(), label.cpu().numpy(), Wc.cpu().numpy(), bc.cpu().numpy(), 1.0 / rows)
+    return {k: v.cpu() for k, v in out.items()}, ref
 
 
 @pytest.mark.parametrize("rows,H,C", [(3000, 1024, 5), (777, 152, 3)])
 def test_static_scratch_matches_caller_scratch_twice_in_a_row(cuda, rows, H, C):
     for call in range(2):                       # second call sees the first call's leftovers in the array
         seed = 100 * call + rows
-        want = _run(cuda, "cavs_fc_softmax_xent", rows, H, C, seed, with_scratch=True)
-        got = _run(cuda, "cavs_fc_softmax_xent_static", rows, H, C, seed, with_scratch=False)
+        want, _ = _run(cuda, "cavs_fc_softmax_xent", rows, H, C, seed, with_scratch=True)
+        got, ref = _run(cuda, "cavs_fc_softmax_xent_static", rows, H, C, seed, with_scratch=False)
+        for k in ref:
+            assert_close(got[k].numpy(), ref[k], 1e-5, f"call {call}: {k} against float64")
         for k in want:
             # same kernel, same grid, same reduction order: the tolerance of the other loss-head
             # checks (1e-5 relative) is kept although the results are expected to be identical
