@@ -98,6 +98,13 @@ struct cavs_treelstm {
   TcOperandMap map_Uiou_mn, map_Uf_mn, map_Uiou_k, map_Uf_k; // weights as B: [k,n] for forward, [n,k] for dgrad
   TcOperandMap map_Uiou_k64, map_Uf_k64;                     // the dgrad maps again for 64-column tiles (small levels)
   TcOperandMap map_P, map_Q, map_ds;                         // level-local outputs (rows past a level's end are scratch)
+  // Gate epilogue (bf16 mode, hidden a multiple of 64): the gate products' epilogue adds the input projection and the
+  // bias, applies sigmoid / tanh and stores the finished gates (fp16) straight into the saved-gate arena, split into
+  // G3 [N,3H] (i|o|u, the head of `gates`) and GF [N,K,H] (forget gates, behind it); P and Q are never stored, and
+  // the forward cell only forms c and h.  CAVS_GATE_EPILOGUE=0 keeps the separate pre-activation arrays.
+  bool gate_epi = false;
+  uint8_t* gates_f = nullptr;
+  TcOperandMap map_G3, map_GF;
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
   // ---- batches: two slots so the tables of the next batch can be packed and uploaded while the
   // current one executes; forward() promotes the staged slot ----
@@ -265,6 +272,8 @@ void InitModes(cavs_treelstm* e, const cavs_treelstm_config& cfg) {
   const char* v1 = std::getenv("CAVS_LEVEL1_BY_TOKEN");
   e->l1_tok = e->TokHead() && e->bf16 && !(v1 != nullptr && v1[0] == '0');
   e->l1_always = v1 != nullptr && v1[0] == '1';
+  const char* v2 = std::getenv("CAVS_GATE_EPILOGUE");
+  e->gate_epi = e->bf16 && cfg.hidden % 64 == 0 && !(v2 != nullptr && v2[0] == '0');
 }
 
 // Carves every device array out of the workspace; with base == nullptr it only sizes it.
@@ -285,6 +294,7 @@ size_t Carve(cavs_treelstm* e, void* base) {
   e->P = w.Take<uint8_t>(L * 3 * H * elt);
   e->Q = w.Take<uint8_t>(L * K * H * elt);
   e->gates = w.Take<uint8_t>(N * (3 + K) * H * elt);
+  e->gates_f = (e->gate_epi && e->gates) ? e->gates + N * 3 * H * elt : nullptr;
   e->state = w.Take<float>((N + (e->leaf_tok ? T : 0)) * 2 * H);   // per-token leaf rows follow the vertex rows
   e->mailbox = w.Take<float>(N * 2 * H);
   // d(pushed h): materialised only by the wide loss head; the fused head hands d(logits) rows (dz8) to the cell gradient
@@ -404,6 +414,8 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
     if (!rc) rc = EncodeTcOutput(&e->map_P, e->P, L, 3 * H, 3 * H, true);
     if (!rc) rc = EncodeTcOutput(&e->map_Q, e->Q, L * K, H, H, true);
     if (!rc) rc = EncodeTcOutput(&e->map_ds, e->ds, L, H, H, false);
+    if (!rc && e->gate_epi) rc = EncodeTcOutput(&e->map_G3, e->gates, N, 3 * H, 3 * H, true);      // fp16: 16-bit elements
+    if (!rc && e->gate_epi) rc = EncodeTcOutput(&e->map_GF, e->gates_f, N * K, H, H, true);
     if (rc) { delete e; return rc; }
   }
   cudaError_t err = cudaHostAlloc(reinterpret_cast<void**>(&e->h_idx), 2 * e->idx_ints * sizeof(int32_t), cudaHostAllocDefault);
@@ -755,7 +767,7 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
       ChainHint(rows <= kChainSmallRows);
       PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (4 + 4 * K + 3 + K) + 4.0 * (K + 2)) + 4), st,
            LaunchCellFwd(e->state, e->gates, e->A, e->PQT, nullptr, e->bf16, B, bt.child_st, bt.tok_slot, nt, off, rows, H, K, false, st,
-                         true, e->cfg.max_vertices));
+                         true, e->cfg.max_vertices, e->gates_f));
       continue;
     }
     // Chained launches: a kernel releases its successor early when that successor is a GEMM (one CTA per
@@ -765,6 +777,31 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     // read K child h rows (fp32) + K indices, write S and HK
     PROF(e, kProfGatherH, static_cast<double>(rows) * (4.0 * K * H + 4.0 * K + elt * (1 + K) * H), st,
          LaunchGatherChildH(e->S, e->HK, e->bf16, e->state, e->leaf_tok ? bt.child_st : bt.child, nt, off, rows, H, K, st));
+    if (e->gate_epi) {
+      // The two gate products finish the gates in their epilogues: G3[t] = act((S.U_iou + A[row(t), :3H]) + b),
+      // GF[t,c] = sigmoid((HK[t,c].U_f + A[row(t), 3H:]) + b_f); the cell then reads them back once.
+      for (int part = 0; part < 2; ++part) {
+        GemmBf16MappedArgs ga;
+        ga.out_mode = 4;
+        ga.a = part == 0 ? &e->map_S : &e->map_HK;
+        ga.b = part == 0 ? &e->map_Uiou_mn : &e->map_Uf_mn;
+        ga.a_row_off = part == 0 ? off : off * K;
+        ga.c = part == 0 ? e->gates : e->gates_f;
+        ga.ldc = part == 0 ? 3 * H : H;
+        ga.c_map = part == 0 ? &e->map_G3 : &e->map_GF;
+        ga.c_row_off = ga.a_row_off;
+        ga.m = part == 0 ? rows : rows * K; ga.n = part == 0 ? 3 * H : H; ga.k = H;
+        ga.status = e->Status();
+        ga.act_a = e->A; ga.act_a_row = bt.tok_slot; ga.act_bias = B;
+        ga.act_col0 = part == 0 ? 0 : 3 * H; ga.act_hidden = H; ga.act_rows_per_vertex = part == 0 ? 1 : K; ga.act_t_off = off;
+        if (part == 1) ChainHint(small);   // second product -> cell -> next level's gather: wide grid-stride kernels
+        PROF(e, kProfGemm, 2.0 * ga.m * ga.n * ga.k, st, GemmBf16Mapped(ga, st));
+      }
+      // read the finished gates ((3+K)H fp16) and child c (KH); write h|c (2H)
+      PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (2.0 * (3 + K) + 4.0 * (K + 2))), st,
+           LaunchCellFwdGated(e->state, e->gates, e->gates_f, e->leaf_tok ? bt.child_st : bt.child, nt, off, rows, H, K, st));
+      continue;
+    }
     const uint8_t* S_l = e->S + static_cast<size_t>(off) * H * e->elt;
     const uint8_t* HK_l = e->HK + static_cast<size_t>(off) * K * H * e->elt;
     if ((rc = Gemm(e, e->P, 3 * H, pre, S_l, H, false, U_iou, 3 * H, false, rows, 3 * H, H, false, st, &e->map_S, off, &e->map_Uiou_mn, &e->map_P))) return rc;
@@ -872,7 +909,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
                        e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
                        e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C, l == 0 ? e->A : nullptr,
                        l == 0 ? bt.tok_slot : nullptr, l == 0 ? e->params + e->OffB() : nullptr,
-                       e->leaf_tok ? bt.child_st : nullptr));
+                       e->leaf_tok ? bt.child_st : nullptr, e->gates_f));
     if (l == 0) break;
     if (l == 1 && bt.l1) {
       // The children are leaves: what they receive is summed per token first (fixed order), and the two products

@@ -172,12 +172,11 @@ __global__ void __launch_bounds__(kThreads)
 CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gates, const TP* __restrict__ A, const TP* __restrict__ P,
         const TP* __restrict__ Q, const float* __restrict__ bias, const int32_t* __restrict__ child,
         const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H, int chain_early, int store_leaf_gates,
-        int tok_base) {
+        int tok_base, typename GateType<TP>::type* __restrict__ gates_f, long long pitch3, long long pitch_f) {
   ChainRelease(chain_early);
   ChainAcquire();
   constexpr bool kFast = sizeof(TP) == 2;
   const int hv = H / V;
-  const int G = (3 + K) * H;
   const long long total = static_cast<long long>(rows) * hv;
   const long long stride = static_cast<long long>(gridDim.x) * kThreads;
   for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
@@ -218,7 +217,8 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
       gu.v[e] = TanhT<kFast>((au.v[e] + pu.v[e]) + bu.v[e]);
       cc.v[e] = gi.v[e] * gu.v[e];
     }
-    typename GateType<TP>::type* g = gates + t * G + j;
+    typename GateType<TP>::type* g = gates + t * pitch3 + j;           // i | o | u
+    typename GateType<TP>::type* gfp = gates_f + t * pitch_f + j;      // f_0 .. f_{K-1}
     // Leaves have no child cell state: their forget gates multiply zeros in the forward pass and
     // receive a zero gradient in the backward pass, so they are neither computed nor stored.
     if (!kLeaf) {
@@ -234,7 +234,7 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
           gf.v[e] = SigmoidT<kFast>((af.v[e] + q.v[e]) + bf.v[e]);
           cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
         }
-        StoreStream<V>(g + (3 + c) * H, gf);
+        StoreStream<V>(gfp + c * H, gf);
       }
     }
 #pragma unroll
@@ -242,6 +242,43 @@ CellFwd(float* __restrict__ state, typename GateType<TP>::type* __restrict__ gat
     // A leaf's gates are a function of its input-projection row alone: when the backward pass recomputes them
     // (LaunchCellBwd with A), they are not stored.
     if (!kLeaf || store_leaf_gates) { StoreStream<V>(g, gi); StoreStream<V>(g + H, go); StoreStream<V>(g + 2 * H, gu); }
+    Store<V>(state + t * 2 * H + j, hh);
+    Store<V>(state + t * 2 * H + H + j, cc);
+  }
+}
+
+// The rest of the forward cell when the gate products' epilogue has already finished the gates (bf16 mode, the
+// gate epilogue of the tensor-core GEMM): c = i o u + sum_c f_c o c_c, h = o o tanh(c).  Reads the saved gates
+// G3 [n_total, 3H] (i|o|u) and GF [n_total, K, H] and the children's cell states, writes h|c.
+template <int K, int V>
+__global__ void __launch_bounds__(kThreads)
+CellFwdGated(float* __restrict__ state, const __half* __restrict__ G3, const __half* __restrict__ GF,
+             const int32_t* __restrict__ child, int n_total, int off, int rows, int H, int chain_early) {
+  ChainRelease(chain_early);
+  ChainAcquire();
+  const int hv = H / V;
+  const long long total = static_cast<long long>(rows) * hv;
+  const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+  for (long long i = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+    const int b = static_cast<int>(i / hv), j = static_cast<int>(i % hv) * V;
+    const size_t t = static_cast<size_t>(off) + b;
+    const __half* g = G3 + t * 3 * H + j;
+    const Vec<V> gi = LoadF<V>(g), go = LoadF<V>(g + H), gu = LoadF<V>(g + 2 * H);
+    Vec<V> cc, hh;
+#pragma unroll
+    for (int e = 0; e < V; ++e) cc.v[e] = gi.v[e] * gu.v[e];
+#pragma unroll
+    for (int c = 0; c < K; ++c) {
+      const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
+      if (ch >= 0) {
+        const Vec<V> gf = LoadF<V>(GF + (t * K + c) * H + j);
+        const Vec<V> cch = LoadF<V>(state + static_cast<size_t>(ch) * 2 * H + H + j);
+#pragma unroll
+        for (int e = 0; e < V; ++e) cc.v[e] = cc.v[e] + gf.v[e] * cch.v[e];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) hh.v[e] = go.v[e] * TanhT<true>(cc.v[e]);
     Store<V>(state + t * 2 * H + j, hh);
     Store<V>(state + t * 2 * H + H + j, cc);
   }
@@ -264,7 +301,8 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
         const int32_t* __restrict__ child, const int32_t* __restrict__ parent, int n_total, int off, int rows, int H,
         const float* __restrict__ dz, const float* __restrict__ Wc, int C, int chain_early,
         const T* __restrict__ A, const int32_t* __restrict__ a_row, const float* __restrict__ bias,
-        const int32_t* __restrict__ child_state) {
+        const int32_t* __restrict__ child_state, const typename GateType<T>::type* __restrict__ gates_f, long long pitch3,
+        long long pitch_f) {
   ChainRelease(chain_early);
   ChainAcquire();
   __shared__ float fold[kThreads * 4 * V];
@@ -290,7 +328,6 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
     __syncthreads();
   }
   const int tpr = H / V;
-  const int G = (3 + K) * H;
   const int rows_per_iter = tpr <= kThreads ? kThreads / tpr : 1;
   const int r_in = tpr <= kThreads ? threadIdx.x / tpr : 0;
   const bool active = r_in < rows_per_iter;
@@ -329,7 +366,8 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
       } else {
         dOutv = LoadF<V>(dOut + t * H + j);
       }
-      const typename GateType<T>::type* g = gates + t * G + j;
+      const typename GateType<T>::type* g = gates + t * pitch3 + j;
+      const typename GateType<T>::type* gfp = gates_f + t * pitch_f + j;
       Vec<V> gi, go, gu, cown;
       if (kLeaf && A != nullptr) {
         // Leaf with recomputation: i, o, u and c = i o u follow from the input-projection row (shared by every
@@ -365,7 +403,7 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
 #pragma unroll
         for (int c = 0; c < K; ++c) {
           const int ch = __ldg(child + static_cast<size_t>(c) * n_total + t);
-          const Vec<V> gf = LoadF<V>(g + (3 + c) * H);
+          const Vec<V> gf = LoadF<V>(gfp + c * H);
           Vec<V> z = Zero<V>();
           if (ch >= 0) {
             // c of the child is read from the state array, then d(c_child) = dc * f_c goes to the
@@ -785,9 +823,19 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
   return CAVS_OK;
 }
 
+// Where the forget gates live and the row pitches (in gate elements) of the two parts of the saved gates.
+template <typename GT>
+struct GateView { GT* f; long long pitch3, pitch_f; };
+template <typename GT>
+GateView<GT> MakeGateView(const void* gates, const void* gates_f, int H, int K) {
+  GT* g = static_cast<GT*>(const_cast<void*>(gates));
+  if (gates_f != nullptr) return {static_cast<GT*>(const_cast<void*>(gates_f)), 3LL * H, static_cast<long long>(K) * H};
+  return {g + 3LL * H, (3LL + K) * H, (3LL + K) * H};
+}
+
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
-                  bool store_leaf_gates, int tok_base) {
+                  bool store_leaf_gates, int tok_base, void* gates_f) {
   CAVS_REQUIRE(tok_base < 0 || (!leaf && P != nullptr), CAVS_ERR_BAD_ARG, "treelstm_cell_fwd: per-token products apply to an internal level");
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
@@ -797,15 +845,32 @@ int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const
     if (preact_bf16) {
       using TP = __nv_bfloat16;
       auto* a = static_cast<const TP*>(A); auto* p = static_cast<const TP*>(P); auto* q = static_cast<const TP*>(Q);
-      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
-      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
+      const GateView<__half> gv = MakeGateView<__half>(gates, gates_f, H, K);
+      if (leaf) LaunchChained(CellFwd<TP, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base, gv.f, gv.pitch3, gv.pitch_f);
+      else LaunchChained(CellFwd<TP, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<__half*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base, gv.f, gv.pitch3, gv.pitch_f);
     } else {
       auto* a = static_cast<const float*>(A); auto* p = static_cast<const float*>(P); auto* q = static_cast<const float*>(Q);
-      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
-      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base);
+      const GateView<float> gv = MakeGateView<float>(gates, gates_f, H, K);
+      if (leaf) LaunchChained(CellFwd<float, K, V, true>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base, gv.f, gv.pitch3, gv.pitch_f);
+      else LaunchChained(CellFwd<float, K, V, false>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<float*>(gates), a, p, q, bias, child, a_row, n_total, off, rows, H, ChainEarly(), store_leaf_gates ? 1 : 0, tok_base, gv.f, gv.pitch3, gv.pitch_f);
     }
   });
   CAVS_LAUNCH_CHECK("treelstm_cell_fwd");
+  return CAVS_OK;
+}
+
+int LaunchCellFwdGated(float* state, const void* gates3, const void* gates_f, const int32_t* child, int n_total, int off, int rows,
+                       int H, int K, cudaStream_t st) {
+  if (int rc = CheckCommon("treelstm_cell_fwd_gated", rows, H, K)) return rc;
+  if (rows == 0) return CAVS_OK;
+  CAVS_REQUIRE(state && gates3 && gates_f && child, CAVS_ERR_BAD_ARG, "treelstm_cell_fwd_gated: null pointer");
+  const int v = VecWidth(H);
+  const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
+  DISPATCH_KV(K, v, {
+    LaunchChained(CellFwdGated<K, V>, dim3(grid), dim3(kThreads), 0, st, state, static_cast<const __half*>(gates3),
+                  static_cast<const __half*>(gates_f), child, n_total, off, rows, H, ChainEarly());
+  });
+  CAVS_LAUNCH_CHECK("treelstm_cell_fwd_gated");
   return CAVS_OK;
 }
 
@@ -819,7 +884,7 @@ int CellBwdGrid(int rows, int H) {
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st, const float* dz, const float* Wc, int C, const void* A,
-                  const int32_t* a_row, const float* bias, const int32_t* child_state) {
+                  const int32_t* a_row, const float* bias, const int32_t* child_state, const void* gates_f) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const bool head = dz != nullptr;
@@ -834,9 +899,13 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
   const size_t head_smem = head ? static_cast<size_t>(C) * H * sizeof(float) : 0;
   CAVS_REQUIRE(head_smem <= 32 * 1024, CAVS_ERR_UNSUPPORTED, "treelstm_cell_bwd: classifier above 32 KB (classes * hidden <= 8192)");
 #define CELL_BWD(TT, GT, LEAF, HEAD)                                                                                   \
-  LaunchChained(CellBwd<TT, K, V, LEAF, HEAD>, dim3(grid), dim3(kThreads), head_smem, st, static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
+  do {                                                                                                                 \
+    const GateView<GT> gv = MakeGateView<GT>(gates, gates_f, H, K);                                                    \
+    LaunchChained(CellBwd<TT, K, V, LEAF, HEAD>, dim3(grid), dim3(kThreads), head_smem, st, static_cast<TT*>(dA), static_cast<TT*>(ZF), mailbox, dB_part, dOut, \
                                                            static_cast<const GT*>(gates), state, child, parent, n_total, off,  \
-                                                           rows, H, dz, Wc, C, ChainEarly(), static_cast<const TT*>(A), a_row, bias, child_state)
+                                                           rows, H, dz, Wc, C, ChainEarly(), static_cast<const TT*>(A), a_row, bias, child_state, \
+                                                           static_cast<const GT*>(gv.f), gv.pitch3, gv.pitch_f);       \
+  } while (0)
   DISPATCH_KV(K, v, {
     if (bf16) {
       if (leaf) { if (head) CELL_BWD(__nv_bfloat16, __half, true, true); else CELL_BWD(__nv_bfloat16, __half, true, false); }

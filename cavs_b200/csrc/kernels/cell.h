@@ -21,7 +21,13 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 // a_row (optional): [n_total] row of A for each vertex (A then holds one row per distinct token).
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
-                  bool store_leaf_gates = true, int tok_base = -1);
+                  bool store_leaf_gates = true, int tok_base = -1, void* gates_f = nullptr);
+// gates_f (here and in LaunchCellBwd): NULL = the saved gates are one array [n_total, (3+K)H] (i|o|u|f_0..f_{K-1});
+// else `gates` is [n_total, 3H] (i|o|u) and gates_f [n_total, K, H] holds the forget gates -- the layout the gate
+// products write when their epilogue finishes the gates (bf16 mode).
+// The rest of the forward cell on finished gates: c = i o u + sum_c f_c o c_c, h = o o tanh(c) (fp16 gates).
+int LaunchCellFwdGated(float* state, const void* gates3, const void* gates_f, const int32_t* child, int n_total, int off, int rows,
+                       int H, int K, cudaStream_t st);
 // tok_base >= 0 (internal level whose children are all leaves with per-token states): `child` holds state rows
 // tok_base + token row, P is [tokens, 4H] = h_tok.U_iou | h_tok.U_f, Q is unused; the level's own P / Q are never formed.
 // store_leaf_gates = false (leaf levels): the gates are not saved; the backward pass must then be given A, a_row and
@@ -36,7 +42,7 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st, const float* dz = nullptr, const float* Wc = nullptr, int C = 0,
                   const void* A = nullptr, const int32_t* a_row = nullptr, const float* bias = nullptr,
-                  const int32_t* child_state = nullptr);
+                  const int32_t* child_state = nullptr, const void* gates_f = nullptr);
 // child_state (optional, [K, n_total]): rows of `state` holding the children's cell state when they differ from
 // the children's tensor ids (leaf states shared per token); the mailbox is always addressed by `child`.
 // A / a_row / bias (optional, leaf levels only): recompute i, o, u and c from the input-projection rows instead of

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <cstddef>
+#include <cstdint>
 
 namespace cavs_b200 {
 
@@ -75,6 +76,17 @@ struct GemmBf16MappedArgs {
   int* status = nullptr;
   unsigned wait_poll_limit = 0;   // see GemmBf16Args
   int withhold_loads = 0;
+  // out_mode 4 (gate epilogue): instead of pre-activations the product stores finished LSTM gates as fp16,
+  //   gate = act((product + act_a[row(t), act_col0 + n]) + bias),  t = act_t_off + r / act_rows_per_vertex,
+  // sigmoid for the i, o, f column blocks and tanh for u (columns in the order i,o,u,f, act_hidden per block, a
+  // multiple of 64); act_a: bf16 [*, 4 act_hidden] input projection with one row per vertex, or per act_a_row[t];
+  // act_bias: [4 act_hidden] fp32 in the order i,f,u,o.  Needs c_map (16-bit elements); c_row_off shifts the rows
+  // the map is written at, so that c_map can cover a whole arena.
+  const void* act_a = nullptr;
+  const int32_t* act_a_row = nullptr;
+  const float* act_bias = nullptr;
+  int act_col0 = 0, act_hidden = 0, act_rows_per_vertex = 1, act_t_off = 0;
+  int c_row_off = 0;
 };
 int EncodeTcOutput(TcOperandMap* out, void* base, long long m, long long n, long long ldc, bool bf16);
 int GemmBf16Mapped(const GemmBf16MappedArgs& args, cudaStream_t stream);

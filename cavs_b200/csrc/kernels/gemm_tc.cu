@@ -178,7 +178,14 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   if (g.m == 0 || g.n == 0) return CAVS_OK;
   CAVS_REQUIRE(g.k > 0, CAVS_ERR_BAD_ARG, "gemm_bf16: k must be positive");
   CAVS_REQUIRE(g.a && g.b && g.c, CAVS_ERR_BAD_ARG, "gemm_bf16: null pointer");
-  CAVS_REQUIRE(g.out_mode >= 0 && g.out_mode <= 3, CAVS_ERR_BAD_ARG, "gemm_bf16: bad out_mode");
+  CAVS_REQUIRE(g.out_mode >= 0 && g.out_mode <= 4, CAVS_ERR_BAD_ARG, "gemm_bf16: bad out_mode");
+  CAVS_REQUIRE(g.out_mode != tc::kGateActF16 ||
+                   (g.c_map && g.act_a && g.act_bias && g.act_hidden > 0 && g.act_hidden % 64 == 0 && g.act_col0 % 64 == 0 &&
+                    g.act_col0 + g.n <= 4 * g.act_hidden && g.act_rows_per_vertex >= 1 && std::max(1, g.splits) == 1 &&
+                    Aligned16(g.act_a) && Aligned16(g.act_bias)),
+               CAVS_ERR_BAD_ARG,
+               "gemm_bf16: the gate epilogue needs an output map, the input projection and bias (16-byte aligned), a hidden size "
+               "that is a multiple of 64 and no K split");
   CAVS_REQUIRE(g.ldc >= g.n, CAVS_ERR_BAD_ARG, "gemm_bf16: ldc < n");
   CAVS_REQUIRE(g.out_mode != tc::kScatterF32 ||
                    (g.scatter_child && g.scatter_addend && g.scatter_slots >= 1 && g.scatter_addend_ld >= g.n &&
@@ -232,6 +239,9 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   p.chain_early = ChainEarly();
   p.sc_child = g.scatter_child; p.sc_addend = g.scatter_addend; p.sc_addend_ld = g.scatter_addend_ld;
   p.sc_n_total = g.scatter_n_total; p.sc_off = g.scatter_off; p.sc_slots = std::max(1, g.scatter_slots);
+  p.act_a = g.act_a; p.act_a_row = g.act_a_row; p.act_bias = g.act_bias;
+  p.act_col0 = g.act_col0; p.act_h = g.act_hidden; p.act_rpv = std::max(1, g.act_rows_per_vertex); p.act_t_off = g.act_t_off;
+  p.c_row_off = g.c_row_off;
   if (eff_splits > 1) {
     p.c = g.scratch; p.ldc = g.n; p.split_stride = static_cast<long long>(g.m) * g.n; p.out_mode = tc::kStoreF32;
   } else {
@@ -240,13 +250,13 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
   // TMA-store epilogue: plain stores (no accumulate, no K split) into a 16-byte aligned output.
   CUtensorMap mc_local;
   const CUtensorMap* mc = &ma;   // placeholder when unused
-  const size_t c_elt = g.out_mode == tc::kStoreBf16 ? 2 : 4;
+  const size_t c_elt = (g.out_mode == tc::kStoreBf16 || g.out_mode == tc::kGateActF16) ? 2 : 4;
   p.tma_store = 0;
   if (eff_splits == 1 && g.out_mode != tc::kAccumF32 && g.out_mode != tc::kScatterF32 && Aligned16(g.c) && (g.ldc * c_elt) % 16 == 0) {
     if (g.c_map) {
       mc = reinterpret_cast<const CUtensorMap*>(g.c_map->bytes);
     } else {
-      if (int erc = EncodeC(&mc_local, g.c, g.n, g.m, g.ldc, g.out_mode == tc::kStoreBf16)) return erc;
+      if (int erc = EncodeC(&mc_local, g.c, g.n, g.m, g.ldc, c_elt == 2)) return erc;
       mc = &mc_local;
     }
     p.tma_store = 1;

@@ -20,6 +20,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -36,7 +37,7 @@ constexpr int kThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 21;
 
 enum Major : int { kMajorK = 0, kMajorMN = 1 };
-enum OutMode : int { kStoreF32 = 0, kAccumF32 = 1, kStoreBf16 = 2, kScatterF32 = 3 };
+enum OutMode : int { kStoreF32 = 0, kAccumF32 = 1, kStoreBf16 = 2, kScatterF32 = 3, kGateActF16 = 4 };
 
 struct Params {
   void* c;            // output, row-major
@@ -55,6 +56,16 @@ struct Params {
   const float* sc_addend;
   long long sc_addend_ld;
   int sc_n_total, sc_off, sc_slots;
+  // kGateActF16: the epilogue finishes the LSTM gates instead of storing pre-activations.  GEMM row r belongs to
+  // vertex t = act_t_off + r / act_rpv; column n of this product is column act_col0 + n of the gate order i,o,u,f
+  // (hidden size act_h per gate).  value = act((acc + act_a[row(t), act_col0 + n]) + bias), sigmoid for i, o, f and
+  // tanh for u, stored as fp16 through the output map at row c_row_off + r.  act_a: bf16 [*, 4 act_h] input
+  // projection, one row per vertex or per act_a_row[t]; act_bias: [4 act_h] in the order i,f,u,o.
+  const void* act_a;
+  const int32_t* act_a_row;
+  const float* act_bias;
+  int act_col0, act_h, act_rpv, act_t_off;
+  int c_row_off;      // added to the row coordinate of TMA stores (an output map over a whole arena)
   int* status;        // device word, set non-zero when a bounded wait expires
   uint32_t spin_limit;    // polls per bounded wait; 0 = kSpinLimit
   int withhold_loads;     // wait self-test: the producer issues no operand load, so every consumer wait runs out
@@ -188,14 +199,21 @@ __device__ __forceinline__ void TmaStore2d(const CUtensorMap* map, uint32_t src,
                : "memory");
 }
 // Writes this lane's 128-byte row of a staging slot: eight 16-byte words at 128-byte-swizzled positions.
-template <int kBase, bool kBf16>
+template <int kBase, int kKind>   // kKind 0: fp32 (32 columns), 1: bf16, 2: fp16 (64 columns)
 __device__ __forceinline__ void StageRow(uint32_t slot, int lane, const uint32_t (&r)[64]) {
   const uint32_t row = slot + lane * 128;
   const uint32_t sw = lane & 7;
 #pragma unroll
   for (int w = 0; w < 8; ++w) {
     uint32_t v0, v1, v2, v3;
-    if (kBf16) {   // 8 columns -> 16 bytes
+    if (kKind == 2) {   // 8 columns -> 16 bytes of fp16
+      __half2 t0 = __floats2half2_rn(__uint_as_float(r[kBase + 8 * w + 0]), __uint_as_float(r[kBase + 8 * w + 1]));
+      __half2 t1 = __floats2half2_rn(__uint_as_float(r[kBase + 8 * w + 2]), __uint_as_float(r[kBase + 8 * w + 3]));
+      __half2 t2 = __floats2half2_rn(__uint_as_float(r[kBase + 8 * w + 4]), __uint_as_float(r[kBase + 8 * w + 5]));
+      __half2 t3 = __floats2half2_rn(__uint_as_float(r[kBase + 8 * w + 6]), __uint_as_float(r[kBase + 8 * w + 7]));
+      v0 = *reinterpret_cast<uint32_t*>(&t0); v1 = *reinterpret_cast<uint32_t*>(&t1);
+      v2 = *reinterpret_cast<uint32_t*>(&t2); v3 = *reinterpret_cast<uint32_t*>(&t3);
+    } else if (kKind == 1) {   // 8 columns -> 16 bytes
       __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 0]), __uint_as_float(r[kBase + 8 * w + 1]));
       __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 2]), __uint_as_float(r[kBase + 8 * w + 3]));
       __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[kBase + 8 * w + 4]), __uint_as_float(r[kBase + 8 * w + 5]));
@@ -252,6 +270,62 @@ __device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[
         if (col0 + j < p.n) dst[j] = (acc ? dst[j] : 0.0f) + __uint_as_float(r[kBase + j]);
     }
   }
+}
+
+// Gate epilogue (kGateActF16): turns this lane's 64 accumulator columns into finished gates,
+//   gate_j = act((acc_j + a_j) + b_j),
+// and leaves them packed as 32 half2 words in r[0..32).  A 64-column step lies inside one gate block (act_h is a
+// multiple of 64).  The pre-activation is summed in fp32; the activation itself runs on packed fp16 pairs with the
+// special-function unit's tanh (one operation per two gates; sigmoid(x) = 0.5 tanh(0.5 x) + 0.5): the gates are
+// stored as fp16 anyway, and an epilogue warp has its scheduler to itself, so instruction and special-function
+// counts decide whether the epilogue hides under the next tile's products.
+__device__ __forceinline__ uint32_t TanhHalf2(uint32_t x) {
+  uint32_t y;
+  asm("tanh.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+__device__ __forceinline__ void GateActivate(const Params& p, uint32_t (&r)[64], int row, int col0) {
+  const int gcol = p.act_col0 + col0;
+  const int g = gcol / p.act_h, j = gcol - g * p.act_h;
+  const int bias_block = g == 0 ? 0 : (g == 1 ? 3 : (g == 2 ? 2 : 1));   // gates i,o,u,f <- bias i,f,u,o
+  const float* bias = p.act_bias + bias_block * p.act_h + j;
+  const int t = p.act_t_off + row / p.act_rpv;
+  const size_t ar = p.act_a_row != nullptr ? static_cast<size_t>(__ldg(p.act_a_row + t)) : static_cast<size_t>(t);
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(p.act_a) + ar * 4 * p.act_h + gcol;
+  const bool is_tanh = g == 2;
+  const __half2 half = __floats2half2_rn(0.5f, 0.5f);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const uint4 av = __ldg(reinterpret_cast<const uint4*>(a + 8 * q));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + 8 * q));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + 8 * q) + 1);
+    const float2 a01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av.x));
+    const float2 a23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av.y));
+    const float2 a45 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av.z));
+    const float2 a67 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&av.w));
+    const float av8[8] = {a01.x, a01.y, a23.x, a23.y, a45.x, a45.y, a67.x, a67.y};
+    const float bv8[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) {
+      const float x0 = (av8[e] + __uint_as_float(r[8 * q + e])) + bv8[e];
+      const float x1 = (av8[e + 1] + __uint_as_float(r[8 * q + e + 1])) + bv8[e + 1];
+      __half2 x = __floats2half2_rn(x0, x1);
+      if (!is_tanh) x = __hmul2(x, half);
+      const uint32_t th = TanhHalf2(*reinterpret_cast<uint32_t*>(&x));
+      __half2 y = *reinterpret_cast<const __half2*>(&th);
+      if (!is_tanh) y = __hfma2(y, half, half);
+      r[4 * q + e / 2] = *reinterpret_cast<uint32_t*>(&y);   // slot 4q + e/2 <= 8q + e: never ahead of the reads
+    }
+  }
+}
+// Writes this lane's 128-byte row of already packed 16-bit pairs (r[0..32)) at 128-byte-swizzled positions.
+__device__ __forceinline__ void StageRowPacked(uint32_t slot, int lane, const uint32_t (&r)[64]) {
+  const uint32_t row = slot + lane * 128;
+  const uint32_t sw = lane & 7;
+#pragma unroll
+  for (int w = 0; w < 8; ++w)
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row + ((w ^ sw) << 4)), "r"(r[4 * w]), "r"(r[4 * w + 1]),
+                 "r"(r[4 * w + 2]), "r"(r[4 * w + 3]) : "memory");
 }
 
 // Scatter epilogue.  A lane serves row i = it * 4 + lane / 8 of the warp's 32 rows (it = 0..7) and the 16-byte
@@ -452,22 +526,24 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t slots = SmemAddr(smem + S::kCOff) + (warp - 2) * 2 * S::kCSlot;
         const int row0 = m0 + quarter * 32;
         const bool bf16_out = p.out_mode == kStoreBf16;
+        const bool gate_out = p.out_mode == kGateActF16;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 64) {
           if (n0 + c0 >= p.n) break;   // warp-uniform
           uint32_t r[64];
           TmemLoad64(t_addr + c0, r);
           if (row0 < p.m) {
-            if (bf16_out) {
-              // 64 columns of bf16 = one 128-byte row: one slot, one store
+            if (bf16_out || gate_out) {
+              // 64 columns of 16-bit values = one 128-byte row: one slot, one store
+              if (gate_out && row < p.m) GateActivate(p, r, row, n0 + c0);
               if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
               __syncwarp();
               const uint32_t slot = slots + (n_stores++ & 1) * S::kCSlot;
-              StageRow<0, true>(slot, lane, r);
+              if (gate_out) StageRowPacked(slot, lane, r); else StageRow<0, 1>(slot, lane, r);
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) {
-                TmaStore2d(&map_c, slot, n0 + c0, row0);
+                TmaStore2d(&map_c, slot, n0 + c0, row0 + p.c_row_off);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
               }
             } else {
@@ -476,22 +552,22 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
               __syncwarp();
               const uint32_t slot_a = slots + (n_stores++ & 1) * S::kCSlot;
-              StageRow<0, false>(slot_a, lane, r);
+              StageRow<0, 0>(slot_a, lane, r);
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) {
-                TmaStore2d(&map_c, slot_a, n0 + c0, row0);
+                TmaStore2d(&map_c, slot_a, n0 + c0, row0 + p.c_row_off);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
               }
               if (n0 + c0 + 32 < p.n) {
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                 __syncwarp();
                 const uint32_t slot_b = slots + (n_stores++ & 1) * S::kCSlot;
-                StageRow<32, false>(slot_b, lane, r);
+                StageRow<32, 0>(slot_b, lane, r);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                  TmaStore2d(&map_c, slot_b, n0 + c0 + 32, row0);
+                  TmaStore2d(&map_c, slot_b, n0 + c0 + 32, row0 + p.c_row_off);
                   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
               }
@@ -512,8 +588,8 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           TmemLoad64(t_addr + c0, r);
           if (m0 + quarter * 32 < p.m) {
             __syncwarp();                      // the previous step has been read out of both slots
-            StageRow<0, false>(slot, lane, r);
-            StageRow<32, false>(slot + S::kCSlot, lane, r);
+            StageRow<0, 0>(slot, lane, r);
+            StageRow<32, 0>(slot + S::kCSlot, lane, r);
             __syncwarp();
             ScatterRows(p, slot, lane, n0 + c0, sc_dst, add0);
             ScatterRows(p, slot + S::kCSlot, lane, n0 + c0 + 32, sc_dst, add1);
