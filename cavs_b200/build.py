@@ -92,7 +92,7 @@ def build_host(force: bool = False) -> Path:
     newest = max(p.stat().st_mtime for p in srcs + hdrs + [LIB])
     if force or not HOST_LIB.exists() or HOST_LIB.stat().st_mtime < newest:
         cmd = [CXX, "-std=c++17", "-O2", "-fPIC", "-shared", "-Wall", f"-I{ROOT / 'include'}", f"-I{PKG}", f"-I{CUDA_HOME / 'include'}",
-               *map(str, srcs), "-o", str(HOST_LIB), f"-L{PKG}", "-lcavs_b200", f"-L{CUDA_HOME / 'lib64'}", "-lcudart",
+               *map(str, srcs), "-o", str(HOST_LIB), f"-L{PKG}", "-lcavs_b200", f"-L{CUDA_HOME / 'lib64'}", "-lcudart", "-ldl",
                "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{CUDA_HOME / 'lib64'}"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

@@ -3,11 +3,13 @@
 #include <cuda_runtime.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <set>
 #include <unordered_map>
 
+#include "cavs/frontend/cxx/generic_session.h"
 #include "cavs/util/op_util.h"
 #include "cavs_b200.h"
 
@@ -62,6 +64,21 @@ std::map<std::string, int> OpCounts(const FunctionDef& f) {
   std::map<std::string, int> c;
   for (const auto& op : f.ops()) c[op.name()]++;
   return c;
+}
+
+// True when Node() has the operator census of one of the two LSTM forms the fused engine implements.
+bool LooksLikeFusedLstm(const Program& prog) {
+  if (prog.functions.empty()) return false;
+  const auto counts = OpCounts(prog.functions.back());
+  auto cnt = [&](const char* n) { auto it = counts.find(n); return it == counts.end() ? 0 : it->second; };
+  const bool tree = cnt("Gather") == 2 && cnt("MatMul") == 4 && cnt("Sigmoid") == 4 && cnt("Tanh") == 2 && cnt("Mul") == 4;
+  const bool chain = cnt("Gather") == 1 && cnt("MatMul") == 2 && cnt("Sigmoid") == 3 && cnt("Tanh") == 2 && cnt("Mul") == 3;
+  if (!((tree || chain) && cnt("Pull") == 1 && cnt("EmbeddingLookup") == 1 && cnt("Scatter") == 1 && cnt("Push") == 1 && cnt("Concat") == 1 &&
+        cnt("Relu") == 0))
+    return false;
+  for (const auto& op : prog.ops)
+    if (op.name() == "Optimizer" && GetSingleArg<float>(op, "clip", 0.f) != 0.f) return false;   // clipping lives in the generic path
+  return true;
 }
 
 Recognised Recognise(const Program& prog) {
@@ -157,6 +174,7 @@ Recognised Recognise(const Program& prog) {
 struct Session::Impl {
   int opt = 0;
   bool compiled = false;
+  std::unique_ptr<frontend::GenericSession> generic;   // set when the program is not one of the fused forms
   Recognised r;
   cavs_treelstm_config cfg{};
   cavs_treelstm* engine = nullptr;
@@ -241,6 +259,11 @@ struct Session::Impl {
 
   void Compile() {
     const Program& prog = *Program::Get();
+    if (!LooksLikeFusedLstm(prog) || std::getenv("CAVS_GENERIC_SESSION") != nullptr) {
+      generic.reset(new frontend::GenericSession(opt));
+      compiled = true;
+      return;
+    }
     r = Recognise(prog);
     cfg.hidden = r.H; cfg.embed = r.E; cfg.vocab = r.V; cfg.classes = r.C; cfg.n_slots = r.K;
     cfg.gemm_bf16 = (opt & OPT_BF16_GEMM) ? 1 : 0;
@@ -296,19 +319,35 @@ Session::~Session() {}
 
 void Session::SetVariable(const Sym& var, const float* host, size_t count) {
   if (!impl_->compiled) impl_->Compile();
+  if (impl_->generic) { impl_->generic->SetVariable(var.output(0), host, count); return; }
   impl_->Download();
   impl_->PackVariable(var.output(0), host, count, &impl_->host_params);
   impl_->Upload();
 }
 void Session::GetVariable(const Sym& var, float* host, size_t count) {
   if (!impl_->compiled) impl_->Compile();
+  if (impl_->generic) { impl_->generic->GetVariable(var.output(0), host, count); return; }
   impl_->Download();
   impl_->UnpackVariable(var.output(0), impl_->host_params, host, count);
+}
+
+void Session::GetGradient(const Sym& var, float* host, size_t count) {
+  if (!impl_->compiled) impl_->Compile();
+  if (impl_->generic) { impl_->generic->GetGradient(var.output(0), host, count); return; }
+  std::vector<float> flat(impl_->n_params);
+  MustCuda(cudaMemcpy(flat.data(), impl_->grads, impl_->n_params * sizeof(float), cudaMemcpyDeviceToHost), "download gradients");
+  impl_->UnpackVariable(var.output(0), flat, host, count);
 }
 
 void Session::Run(std::vector<Sym> outputs, const std::initializer_list<std::pair<Sym&, void*>>& feed) {
   Impl& m = *impl_;
   if (!m.compiled) m.Compile();
+  if (m.generic) {
+    std::vector<std::pair<std::string, void*>> named;
+    for (const auto& f : feed) named.emplace_back(f.first.output(0), f.second);
+    m.generic->Run(outputs, named);
+    return;
+  }
   const Recognised& r = m.r;
   const Program& prog = *Program::Get();
   const void *graph = nullptr, *vertex = nullptr, *label = nullptr;

@@ -1,11 +1,12 @@
 // Session::Run with the reference's signature (cavs/frontend/cxx/session.h:13-30).  Where the reference
 // compiles the recorded program into a statement list and interprets the vertex function op by op per
-// level, this Session recognises the program --
+// level, this Session first tries to recognise the program --
 //     GraphOutput(Node) -> FullyConnected -> SoftmaxEntropyLoss [-> Optimizer | Reduce_mean]
 // with Node() the child-sum Tree-LSTM (apps/paper/tree-lstm-cavs.cc:129-172) or the chain LSTM
 // (apps/paper/seq-lstm-cavs.cc:62-86) -- and binds it to the fused engine behind the C ABI
-// (cavs_treelstm_*).  Any other program is a fatal error: there is no generic interpreter and no
-// CPU fallback.
+// (cavs_treelstm_*).  Any other vertex function (Tree-FC, apps/paper/tree-fc-cavs.cc:29-36, or a user's own) runs
+// operator by operator per level with run-time-compiled fused elementwise groups (generic_session.h,
+// cavs/midend/generic_function.h), on the GPU as well: there is no CPU fallback.
 //
 // Optimisation bits (cavs/proto/opt.proto:3-8): OPT_BATCHING is honoured as in the reference
 // (cavs/midend/graph_session.h:20-24) -- with it every level of the batch is one round, without it the
@@ -40,6 +41,8 @@ class Session {
   // (the reference fills every Uniform variable from the same default-seeded engine, functor_filler.h:93-97).
   void SetVariable(const Sym& var, const float* host, size_t count);
   void GetVariable(const Sym& var, float* host, size_t count);
+  // d(loss)/d(var) of the last Run, in the declared layout (after clipping, if the program clips).
+  void GetGradient(const Sym& var, float* host, size_t count);
 
  private:
   struct Impl;

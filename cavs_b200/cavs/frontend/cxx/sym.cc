@@ -106,6 +106,7 @@ Sym Sym::Optimizer(const Sym& a, std::vector<Sym> variables, float lr, float cli
 }
 Sym Sym::Sigmoid(const Sym& a, string device) { return Unary("Sigmoid", a, device); }
 Sym Sym::Tanh(const Sym& a, string device) { return Unary("Tanh", a, device); }
+Sym Sym::Relu(const Sym& a, string device) { return Unary("Relu", a, device); }
 Sym Sym::Mirror(const Sym& a) { return Unary("Mirror", a, a.device() == GPU ? "GPU" : "CPU"); }
 Sym Sym::Slice(const Sym& a, int offset, int stride) {
   CHECK(offset >= 0 && stride > 0 && offset + stride <= Count(a.shape(0))) << a.def().DebugString();

@@ -2,8 +2,8 @@
 // vertex functions and their training programs are written in.  Constructing a Sym records an
 // OpDef -- into the function being defined when FuncConf::CheckInFunc() (GraphSupport::Node()),
 // else into the main program -- exactly like the reference (cavs/frontend/cxx/sym.cc:15-55); there
-// is no protobuf serialisation and no general graph compiler behind it: Session recognises the
-// recorded program (see session.h).
+// is no protobuf serialisation behind it: Session binds the recorded program either to a fused engine or
+// to the operator-by-operator executor (see session.h).
 #ifndef CAVS_FRONTEND_CXX_SYM_H_
 #define CAVS_FRONTEND_CXX_SYM_H_
 
@@ -48,6 +48,7 @@ class Sym {
                        const string& projections = "");
   static Sym Sigmoid(const Sym& a, string device = "GPU");
   static Sym Tanh(const Sym& a, string device = "GPU");
+  static Sym Relu(const Sym& a, string device = "GPU");
   static Sym Slice(const Sym& a, int offset, int stride);
   static Sym Mirror(const Sym& a);
   static std::tuple<Sym, Sym> Split2(const Sym& a);
@@ -83,6 +84,7 @@ class Sym {
   }
   Sym Sigmoid() { return Sigmoid(*this); }
   Sym Tanh() { return Tanh(*this); }
+  Sym Relu() { return Relu(*this); }
   Sym Slice(int offset, int stride) { return Slice(*this, offset, stride); }
   Sym Mirror() { return Mirror(*this); }
   std::tuple<Sym, Sym> Split2() { return Split2(*this); }

@@ -152,4 +152,112 @@ int LaunchColumnSum(float* out, const void* x, bool bf16, long long pitch, int r
   return CAVS_OK;
 }
 
+
+namespace {
+constexpr int kSumParts = 1024;
+// out[blockIdx.x] = sum of |x| over the CTA's strided share, folded in a fixed tree: deterministic.
+__global__ void __launch_bounds__(kThreads) AbsSumStage1(float* __restrict__ partial, const float* __restrict__ x, size_t n) {
+  __shared__ float sm[kThreads];
+  float acc = 0.0f;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * kThreads)
+    acc += fabsf(x[i]);
+  sm[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = kThreads / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[blockIdx.x] = sm[0];
+}
+__global__ void AbsSumStage2(float* __restrict__ out, const float* __restrict__ partial, int parts) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float acc = 0.0f;
+    for (int i = 0; i < parts; ++i) acc += partial[i];
+    *out = acc;
+  }
+}
+__global__ void __launch_bounds__(kThreads) FillKernel(float* __restrict__ x, size_t n, float v) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * kThreads) x[i] = v;
+}
+__global__ void __launch_bounds__(kThreads) AxpyKernel(float* __restrict__ y, const float* __restrict__ x, size_t n, float a) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * kThreads)
+    y[i] = y[i] + a * x[i];
+}
+// norms[b] = ||g[off_b : off_b + len_b]||_2, one CTA per block, fixed reduction order.
+__global__ void __launch_bounds__(kThreads) BlockNormKernel(float* __restrict__ norms, const float* __restrict__ g,
+                                                           const unsigned long long* __restrict__ offs, int n_blocks) {
+  __shared__ float sm[kThreads];
+  const int b = blockIdx.x;
+  const size_t lo = offs[b], hi = offs[b + 1];
+  float acc = 0.0f;
+  for (size_t i = lo + threadIdx.x; i < hi; i += kThreads) acc += g[i] * g[i];
+  sm[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = kThreads / 2; o > 0; o >>= 1) {
+    if (threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) norms[b] = sqrtf(sm[0]);
+}
+// g *= clip / max(sum of the block norms, clip)
+__global__ void __launch_bounds__(kThreads) ClipScaleKernel(float* __restrict__ g, size_t n, const float* __restrict__ norms, int n_blocks,
+                                                           float clip) {
+  float sum = 0.0f;
+  for (int b = 0; b < n_blocks; ++b) sum += norms[b];
+  const float scale = clip / fmaxf(sum, clip);
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * kThreads) g[i] *= scale;
+}
+}  // namespace
+
 }  // namespace cavs_b200
+
+using namespace cavs_b200;
+
+extern "C" int cavs_abs_sum(float* out, const float* x, size_t count, float* scratch, void* stream) {
+  CAVS_REQUIRE(out && scratch && (x || count == 0), CAVS_ERR_BAD_ARG, "abs_sum: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int parts = static_cast<int>(std::min<size_t>(kSumParts, std::max<size_t>(1, (count + kThreads - 1) / kThreads)));
+  AbsSumStage1<<<parts, kThreads, 0, st>>>(scratch, x, count);
+  CAVS_LAUNCH_CHECK("abs_sum stage 1");
+  AbsSumStage2<<<1, 32, 0, st>>>(out, scratch, parts);
+  CAVS_LAUNCH_CHECK("abs_sum stage 2");
+  return CAVS_OK;
+}
+
+extern "C" int cavs_fill(float* x, size_t count, float value, void* stream) {
+  if (count == 0) return CAVS_OK;
+  CAVS_REQUIRE(x, CAVS_ERR_BAD_ARG, "fill: null pointer");
+  FillKernel<<<GridForElems(count, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, count, value);
+  CAVS_LAUNCH_CHECK("fill");
+  return CAVS_OK;
+}
+
+extern "C" int cavs_axpy(float* y, const float* x, size_t count, float alpha, void* stream) {
+  if (count == 0) return CAVS_OK;
+  CAVS_REQUIRE(x && y, CAVS_ERR_BAD_ARG, "axpy: null pointer");
+  AxpyKernel<<<GridForElems(count, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(y, x, count, alpha);
+  CAVS_LAUNCH_CHECK("axpy");
+  return CAVS_OK;
+}
+
+extern "C" int cavs_clip_gradients(float* g, const unsigned long long* block_offsets, int n_blocks, float clip, float* scratch,
+                                   void* stream) {
+  CAVS_REQUIRE(g && block_offsets && scratch && n_blocks >= 1 && n_blocks <= 256, CAVS_ERR_BAD_ARG, "clip_gradients: bad argument");
+  CAVS_REQUIRE(clip > 0.0f, CAVS_ERR_BAD_ARG, "clip_gradients: the threshold must be positive");
+  CAVS_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, CAVS_ERR_BAD_ARG, "clip_gradients: scratch must be 8-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // block_offsets is a host array; it travels as the head of the scratch buffer
+  unsigned long long* d_offs = reinterpret_cast<unsigned long long*>(scratch);
+  float* norms = scratch + 2 * (n_blocks + 1);
+  CAVS_CUDA(cudaMemcpyAsync(d_offs, block_offsets, sizeof(unsigned long long) * (n_blocks + 1), cudaMemcpyHostToDevice, st));
+  BlockNormKernel<<<n_blocks, kThreads, 0, st>>>(norms, g, d_offs, n_blocks);
+  CAVS_LAUNCH_CHECK("clip_gradients norms");
+  const size_t n = block_offsets[n_blocks];
+  ClipScaleKernel<<<GridForElems(n, kThreads), kThreads, 0, st>>>(g, n, norms, n_blocks, clip);
+  CAVS_LAUNCH_CHECK("clip_gradients scale");
+  return CAVS_OK;
+}
+
+extern "C" size_t cavs_clip_gradients_scratch_bytes(int n_blocks) {
+  return sizeof(float) * (2 * (static_cast<size_t>(n_blocks) + 1) + n_blocks + 8);
+}

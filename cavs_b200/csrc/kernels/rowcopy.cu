@@ -87,6 +87,28 @@ __global__ void __launch_bounds__(kThreads) ZeroWords4(uint32_t* __restrict__ ou
 
 bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Strided form: rows of `width` floats inside wider rows (pitches in floats), optional row indices on either
+// side, optional accumulation.  One warp per row.
+__global__ void __launch_bounds__(kThreads) RowCopy2d(float* __restrict__ dst, long long dst_pitch,
+                                                      const int32_t* __restrict__ dst_ids, const float* __restrict__ src,
+                                                      long long src_pitch, const int32_t* __restrict__ src_ids, int rows,
+                                                      int width, int accumulate) {
+  const int lane = threadIdx.x & 31;
+  const int warp0 = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  const int n_warps = gridDim.x * kWarpsPerCta;
+  for (int b = warp0; b < rows; b += n_warps) {
+    const int dr = dst_ids ? __ldg(dst_ids + b) : b;
+    const int sr = src_ids ? __ldg(src_ids + b) : b;
+    if (dr < 0) continue;
+    float* d = dst + static_cast<long long>(dr) * dst_pitch;
+    const float* s = sr >= 0 ? src + static_cast<long long>(sr) * src_pitch : nullptr;
+    for (int c = lane; c < width; c += 32) {
+      const float v = s ? s[c] : 0.0f;
+      d[c] = accumulate ? d[c] + v : v;
+    }
+  }
+}
+
 template <Dir kDir>
 int RowCopy(void* out, const void* inp, const int32_t* ids, int n_ids, size_t row_bytes, cudaStream_t stream,
             const char* name) {
@@ -120,6 +142,17 @@ extern "C" int cavs_gather_rows(void* out, const void* inp, const int32_t* ids, 
 extern "C" int cavs_scatter_rows(void* out, const int32_t* ids, const void* inp, int n_ids, size_t row_bytes,
                                  void* stream) {
   return RowCopy<Dir::kScatter>(out, inp, ids, n_ids, row_bytes, static_cast<cudaStream_t>(stream), "scatter_rows");
+}
+
+extern "C" int cavs_copy_rows_2d(float* dst, long long dst_pitch, const int32_t* dst_ids, const float* src, long long src_pitch,
+                                 const int32_t* src_ids, int rows, int width, int accumulate, void* stream) {
+  CAVS_REQUIRE(rows >= 0 && width >= 0 && dst_pitch >= width && src_pitch >= 0, CAVS_ERR_BAD_ARG, "copy_rows_2d: bad shape");
+  if (rows == 0 || width == 0) return CAVS_OK;
+  CAVS_REQUIRE(dst && src, CAVS_ERR_BAD_ARG, "copy_rows_2d: null pointer");
+  RowCopy2d<<<GridForWarps(rows, kWarpsPerCta), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      dst, dst_pitch, dst_ids, src, src_pitch, src_ids, rows, width, accumulate ? 1 : 0);
+  CAVS_LAUNCH_CHECK("copy_rows_2d");
+  return CAVS_OK;
 }
 
 extern "C" int cavs_zero_rows(void* out, int n_rows, size_t row_bytes, void* stream) {

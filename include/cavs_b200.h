@@ -114,6 +114,12 @@ CAVS_API int cavs_gather_rows(void* out, const void* inp, const int32_t* ids, in
  * op_impl_graphop.cu:144-157,304-318).  Extension: ids[b] < 0 skips the row.  Target rows must
  * be distinct (they are: one mailbox row per vertex). */
 CAVS_API int cavs_scatter_rows(void* out, const int32_t* ids, const void* inp, int n_ids, size_t row_bytes, void* stream);
+/* The strided form behind vertex functions that are executed op by op (Slice / Concat views of wider rows,
+ * cavs/backend/op_impl_slice_join.cu:35-149): for b < rows, dst[dst_ids[b], :width] (+)= src[src_ids[b], :width], fp32,
+ * pitches in floats; a NULL index list means row b itself, a negative source row reads zeros, a negative target row is
+ * skipped.  Target rows must be distinct. */
+CAVS_API int cavs_copy_rows_2d(float* dst, long long dst_pitch, const int32_t* dst_ids, const float* src, long long src_pitch,
+                               const int32_t* src_ids, int rows, int width, int accumulate, void* stream);
 /* out[b,:] = 0 for b < n_rows.  Replaces BatchedDynamicSelectedAssignZeroKernel, which ignores
  * the id values it is given and clears the first n rows (functor_batched_memcpy.cuh:64-75,
  * op_impl_graphop.cu:77-86). */
@@ -250,6 +256,20 @@ CAVS_API int cavs_column_sum(float* out, const void* x, int bf16, long long pitc
 CAVS_API int cavs_sgd(float* w, const float* g, size_t count, float lr, void* stream);
 /* acc += g^2; w <- w - lr*g/(sqrt(acc)+eps).  No counterpart in the reference (it registers only SGD). */
 CAVS_API int cavs_adagrad(float* w, float* acc, const float* g, size_t count, float lr, float eps, void* stream);
+/* *out = sum |x[i]|: what the reference's Reduce_sum computes (cublasSasum, cavs/backend/op_impl_blas1_cublas.cc:48-77).
+ * Fixed reduction order; scratch: 1024 floats. */
+CAVS_API int cavs_abs_sum(float* out, const float* x, size_t count, float* scratch, void* stream);
+/* x[i] = value (the gradient seed ConstOp / Fill, cavs/midend/graph_util.cc:106-112, cavs/backend/op_decl_reduction.cc:19-28). */
+CAVS_API int cavs_fill(float* x, size_t count, float value, void* stream);
+/* y += alpha * x. */
+CAVS_API int cavs_axpy(float* y, const float* x, size_t count, float alpha, void* stream);
+/* Gradient clipping as Sym::Optimizer(vars, lr, clip) asks for it (cavs/backend/op_impl_clip.cu:25-45,
+ * cavs/midend/graph_util.cc:209-225): s = the SUM of the L2 norms of the gradient blocks (one block per variable;
+ * block_offsets is a HOST array of n_blocks + 1 offsets into g), then g *= clip / max(s, clip).  The reference takes the
+ * norms with a host-synchronous cublasSnrm2; here nothing leaves the device.  scratch: cavs_clip_gradients_scratch_bytes. */
+CAVS_API size_t cavs_clip_gradients_scratch_bytes(int n_blocks);
+CAVS_API int cavs_clip_gradients(float* g, const unsigned long long* block_offsets, int n_blocks, float clip, float* scratch,
+                                 void* stream);
 /* dst (bf16) = src (fp32): shadow copies of the GEMM weights after an update. */
 CAVS_API int cavs_cast_bf16(void* dst, const float* src, size_t count, void* stream);
 

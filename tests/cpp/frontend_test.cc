@@ -3,9 +3,11 @@
 //
 //   frontend_test cpu   what Node() records (no CUDA call)
 //   frontend_test gpu   one training step of a Tree-LSTM and of a chain LSTM through Session::Run, compared with
-//                       the CPU oracle (loss per vertex, every updated Variable), 1e-5 relative
+//                       the CPU oracle (loss per vertex, every updated Variable), 1e-5 relative; once bound to the
+//                       fused engine and once run operator by operator (CAVS_GENERIC_SESSION=1)
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <tuple>
@@ -249,6 +251,13 @@ int main(int argc, char** argv) {
     TestTrainingStep(true, OPT_BATCHING | OPT_FUSION | OPT_STREAMMING);
     TestTrainingStep(false, OPT_NONE);
     TestTrainingStep(true, OPT_FUSION);
+    // The same two programs through the operator-by-operator executor (run-time-compiled elementwise groups) instead
+    // of the fused engine: same oracle, same tolerance.
+    setenv("CAVS_GENERIC_SESSION", "1", 1);
+    TestTrainingStep(false, OPT_BATCHING);
+    TestTrainingStep(true, OPT_BATCHING);
+    TestTrainingStep(false, OPT_NONE);
+    unsetenv("CAVS_GENERIC_SESSION");
   }
   if (g_failures == 0) std::printf("frontend_test %s: ok\n", mode.c_str());
   return g_failures == 0 ? 0 : 1;
