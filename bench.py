@@ -40,6 +40,17 @@ WORKLOADS = {
     "sst_treelstm": dict(batch=64, leaf_lo=2, leaf_hi=50, hidden=150, embed=300, vocab=21701, classes=5, bf16=False,
                          init_scale=0.05, lr=0.05),
 }
+# The other configurations: launch-latency-bound at their sizes (tens of levels of a few hundred rows), so their line
+# carries the measured latency floor -- the same engine stepped on a batch with the same number of levels and one
+# or two vertices per level -- beside the achieved step time.  One GPU only.
+SMALL_WORKLOADS = {
+    "chain_lm": dict(kind="chain", batch=20, len_lo=20, len_hi=20, hidden=200, embed=200, vocab=10000, layers=1, bf16=False,
+                     init_scale=0.1, optimizer="sgd", lr=1.0, unit="sequences/s"),
+    "ragged_chain_2layer": dict(kind="chain", batch=256, len_lo=10, len_hi=100, hidden=512, embed=512, vocab=10000, layers=2, bf16=False,
+                                init_scale=0.05, optimizer=None, lr=0.0, unit="sequences/s"),
+    "nary_treegru": dict(kind="gru", batch=512, leaf_lo=8, leaf_hi=128, arity=4, hidden=1024, embed=512, vocab=32000, classes=2, bf16=True,
+                         init_scale=0.05, optimizer=None, lr=0.0, unit="trees/s"),
+}
 POOL = 16            # distinct pre-generated batches cycled through by the end-to-end loop
 SEED = 0xC0FFEE00
 
@@ -230,16 +241,180 @@ def run_reference(args, wl, rank, world):
     print(json.dumps(line))
 
 
+def run_small_workload(args, name, wl):
+    """Chain LM, two stacked ragged-chain layers, N-ary Tree-GRU: step time, end-to-end time and latency floor on one GPU."""
+    import torch
+    from cavs_b200 import lib, schedule as S
+    from cavs_b200.treegru import TreeGRU
+    from cavs_b200.treelstm import TreeLSTM
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(0)
+    L = lib()
+    L.cavs_launch_count.restype = ctypes.c_ulonglong
+    H, E, V, B = wl["hidden"], wl["embed"], wl["vocab"], wl["batch"]
+    K = 1 if wl["kind"] == "chain" else wl["arity"]
+    pool_n = 8
+
+    def make(idx):
+        seed = SEED + 977 * (idx + 1) + (hash(name) & 0xffff)
+        if wl["kind"] == "chain":
+            parents = S.synth_chains(seed, B, wl["len_lo"], wl["len_hi"])
+            lens = (parents == -1).argmax(1) + 1
+            n = int(lens.sum())
+            tok = S.synth_zipf(seed + 1, 1.1, V, n)
+            lab = np.empty(n, np.int32)           # next token; the last position predicts token 0
+            off = 0
+            for ln in lens:
+                lab[off:off + ln - 1] = tok[off + 1:off + ln]; lab[off + ln - 1] = 0; off += ln
+            return parents, tok, lab, n
+        parents, is_leaf = S.synth_trees(seed, B, wl["leaf_lo"], wl["leaf_hi"], wl["arity"])
+        lens = (parents == -1).argmax(1) + 1
+        n = int(lens.sum())
+        mask = np.arange(parents.shape[1])[None, :] < lens[:, None]
+        tok = (S.synth_zipf(seed + 1, 1.1, V, parents.size).reshape(parents.shape) * is_leaf)[mask].astype(np.int32)
+        lab = np.full(n, -1, np.int32)            # root-only loss: the root is each sample's last vertex
+        lab[np.cumsum(lens) - 1] = S.synth_uniform_int(seed + 2, wl["classes"], B)
+        return parents, tok, lab, n
+
+    pool = [make(i) for i in range(pool_n)]
+    scheds = [S.Schedule().load(p[0], n_slots=K) for p in pool]
+    levels = max(s.n_levels for s in scheds)
+    # the floor batch: one sample with as many levels as the deepest batch (a chain, or a tree whose internal vertices
+    # each have one leaf child and one internal child)
+    if K == 1:
+        floor_parents = np.full((1, levels), -1, np.int32); floor_parents[0, :levels - 1] = np.arange(1, levels)
+    else:
+        m = 2 * levels - 1                        # leaf, leaf, parent, leaf, parent, ... in post-order
+        floor_parents = np.full((1, m), -1, np.int32)
+        floor_parents[0, 0] = floor_parents[0, 1] = 2
+        for v in range(2, m - 1, 2):
+            floor_parents[0, v] = v + 2; floor_parents[0, v + 1] = v + 2
+    floor_sched = S.Schedule().load(floor_parents, n_slots=K)
+    max_n = max(max(s.n_total for s in scheds), floor_sched.n_total)
+    max_rows = max(s.max_level_rows for s in scheds)
+    sc = wl["init_scale"]
+    u = lambda seed, *shape: S.synth_uniform_float(SEED + seed, sc, shape)
+    cap = dict(n_slots=K, gemm_bf16=wl["bf16"], max_vertices=max_n, max_level_rows=max_rows)
+    if wl["kind"] == "gru":
+        C = wl["classes"]
+        engines = [TreeGRU(H, E, V, C, **cap)]
+        engines[0].set_params(dict(Emb=u(1, V, E), W=u(2, E * 3 * H), U=u(3, 3 * H * H), B=np.zeros(3 * H, np.float32), Wc=u(4, C, H),
+                                   bc=np.zeros(C, np.float32)))
+    else:
+        C = V
+        n_layers = wl["layers"]
+        engines = []
+        for li in range(n_layers):
+            eng = TreeLSTM(H, E if li == 0 else H, V if li == 0 else 0, C if li == n_layers - 1 else 0, **cap)
+            Ei = E if li == 0 else H
+            eng.set_params(dict(Emb=u(10 * li + 1, V, E) if li == 0 else np.zeros(0, np.float32), W=u(10 * li + 2, Ei * 4 * H),
+                                U=u(10 * li + 3, 4 * H * H), B=np.zeros(4 * H, np.float32),
+                                Wc=u(10 * li + 4, C, H) if li == n_layers - 1 else np.zeros(0, np.float32),
+                                bc=np.zeros(C if li == n_layers - 1 else 0, np.float32)))
+            engines.append(eng)
+
+    def load(sched, tok, lab, rows):
+        for li, eng in enumerate(engines):
+            if wl["kind"] == "gru":
+                eng.load_batch(sched, tok, lab, loss_rows=rows)
+            else:
+                eng.load_batch(sched, tok if li == 0 else None, lab if li == len(engines) - 1 else None, loss_rows=rows)
+
+    def step(n_rows):
+        if wl["kind"] == "gru":
+            engines[0].forward(); engines[0].backward()
+            return
+        for li, eng in enumerate(engines):       # bottom-up: a layer's h columns feed the next layer
+            if li > 0:
+                below = engines[li - 1]
+                eng.set_dense_input(below.device_view(0, (n_rows, 2 * H))[:, :H])
+            eng.forward()
+        for li in range(len(engines) - 1, -1, -1):   # top-down: a layer's d(x) is the output gradient of the layer below
+            eng = engines[li]
+            if li < len(engines) - 1:
+                eng.set_output_grad(engines[li + 1].device_view(5, (n_rows, H)))
+            eng.backward()
+        if wl["optimizer"] == "sgd":
+            for eng in engines:
+                eng.sgd(wl["lr"])
+
+    def timed_steps(k, n_rows):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        l0 = L.cavs_launch_count()
+        a.record()
+        for _ in range(k):
+            step(n_rows)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / k, (L.cavs_launch_count() - l0) // k
+
+    warm = max(args.warmup, 3)
+    # latency floor: same engines, same level count, one or two vertices per level
+    n_floor = floor_sched.n_total
+    load(floor_sched, np.zeros(n_floor, np.int32), np.zeros(n_floor, np.int32), n_floor)
+    for _ in range(warm):
+        step(n_floor)
+    floor_ms, floor_launches = timed_steps(args.steps, n_floor)
+    # device-resident arm (tables of batch 0 in HBM)
+    load(scheds[0], pool[0][1], pool[0][2], B if wl["kind"] == "gru" else pool[0][3])
+    for _ in range(warm):
+        step(scheds[0].n_total)
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_dev, launches = timed_steps(args.steps, scheds[0].n_total)
+    loss_dev = engines[-1].read_loss()
+    # end-to-end arm: host scheduling, table upload, step and loss read-back for every batch of the pool
+    host = S.Schedule()
+
+    def e2e(k):
+        for i in range(k):
+            par, tok, lab, n = pool[i % pool_n]
+            host.load(par, n_slots=K)
+            load(host, tok, lab, B if wl["kind"] == "gru" else n)
+            step(host.n_total)
+            engines[-1].read_loss()
+    e2e(warm)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e2e(args.steps)
+    torch.cuda.synchronize()
+    ms_e2e = (time.perf_counter() - t0) * 1e3 / args.steps
+    clocks = sampler.stop()
+    up = engines[0].upload_bytes() if wl["kind"] != "gru" else 0
+    n_v = int(scheds[0].n_total)
+    line = dict(metric=f"{name}_train_{wl['unit'].split('/')[0]}_per_sec", value=B / (ms_dev * 1e-3), unit=wl["unit"], n_gpus=1, steps=args.steps,
+                warmup=warm, ms_per_step=ms_dev, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="bf16" if wl["bf16"] else "f32", data="synthetic",
+                config=dict(workload=name, batch=B, hidden=H, embed=E, vocab=V, layers=wl.get("layers", 1), child_slots=K,
+                            vertices=n_v, levels=int(scheds[0].n_levels), optimizer=wl["optimizer"] or "none (forward + backward)",
+                            l2="per-step working set below L2: the step is bound by its dependent launches, see latency_floor"),
+                e2e=dict(value=B / (ms_e2e * 1e-3), unit=wl["unit"], ms_per_step=ms_e2e, h2d_bytes_per_step=int(up), d2h_bytes_per_step=8),
+                gpu_launches=int(launches) * args.steps, gpu_launches_per_step=int(launches), loss_sum=loss_dev, clocks=clocks,
+                latency_floor=dict(ms_per_step=floor_ms, launches_per_step=int(floor_launches), levels=int(levels),
+                                   us_per_level=1e3 * floor_ms / max(levels, 1), frac_of_step=floor_ms / ms_dev,
+                                   note="the same engines stepped on one sample with the same number of levels and one or two "
+                                        "vertices per level: what the level loop costs before any data moves"),
+                roofline=dict(bound="latency", achieved=ms_dev, peak=floor_ms, unit="ms per step (achieved) vs measured latency floor",
+                              frac=floor_ms / ms_dev, traffic=None))
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dp_treelstm", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="dp_treelstm", choices=sorted(WORKLOADS) + sorted(SMALL_WORKLOADS))
     ap.add_argument("--sample-trees", type=int, default=256, help="trees per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload in SMALL_WORKLOADS:
+        if int(os.environ.get("RANK", "0")) == 0:
+            run_small_workload(args, args.workload, SMALL_WORKLOADS[args.workload])
+        return
     wl = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -76,7 +76,8 @@ def test_generic_vertex_functions_against_autograd(cuda, tmp_path):
     want_out = np.zeros((n, H))
     want_out[t2j] = out.detach().numpy()                      # fetched in job order
     assert_close(got_out, want_out, 1e-5, "Tree-FC output")
-    assert abs(float(d["fc.loss"][0]) - float(out.abs().sum())) <= 1e-5 * float(out.abs().sum())
+    want_loss = float(out.detach().abs().sum())
+    assert abs(float(d["fc.loss"][0]) - want_loss) <= 1e-5 * want_loss
     for name, g in zip(("fc.gW", "fc.gWx", "fc.gb", "fc.ghalf"), grads):
         assert_close(d[name], (scale * g).numpy().ravel(), 1e-5, name)
     for name, w, g in (("fc.W1", W, W.grad), ("fc.Wx1", Wx, Wx.grad), ("fc.b1", b, b.grad)):
