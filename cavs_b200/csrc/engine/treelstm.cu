@@ -103,6 +103,7 @@ struct cavs_treelstm {
   // G3 [N,3H] (i|o|u, the head of `gates`) and GF [N,K,H] (forget gates, behind it); P and Q are never stored, and
   // the forward cell only forms c and h.  CAVS_GATE_EPILOGUE=0 keeps the separate pre-activation arrays.
   bool gate_epi = false;
+  bool dual_gemm = true;       // small levels: both products of a level in one launch (CAVS_DUAL_GEMM=0: never)
   uint8_t* gates_f = nullptr;
   TcOperandMap map_G3, map_GF;
   float *params = nullptr, *grads = nullptr;   // flat fp32: Emb | W | U | B | Wc | bc
@@ -249,7 +250,8 @@ size_t IdxInts(const cavs_treelstm_config& c) {
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
 size_t SplitKBytes(const cavs_treelstm_config& c) {
-  if (!c.gemm_bf16) return 0;
+  // fp32 mode: room for the k-split partials of a narrow level's products (up to 16 slabs of 64 rows x 4H)
+  if (!c.gemm_bf16) return static_cast<size_t>(16) * 64 * 4 * c.hidden * sizeof(float);
   const int N = c.max_vertices, H = c.hidden, E = c.embed, K = c.n_slots;
   size_t b = GemmBf16ScratchBytes(E, 4 * H, 32);
   b = std::max(b, GemmBf16ScratchBytes(H, 3 * H, 32));
@@ -272,6 +274,8 @@ void InitModes(cavs_treelstm* e, const cavs_treelstm_config& cfg) {
   const char* v1 = std::getenv("CAVS_LEVEL1_BY_TOKEN");
   e->l1_tok = e->TokHead() && e->bf16 && !(v1 != nullptr && v1[0] == '0');
   e->l1_always = v1 != nullptr && v1[0] == '1';
+  const char* v3 = std::getenv("CAVS_DUAL_GEMM");
+  e->dual_gemm = !(v3 != nullptr && v3[0] == '0');
   const char* v2 = std::getenv("CAVS_GATE_EPILOGUE");
   e->gate_epi = e->bf16 && cfg.hidden % 64 == 0 && !(v2 != nullptr && v2[0] == '0');
 }
@@ -365,6 +369,7 @@ int Gemm(cavs_treelstm* e, void* c, long long ldc, int accumulate, const void* a
   g.a = static_cast<const float*>(a); g.a_rs = a_t ? 1 : lda; g.a_cs = a_t ? lda : 1;
   g.b = static_cast<const float*>(b); g.b_rs = b_t ? 1 : ldb; g.b_cs = b_t ? ldb : 1;
   g.m = m; g.n = n; g.k = k;
+  g.scratch = e->splitk_scratch; g.scratch_bytes = e->splitk_bytes;
   PROF(e, kProfGemm, 2.0 * m * n * k, st, GemmF32(g, st));
   return CAVS_OK;
 }
@@ -780,8 +785,9 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
     if (e->gate_epi) {
       // The two gate products finish the gates in their epilogues: G3[t] = act((S.U_iou + A[row(t), :3H]) + b),
       // GF[t,c] = sigmoid((HK[t,c].U_f + A[row(t), 3H:]) + b_f); the cell then reads them back once.
+      GemmBf16MappedArgs gp[2];
       for (int part = 0; part < 2; ++part) {
-        GemmBf16MappedArgs ga;
+        GemmBf16MappedArgs& ga = gp[part];
         ga.out_mode = 4;
         ga.a = part == 0 ? &e->map_S : &e->map_HK;
         ga.b = part == 0 ? &e->map_Uiou_mn : &e->map_Uf_mn;
@@ -794,8 +800,19 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
         ga.status = e->Status();
         ga.act_a = e->A; ga.act_a_row = bt.tok_slot; ga.act_bias = B;
         ga.act_col0 = part == 0 ? 0 : 3 * H; ga.act_hidden = H; ga.act_rows_per_vertex = part == 0 ? 1 : K; ga.act_t_off = off;
-        if (part == 1) ChainHint(small);   // second product -> cell -> next level's gather: wide grid-stride kernels
-        PROF(e, kProfGemm, 2.0 * ga.m * ga.n * ga.k, st, GemmBf16Mapped(ga, st));
+      }
+      // Levels whose two products together stay within a few waves of tiles go out as ONE launch (they are bound by
+      // launch and pipeline-fill latency, which is then paid once); larger levels keep two launches, each with the
+      // tile shape that suits it.
+      const long long tiles = static_cast<long long>((rows + 127) / 128) * ((3 * H + 255) / 256) +
+                              static_cast<long long>((rows * K + 127) / 128) * ((H + 255) / 256);
+      if (e->dual_gemm && tiles <= 3LL * SmCount()) {
+        ChainHint(small);     // the launch is followed by the cell: a wide grid-stride kernel
+        PROF(e, kProfGemm, 2.0 * gp[0].m * gp[0].n * gp[0].k + 2.0 * gp[1].m * gp[1].n * gp[1].k, st, GemmBf16MappedDual(gp[0], gp[1], st));
+      } else {
+        PROF(e, kProfGemm, 2.0 * gp[0].m * gp[0].n * gp[0].k, st, GemmBf16Mapped(gp[0], st));
+        ChainHint(small);     // second product -> cell -> next level's gather: wide grid-stride kernels
+        PROF(e, kProfGemm, 2.0 * gp[1].m * gp[1].n * gp[1].k, st, GemmBf16Mapped(gp[1], st));
       }
       // read the finished gates ((3+K)H fp16) and child c (KH); write h|c (2H)
       PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (2.0 * (3 + K) + 4.0 * (K + 2))), st,
@@ -939,7 +956,9 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     if (e->bf16) {
       // dq = Zf U_f^T with the child-gradient scatter in its epilogue: row (t, c) of the product plus ds[t] goes
       // straight to the h half of mailbox[child_c(t)] (Scatter(Child=c), cavs/backend/op_decl_graphop.cc:25-41),
-      // so dq is never stored and no separate scatter pass runs.
+      // so dq is never stored and no separate scatter pass runs.  (Making the two products independent -- the
+      // readers of a child's mailbox row adding their parent's ds row themselves -- so that they could share one
+      // launch was measured: the extra gathered read per vertex cost more than the saved launch.)
       GemmBf16MappedArgs ga;
       ga.c = e->mailbox; ga.ldc = 2 * H; ga.out_mode = 3;
       ga.a = &e->map_ZF; ga.a_row_off = off * K; ga.b = &e->map_Uf_k; ga.b_small = &e->map_Uf_k64;

@@ -81,7 +81,9 @@ struct GemmBf16MappedArgs {
   // sigmoid for the i, o, f column blocks and tanh for u (columns in the order i,o,u,f, act_hidden per block, a
   // multiple of 64); act_a: bf16 [*, 4 act_hidden] input projection with one row per vertex, or per act_a_row[t];
   // act_bias: [4 act_hidden] fp32 in the order i,f,u,o.  Needs c_map (16-bit elements); c_row_off shifts the rows
-  // the map is written at, so that c_map can cover a whole arena.
+  // the map is written at, so that c_map can cover a whole arena -- the last 32-row slab of a product is stored
+  // whole, so up to 31 arena rows behind the product's last row are overwritten with meaningless values: only for
+  // arenas whose following rows are rewritten before they are next read (the saved gates of later levels).
   const void* act_a = nullptr;
   const int32_t* act_a_row = nullptr;
   const float* act_bias = nullptr;
@@ -90,6 +92,10 @@ struct GemmBf16MappedArgs {
 };
 int EncodeTcOutput(TcOperandMap* out, void* base, long long m, long long n, long long ldc, bool bf16);
 int GemmBf16Mapped(const GemmBf16MappedArgs& args, cudaStream_t stream);
+// Two independent products of equal operand layout in ONE launch (the two gate products of a level, or its two
+// gradient products): their tiles share the persistent grid, so a small level pays the launch and pipeline-fill
+// latency once.  Each product: K-major A map, no K split, output through c_map or the scatter epilogue.
+int GemmBf16MappedDual(const GemmBf16MappedArgs& first, const GemmBf16MappedArgs& second, cudaStream_t stream);
 size_t GemmBf16ScratchBytes(int m, int n, int splits);
 int GemmBf16SplitsFor(int m, int n, int k);
 int GemmBf16SplitsForTile(int m, int n, int k, int tile_m);   // the same choice for tiles of tile_m rows
@@ -108,6 +114,12 @@ struct GemmF32Args {
   const float* b = nullptr;
   long long b_rs = 0, b_cs = 0;
   int m = 0, n = 0, k = 0;
+  // Optional scratch for splitting k across CTAs when the output has too few tiles to occupy the machine (a level of
+  // a few rows against wide weights is otherwise one long serial k loop on a handful of SMs): partial products go to
+  // scratch [splits, m, n] and are summed in split order by a second kernel.  Without scratch k is never split.
+  float* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  int k_per_split = 0;   // set by GemmF32 (0: no split)
 };
 int GemmF32(const GemmF32Args& args, cudaStream_t stream);
 

@@ -8,6 +8,9 @@
 
 #include "abi_common.h"
 #include "kernels/gemm.h"
+#include "kernels/launch.h"
+
+#include <algorithm>
 
 namespace cavs_b200 {
 namespace {
@@ -54,14 +57,19 @@ __global__ void __launch_bounds__(256) GemmF32Kernel(GemmF32Args g) {
   __shared__ float sb[2][kTK][kTN + 4];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
+  // k split: CTA z multiplies the k range [z * k_per_split, ...) and stores its partial product into slab z of the scratch
+  const int k_begin = g.k_per_split > 0 ? blockIdx.z * g.k_per_split : 0;
+  const int k_end = g.k_per_split > 0 ? min(g.k, k_begin + g.k_per_split) : g.k;
+  if (g.k_per_split > 0) { g.c = g.scratch + static_cast<size_t>(blockIdx.z) * g.m * g.n; g.ldc = g.n; g.accumulate = 0; }
+  g.k = k_end;   // the tile loaders guard against k
   float acc[4][4] = {};
   TileRegs regs;
-  LoadTile(g, m0, n0, 0, regs);
+  LoadTile(g, m0, n0, k_begin, regs);
   StoreTile(g, sa[0], sb[0], regs);
   __syncthreads();
   int cur = 0;
-  for (int k0 = 0; k0 < g.k; k0 += kTK) {
-    const bool more = k0 + kTK < g.k;
+  for (int k0 = k_begin; k0 < k_end; k0 += kTK) {
+    const bool more = k0 + kTK < k_end;
     if (more) LoadTile(g, m0, n0, k0 + kTK, regs);
 #pragma unroll
     for (int kk = 0; kk < kTK; ++kk) {
@@ -93,15 +101,46 @@ __global__ void __launch_bounds__(256) GemmF32Kernel(GemmF32Args g) {
   }
 }
 
+// C[i,j] (+)= sum over splits, in split order
+__global__ void __launch_bounds__(256) GemmF32Reduce(float* __restrict__ c, long long ldc, const float* __restrict__ part, int m, int n,
+                                                     int splits, int accumulate) {
+  const long long total = static_cast<long long>(m) * n;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<long long>(gridDim.x) * 256) {
+    float acc = 0.0f;
+    for (int z = 0; z < splits; ++z) acc += part[z * total + i];
+    float* dst = c + (i / n) * ldc + (i % n);
+    *dst = accumulate ? *dst + acc : acc;
+  }
+}
+
 }  // namespace
 
-int GemmF32(const GemmF32Args& g, cudaStream_t stream) {
+int GemmF32(const GemmF32Args& g_in, cudaStream_t stream) {
+  GemmF32Args g = g_in;
   CAVS_REQUIRE(g.m >= 0 && g.n >= 0 && g.k >= 0, CAVS_ERR_BAD_ARG, "gemm_f32: negative dimension");
   if (g.m == 0 || g.n == 0) return CAVS_OK;
   CAVS_REQUIRE(g.a && g.b && g.c, CAVS_ERR_BAD_ARG, "gemm_f32: null pointer");
   dim3 grid((g.n + kTN - 1) / kTN, (g.m + kTM - 1) / kTM);
+  // Few tiles and a long k loop: split k over enough CTAs to fill the machine once (at least 64 k per split).
+  const long long tiles = static_cast<long long>(grid.x) * grid.y;
+  int splits = 1;
+  if (g.scratch != nullptr && tiles < SmCount() && g.k >= 256) {
+    splits = static_cast<int>(std::min<long long>(std::min<long long>(16, g.k / 64), (2LL * SmCount()) / tiles));
+    while (splits > 1 && static_cast<size_t>(splits) * g.m * g.n * sizeof(float) > g.scratch_bytes) --splits;
+  }
+  g.k_per_split = 0;
+  if (splits > 1) {
+    g.k_per_split = ((g.k + splits - 1) / splits + kTK - 1) / kTK * kTK;
+    splits = (g.k + g.k_per_split - 1) / g.k_per_split;
+    grid.z = splits;
+  }
   GemmF32Kernel<<<grid, 256, 0, stream>>>(g);
   CAVS_LAUNCH_CHECK("gemm_f32");
+  if (splits > 1) {
+    GemmF32Reduce<<<GridForElems(static_cast<size_t>(g.m) * g.n, 256), 256, 0, stream>>>(g_in.c, g_in.ldc, g.scratch, g.m, g.n, splits,
+                                                                                          g_in.accumulate ? 1 : 0);
+    CAVS_LAUNCH_CHECK("gemm_f32 split reduce");
+  }
   return CAVS_OK;
 }
 

@@ -107,6 +107,22 @@ int Dispatch(int a_major, int b_major, const CUtensorMap& ma, const CUtensorMap&
 
 bool Aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+template <int kBN, int kAMajor, int kBMajor>
+int LaunchDual(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const tc::Params& p, const CUtensorMap& ma1,
+               const CUtensorMap& mb1, const CUtensorMap& mc1, const tc::Params& p1, dim3 grid, cudaStream_t stream) {
+  using S = tc::Smem<kBN, 1>;
+  auto kern = tc::GemmBf16DualKernel<kBN, kAMajor, kBMajor>;
+  static bool configured[kMaxDevices] = {};
+  const int dev = CurrentDevice();
+  if (!configured[dev]) {
+    CAVS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
+    configured[dev] = true;
+  }
+  CAVS_CUDA(LaunchChained(kern, grid, dim3(tc::kThreads), S::kBytes, stream, ma, mb, mc, p, ma1, mb1, mc1, p1));
+  CAVS_LAUNCH_CHECK("gemm_bf16 (two products)");
+  return CAVS_OK;
+}
+
 }  // namespace
 
 size_t GemmBf16ScratchBytes(int m, int n, int splits) {
@@ -188,11 +204,12 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
                "that is a multiple of 64 and no K split");
   CAVS_REQUIRE(g.ldc >= g.n, CAVS_ERR_BAD_ARG, "gemm_bf16: ldc < n");
   CAVS_REQUIRE(g.out_mode != tc::kScatterF32 ||
-                   (g.scatter_child && g.scatter_addend && g.scatter_slots >= 1 && g.scatter_addend_ld >= g.n &&
-                    std::max(1, g.splits) == 1 && g.n % 4 == 0 && g.ldc % 4 == 0 && g.scatter_addend_ld % 4 == 0 &&
-                    Aligned16(g.c) && Aligned16(g.scatter_addend)),
+                   (g.scatter_child && g.scatter_slots >= 1 && std::max(1, g.splits) == 1 && g.n % 4 == 0 && g.ldc % 4 == 0 &&
+                    Aligned16(g.c) &&
+                    (g.scatter_addend == nullptr ||
+                     (g.scatter_addend_ld >= g.n && g.scatter_addend_ld % 4 == 0 && Aligned16(g.scatter_addend)))),
                CAVS_ERR_BAD_ARG,
-               "gemm_bf16: scatter output needs the child table, 16-byte aligned addend / output rows (n, pitches multiples of 4) and no K split");
+               "gemm_bf16: scatter output needs the child table, 16-byte aligned output (and addend) rows (n, pitches multiples of 4) and no K split");
   CAVS_REQUIRE(g.a_row_off == 0 || g.a->major == tc::kMajorK, CAVS_ERR_BAD_ARG, "gemm_bf16: row offsets need a K-major A");
   int splits = std::max(1, g.splits);
   int bn = GemmBf16TileN(g.n);
@@ -278,6 +295,77 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
     CAVS_LAUNCH_CHECK("gemm_bf16 split-K reduce");
   }
   return CAVS_OK;
+}
+
+// Two independent products in one launch (see GemmBf16DualKernel).  Both: K-major A through an arena map, the same B
+// major, no K split, outputs through c_map (TMA store or gate epilogue) or the scatter epilogue.
+int GemmBf16MappedDual(const GemmBf16MappedArgs& g0, const GemmBf16MappedArgs& g1, cudaStream_t stream) {
+  const GemmBf16MappedArgs* gs[2] = {&g0, &g1};
+  if (g0.m == 0 || g0.n == 0) return GemmBf16Mapped(g1, stream);
+  if (g1.m == 0 || g1.n == 0) return GemmBf16Mapped(g0, stream);
+  for (const auto* g : gs) {
+    CAVS_REQUIRE(g->m > 0 && g->n > 0 && g->k > 0 && g->a && g->b && g->c, CAVS_ERR_BAD_ARG, "gemm_bf16 (two products): bad product");
+    CAVS_REQUIRE(std::max(1, g->splits) == 1 && g->a->major == tc::kMajorK && g->a->tile_rows == tc::kBM, CAVS_ERR_BAD_ARG,
+                 "gemm_bf16 (two products): needs K-major A maps for 128-row tiles and no K split");
+    CAVS_REQUIRE(g->out_mode == tc::kScatterF32 || g->c_map != nullptr, CAVS_ERR_BAD_ARG,
+                 "gemm_bf16 (two products): outputs go through a pre-encoded map or the scatter epilogue");
+    CAVS_REQUIRE(g->out_mode != tc::kAccumF32, CAVS_ERR_BAD_ARG, "gemm_bf16 (two products): no accumulating output");
+  }
+  CAVS_REQUIRE(g0.b->major == g1.b->major, CAVS_ERR_BAD_ARG, "gemm_bf16 (two products): the B operands must share a major");
+  // one tile width for both: 64 columns when that still fits one wave, else 256 (128 for narrow outputs)
+  const long long tiles64 = static_cast<long long>((g0.m + tc::kBM - 1) / tc::kBM) * ((g0.n + 63) / 64) +
+                            static_cast<long long>((g1.m + tc::kBM - 1) / tc::kBM) * ((g1.n + 63) / 64);
+  int bn = std::max(GemmBf16TileN(g0.n), GemmBf16TileN(g1.n));
+  const TcOperandMap* bmaps[2] = {g0.b, g1.b};
+  const bool kmajor_b = g0.b->major == tc::kMajorK;
+  if (tiles64 <= SmCount() && std::max(g0.k, g1.k) <= 64 * tc::kBK && std::min(g0.n, g1.n) > 64 &&
+      (!kmajor_b || (g0.b_small && g1.b_small && g0.b_small->tile_rows == 64 && g1.b_small->tile_rows == 64))) {
+    bn = 64;
+    if (kmajor_b) { bmaps[0] = g0.b_small; bmaps[1] = g1.b_small; }
+  }
+  for (int i = 0; i < 2; ++i)
+    CAVS_REQUIRE(bmaps[i]->major != tc::kMajorK || bmaps[i]->tile_rows == bn, CAVS_ERR_BAD_ARG,
+                 "gemm_bf16 (two products): a B map was encoded for a different N tile");
+  tc::Params ps[2];
+  const CUtensorMap* mcs[2];
+  long long n_work = 0;
+  for (int i = 0; i < 2; ++i) {
+    const GemmBf16MappedArgs& g = *gs[i];
+    tc::Params p{};
+    p.m = g.m; p.n = g.n; p.k = g.k;
+    p.kb_per_split = (g.k + tc::kBK - 1) / tc::kBK;
+    p.n_splits = 1;
+    p.a_row_off = g.a_row_off;
+    p.status = g.status;
+    p.spin_limit = g.wait_poll_limit;
+    p.withhold_loads = g.withhold_loads;
+    p.chain_early = ChainEarly();
+    p.sc_child = g.scatter_child; p.sc_addend = g.scatter_addend; p.sc_addend_ld = g.scatter_addend_ld;
+    p.sc_n_total = g.scatter_n_total; p.sc_off = g.scatter_off; p.sc_slots = std::max(1, g.scatter_slots);
+    p.act_a = g.act_a; p.act_a_row = g.act_a_row; p.act_bias = g.act_bias;
+    p.act_col0 = g.act_col0; p.act_h = g.act_hidden; p.act_rpv = std::max(1, g.act_rows_per_vertex); p.act_t_off = g.act_t_off;
+    p.c_row_off = g.c_row_off;
+    p.c = g.c; p.ldc = g.ldc; p.split_stride = 0; p.out_mode = g.out_mode;
+    p.tma_store = g.out_mode == tc::kScatterF32 ? 0 : 1;
+    CAVS_REQUIRE(g.out_mode != tc::kGateActF16 || (g.act_a && g.act_bias && g.act_hidden % 64 == 0 && g.act_col0 % 64 == 0),
+                 CAVS_ERR_BAD_ARG, "gemm_bf16 (two products): incomplete gate epilogue");
+    CAVS_REQUIRE(g.out_mode != tc::kScatterF32 || (g.scatter_child && g.n % 4 == 0 && g.ldc % 4 == 0 && Aligned16(g.c) &&
+                                                   (g.scatter_addend == nullptr || (g.scatter_addend_ld % 4 == 0 && Aligned16(g.scatter_addend)))),
+                 CAVS_ERR_BAD_ARG, "gemm_bf16 (two products): incomplete scatter epilogue");
+    ps[i] = p;
+    mcs[i] = g.c_map ? reinterpret_cast<const CUtensorMap*>(g.c_map->bytes) : reinterpret_cast<const CUtensorMap*>(g.a->bytes);
+    n_work += static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tc::kBM - 1) / tc::kBM);
+  }
+  const CUtensorMap& ma0 = *reinterpret_cast<const CUtensorMap*>(g0.a->bytes);
+  const CUtensorMap& ma1 = *reinterpret_cast<const CUtensorMap*>(g1.a->bytes);
+  const CUtensorMap& mb0 = *reinterpret_cast<const CUtensorMap*>(bmaps[0]->bytes);
+  const CUtensorMap& mb1 = *reinterpret_cast<const CUtensorMap*>(bmaps[1]->bytes);
+  dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
+#define CAVS_DUAL(BN)                                                                                                            \
+  (kmajor_b ? LaunchDual<BN, 0, 0>(ma0, mb0, *mcs[0], ps[0], ma1, mb1, *mcs[1], ps[1], grid, stream)                            \
+            : LaunchDual<BN, 0, 1>(ma0, mb0, *mcs[0], ps[0], ma1, mb1, *mcs[1], ps[1], grid, stream))
+  return bn == 256 ? CAVS_DUAL(256) : (bn == 128 ? CAVS_DUAL(128) : CAVS_DUAL(64));
+#undef CAVS_DUAL
 }
 
 int GemmBf16(const GemmBf16Args& g, cudaStream_t stream) {

@@ -65,7 +65,8 @@ struct Params {
   const int32_t* act_a_row;
   const float* act_bias;
   int act_col0, act_h, act_rpv, act_t_off;
-  int c_row_off;      // added to the row coordinate of TMA stores (an output map over a whole arena)
+  int c_row_off;      // added to the output row (an output map / pointer over a whole arena); the last 32-row slab of a
+                      // bulk-stored product may spill up to 31 rows past row m - 1 of such an arena
   int* status;        // device word, set non-zero when a bounded wait expires
   uint32_t spin_limit;    // polls per bounded wait; 0 = kSpinLimit
   int withhold_loads;     // wait self-test: the producer issues no operand load, so every consumer wait runs out
@@ -232,7 +233,7 @@ template <int kBase>
 __device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[64], int row, int col0, long long zoff) {
   if (row >= p.m || col0 >= p.n) return;
   if (p.out_mode == kStoreBf16) {
-    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c) + zoff + static_cast<long long>(row + p.c_row_off) * p.ldc + col0;
     if (col0 + 32 <= p.n && (p.ldc & 7) == 0) {
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
@@ -251,7 +252,7 @@ __device__ __forceinline__ void StoreChunk(const Params& p, const uint32_t (&r)[
         if (col0 + j < p.n) dst[j] = __float2bfloat16_rn(__uint_as_float(r[kBase + j]));
     }
   } else {
-    float* dst = static_cast<float*>(p.c) + zoff + static_cast<long long>(row) * p.ldc + col0;
+    float* dst = static_cast<float*>(p.c) + zoff + static_cast<long long>(row + p.c_row_off) * p.ldc + col0;
     const bool acc = p.out_mode == kAccumF32;
     if (col0 + 32 <= p.n && (p.ldc & 3) == 0) {
 #pragma unroll
@@ -347,7 +348,7 @@ __device__ __forceinline__ void ScatterAddends(const Params& p, int lane, int co
   const int col = col0 + (lane & 7) * 4;
 #pragma unroll
   for (int it = 0; it < 8; ++it)
-    a[it] = (dst_row[it] >= 0 && col + 4 <= p.n)
+    a[it] = (p.sc_addend != nullptr && dst_row[it] >= 0 && col + 4 <= p.n)
                 ? __ldg(reinterpret_cast<const float4*>(p.sc_addend + static_cast<long long>(add_row[it]) * p.sc_addend_ld + col))
                 : make_float4(0.f, 0.f, 0.f, 0.f);
 }
@@ -375,10 +376,13 @@ __device__ __forceinline__ void ScatterRows(const Params& p, uint32_t slot, int 
 // work item -> (tile, K-split) with the N tile index fastest, so the CTAs of one wave share A
 // row blocks through L2.  Two TMEM accumulators alternate between tiles: while the epilogue
 // warps drain one, the MMA warp already fills the other, and the TMA ring never drains.
-template <int kBN, int kAMajor, int kBMajor, int kMB = 1>
-__global__ void __launch_bounds__(kThreads, 1)
-GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_c, const Params p) {
+// kDual: the launch carries a second, independent product (its own operand / output maps and Params p1) with the
+// same tile shape and operand majors; its tiles follow the first product's in the work list, so two small products
+// of a level (the two gate products; the two gradient products) fill the machine as one launch and pay the launch
+// and pipeline-fill latency once.  The second product is never K-split.
+template <int kBN, int kAMajor, int kBMajor, int kMB, bool kDual>
+__device__ __forceinline__ void GemmBody(const CUtensorMap* ma0, const CUtensorMap* mb0, const CUtensorMap* mc0, const Params& p,
+                                         const CUtensorMap* ma1, const CUtensorMap* mb1, const CUtensorMap* mc1, const Params& p1) {
   using S = Smem<kBN, kMB>;
   static_assert(kMB == 1 || (kMB == 2 && kBN == 256), "two row blocks need both 256-column accumulators");
   constexpr int kTileM = kBM * kMB;
@@ -395,10 +399,11 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tiles_n = (p.n + kBN - 1) / kBN;
-  const int n_tiles_m = (p.m + kTileM - 1) / kTileM;
-  const int nkb_total = (p.k + kBK - 1) / kBK;
-  const int n_work = n_tiles_m * n_tiles_n * p.n_splits;
+  const Params& p_first = p;
+  const int n_tiles_n0 = (p.n + kBN - 1) / kBN;
+  const int n_work0 = ((p.m + kTileM - 1) / kTileM) * n_tiles_n0 * p.n_splits;
+  const int n_tiles_n1 = kDual ? (p1.n + kBN - 1) / kBN : 1;
+  const int n_work = n_work0 + (kDual ? ((p1.m + kTileM - 1) / kTileM) * n_tiles_n1 : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
@@ -429,10 +434,16 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (ElectOne() && !p.withhold_loads) {
       uint32_t it = 0;   // ring position, continuous across work items
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
-        const int z = w % p.n_splits, tile = w / p.n_splits;
+        const bool second = kDual && w >= n_work0;
+        const Params& q = second ? p1 : p;
+        const CUtensorMap* map_a = second ? ma1 : ma0;
+        const CUtensorMap* map_b = second ? mb1 : mb0;
+        const int wl = second ? w - n_work0 : w;
+        const int n_tiles_n = second ? n_tiles_n1 : n_tiles_n0;
+        const int z = wl % q.n_splits, tile = wl / q.n_splits;
         const int m0 = (tile / n_tiles_n) * kTileM, n0 = (tile % n_tiles_n) * kBN;
-        const int kb_begin = z * p.kb_per_split;
-        const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
+        const int kb_begin = z * q.kb_per_split;
+        const int kb_count = min(q.kb_per_split, (q.k + kBK - 1) / kBK - kb_begin);
         for (int i = 0; i < kb_count; ++i, ++it) {
           const int s = it % S::kStages;
           const uint32_t phase = (it / S::kStages) & 1;
@@ -446,16 +457,16 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (kAMajor == kMajorK) {
 #pragma unroll
             for (int mb = 0; mb < kMB; ++mb)                                          // box {64 k, 128 rows}
-              TmaLoad2d(a_dst + mb * (kBM * kBK * 2), &map_a, bar, k0, m0 + kBM * mb + p.a_row_off);
+              TmaLoad2d(a_dst + mb * (kBM * kBK * 2), map_a, bar, k0, m0 + kBM * mb + q.a_row_off);
           } else {
 #pragma unroll
-            for (int j = 0; j < kTileM / 64; ++j) TmaLoad2d(a_dst + j * 8192, &map_a, bar, m0 + 64 * j, k0);  // box {64 mn, 64 k}
+            for (int j = 0; j < kTileM / 64; ++j) TmaLoad2d(a_dst + j * 8192, map_a, bar, m0 + 64 * j, k0);  // box {64 mn, 64 k}
           }
           if (kBMajor == kMajorK) {
-            TmaLoad2d(b_dst, &map_b, bar, k0, n0);                                    // box {64 k, kBN rows}
+            TmaLoad2d(b_dst, map_b, bar, k0, n0);                                    // box {64 k, kBN rows}
           } else {
 #pragma unroll
-            for (int j = 0; j < kBN / 64; ++j) TmaLoad2d(b_dst + j * 8192, &map_b, bar, n0 + 64 * j, k0);
+            for (int j = 0; j < kBN / 64; ++j) TmaLoad2d(b_dst + j * 8192, map_b, bar, n0 + 64 * j, k0);
           }
         }
       }
@@ -468,9 +479,11 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       constexpr uint32_t b_step = (kBMajor == kMajorK) ? (kUmmaK * 2 >> 4) : (kUmmaK * 128 >> 4);
       uint32_t it = 0, t_local = 0;
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++t_local) {
-        const int z = w % p.n_splits;
-        const int kb_begin = z * p.kb_per_split;
-        const int kb_count = min(p.kb_per_split, nkb_total - kb_begin);
+        const bool second = kDual && w >= n_work0;
+        const Params& q = second ? p1 : p;
+        const int z = (second ? w - n_work0 : w) % q.n_splits;
+        const int kb_begin = z * q.kb_per_split;
+        const int kb_count = min(q.kb_per_split, (q.k + kBK - 1) / kBK - kb_begin);
         // kMB = 1: two accumulators alternate between tiles; kMB = 2: one accumulator pair, reused by every tile
         const uint32_t acc = kMB == 2 ? 0 : (t_local & 1), acc_phase = kMB == 2 ? (t_local & 1) : ((t_local >> 1) & 1);
         ok = MbarWait(SmemAddr(acc_empty + acc), acc_phase ^ 1, spin);   // epilogue has drained this accumulator
@@ -504,7 +517,12 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t t_local = 0;
     uint32_t n_stores = 0;   // bulk stores issued by this warp; picks the staging slot (alternating)
     for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++t_local) {
-      const int z = w % p.n_splits, tile = w / p.n_splits;
+      const bool second = kDual && w >= n_work0;
+      const Params& p = second ? p1 : p_first;          // this work item's product (shadows the first product's)
+      const CUtensorMap* map_c = second ? mc1 : mc0;
+      const int wl = second ? w - n_work0 : w;
+      const int n_tiles_n = second ? n_tiles_n1 : n_tiles_n0;
+      const int z = wl % p.n_splits, tile = wl / p.n_splits;
       const int m0_tile = (tile / n_tiles_n) * kTileM, n0 = (tile % n_tiles_n) * kBN;
       const uint32_t acc = kMB == 2 ? 0 : (t_local & 1), acc_phase = kMB == 2 ? (t_local & 1) : ((t_local >> 1) & 1);
       int sc_dst[8], sc_add[8];
@@ -543,7 +561,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) {
-                TmaStore2d(&map_c, slot, n0 + c0, row0 + p.c_row_off);
+                TmaStore2d(map_c, slot, n0 + c0, row0 + p.c_row_off);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
               }
             } else {
@@ -556,7 +574,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
               if (lane == 0) {
-                TmaStore2d(&map_c, slot_a, n0 + c0, row0 + p.c_row_off);
+                TmaStore2d(map_c, slot_a, n0 + c0, row0 + p.c_row_off);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
               }
               if (n0 + c0 + 32 < p.n) {
@@ -567,7 +585,7 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
-                  TmaStore2d(&map_c, slot_b, n0 + c0 + 32, row0 + p.c_row_off);
+                  TmaStore2d(map_c, slot_b, n0 + c0 + 32, row0 + p.c_row_off);
                   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
               }
@@ -612,13 +630,28 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (lane == 0) MbarArrive(SmemAddr(acc_empty + acc));
     }
   }
-  if (warp >= 2 && lane == 0 && p.tma_store) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  if (warp >= 2 && lane == 0 && (p.tma_store || (kDual && p1.tma_store))) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   if (!ok && p.status != nullptr) atomicExch(p.status, 1);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * kBN));
   }
+}
+
+template <int kBN, int kAMajor, int kBMajor, int kMB = 1>
+__global__ void __launch_bounds__(kThreads, 1)
+GemmBf16Kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, const Params p) {
+  GemmBody<kBN, kAMajor, kBMajor, kMB, false>(&map_a, &map_b, &map_c, p, &map_a, &map_b, &map_c, p);
+}
+
+template <int kBN, int kAMajor, int kBMajor>
+__global__ void __launch_bounds__(kThreads, 1)
+GemmBf16DualKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_c, const Params p, const __grid_constant__ CUtensorMap map_a1,
+                   const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_c1, const Params p1) {
+  GemmBody<kBN, kAMajor, kBMajor, 1, true>(&map_a, &map_b, &map_c, p, &map_a1, &map_b1, &map_c1, p1);
 }
 
 }  // namespace tc
