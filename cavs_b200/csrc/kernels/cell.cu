@@ -523,7 +523,6 @@ TokenGradChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t*
   T* final_row = direct >= 0 ? out + static_cast<size_t>(direct) * width : nullptr;
   if ((rows_sm[0] & (kOrderNoDh - 1)) >= lg.n_leaf) {
     // internal vertices: sum the stored rows
-#pragma unroll 2
     for (int e = threadIdx.x * V; e < width; e += kThreads * V) {
       Vec<V> acc[4];
 #pragma unroll
@@ -746,9 +745,6 @@ LinkSumChunks(float* __restrict__ partial, T* __restrict__ out, const int32_t* _
   const int direct = chunk_out[chunk];
   float* mine = partial + static_cast<size_t>(chunk) * width;
   T* final_row = direct >= 0 ? out + static_cast<size_t>(direct) * width : nullptr;
-  // Most chunks are short (a few links of a rare token): the column steps are unrolled so that the row loads of all
-  // of a thread's steps are in flight together instead of one dependent round trip per step.
-#pragma unroll 4
   for (int e = threadIdx.x * V; e < width; e += kThreads * V) {
     const bool own = e >= 3 * H;                       // the forget-gate block comes from the link's own ZF row
     const T* base = own ? ZF + (e - 3 * H) : dA + e;
