@@ -7,6 +7,15 @@ Small, self-contained cases of the library's kernels, sized for profiler capture
     python -m cavs_b200.cases loss    the fused loss head on 65536 rows of hidden size 1024, 5 classes
     python -m cavs_b200.cases cell    one interior level of 32768 two-child vertices (hidden 1024, 2 slots, bf16 mode):
                                       child-state gather, cell forward, cell backward, child-gradient scatter
+    python -m cavs_b200.cases level   three training steps of the Tree-LSTM engine on 32768 two-leaf trees with level 1 run per
+                                      vertex (CAVS_LEVEL1_BY_TOKEN=0): one interior level of 32768 rows through exactly the
+                                      kernels of the benchmark step's levels from 2 up -- child-state gather, the two gate
+                                      products with the gate epilogue, the light forward cell, the backward cell with the
+                                      fused loss-head gradient, the two gradient products (hidden 1024, bf16, ~3 GB)
+    python -m cavs_b200.cases gru     three forward + backward passes of the Tree-GRU engine on 16384 trees of 2..4 leaves
+                                      under one root (hidden 1024, embedding 512, 4 child slots, bf16): one interior level
+    python -m cavs_b200.cases rows    the graph ops' row kernels: gather and scatter of 88320 rows of 8 KB (h|c of hidden 1024)
+                                      through a random index list, three times each (1.4 GB)
     python -m cavs_b200.cases shard   two training steps of the Tree-LSTM engine on one rank's shard of the
                                       benchmark workload at 8 GPUs (512 trees, ~66 k vertices, ~4 GB);
                                       `shard 50` also times 50 further steps with CUDA events
@@ -131,6 +140,67 @@ def shard(steps: int = 2) -> None:
         print("ms_per_step", a.elapsed_time(b) / steps)
 
 
+def rows(iters: int = 3) -> None:
+    L, dev = lib(), torch.device("cuda")
+    n, n_src, row_bytes = 88320, 176640, 8192
+    ids = torch.randperm(n_src, device=dev)[:n].to(torch.int32)
+    src = torch.randn((n_src, row_bytes // 4), device=dev)
+    dst = torch.empty((n, row_bytes // 4), device=dev)
+    for _ in range(iters):
+        assert L.cavs_gather_rows(_p(dst), _p(src), _p(ids), n, ctypes.c_size_t(row_bytes), _st()) == 0, L.cavs_last_error()
+        assert L.cavs_scatter_rows(_p(src), _p(ids), _p(dst), n, ctypes.c_size_t(row_bytes), _st()) == 0, L.cavs_last_error()
+    torch.cuda.synchronize()
+
+
+def level(steps: int = 3) -> None:
+    import os
+    import numpy as np
+    os.environ["CAVS_LEVEL1_BY_TOKEN"] = "0"
+    H, E, V, C, trees = 1024, 1024, 50000, 5, 32768
+    parents = np.full((trees, 3), -1, np.int32)
+    parents[:, 0] = parents[:, 1] = 2                      # two leaves under one root
+    tok = np.zeros((trees, 3), np.int32)
+    tok[:, :2] = S.synth_zipf(5, 1.1, V, 2 * trees).reshape(trees, 2)
+    lab = S.synth_uniform_int(6, C, 3 * trees)
+    s = S.Schedule().load(parents)
+    eng = TreeLSTM(H, E, V, C, gemm_bf16=True, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+    u = lambda seed, *shape: S.synth_uniform_float(seed, 0.05, shape)
+    eng.set_params(dict(Emb=u(1, V, E), W=u(2, E * 4 * H), U=u(3, 4 * H * H), B=np.zeros(4 * H, np.float32), Wc=u(4, C, H),
+                        bc=np.zeros(C, np.float32)))
+    eng.load_batch(s, tok.reshape(-1), lab)
+    for _ in range(steps):
+        eng.forward()
+        eng.backward()
+    print("loss", eng.read_loss(), "vertices", s.n_total, "levels", s.n_levels, "level rows", np.diff(s.level_off).tolist())
+
+
+def gru(steps: int = 3) -> None:
+    import numpy as np
+    from cavs_b200.treegru import TreeGRU
+    H, E, V, C, trees, K = 1024, 512, 32000, 2, 16384, 4
+    leaves = 2 + (np.arange(trees) % 3)                    # 2, 3 or 4 leaves under one root
+    parents = np.full((trees, 5), -1, np.int32)
+    tok = np.zeros((trees, 5), np.int32)
+    for k in (2, 3, 4):
+        rows = leaves == k
+        parents[rows, :k] = k
+        tok[rows, :k] = S.synth_zipf(5 + k, 1.1, V, int(rows.sum()) * k).reshape(-1, k)
+    lens = leaves + 1
+    mask = np.arange(5)[None, :] < lens[:, None]
+    lab = np.full(int(lens.sum()), -1, np.int32)
+    lab[np.cumsum(lens) - 1] = S.synth_uniform_int(9, C, trees)
+    s = S.Schedule().load(parents, n_slots=K)
+    eng = TreeGRU(H, E, V, C, n_slots=K, gemm_bf16=True, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
+    u = lambda seed, *shape: S.synth_uniform_float(seed, 0.05, shape)
+    eng.set_params(dict(Emb=u(1, V, E), W=u(2, E * 3 * H), U=u(3, 3 * H * H), B=np.zeros(3 * H, np.float32), Wc=u(4, C, H),
+                        bc=np.zeros(C, np.float32)))
+    eng.load_batch(s, tok[mask].astype(np.int32), lab, loss_rows=trees)
+    for _ in range(steps):
+        eng.forward()
+        eng.backward()
+    print("loss", eng.read_loss(), "vertices", s.n_total, "levels", s.n_levels, "level rows", np.diff(s.level_off).tolist())
+
+
 def unbatched(steps: int = 10) -> None:
     import numpy as np
     H, E, V, C, batch = 150, 300, 21701, 5, 64
@@ -165,6 +235,6 @@ def unbatched(steps: int = 10) -> None:
 
 
 if __name__ == "__main__":
-    fn = {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard, "unbatched": unbatched}[sys.argv[1]]
+    fn = {"gemm": gemm, "loss": loss, "cell": cell, "shard": shard, "unbatched": unbatched, "level": level, "gru": gru, "rows": rows}[sys.argv[1]]
     fn(*(int(a) for a in sys.argv[2:3]))   # optional iteration / step count
     print("ok", sys.argv[1])

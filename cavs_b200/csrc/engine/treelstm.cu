@@ -23,9 +23,11 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <thread>
 #include <vector>
@@ -135,6 +137,20 @@ struct cavs_treelstm {
   // weight-gradient products still run; comm_done marks the end of that reduction
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t comm_done = nullptr;
+  // cavs_treelstm_stage_async: one helper thread per engine schedules and packs the next batch while the caller's
+  // thread enqueues the current step; forward() joins the pending request before it promotes the staged tables.
+  struct Stager {
+    std::thread thread;
+    std::mutex mu;
+    std::condition_variable cv;
+    bool has_job = false, busy = false, quit = false;
+    int device = 0, status = CAVS_OK;
+    std::string error;
+    cavs_sched* sched = nullptr;
+    const int32_t *parents = nullptr, *tok = nullptr, *label = nullptr;
+    int batch = 0, max_len = 0, loss_rows = 0;
+  };
+  Stager* stager = nullptr;
   bool slot_used[2] = {false, false};
   std::vector<int32_t> bucket, slot_of_token, leaf_count, link_bucket;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
@@ -448,6 +464,15 @@ extern "C" int cavs_treelstm_create(const cavs_treelstm_config* cfg, void* works
 
 extern "C" void cavs_treelstm_destroy(cavs_treelstm* e) {
   if (!e) return;
+  if (e->stager) {
+    {
+      std::lock_guard<std::mutex> lock(e->stager->mu);
+      e->stager->quit = true;
+    }
+    e->stager->cv.notify_all();
+    if (e->stager->thread.joinable()) e->stager->thread.join();
+    delete e->stager;
+  }
   if (e->h_idx) cudaFreeHost(e->h_idx);
   for (cudaEvent_t ev : e->ev_pool) cudaEventDestroy(ev);
   for (int i = 0; i < 2; ++i) {
@@ -709,6 +734,7 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
 extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
   CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_forward: parameters not bound");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (int rc = cavs_treelstm_stage_wait(e)) return rc;   // a batch being staged by the helper thread
   if (e->staged >= 0) {
     e->active = e->staged;
     e->staged = -1;
@@ -1071,6 +1097,55 @@ extern "C" int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_
   CAVS_REQUIRE(e && s, CAVS_ERR_BAD_ARG, "treelstm_stage: null handle");
   if (int rc = cavs_sched_load(s, parents, batch, max_len, e->cfg.n_slots)) return rc;
   return cavs_treelstm_load_batch(e, s, tok_job, label_job, loss_rows, nullptr);
+}
+
+extern "C" int cavs_treelstm_stage_async(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
+                                         const int32_t* tok_job, const int32_t* label_job, int loss_rows) {
+  CAVS_REQUIRE(e && s && parents, CAVS_ERR_BAD_ARG, "treelstm_stage_async: null pointer");
+  if (int rc = cavs_treelstm_stage_wait(e)) return rc;   // one request at a time
+  if (e->stager == nullptr) {
+    e->stager = new cavs_treelstm::Stager();
+    CAVS_CUDA(cudaGetDevice(&e->stager->device));
+    cavs_treelstm::Stager* w = e->stager;
+    w->thread = std::thread([e, w] {
+      cudaSetDevice(w->device);
+      std::unique_lock<std::mutex> lock(w->mu);
+      for (;;) {
+        w->cv.wait(lock, [w] { return w->has_job || w->quit; });
+        if (w->quit) return;
+        w->has_job = false;
+        lock.unlock();
+        const int rc = cavs_treelstm_stage(e, w->sched, w->parents, w->batch, w->max_len, w->tok, w->label, w->loss_rows);
+        const std::string msg = rc ? cavs_last_error() : "";
+        lock.lock();
+        w->status = rc;
+        w->error = msg;
+        w->busy = false;
+        w->cv.notify_all();
+      }
+    });
+  }
+  cavs_treelstm::Stager* w = e->stager;
+  {
+    std::lock_guard<std::mutex> lock(w->mu);
+    w->sched = s; w->parents = parents; w->tok = tok_job; w->label = label_job;
+    w->batch = batch; w->max_len = max_len; w->loss_rows = loss_rows;
+    w->has_job = true; w->busy = true;
+  }
+  w->cv.notify_all();
+  return CAVS_OK;
+}
+
+extern "C" int cavs_treelstm_stage_wait(cavs_treelstm* e) {
+  CAVS_REQUIRE(e, CAVS_ERR_BAD_ARG, "treelstm_stage_wait: null handle");
+  if (e->stager == nullptr) return CAVS_OK;
+  cavs_treelstm::Stager* w = e->stager;
+  std::unique_lock<std::mutex> lock(w->mu);
+  w->cv.wait(lock, [w] { return !w->busy; });
+  const int rc = w->status;
+  w->status = CAVS_OK;
+  if (rc) return Fail(rc, "treelstm_stage_async: " + w->error);
+  return CAVS_OK;
 }
 
 extern "C" int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimizer, float* opt_state, float lr, float eps,

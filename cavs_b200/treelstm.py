@@ -91,6 +91,21 @@ class TreeLSTM:
         sched._refresh()
         self.n = sched.n_scheduled
 
+    def stage_async(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0) -> None:
+        """stage() on the engine's helper thread: returns at once; the next step() / forward() waits for it.  The arrays
+        are kept alive here until then."""
+        assert parents.dtype == np.int32 and parents.flags.c_contiguous
+        self._staging = (sched, parents, tok_job, label_job)
+        check(lib().cavs_treelstm_stage_async(self._h, sched._h, ptr(parents), parents.shape[0], parents.shape[1],
+                                              ptr(tok_job) if self.cfg.vocab else ptr(None),
+                                              ptr(label_job) if self.cfg.classes else ptr(None), loss_rows))
+
+    def stage_wait(self) -> None:
+        check(lib().cavs_treelstm_stage_wait(self._h))
+        if getattr(self, "_staging", None) is not None:
+            self._staging[0]._refresh()
+            self.n = self._staging[0].n_scheduled
+
     OPT_NONE, OPT_SGD, OPT_ADAGRAD = 0, 1, 2
 
     def step(self, comm=None, optimizer: int = 0, opt_state: torch.Tensor | None = None, lr: float = 0.0, eps: float = 1e-10) -> None:

@@ -332,6 +332,14 @@ CAVS_API int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, con
  * in one call: everything the host does per batch before the device step. */
 CAVS_API int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
                                  const int32_t* tok_job, const int32_t* label_job, int loss_rows);
+/* The same on a helper thread of the engine: returns at once, so that the caller's thread can enqueue the step of the
+ * batch in flight while this one is scheduled and packed (the host side of a step is then the longer of the two, not
+ * their sum).  The arrays must stay valid until the request has finished; the next cavs_treelstm_forward / _step (or
+ * cavs_treelstm_stage_wait, which also reports the request's status) waits for it.  One request at a time; `s` must not
+ * be used by the caller until then. */
+CAVS_API int cavs_treelstm_stage_async(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
+                                       const int32_t* tok_job, const int32_t* label_job, int loss_rows);
+CAVS_API int cavs_treelstm_stage_wait(cavs_treelstm* e);
 /* One training step in one call: forward, backward, the sum of the gradients over the ranks of `comm` (NULL or a
  * world of one: none) and the update of the flat parameter buffer -- optimizer 0: none (gradients only), 1: SGD,
  * 2: Adagrad with accumulator opt_state [param_count] -- followed by the refresh of the bf16 weight copies.  What

@@ -450,3 +450,40 @@ def test_expired_device_wait_surfaces_as_timeout(cuda):
     torch.cuda.synchronize()
     want = a.float() @ b.float()
     assert float((c - want).abs().max() / want.abs().max()) < 1e-5
+
+
+def test_staging_on_the_helper_thread_gives_the_same_steps(cuda):
+    # stage_async schedules and packs batch i+1 on the engine's helper thread while this thread enqueues step i; the
+    # results must be those of the synchronous sequence, bit for bit, and a malformed batch must surface at the wait.
+    from cavs_b200 import CavsError
+    H, E, V, C = 64, 64, 300, 5
+    params = make_params(31, H, E, V, C, scale=0.08, bias_scale=0.03)
+    batches = [make_tree_batch(700 + i, b, 2, hi, V, C) for i, (b, hi) in enumerate([(20, 30), (3, 4), (25, 40), (9, 12)])]
+    cap = dict(gemm_bf16=True, max_vertices=4096, max_level_rows=4096)
+
+    def run(async_mode):
+        eng = TreeLSTM(H, E, V, C, **cap)
+        eng.set_params(params)
+        s = S.Schedule()
+        keep = [(np.ascontiguousarray(p), np.ascontiguousarray(t), np.ascontiguousarray(l)) for p, t, l in batches]
+        out = []
+        if async_mode:
+            eng.stage_async(s, *keep[0])
+        for i in range(len(keep)):
+            if not async_mode:
+                eng.stage(s, *keep[i])
+            eng.step(None, eng.OPT_SGD, None, 0.05)        # waits for the pending request, promotes, runs the step
+            if async_mode and i + 1 < len(keep):
+                eng.stage_async(s, *keep[i + 1])
+            out.append((eng.read_loss(), eng.grads.cpu().numpy().copy()))
+        return out
+
+    for (la, ga), (lb, gb) in zip(run(True), run(False)):
+        assert la == lb and np.array_equal(ga, gb)
+    eng = TreeLSTM(H, E, V, C, **cap)
+    eng.set_params(params)
+    bad = np.array([[5, 5, -1, -1]], np.int32)             # parent index out of range
+    eng.stage_async(S.Schedule(), bad, np.zeros(4, np.int32), np.zeros(4, np.int32))
+    with pytest.raises(CavsError) as e:
+        eng.stage_wait()
+    assert e.value.status == 2
