@@ -53,7 +53,7 @@ enum class Kind { kTreeLstm, kChainLstm };
 struct Recognised {
   Kind kind;
   int H = 0, E = 0, V = 0, C = 0, K = 0, max_vertices = 0;
-  float lr = 0.f;
+  float lr = 0.f, clip = 0.f;
   bool has_optimizer = false;
   std::string graph_ph, vertex_ph, label_ph;
   std::string emb, w, u, b, fc_w, fc_b;   // Variable tensor names (chain LSTM: w == u == the joint weight variable)
@@ -76,8 +76,6 @@ bool LooksLikeFusedLstm(const Program& prog) {
   if (!((tree || chain) && cnt("Pull") == 1 && cnt("EmbeddingLookup") == 1 && cnt("Scatter") == 1 && cnt("Push") == 1 && cnt("Concat") == 1 &&
         cnt("Relu") == 0))
     return false;
-  for (const auto& op : prog.ops)
-    if (op.name() == "Optimizer" && GetSingleArg<float>(op, "clip", 0.f) != 0.f) return false;   // clipping lives in the generic path
   return true;
 }
 
@@ -163,7 +161,8 @@ Recognised Recognise(const Program& prog) {
       r.optimizer = op.output(0);
       r.has_optimizer = true;
       r.lr = GetSingleArg<float>(op, "lr");
-      CHECK(GetSingleArg<float>(op, "clip", 0.f) == 0.f) << "gradient clipping is not supported";
+      r.clip = GetSingleArg<float>(op, "clip", 0.f);
+      CHECK(r.clip >= 0.f);
     }
   }
   return r;
@@ -181,6 +180,7 @@ struct Session::Impl {
   cavs_sched* sched = nullptr;
   void* workspace = nullptr;
   float *params = nullptr, *grads = nullptr;   // device, engine layout: Emb | W | U | B | Wc | bc
+  float* clip_scratch = nullptr;
   size_t n_params = 0;
   std::vector<float> host_params;              // staging for Set/GetVariable
   std::vector<int32_t> tok_job, label_job, t2j, j2t;
@@ -198,6 +198,7 @@ struct Session::Impl {
     if (workspace) cudaFree(workspace);
     if (params) cudaFree(params);
     if (grads) cudaFree(grads);
+    if (clip_scratch) cudaFree(clip_scratch);
   }
 
   // ---- declared (app) layout <-> engine layout, on the host ----
@@ -421,6 +422,16 @@ void Session::Run(std::vector<Sym> outputs, const std::initializer_list<std::pai
   }
   if (update) {
     CHECK(r.has_optimizer);
+    if (r.clip > 0.f) {
+      // Clip (cavs/backend/op_impl_clip.cu:25-45): scale by clip / max(sum of the per-VARIABLE L2 norms, clip).  The
+      // engine's blocks are the declared variables, except that the chain LSTM's joint weight is W and U together.
+      std::vector<unsigned long long> offs = {0, m.OffW()};
+      if (r.kind == Kind::kTreeLstm) offs.push_back(m.OffU());
+      offs.push_back(m.OffB()); offs.push_back(m.OffWc()); offs.push_back(m.Offbc()); offs.push_back(m.n_params);
+      const int n_blocks = static_cast<int>(offs.size()) - 1;
+      if (!m.clip_scratch) MustCuda(cudaMalloc(reinterpret_cast<void**>(&m.clip_scratch), cavs_clip_gradients_scratch_bytes(8)), "clip scratch");
+      Must(cavs_clip_gradients(m.grads, offs.data(), n_blocks, r.clip, m.clip_scratch, nullptr), "cavs_clip_gradients");
+    }
     // one SGD launch over the flat parameter buffer (every Variable, as `Optimizer({}, lr)` asks: c_api.cc:123-137)
     Must(cavs_sgd(m.params, m.grads, m.n_params, r.lr, nullptr), "cavs_sgd");
     Must(cavs_treelstm_refresh_weights(m.engine, nullptr), "cavs_treelstm_refresh_weights");

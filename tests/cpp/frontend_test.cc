@@ -138,7 +138,7 @@ static double RelErr(const std::vector<float>& a, const std::vector<float>& b) {
 
 // One training step through Session::Run vs the oracle.  `chain`: which vertex function; `opt`: the
 // Session's optimisation bits (without OPT_BATCHING the vertices run one per round).
-static void TestTrainingStep(bool chain, int opt) {
+static void TestTrainingStep(bool chain, int opt, float clip = 0.f) {
   frontend::Program::Reset();
   const int H = kHidden, E = chain ? kHidden : kEmbed, V = kVocab, C = kClasses, K = chain ? 1 : 2;
   const int B = 3, L = 7;
@@ -164,7 +164,7 @@ static void TestTrainingStep(bool chain, int opt) {
   label_col.ControlDependency(graph_output);
   Sym loss = graph_output.FullyConnected(fc_w, fc_b).SoftmaxEntropyLoss(label_col);
   const float lr = 0.5f;
-  Sym train = loss.Optimizer({}, lr);
+  Sym train = loss.Optimizer({}, lr, clip);
   Sym mean_loss = loss.Reduce_mean();
   Session sess(opt);
 
@@ -219,8 +219,18 @@ static void TestTrainingStep(bool chain, int opt) {
   double mean = 0; for (float v : want_loss) mean += v; mean /= n;
   EXPECT(std::fabs(*reinterpret_cast<const float*>(mean_loss.eval()) - mean) < 1e-5 * mean);
 
-  // updated variables: w - lr * g, compared in the declared layouts
-  auto sgd = [&](std::vector<float> w, const std::vector<float>& g) { for (size_t i = 0; i < w.size(); i++) w[i] -= lr * g[i]; return w; };
+  // gradient clipping (op_impl_clip.cu:25-45): every gradient is scaled by clip / max(sum of the variables' L2 norms, clip);
+  // the chain cell's joint weight is ONE variable, so its two parts share a norm
+  float scale = 1.f;
+  if (clip > 0.f) {
+    auto sq = [](const std::vector<float>& g) { double s = 0; for (float v : g) s += (double)v * v; return s; };
+    double sum = std::sqrt(sq(dEmb)) + std::sqrt(sq(dB)) + std::sqrt(sq(dWc)) + std::sqrt(sq(dbc));
+    sum += chain ? std::sqrt(sq(dW) + sq(dU)) : std::sqrt(sq(dW)) + std::sqrt(sq(dU));
+    scale = static_cast<float>(clip / std::fmax(sum, (double)clip));
+    EXPECT(scale < 0.9f);   // the case must actually clip
+  }
+  // updated variables: w - lr * scale * g, compared in the declared layouts
+  auto sgd = [&](std::vector<float> w, const std::vector<float>& g) { for (size_t i = 0; i < w.size(); i++) w[i] -= lr * scale * g[i]; return w; };
   auto fetch = [&](const Sym& v, size_t count) { std::vector<float> out(count); sess.GetVariable(v, out.data(), count); return out; };
   EXPECT(RelErr(fetch(chain ? chn->table : tree->table, table.size()), sgd(table, dEmb)) < 1e-5);
   EXPECT(RelErr(fetch(chain ? chn->bias : tree->bias, bias.size()), sgd(bias, dB)) < 1e-5);
@@ -251,12 +261,15 @@ int main(int argc, char** argv) {
     TestTrainingStep(true, OPT_BATCHING | OPT_FUSION | OPT_STREAMMING);
     TestTrainingStep(false, OPT_NONE);
     TestTrainingStep(true, OPT_FUSION);
+    TestTrainingStep(false, OPT_BATCHING, 0.05f);   // Optimizer(vars, lr, clip)
+    TestTrainingStep(true, OPT_BATCHING, 0.05f);
     // The same two programs through the operator-by-operator executor (run-time-compiled elementwise groups) instead
     // of the fused engine: same oracle, same tolerance.
     setenv("CAVS_GENERIC_SESSION", "1", 1);
     TestTrainingStep(false, OPT_BATCHING);
     TestTrainingStep(true, OPT_BATCHING);
     TestTrainingStep(false, OPT_NONE);
+    TestTrainingStep(true, OPT_BATCHING, 0.05f);
     unsetenv("CAVS_GENERIC_SESSION");
   }
   if (g_failures == 0) std::printf("frontend_test %s: ok\n", mode.c_str());
