@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstring>
 
+#include "cavs/frontend/cxx/session.h"
 #include "cavs/proto/opt.pb.h"
 #include "cavs/util/op_util.h"
 
@@ -148,12 +149,17 @@ void GenericSession::Run(std::vector<Sym>& outputs, const std::vector<std::pair<
       bs(static_cast<size_t>(n_slots_) * n_total);
   Must(cavs_sched_level_offsets(sched_, level_off.data(), n_levels + 1), "cavs_sched_level_offsets");
   Must(cavs_sched_maps(sched_, t2j.data(), j2t.data(), n_total), "cavs_sched_maps");
-  Must(cavs_sched_tables(sched_, 0, fg.data(), fs.data(), bg.data(), bs.data(), n_total), "cavs_sched_tables");
-  // compact the child table to the scheduled rows
-  std::vector<int32_t> child(static_cast<size_t>(n_slots_) * std::max(n, 1));
+  // Row alignment: 0 = every row pairs with its own children / parent; 1 = the reference's positional pairing of its compact
+  // per-round lists with level rows (op_impl_graphop.cu:62-76,144-157), which shifts rows on skewed batches.
+  Must(cavs_sched_tables(sched_, (opt_ & OPT_REF_COMPAT_ROWS) ? 1 : 0, fg.data(), fs.data(), bg.data(), bs.data(), n_total), "cavs_sched_tables");
+  // compact the slot-major tables to the scheduled rows
+  std::vector<int32_t> cfg(static_cast<size_t>(n_slots_) * std::max(n, 1)), cbs(cfg.size());
   for (int c = 0; c < n_slots_; ++c)
-    for (int t = 0; t < n; ++t) child[static_cast<size_t>(c) * n + t] = fg[static_cast<size_t>(c) * n_total + t];
-  fn_->LoadBatch(child.data(), n_slots_, t2j.data(), n, level_off, static_cast<const float*>(vertex));
+    for (int t = 0; t < n; ++t) {
+      cfg[static_cast<size_t>(c) * n + t] = fg[static_cast<size_t>(c) * n_total + t];
+      cbs[static_cast<size_t>(c) * n + t] = bs[static_cast<size_t>(c) * n_total + t];
+    }
+  fn_->LoadBatch(cfg.data(), fs.data(), bg.data(), cbs.data(), n_slots_, t2j.data(), n, level_off, static_cast<const float*>(vertex));
   fn_->Forward();
   const int wo = fn_->out_width();
   MustCuda(cudaMemsetAsync(grads_, 0, std::max<size_t>(fn_->param_count(), 4) * sizeof(float), nullptr), "zero gradients");

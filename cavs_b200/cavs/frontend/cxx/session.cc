@@ -260,7 +260,7 @@ struct Session::Impl {
 
   void Compile() {
     const Program& prog = *Program::Get();
-    if (!LooksLikeFusedLstm(prog) || std::getenv("CAVS_GENERIC_SESSION") != nullptr) {
+    if (!LooksLikeFusedLstm(prog) || (opt & OPT_REF_COMPAT_ROWS) || std::getenv("CAVS_GENERIC_SESSION") != nullptr) {
       generic.reset(new frontend::GenericSession(opt));
       compiled = true;
       return;

@@ -52,4 +52,9 @@ class Session {
 // Extra optimisation bit understood by this Session only: run the gate GEMMs on the tensor cores with
 // bf16 operands (the default, like the reference, is fp32 throughout).
 enum { OPT_BF16_GEMM = 8 };
+// Extra bit: pair gathered / scattered rows with level rows the way the reference's graph ops do -- positionally, which
+// shifts rows on batches whose levels mix vertices with and without a given child slot or parent
+// (cavs/backend/op_impl_graphop.cu:57-76,140-157).  The default pairs every row with its own children.  Honoured by the
+// operator-by-operator executor (the Session then uses it for every vertex function); the fused engines pair rows correctly.
+enum { OPT_REF_COMPAT_ROWS = 16 };
 #endif

@@ -229,7 +229,10 @@ void GenericFunction::Allocate() {
     for (auto& g : groups_) max_w = std::max(max_w, g->desc.width);
     tmp_ = take(static_cast<size_t>(max_w));
     col_scratch_ = take(cavs_column_sum_scratch_bytes(max_w) / sizeof(float) + 4);
-    d_child_ = reinterpret_cast<int32_t*>(take(N * max_slots_));
+    d_fg_ = reinterpret_cast<int32_t*>(take(N * max_slots_));
+    d_bs_ = reinterpret_cast<int32_t*>(take(N * max_slots_));
+    d_fs_ = reinterpret_cast<int32_t*>(take(N));
+    d_bg_ = reinterpret_cast<int32_t*>(take(N));
     d_t2j_ = reinterpret_cast<int32_t*>(take(N));
     grad_region_off_ = used;
     for (auto& b : bufs_) b.grad = take(N * b.width);
@@ -263,15 +266,19 @@ float* GenericFunction::GradPtr(const Ref& r, long long row) const {
   return bufs_[r.buf].grad + row * bufs_[r.buf].width + r.col;
 }
 
-void GenericFunction::LoadBatch(const int32_t* child, int n_slots, const int32_t* t2j, int n, const std::vector<int32_t>& level_off,
-                                const float* vertex_input) {
+void GenericFunction::LoadBatch(const int32_t* fg, const int32_t* fs, const int32_t* bg, const int32_t* bs, int n_slots,
+                                const int32_t* t2j, int n, const std::vector<int32_t>& level_off, const float* vertex_input) {
   CHECK(params_ != nullptr) << "Bind() first";
   CHECK(n <= max_vertices_) << "batch of " << n << " vertices exceeds the declared maximum " << max_vertices_;
   CHECK(n_slots >= max_slots_) << "the vertex function gathers slot " << max_slots_ - 1 << " but the schedule has " << n_slots << " slots";
   n_ = n; n_slots_ = n_slots; level_off_ = level_off;
-  for (int c = 0; c < max_slots_; ++c)
-    MustCuda(cudaMemcpy(d_child_ + static_cast<size_t>(c) * n, child + static_cast<size_t>(c) * n, sizeof(int32_t) * n, cudaMemcpyHostToDevice), "child table");
+  MustCuda(cudaMemcpy(d_fg_, fg, sizeof(int32_t) * n * max_slots_, cudaMemcpyHostToDevice), "gather table");
+  MustCuda(cudaMemcpy(d_bs_, bs, sizeof(int32_t) * n * max_slots_, cudaMemcpyHostToDevice), "gradient scatter table");
+  MustCuda(cudaMemcpy(d_fs_, fs, sizeof(int32_t) * n, cudaMemcpyHostToDevice), "scatter table");
+  MustCuda(cudaMemcpy(d_bg_, bg, sizeof(int32_t) * n, cudaMemcpyHostToDevice), "gradient gather table");
   MustCuda(cudaMemcpy(d_t2j_, t2j, sizeof(int32_t) * n, cudaMemcpyHostToDevice), "t2j");
+  // a mailbox row that no vertex of this batch writes reads as zeros (the reference zero-fills, op_impl_graphop.cu:77-86)
+  MustCuda(cudaMemset(mailbox_, 0, sizeof(float) * static_cast<size_t>(std::max(n, 1)) * state_width_), "mailbox");
   if (pull_width_ > 0) {
     CHECK(vertex_input != nullptr) << "the vertex function pulls its input: feed the vertex placeholder";
     MustCuda(cudaMemcpy(vin_, vertex_input, sizeof(float) * static_cast<size_t>(n) * pull_width_, cudaMemcpyHostToDevice), "vertex input");
@@ -323,7 +330,7 @@ void GenericFunction::RunLevel(int off, int rows) {
         // out[b] = mailbox[child_slot(t)], zeros without a child (op_impl_graphop.cu:32-90)
         const int w = bufs_[st.out].width;
         Must(cavs_copy_rows_2d(bufs_[st.out].val + static_cast<size_t>(off) * w, w, nullptr, mailbox_, state_width_,
-                               d_child_ + static_cast<size_t>(st.slot) * n_ + off, rows, w, 0, nullptr), "Gather");
+                               d_fg_ + static_cast<size_t>(st.slot) * n_ + off, rows, w, 0, nullptr), "Gather");
         break;
       }
       case Kind::kPull: {
@@ -375,9 +382,9 @@ void GenericFunction::RunLevel(int off, int rows) {
         break;
       }
       case Kind::kScatter:
-        // the state a parent will gather: row t of the mailbox (op_impl_graphop.cu:108-161)
-        Must(cavs_copy_rows_2d(mailbox_ + static_cast<size_t>(off) * state_width_, state_width_, nullptr, ValPtr(st.in, off),
-                               bufs_[st.in.buf].width, nullptr, rows, state_width_, 0, nullptr), "Scatter");
+        // the state a parent will gather: mailbox[fs[t]] = row t (op_impl_graphop.cu:108-161); roots have no target
+        Must(cavs_copy_rows_2d(mailbox_, state_width_, d_fs_ + off, ValPtr(st.in, off), bufs_[st.in.buf].width, nullptr, rows,
+                               state_width_, 0, nullptr), "Scatter");
         break;
       case Kind::kPush:
         Must(cavs_copy_rows_2d(out_val_ + static_cast<size_t>(off) * out_width_, out_width_, nullptr, ValPtr(st.in, off),
@@ -401,8 +408,8 @@ void GenericFunction::RunLevelBackward(int off, int rows) {
                                nullptr, rows, out_width_, 1, nullptr), "Push gradient");
         break;
       case Kind::kScatter:  // what the parent left for this vertex; zeros for roots (op_decl_graphop.cc:49-69)
-        Must(cavs_copy_rows_2d(GradPtr(st.in, off), bufs_[st.in.buf].width, nullptr, dmail_ + static_cast<size_t>(off) * state_width_, state_width_,
-                               nullptr, rows, state_width_, 1, nullptr), "Scatter gradient");
+        Must(cavs_copy_rows_2d(GradPtr(st.in, off), bufs_[st.in.buf].width, nullptr, dmail_, state_width_, d_bg_ + off, rows, state_width_, 1,
+                               nullptr), "Scatter gradient");
         break;
       case Kind::kGroup: {
         Group& g = *groups_[st.group];
@@ -444,7 +451,7 @@ void GenericFunction::RunLevelBackward(int off, int rows) {
       }
       case Kind::kGather: { // Scatter(Child = slot) of the gathered state's gradient to the child's row (op_decl_graphop.cc:25-41)
         const int w = bufs_[st.out].width;
-        Must(cavs_copy_rows_2d(dmail_, state_width_, d_child_ + static_cast<size_t>(st.slot) * n_ + off, bufs_[st.out].grad + static_cast<size_t>(off) * w,
+        Must(cavs_copy_rows_2d(dmail_, state_width_, d_bs_ + static_cast<size_t>(st.slot) * n_ + off, bufs_[st.out].grad + static_cast<size_t>(off) * w,
                                w, nullptr, rows, w, 0, nullptr), "Gather gradient");
         break;
       }

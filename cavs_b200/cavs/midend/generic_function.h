@@ -46,10 +46,12 @@ class GenericFunction {
 
   // ---- device side (needs a GPU) ----
   void Bind(float* params, float* grads);   // flat fp32 device buffers of param_count() floats
-  // Tables of one batch: child [n_slots, n] (tensor id of each child or -1), t2j [n], level offsets; vertex_input:
-  // host rows [n, pull_width()] in job order (may be null without a Pull).
-  void LoadBatch(const int32_t* child, int n_slots, const int32_t* t2j, int n, const std::vector<int32_t>& level_off,
-                 const float* vertex_input);
+  // Tables of one batch, in tensor-id space (cavs_sched_tables; either row-alignment mode): fg [n_slots, n] forward Gather
+  // source rows, fs [n] forward Scatter target rows, bg [n] backward Gather source rows, bs [n_slots, n] backward
+  // Scatter target rows (-1: zero row / no target); t2j [n]; level offsets; vertex_input: host rows [n, pull_width()] in
+  // job order (may be null without a Pull).
+  void LoadBatch(const int32_t* fg, const int32_t* fs, const int32_t* bg, const int32_t* bs, int n_slots, const int32_t* t2j, int n,
+                 const std::vector<int32_t>& level_off, const float* vertex_input);
   void Forward();
   float* output() const { return out_val_; }          // [n, out_width()] in tensor-id order (device)
   float* output_grad() const { return out_grad_; }     // the loss head writes d(loss)/d(output) here before Backward
@@ -98,7 +100,7 @@ class GenericFunction {
   float *mailbox_ = nullptr, *dmail_ = nullptr, *out_val_ = nullptr, *out_grad_ = nullptr, *vin_ = nullptr, *tmp_ = nullptr, *col_scratch_ = nullptr;
   void* arena_ = nullptr;        // one allocation behind every per-vertex array
   size_t grad_region_off_ = 0, grad_region_bytes_ = 0;
-  int32_t *d_child_ = nullptr, *d_t2j_ = nullptr;
+  int32_t *d_fg_ = nullptr, *d_bs_ = nullptr, *d_fs_ = nullptr, *d_bg_ = nullptr, *d_t2j_ = nullptr;
   std::vector<int32_t> level_off_, h_tok_tid_;
   int max_slots_ = 0;
   // embedding gradient tables (device) rebuilt per batch

@@ -138,7 +138,7 @@ static double RelErr(const std::vector<float>& a, const std::vector<float>& b) {
 
 // One training step through Session::Run vs the oracle.  `chain`: which vertex function; `opt`: the
 // Session's optimisation bits (without OPT_BATCHING the vertices run one per round).
-static void TestTrainingStep(bool chain, int opt, float clip = 0.f) {
+static std::vector<float> TestTrainingStep(bool chain, int opt, float clip = 0.f) {
   frontend::Program::Reset();
   const int H = kHidden, E = chain ? kHidden : kEmbed, V = kVocab, C = kClasses, K = chain ? 1 : 2;
   const int B = 3, L = 7;
@@ -184,7 +184,8 @@ static void TestTrainingStep(bool chain, int opt, float clip = 0.f) {
   // inputs: floats in compact job order
   int n = 0, levels = 0;
   std::vector<int> level_off(L + 2), t2j(B * L), j2t(B * L), fg(K * B * L), fs(B * L), bg(B * L), bs(K * B * L);
-  levels = cavs_oracle_tables(parents.data(), B, L, K, 0, &n, level_off.data(), (int)level_off.size(), t2j.data(), j2t.data(),
+  // row alignment of the oracle's tables: the reference's positional pairing when the Session is asked for it
+  levels = cavs_oracle_tables(parents.data(), B, L, K, (opt & OPT_REF_COMPAT_ROWS) ? 1 : 0, &n, level_off.data(), (int)level_off.size(), t2j.data(), j2t.data(),
                               fg.data(), fs.data(), bg.data(), bs.data());
   EXPECT(levels > 0);
   std::vector<float> words_f(B * L, 0.f), label_f(B * L, -1.f);
@@ -251,6 +252,7 @@ static void TestTrainingStep(bool chain, int opt, float clip = 0.f) {
     EXPECT(RelErr(fetch(tree->w_rec, w_rec.size()), sgd(w_rec, dU)) < 1e-5);
   }
   delete tree; delete chn;
+  return got_loss;
 }
 
 int main(int argc, char** argv) {
@@ -271,6 +273,12 @@ int main(int argc, char** argv) {
     TestTrainingStep(false, OPT_NONE);
     TestTrainingStep(true, OPT_BATCHING, 0.05f);
     unsetenv("CAVS_GENERIC_SESSION");
+    // Row alignment of the reference's graph ops (positional pairing: rows shift on this batch of three different tree
+    // shapes) against the oracle on the reference-compatible tables; the losses must differ from the aligned run's.
+    const std::vector<float> aligned = TestTrainingStep(false, OPT_BATCHING);
+    const std::vector<float> shifted = TestTrainingStep(false, OPT_BATCHING | OPT_REF_COMPAT_ROWS);
+    EXPECT(RelErr(shifted, aligned) > 1e-3);
+    TestTrainingStep(true, OPT_BATCHING | OPT_REF_COMPAT_ROWS);   // ragged chains: shorter chains first, rows shift too
   }
   if (g_failures == 0) std::printf("frontend_test %s: ok\n", mode.c_str());
   return g_failures == 0 ? 0 : 1;
