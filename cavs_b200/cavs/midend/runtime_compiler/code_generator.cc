@@ -114,5 +114,23 @@ std::string GenBackward(const EwiseGroup& g, const std::string& name) {
   return s.str();
 }
 
+// One operator as its own kernel, with the operand patterns of the reference's stand-alone elementwise operators
+// (cavs/backend/op_impl_elementwise.cuh:60-76 unary, :118-206 binary): equal sizes; a one-element operand read as a
+// scalar; a shorter operand repeated along the longer one (i % n).
+std::string GenStandalone(const std::string& op_name, const std::string& name) {
+  EwiseOp op;
+  op.name = op_name;
+  op.in.push_back({EwiseOperand::kInput, 0});
+  if (Arity(op_name) == 2) op.in.push_back({EwiseOperand::kInput, 1});
+  std::ostringstream s;
+  s << "extern \"C\" __global__ void " << name
+    << "(float* out, long long n, const float* in0, long long n0, const float* in1, long long n1) {\n";
+  s << "  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {\n";
+  s << "    const float x0 = in0[n0 == n ? i : (n0 == 1 ? 0 : i % n0)];\n";
+  if (op.in.size() > 1) s << "    const float x1 = in1[n1 == n ? i : (n1 == 1 ? 0 : i % n1)];\n";
+  s << "    out[i] = " << ForwardExpr(op) << ";\n  }\n}\n";
+  return s.str();
+}
+
 }  // namespace RTC
 }  // namespace midend

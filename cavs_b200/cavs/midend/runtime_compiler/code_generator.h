@@ -42,6 +42,10 @@ std::string GenForward(const EwiseGroup& g, const std::string& kernel_name);
 //   per variable: const float* var, float* var_rows (arena [*, width]: this row's contribution to the variable's gradient)
 //   per operator: const float* out, const float* grad_out
 std::string GenBackward(const EwiseGroup& g, const std::string& kernel_name);
+// One operator (IsElementwise) as a kernel of its own.  Kernel arguments, in order: float* out, long long n,
+//   const float* in0, long long n0, const float* in1, long long n1 (in1 / n1 ignored by unary operators); an operand
+//   with fewer elements than the output is read at i % its size.
+std::string GenStandalone(const std::string& op_name, const std::string& kernel_name);
 
 }  // namespace RTC
 }  // namespace midend

@@ -43,3 +43,21 @@ def test_session_run_matches_oracle_on_device(cuda):
     r = subprocess.run([str(_build(FRONTEND)), "gpu"], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "ok" in r.stdout
+
+
+VERTEX_OPS = BIN / "vertex_ops_test"
+
+
+def test_standalone_vertex_ops_registered_and_compile_cpu():
+    """MatMul / Add / Sub / Mul / Sigmoid / Tanh / Relu / Slice / Concat / Mirror under the reference's keys; the
+    generated elementwise kernels compile for sm_100a without a GPU."""
+    r = subprocess.run([str(_build(VERTEX_OPS)), "cpu"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ok" in r.stdout
+
+
+@pytest.mark.gpu
+def test_standalone_vertex_ops_on_device(cuda):
+    r = subprocess.run([str(_build(VERTEX_OPS)), "gpu"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "ok" in r.stdout
