@@ -55,8 +55,10 @@ POOL = 16            # distinct pre-generated batches cycled through by the end-
 SEED = 0xC0FFEE00
 
 
-def make_batch(wl, idx, rank, world):
-    """Global batch `idx`, then this rank's shard of it.  Returns (parents, tok_job, label_job, global_vertices)."""
+def make_batch(wl, idx, rank, world, with_rows=False):
+    """Global batch `idx`, then this rank's shard of it.  Returns (parents, tok_job, label_job, global_vertices) and, with
+    `with_rows`, the distinct token ids of the GLOBAL batch in ascending order: the embedding rows any rank touches, which
+    every rank's loader knows because it reads the global batch's ids before it takes its shard."""
     from cavs_b200 import schedule as S
     b = wl["batch"]
     parents, is_leaf = S.synth_trees(SEED + 16 * 5 + 1000 * idx, b, wl["leaf_lo"], wl["leaf_hi"])
@@ -68,7 +70,12 @@ def make_batch(wl, idx, rank, world):
     mask = np.arange(parents.shape[1])[None, :] < lens[lo:hi, None]
     tok_job = np.ascontiguousarray(tok_pad[lo:hi][mask], np.int32)
     label_job = np.ascontiguousarray(lab_pad[lo:hi][mask], np.int32)
-    return np.ascontiguousarray(parents[lo:hi]), tok_job, label_job, int(lens.sum())
+    out = (np.ascontiguousarray(parents[lo:hi]), tok_job, label_job, int(lens.sum()))
+    if with_rows:
+        all_mask = np.arange(parents.shape[1])[None, :] < lens[:, None]
+        seen = np.bincount(tok_pad[all_mask].astype(np.int64), minlength=wl["vocab"])
+        out += (np.flatnonzero(seen).astype(np.int32),)
+    return out
 
 
 def make_params(wl):
@@ -410,6 +417,8 @@ def main():
     ap.add_argument("--workload", default="dp_treelstm", choices=sorted(WORKLOADS) + sorted(SMALL_WORKLOADS))
     ap.add_argument("--sample-trees", type=int, default=256, help="trees per CPU-baseline step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dense-exchange", action="store_true",
+                    help="data parallel: all-reduce the whole embedding-gradient block instead of the rows the global batch touches")
     args = ap.parse_args()
     if args.workload in SMALL_WORKLOADS:
         if int(os.environ.get("RANK", "0")) == 0:
@@ -444,7 +453,10 @@ def main():
     def lib_check(rc):
         if rc != 0:
             raise RuntimeError(L.cavs_last_error().decode())
-    pool = [make_batch(wl, i, rank, world) for i in range(POOL)]
+    # Data parallel: the ranks exchange the gradients of the embedding rows the global batch touches, not the whole table.
+    sparse = world > 1 and not args.dense_exchange
+    pool = [make_batch(wl, i, rank, world, with_rows=True) for i in range(POOL)]
+    xrows = [p[4] if sparse else None for p in pool]
     scheds = [S.Schedule().load(p[0]) for p in pool]
     max_n = max(s.n_total for s in scheds)
     max_rows = max(s.max_level_rows for s in scheds)
@@ -476,7 +488,7 @@ def main():
         this thread's enqueueing of the step in flight; the next step waits for it and promotes the staged tables."""
         par, tok, lab = pinned_np[i % POOL]
         t0 = time.perf_counter()
-        eng.stage_async(host_sched, par, tok, lab, loss_rows=pool[i % POOL][3])
+        eng.stage_async(host_sched, par, tok, lab, loss_rows=pool[i % POOL][3], exchange_rows=xrows[i % POOL])
         host_ms[0] += (time.perf_counter() - t0) * 1e3
         host_ms[1] += 1
 
@@ -485,20 +497,22 @@ def main():
         par, tok, lab = pinned_np[0]
         eng.stage_wait()
         t0 = time.perf_counter()
-        eng.stage(host_sched, par, tok, lab, loss_rows=pool[0][3])
+        eng.stage(host_sched, par, tok, lab, loss_rows=pool[0][3], exchange_rows=xrows[0])
         return (time.perf_counter() - t0) * 1e3
 
     tail_view = eng.device_view(6, (2,))                       # [loss sum, status word] on the device
-    loss_pinned = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_ready = [torch.cuda.Event() for _ in range(2)]
+    LOSS_LAG = 2                                               # a step's loss is collected this many steps later
+    loss_pinned = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(LOSS_LAG + 1)]
+    loss_ready = [torch.cuda.Event() for _ in range(LOSS_LAG + 1)]
 
     pipeline = dict(primed=False, next=0)
 
     def e2e_loop(steps):
         # Software-pipelined like a data loader: while the GPU runs step i the host schedules batch i+1 and
         # enqueues its upload; every step's tables still cross PCIe inside the timed region, and every step's
-        # loss comes back to the host -- through a pinned slot, collected one step later so that the host never
-        # drains the GPU's queue between steps.
+        # loss comes back to the host -- through a pinned slot, collected two steps later (all of them before the
+        # timed region ends) so that the host never drains the GPU's queue between steps: with a lag of one step the
+        # ranks' host loops, each gated by its own GPU, cost 0.5 to 0.9 ms per step at 2 to 8 GPUs.
         losses = []
 
         def collect(slot):
@@ -514,18 +528,22 @@ def main():
             stage(pipeline["next"])
             pipeline["next"] += 1
             pipeline["primed"] = True
-        pending = None
+        pending = []
         for i in range(steps):
-            device_step()
-            slot = i & 1
-            loss_pinned[slot].copy_(tail_view, non_blocking=True)
-            loss_ready[slot].record()
+            # the batch staged during the previous step becomes current; the helper thread starts on the next one
+            # at once, so it works beside this thread's enqueueing of the step (host side = the longer of the two)
+            eng.promote()
             stage(pipeline["next"])
             pipeline["next"] += 1
-            if pending is not None:
-                collect(pending)
-            pending = slot
-        collect(pending)
+            device_step()
+            slot = i % (LOSS_LAG + 1)
+            loss_pinned[slot].copy_(tail_view, non_blocking=True)
+            loss_ready[slot].record()
+            pending.append(slot)
+            if len(pending) > LOSS_LAG:
+                collect(pending.pop(0))
+        while pending:
+            collect(pending.pop(0))
         return losses
 
     def barrier():
@@ -550,7 +568,7 @@ def main():
         return ms, launches
 
     # ---- device-resident arm: tables of batch 0 already in HBM ----
-    eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3])
+    eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3], exchange_rows=xrows[0])
     for _ in range(args.warmup):
         device_step()
     sampler = ClockSampler(local_rank)
@@ -574,7 +592,8 @@ def main():
     # ---- per-kernel-class timing for the roofline (separate instrumented steps) ----
     L.cavs_treelstm_profile(eng._h, 1)
     prof_steps = 3
-    eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3])
+    eng.load_batch(scheds[0], pool[0][1], pool[0][2], loss_rows=pool[0][3], exchange_rows=xrows[0])
+    eng.promote()     # the end-to-end loop promoted explicitly; the engine has stopped doing it by itself
     for _ in range(prof_steps):
         device_step()
     torch.cuda.synchronize()
@@ -605,7 +624,12 @@ def main():
                          exposed_wait_ms=ms_of("allreduce_exposed_wait"),
                          hidden_ms=max(0.0, ms_of("allreduce_embedding") - ms_of("allreduce_exposed_wait")),
                          on_compute_stream_ms=ms_of("allreduce_weights") + ms_of("allreduce_exposed_wait"),
-                         allreduce_bytes_per_step=4 * int(eng.params.numel()), nccl_version=comm.nccl_version(),
+                         allreduce_bytes_per_step=4 * (int(eng.params.numel()) - (wl["vocab"] - int(np.mean([len(x) for x in xrows]))) * wl["embed"]
+                                                       if sparse else int(eng.params.numel())),
+                         dense_allreduce_bytes_per_step=4 * int(eng.params.numel()),
+                         embedding_exchange=("rows the global batch touches (cavs_treelstm_set_exchange_rows): mean %d of %d table rows"
+                                             % (int(np.mean([len(x) for x in xrows])), wl["vocab"])) if sparse else "dense block",
+                         nccl_version=comm.nccl_version(),
                          issued_by="cavs_treelstm_step -> cavs_allreduce (ncclAllReduce called from the library)")
     optimizer_ms = ms_of("optimizer")
     for nm in ("allreduce_embedding", "allreduce_weights", "allreduce_exposed_wait", "optimizer"):

@@ -124,6 +124,10 @@ struct cavs_treelstm {
     int32_t *l_order = nullptr, *l_chunk_off = nullptr, *l_chunk_out = nullptr, *l_seg_first = nullptr, *l_multi = nullptr;
     int n_l_chunks = 0, n_l_multi = 0, n_links = 0;
     bool l1 = false;         // this batch runs level 1 by token (it has a level 1)
+    // exchange rows (cavs_treelstm_set_exchange_rows): the embedding rows whose gradients exist for this batch, in
+    // ascending order, and for each token segment its position in that list; n_xrows == 0: dense gradient block
+    int32_t *xrows = nullptr, *seg_pos = nullptr;
+    int n_xrows = 0;
   };
   Batch slot[2];
   int active = -1, staged = -1;
@@ -152,6 +156,9 @@ struct cavs_treelstm {
   };
   Stager* stager = nullptr;
   bool slot_used[2] = {false, false};
+  std::vector<int32_t> pending_xrows;   // consumed by the next load_batch
+  int reserve_sms = 0;             // SMs the weight-gradient products leave to a concurrent all-reduce (set by step)
+  bool explicit_promote = false;   // set by cavs_treelstm_promote: forward() then leaves the staged batch alone
   std::vector<int32_t> bucket, slot_of_token, leaf_count, link_bucket;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
   bool prof_on = false;
@@ -261,7 +268,8 @@ size_t MaxLinkChunks(const cavs_treelstm_config& c) {
 size_t IdxInts(const cavs_treelstm_config& c) {
   const size_t n = c.max_vertices;
   return (2 * c.n_slots + 7) * n + 4 * (MaxChunks(c) + 1) + (MaxSegments(c) + 1) + 10 * MaxSegments(c) + 64 +
-         c.n_slots * n + 2 * (MaxLinkChunks(c) + 1) + 2 * (MaxSegments(c) + 1);   // link lists (level 1 by token)
+         c.n_slots * n + 2 * (MaxLinkChunks(c) + 1) + 2 * (MaxSegments(c) + 1) +   // link lists (level 1 by token)
+         static_cast<size_t>(std::max(c.vocab, 0)) + MaxSegments(c) + 2;            // exchange rows and their positions
 }
 
 // Split-K scratch large enough for the three weight-gradient GEMMs at full capacity.
@@ -508,6 +516,19 @@ extern "C" int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream) {
   return LaunchCastBf16(e->U_bf, e->params + e->OffU(), 4 * H * H, st);
 }
 
+extern "C" int cavs_treelstm_set_exchange_rows(cavs_treelstm* e, const int32_t* rows, int n_rows) {
+  CAVS_REQUIRE(e && n_rows >= 0 && (rows || n_rows == 0), CAVS_ERR_BAD_ARG, "treelstm_set_exchange_rows: bad arguments");
+  CAVS_REQUIRE(!e->Dense(), CAVS_ERR_BAD_ARG, "treelstm_set_exchange_rows: the engine has no embedding table");
+  if (int rc = cavs_treelstm_stage_wait(e)) return rc;   // the helper thread may be reading the previous list
+  CAVS_REQUIRE(n_rows <= e->cfg.vocab, CAVS_ERR_BAD_ARG, "treelstm_set_exchange_rows: more rows than the table has");
+  CAVS_REQUIRE(e->cfg.embed % 4 == 0, CAVS_ERR_UNSUPPORTED, "treelstm_set_exchange_rows: embedding width must be a multiple of 4");
+  for (int i = 0; i < n_rows; ++i)
+    CAVS_REQUIRE(rows[i] >= 0 && rows[i] < e->cfg.vocab && (i == 0 || rows[i] > rows[i - 1]), CAVS_ERR_BAD_ARG,
+                 "treelstm_set_exchange_rows: rows must be table indices in strictly ascending order");
+  e->pending_xrows.assign(rows, rows + n_rows);
+  return CAVS_OK;
+}
+
 extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job,
                                         const int32_t* label_job, int loss_rows, void* stream) {
   CAVS_REQUIRE(e && s && s->loaded, CAVS_ERR_BAD_ARG, "treelstm_load_batch: null pointer or empty schedule");
@@ -721,6 +742,28 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
     });
   }
   bt.n_seg = n_seg; bt.n_chunks = n_chunks;
+  // Exchange rows given for this batch: every token segment's position in the list (both ascending: one merge).
+  bt.n_xrows = 0;
+  bt.xrows = bt.seg_pos = nullptr;
+  if (!e->pending_xrows.empty()) {
+    std::vector<int32_t> rows;
+    rows.swap(e->pending_xrows);          // consumed by this load, whatever its outcome
+    CAVS_REQUIRE(!e->Dense(), CAVS_ERR_BAD_ARG, "treelstm_load_batch: exchange rows need an embedding table");
+    const int U = static_cast<int>(rows.size());
+    int32_t* h_xrows = view(U, &bt.xrows);
+    int32_t* h_seg_pos = view(n_seg, &bt.seg_pos);
+    CAVS_REQUIRE(o <= e->idx_ints, CAVS_ERR_CAPACITY, "treelstm_load_batch: index blob overflow");
+    std::memcpy(h_xrows, rows.data(), sizeof(int32_t) * U);
+    const int32_t* h_seg_tok_c = h + (bt.seg_tok - d);
+    int pos = 0;
+    for (int si = 0; si < n_seg; ++si) {
+      while (pos < U && rows[pos] < h_seg_tok_c[si]) ++pos;
+      CAVS_REQUIRE(pos < U && rows[pos] == h_seg_tok_c[si], CAVS_ERR_BAD_ARG,
+                   "treelstm_load_batch: token " + std::to_string(h_seg_tok_c[si]) + " of the batch is not among the exchange rows");
+      h_seg_pos[si] = pos;
+    }
+    bt.n_xrows = U;
+  }
   // The device half is free once the last pass that read it has finished.
   (void)stream;
   if (e->slot_used[which]) CAVS_CUDA(cudaStreamWaitEvent(e->copy_stream, e->slot_done[which], 0));
@@ -731,15 +774,32 @@ extern "C" int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, c
   return CAVS_OK;
 }
 
-extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
-  CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_forward: parameters not bound");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int rc = cavs_treelstm_stage_wait(e)) return rc;   // a batch being staged by the helper thread
+namespace {
+// Joins a staging request in flight and makes the staged batch (if any) the current one.
+int PromoteStaged(cavs_treelstm* e, cudaStream_t st) {
+  if (int rc = cavs_treelstm_stage_wait(e)) return rc;
   if (e->staged >= 0) {
     e->active = e->staged;
     e->staged = -1;
     CAVS_CUDA(cudaStreamWaitEvent(st, e->copied[e->active], 0));   // tables of this batch are in place
   }
+  return CAVS_OK;
+}
+}  // namespace
+
+extern "C" int cavs_treelstm_promote(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e, CAVS_ERR_BAD_ARG, "treelstm_promote: null handle");
+  e->explicit_promote = true;
+  return PromoteStaged(e, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
+  CAVS_REQUIRE(e && e->params, CAVS_ERR_BAD_ARG, "treelstm_forward: parameters not bound");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Without explicit promotion the pass takes the staged batch itself, after joining a request still on the helper
+  // thread; a caller that promotes explicitly may have the batch after this one on the helper thread right now.
+  if (!e->explicit_promote)
+    if (int rc = PromoteStaged(e, st)) return rc;
   CAVS_REQUIRE(e->active >= 0, CAVS_ERR_BAD_ARG, "treelstm_forward: no batch loaded");
   const cavs_treelstm::Batch& bt = e->slot[e->active];
   const int n = bt.n, nt = bt.n_total, H = e->cfg.hidden, E = e->cfg.embed, K = e->cfg.n_slots;
@@ -1048,9 +1108,14 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
                                  bt.seg_first_chunk, n_tok, e->emb_scratch, st, bt.chunk_out, bt.multi_seg, bt.n_multi));
     }
     if ((rc = Gemm(e, e->dX, E, 0, e->dAtok, 4 * H, false, W, 4 * H, true, n_tok, E, 4 * H, false, st))) return rc;
-    CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(e->cfg.vocab) * E * sizeof(float), st));
-    if ((rc = cavs_scatter_rows(g, bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
+    // The embedding block of the gradient buffer: row v = d(Emb[v]) -- or, with exchange rows, row i = d(Emb[xrows[i]]):
+    // only those rows are cleared, filled, exchanged between the ranks and applied.
+    const bool compact = bt.n_xrows > 0;
+    CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(compact ? bt.n_xrows : e->cfg.vocab) * E * sizeof(float), st));
+    if ((rc = cavs_scatter_rows(g, compact ? bt.seg_pos : bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
     CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
+    // From here on the embedding block's all-reduce may run on the communication stream: leave it a few SMs.
+    ReserveSms(e->reserve_sms);
     if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
   }
   // first row of the per-vertex weight-gradient products: the first internal row, or with level 1 by token the
@@ -1087,6 +1152,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
          LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
   }
   (void)rc;
+  ReserveSms(0);
   CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
   e->slot_used[e->active] = true;
   return CAVS_OK;
@@ -1154,11 +1220,24 @@ extern "C" int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimiz
   CAVS_REQUIRE(optimizer == 0 || optimizer == 1 || optimizer == 2, CAVS_ERR_BAD_ARG, "treelstm_step: optimizer must be 0 (none), 1 (SGD) or 2 (Adagrad)");
   CAVS_REQUIRE(optimizer != 2 || opt_state, CAVS_ERR_BAD_ARG, "treelstm_step: Adagrad needs its accumulator");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (int rc = cavs_treelstm_forward(e, stream)) return rc;
-  if (int rc = cavs_treelstm_backward(e, stream)) return rc;
   int world = 1;
   if (comm) cavs_comm_info(comm, nullptr, &world, nullptr);
+  static const int reserve = [] {
+    const char* env = std::getenv("CAVS_COMM_RESERVE_SMS");
+    return env ? std::max(0, std::min(64, std::atoi(env))) : 0;
+  }();
+  e->reserve_sms = world > 1 ? reserve : 0;
+  if (int rc = cavs_treelstm_forward(e, stream)) return rc;
+  const int rc_bwd = cavs_treelstm_backward(e, stream);
+  e->reserve_sms = 0;
+  ReserveSms(0);   // also on an error return out of the middle of backward
+  if (rc_bwd) return rc_bwd;
   const size_t n_all = e->ParamCount(), n_emb = e->OffW();
+  // With exchange rows the embedding block holds one gradient row per listed table row: that is what travels and what
+  // the update walks.  Every rank must have been given the same list, or the ranks' reductions differ in size.
+  const cavs_treelstm::Batch& bt = e->slot[e->active];
+  const bool compact = bt.n_xrows > 0;
+  const size_t n_emb_x = compact ? static_cast<size_t>(bt.n_xrows) * e->cfg.embed : n_emb;
   if (world > 1) {
     // Sum of the per-GPU gradients (cavs/midend/session_mpi.cc:31-80 inserts one all-reduce per variable gradient;
     // here the flat buffer goes in two pieces).  backward finishes the embedding block -- the bulk of the buffer --
@@ -1167,10 +1246,10 @@ extern "C" int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimiz
     cudaEvent_t a0 = nullptr, a1 = nullptr, x0 = nullptr, x1 = nullptr;
     CAVS_CUDA(cudaStreamWaitEvent(e->comm_stream, e->emb_ready, 0));
     if (e->prof_on) { a0 = e->NextEvent(); a1 = e->NextEvent(); CAVS_CUDA(cudaEventRecord(a0, e->comm_stream)); }
-    if (int rc = cavs_allreduce(e->grads, n_emb, comm, e->comm_stream)) return rc;
+    if (int rc = cavs_allreduce(e->grads, n_emb_x, comm, e->comm_stream)) return rc;
     if (e->prof_on) {
       CAVS_CUDA(cudaEventRecord(a1, e->comm_stream));
-      e->recs.push_back({kProfCommEmbed, a0, a1, 4.0 * static_cast<double>(n_emb)});
+      e->recs.push_back({kProfCommEmbed, a0, a1, 4.0 * static_cast<double>(n_emb_x)});
     }
     CAVS_CUDA(cudaEventRecord(e->comm_done, e->comm_stream));
     PROF(e, kProfCommRest, 4.0 * static_cast<double>(n_all - n_emb), st, cavs_allreduce(e->grads + n_emb, n_all - n_emb, comm, st));
@@ -1185,11 +1264,23 @@ extern "C" int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimiz
   if (optimizer != 0) {
     // w <- w - lr g (SGD, cavs/backend/op_impl_sgd.cu:15-47) or the Adagrad form, over the whole flat buffer, then the
     // bf16 shadows of the GEMM weights
-    const double bytes = (optimizer == 2 ? 20.0 : 12.0) * static_cast<double>(n_all);
-    PROF(e, kProfOptimizer, bytes, st,
-         optimizer == 2 ? LaunchAdagrad(e->params, opt_state, e->grads, n_all, lr, eps, st) : LaunchSgd(e->params, e->grads, n_all, lr, st));
+    const double per = optimizer == 2 ? 20.0 : 12.0;
+    if (compact) {
+      // listed rows of the table, then the other blocks
+      PROF(e, kProfOptimizer, per * static_cast<double>(n_emb_x), st,
+           LaunchUpdateRows(e->params, optimizer == 2 ? opt_state : nullptr, e->grads, bt.xrows, bt.n_xrows, e->cfg.embed, lr, eps, st));
+      PROF(e, kProfOptimizer, per * static_cast<double>(n_all - n_emb), st,
+           optimizer == 2 ? LaunchAdagrad(e->params + n_emb, opt_state + n_emb, e->grads + n_emb, n_all - n_emb, lr, eps, st)
+                          : LaunchSgd(e->params + n_emb, e->grads + n_emb, n_all - n_emb, lr, st));
+    } else {
+      PROF(e, kProfOptimizer, per * static_cast<double>(n_all), st,
+           optimizer == 2 ? LaunchAdagrad(e->params, opt_state, e->grads, n_all, lr, eps, st) : LaunchSgd(e->params, e->grads, n_all, lr, st));
+    }
     if (int rc = cavs_treelstm_refresh_weights(e, stream)) return rc;
   }
+  // The update of listed rows reads the slot's tables (the row list) after backward's own mark: only now may the
+  // upload of the batch after next overwrite them.
+  CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
   return CAVS_OK;
 }
 

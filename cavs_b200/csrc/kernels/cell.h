@@ -139,6 +139,9 @@ int LaunchColumnSum(float* out, const void* x, bool bf16, long long pitch, int r
 
 int LaunchSgd(float* w, const float* g, size_t n, float lr, cudaStream_t st);
 int LaunchAdagrad(float* w, float* acc, const float* g, size_t n, float lr, float eps, cudaStream_t st);
+// w[rows[i], :width] takes gradient row g[i, :width]: SGD, or Adagrad when acc (same shape as w) is given.
+int LaunchUpdateRows(float* w, float* acc, const float* g, const int32_t* rows, int n_rows, int width, float lr, float eps,
+                     cudaStream_t st);
 // dst_bf16[i] = bf16(src[i])
 int LaunchCastBf16(void* dst, const float* src, size_t n, cudaStream_t st);
 // dst [rows, cols] (dense, bf16) = src [rows, cols] with row pitch src_pitch (fp32)

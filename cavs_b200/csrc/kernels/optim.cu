@@ -56,6 +56,34 @@ AdagradKernel(float* __restrict__ w, float* __restrict__ acc, const float* __res
   }
 }
 
+// The update of listed rows of a table: w[rows[i], :] takes gradient row g[i, :] (SGD, or Adagrad when acc is given),
+// the same arithmetic per element as the dense kernels above.  width is a multiple of 4.
+template <bool kAdagrad>
+__global__ void __launch_bounds__(kThreads)
+UpdateRowsKernel(float* __restrict__ w, float* __restrict__ acc, const float* __restrict__ g, const int32_t* __restrict__ rows,
+                 int n_rows, int width, float lr, float eps) {
+  const int w4 = width / 4;
+  const size_t total = static_cast<size_t>(n_rows) * w4;
+  const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < total; i += stride) {
+    const int r = static_cast<int>(i / w4), c = static_cast<int>(i % w4);
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    if (kAdagrad && gv.x == 0.0f && gv.y == 0.0f && gv.z == 0.0f && gv.w == 0.0f) continue;
+    const size_t at = static_cast<size_t>(__ldg(rows + r)) * w4 + c;
+    float4 wv = reinterpret_cast<float4*>(w)[at];
+    if (kAdagrad) {
+      float4 av = reinterpret_cast<float4*>(acc)[at];
+      av.x += gv.x * gv.x; av.y += gv.y * gv.y; av.z += gv.z * gv.z; av.w += gv.w * gv.w;
+      wv.x -= lr * gv.x / (sqrtf(av.x) + eps); wv.y -= lr * gv.y / (sqrtf(av.y) + eps);
+      wv.z -= lr * gv.z / (sqrtf(av.z) + eps); wv.w -= lr * gv.w / (sqrtf(av.w) + eps);
+      reinterpret_cast<float4*>(acc)[at] = av;
+    } else {
+      wv.x -= lr * gv.x; wv.y -= lr * gv.y; wv.z -= lr * gv.z; wv.w -= lr * gv.w;
+    }
+    reinterpret_cast<float4*>(w)[at] = wv;
+  }
+}
+
 __global__ void __launch_bounds__(kThreads) CastBf16Kernel(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, size_t n) {
   const size_t stride = static_cast<size_t>(gridDim.x) * kThreads;
   for (size_t i = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
@@ -105,6 +133,19 @@ int LaunchSgd(float* w, const float* g, size_t n, float lr, cudaStream_t st) {
   CAVS_REQUIRE(((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g)) & 15u) == 0, CAVS_ERR_BAD_ARG, "sgd: buffers must be 16-byte aligned");
   SgdKernel<<<GridForElems(n / 4 + 1, kThreads), kThreads, 0, st>>>(w, g, n, lr);
   CAVS_LAUNCH_CHECK("sgd");
+  return CAVS_OK;
+}
+
+int LaunchUpdateRows(float* w, float* acc, const float* g, const int32_t* rows, int n_rows, int width, float lr, float eps,
+                     cudaStream_t st) {
+  if (n_rows == 0 || width == 0) return CAVS_OK;
+  CAVS_REQUIRE(w && g && rows && n_rows > 0, CAVS_ERR_BAD_ARG, "update_rows: null pointer");
+  CAVS_REQUIRE(width % 4 == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(acc)) & 15u) == 0,
+               CAVS_ERR_BAD_ARG, "update_rows: rows must be 16-byte aligned and a multiple of 4 floats wide");
+  const int grid = GridForElems(static_cast<size_t>(n_rows) * (width / 4), kThreads);
+  if (acc) UpdateRowsKernel<true><<<grid, kThreads, 0, st>>>(w, acc, g, rows, n_rows, width, lr, eps);
+  else UpdateRowsKernel<false><<<grid, kThreads, 0, st>>>(w, nullptr, g, rows, n_rows, width, lr, eps);
+  CAVS_LAUNCH_CHECK("update_rows");
   return CAVS_OK;
 }
 

@@ -73,8 +73,17 @@ class TreeLSTM:
     def refresh_weights(self) -> None:
         check(lib().cavs_treelstm_refresh_weights(self._h, _stream()))
 
-    def load_batch(self, sched: Schedule, tok_job=None, label_job=None, loss_rows: int = 0) -> None:
+    def set_exchange_rows(self, rows) -> None:
+        """Sparse exchange of the embedding gradient for the NEXT batch loaded or staged: `rows` = ascending table rows
+        touched by any rank's shard of it (identical on every rank).  The embedding block of `grads` then holds one row
+        per listed row, step() all-reduces and applies only those.  None / empty: dense block."""
+        rows = np.ascontiguousarray(rows if rows is not None else [], np.int32)
+        check(lib().cavs_treelstm_set_exchange_rows(self._h, ptr(rows) if rows.size else ptr(None), int(rows.size)))
+
+    def load_batch(self, sched: Schedule, tok_job=None, label_job=None, loss_rows: int = 0, exchange_rows=None) -> None:
         # tokens are ignored by a dense-input engine (vocab == 0), labels by a headless one (classes == 0)
+        if exchange_rows is not None:
+            self.set_exchange_rows(exchange_rows)
         tok_job = np.ascontiguousarray(tok_job, np.int32) if self.cfg.vocab else None
         label_job = np.ascontiguousarray(label_job, np.int32) if self.cfg.classes else None
         assert tok_job is None or tok_job.size >= sched.n_total
@@ -82,23 +91,35 @@ class TreeLSTM:
         check(lib().cavs_treelstm_load_batch(self._h, sched._h, ptr(tok_job), ptr(label_job), loss_rows, _stream()))
         self.n = sched.n_scheduled
 
-    def stage(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0) -> None:
+    def stage(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0, exchange_rows=None) -> None:
         """Level scheduling of `parents` into `sched` and the upload of the batch's tables, in one C call."""
         assert parents.dtype == np.int32 and parents.flags.c_contiguous
+        if exchange_rows is not None:
+            self.set_exchange_rows(exchange_rows)
         check(lib().cavs_treelstm_stage(self._h, sched._h, ptr(parents), parents.shape[0], parents.shape[1],
                                         ptr(tok_job) if self.cfg.vocab else ptr(None), ptr(label_job) if self.cfg.classes else ptr(None),
                                         loss_rows))
         sched._refresh()
         self.n = sched.n_scheduled
 
-    def stage_async(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0) -> None:
+    def stage_async(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0, exchange_rows=None) -> None:
         """stage() on the engine's helper thread: returns at once; the next step() / forward() waits for it.  The arrays
         are kept alive here until then."""
         assert parents.dtype == np.int32 and parents.flags.c_contiguous
+        if exchange_rows is not None:
+            self.set_exchange_rows(exchange_rows)      # copied by the library before it returns
         self._staging = (sched, parents, tok_job, label_job)
         check(lib().cavs_treelstm_stage_async(self._h, sched._h, ptr(parents), parents.shape[0], parents.shape[1],
                                               ptr(tok_job) if self.cfg.vocab else ptr(None),
                                               ptr(label_job) if self.cfg.classes else ptr(None), loss_rows))
+
+    def promote(self) -> None:
+        """Join a staging request in flight and make the staged batch current; from then on forward() / step() run the
+        batch last promoted, so the next batch can be staged while this one's step is being enqueued."""
+        check(lib().cavs_treelstm_promote(self._h, _stream()))
+        if getattr(self, "_staging", None) is not None:
+            self._staging[0]._refresh()
+            self.n = self._staging[0].n_scheduled
 
     def stage_wait(self) -> None:
         check(lib().cavs_treelstm_stage_wait(self._h))

@@ -328,6 +328,17 @@ CAVS_API int cavs_treelstm_refresh_weights(cavs_treelstm* e, void* stream);
  * loss_rows: divisor of the loss gradient (0 = this batch's vertex count). */
 CAVS_API int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, const int32_t* tok_job, const int32_t* label_job,
                                       int loss_rows, void* stream);
+/* Sparse exchange of the embedding gradient.  rows: the table rows that ANY rank's shard of the coming batch touches
+ * (strictly ascending, every token of this rank's shard among them), identical on every rank -- a data-parallel loader
+ * that reads the global batch's token ids has them.  The list is consumed by the next cavs_treelstm_load_batch /
+ * _stage / _stage_async.  For that batch the embedding block of the gradient buffer then holds ONE ROW PER LISTED ROW,
+ * in list order (row i = d(Emb[rows[i]])): backward clears and fills only those rows, cavs_treelstm_step all-reduces
+ * n_rows * embed floats instead of vocab * embed and updates the listed rows of the table only.  A list that differs
+ * between ranks makes their reductions differ in size: the caller's contract, as with any collective.  Without a list
+ * (or n_rows = 0) the block is dense.  Embedding width must be a multiple of 4.  The reference reduces every variable's
+ * whole gradient (cavs/midend/session_mpi.cc:31-80) and scatters the embedding gradient into the dense table-sized
+ * tensor (cavs/backend/op_impl_embedding_lookup.cu:91-103). */
+CAVS_API int cavs_treelstm_set_exchange_rows(cavs_treelstm* e, const int32_t* rows, int n_rows);
 /* Level scheduling of a batch (cavs_sched_load into `s`, with the engine's slot count) and cavs_treelstm_load_batch
  * in one call: everything the host does per batch before the device step. */
 CAVS_API int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
@@ -340,6 +351,13 @@ CAVS_API int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t*
 CAVS_API int cavs_treelstm_stage_async(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
                                        const int32_t* tok_job, const int32_t* label_job, int loss_rows);
 CAVS_API int cavs_treelstm_stage_wait(cavs_treelstm* e);
+/* Joins a request in flight and makes the staged batch the current one (what the next forward would do by itself).
+ * For a loop that keeps the helper thread busy DURING the enqueueing of a step:
+ *     promote(batch i);  stage_async(batch i+1);  step();        -- host side per step = max(schedule, enqueue)
+ * instead of stage_async(batch i+1) only after step i has been enqueued (their sum, when the device step is shorter).
+ * After the first call the engine no longer promotes by itself: forward / step run the batch last promoted and leave
+ * a staged one (or a request in flight) alone.  No counterpart in the reference, which schedules inside Session::Run. */
+CAVS_API int cavs_treelstm_promote(cavs_treelstm* e, void* stream);
 /* One training step in one call: forward, backward, the sum of the gradients over the ranks of `comm` (NULL or a
  * world of one: none) and the update of the flat parameter buffer -- optimizer 0: none (gradients only), 1: SGD,
  * 2: Adagrad with accumulator opt_state [param_count] -- followed by the refresh of the bf16 weight copies.  What

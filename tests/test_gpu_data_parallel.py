@@ -1,7 +1,9 @@
 """Two GPUs, one process each: cavs_treelstm_step with the library's own NCCL communicator gives every rank the
 gradient of the GLOBAL batch -- equal to what one GPU computes for the whole batch -- and, after identical SGD
 updates (linear in the gradient, so the comparison keeps its tolerance), the same parameters.  Skipped where fewer than two GPUs are visible.  The ranks are child processes;
-the communicator id travels through a file (no torch.distributed involved), NVLS is off (plain ring / tree kernels)."""
+the communicator id travels through a file (no torch.distributed involved), NVLS is off (plain ring / tree kernels).
+With `sparse` the ranks exchange only the embedding rows the global batch touches (cavs_treelstm_set_exchange_rows): same
+gradients, same parameters."""
 import os
 import subprocess
 import sys
@@ -16,6 +18,7 @@ pytestmark = pytest.mark.gpu
 WORKER = r'''
 import sys
 rank, world, id_file, out_file, bf16, root = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4], int(sys.argv[5]), sys.argv[6]
+sparse = int(sys.argv[7])
 sys.path.insert(0, root); sys.path.insert(0, root + "/tests")
 import numpy as np, torch
 from cavs_b200 import schedule as S
@@ -37,12 +40,19 @@ eng.set_params(params)
 shard = np.ascontiguousarray(parents[lo:hi])
 tok, lab = np.ascontiguousarray(tok_job[starts[lo]:starts[hi]]), np.ascontiguousarray(label_job[starts[lo]:starts[hi]])
 out = {}
-eng.stage(s, shard, tok, lab, loss_rows=int(lens.sum()))
+# sparse exchange: the table rows any rank touches -- the distinct tokens of the GLOBAL batch, the same list on every rank
+rows = np.unique(tok_job).astype(np.int32) if sparse else None
+eng.stage(s, shard, tok, lab, loss_rows=int(lens.sum()), exchange_rows=rows)
 eng.step(comm, eng.OPT_NONE)                       # gradients only: summed over the ranks
-out["grads"] = eng.grads.cpu().numpy()
+g = eng.grads.cpu().numpy()
+if sparse:                                         # one gradient row per listed row -> back to table layout for the comparison
+    dense = np.zeros(V * E, np.float32).reshape(V, E)
+    dense[rows] = g[:rows.size * E].reshape(rows.size, E)
+    g = np.concatenate([dense.reshape(-1), g[V * E:]])
+out["grads"] = g
 out["loss"] = np.array([eng.read_loss()])
 for _ in range(3):                                 # three full training steps
-    eng.stage(s, shard, tok, lab, loss_rows=int(lens.sum()))
+    eng.stage(s, shard, tok, lab, loss_rows=int(lens.sum()), exchange_rows=rows)
     eng.step(comm, eng.OPT_SGD, None, 0.1)
 torch.cuda.synchronize()
 out["params"] = eng.params.cpu().numpy()
@@ -64,8 +74,8 @@ comm.close()
 '''
 
 
-@pytest.mark.parametrize("bf16", [0, 1])
-def test_two_ranks_compute_the_single_gpu_step(cuda, tmp_path, bf16):
+@pytest.mark.parametrize("bf16,sparse", [(0, 0), (1, 0), (0, 1), (1, 1)])
+def test_two_ranks_compute_the_single_gpu_step(cuda, tmp_path, bf16, sparse):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -73,7 +83,7 @@ def test_two_ranks_compute_the_single_gpu_step(cuda, tmp_path, bf16):
     from helpers import rel_err
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     id_file, out_file = str(tmp_path / "comm_id"), str(tmp_path / "out")
-    procs = [subprocess.Popen([sys.executable, "-c", WORKER, str(r), "2", id_file, out_file, str(bf16), str(ROOT)], env=env)
+    procs = [subprocess.Popen([sys.executable, "-c", WORKER, str(r), "2", id_file, out_file, str(bf16), str(ROOT), str(sparse)], env=env)
              for r in range(2)]
     for p in procs:
         assert p.wait(timeout=600) == 0

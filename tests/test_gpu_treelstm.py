@@ -461,25 +461,32 @@ def test_staging_on_the_helper_thread_gives_the_same_steps(cuda):
     batches = [make_tree_batch(700 + i, b, 2, hi, V, C) for i, (b, hi) in enumerate([(20, 30), (3, 4), (25, 40), (9, 12)])]
     cap = dict(gemm_bf16=True, max_vertices=4096, max_level_rows=4096)
 
-    def run(async_mode):
+    def run(mode):
         eng = TreeLSTM(H, E, V, C, **cap)
         eng.set_params(params)
         s = S.Schedule()
         keep = [(np.ascontiguousarray(p), np.ascontiguousarray(t), np.ascontiguousarray(l)) for p, t, l in batches]
         out = []
-        if async_mode:
+        if mode != "sync":
             eng.stage_async(s, *keep[0])
         for i in range(len(keep)):
-            if not async_mode:
+            if mode == "sync":
                 eng.stage(s, *keep[i])
-            eng.step(None, eng.OPT_SGD, None, 0.05)        # waits for the pending request, promotes, runs the step
-            if async_mode and i + 1 < len(keep):
+            if mode == "promote":
+                # explicit promotion: batch i becomes current, batch i+1 is staged WHILE step i is being enqueued
+                eng.promote()
+                if i + 1 < len(keep):
+                    eng.stage_async(s, *keep[i + 1])
+            eng.step(None, eng.OPT_SGD, None, 0.05)        # "async": waits for the pending request, promotes, runs the step
+            if mode == "async" and i + 1 < len(keep):
                 eng.stage_async(s, *keep[i + 1])
             out.append((eng.read_loss(), eng.grads.cpu().numpy().copy()))
         return out
 
-    for (la, ga), (lb, gb) in zip(run(True), run(False)):
-        assert la == lb and np.array_equal(ga, gb)
+    want = run("sync")
+    for mode in ("async", "promote"):
+        for (la, ga), (lb, gb) in zip(run(mode), want):
+            assert la == lb and np.array_equal(ga, gb), mode
     eng = TreeLSTM(H, E, V, C, **cap)
     eng.set_params(params)
     bad = np.array([[5, 5, -1, -1]], np.int32)             # parent index out of range
@@ -487,3 +494,77 @@ def test_staging_on_the_helper_thread_gives_the_same_steps(cuda):
     with pytest.raises(CavsError) as e:
         eng.stage_wait()
     assert e.value.status == 2
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_exchange_rows_give_the_dense_update(cuda, bf16):
+    # With a list of exchange rows the embedding block of the gradient buffer is compact (one row per listed row) and
+    # step() updates only the listed rows: the parameters after Adagrad steps must equal the dense path's bit for bit,
+    # whether the list is exactly the batch's tokens or a superset of them.
+    from cavs_b200 import CavsError
+    H, E, V, C = 64, 64, 500, 5
+    params = make_params(41, H, E, V, C, scale=0.08, bias_scale=0.03)
+    batches = [make_tree_batch(900 + i, 12, 2, 20, V, C) for i in range(3)]
+    cap = dict(gemm_bf16=bf16, max_vertices=2048, max_level_rows=2048)
+
+    def run(mode):
+        eng = TreeLSTM(H, E, V, C, **cap)
+        eng.set_params(params)
+        acc = torch.zeros_like(eng.params)
+        s = S.Schedule()
+        emb_grads = []
+        for p, t, l in batches:
+            rows = None
+            if mode == "exact":
+                rows = np.unique(t)
+            elif mode == "superset":
+                rows = np.union1d(np.unique(t), np.arange(0, V, 7))
+            eng.stage(s, np.ascontiguousarray(p), t, l, exchange_rows=rows)
+            eng.step(None, eng.OPT_ADAGRAD, acc, 0.05)
+            g = eng.grads.cpu().numpy()
+            if rows is not None:
+                dense = np.zeros((V, E), np.float32)
+                dense[rows] = g[:rows.size * E].reshape(rows.size, E)
+                g = np.concatenate([dense.reshape(-1), g[V * E:]])
+            emb_grads.append(g)
+        return eng.params.cpu().numpy(), acc.cpu().numpy(), emb_grads
+
+    want = run("dense")
+    for mode in ("exact", "superset"):
+        got = run(mode)
+        assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]), mode
+        for a, b in zip(got[2], want[2]):
+            assert np.array_equal(a, b), mode
+
+    # the pipelined loop (explicit promotion, next batch staged on the helper thread while this step is enqueued, no
+    # host synchronisation between steps): the row update of step i reads its row list from tables that the upload of
+    # batch i+2 must not overwrite before it has run
+    eng = TreeLSTM(H, E, V, C, **cap)
+    eng.set_params(params)
+    acc = torch.zeros_like(eng.params)
+    s = S.Schedule()
+    keep = [(np.ascontiguousarray(p), np.ascontiguousarray(t), np.ascontiguousarray(l)) for p, t, l in batches]
+    eng.stage_async(s, *keep[0], exchange_rows=np.unique(keep[0][1]))
+    for i in range(len(keep)):
+        eng.promote()
+        if i + 1 < len(keep):
+            eng.stage_async(s, *keep[i + 1], exchange_rows=np.unique(keep[i + 1][1]))
+        eng.step(None, eng.OPT_ADAGRAD, acc, 0.05)
+    torch.cuda.synchronize()
+    assert np.array_equal(eng.params.cpu().numpy(), want[0]) and np.array_equal(acc.cpu().numpy(), want[1])
+    # the list is consumed by one load: the next batch is dense again
+    eng = TreeLSTM(H, E, V, C, **cap)
+    eng.set_params(params)
+    s = S.Schedule()
+    p, t, l = batches[0]
+    eng.stage(s, np.ascontiguousarray(p), t, l, exchange_rows=np.unique(t))
+    eng.stage(s, np.ascontiguousarray(p), t, l)
+    eng.step(None, eng.OPT_NONE)
+    assert np.array_equal(eng.grads.cpu().numpy(), want[2][0])
+    # a token of the batch missing from the list, or a list out of order, is an argument error at load time
+    with pytest.raises(CavsError) as e:
+        eng.stage(s, np.ascontiguousarray(p), t, l, exchange_rows=np.unique(t)[1:])
+    assert e.value.status == 1
+    with pytest.raises(CavsError) as e:
+        eng.set_exchange_rows(np.array([5, 3], np.int32))
+    assert e.value.status == 1
