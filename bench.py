@@ -453,8 +453,9 @@ def main():
     def lib_check(rc):
         if rc != 0:
             raise RuntimeError(L.cavs_last_error().decode())
-    # Data parallel: the ranks exchange the gradients of the embedding rows the global batch touches, not the whole table.
-    sparse = world > 1 and not args.dense_exchange
+    # The embedding gradient is kept, exchanged between the ranks and applied for the rows the global batch touches, not
+    # for the whole table (at one GPU there is no exchange, but the same compact block and row update).
+    sparse = not args.dense_exchange
     pool = [make_batch(wl, i, rank, world, with_rows=True) for i in range(POOL)]
     xrows = [p[4] if sparse else None for p in pool]
     scheds = [S.Schedule().load(p[0]) for p in pool]
@@ -710,9 +711,12 @@ def main():
                 config=dict(workload=args.workload, global_batch=trees, trees_per_gpu=trees // world, hidden=wl["hidden"],
                             embed=wl["embed"], vocab=wl["vocab"], classes=wl["classes"], leaves=[wl["leaf_lo"], wl["leaf_hi"]],
                             vertices_per_gpu=int(scheds[0].n_total), levels=int(scheds[0].n_levels), optimizer="adagrad",
-                            parallelism=f"dp{world}", l2="working set per step (tens of GB) exceeds L2; no flush needed"),
+                            parallelism=f"dp{world}", l2="working set per step (tens of GB) exceeds L2; no flush needed",
+                            embedding_gradient=("rows the global batch touches (mean %d of %d), listed with the batch"
+                                                % (int(np.mean([len(x) for x in xrows])), wl["vocab"])) if sparse else "dense block"),
                 e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8,
-                         host_stage_ms=host_stage_sync_ms, host_stage_mode="helper thread of the engine (cavs_treelstm_stage_async)"),
+                         host_stage_ms=host_stage_sync_ms, host_stage_mode="helper thread of the engine (cavs_treelstm_promote, then cavs_treelstm_stage_async beside the step's enqueueing)",
+                         loss_read="every step into a pinned slot, collected two steps later"),
                 gpu_launches=int(launches), gpu_launches_per_step=int(launches) // max(args.steps, 1), loss_sum=loss_dev,
                 global_loss_sum=global_loss, comm=comm_info, optimizer_ms=optimizer_ms, clocks=clocks, roofline=roofline,
                 kernel_classes=classes, graph_ops=graph_ops)
