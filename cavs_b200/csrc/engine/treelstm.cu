@@ -1037,6 +1037,8 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     const uint8_t* dA_l = e->dA + static_cast<size_t>(off) * 4 * H * e->elt;
     const uint8_t* ZF_l = e->ZF + static_cast<size_t>(off) * K * H * e->elt;
     // ds = dP U_iou^T, dq = Zf U_f^T  (dX = dY W^T, cavs/backend/op_decl_matmul.cc:21-31)
+    // (Cutting a narrow level's ds product into K slices on more SMs, the partial products left unreduced for the dq
+    // product's epilogue to add, was measured: 2.68 against 2.69 ms on a 512-tree shard -- not worth its code.)
     if ((rc = Gemm(e, e->ds, H, 0, dA_l, 4 * H, false, U_iou, 3 * H, true, rows, H, 3 * H, false, st, &e->map_dA3, off, &e->map_Uiou_k, &e->map_ds, &e->map_Uiou_k64))) return rc;
     ChainHint(rows <= kChainSmallRows);   // dq GEMM (-> scatter) -> next level's cell gradient
     if (e->bf16) {
@@ -1374,8 +1376,11 @@ extern "C" int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_p
       if (e->FusedDh()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(h) is not materialised with the fused loss head");
       *dev_ptr = e->dOut; *bytes = n * H * sizeof(float); break;
     case 3: *dev_ptr = e->mailbox; *bytes = n * 2 * H * sizeof(float); break;    // child-gradient mailbox
-    case 4:                                                                      // saved gates; leaf rows are not written
-      *dev_ptr = e->gates; *bytes = n * (3 + e->cfg.n_slots) * H * e->elt; break;
+    case 4: {                                                                    // saved gates; leaf rows are not written
+      // with the gate epilogue the arena is split at its capacity: G3 [max_vertices, 3H], then GF [max_vertices, K, H]
+      const size_t rows = e->gate_epi ? static_cast<size_t>(e->cfg.max_vertices) : n;
+      *dev_ptr = e->gates; *bytes = rows * (3 + e->cfg.n_slots) * H * e->elt; break;
+    }
     case 6: *dev_ptr = e->tail; *bytes = 2 * sizeof(float); break;               // [0] loss sum, [1] status word (int)
     case 5:                                                                      // d(loss)/d(dense input)
       if (!e->Dense()) return Fail(CAVS_ERR_UNSUPPORTED, "treelstm_peek: d(x) exists only with dense inputs");

@@ -364,7 +364,8 @@ CAVS_API int cavs_treelstm_promote(cavs_treelstm* e, void* stream);
  * Session::Run does for a fetched train op (cavs/midend/session_mpi.cc:84-138).  For the summed gradient to equal
  * the single-GPU gradient of the global batch, every rank passes the GLOBAL loss-row count to load_batch / stage.
  * The embedding block of the gradient is reduced on an internal stream while the weight gradients are still being
- * computed.  Enqueues only; the loss of this rank's shard is read with cavs_treelstm_read_loss or peek array 6. */
+ * computed; with exchange rows (cavs_treelstm_set_exchange_rows) only the listed rows travel and are updated.
+ * Enqueues only; the loss of this rank's shard is read with cavs_treelstm_read_loss or peek array 6. */
 CAVS_API int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimizer, float* opt_state, float lr, float eps,
                                 void* stream);
 /* Embedding lookup and input projection over the batch's distinct tokens, then the forward level loop. */
@@ -406,7 +407,9 @@ CAVS_API int cavs_treelstm_read_loss(cavs_treelstm* e, float* loss_sum_host, int
 CAVS_API int cavs_treelstm_profile(cavs_treelstm* e, int enable);
 CAVS_API int cavs_treelstm_profile_read(cavs_treelstm* e, double* ms, double* work, int* launches, int n_classes);
 /* Device views for inspection: 0 state [n,2H], 1 loss [n], 2 dOut [n,H] (classes > 8 only: the fused
- * loss head does not materialise it), 3 mailbox [n,2H], 4 gates, 5 d(x) [n,E] (dense-input engines),
+ * loss head does not materialise it), 3 mailbox [n,2H], 4 saved gates (fp32 mode: float [n,(3+K)H] = i|o|u|f_0..f_{K-1};
+ * bf16 mode with hidden a multiple of 64: half, the whole arena, G3 [max_vertices,3H] = i|o|u followed by
+ * GF [max_vertices,K,H] = the forget gates), 5 d(x) [n,E] (dense-input engines),
  * 6 the two words cavs_treelstm_read_loss copies: loss sum (float) and status (int) -- for callers that fetch
  * them with their own asynchronous copy instead of the blocking read. */
 CAVS_API int cavs_treelstm_peek(cavs_treelstm* e, int what, const void** dev_ptr, size_t* bytes);

@@ -377,6 +377,21 @@ def test_peek_returns_every_array_with_its_size(cuda):
     first_internal = int(s.level_off[1])
     g = gates[first_internal:]
     assert (g[:, :2 * H] > 0).all() and (g[:, :2 * H] < 1).all() and (np.abs(g[:, 2 * H:3 * H]) < 1).all()
+    # bf16 mode with the gate epilogue: the arena is split at its capacity, G3 [cap, 3H] then GF [cap, K, H], in half
+    cap = s.n_total + 7
+    engb = TreeLSTM(H, E, V, 5, gemm_bf16=True, max_vertices=cap, max_level_rows=s.max_level_rows)
+    engb.set_params(make_params(1, H, E, V, 5))
+    engb.load_batch(s, tok_job, label_job % 5)
+    engb.forward()
+    p, b = ctypes.c_void_p(), ctypes.c_size_t()
+    check(lib().cavs_treelstm_peek(engb._h, 4, ctypes.byref(p), ctypes.byref(b)))
+    assert b.value == cap * (3 + K) * H * 2
+    off = p.value - engb.workspace.data_ptr()
+    arena = engb.workspace[off:off + b.value].view(torch.float16).cpu().numpy().astype(np.float32)
+    g3, gf = arena[:cap * 3 * H].reshape(cap, 3 * H), arena[cap * 3 * H:].reshape(cap, K, H)
+    assert (g3[first_internal:n, :2 * H] > 0).all() and (g3[first_internal:n, :2 * H] < 1).all()
+    assert (np.abs(g3[first_internal:n, 2 * H:]) <= 1).all()
+    assert (gf[first_internal:n] > 0).all() and (gf[first_internal:n] < 1).all()
     # fused head: d(h) is not materialised and peek says so
     eng5 = TreeLSTM(H, E, V, 5, max_vertices=s.n_total, max_level_rows=s.max_level_rows)
     with pytest.raises(CavsError) as e:
