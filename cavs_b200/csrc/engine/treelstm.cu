@@ -1012,7 +1012,7 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
                        e->gates, e->state, bt.child, bt.parent, nt, off, rows, H, K, l == 0, st,
                        e->FusedDh() ? e->dz8 : nullptr, e->params + e->OffWc(), C, l == 0 ? e->A : nullptr,
                        l == 0 ? bt.tok_slot : nullptr, l == 0 ? e->params + e->OffB() : nullptr,
-                       e->leaf_tok ? bt.child_st : nullptr, e->gates_f));
+                       e->leaf_tok ? bt.child_st : nullptr, e->gates_f, e->Status()));
     if (l == 0) break;
     if (l == 1 && bt.l1) {
       // The children are leaves: what they receive is summed per token first (fixed order), and the two products

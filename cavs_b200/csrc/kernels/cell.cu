@@ -21,8 +21,10 @@
 #include <cuda_fp16.h>
 
 #include <cstdint>
+#include <cstdlib>
 
 #include "abi_common.h"
+#include "kernels/bulk.cuh"
 #include "kernels/cell.h"
 #include "kernels/launch.h"
 
@@ -445,6 +447,209 @@ CellBwd(T* __restrict__ dA, T* __restrict__ ZF, float* __restrict__ mailbox, flo
         for (int r = 0; r < rows_per_iter; ++r) acc += fold[((r * tpr + threadIdx.x) * 4 + g4) * V + e];
         mine[g4 * H + threadIdx.x * V + e] += acc;
       }
+  }
+}
+
+// The backward cell of an internal level in the bf16 configuration with the fused loss-head gradient, as a streaming
+// kernel: one producer thread per CTA fetches each row's operands -- mailbox row, saved gates, own and children's cell
+// states, d(logits) row -- into shared memory with bulk copies that complete on an mbarrier, kBwdStages rows ahead
+// (the row's index entries one further), so DRAM latency is hidden by copies in flight rather than by resident warps:
+// the register-heavy arithmetic (80 registers, a third of the warp slots) no longer limits the bytes in flight.
+// H / 4 consumer threads own four hidden units each, as in CellBwd, and compute the same expressions in the same
+// order.  Every wait is bounded; one that expires raises *status and ends the CTA's loop.
+constexpr int kBwdStages = 2;
+constexpr int kBwdConsumers = 256;
+constexpr int kBwdThreads = kBwdConsumers + 32;
+
+template <int K>
+struct BwdStageLayout {
+  // byte offsets inside one stage; every array starts on a 16-byte boundary (H a multiple of 8)
+  int hdr, dz, mail, g3, gf, cown, cch, bytes;
+  __host__ __device__ explicit BwdStageLayout(int H) {
+    hdr = 0;                       // int32: parent, child rows (targets of d(c)) ...
+    dz = 64;                       // kHeadDzPitch floats
+    mail = dz + 32;                // 2H floats: d(h) | d(c) left by the parent
+    g3 = mail + 8 * H;             // 3H halves: i | o | u
+    gf = g3 + 6 * H;               // K x H halves
+    cown = gf + 2 * K * H;         // H floats
+    cch = cown + 4 * H;            // K x H floats
+    bytes = cch + 4 * K * H;
+  }
+};
+
+__device__ __forceinline__ void MbarArrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int K>
+__global__ void __launch_bounds__(kBwdThreads, 2)
+CellBwdStream(__nv_bfloat16* __restrict__ dA, __nv_bfloat16* __restrict__ ZF, float* __restrict__ mailbox, float* __restrict__ dB_part,
+              const __half* __restrict__ gates, const __half* __restrict__ gates_f, long long pitch3, long long pitch_f,
+              const float* __restrict__ state, const int32_t* __restrict__ child, const int32_t* __restrict__ child_state,
+              const int32_t* __restrict__ parent, int n_total, int off, int rows, int H, const float* __restrict__ dz,
+              const float* __restrict__ Wc, int C, int chain_early, int* __restrict__ status) {
+  ChainRelease(chain_early);
+  ChainAcquire();
+  extern __shared__ __align__(128) unsigned char bwd_smem[];
+  __shared__ __align__(8) unsigned long long full_bar[kBwdStages], empty_bar[kBwdStages];
+  const BwdStageLayout<K> lay(H);
+  float* s_wc = reinterpret_cast<float*>(bwd_smem);                              // [C, H]
+  unsigned char* stages = bwd_smem + ((static_cast<size_t>(C) * H * 4 + 127) / 128) * 128;
+  const int tid = threadIdx.x;
+  const int tpr = H / 4;                     // consumer threads in use
+  const bool consumer = tid < tpr;
+  const bool producer = tid == kBwdConsumers;
+  for (int i = tid; i < C * H; i += kBwdThreads) s_wc[i] = Wc[i];
+  if (tid == 0) {
+    for (int s = 0; s < kBwdStages; ++s) {
+      bulk::MbarInit(bulk::SmemAddr(&full_bar[s]), 1);
+      bulk::MbarInit(bulk::SmemAddr(&empty_bar[s]), tpr);
+    }
+    bulk::FenceMbarInit();
+  }
+  __syncthreads();
+  const int n_my = blockIdx.x < rows ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  float sb[4][4];
+#pragma unroll
+  for (int g4 = 0; g4 < 4; ++g4)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sb[g4][e] = 0.0f;
+
+  if (producer) {
+    int par = -1, ch[K], chs[K];
+    auto fetch = [&](int i) {
+      const size_t t = static_cast<size_t>(off) + blockIdx.x + static_cast<size_t>(i) * gridDim.x;
+      par = __ldg(parent + t);
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        ch[c] = __ldg(child + static_cast<size_t>(c) * n_total + t);
+        chs[c] = child_state ? __ldg(child_state + static_cast<size_t>(c) * n_total + t) : ch[c];
+      }
+    };
+    if (n_my > 0) fetch(0);
+    int issued = 0;
+    for (int i = 0; i < n_my; ++i) {
+      const int s = i % kBwdStages;
+      if (i >= kBwdStages && !bulk::MbarWait(bulk::SmemAddr(&empty_bar[s]), ((i / kBwdStages) - 1) & 1)) {
+        if (status != nullptr) atomicExch(status, 1);
+        break;
+      }
+      const size_t t = static_cast<size_t>(off) + blockIdx.x + static_cast<size_t>(i) * gridDim.x;
+      const int my_par = par;
+      int my_ch[K], my_chs[K];
+#pragma unroll
+      for (int c = 0; c < K; ++c) { my_ch[c] = ch[c]; my_chs[c] = chs[c]; }
+      if (i + 1 < n_my) fetch(i + 1);                      // the next row's index entries travel while this row is issued
+      unsigned char* st = stages + static_cast<size_t>(s) * lay.bytes;
+      int32_t* hdr = reinterpret_cast<int32_t*>(st + lay.hdr);
+      hdr[0] = my_par;
+#pragma unroll
+      for (int c = 0; c < K; ++c) hdr[1 + c] = my_ch[c];
+      uint32_t bytes = 32u + 6u * H + 2u * K * H + 4u * H;
+      if (my_par >= 0) bytes += 8u * H;
+#pragma unroll
+      for (int c = 0; c < K; ++c)
+        if (my_ch[c] >= 0) bytes += 4u * H;
+      const uint32_t bar = bulk::SmemAddr(&full_bar[s]);
+      bulk::MbarExpectTx(bar, bytes);                       // release: the header is visible to whoever sees the phase flip
+      bulk::Load(bulk::SmemAddr(st + lay.dz), dz + t * kHeadDzPitch, 32u, bar);
+      if (my_par >= 0) bulk::Load(bulk::SmemAddr(st + lay.mail), mailbox + t * 2 * H, 8u * H, bar);
+      bulk::Load(bulk::SmemAddr(st + lay.g3), gates + t * pitch3, 6u * H, bar);
+      bulk::Load(bulk::SmemAddr(st + lay.gf), gates_f + t * pitch_f, 2u * K * H, bar);
+      bulk::Load(bulk::SmemAddr(st + lay.cown), state + t * 2 * H + H, 4u * H, bar);
+#pragma unroll
+      for (int c = 0; c < K; ++c)
+        if (my_ch[c] >= 0)
+          bulk::Load(bulk::SmemAddr(st + lay.cch + c * 4 * H), state + static_cast<size_t>(my_chs[c]) * 2 * H + H, 4u * H, bar);
+      issued = i + 1;
+    }
+    // Error path only: copies of rows nobody will consume may still be in flight; wait for them (bounded) before the
+    // CTA leaves, so that none lands in shared memory that is no longer this CTA's.
+    if (issued < n_my || (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0)) {
+      for (int i = max(0, issued - kBwdStages); i < issued; ++i)
+        bulk::MbarWait(bulk::SmemAddr(&full_bar[i % kBwdStages]), (i / kBwdStages) & 1);
+    }
+  } else if (consumer) {
+    const int j = tid * 4;
+    for (int i = 0; i < n_my; ++i) {
+      const int s = i % kBwdStages;
+      if (!bulk::MbarWait(bulk::SmemAddr(&full_bar[s]), (i / kBwdStages) & 1)) {
+        if (status != nullptr) atomicExch(status, 1);
+        break;
+      }
+      const size_t t = static_cast<size_t>(off) + blockIdx.x + static_cast<size_t>(i) * gridDim.x;
+      const unsigned char* st = stages + static_cast<size_t>(s) * lay.bytes;
+      const int32_t* hdr = reinterpret_cast<const int32_t*>(st + lay.hdr);
+      const bool has_parent = hdr[0] >= 0;
+      int ch[K];
+#pragma unroll
+      for (int c = 0; c < K; ++c) ch[c] = hdr[1 + c];
+      const float* sdz = reinterpret_cast<const float*>(st + lay.dz);
+      const float4 d0 = *reinterpret_cast<const float4*>(sdz), d1 = *reinterpret_cast<const float4*>(sdz + 4);
+      const float dzr[kHeadDzPitch] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+      const float* smail = reinterpret_cast<const float*>(st + lay.mail);
+      const Vec<4> mh = has_parent ? LoadF<4>(smail + j) : Zero<4>();
+      const Vec<4> mc = has_parent ? LoadF<4>(smail + H + j) : Zero<4>();
+      const __half* sg = reinterpret_cast<const __half*>(st + lay.g3);
+      const Vec<4> gi = LoadF<4>(sg + j), go = LoadF<4>(sg + H + j), gu = LoadF<4>(sg + 2 * H + j);
+      const Vec<4> cown = LoadF<4>(reinterpret_cast<const float*>(st + lay.cown) + j);
+      Vec<4> gfv[K], cchv[K];
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        gfv[c] = LoadF<4>(reinterpret_cast<const __half*>(st + lay.gf) + c * H + j);
+        cchv[c] = ch[c] >= 0 ? LoadF<4>(reinterpret_cast<const float*>(st + lay.cch) + c * H + j) : Zero<4>();
+      }
+      MbarArrive(bulk::SmemAddr(&empty_bar[s]));             // everything of this stage is in registers
+      // d(pushed h) = d(logits) . Wc[:, j]: same fused-multiply-add order as the loss head (see CellBwd)
+      Vec<4> dOutv = Zero<4>();
+#pragma unroll
+      for (int c = 0; c < kHeadDzPitch; ++c) {
+        if (c < C) {
+          const Vec<4> w = LoadF<4>(s_wc + static_cast<size_t>(c) * H + j);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) dOutv.v[e] = fmaf(dzr[c], w.v[e], dOutv.v[e]);
+        }
+      }
+      Vec<4> zi, zo, zu, dc, zfs = Zero<4>();
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float dh = dOutv.v[e] + mh.v[e];
+        const float th = TanhT<true>(cown.v[e]);
+        const float d_o = dh * th;
+        dc.v[e] = mc.v[e] + (dh * go.v[e]) * (1.0f - th * th);
+        zi.v[e] = (dc.v[e] * gu.v[e]) * gi.v[e] * (1.0f - gi.v[e]);
+        zo.v[e] = d_o * go.v[e] * (1.0f - go.v[e]);
+        zu.v[e] = (dc.v[e] * gi.v[e]) * (1.0f - gu.v[e] * gu.v[e]);
+      }
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        Vec<4> z = Zero<4>();
+        if (ch[c] >= 0) {
+          Vec<4> dcc;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            z.v[e] = (dc.v[e] * cchv[c].v[e]) * gfv[c].v[e] * (1.0f - gfv[c].v[e]);
+            dcc.v[e] = dc.v[e] * gfv[c].v[e];
+            zfs.v[e] += z.v[e];
+          }
+          Store<4>(mailbox + static_cast<size_t>(ch[c]) * 2 * H + H + j, dcc);
+        }
+        Store<4>(ZF + (t * K + c) * H + j, z);
+      }
+      __nv_bfloat16* d = dA + t * 4 * H + j;
+      Store<4>(d, zi); Store<4>(d + H, zo); Store<4>(d + 2 * H, zu); Store<4>(d + 3 * H, zfs);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { sb[0][e] += zi.v[e]; sb[1][e] += zo.v[e]; sb[2][e] += zu.v[e]; sb[3][e] += zfs.v[e]; }
+    }
+  }
+  __syncthreads();
+  if (dB_part != nullptr && consumer) {
+    // one row per CTA iteration, so a thread's sums are final: they go straight into this CTA's partial row
+    float* mine = dB_part + static_cast<size_t>(blockIdx.x) * 4 * H;
+#pragma unroll
+    for (int g4 = 0; g4 < 4; ++g4)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) mine[g4 * H + tid * 4 + e] += sb[g4][e];
   }
 }
 
@@ -884,7 +1089,7 @@ int CellBwdGrid(int rows, int H) {
 int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part, const float* dOut, const void* gates,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st, const float* dz, const float* Wc, int C, const void* A,
-                  const int32_t* a_row, const float* bias, const int32_t* child_state, const void* gates_f) {
+                  const int32_t* a_row, const float* bias, const int32_t* child_state, const void* gates_f, int* status) {
   if (int rc = CheckCommon("treelstm_cell_bwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const bool head = dz != nullptr;
@@ -895,9 +1100,40 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
   const int v = VecWidth(H);
   CAVS_REQUIRE(dB_part == nullptr || H / v <= kThreads, CAVS_ERR_UNSUPPORTED,
                "treelstm_cell_bwd: the fused bias gradient needs hidden / vector width <= 256");
-  const int grid = CellBwdGrid(rows, H);
   const size_t head_smem = head ? static_cast<size_t>(C) * H * sizeof(float) : 0;
   CAVS_REQUIRE(head_smem <= 32 * 1024, CAVS_ERR_UNSUPPORTED, "treelstm_cell_bwd: classifier above 32 KB (classes * hidden <= 8192)");
+  // Internal levels of the bf16 configuration with the fused loss-head gradient stream their rows through shared
+  // memory (CellBwdStream) when the rows are wide enough to keep a CTA's consumers busy and 16-byte granular.
+  static const bool stream_ok = [] { const char* v = std::getenv("CAVS_CELL_BWD_STREAM"); return !(v != nullptr && v[0] == '0'); }();
+  if (stream_ok && bf16 && !leaf && head && A == nullptr && H % 8 == 0 && H / 4 <= kBwdConsumers && H / 4 >= 128 && dB_part != nullptr) {
+    const GateView<__half> gv = MakeGateView<__half>(gates, gates_f, H, K);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(mailbox) | reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(gates) |
+                           reinterpret_cast<uintptr_t>(gv.f) | reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(dA) |
+                           reinterpret_cast<uintptr_t>(ZF)) & 15u) == 0;
+    if (aligned) {
+      size_t smem = 0;
+      DISPATCH_KV(K, 4, { (void)V; smem = (head_smem + 127) / 128 * 128 + static_cast<size_t>(kBwdStages) * BwdStageLayout<K>(H).bytes; });
+      if (smem <= 100 * 1024) {
+        const int sgrid = static_cast<int>(std::min<long long>(rows, 2LL * SmCount()));
+        DISPATCH_KV(K, 4, {
+          (void)V;
+          static bool configured[kMaxDevices] = {};
+          const int dev = CurrentDevice();
+          if (!configured[dev]) {
+            CAVS_CUDA(cudaFuncSetAttribute(CellBwdStream<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            configured[dev] = true;
+          }
+          LaunchChained(CellBwdStream<K>, dim3(sgrid), dim3(kBwdThreads), smem, st, static_cast<__nv_bfloat16*>(dA),
+                        static_cast<__nv_bfloat16*>(ZF), mailbox, dB_part, static_cast<const __half*>(gates),
+                        static_cast<const __half*>(gv.f), gv.pitch3, gv.pitch_f, state, child, child_state, parent, n_total, off, rows, H,
+                        dz, Wc, C, ChainEarly(), status);
+        });
+        CAVS_LAUNCH_CHECK("treelstm_cell_bwd (streaming)");
+        return CAVS_OK;
+      }
+    }
+  }
+  const int grid = CellBwdGrid(rows, H);
 #define CELL_BWD(TT, GT, LEAF, HEAD)                                                                                   \
   do {                                                                                                                 \
     const GateView<GT> gv = MakeGateView<GT>(gates, gates_f, H, K);                                                    \

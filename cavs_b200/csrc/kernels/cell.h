@@ -42,9 +42,10 @@ int LaunchCellBwd(void* dA, void* ZF, bool bf16, float* mailbox, float* dB_part,
                   const float* state, const int32_t* child, const int32_t* parent, int n_total, int off, int rows, int H,
                   int K, bool leaf, cudaStream_t st, const float* dz = nullptr, const float* Wc = nullptr, int C = 0,
                   const void* A = nullptr, const int32_t* a_row = nullptr, const float* bias = nullptr,
-                  const int32_t* child_state = nullptr, const void* gates_f = nullptr);
+                  const int32_t* child_state = nullptr, const void* gates_f = nullptr, int* status = nullptr);
 // child_state (optional, [K, n_total]): rows of `state` holding the children's cell state when they differ from
 // the children's tensor ids (leaf states shared per token); the mailbox is always addressed by `child`.
+// status (optional): device word raised when a bounded wait of the streaming form expires.
 // A / a_row / bias (optional, leaf levels only): recompute i, o, u and c from the input-projection rows instead of
 // reading the saved gates and cell state (A in the same precision as dA).
 // dz / Wc / C (optional): rebuild d(pushed h) = dz[t,:] . Wc inside the kernel instead of reading dOut

@@ -92,6 +92,22 @@ def test_bf16_parity_with_oracle(cuda):
         assert rel_err(out[k], refbf[k]) < 5e-3, k      # same rounding points as the oracle's bf16 mode
 
 
+@pytest.mark.parametrize("H,K", [(512, 2), (1024, 2), (512, 3)])
+def test_bf16_wide_hidden_parity_with_oracle(cuda, H, K):
+    # Hidden sizes of 512 and more: the internal levels' cell gradient runs as the streaming kernel (rows staged in
+    # shared memory by bulk copies); roots, missing children (K = 3 over binary trees) and ragged levels included.
+    E, V, C = 64, 200, 5
+    parents, tok_job, label_job = make_tree_batch(77 + H + K, 10, 2, 12, V, C)
+    params = make_params(13, H, E, V, C, scale=0.04, bias_scale=0.02)
+    s, eng, out, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, K=K, bf16=True)
+    refbf = _oracle(s, tok_job, label_job, params, H, E, V, C, K=K, bf16=True)
+    for k in KEYS:
+        assert rel_err(out[k], refbf[k]) < 5e-3, k
+    s2, eng2, again, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, K=K, bf16=True)
+    for k in KEYS:
+        assert np.array_equal(out[k], again[k]), k          # deterministic
+
+
 @pytest.mark.parametrize("K,arity", [(1, None), (4, 4)])
 def test_other_slot_counts_fp32(cuda, K, arity):
     H, E, V, C = 24, 16, 50, 4
