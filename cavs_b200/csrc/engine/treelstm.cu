@@ -157,7 +157,6 @@ struct cavs_treelstm {
   Stager* stager = nullptr;
   bool slot_used[2] = {false, false};
   std::vector<int32_t> pending_xrows;   // consumed by the next load_batch
-  int reserve_sms = 0;             // SMs the weight-gradient products leave to a concurrent all-reduce (set by step)
   bool explicit_promote = false;   // set by cavs_treelstm_promote: forward() then leaves the staged batch alone
   std::vector<int32_t> bucket, slot_of_token, leaf_count, link_bucket;
   // ---- optional per-kernel-class timing (cavs_treelstm_profile) ----
@@ -1116,8 +1115,6 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
     CAVS_CUDA(cudaMemsetAsync(g, 0, static_cast<size_t>(compact ? bt.n_xrows : e->cfg.vocab) * E * sizeof(float), st));
     if ((rc = cavs_scatter_rows(g, compact ? bt.seg_pos : bt.seg_tok, e->dX, n_tok, static_cast<size_t>(E) * sizeof(float), st))) return rc;
     CAVS_CUDA(cudaEventRecord(e->emb_ready, st));
-    // From here on the embedding block's all-reduce may run on the communication stream: leave it a few SMs.
-    ReserveSms(e->reserve_sms);
     if ((rc = Gemm(e, g + e->OffW(), 4 * H, 0, e->X, E, true, e->dAtok, 4 * H, false, E, 4 * H, n_tok, true, st))) return rc;
   }
   // first row of the per-vertex weight-gradient products: the first internal row, or with level 1 by token the
@@ -1154,7 +1151,6 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
          LaunchColumnSum(g + e->OffB(), e->dA, e->bf16, 4 * H, n, 4 * H, e->col_scratch, st, H, 0, 3, 2, 1));
   }
   (void)rc;
-  ReserveSms(0);
   CAVS_CUDA(cudaEventRecord(e->slot_done[e->active], st));
   e->slot_used[e->active] = true;
   return CAVS_OK;
@@ -1224,16 +1220,8 @@ extern "C" int cavs_treelstm_step(cavs_treelstm* e, cavs_comm* comm, int optimiz
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int world = 1;
   if (comm) cavs_comm_info(comm, nullptr, &world, nullptr);
-  static const int reserve = [] {
-    const char* env = std::getenv("CAVS_COMM_RESERVE_SMS");
-    return env ? std::max(0, std::min(64, std::atoi(env))) : 0;
-  }();
-  e->reserve_sms = world > 1 ? reserve : 0;
   if (int rc = cavs_treelstm_forward(e, stream)) return rc;
-  const int rc_bwd = cavs_treelstm_backward(e, stream);
-  e->reserve_sms = 0;
-  ReserveSms(0);   // also on an error return out of the middle of backward
-  if (rc_bwd) return rc_bwd;
+  if (int rc = cavs_treelstm_backward(e, stream)) return rc;
   const size_t n_all = e->ParamCount(), n_emb = e->OffW();
   // With exchange rows the embedding block holds one gradient row per listed table row: that is what travels and what
   // the update walks.  Every rank must have been given the same list, or the ranks' reductions differ in size.

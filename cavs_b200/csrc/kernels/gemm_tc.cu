@@ -279,7 +279,7 @@ int GemmBf16Mapped(const GemmBf16MappedArgs& g, cudaStream_t stream) {
     p.tma_store = 1;
   }
   const long long n_work = static_cast<long long>((g.n + bn - 1) / bn) * ((g.m + tile_m - 1) / tile_m) * eff_splits;
-  dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, PersistentGridCap())));
+  dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
   int rc = tall_wgrad  ? Launch<256, 1, 1, 2>(ma, mb, *mc, p, grid, stream)
            : tall_dgrad ? (bmap->major == tc::kMajorK ? Launch<256, 0, 0, 2>(ma, mb, *mc, p, grid, stream)
                                                       : Launch<256, 0, 1, 2>(ma, mb, *mc, p, grid, stream))
@@ -360,7 +360,7 @@ int GemmBf16MappedDual(const GemmBf16MappedArgs& g0, const GemmBf16MappedArgs& g
   const CUtensorMap& ma1 = *reinterpret_cast<const CUtensorMap*>(g1.a->bytes);
   const CUtensorMap& mb0 = *reinterpret_cast<const CUtensorMap*>(bmaps[0]->bytes);
   const CUtensorMap& mb1 = *reinterpret_cast<const CUtensorMap*>(bmaps[1]->bytes);
-  dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, PersistentGridCap())));
+  dim3 grid(static_cast<unsigned>(std::min<long long>(n_work, SmCount())));
 #define CAVS_DUAL(BN)                                                                                                            \
   (kmajor_b ? LaunchDual<BN, 0, 0>(ma0, mb0, *mcs[0], ps[0], ma1, mb1, *mcs[1], ps[1], grid, stream)                            \
             : LaunchDual<BN, 0, 1>(ma0, mb0, *mcs[0], ps[0], ma1, mb1, *mcs[1], ps[1], grid, stream))

@@ -77,12 +77,6 @@ inline thread_local int g_chain_early = 0;
 inline void ChainHint(bool release_early) { g_chain_early = release_early ? 1 : 0; }
 inline int ChainEarly() { return g_chain_early; }
 
-// SMs the persistent GEMM launches of this host thread leave free (0: none): a collective that runs on another stream
-// beside them needs a few SMs for its own CTAs, which a grid of one CTA per SM would otherwise hold until it retires.
-inline thread_local int g_sm_reserve = 0;
-inline void ReserveSms(int n) { g_sm_reserve = n > 0 ? n : 0; }
-inline int PersistentGridCap() { return std::max(1, SmCount() - g_sm_reserve); }
-
 template <typename... KArgs, typename... Args>
 inline cudaError_t LaunchChained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg{};
