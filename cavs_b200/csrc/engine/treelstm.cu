@@ -857,7 +857,7 @@ extern "C" int cavs_treelstm_forward(cavs_treelstm* e, void* stream) {
       ChainHint(rows <= kChainSmallRows);
       PROF(e, kProfCellFwd, static_cast<double>(rows) * (H * (elt * (4 + 4 * K + 3 + K) + 4.0 * (K + 2)) + 4), st,
            LaunchCellFwd(e->state, e->gates, e->A, e->PQT, nullptr, e->bf16, B, bt.child_st, bt.tok_slot, nt, off, rows, H, K, false, st,
-                         true, e->cfg.max_vertices, e->gates_f));
+                         true, e->cfg.max_vertices, e->gates_f, e->Status()));
       continue;
     }
     // Chained launches: a kernel releases its successor early when that successor is a GEMM (one CTA per

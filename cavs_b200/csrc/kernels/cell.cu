@@ -653,6 +653,141 @@ CellBwdStream(__nv_bfloat16* __restrict__ dA, __nv_bfloat16* __restrict__ ZF, fl
   }
 }
 
+// The forward cell of a level whose children are all leaves with per-token states (CellFwd with tok_base >= 0), bf16
+// configuration, as a streaming kernel on the scheme of CellBwdStream: per row the producer thread fetches the input
+// projection row and, per child, the child token's product row and cell state into shared memory, two rows ahead; the
+// bias sits in shared memory for the CTA's life.  Same expressions in the same order as CellFwd.
+template <int K>
+__global__ void __launch_bounds__(kBwdThreads, 2)
+CellFwdTokStream(float* __restrict__ state, __half* __restrict__ gates, __half* __restrict__ gates_f, long long pitch3, long long pitch_f,
+                 const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ P, const float* __restrict__ bias,
+                 const int32_t* __restrict__ child, const int32_t* __restrict__ a_row, int n_total, int off, int rows, int H,
+                 int tok_base, int chain_early, int* __restrict__ status) {
+  ChainRelease(chain_early);
+  ChainAcquire();
+  extern __shared__ __align__(128) unsigned char fwd_smem[];
+  __shared__ __align__(8) unsigned long long full_bar[kBwdStages], empty_bar[kBwdStages];
+  // stage: header (child rows) | A row (4H bf16) | K product rows (4H bf16 each) | K cell-state rows (H floats each)
+  const int o_a = 64, o_p = o_a + 8 * H, o_c = o_p + K * 8 * H, stage_bytes = o_c + K * 4 * H;
+  float* s_bias = reinterpret_cast<float*>(fwd_smem);                           // [4H]: i | f | u | o
+  unsigned char* stages = fwd_smem + static_cast<size_t>(16) * H;
+  const int tid = threadIdx.x;
+  const int tpr = H / 4;
+  const bool consumer = tid < tpr;
+  const bool producer = tid == kBwdConsumers;
+  for (int i = tid; i < 4 * H; i += kBwdThreads) s_bias[i] = bias[i];
+  if (tid == 0) {
+    for (int s = 0; s < kBwdStages; ++s) {
+      bulk::MbarInit(bulk::SmemAddr(&full_bar[s]), 1);
+      bulk::MbarInit(bulk::SmemAddr(&empty_bar[s]), tpr);
+    }
+    bulk::FenceMbarInit();
+  }
+  __syncthreads();
+  const int n_my = blockIdx.x < rows ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  if (producer) {
+    int ar = 0, ch[K];
+    auto fetch = [&](int i) {
+      const size_t t = static_cast<size_t>(off) + blockIdx.x + static_cast<size_t>(i) * gridDim.x;
+      ar = a_row ? __ldg(a_row + t) : static_cast<int>(t);
+#pragma unroll
+      for (int c = 0; c < K; ++c) ch[c] = __ldg(child + static_cast<size_t>(c) * n_total + t);
+    };
+    if (n_my > 0) fetch(0);
+    int issued = 0;
+    for (int i = 0; i < n_my; ++i) {
+      const int s = i % kBwdStages;
+      if (i >= kBwdStages && !bulk::MbarWait(bulk::SmemAddr(&empty_bar[s]), ((i / kBwdStages) - 1) & 1)) {
+        if (status != nullptr) atomicExch(status, 1);
+        break;
+      }
+      const int my_ar = ar;
+      int my_ch[K];
+#pragma unroll
+      for (int c = 0; c < K; ++c) my_ch[c] = ch[c];
+      if (i + 1 < n_my) fetch(i + 1);
+      unsigned char* st = stages + static_cast<size_t>(s) * stage_bytes;
+      int32_t* hdr = reinterpret_cast<int32_t*>(st);
+      uint32_t bytes = 8u * H;
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        hdr[c] = my_ch[c];
+        if (my_ch[c] >= 0) bytes += 12u * H;
+      }
+      const uint32_t bar = bulk::SmemAddr(&full_bar[s]);
+      bulk::MbarExpectTx(bar, bytes);
+      bulk::Load(bulk::SmemAddr(st + o_a), A + static_cast<size_t>(my_ar) * 4 * H, 8u * H, bar);
+#pragma unroll
+      for (int c = 0; c < K; ++c)
+        if (my_ch[c] >= 0) {
+          bulk::Load(bulk::SmemAddr(st + o_p + c * 8 * H), P + static_cast<size_t>(my_ch[c] - tok_base) * 4 * H, 8u * H, bar);
+          bulk::Load(bulk::SmemAddr(st + o_c + c * 4 * H), state + static_cast<size_t>(my_ch[c]) * 2 * H + H, 4u * H, bar);
+        }
+      issued = i + 1;
+    }
+    if (issued < n_my || (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0)) {
+      for (int i = max(0, issued - kBwdStages); i < issued; ++i)
+        bulk::MbarWait(bulk::SmemAddr(&full_bar[i % kBwdStages]), (i / kBwdStages) & 1);
+    }
+  } else if (consumer) {
+    const int j = tid * 4;
+    const Vec<4> bi = LoadF<4>(s_bias + j), bf = LoadF<4>(s_bias + H + j), bu = LoadF<4>(s_bias + 2 * H + j), bo = LoadF<4>(s_bias + 3 * H + j);
+    for (int i = 0; i < n_my; ++i) {
+      const int s = i % kBwdStages;
+      if (!bulk::MbarWait(bulk::SmemAddr(&full_bar[s]), (i / kBwdStages) & 1)) {
+        if (status != nullptr) atomicExch(status, 1);
+        break;
+      }
+      const size_t t = static_cast<size_t>(off) + blockIdx.x + static_cast<size_t>(i) * gridDim.x;
+      const unsigned char* st = stages + static_cast<size_t>(s) * stage_bytes;
+      const int32_t* hdr = reinterpret_cast<const int32_t*>(st);
+      const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(st + o_a) + j;
+      const Vec<4> ai = LoadF<4>(a), ao = LoadF<4>(a + H), au = LoadF<4>(a + 2 * H), af = LoadF<4>(a + 3 * H);
+      Vec<4> pi = Zero<4>(), po = Zero<4>(), pu = Zero<4>(), q[K], cch[K];
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        if (hdr[c] >= 0) {
+          const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(st + o_p + c * 8 * H) + j;
+          const Vec<4> xi = LoadF<4>(p), xo = LoadF<4>(p + H), xu = LoadF<4>(p + 2 * H);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { pi.v[e] += xi.v[e]; po.v[e] += xo.v[e]; pu.v[e] += xu.v[e]; }
+          q[c] = LoadF<4>(p + 3 * H);
+          cch[c] = LoadF<4>(reinterpret_cast<const float*>(st + o_c + c * 4 * H) + j);
+        } else {
+          q[c] = Zero<4>();
+          cch[c] = Zero<4>();
+        }
+      }
+      MbarArrive(bulk::SmemAddr(&empty_bar[s]));
+      Vec<4> gi, go, gu, cc, hh;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        gi.v[e] = SigmoidT<true>((ai.v[e] + pi.v[e]) + bi.v[e]);
+        go.v[e] = SigmoidT<true>((ao.v[e] + po.v[e]) + bo.v[e]);
+        gu.v[e] = TanhT<true>((au.v[e] + pu.v[e]) + bu.v[e]);
+        cc.v[e] = gi.v[e] * gu.v[e];
+      }
+      __half* g = gates + t * pitch3 + j;
+      __half* gfp = gates_f + t * pitch_f + j;
+#pragma unroll
+      for (int c = 0; c < K; ++c) {
+        Vec<4> gf;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          gf.v[e] = SigmoidT<true>((af.v[e] + q[c].v[e]) + bf.v[e]);
+          cc.v[e] = cc.v[e] + gf.v[e] * cch[c].v[e];
+        }
+        StoreStream<4>(gfp + c * H, gf);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) hh.v[e] = go.v[e] * TanhT<true>(cc.v[e]);
+      StoreStream<4>(g, gi); StoreStream<4>(g + H, go); StoreStream<4>(g + 2 * H, gu);
+      Store<4>(state + t * 2 * H + j, hh);
+      Store<4>(state + t * 2 * H + H + j, cc);
+    }
+  }
+}
+
 // mailbox[child_c(t)].h = ds[b] + dq[b,c]: Scatter(Child=c) of the child-state gradient
 // (cavs/backend/op_decl_graphop.cc:25-41).
 template <int K, int V>
@@ -1040,11 +1175,36 @@ GateView<GT> MakeGateView(const void* gates, const void* gates_f, int H, int K) 
 
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
-                  bool store_leaf_gates, int tok_base, void* gates_f) {
+                  bool store_leaf_gates, int tok_base, void* gates_f, int* status) {
   CAVS_REQUIRE(tok_base < 0 || (!leaf && P != nullptr), CAVS_ERR_BAD_ARG, "treelstm_cell_fwd: per-token products apply to an internal level");
   if (int rc = CheckCommon("treelstm_cell_fwd", rows, H, K)) return rc;
   if (rows == 0) return CAVS_OK;
   const int v = VecWidth(H);
+  // The by-token level of the bf16 configuration streams its rows through shared memory (CellFwdTokStream).
+  static const bool stream_ok = [] { const char* e = std::getenv("CAVS_CELL_FWD_STREAM"); return !(e != nullptr && e[0] == '0'); }();
+  if (stream_ok && preact_bf16 && tok_base >= 0 && !leaf && H % 8 == 0 && H / 4 <= kBwdConsumers && H / 4 >= 128) {
+    const GateView<__half> gv = MakeGateView<__half>(gates, gates_f, H, K);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(gates) | reinterpret_cast<uintptr_t>(gv.f) |
+                           reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(P) | reinterpret_cast<uintptr_t>(bias)) & 15u) == 0;
+    const size_t smem = static_cast<size_t>(16) * H + static_cast<size_t>(kBwdStages) * (64 + 8 * H + static_cast<size_t>(K) * 12 * H);
+    if (aligned && smem <= 100 * 1024) {
+      const int sgrid = static_cast<int>(std::min<long long>(rows, 2LL * SmCount()));
+      DISPATCH_KV(K, 4, {
+        (void)V;
+        static bool configured[kMaxDevices] = {};
+        const int dev = CurrentDevice();
+        if (!configured[dev]) {
+          CAVS_CUDA(cudaFuncSetAttribute(CellFwdTokStream<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+          configured[dev] = true;
+        }
+        LaunchChained(CellFwdTokStream<K>, dim3(sgrid), dim3(kBwdThreads), smem, st, state, static_cast<__half*>(gates), gv.f, gv.pitch3,
+                      gv.pitch_f, static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(P), bias, child, a_row, n_total, off,
+                      rows, H, tok_base, ChainEarly(), status);
+      });
+      CAVS_LAUNCH_CHECK("treelstm_cell_fwd (streaming)");
+      return CAVS_OK;
+    }
+  }
   const int grid = GridForElems(static_cast<size_t>(rows) * (H / v), kThreads);
   DISPATCH_KV(K, v, {
     if (preact_bf16) {

@@ -21,7 +21,7 @@ int LaunchGatherChildH(void* S, void* HK, bool bf16, const float* state, const i
 // a_row (optional): [n_total] row of A for each vertex (A then holds one row per distinct token).
 int LaunchCellFwd(float* state, void* gates, const void* A, const void* P, const void* Q, bool preact_bf16, const float* bias,
                   const int32_t* child, const int32_t* a_row, int n_total, int off, int rows, int H, int K, bool leaf, cudaStream_t st,
-                  bool store_leaf_gates = true, int tok_base = -1, void* gates_f = nullptr);
+                  bool store_leaf_gates = true, int tok_base = -1, void* gates_f = nullptr, int* status = nullptr);
 // gates_f (here and in LaunchCellBwd): NULL = the saved gates are one array [n_total, (3+K)H] (i|o|u|f_0..f_{K-1});
 // else `gates` is [n_total, 3H] (i|o|u) and gates_f [n_total, K, H] holds the forget gates -- the layout the gate
 // products write when their epilogue finishes the gates (bf16 mode).
