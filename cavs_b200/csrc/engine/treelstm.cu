@@ -34,6 +34,7 @@
 
 #include "abi_common.h"
 #include "host/sched_handle.h"
+#include "host/threads.h"
 #include "kernels/cell.h"
 #include "kernels/gemm.h"
 #include "kernels/launch.h"
@@ -184,14 +185,10 @@ namespace {
 size_t Align(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 // Host-side packing of a batch's tables runs next to the device step of the previous batch; its loops over vertices
-// that touch disjoint outputs are split over a few threads (CAVS_HOST_THREADS, default min(cores, 4); short loops
-// stay on the caller's thread).
+// that touch disjoint outputs are split over a few threads (CAVS_HOST_THREADS, default: the host's threads shared out
+// among its GPUs, at most 8; short loops stay on the caller's thread).
 int PackThreads() {
-  static const int n = [] {
-    const char* env = std::getenv("CAVS_HOST_THREADS");
-    if (env) return std::max(1, std::min(16, std::atoi(env)));
-    return static_cast<int>(std::max(1u, std::min(std::thread::hardware_concurrency(), 4u)));
-  }();
+  static const int n = HostThreadBudget(8);
   return n;
 }
 template <typename F>

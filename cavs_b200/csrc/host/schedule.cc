@@ -6,6 +6,7 @@
 #include <thread>
 
 #include "abi_common.h"
+#include "host/threads.h"
 
 namespace cavs_b200 {
 
@@ -27,12 +28,7 @@ void ParallelFor(int n, int threads, F fn) {
 }
 
 int HostThreads() {
-  static int n = [] {
-    const char* env = std::getenv("CAVS_HOST_THREADS");
-    if (env) return std::max(1, std::atoi(env));
-    const unsigned hw = std::thread::hardware_concurrency();
-    return static_cast<int>(std::max(1u, std::min(hw, 8u)));
-  }();
+  static const int n = HostThreadBudget(16);
   return n;
 }
 
