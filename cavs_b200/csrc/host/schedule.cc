@@ -27,6 +27,18 @@ void ParallelFor(int n, int threads, F fn) {
   for (auto& th : pool) th.join();
 }
 
+// v = n copies of value, the fill split over the host threads (the per-batch arrays are tens of megabytes together:
+// filled by one thread they cost as much as the scheduling itself).
+void ParallelAssign(std::vector<int32_t>* v, size_t n, int32_t value, int threads) {
+  v->resize(n);
+  int32_t* p = v->data();
+  constexpr size_t kBlock = 1 << 15;
+  const int blocks = static_cast<int>((n + kBlock - 1) / kBlock);
+  ParallelFor(blocks, std::min(threads, std::max(1, blocks / 4)), [=](int b0, int b1) {
+    std::fill(p + static_cast<size_t>(b0) * kBlock, p + std::min(n, static_cast<size_t>(b1) * kBlock), value);
+  });
+}
+
 int HostThreads() {
   static const int n = HostThreadBudget(16);
   return n;
@@ -55,11 +67,11 @@ int LevelSchedule::Load(const int32_t* parents, int batch, int max_len, int n_sl
   // vertex its level and its position inside the sample's list of that level.
   // local_[i*max_len + j] = level << 16 | position  (max_len <= 65535 enforced below), -1 if unscheduled.
   if (max_len > 65535) { *err = "schedule: max_len above 65535"; return CAVS_ERR_UNSUPPORTED; }
-  local_.assign(static_cast<size_t>(batch) * max_len, -1);
+  ParallelAssign(&local_, static_cast<size_t>(batch) * max_len, -1, threads);
   sample_len_.assign(batch, 0);
   sample_levels_.assign(batch, 0);
   // per-sample level counts, laid out [batch][max_len] lazily: only the first sample_levels_[i] entries are used
-  level_cnt_.assign(static_cast<size_t>(batch) * max_len, 0);
+  ParallelAssign(&level_cnt_, static_cast<size_t>(batch) * max_len, 0, threads);
   std::vector<int> first_error(batch, 0);
   ParallelFor(batch, threads, [&](int b0, int b1) {
     std::vector<int32_t> nchild(max_len), hits(max_len), cur(max_len), nxt(max_len);
@@ -155,12 +167,12 @@ int LevelSchedule::Load(const int32_t* parents, int batch, int max_len, int n_sl
   }
 
   // Phase C (parallel over samples): global tensor ids and tensor-id-space adjacency.
-  t2j_.assign(nz, 0);
-  j2t_.assign(nz, -1);
-  child_t_.assign(nz * n_slots, -1);
-  parent_t_.assign(nz, -1);
-  child_j_.assign(nz * n_slots, -1);
-  parent_j_.assign(nz, -1);
+  ParallelAssign(&t2j_, nz, 0, threads);
+  ParallelAssign(&j2t_, nz, -1, threads);
+  ParallelAssign(&child_t_, nz * n_slots, -1, threads);
+  ParallelAssign(&parent_t_, nz, -1, threads);
+  ParallelAssign(&child_j_, nz * n_slots, -1, threads);
+  ParallelAssign(&parent_j_, nz, -1, threads);
   std::vector<int> roots_per_thread_sample(batch, 0);
   ParallelFor(batch, threads, [&](int b0, int b1) {
     std::vector<int32_t> slot_used(max_len);
