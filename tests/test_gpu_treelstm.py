@@ -92,12 +92,19 @@ def test_bf16_parity_with_oracle(cuda):
         assert rel_err(out[k], refbf[k]) < 5e-3, k      # same rounding points as the oracle's bf16 mode
 
 
-@pytest.mark.parametrize("H,K", [(512, 2), (1024, 2), (512, 3)])
+@pytest.mark.parametrize("H,K", [(512, 2), (1024, 2), (512, 3), (512, 1), (512, 4)])
 def test_bf16_wide_hidden_parity_with_oracle(cuda, H, K):
-    # Hidden sizes of 512 and more: the internal levels' cell gradient runs as the streaming kernel (rows staged in
-    # shared memory by bulk copies); roots, missing children (K = 3 over binary trees) and ragged levels included.
+    # Hidden sizes of 512 and more: the internal levels' cell gradient and the by-token level's forward cell run as the
+    # streaming kernels (rows staged in shared memory by bulk copies); roots, missing children (K = 3 over binary
+    # trees), chains (K = 1), four-ary trees and ragged levels included.
     E, V, C = 64, 200, 5
-    parents, tok_job, label_job = make_tree_batch(77 + H + K, 10, 2, 12, V, C)
+    if K == 1:
+        parents = S.synth_chains(77 + H, 10, 2, 14)
+        lens = (parents == -1).argmax(1) + 1
+        tok_job = S.synth_zipf(78 + H, 1.1, V, int(lens.sum()))
+        label_job = S.synth_uniform_int(79 + H, C, int(lens.sum()))
+    else:
+        parents, tok_job, label_job = make_tree_batch(77 + H + K, 10, 2, 12, V, C, max_arity=4 if K == 4 else 2)
     params = make_params(13, H, E, V, C, scale=0.04, bias_scale=0.02)
     s, eng, out, _ = _run(cuda, parents, tok_job, label_job, params, H, E, V, C, K=K, bf16=True)
     refbf = _oracle(s, tok_job, label_job, params, H, E, V, C, K=K, bf16=True)
