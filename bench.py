@@ -484,18 +484,37 @@ def main():
 
     pinned_np = [tuple(t.numpy() for t in p) for p in pinned]
 
+    # Host pipeline of the end-to-end loop, three stations: level scheduling of batch i+2 on a thread of this script
+    # (cavs_sched_load releases the interpreter lock), table packing + upload of batch i+1 on the engine's helper thread,
+    # enqueueing of step i on this thread.  Two schedule objects alternate: the one being packed from is not written.
+    from concurrent.futures import ThreadPoolExecutor
+    sched_pool = ThreadPoolExecutor(max_workers=1)
+    host_scheds = [host_sched, S.Schedule()]
+    sched_job = {}
+
+    def schedule_ahead(i):
+        sched_job[i] = sched_pool.submit(host_scheds[i % 2].load, pinned_np[i % POOL][0])
+
     def stage(i):
-        """Host scheduling of batch i and the pinned upload of its tables, on the engine's helper thread: it runs beside
-        this thread's enqueueing of the step in flight; the next step waits for it and promotes the staged tables."""
+        """Packing and pinned upload of batch i's tables on the engine's helper thread, from the schedule the scheduling
+        thread has finished (started one step earlier); then batch i+1's scheduling starts.  Both run beside this
+        thread's enqueueing of the step in flight."""
         par, tok, lab = pinned_np[i % POOL]
         t0 = time.perf_counter()
-        eng.stage_async(host_sched, par, tok, lab, loss_rows=pool[i % POOL][3], exchange_rows=xrows[i % POOL])
+        if i not in sched_job:
+            schedule_ahead(i)
+        sched_job.pop(i).result()
+        eng.stage_async(host_scheds[i % 2], None, tok, lab, loss_rows=pool[i % POOL][3], exchange_rows=xrows[i % POOL])
+        schedule_ahead(i + 1)
         host_ms[0] += (time.perf_counter() - t0) * 1e3
         host_ms[1] += 1
 
     def stage_time():
         """What one batch's host scheduling + packing + upload costs when run synchronously (reported, not timed in e2e)."""
         par, tok, lab = pinned_np[0]
+        for job in list(sched_job.values()):     # the scheduling thread is idle from here on
+            job.result()
+        sched_job.clear()
         eng.stage_wait()
         t0 = time.perf_counter()
         eng.stage(host_sched, par, tok, lab, loss_rows=pool[0][3], exchange_rows=xrows[0])
@@ -715,7 +734,9 @@ def main():
                             embedding_gradient=("rows the global batch touches (mean %d of %d), listed with the batch"
                                                 % (int(np.mean([len(x) for x in xrows])), wl["vocab"])) if sparse else "dense block"),
                 e2e=dict(value=e2e_value, unit="trees/s", ms_per_step=ms_e2e / args.steps, h2d_bytes_per_step=h2d, d2h_bytes_per_step=8,
-                         host_stage_ms=host_stage_sync_ms, host_stage_mode="helper thread of the engine (cavs_treelstm_promote, then cavs_treelstm_stage_async beside the step's enqueueing)",
+                         host_stage_ms=host_stage_sync_ms, host_stage_mode=("three stations: cavs_sched_load of batch i+2 on a thread of the script, packing + upload of batch "
+                                          "i+1 on the engine's helper thread (cavs_treelstm_promote, cavs_treelstm_stage_async), "
+                                          "enqueueing of step i"),
                          loss_read="every step into a pinned slot, collected two steps later"),
                 gpu_launches=int(launches), gpu_launches_per_step=int(launches) // max(args.steps, 1), loss_sum=loss_dev,
                 global_loss_sum=global_loss, comm=comm_info, optimizer_ms=optimizer_ms, clocks=clocks, roofline=roofline,

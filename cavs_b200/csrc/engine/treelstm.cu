@@ -1156,13 +1156,16 @@ extern "C" int cavs_treelstm_backward(cavs_treelstm* e, void* stream) {
 extern "C" int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
                                    const int32_t* tok_job, const int32_t* label_job, int loss_rows) {
   CAVS_REQUIRE(e && s, CAVS_ERR_BAD_ARG, "treelstm_stage: null handle");
-  if (int rc = cavs_sched_load(s, parents, batch, max_len, e->cfg.n_slots)) return rc;
+  // parents == NULL: `s` already holds the batch's schedule (the caller ran cavs_sched_load itself, e.g. on a thread
+  // of its own beside the packing of the previous batch); only the tables are packed and uploaded
+  if (parents != nullptr)
+    if (int rc = cavs_sched_load(s, parents, batch, max_len, e->cfg.n_slots)) return rc;
   return cavs_treelstm_load_batch(e, s, tok_job, label_job, loss_rows, nullptr);
 }
 
 extern "C" int cavs_treelstm_stage_async(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
                                          const int32_t* tok_job, const int32_t* label_job, int loss_rows) {
-  CAVS_REQUIRE(e && s && parents, CAVS_ERR_BAD_ARG, "treelstm_stage_async: null pointer");
+  CAVS_REQUIRE(e && s, CAVS_ERR_BAD_ARG, "treelstm_stage_async: null handle");
   if (int rc = cavs_treelstm_stage_wait(e)) return rc;   // one request at a time
   if (e->stager == nullptr) {
     e->stager = new cavs_treelstm::Stager();

@@ -105,11 +105,13 @@ class TreeLSTM:
     def stage_async(self, sched: Schedule, parents: np.ndarray, tok_job, label_job, loss_rows: int = 0, exchange_rows=None) -> None:
         """stage() on the engine's helper thread: returns at once; the next step() / forward() waits for it.  The arrays
         are kept alive here until then."""
-        assert parents.dtype == np.int32 and parents.flags.c_contiguous
+        # parents None: `sched` was loaded by the caller (Schedule.load, possibly on another thread); only the packing runs
+        assert parents is None or (parents.dtype == np.int32 and parents.flags.c_contiguous)
         if exchange_rows is not None:
             self.set_exchange_rows(exchange_rows)      # copied by the library before it returns
         self._staging = (sched, parents, tok_job, label_job)
-        check(lib().cavs_treelstm_stage_async(self._h, sched._h, ptr(parents), parents.shape[0], parents.shape[1],
+        check(lib().cavs_treelstm_stage_async(self._h, sched._h, ptr(parents), parents.shape[0] if parents is not None else 0,
+                                              parents.shape[1] if parents is not None else 0,
                                               ptr(tok_job) if self.cfg.vocab else ptr(None),
                                               ptr(label_job) if self.cfg.classes else ptr(None), loss_rows))
 

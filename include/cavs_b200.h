@@ -340,7 +340,9 @@ CAVS_API int cavs_treelstm_load_batch(cavs_treelstm* e, const cavs_sched* s, con
  * tensor (cavs/backend/op_impl_embedding_lookup.cu:91-103). */
 CAVS_API int cavs_treelstm_set_exchange_rows(cavs_treelstm* e, const int32_t* rows, int n_rows);
 /* Level scheduling of a batch (cavs_sched_load into `s`, with the engine's slot count) and cavs_treelstm_load_batch
- * in one call: everything the host does per batch before the device step. */
+ * in one call: everything the host does per batch before the device step.  parents == NULL (here and in
+ * cavs_treelstm_stage_async): `s` already holds the batch's schedule -- the caller ran cavs_sched_load itself, for
+ * instance on a thread of its own while the previous batch was being packed -- and only the tables are packed. */
 CAVS_API int cavs_treelstm_stage(cavs_treelstm* e, cavs_sched* s, const int32_t* parents, int batch, int max_len,
                                  const int32_t* tok_job, const int32_t* label_job, int loss_rows);
 /* The same on a helper thread of the engine: returns at once, so that the caller's thread can enqueue the step of the

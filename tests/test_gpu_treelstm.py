@@ -525,6 +525,28 @@ def test_staging_on_the_helper_thread_gives_the_same_steps(cuda):
     for mode in ("async", "promote"):
         for (la, ga), (lb, gb) in zip(run(mode), want):
             assert la == lb and np.array_equal(ga, gb), mode
+
+    # the caller schedules on a thread of its own (two schedule objects alternate) and hands the engine a loaded
+    # schedule: only the packing runs on the helper thread
+    import threading
+    eng = TreeLSTM(H, E, V, C, **cap)
+    eng.set_params(params)
+    keep = [(np.ascontiguousarray(p), np.ascontiguousarray(t), np.ascontiguousarray(l)) for p, t, l in batches]
+    scheds = [S.Schedule(), S.Schedule()]
+    scheds[0].load(keep[0][0])
+    eng.stage_async(scheds[0], None, keep[0][1], keep[0][2])
+    worker = threading.Thread(target=scheds[1].load, args=(keep[1][0],))
+    worker.start()
+    for i in range(len(keep)):
+        eng.promote()
+        if i + 1 < len(keep):
+            worker.join()
+            eng.stage_async(scheds[(i + 1) % 2], None, keep[i + 1][1], keep[i + 1][2])
+            if i + 2 < len(keep):
+                worker = threading.Thread(target=scheds[i % 2].load, args=(keep[i + 2][0],))
+                worker.start()
+        eng.step(None, eng.OPT_SGD, None, 0.05)
+        assert eng.read_loss() == want[i][0] and np.array_equal(eng.grads.cpu().numpy(), want[i][1]), i
     eng = TreeLSTM(H, E, V, C, **cap)
     eng.set_params(params)
     bad = np.array([[5, 5, -1, -1]], np.int32)             # parent index out of range
